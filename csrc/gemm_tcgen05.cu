@@ -1,0 +1,497 @@
+// Persistent, warp-specialised bf16 GEMM for sm_100a built directly on tcgen05.mma + TMEM + TMA.
+//
+//   C[b] = alpha * act(A[b] * B[b]^T-or-not) + beta * Aux[b]
+//
+// * Operands are bf16 in global memory.  Each operand is either K-major (reduction dimension
+//   contiguous) or MN-major (row/column dimension contiguous), so the forward (X*W^T), the
+//   data-gradient (dY*W) and the weight-gradient (dY^T*X) products of a linear layer all run
+//   without a transpose pass.
+// * One CTA per SM, 192 threads: warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner,
+//   warps 2..5 = epilogue (one TMEM lane quarter each).  The fp32 accumulator lives in TMEM
+//   and is double buffered (2 x BN columns) so the epilogue of tile i overlaps the main loop
+//   of tile i+1.
+// * Work is either split at tile granularity (plain stores) or as an even stream-K partition of
+//   all (tile, k-block) units with fp32 `red.global.add` accumulation into a zero-initialised
+//   (or gradient-accumulating) output, which removes wave quantisation for the weight-gradient
+//   shapes (few output tiles, very long K).
+// * Every mbarrier wait is bounded; a timeout records an error and unwinds through the normal
+//   teardown (TMEM is released).
+//
+// What the reference does for the same products: cuBLAS through torch::linear / mm / bmm
+// (cc/src/tyr.cpp:1003-1036, 1267-1300) followed by separate elementwise kernels.
+#include "common.cuh"
+#include <cstdio>
+#include <mutex>
+
+namespace tyr {
+
+constexpr int BM = 128;
+constexpr int BK = 64;        // 64 bf16 = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+
+struct GemmParams {
+  int M, N, K, batch;
+  void* C;
+  const __nv_bfloat16* aux;
+  long long ldc, ldaux, sC, sAux;
+  float alpha, beta;
+  int act;        // 0 none, 1 relu(x)^2, 2 relu, 3 acc * 2*sqrt(aux)
+  int out_mode;   // 0 bf16 store, 1 fp32 store, 2 fp32 atomic add (stream-K)
+  int* err;
+};
+
+template <int BN, int STAGES>
+struct __align__(1024) GemmSmem {
+  uint8_t a[STAGES][BM * BK * 2];
+  uint8_t b[STAGES][BN * BK * 2];
+  uint64_t full[STAGES];
+  uint64_t empty[STAGES];
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+__device__ __forceinline__ float apply_act(float v, int act) {
+  if (act == 1) {
+    float r = fmaxf(v, 0.f);
+    return r * r;
+  } else if (act == 2) {
+    return fmaxf(v, 0.f);
+  }
+  return v;
+}
+
+template <int BN, int STAGES, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(192, 1)
+gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
+                         const __grid_constant__ CUtensorMap tmB, GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  using Smem = GemmSmem<BN, STAGES>;
+  Smem& s = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                     ~static_cast<uintptr_t>(1023));
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int tiles_m = (p.M + BM - 1) / BM;
+  const int tiles_n = (p.N + BN - 1) / BN;
+  const int num_kb = (p.K + BK - 1) / BK;
+  const long long tiles = static_cast<long long>(tiles_m) * tiles_n * p.batch;
+
+  // Work range for this CTA, in (tile, k-block) units.
+  long long unit_begin, unit_end;
+  if (p.out_mode == 2) {
+    const long long units = tiles * num_kb;
+    unit_begin = units * blockIdx.x / gridDim.x;
+    unit_end = units * (blockIdx.x + 1) / gridDim.x;
+  } else {
+    // tile-granular, strided assignment expressed in the same unit space
+    unit_begin = 0;
+    unit_end = 0;
+  }
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < STAGES; ++i) {
+      mbar_init(&s.full[i], 1);
+      mbar_init(&s.empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s.acc_full[i], 1);
+      mbar_init(&s.acc_empty[i], 4);  // one arrival per epilogue warp
+    }
+    s.abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&s.tmem_base, 2 * BN);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = s.tmem_base;
+
+  constexpr uint32_t kStageBytes = BM * BK * 2 + BN * BK * 2;
+
+  // Segment iterator shared by the three roles (identical sequence in each).
+  auto next_segment = [&](long long& cursor, long long& tile, int& kb0, int& kb1) -> bool {
+    if (p.out_mode == 2) {
+      if (cursor >= unit_end) return false;
+      tile = cursor / num_kb;
+      kb0 = static_cast<int>(cursor % num_kb);
+      long long remain = unit_end - cursor;
+      kb1 = static_cast<int>(min(static_cast<long long>(num_kb), kb0 + remain));
+      cursor += kb1 - kb0;
+      return true;
+    } else {
+      if (cursor >= tiles) return false;
+      tile = cursor;
+      kb0 = 0;
+      kb1 = num_kb;
+      cursor += gridDim.x;
+      return true;
+    }
+  };
+  auto decode_tile = [&](long long tile, int& bi, int& m0, int& n0) {
+    const int per_batch = tiles_m * tiles_n;
+    bi = static_cast<int>(tile / per_batch);
+    const int r = static_cast<int>(tile % per_batch);
+    // n fastest: concurrently resident tiles share A rows and keep B (weights) in L2.
+    m0 = (r / tiles_n) * BM;
+    n0 = (r % tiles_n) * BN;
+  };
+  const long long cursor0 = (p.out_mode == 2) ? unit_begin : static_cast<long long>(blockIdx.x);
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      tma_prefetch_desc(&tmA);
+      tma_prefetch_desc(&tmB);
+      long long cursor = cursor0, tile;
+      int kb0, kb1;
+      uint32_t it = 0;
+      bool ok = true;
+      while (ok && next_segment(cursor, tile, kb0, kb1)) {
+        int bi, m0, n0;
+        decode_tile(tile, bi, m0, n0);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const int st = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&s.empty[st], ph ^ 1, p.err, 100 + st)) {
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(&s.full[st], kStageBytes);
+          const int k0 = kb * BK;
+          if (!A_MN) {
+            tma_load_3d(s.a[st], &tmA, &s.full[st], k0, m0, bi);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BM / 64; ++c)
+              tma_load_3d(s.a[st] + c * (64 * BK * 2), &tmA, &s.full[st], m0 + c * 64, k0, bi);
+          }
+          if (!B_MN) {
+            tma_load_3d(s.b[st], &tmB, &s.full[st], k0, n0, bi);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c)
+              tma_load_3d(s.b[st] + c * (64 * BK * 2), &tmB, &s.full[st], n0 + c * 64, k0, bi);
+          }
+        }
+      }
+      if (!ok) {
+        s.abort_flag = 1;
+        // Drain copies that were issued: each issued stage completes its own full barrier.
+        for (uint32_t j = (it > STAGES ? it - STAGES : 0); j < it; ++j)
+          mbar_wait(&s.full[j % STAGES], (j / STAGES) & 1, nullptr, 0);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      constexpr uint32_t idesc = make_idesc_f16(1, BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      long long cursor = cursor0, tile;
+      int kb0, kb1;
+      uint32_t it = 0, seg = 0;
+      bool ok = true;
+      while (ok && next_segment(cursor, tile, kb0, kb1)) {
+        const uint32_t buf = seg & 1;
+        const uint32_t acc_ph = (seg >> 1) & 1;
+        if (!mbar_wait(&s.acc_empty[buf], acc_ph ^ 1, p.err, 200 + buf)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const int st = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&s.full[st], ph, p.err, 300 + st)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(s.a[st]);
+          const uint32_t b_addr = smem_u32(s.b[st]);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            uint64_t da, db;
+            if (!A_MN)
+              da = make_smem_desc_sw128(a_addr + k * (UMMA_K * 2), 16, 1024);
+            else
+              da = make_smem_desc_sw128(a_addr + k * (UMMA_K * 128), 64 * BK * 2, 1024);
+            if (!B_MN)
+              db = make_smem_desc_sw128(b_addr + k * (UMMA_K * 2), 16, 1024);
+            else
+              db = make_smem_desc_sw128(b_addr + k * (UMMA_K * 128), 64 * BK * 2, 1024);
+            umma_f16_ss(d_tmem, da, db, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&s.empty[st]);  // frees the smem stage once these MMAs retire
+        }
+        if (ok) umma_commit(&s.acc_full[buf]);
+        ++seg;
+      }
+      if (!ok) s.abort_flag = 1;
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue warps
+    const int quarter = warp & 3;  // TMEM lane quarter this warp may access
+    long long cursor = cursor0, tile;
+    int kb0, kb1;
+    uint32_t seg = 0;
+    bool ok = true;
+    while (ok && next_segment(cursor, tile, kb0, kb1)) {
+      int bi, m0, n0;
+      decode_tile(tile, bi, m0, n0);
+      const uint32_t buf = seg & 1;
+      const uint32_t acc_ph = (seg >> 1) & 1;
+      if (!mbar_wait(&s.acc_full[buf], acc_ph, p.err, 400 + buf)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const int row = m0 + quarter * 32 + lane;
+      const uint32_t t_row = tmem_base + buf * BN + (static_cast<uint32_t>(quarter * 32) << 16);
+      const bool row_ok = row < p.M;
+      const long long c_off = static_cast<long long>(bi) * p.sC + static_cast<long long>(row) * p.ldc;
+      const long long x_off =
+          static_cast<long long>(bi) * p.sAux + static_cast<long long>(row) * p.ldaux;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_row + c * 32, r);
+        tmem_wait_ld();
+        if (c == BN / 32 - 1) {
+          // accumulator fully read: hand the TMEM buffer back to the MMA warp
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&s.acc_empty[buf]);
+        }
+        const int col = n0 + c * 32;
+        if (!row_ok || col >= p.N) continue;
+        float v[32];
+        const bool full = (col + 32 <= p.N);
+        const bool use_aux = p.aux != nullptr && (p.beta != 0.f || p.act == 3);
+        float ax[32];
+        if (use_aux) {
+          const __nv_bfloat16* axp = p.aux + x_off + col;
+          if (full) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 u = *reinterpret_cast<const uint4*>(axp + q * 8);
+              float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y), f2 = unpack_bf16x2(u.z),
+                     f3 = unpack_bf16x2(u.w);
+              ax[q * 8 + 0] = f0.x; ax[q * 8 + 1] = f0.y; ax[q * 8 + 2] = f1.x; ax[q * 8 + 3] = f1.y;
+              ax[q * 8 + 4] = f2.x; ax[q * 8 + 5] = f2.y; ax[q * 8 + 6] = f3.x; ax[q * 8 + 7] = f3.y;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) ax[j] = (col + j < p.N) ? __bfloat162float(axp[j]) : 0.f;
+          }
+        }
+        if (p.act == 3) {
+          // gradient of y = relu(z)^2 given aux = y:  dz = acc * 2*sqrt(y)
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            v[j] = p.alpha * __uint_as_float(r[j]) * 2.f * sqrtf(fmaxf(ax[j], 0.f));
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = p.alpha * apply_act(__uint_as_float(r[j]), p.act);
+          if (use_aux) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] += p.beta * ax[j];
+          }
+        }
+        if (p.out_mode == 0) {
+          __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.C) + c_off + col;
+          if (full) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 u;
+              u.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
+              u.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
+              u.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
+              u.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
+              *reinterpret_cast<uint4*>(out + q * 8) = u;
+            }
+          } else {
+            #pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col + j < p.N) out[j] = __float2bfloat16(v[j]);
+          }
+        } else if (p.out_mode == 1) {
+          float* out = reinterpret_cast<float*>(p.C) + c_off + col;
+          if (full) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              *reinterpret_cast<float4*>(out + q * 4) =
+                  make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+          } else {
+            #pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col + j < p.N) out[j] = v[j];
+          }
+        } else {
+          float* out = reinterpret_cast<float*>(p.C) + c_off + col;
+          if (full) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(out + q * 4),
+                           "f"(v[q * 4]), "f"(v[q * 4 + 1]), "f"(v[q * 4 + 2]), "f"(v[q * 4 + 3])
+                           : "memory");
+          } else {
+            #pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col + j < p.N) atomicAdd(out + j, v[j]);
+          }
+        }
+      }
+      ++seg;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 2 * BN);
+  }
+}
+
+// ----------------------------------------------------------------------------------------
+// host side
+// ----------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) ==
+            cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  });
+  return fn;
+}
+
+// 3-D bf16 tensor map {inner, outer, batch} with a 128-byte swizzled box {64, box_outer, 1}.
+int make_tmap_bf16_3d(CUtensorMap* tm, const void* base, uint64_t inner, uint64_t outer,
+                      uint64_t batch, uint64_t ld_elems, uint64_t batch_stride_elems,
+                      uint32_t box_outer) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return -1;
+  cuuint64_t dims[3] = {inner, outer, batch};
+  cuuint64_t strides[2] = {ld_elems * 2, batch_stride_elems * 2};
+  if (batch <= 1) strides[1] = ld_elems * 2 * outer;
+  cuuint32_t box[3] = {64, box_outer, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
+}
+
+}  // namespace tyr
+
+extern "C" {
+
+struct TyrGemmArgs {
+  const void* A;
+  const void* B;
+  void* C;
+  const void* aux;
+  int M, N, K, batch;
+  long long lda, ldb, ldc, ldaux;   // leading strides in elements
+  long long sA, sB, sC, sAux;       // batch strides in elements
+  int a_mn, b_mn;                   // 0 = K-major (K contiguous), 1 = MN-major
+  int out_mode;                     // 0 bf16, 1 fp32, 2 fp32 atomic accumulate (stream-K)
+  int act;                          // 0 none, 1 relu^2, 2 relu
+  float alpha, beta;
+  int bn;                           // 128 or 256 (0 = choose)
+  int sm_count;                     // CTAs to launch (0 = all SMs)
+  int* err;
+  void* stream;
+};
+
+}  // extern "C"
+
+static int g_sm_count = 0;
+
+template <int BN, int STAGES, bool A_MN, bool B_MN>
+static int launch_gemm(const TyrGemmArgs& a, const CUtensorMap& tmA, const CUtensorMap& tmB) {
+  using namespace tyr;
+  auto kern = gemm_bf16_tcgen05_kernel<BN, STAGES, A_MN, B_MN>;
+  constexpr size_t smem = sizeof(GemmSmem<BN, STAGES>) + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(smem));
+    if (e != cudaSuccess) return 1000 + static_cast<int>(e);
+    configured = true;
+  }
+  GemmParams p;
+  p.M = a.M; p.N = a.N; p.K = a.K; p.batch = a.batch;
+  p.C = a.C; p.aux = reinterpret_cast<const __nv_bfloat16*>(a.aux);
+  p.ldc = a.ldc; p.ldaux = a.ldaux; p.sC = a.sC; p.sAux = a.sAux;
+  p.alpha = a.alpha; p.beta = a.beta; p.act = a.act; p.out_mode = a.out_mode; p.err = a.err;
+  const long long tiles = static_cast<long long>((a.M + BM - 1) / BM) * ((a.N + BN - 1) / BN) * a.batch;
+  int grid = a.sm_count > 0 ? a.sm_count : g_sm_count;
+  if (a.out_mode != 2 && tiles < grid) grid = static_cast<int>(tiles);
+  if (a.out_mode == 2) {
+    const long long units = tiles * ((a.K + BK - 1) / BK);
+    if (units < grid) grid = static_cast<int>(units);
+  }
+  if (grid < 1) grid = 1;
+  kern<<<grid, 192, smem, reinterpret_cast<cudaStream_t>(a.stream)>>>(tmA, tmB, p);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 2000 + static_cast<int>(e);
+}
+
+// Returns 0 on success; negative = invalid argument; positive = CUDA/driver error.
+extern "C" TYR_EXPORT int tyr_gemm_bf16(const TyrGemmArgs* args) {
+  using namespace tyr;
+  const TyrGemmArgs& a = *args;
+  if (a.M <= 0 || a.N <= 0 || a.K <= 0 || a.batch <= 0) return -1;
+  if ((reinterpret_cast<uintptr_t>(a.A) & 15) || (reinterpret_cast<uintptr_t>(a.B) & 15) ||
+      (reinterpret_cast<uintptr_t>(a.C) & 15))
+    return -2;
+  if ((a.lda & 7) || (a.ldb & 7) || (a.sA & 7) || (a.sB & 7)) return -3;
+  if (a.out_mode == 0 ? (a.ldc & 7) : (a.ldc & 3)) return -4;
+  if (a.aux && ((a.ldaux & 7) || (reinterpret_cast<uintptr_t>(a.aux) & 15))) return -5;
+  if (g_sm_count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
+  }
+  int bn = a.bn;
+  if (bn == 0) bn = (a.N <= 128) ? 128 : 256;
+  CUtensorMap tmA, tmB;
+  int r;
+  if (!a.a_mn)
+    r = make_tmap_bf16_3d(&tmA, a.A, a.K, a.M, a.batch, a.lda, a.sA, BM);
+  else
+    r = make_tmap_bf16_3d(&tmA, a.A, a.M, a.K, a.batch, a.lda, a.sA, BK);
+  if (r) return 3000 + r;
+  if (!a.b_mn)
+    r = make_tmap_bf16_3d(&tmB, a.B, a.K, a.N, a.batch, a.ldb, a.sB, bn);
+  else
+    r = make_tmap_bf16_3d(&tmB, a.B, a.N, a.K, a.batch, a.ldb, a.sB, BK);
+  if (r) return 4000 + r;
+#define TYR_DISPATCH(BNv, ST)                                                   \
+  do {                                                                          \
+    if (!a.a_mn && !a.b_mn) return launch_gemm<BNv, ST, false, false>(a, tmA, tmB); \
+    if (!a.a_mn && a.b_mn) return launch_gemm<BNv, ST, false, true>(a, tmA, tmB);   \
+    if (a.a_mn && a.b_mn) return launch_gemm<BNv, ST, true, true>(a, tmA, tmB);     \
+    return launch_gemm<BNv, ST, true, false>(a, tmA, tmB);                      \
+  } while (0)
+  if (bn == 256) TYR_DISPATCH(256, 4);
+  if (bn == 128) TYR_DISPATCH(128, 6);
+#undef TYR_DISPATCH
+  return -6;
+}

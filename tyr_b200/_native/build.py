@@ -1,0 +1,120 @@
+"""In-tree build of the native libraries.
+
+Two shared objects are produced next to this file:
+
+* ``libtyr_kernels.so`` - every ``csrc/*.cu`` file, compiled by nvcc for ``sm_100a`` only
+  (``-gencode arch=compute_100a,code=sm_100a -lineinfo``).  The kernels are exported as plain
+  ``extern "C"`` launchers that take raw device pointers and a stream, so the library does not
+  depend on libtorch and compiles in seconds.
+* ``libtyr_host.so`` - every ``csrc/host/*.cpp`` file (safetensors reader, token-shard loader,
+  BOS finder, float ring buffer, WAV/PPM writers, parquet bridge, process-group bookkeeping),
+  compiled with g++.
+
+The reference builds one ``libTyrC`` with exactly one ``-gencode`` pair chosen by ``-Kgpu``
+(cc/Makefile:112-128); here the only supported target is B200.
+"""
+from __future__ import annotations
+
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parents[2]
+CSRC = ROOT / "csrc"
+OUT_DIR = Path(__file__).resolve().parent
+OBJ_DIR = ROOT / "build" / "obj"
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a",
+    "-lineinfo", "-O3", "-std=c++17", "--use_fast_math",
+    "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
+    "--expt-relaxed-constexpr",
+]
+CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-Wall", "-pthread"]
+
+
+def _nvcc() -> str:
+    cand = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(cand):
+        raise RuntimeError("nvcc not found; cannot build tyr_b200 kernels")
+    return cand
+
+
+def _digest(paths, extra: str) -> str:
+    h = hashlib.sha256(extra.encode())
+    for p in sorted(paths):
+        h.update(str(p.name).encode())
+        h.update(p.read_bytes())
+    return h.hexdigest()
+
+
+def _run(cmd):
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("build command failed:\n  %s\n%s\n%s" % (" ".join(map(str, cmd)), r.stdout, r.stderr))
+    return r.stdout + r.stderr
+
+
+def build_kernels(verbose: bool = False, force: bool = False) -> Path:
+    srcs = sorted(CSRC.glob("*.cu"))
+    hdrs = sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h"))
+    out = OUT_DIR / "libtyr_kernels.so"
+    OBJ_DIR.mkdir(parents=True, exist_ok=True)
+    hdr_digest = _digest(hdrs, " ".join(NVCC_FLAGS))
+    nvcc = _nvcc()
+    jobs = []
+    objs = []
+    for s in srcs:
+        obj = OBJ_DIR / (s.stem + ".o")
+        stamp = OBJ_DIR / (s.stem + ".sha")
+        dig = _digest([s], hdr_digest)
+        objs.append(obj)
+        if force or not obj.exists() or not stamp.exists() or stamp.read_text() != dig:
+            jobs.append((s, obj, stamp, dig))
+
+    def compile_one(job):
+        s, obj, stamp, dig = job
+        flags = list(NVCC_FLAGS)
+        if verbose:
+            flags += ["-Xptxas", "-v"]
+        log = _run([nvcc, *flags, "-I", str(CSRC), "-c", str(s), "-o", str(obj)])
+        stamp.write_text(dig)
+        return s.name, log
+
+    if jobs:
+        with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
+            for name, log in ex.map(compile_one, jobs):
+                if verbose and log.strip():
+                    print("[%s]\n%s" % (name, log))
+    if jobs or not out.exists():
+        _run([nvcc, "-shared", "-o", str(out), *map(str, objs), "-lcudart"])
+    return out
+
+
+def build_host(force: bool = False) -> Path:
+    srcs = sorted((CSRC / "host").glob("*.cpp"))
+    hdrs = sorted((CSRC / "host").glob("*.h"))
+    out = OUT_DIR / "libtyr_host.so"
+    stamp = OBJ_DIR / "host.sha"
+    OBJ_DIR.mkdir(parents=True, exist_ok=True)
+    dig = _digest(srcs + hdrs, " ".join(CXX_FLAGS))
+    if not force and out.exists() and stamp.exists() and stamp.read_text() == dig:
+        return out
+    cxx = shutil.which("g++") or "g++"
+    _run([cxx, *CXX_FLAGS, "-shared", "-o", str(out), *map(str, srcs), "-ldl"])
+    stamp.write_text(dig)
+    return out
+
+
+def build_all(verbose: bool = False, force: bool = False):
+    return build_kernels(verbose=verbose, force=force), build_host(force=force)
+
+
+if __name__ == "__main__":
+    k, h = build_all(verbose="-v" in sys.argv, force="-f" in sys.argv)
+    print(k)
+    print(h)
