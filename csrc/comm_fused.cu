@@ -1,0 +1,387 @@
+// Fused compute + collective kernels over NVLink peer memory (plain P2P loads/stores on
+// IPC-mapped buffers; no NCCL call, no multicast loads).
+//
+// Data-parallel optimizer step.  Every rank holds complete local gradients in a symmetric
+// buffer (same layout on every rank, mapped into every peer).  The reference does, per tensor,
+// a blocking NCCL reduce_scatter, ~15 elementwise kernels and two or three all_gathers
+// (Tyr/Optim/DistAdam.lean:185-267, Tyr/Optim/NorMuon.lean:346-425).  Here each of these is ONE
+// kernel per parameter group:
+//
+//  * dp_adam_shard: the owner of a row shard pulls that shard of the gradient from all W peers
+//    (16-byte P2P loads), averages in fp32, applies bias-corrected AdamW to its fp32 master shard
+//    and moment shards (state is truly sharded), and pushes the refreshed bf16 parameters into
+//    the working copy of EVERY rank (P2P stores) - reduce-scatter + update + all-gather.
+//  * dp_muon_gather: the owner of a whole matrix (block-cyclic ownership, as the reference) pulls
+//    and averages its gradient from all peers and applies momentum + Nesterov, emitting the bf16
+//    Newton-Schulz input and its squared norm.
+//  * dp_muon_apply_push: after the owner's Newton-Schulz GEMMs, applies the update to the fp32
+//    master and pushes bf16 parameters to all ranks.
+//  * signal / wait_all: a flag barrier in symmetric memory (st.release.sys / ld.acquire.sys).
+//    Waits are bounded: on timeout the kernel records ERR_PEER_FLAG_TIMEOUT and returns.
+//
+// Tensor-parallel and expert-parallel fused kernels (GEMM -> reduce-scatter epilogue, all-gather
+// prologue, MoE dispatch/combine) live in tp_fused.cu / moe_ep.cu and reuse the helpers here.
+#include "common.cuh"
+
+namespace tyr {
+
+constexpr int kMaxRanks = 8;
+
+struct PeerPtrs {
+  void* p[kMaxRanks];
+};
+
+__device__ __forceinline__ void st_release_sys(unsigned long long* addr, unsigned long long v) {
+  asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(addr), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long long* addr) {
+  unsigned long long v;
+  asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ float4 ld_peer_f4(const float* p) {
+  float4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "l"(p));
+  return v;
+}
+
+// Each rank writes `value` into slot [my_rank] of every peer's flag array.
+__global__ void signal_kernel(PeerPtrs flags, int world, int my_rank, int slot_base,
+                              unsigned long long value) {
+  const int r = threadIdx.x;
+  if (r < world) {
+    __threadfence_system();
+    unsigned long long* f = reinterpret_cast<unsigned long long*>(flags.p[r]) + slot_base + my_rank;
+    st_release_sys(f, value);
+  }
+}
+
+// Waits until every slot [slot_base + r] of the LOCAL flag array is >= value.
+__global__ void wait_all_kernel(const unsigned long long* local_flags, int world, int slot_base,
+                                unsigned long long value, int* err) {
+  const int r = threadIdx.x;
+  if (r < world) {
+    const unsigned long long* f = local_flags + slot_base + r;
+    long long start = clock64();
+    while (ld_acquire_sys(f) < value) {
+      if (clock64() - start > kWaitBudgetCycles * 4) {
+        report_error(err, ERR_PEER_FLAG_TIMEOUT, slot_base + r);
+        break;
+      }
+      __nanosleep(200);
+    }
+  }
+}
+
+__device__ __forceinline__ bool wait_flags_in_kernel(const unsigned long long* local_flags, int world,
+                                                     int slot_base, unsigned long long value,
+                                                     int* err) {
+  // executed by one thread of the CTA
+  for (int r = 0; r < world; ++r) {
+    const unsigned long long* f = local_flags + slot_base + r;
+    long long start = clock64();
+    while (ld_acquire_sys(f) < value) {
+      if (clock64() - start > kWaitBudgetCycles * 4) {
+        report_error(err, ERR_PEER_FLAG_TIMEOUT, slot_base + r);
+        return false;
+      }
+      __nanosleep(200);
+    }
+  }
+  return true;
+}
+
+struct DpAdamArgs {
+  PeerPtrs grads;          // fp32 gradient buffers of all ranks (same offsets everywhere)
+  PeerPtrs work;           // bf16 working-parameter buffers of all ranks
+  long long grad_off;      // element offset of this tensor's shard start in the gradient buffers
+  long long work_off;      // element offset of the shard start in the working buffers
+  float* master;           // local fp32 master shard
+  float* m;
+  float* v;
+  long long n;             // shard elements (multiple of 4)
+  int world;
+  float lr, beta1, beta2, eps, wd, bc1, bc2, grad_scale;
+  const unsigned long long* wait_flags;   // nullable: wait for all ranks' gradients first
+  int wait_slot;
+  unsigned long long wait_value;
+  int* err;
+};
+
+__global__ void __launch_bounds__(256) dp_adam_shard_kernel(DpAdamArgs a) {
+  if (a.wait_flags) {
+    __shared__ int ok_s;
+    if (threadIdx.x == 0)
+      ok_s = wait_flags_in_kernel(a.wait_flags, a.world, a.wait_slot, a.wait_value, a.err) ? 1 : 0;
+    __syncthreads();
+    if (!ok_s) return;
+  }
+  const long long n4 = a.n >> 2;
+  const float inv_w = a.grad_scale / a.world;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n4;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float4 g = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int r = 0; r < kMaxRanks; ++r) {
+      if (r < a.world) {
+        float4 t = ld_peer_f4(reinterpret_cast<const float*>(a.grads.p[r]) + a.grad_off + i * 4);
+        g.x += t.x; g.y += t.y; g.z += t.z; g.w += t.w;
+      }
+    }
+    float4 p = reinterpret_cast<float4*>(a.master)[i];
+    float4 m = reinterpret_cast<float4*>(a.m)[i];
+    float4 v = reinterpret_cast<float4*>(a.v)[i];
+    float gg[4] = {g.x * inv_w, g.y * inv_w, g.z * inv_w, g.w * inv_w};
+    float pp[4] = {p.x, p.y, p.z, p.w}, mm[4] = {m.x, m.y, m.z, m.w}, vv[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      mm[j] = a.beta1 * mm[j] + (1.f - a.beta1) * gg[j];
+      vv[j] = a.beta2 * vv[j] + (1.f - a.beta2) * gg[j] * gg[j];
+      pp[j] = pp[j] * (1.f - a.lr * a.wd) - a.lr * (mm[j] / a.bc1) / (sqrtf(vv[j] / a.bc2) + a.eps);
+    }
+    reinterpret_cast<float4*>(a.master)[i] = make_float4(pp[0], pp[1], pp[2], pp[3]);
+    reinterpret_cast<float4*>(a.m)[i] = make_float4(mm[0], mm[1], mm[2], mm[3]);
+    reinterpret_cast<float4*>(a.v)[i] = make_float4(vv[0], vv[1], vv[2], vv[3]);
+    uint2 w;
+    w.x = pack_bf16x2(pp[0], pp[1]);
+    w.y = pack_bf16x2(pp[2], pp[3]);
+#pragma unroll
+    for (int r = 0; r < kMaxRanks; ++r)
+      if (r < a.world)
+        reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(a.work.p[r]) + a.work_off)[i] = w;
+  }
+}
+
+struct DpMuonGatherArgs {
+  PeerPtrs grads;
+  const long long* grad_offs;   // [B_own] element offset of each owned matrix in the gradient buffers
+  float* mom;                   // [B_own, per] local momentum of owned matrices
+  __nv_bfloat16* u;             // [B_own, per]
+  float* sumsq;                 // [B_own] zero on entry
+  long long per;
+  int B_own, world;
+  float mu, grad_scale;
+  const unsigned long long* wait_flags;
+  int wait_slot;
+  unsigned long long wait_value;
+  int* err;
+};
+
+__global__ void __launch_bounds__(256) dp_muon_gather_kernel(DpMuonGatherArgs a) {
+  if (a.wait_flags) {
+    __shared__ int ok_s;
+    if (threadIdx.x == 0)
+      ok_s = wait_flags_in_kernel(a.wait_flags, a.world, a.wait_slot, a.wait_value, a.err) ? 1 : 0;
+    __syncthreads();
+    if (!ok_s) return;
+  }
+  const int b = blockIdx.y;
+  const long long goff = a.grad_offs[b];
+  const long long base = static_cast<long long>(b) * a.per;
+  const long long n4 = a.per >> 2;
+  const float inv_w = a.grad_scale / a.world;
+  const float om = 1.f - a.mu;
+  float ss = 0.f;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n4;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float4 g = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int r = 0; r < kMaxRanks; ++r) {
+      if (r < a.world) {
+        float4 t = ld_peer_f4(reinterpret_cast<const float*>(a.grads.p[r]) + goff + i * 4);
+        g.x += t.x; g.y += t.y; g.z += t.z; g.w += t.w;
+      }
+    }
+    g.x *= inv_w; g.y *= inv_w; g.z *= inv_w; g.w *= inv_w;
+    float4 m = *reinterpret_cast<float4*>(a.mom + base + i * 4);
+    m.x = a.mu * m.x + om * g.x; m.y = a.mu * m.y + om * g.y;
+    m.z = a.mu * m.z + om * g.z; m.w = a.mu * m.w + om * g.w;
+    *reinterpret_cast<float4*>(a.mom + base + i * 4) = m;
+    uint2 w;
+    w.x = pack_bf16x2(om * g.x + a.mu * m.x, om * g.y + a.mu * m.y);
+    w.y = pack_bf16x2(om * g.z + a.mu * m.z, om * g.w + a.mu * m.w);
+    *reinterpret_cast<uint2*>(a.u + base + i * 4) = w;
+    float2 r0 = unpack_bf16x2(w.x), r1 = unpack_bf16x2(w.y);
+    ss += r0.x * r0.x + r0.y * r0.y + r1.x * r1.x + r1.y * r1.y;
+  }
+  __shared__ float red[8];
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int w = 0; w < (blockDim.x >> 5); ++w) t += red[w];
+    atomicAdd(a.sumsq + b, t);
+  }
+}
+
+struct DpMuonApplyArgs {
+  PeerPtrs work;
+  const long long* work_offs;   // [B_own]
+  float* master;                // [B_own, per]
+  const __nv_bfloat16* o;       // [B_own, per] orthogonalised update
+  long long per;
+  int B_own, world;
+  float lr, wd;
+};
+
+__global__ void __launch_bounds__(256) dp_muon_apply_push_kernel(DpMuonApplyArgs a) {
+  const int b = blockIdx.y;
+  const long long woff = a.work_offs[b];
+  const long long base = static_cast<long long>(b) * a.per;
+  const long long n4 = a.per >> 2;
+  const float decay = 1.f - a.lr * a.wd;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n4;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float4 w = *reinterpret_cast<float4*>(a.master + base + i * 4);
+    uint2 u = *reinterpret_cast<const uint2*>(a.o + base + i * 4);
+    float2 x = unpack_bf16x2(u.x), y = unpack_bf16x2(u.y);
+    w.x = w.x * decay - __bfloat162float(__float2bfloat16(x.x * a.lr));
+    w.y = w.y * decay - __bfloat162float(__float2bfloat16(x.y * a.lr));
+    w.z = w.z * decay - __bfloat162float(__float2bfloat16(y.x * a.lr));
+    w.w = w.w * decay - __bfloat162float(__float2bfloat16(y.y * a.lr));
+    *reinterpret_cast<float4*>(a.master + base + i * 4) = w;
+    uint2 q;
+    q.x = pack_bf16x2(w.x, w.y);
+    q.y = pack_bf16x2(w.z, w.w);
+#pragma unroll
+    for (int r = 0; r < kMaxRanks; ++r)
+      if (r < a.world)
+        *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(a.work.p[r]) + woff + i * 4) = q;
+  }
+}
+
+// Generic peer reduce: out[i] = scale * sum_r src_r[off + i]  (fp32), used for small tensors and
+// for the all-reduce flavour of the public API.
+__global__ void __launch_bounds__(256)
+peer_sum_kernel(PeerPtrs src, long long off, float* out, long long n, int world, float scale) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float s = 0.f;
+    for (int r = 0; r < world; ++r) s += reinterpret_cast<const float*>(src.p[r])[off + i];
+    out[i] = s * scale;
+  }
+}
+
+}  // namespace tyr
+
+using namespace tyr;
+
+// ----------------------------------------------------------------------------------------
+// symmetric memory: allocation + CUDA IPC export/import
+// ----------------------------------------------------------------------------------------
+extern "C" TYR_EXPORT int tyr_symm_alloc(void** out, long long bytes) {
+  cudaError_t e = cudaMalloc(out, (size_t)bytes);
+  if (e != cudaSuccess) return (int)e;
+  e = cudaMemset(*out, 0, (size_t)bytes);
+  return (int)e;
+}
+extern "C" TYR_EXPORT int tyr_symm_free(void* p) { return (int)cudaFree(p); }
+extern "C" TYR_EXPORT int tyr_ipc_export(void* p, void* handle64) {
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, p);
+  if (e != cudaSuccess) return (int)e;
+  memcpy(handle64, &h, sizeof(h));
+  return 0;
+}
+extern "C" TYR_EXPORT int tyr_ipc_open(const void* handle64, void** out) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, sizeof(h));
+  return (int)cudaIpcOpenMemHandle(out, h, cudaIpcMemLazyEnablePeerAccess);
+}
+extern "C" TYR_EXPORT int tyr_ipc_close(void* p) { return (int)cudaIpcCloseMemHandle(p); }
+
+static PeerPtrs make_peers(void* const* ptrs, int world) {
+  PeerPtrs pp;
+  for (int i = 0; i < kMaxRanks; ++i) pp.p[i] = i < world ? ptrs[i] : nullptr;
+  return pp;
+}
+
+extern "C" TYR_EXPORT int tyr_signal(void* const* flag_ptrs, int world, int my_rank, int slot_base,
+                                     unsigned long long value, void* stream) {
+  if (world < 1 || world > kMaxRanks) return -1;
+  signal_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(make_peers(flag_ptrs, world), world, my_rank,
+                                                    slot_base, value);
+  return (int)cudaGetLastError();
+}
+extern "C" TYR_EXPORT int tyr_wait_all(const void* local_flags, int world, int slot_base,
+                                       unsigned long long value, int* err, void* stream) {
+  if (world < 1 || world > kMaxRanks) return -1;
+  wait_all_kernel<<<1, 32, 0, (cudaStream_t)stream>>>((const unsigned long long*)local_flags, world,
+                                                      slot_base, value, err);
+  return (int)cudaGetLastError();
+}
+
+extern "C" TYR_EXPORT int tyr_dp_adam_shard(void* const* grad_ptrs, void* const* work_ptrs, int world,
+                                            long long grad_off, long long work_off, float* master,
+                                            float* m, float* v, long long n, float lr, float beta1,
+                                            float beta2, float eps, float wd, float bc1, float bc2,
+                                            float grad_scale, const void* wait_flags, int wait_slot,
+                                            unsigned long long wait_value, int* err, int ctas,
+                                            void* stream) {
+  if (world < 1 || world > kMaxRanks || n <= 0 || (n & 3) || (grad_off & 3) || (work_off & 3)) return -1;
+  DpAdamArgs a;
+  a.grads = make_peers(grad_ptrs, world);
+  a.work = make_peers(work_ptrs, world);
+  a.grad_off = grad_off; a.work_off = work_off;
+  a.master = master; a.m = m; a.v = v; a.n = n; a.world = world;
+  a.lr = lr; a.beta1 = beta1; a.beta2 = beta2; a.eps = eps; a.wd = wd; a.bc1 = bc1; a.bc2 = bc2;
+  a.grad_scale = grad_scale;
+  a.wait_flags = (const unsigned long long*)wait_flags; a.wait_slot = wait_slot; a.wait_value = wait_value;
+  a.err = err;
+  long long blocks = (n / 4 + 255) / 256;
+  const int cap = ctas > 0 ? ctas : 148 * 4;
+  if (blocks > cap) blocks = cap;
+  dp_adam_shard_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>(a);
+  return (int)cudaGetLastError();
+}
+
+extern "C" TYR_EXPORT int tyr_dp_muon_gather(void* const* grad_ptrs, int world, const long long* grad_offs,
+                                             float* mom, void* u, float* sumsq, long long per, int B_own,
+                                             float mu, float grad_scale, const void* wait_flags,
+                                             int wait_slot, unsigned long long wait_value, int* err,
+                                             int ctas, void* stream) {
+  if (world < 1 || world > kMaxRanks || per <= 0 || (per & 3) || B_own <= 0) return -1;
+  DpMuonGatherArgs a;
+  a.grads = make_peers(grad_ptrs, world);
+  a.grad_offs = grad_offs; a.mom = mom; a.u = (__nv_bfloat16*)u; a.sumsq = sumsq; a.per = per;
+  a.B_own = B_own; a.world = world; a.mu = mu; a.grad_scale = grad_scale;
+  a.wait_flags = (const unsigned long long*)wait_flags; a.wait_slot = wait_slot; a.wait_value = wait_value;
+  a.err = err;
+  const int cap = ctas > 0 ? ctas : 148 * 4;
+  int gx = (int)((per / 4 + 255) / 256);
+  int per_b = (cap + B_own - 1) / B_own;
+  if (per_b < 1) per_b = 1;
+  if (gx > per_b) gx = per_b;
+  dp_muon_gather_kernel<<<dim3(gx, B_own), 256, 0, (cudaStream_t)stream>>>(a);
+  return (int)cudaGetLastError();
+}
+
+extern "C" TYR_EXPORT int tyr_dp_muon_apply_push(void* const* work_ptrs, int world, const long long* work_offs,
+                                                 float* master, const void* o, long long per, int B_own,
+                                                 float lr, float wd, int ctas, void* stream) {
+  if (world < 1 || world > kMaxRanks || per <= 0 || (per & 3) || B_own <= 0) return -1;
+  DpMuonApplyArgs a;
+  a.work = make_peers(work_ptrs, world);
+  a.work_offs = work_offs; a.master = master; a.o = (const __nv_bfloat16*)o; a.per = per;
+  a.B_own = B_own; a.world = world; a.lr = lr; a.wd = wd;
+  const int cap = ctas > 0 ? ctas : 148 * 4;
+  int gx = (int)((per / 4 + 255) / 256);
+  int per_b = (cap + B_own - 1) / B_own;
+  if (per_b < 1) per_b = 1;
+  if (gx > per_b) gx = per_b;
+  dp_muon_apply_push_kernel<<<dim3(gx, B_own), 256, 0, (cudaStream_t)stream>>>(a);
+  return (int)cudaGetLastError();
+}
+
+extern "C" TYR_EXPORT int tyr_peer_sum(void* const* src_ptrs, int world, long long off, float* out,
+                                       long long n, float scale, void* stream) {
+  if (world < 1 || world > kMaxRanks || n <= 0) return -1;
+  long long blocks = (n + 255) / 256;
+  if (blocks > 148 * 4) blocks = 148 * 4;
+  peer_sum_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>(make_peers(src_ptrs, world), off, out, n,
+                                                                 world, scale);
+  return (int)cudaGetLastError();
+}

@@ -453,6 +453,20 @@ static int launch_gemm(const TyrGemmArgs& a, const CUtensorMap& tmA, const CUten
   return e == cudaSuccess ? 0 : 2000 + static_cast<int>(e);
 }
 
+// Binds the given device (and its primary context) to the calling thread.  Host threads that
+// never touched the runtime of this library (for example autograd worker threads) have no
+// current context for the driver-level tensor-map encoder, and would default to device 0.
+extern "C" TYR_EXPORT int tyr_bind_device(int device) {
+  static thread_local int bound = -1;
+  if (bound == device) return 0;
+  cudaError_t e = cudaSetDevice(device);
+  if (e != cudaSuccess) return (int)e;
+  e = cudaFree(0);
+  if (e != cudaSuccess) return (int)e;
+  bound = device;
+  return 0;
+}
+
 // Returns 0 on success; negative = invalid argument; positive = CUDA/driver error.
 extern "C" TYR_EXPORT int tyr_gemm_bf16(const TyrGemmArgs* args) {
   using namespace tyr;

@@ -270,3 +270,40 @@ def test_nanochat_fused_vs_reference_gpu():
         assert e < 8e-2, (name, e)
     e = _rel_err(params.work["scalars"].grad, ref_p["scalars.values"].grad)
     assert e < 8e-2, ("scalars", e)
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,Tq,Tk,causal,window", [
+    (2, 2, 2, 256, 256, True, None),
+    (1, 4, 2, 384, 384, True, None),
+    (2, 2, 2, 512, 512, True, 200),
+    (1, 2, 2, 200, 200, True, None),
+    (1, 2, 1, 300, 300, False, None),
+    (1, 2, 2, 128, 640, True, None),
+    (2, 3, 3, 1024, 1024, True, None),
+])
+def test_flash_attention_forward(B, Hq, Hkv, Tq, Tk, causal, window):
+    from tyr_b200.ops import flash
+    from tyr_b200.ops.attention import attention_ref
+    if not flash.has_fwd():
+        pytest.skip("flash forward kernel not built")
+    g = torch.Generator(device="cuda").manual_seed(11)
+    D = 128
+    q = torch.randn(B, Tq, Hq, D, device=_dev(), generator=g).bfloat16()
+    k = torch.randn(B, Tk, Hkv, D, device=_dev(), generator=g).bfloat16()
+    v = torch.randn(B, Tk, Hkv, D, device=_dev(), generator=g).bfloat16()
+    o, lse = flash.flash_fwd_bthd(q, k, v, causal=causal, window=window, scale=None)
+    ref = attention_ref(q.transpose(1, 2).float(), k.transpose(1, 2).float(), v.transpose(1, 2).float(),
+                        causal=causal, window=window).transpose(1, 2)
+    assert _rel_err(o, ref) < 2e-2, _rel_err(o, ref)
+    # log-sum-exp against the explicit scores
+    rep = Hq // Hkv
+    s = torch.einsum("bqhd,bkhd->bhqk", q.float(), k.float().repeat_interleave(rep, dim=2)) / math.sqrt(D)
+    qi = torch.arange(Tq, device=_dev())[:, None] + (Tk - Tq)
+    ki = torch.arange(Tk, device=_dev())[None, :]
+    m = torch.ones(Tq, Tk, dtype=torch.bool, device=_dev())
+    if causal:
+        m &= ki <= qi
+    if window:
+        m &= ki > qi - window
+    s = s.masked_fill(~m, float("-inf"))
+    assert torch.allclose(lse, torch.logsumexp(s, -1), rtol=1e-2, atol=2e-2)

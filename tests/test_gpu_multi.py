@@ -1,0 +1,27 @@
+"""Multi-GPU tests (child processes under torchrun, one rank per GPU, NVLS off)."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _run_torchrun(script, nproc, timeout=300, port=29611):
+    env = dict(os.environ)
+    env["NCCL_NVLS_ENABLE"] = "0"
+    env["MASTER_ADDR"] = "127.0.0.1"
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), script]
+    return subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=timeout)
+
+
+@pytest.mark.parametrize("nproc", [2, 4, 8])
+def test_fused_data_parallel_matches_accumulation(nproc):
+    if torch.cuda.device_count() < nproc:
+        pytest.skip(f"needs {nproc} GPUs")
+    r = _run_torchrun(os.path.join(ROOT, "tests", "workers", "dp_worker.py"), nproc, port=29611 + nproc)
+    assert "DP_WORKER_RESULT PASS" in r.stdout, (r.stdout[-3000:], r.stderr[-3000:])

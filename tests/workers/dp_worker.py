@@ -1,0 +1,82 @@
+"""Child process of tests/test_gpu_multi.py: one rank of a fused data-parallel run.
+
+Each rank trains a small NanoChat model for a few steps on its own micro-batches through
+FusedDataParallel; rank 0 then repeats the same steps in a single process with gradient
+accumulation over all ranks' micro-batches and compares parameters."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+
+from tyr_b200.models import nanochat as nc  # noqa: E402
+from tyr_b200.ops._common import raise_on_device_error  # noqa: E402
+from tyr_b200.parallel.dp import FusedDataParallel  # noqa: E402
+from tyr_b200.train import nanochat_engine as eng  # noqa: E402
+
+
+def main():
+    rank = int(os.environ["RANK"])
+    world = int(os.environ["WORLD_SIZE"])
+    local = int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    cfg = nc.Config(vocab_size=2048, n_layer=7, n_head=2, half_head_dim=64, max_seq_len=128)
+    hp = eng.Hyperparameters(device_batch_size=4, max_seq_len=128, total_batch_size_tokens=4 * 128 * world)
+    steps = 3
+    gen = torch.Generator().manual_seed(123)
+    toks = torch.randint(0, cfg.vocab_size, (steps, world, 4, 129), generator=gen)
+
+    dp = FusedDataParallel(rank, world, dev)
+    tr = eng.NanoChatTrainer(cfg, hp, device=dev, seed=7, world_size=world, rank=rank, dp=dp, ce_chunk_rows=256)
+    losses = []
+    for s in range(steps):
+        t = toks[s, rank].to(dev)
+        res = tr.step([(t[:, :-1].contiguous(), t[:, 1:].contiguous())])
+        losses.append(res.loss)
+    torch.cuda.synchronize()
+    raise_on_device_error(dev)
+    dist.barrier()
+    work = {k: v.detach().float().clone() for k, v in tr.params.named_parameters("work").items()}
+
+    ok = True
+    msg = ""
+    # every rank must hold identical working parameters
+    for k, v in work.items():
+        ref = v.clone()
+        dist.broadcast(ref, src=0)
+        if not torch.equal(ref, v):
+            ok = False
+            msg += f"rank {rank}: {k} differs from rank 0\n"
+    if rank == 0:
+        single = eng.NanoChatTrainer(cfg, hp, device=dev, seed=7, ce_chunk_rows=256)
+        for s in range(steps):
+            mbs = []
+            for r in range(world):
+                t = toks[s, r].to(dev)
+                mbs.append((t[:, :-1].contiguous(), t[:, 1:].contiguous()))
+            single.step(mbs)
+        torch.cuda.synchronize()
+        ref = single.params.named_parameters("work")
+        for k, v in work.items():
+            a, b = v, ref[k].float()
+            err = ((a - b).norm() / (b.norm() + 1e-9)).item()
+            if not err < 2e-2:
+                ok = False
+                msg += f"{k}: rel err {err:.4f} vs single-process accumulation\n"
+    flag = torch.tensor([0 if ok else 1], device=dev)
+    dist.all_reduce(flag)
+    if rank == 0:
+        print("DP_WORKER_RESULT", "PASS" if flag.item() == 0 else "FAIL")
+    if msg:
+        print(msg)
+    dp.close()
+    dist.destroy_process_group()
+    sys.exit(0 if flag.item() == 0 else 1)
+
+
+if __name__ == "__main__":
+    main()

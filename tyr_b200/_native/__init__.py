@@ -101,6 +101,7 @@ def _sig(lib, name, argtypes, restype=c_int):
 def _declare_kernels(lib):
     P = c_void_p
     _sig(lib, "tyr_gemm_bf16", [ctypes.POINTER(GemmArgs)])
+    _sig(lib, "tyr_bind_device", [c_int])
     _sig(lib, "tyr_lincomb_rmsnorm_fwd", [P, P, P, P, P, c_int, c_int, c_int, P, P, c_float, P])
     _sig(lib, "tyr_lincomb_rmsnorm_bwd",
          [ctypes.POINTER(P), ctypes.POINTER(P), P, P, P, P, P, c_int, c_int, c_int, c_float, P])

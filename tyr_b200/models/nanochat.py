@@ -144,7 +144,22 @@ class ModdedGPTParams:
     MATRIX_GROUPS = ("attn_w", "mlp_w")
     ADAM_GROUPS = ("embed", "value_embeds", "lm_head")
 
-    def __init__(self, cfg: Config, device="cpu", compute_dtype=torch.bfloat16, seed: Optional[int] = None):
+    @staticmethod
+    def storage_plan(cfg: Config, compute_dtype=torch.bfloat16):
+        """(shape, dtype) of every tensor requested from ``alloc``, in allocation order."""
+        d, V, L = cfg.model_dim, cfg.vocab_size, cfg.n_layer
+        La = L - (1 if L > SKIP_ATTN_LAYER else 0)
+        shapes = [(V, d), (cfg.num_value_embeds, V, d), (La, 4, d, d), (L, 2, 4 * d, d), (V, d)]
+        plan = []
+        for s in shapes:
+            plan.append((s, compute_dtype))
+            plan.append((s, torch.float32))
+        return plan
+
+    def __init__(self, cfg: Config, device="cpu", compute_dtype=torch.bfloat16, seed: Optional[int] = None,
+                 alloc=None):
+        """``alloc(shape, dtype) -> tensor`` (optional) provides the storage of the working copies
+        and gradient accumulators, e.g. from a symmetric heap that peers can address."""
         self.cfg = cfg
         self.device = torch.device(device)
         self.compute_dtype = compute_dtype
@@ -182,6 +197,11 @@ class ModdedGPTParams:
             if k in ("scalars", "smear_gate"):
                 self.work[k] = v.detach().clone().requires_grad_(True)
                 self.grad[k] = None
+            elif alloc is not None:
+                self.work[k] = alloc(tuple(v.shape), compute_dtype)
+                self.work[k].copy_(v)
+                self.grad[k] = alloc(tuple(v.shape), torch.float32)
+                self.grad[k].zero_()
             else:
                 self.work[k] = v.to(compute_dtype)
                 self.grad[k] = torch.zeros_like(v)

@@ -21,7 +21,15 @@ def ptr(t):
 
 
 def cur_stream(device=None):
-    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+    """Current torch stream of ``device`` as a raw handle.  Also binds that device to the calling
+    host thread inside the kernel library (autograd worker threads start without one)."""
+    idx = torch.device(device).index if device is not None else None
+    if idx is None:
+        idx = torch.cuda.current_device()
+    rc = kernels().tyr_bind_device(idx)
+    if rc != 0:
+        raise RuntimeError(f"tyr_bind_device({idx}) failed with CUDA error {rc}")
+    return ctypes.c_void_p(torch.cuda.current_stream(idx).cuda_stream)
 
 
 def check(rc: int, what: str):

@@ -192,24 +192,34 @@ class NanoChatTrainer:
         self.hp = hp or Hyperparameters()
         self.device = torch.device(device)
         self.world_size, self.rank = world_size, rank
-        self.params = nc.ModdedGPTParams(cfg, device=device, compute_dtype=compute_dtype, seed=seed)
+        alloc = None
+        if dp is not None and world_size > 1:
+            plan = nc.ModdedGPTParams.storage_plan(cfg, compute_dtype)
+            plan += [((cfg.n_layer * 4 + 8,), torch.float32), ((1, 12), torch.float32)]
+            dp.plan_heap(plan)
+            alloc = dp.alloc
+        self.params = nc.ModdedGPTParams(cfg, device=device, compute_dtype=compute_dtype, seed=seed, alloc=alloc)
         self.step_index = 0
         self.ce_chunk_rows = ce_chunk_rows
         self.dp = dp
         p = self.params
-        self.muon_groups: Dict[str, MuonGroup] = {
+        sharded = dp is not None and world_size > 1
+        self.muon_groups: Dict[str, MuonGroup] = {} if sharded else {
             "attn_w": MuonGroup(p.master["attn_w"], p.work["attn_w"], p.grad["attn_w"]),
             "mlp_w": MuonGroup(p.master["mlp_w"], p.work["mlp_w"], p.grad["mlp_w"]),
         }
         self.smear_momentum = torch.zeros_like(p.master["smear_gate"])
         self.adam_groups: Dict[str, AdamGroup] = {
-            "embed": AdamGroup(p.master["embed"], p.work["embed"], lambda: p.grad["embed"]),
-            "value_embeds": AdamGroup(p.master["value_embeds"], p.work["value_embeds"],
-                                      lambda: p.grad["value_embeds"]),
-            "lm_head": AdamGroup(p.master["lm_head"], p.work["lm_head"], lambda: p.grad["lm_head"]),
             "scalars": AdamGroup(p.master["scalars"], p.work["scalars"], lambda: p.work["scalars"].grad),
         }
-        if dp is not None:
+        if not sharded:
+            self.adam_groups.update({
+                "embed": AdamGroup(p.master["embed"], p.work["embed"], lambda: p.grad["embed"]),
+                "value_embeds": AdamGroup(p.master["value_embeds"], p.work["value_embeds"],
+                                          lambda: p.grad["value_embeds"]),
+                "lm_head": AdamGroup(p.master["lm_head"], p.work["lm_head"], lambda: p.grad["lm_head"]),
+            })
+        if sharded:
             dp.attach(self)
 
     # ------------------------------------------------------------------------------------------
