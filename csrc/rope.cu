@@ -192,6 +192,194 @@ __global__ void __launch_bounds__(256) qkv_post_bwd_kernel(QkvPostBwdArgs a) {
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// D == 128 fast path: 8 lanes per (row, head), 16-byte loads/stores; a warp covers 4 heads and a
+// block walks the (row, head-group) units.  x1/x2 halves of a head are 128 B each, so every group
+// of 8 lanes reads two fully coalesced 128-byte segments.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void ld8(const __nv_bfloat16* p, float (&f)[8]) {
+  uint4 u = *reinterpret_cast<const uint4*>(p);
+  float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+}
+__device__ __forceinline__ void st8(__nv_bfloat16* p, const float (&f)[8]) {
+  uint4 u;
+  u.x = pack_bf16x2(f[0], f[1]); u.y = pack_bf16x2(f[2], f[3]);
+  u.z = pack_bf16x2(f[4], f[5]); u.w = pack_bf16x2(f[6], f[7]);
+  *reinterpret_cast<uint4*>(p) = u;
+}
+__device__ __forceinline__ void ldf8(const float* p, float (&f)[8]) {
+  float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+__device__ __forceinline__ float group8_sum(float v) {
+  v += __shfl_xor_sync(0xffffffffu, v, 1);
+  v += __shfl_xor_sync(0xffffffffu, v, 2);
+  v += __shfl_xor_sync(0xffffffffu, v, 4);
+  return v;
+}
+
+__global__ void __launch_bounds__(256) qkv_post_fwd_d128_kernel(QkvPostArgs a) {
+  const int lane = threadIdx.x & 31;
+  const int sub = lane >> 3;          // head within the group of 4
+  const int ch = (lane & 7) * 8;      // channel offset inside a 64-wide half
+  const int groups = (3 * a.H + 3) / 4;   // 4 (which, head) slots per warp step
+  const long long units = static_cast<long long>(a.rows) * groups;
+  const long long stride = static_cast<long long>(gridDim.x) * (blockDim.x >> 5);
+  const float mix = a.mix ? *a.mix : 0.f;
+  const int HD = a.H * 128;
+  for (long long u = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); u < units;
+       u += stride) {
+    const long long row = u / groups;
+    const int slot = static_cast<int>(u % groups) * 4 + sub;   // index into [3*H]
+    const bool live = slot < 3 * a.H;
+    const int which = live ? slot / a.H : 0;
+    const int head = live ? slot % a.H : 0;
+    const long long off = row * (3LL * HD) + static_cast<long long>(which) * HD + head * 128;
+    float x1[8], x2[8];
+    if (live) {
+      ld8(a.qkv + off + ch, x1);
+      ld8(a.qkv + off + 64 + ch, x2);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x1[j] = x2[j] = 0.f;
+    }
+    if (which == 2) {
+      if (live) {
+        if (a.ve) {
+          float e1[8], e2[8];
+          const long long voff = row * HD + head * 128;
+          ld8(a.ve + voff + ch, e1);
+          ld8(a.ve + voff + 64 + ch, e2);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            x1[j] = (1.f - mix) * x1[j] + mix * e1[j];
+            x2[j] = (1.f - mix) * x2[j] + mix * e2[j];
+          }
+        }
+        st8(a.out + off + ch, x1);
+        st8(a.out + off + 64 + ch, x2);
+      }
+      // the q/k lanes of this warp still run the shuffles below; v lanes join them with zeros
+    }
+    const int pos = static_cast<int>(row % a.T);
+    float c[8], sn[8], r1[8], r2[8];
+    ldf8(a.cosT + static_cast<long long>(pos) * 64 + ch, c);
+    ldf8(a.sinT + static_cast<long long>(pos) * 64 + ch, sn);
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      r1[j] = x1[j] * c[j] - x2[j] * sn[j];
+      r2[j] = x1[j] * sn[j] + x2[j] * c[j];
+      ss += r1[j] * r1[j] + r2[j] * r2[j];
+    }
+    ss = group8_sum(ss);
+    if (live && which != 2) {
+      const float rstd = rsqrtf(ss * (1.f / 128.f) + a.eps);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        r1[j] *= rstd;
+        r2[j] *= rstd;
+      }
+      st8(a.out + off + ch, r1);
+      st8(a.out + off + 64 + ch, r2);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) qkv_post_bwd_d128_kernel(QkvPostBwdArgs a) {
+  const int lane = threadIdx.x & 31;
+  const int wid = threadIdx.x >> 5;
+  const int sub = lane >> 3;
+  const int ch = (lane & 7) * 8;
+  const int groups = (3 * a.H + 3) / 4;
+  const long long units = static_cast<long long>(a.rows) * groups;
+  const long long stride = static_cast<long long>(gridDim.x) * (blockDim.x >> 5);
+  const float mix = a.mix ? *a.mix : 0.f;
+  const int HD = a.H * 128;
+  float dmix_acc = 0.f;
+  for (long long u = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + wid; u < units; u += stride) {
+    const long long row = u / groups;
+    const int slot = static_cast<int>(u % groups) * 4 + sub;
+    const bool live = slot < 3 * a.H;
+    const int which = live ? slot / a.H : 0;
+    const int head = live ? slot % a.H : 0;
+    const long long off = row * (3LL * HD) + static_cast<long long>(which) * HD + head * 128;
+    float x1[8], x2[8], g1[8], g2[8];
+    if (live) {
+      ld8(a.qkv + off + ch, x1);
+      ld8(a.qkv + off + 64 + ch, x2);
+      ld8(a.dy + off + ch, g1);
+      ld8(a.dy + off + 64 + ch, g2);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x1[j] = x2[j] = g1[j] = g2[j] = 0.f;
+    }
+    if (live && which == 2) {
+      if (a.ve) {
+        float e1[8], e2[8];
+        const long long voff = row * HD + head * 128;
+        ld8(a.ve + voff + ch, e1);
+        ld8(a.ve + voff + 64 + ch, e2);
+        float d1[8], d2[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          dmix_acc += g1[j] * (e1[j] - x1[j]) + g2[j] * (e2[j] - x2[j]);
+          d1[j] = mix * g1[j];
+          d2[j] = mix * g2[j];
+          g1[j] *= (1.f - mix);
+          g2[j] *= (1.f - mix);
+        }
+        if (a.dve) {
+          st8(a.dve + voff + ch, d1);
+          st8(a.dve + voff + 64 + ch, d2);
+        }
+      }
+      st8(a.dqkv + off + ch, g1);
+      st8(a.dqkv + off + 64 + ch, g2);
+    }
+    const int pos = static_cast<int>(row % a.T);
+    float c[8], sn[8], r1[8], r2[8];
+    ldf8(a.cosT + static_cast<long long>(pos) * 64 + ch, c);
+    ldf8(a.sinT + static_cast<long long>(pos) * 64 + ch, sn);
+    float ss = 0.f, dot = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      r1[j] = x1[j] * c[j] - x2[j] * sn[j];
+      r2[j] = x1[j] * sn[j] + x2[j] * c[j];
+      ss += r1[j] * r1[j] + r2[j] * r2[j];
+      dot += r1[j] * g1[j] + r2[j] * g2[j];
+    }
+    ss = group8_sum(ss);
+    dot = group8_sum(dot);
+    if (live && which != 2) {
+      const float rstd = rsqrtf(ss * (1.f / 128.f) + a.eps);
+      const float coef = rstd * rstd * rstd * dot * (1.f / 128.f);
+      float o1[8], o2[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float a1 = rstd * g1[j] - coef * r1[j];
+        const float a2 = rstd * g2[j] - coef * r2[j];
+        o1[j] = a1 * c[j] + a2 * sn[j];
+        o2[j] = -a1 * sn[j] + a2 * c[j];
+      }
+      st8(a.dqkv + off + ch, o1);
+      st8(a.dqkv + off + 64 + ch, o2);
+    }
+  }
+  if (a.dmix) {
+    __shared__ float red[8];
+    float v = warp_sum(dmix_acc);
+    if (lane == 0) red[wid] = v;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float t = 0.f;
+      for (int w = 0; w < (blockDim.x >> 5); ++w) t += red[w];
+      if (t != 0.f) atomicAdd(a.dmix, t);
+    }
+  }
+}
+
 // Generic rope for the inference families: x [rows, H, D] (row stride given), optional RMSNorm
 // with weight over the head BEFORE rotation, rotary applied to the first `rot` channels of each
 // head (half-split inside that span), position ids explicit (nullptr = row % T).
@@ -269,6 +457,11 @@ extern "C" TYR_EXPORT int tyr_qkv_post_fwd(const void* qkv, const void* ve, cons
   if (D > 512) return -2;
   QkvPostArgs a{(const __nv_bfloat16*)qkv, (const __nv_bfloat16*)ve, mix, cosT, sinT,
                 (__nv_bfloat16*)out, rows, T, H, D, eps};
+  if (D == 128) {
+    const long long units = static_cast<long long>(rows) * ((3 * H + 3) / 4);
+    qkv_post_fwd_d128_kernel<<<grid_for_units(units, 8), 256, 0, (cudaStream_t)stream>>>(a);
+    return (int)cudaGetLastError();
+  }
   qkv_post_fwd_kernel<<<grid_for_units(3LL * rows * H, 8), 256, 0, (cudaStream_t)stream>>>(a);
   return (int)cudaGetLastError();
 }
@@ -282,6 +475,11 @@ extern "C" TYR_EXPORT int tyr_qkv_post_bwd(const void* qkv, const void* ve, cons
   QkvPostBwdArgs a{(const __nv_bfloat16*)qkv, (const __nv_bfloat16*)ve, mix, cosT, sinT,
                    (const __nv_bfloat16*)dy, (__nv_bfloat16*)dqkv, (__nv_bfloat16*)dve, dmix,
                    rows, T, H, D, eps};
+  if (D == 128) {
+    const long long units = static_cast<long long>(rows) * ((3 * H + 3) / 4);
+    qkv_post_bwd_d128_kernel<<<grid_for_units(units, 8), 256, 0, (cudaStream_t)stream>>>(a);
+    return (int)cudaGetLastError();
+  }
   qkv_post_bwd_kernel<<<grid_for_units(3LL * rows * H, 8), 256, 0, (cudaStream_t)stream>>>(a);
   return (int)cudaGetLastError();
 }

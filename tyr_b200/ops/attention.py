@@ -73,16 +73,46 @@ def attention(q, k, v, *, causal=True, window: Optional[int] = None, scale: Opti
                          key_padding_mask=key_padding_mask, edge_mask=edge_mask)
 
 
+class _SdpaPackedFn(torch.autograd.Function):
+    """Library attention on the packed projection without autograd's per-slice zero-fill: the
+    inner graph is kept and differentiated once, and the three gradients are written straight
+    into one packed buffer."""
+
+    @staticmethod
+    def forward(ctx, qkv, B, T, H, D, causal, scale):
+        x = qkv.detach().view(B, T, 3, H, D)
+        with torch.enable_grad():
+            q = x[:, :, 0].transpose(1, 2).requires_grad_(True)
+            k = x[:, :, 1].transpose(1, 2).requires_grad_(True)
+            v = x[:, :, 2].transpose(1, 2).requires_grad_(True)
+            o = F.scaled_dot_product_attention(q, k, v, is_causal=causal, scale=scale)
+        ctx.inner = (q, k, v, o)
+        ctx.dims = (B, T, H, D)
+        return o.detach().transpose(1, 2).reshape(B * T, H * D)
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, o = ctx.inner
+        B, T, H, D = ctx.dims
+        do4 = do.view(B, T, H, D).transpose(1, 2)
+        dq, dk, dv = torch.autograd.grad(o, (q, k, v), do4)
+        out = torch.empty((B, T, 3, H, D), dtype=do.dtype, device=do.device)
+        out[:, :, 0].copy_(dq.transpose(1, 2))
+        out[:, :, 1].copy_(dk.transpose(1, 2))
+        out[:, :, 2].copy_(dv.transpose(1, 2))
+        ctx.inner = None
+        return out.view(B * T, 3 * H * D), None, None, None, None, None, None
+
+
 def attention_packed(qkv: torch.Tensor, B: int, T: int, H: int, D: int, *, causal: bool = True,
                      window: Optional[int] = None, scale: Optional[float] = None) -> torch.Tensor:
     """qkv: [B*T, 3*H*D] packed (q | k | v, heads inner) -> [B*T, H*D]."""
     from . import flash
     if qkv.is_cuda and qkv.dtype == torch.bfloat16 and flash.supported_packed(H, D, T, causal, window):
         return flash.flash_attention_packed(qkv, B, T, H, D, causal=causal, window=window, scale=scale)
+    if qkv.is_cuda and window is None:
+        return _SdpaPackedFn.apply(qkv, B, T, H, D, causal, scale)
     x = qkv.view(B, T, 3, H, D)
     q, k, v = (x[:, :, i].transpose(1, 2) for i in range(3))
-    if qkv.is_cuda and window is None:
-        o = F.scaled_dot_product_attention(q, k, v, is_causal=causal, scale=scale)
-    else:
-        o = attention_ref(q, k, v, causal=causal, window=window, scale=scale)
+    o = attention_ref(q, k, v, causal=causal, window=window, scale=scale)
     return o.transpose(1, 2).reshape(B * T, H * D)
