@@ -509,3 +509,79 @@ extern "C" TYR_EXPORT int tyr_gemm_bf16(const TyrGemmArgs* args) {
 #undef TYR_DISPATCH
   return -6;
 }
+
+// ----------------------------------------------------------------------------------------
+// Newton-Schulz iteration chain on the GEMM above (Muon orthogonalisation).
+//
+//   X <- a X + (b A + c A A) X,   A = X X^T        (X: [batch, R, C] bf16, already normalised)
+//
+// Tall matrices (R > C) run the same iteration on X^T through operand layouts.  Each iteration is
+// three GEMM launches with the scale/add terms in the epilogue.  Needs scratch for A, bA + cAA
+// (both [batch, S, S], S = min(R, C)) and one extra X buffer; the result is written back to `x`.
+// Reference: cc/src/tyr_polar.cpp:267-317 (15 cuBLAS GEMMs + 15 elementwise kernels per matrix).
+// ----------------------------------------------------------------------------------------
+extern "C" TYR_EXPORT long long tyr_newton_schulz_scratch_bytes(int batch, int R, int C) {
+  const long long S = R < C ? R : C;
+  return (2LL * batch * S * S + 1LL * batch * R * C) * 2;
+}
+
+static int ns_chain(void* x, void* scratch, int batch, int R, int C, int iters, float a, float b,
+                    float c, int* err, void* stream) {
+  const long long S = R < C ? R : C;
+  __nv_bfloat16* A = reinterpret_cast<__nv_bfloat16*>(scratch);
+  __nv_bfloat16* Bm = A + 1LL * batch * S * S;
+  __nv_bfloat16* X2 = Bm + 1LL * batch * S * S;
+  __nv_bfloat16* cur = reinterpret_cast<__nv_bfloat16*>(x);
+  __nv_bfloat16* nxt = X2;
+  const bool tall = R > C;
+  for (int it = 0; it < iters; ++it) {
+    TyrGemmArgs g;
+    memset(&g, 0, sizeof(g));
+    g.batch = batch; g.alpha = 1.f; g.beta = 0.f; g.err = err; g.stream = stream;
+    // A = X X^T (wide) or X^T X (tall)
+    g.A = cur; g.B = cur; g.C = A; g.M = (int)S; g.N = (int)S; g.K = tall ? R : C;
+    g.lda = C; g.ldb = C; g.ldc = S; g.sA = 1LL * R * C; g.sB = 1LL * R * C; g.sC = S * S;
+    g.a_mn = tall ? 1 : 0; g.b_mn = tall ? 1 : 0;
+    int rc = tyr_gemm_bf16(&g);
+    if (rc) return rc;
+    // Bm = c A A + b A   (A symmetric)
+    memset(&g, 0, sizeof(g));
+    g.batch = batch; g.err = err; g.stream = stream;
+    g.A = A; g.B = A; g.C = Bm; g.aux = A; g.M = g.N = g.K = (int)S;
+    g.lda = g.ldb = g.ldc = g.ldaux = S; g.sA = g.sB = g.sC = g.sAux = S * S;
+    g.alpha = c; g.beta = b;
+    rc = tyr_gemm_bf16(&g);
+    if (rc) return rc;
+    // X' = Bm X + a X (wide)   or   X' = X Bm + a X (tall)
+    memset(&g, 0, sizeof(g));
+    g.batch = batch; g.err = err; g.stream = stream; g.alpha = 1.f; g.beta = a;
+    g.C = nxt; g.aux = cur; g.ldc = C; g.ldaux = C; g.sC = g.sAux = 1LL * R * C;
+    g.M = R; g.N = C;
+    if (!tall) {
+      g.A = Bm; g.lda = S; g.sA = S * S; g.a_mn = 0;
+      g.B = cur; g.ldb = C; g.sB = 1LL * R * C; g.b_mn = 1; g.K = R;
+    } else {
+      g.A = cur; g.lda = C; g.sA = 1LL * R * C; g.a_mn = 0;
+      g.B = Bm; g.ldb = S; g.sB = S * S; g.b_mn = 0; g.K = C;
+    }
+    rc = tyr_gemm_bf16(&g);
+    if (rc) return rc;
+    __nv_bfloat16* t = cur; cur = nxt; nxt = t;
+  }
+  if (cur != x) {
+    cudaError_t e = cudaMemcpyAsync(x, cur, 2LL * batch * R * C, cudaMemcpyDeviceToDevice,
+                                    reinterpret_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return 2000 + static_cast<int>(e);
+  }
+  return 0;
+}
+
+// Caller-provided scratch of at least tyr_newton_schulz_scratch_bytes(batch, R, C) bytes.
+extern "C" TYR_EXPORT int tyr_newton_schulz_bf16(void* x, void* scratch, long long scratch_bytes,
+                                                 int batch, int R, int C, int iters, float a, float b,
+                                                 float c, int* err, void* stream) {
+  if (batch <= 0 || R <= 0 || C <= 0 || iters < 0 || (R & 7) || (C & 7)) return -1;
+  if (scratch_bytes < tyr_newton_schulz_scratch_bytes(batch, R, C)) return -7;
+  if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(scratch) & 15)) return -2;
+  return ns_chain(x, scratch, batch, R, C, iters, a, b, c, err, stream);
+}

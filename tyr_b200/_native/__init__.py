@@ -102,6 +102,8 @@ def _declare_kernels(lib):
     P = c_void_p
     _sig(lib, "tyr_gemm_bf16", [ctypes.POINTER(GemmArgs)])
     _sig(lib, "tyr_bind_device", [c_int])
+    _sig(lib, "tyr_newton_schulz_scratch_bytes", [c_int, c_int, c_int], c_ll)
+    _sig(lib, "tyr_newton_schulz_bf16", [P, P, c_ll, c_int, c_int, c_int, c_int, c_float, c_float, c_float, P, P])
     _sig(lib, "tyr_lincomb_rmsnorm_fwd", [P, P, P, P, P, c_int, c_int, c_int, P, P, c_float, P])
     _sig(lib, "tyr_lincomb_rmsnorm_bwd",
          [ctypes.POINTER(P), ctypes.POINTER(P), P, P, P, P, P, c_int, c_int, c_int, c_float, P])

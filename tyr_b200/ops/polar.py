@@ -61,8 +61,33 @@ def _tall_step(g: torch.Tensor, a: float, b: float, c: float) -> torch.Tensor:
     return a * g + g @ Bm
 
 
+_scratch = {}
+
+
+def _native_chain(x: torch.Tensor, num_iters: int) -> torch.Tensor:
+    """All iterations through one native call (csrc/gemm_tcgen05.cu: tyr_newton_schulz_bf16);
+    the scratch buffer is cached per (device, size)."""
+    from ._common import check, cur_stream, err_word, lib, ptr
+    xb = x if x.dim() == 3 else x.unsqueeze(0)
+    B, R, C = xb.shape
+    out = xb.contiguous().clone()
+    need = lib().tyr_newton_schulz_scratch_bytes(B, R, C)
+    key = (x.device.index, need)
+    buf = _scratch.get(key)
+    if buf is None:
+        buf = torch.empty(need, dtype=torch.uint8, device=x.device)
+        _scratch.clear()
+        _scratch[key] = buf
+    a, b, c = MUON_COEFFS
+    check(lib().tyr_newton_schulz_bf16(ptr(out), ptr(buf), need, B, R, C, num_iters, a, b, c,
+                                       ptr(err_word(x.device)), cur_stream(x.device)), "newton_schulz")
+    return out if x.dim() == 3 else out[0]
+
+
 def newton_schulz_(x: torch.Tensor, num_iters: int, coeffs=None) -> torch.Tensor:
     """Iterate on an already normalised bf16 matrix (or stacked batch)."""
+    if coeffs is None and _use_native(x) and x.dtype == torch.bfloat16:
+        return _native_chain(x, num_iters)
     tall = x.shape[-2] > x.shape[-1]
     for i in range(num_iters):
         a, b, c = coeffs[i] if coeffs is not None else MUON_COEFFS
