@@ -585,3 +585,46 @@ extern "C" TYR_EXPORT int tyr_newton_schulz_bf16(void* x, void* scratch, long lo
   if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(scratch) & 15)) return -2;
   return ns_chain(x, scratch, batch, R, C, iters, a, b, c, err, stream);
 }
+
+// ----------------------------------------------------------------------------------------
+// Allocation-free variant (declared in no_alloc.h): temporaries in a file-scope device array.
+// ----------------------------------------------------------------------------------------
+#include "no_alloc.h"
+
+static __device__ __align__(256) unsigned char g_ns_static_scratch[TYR_NS_STATIC_SCRATCH_BYTES];
+
+namespace {
+constexpr int kMaxDevices = 64;
+void* g_ns_static_ptr[kMaxDevices] = {nullptr};
+std::mutex g_ns_static_mu;
+
+// `g_ns_static_scratch` is only a host-side handle here; the address a kernel can use has to be
+// asked for, per device, with that device current.
+int ns_static_address(void** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return 9000 + static_cast<int>(e);
+  if (dev < 0 || dev >= kMaxDevices) return 9000;
+  std::lock_guard<std::mutex> lock(g_ns_static_mu);
+  if (g_ns_static_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_ns_static_scratch);
+    if (e != cudaSuccess) return 9000 + static_cast<int>(e);
+    g_ns_static_ptr[dev] = p;
+  }
+  *out = g_ns_static_ptr[dev];
+  return 0;
+}
+}  // namespace
+
+extern "C" TYR_EXPORT int tyr_newton_schulz_bf16_static(void* x, int batch, int R, int C, int iters,
+                                                        float a, float b, float c, int* err,
+                                                        void* stream) {
+  if (batch <= 0 || R <= 0 || C <= 0 || iters < 0 || (R & 7) || (C & 7)) return -1;
+  if (reinterpret_cast<uintptr_t>(x) & 15) return -2;
+  if (tyr_newton_schulz_scratch_bytes(batch, R, C) > TYR_NS_STATIC_SCRATCH_BYTES) return -8;
+  void* scratch = nullptr;
+  int rc = ns_static_address(&scratch);
+  if (rc) return rc;
+  return ns_chain(x, scratch, batch, R, C, iters, a, b, c, err, stream);
+}
