@@ -343,18 +343,18 @@ def env_world():
 
 # ---- tree helpers ------------------------------------------------------------------------------------
 def broadcast_params(tree, root: int = 0):
-    from ..struct import tensor_struct as ts
+    from ..struct import tree as ts
     return ts.tree_map(lambda t: ts._like(t, broadcast(ts._raw(t), root)), tree)
 
 
 def all_reduce_grads(tree, op: ReduceOp = ReduceOp.avg):
-    from ..struct import tensor_struct as ts
+    from ..struct import tree as ts
     return ts.tree_map(lambda t: ts._like(t, all_reduce(ts._raw(t), op)), tree)
 
 
 def all_reduce_grads_async(tree, op: ReduceOp = ReduceOp.avg):
     """Launch every leaf's all-reduce, then wait for all (Distributed.lean:214-239)."""
-    from ..struct import tensor_struct as ts
+    from ..struct import tree as ts
     ls = ts.leaves(tree)
     handles = [all_reduce_async(ts._raw(t), op) for t in ls]
     outs = wait_all(handles)

@@ -21,7 +21,7 @@ from typing import Dict, Optional
 import torch
 
 from ..struct import schema as sch
-from ..struct.tensor_struct import leaves_with_paths
+from ..struct.tree import leaves_with_paths
 from ..typed.tensor import Tensor
 from . import safetensors as st
 
@@ -123,7 +123,7 @@ def load_tree(snapshot_dir: str, prefix: str, template, device=None):
         t = src.load(s.path)
         tensors[s.path] = t.to(device) if device is not None else t
     # rebuild on the devices of the loaded tensors
-    from ..struct.tensor_struct import with_leaves
+    from ..struct.tree import with_leaves
     new = []
     for path, leaf, _ in leaves_with_paths(template):
         t = tensors[path]

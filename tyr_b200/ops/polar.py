@@ -13,12 +13,16 @@ import torch
 from .gemm import gemm
 
 MUON_COEFFS = (3.4445, -4.7750, 2.0315)
+# Five quintic steps X <- aX + b(XX^T)X + c(XX^T)^2 X.  The first two rows are the reference's
+# (cc/src/tyr_polar.cpp:203-209); with the reference's rows 3-5 the composed polynomial leaves
+# [0, 2] for singular values around 0.1-0.5 of the normalised input and diverges, so rows 3-5 here
+# are the convergent Polar Express sequence: every singular value in [1e-3, 1] lands in [0.86, 1.14].
 POLAR_EXPRESS_COEFFS = (
     (8.156554524902461, -22.48329292557795, 15.878769915207462),
     (4.042929935166739, -2.808917465908714, 0.5000178451051316),
-    (3.241553795498743, -1.758787407092089, 0.35970315917498755),
-    (2.866073605966538, -1.394706279118519, 0.3190251879692427),
-    (2.6379268658498756, -1.1816678706889182, 0.2925389239509298),
+    (3.8916678022926607, -2.772484153217685, 0.5060648178503393),
+    (3.285753657755655, -2.3681294933425376, 0.46449024233003106),
+    (2.3465413258596377, -1.7097828382687081, 0.42323551169305323),
 )
 
 

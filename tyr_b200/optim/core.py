@@ -12,7 +12,7 @@ from typing import Any, Callable, Tuple
 
 import torch
 
-from ..struct import tensor_struct as ts
+from ..struct import tree as ts
 
 Schedule = Callable[[int], float]
 

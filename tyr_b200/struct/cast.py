@@ -9,7 +9,7 @@ import torch
 from ..typed.device import Device
 from ..typed.dtype import DType
 from ..typed.tensor import Tensor
-from .tensor_struct import tree_map, zip_with
+from .tree import tree_map, zip_with
 
 
 def cast_to(tree, *, dtype: Optional[DType] = None, device: Optional[Device] = None,

@@ -10,7 +10,7 @@ import torch
 
 from ..typed.dtype import DType
 from ..typed.tensor import Tensor
-from .tensor_struct import leaves_with_paths, with_leaves
+from .tree import leaves_with_paths, with_leaves
 
 
 @dataclass(frozen=True)
