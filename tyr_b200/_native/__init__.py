@@ -137,6 +137,8 @@ def register_signatures(fn):
 
 
 def _declare_host(lib):
+    if hasattr(lib, "tyr_host_last_error"):
+        lib.tyr_host_last_error.restype = ctypes.c_char_p
     for fn in _extra_host_sigs:
         fn(lib)
 

@@ -1,0 +1,275 @@
+"""Byte-level BPE tokenizer (Tyr/Tokenizer/{Types,Encode,Decode,Training,IO,Pretokenize,
+SpecialTokens,TokenBytes}.lean): training (`train_bpe`, Training.lean:211), encode/decode with
+special tokens, the GPT-4 split pattern (IO.lean:23), the `TYR_BPE1` binary format (IO.lean:19-197:
+magic, u32 version / vocab / merges / specials, u16-length-prefixed token bytes, u32 merge triples,
+specials as u16 length + utf-8 + u32 id) and the bytes-per-token table used for bits-per-byte
+evaluation (TokenBytes.lean:25-135).
+"""
+from __future__ import annotations
+
+import struct
+from collections import Counter
+from dataclasses import dataclass, field
+from typing import Dict, Iterable, List, Optional, Sequence, Tuple
+
+try:
+    import regex as _re
+except ImportError:  # pragma: no cover
+    import re as _re
+
+MAGIC = b"TYR_BPE1"
+FORMAT_VERSION = 1
+
+GPT4_SPLIT_PATTERN = (r"'(?i:[sdmt]|ll|ve|re)|[^\r\n\p{L}\p{N}]?+\p{L}+|\p{N}{1,3}| ?[^\s\p{L}\p{N}]++[\r\n]*|"
+                      r"\s*[\r\n]|\s+(?!\S)|\s+")
+DEFAULT_SPECIAL_TOKENS = ["<|bos|>", "<|user_start|>", "<|user_end|>", "<|assistant_start|>", "<|assistant_end|>",
+                          "<|python_start|>", "<|python_end|>", "<|output_start|>", "<|output_end|>"]
+
+
+def pretokenize(text: str, pattern: str = GPT4_SPLIT_PATTERN) -> List[str]:
+    return _re.findall(pattern, text)
+
+
+@dataclass
+class MergeRule:
+    left: int
+    right: int
+    result: int
+
+
+class BPETokenizer:
+    def __init__(self, id_to_bytes: List[bytes], merges: List[MergeRule], special_tokens: Optional[Dict[str, int]] = None,
+                 pattern: str = GPT4_SPLIT_PATTERN):
+        self.id_to_bytes = list(id_to_bytes)
+        self.merges = list(merges)
+        self.special_tokens = dict(special_tokens or {})
+        self.id_to_special = {v: k for k, v in self.special_tokens.items()}
+        self.pattern = pattern
+        self.bytes_to_id = {b: i for i, b in enumerate(self.id_to_bytes) if b}
+        self.merge_lookup = {(m.left, m.right): m.result for m in self.merges}
+        self.merge_priority = {(m.left, m.right): i for i, m in enumerate(self.merges)}
+        self._cache: Dict[str, List[int]] = {}
+
+    @property
+    def vocab_size(self) -> int:
+        return max(len(self.id_to_bytes), max(self.special_tokens.values(), default=-1) + 1)
+
+    @staticmethod
+    def byte_level() -> "BPETokenizer":
+        return BPETokenizer([bytes([i]) for i in range(256)], [])
+
+    # -- encoding ------------------------------------------------------------------------------------------
+    def _encode_chunk(self, chunk: str) -> List[int]:
+        hit = self._cache.get(chunk)
+        if hit is not None:
+            return hit
+        ids = [self.bytes_to_id[bytes([b])] for b in chunk.encode("utf-8")]
+        while len(ids) >= 2:
+            best, best_rank = None, None
+            for i in range(len(ids) - 1):
+                r = self.merge_priority.get((ids[i], ids[i + 1]))
+                if r is not None and (best_rank is None or r < best_rank):
+                    best, best_rank = i, r
+            if best is None:
+                break
+            pair = (ids[best], ids[best + 1])
+            new, out, i = self.merge_lookup[pair], [], 0
+            while i < len(ids):
+                if i < len(ids) - 1 and (ids[i], ids[i + 1]) == pair:
+                    out.append(new)
+                    i += 2
+                else:
+                    out.append(ids[i])
+                    i += 1
+            ids = out
+        if len(self._cache) < 200000:
+            self._cache[chunk] = ids
+        return ids
+
+    def encode_ordinary(self, text: str) -> List[int]:
+        out: List[int] = []
+        for chunk in pretokenize(text, self.pattern):
+            out.extend(self._encode_chunk(chunk))
+        return out
+
+    def encode(self, text: str, allowed_special: bool = True, prepend: Optional[str] = None,
+               append: Optional[str] = None) -> List[int]:
+        out: List[int] = []
+        if prepend is not None:
+            out.append(self.encode_special(prepend))
+        if allowed_special and self.special_tokens:
+            pat = "(" + "|".join(_re.escape(s) for s in sorted(self.special_tokens, key=len, reverse=True)) + ")"
+            for part in _re.split(pat, text):
+                if part in self.special_tokens:
+                    out.append(self.special_tokens[part])
+                elif part:
+                    out.extend(self.encode_ordinary(part))
+        else:
+            out.extend(self.encode_ordinary(text))
+        if append is not None:
+            out.append(self.encode_special(append))
+        return out
+
+    def encode_special(self, token: str) -> int:
+        if token not in self.special_tokens:
+            raise KeyError(f"unknown special token {token!r}")
+        return self.special_tokens[token]
+
+    def get_bos_token_id(self) -> int:
+        for name in ("<|bos|>", "<|endoftext|>"):
+            if name in self.special_tokens:
+                return self.special_tokens[name]
+        raise KeyError("tokenizer has no BOS token")
+
+    def encode_batch(self, texts: Sequence[str], **kw) -> List[List[int]]:
+        return [self.encode(t, **kw) for t in texts]
+
+    # -- decoding ------------------------------------------------------------------------------------------
+    def decode_bytes(self, ids: Iterable[int]) -> bytes:
+        out = bytearray()
+        for i in ids:
+            if i in self.id_to_special:
+                out += self.id_to_special[i].encode("utf-8")
+            elif 0 <= i < len(self.id_to_bytes):
+                out += self.id_to_bytes[i]
+            else:
+                raise ValueError(f"token id {i} outside the vocabulary")
+        return bytes(out)
+
+    def decode(self, ids: Iterable[int]) -> str:
+        return self.decode_bytes(ids).decode("utf-8", errors="replace")
+
+    def token_bytes(self) -> List[int]:
+        """Byte length of every token id (0 for special tokens): the bits-per-byte denominator."""
+        n = self.vocab_size
+        out = [0] * n
+        for i, b in enumerate(self.id_to_bytes):
+            out[i] = len(b)
+        for i in self.id_to_special:
+            if i < n:
+                out[i] = 0
+        return out
+
+    # -- binary format -------------------------------------------------------------------------------------
+    def serialize(self) -> bytes:
+        entries = max(self.vocab_size if not self.special_tokens else len(self.id_to_bytes), len(self.id_to_bytes))
+        out = bytearray(MAGIC)
+        out += struct.pack("<IIII", FORMAT_VERSION, entries, len(self.merges), len(self.special_tokens))
+        for i in range(entries):
+            b = self.id_to_bytes[i] if i < len(self.id_to_bytes) else b""
+            if len(b) > 65535:
+                raise ValueError(f"token byte length {len(b)} exceeds UInt16 range for token id {i}")
+            out += struct.pack("<H", len(b)) + b
+        for m in self.merges:
+            out += struct.pack("<III", m.left, m.right, m.result)
+        for s, i in self.special_tokens.items():
+            sb = s.encode("utf-8")
+            out += struct.pack("<H", len(sb)) + sb + struct.pack("<I", i)
+        return bytes(out)
+
+    @staticmethod
+    def deserialize(data: bytes) -> "BPETokenizer":
+        if len(data) < 24 or data[:8] != MAGIC:
+            raise ValueError("not a TYR_BPE1 tokenizer file")
+        ver, vocab, nm, ns = struct.unpack_from("<IIII", data, 8)
+        if ver != FORMAT_VERSION:
+            raise ValueError(f"unsupported tokenizer format version {ver}")
+        off = 24
+        id_to_bytes = []
+        for _ in range(vocab):
+            if off + 2 > len(data):
+                raise ValueError("truncated tokenizer file (vocabulary)")
+            (ln,) = struct.unpack_from("<H", data, off)
+            off += 2
+            if off + ln > len(data):
+                raise ValueError("truncated tokenizer file (token bytes)")
+            id_to_bytes.append(data[off:off + ln])
+            off += ln
+        merges = []
+        for _ in range(nm):
+            if off + 12 > len(data):
+                raise ValueError("truncated tokenizer file (merges)")
+            l, r, res = struct.unpack_from("<III", data, off)
+            merges.append(MergeRule(l, r, res))
+            off += 12
+        specials = {}
+        for _ in range(ns):
+            (ln,) = struct.unpack_from("<H", data, off)
+            off += 2
+            s = data[off:off + ln].decode("utf-8")
+            off += ln
+            (i,) = struct.unpack_from("<I", data, off)
+            off += 4
+            specials[s] = i
+        return BPETokenizer(id_to_bytes, merges, specials)
+
+    def save(self, path: str) -> None:
+        with open(path, "wb") as f:
+            f.write(self.serialize())
+
+    @staticmethod
+    def load(path: str) -> "BPETokenizer":
+        with open(path, "rb") as f:
+            return BPETokenizer.deserialize(f.read())
+
+
+def train_bpe(texts: Iterable[str], vocab_size: int, special_tokens: Optional[Sequence[str]] = None,
+              pattern: str = GPT4_SPLIT_PATTERN, doc_cap: Optional[int] = None, max_chars: Optional[int] = None) -> BPETokenizer:
+    """Classic BPE over pre-tokenised chunks with incremental pair counts.  ``vocab_size`` includes
+    the 256 byte tokens and the special tokens."""
+    specials = list(special_tokens if special_tokens is not None else [])
+    n_merges = vocab_size - 256 - len(specials)
+    if n_merges < 0:
+        raise ValueError("vocab_size must be at least 256 + number of special tokens")
+    words: Counter = Counter()
+    seen = 0
+    for t in texts:
+        if doc_cap is not None:
+            t = t[:doc_cap]
+        if max_chars is not None:
+            if seen >= max_chars:
+                break
+            t = t[:max_chars - seen]
+        seen += len(t)
+        words.update(pretokenize(t, pattern))
+    seqs = [list(w.encode("utf-8")) for w in words]
+    freqs = [words[w] for w in words]
+    pair_counts: Counter = Counter()
+    where: Dict[Tuple[int, int], set] = {}
+    for wi, s in enumerate(seqs):
+        for a, b in zip(s, s[1:]):
+            pair_counts[(a, b)] += freqs[wi]
+            where.setdefault((a, b), set()).add(wi)
+    id_to_bytes = [bytes([i]) for i in range(256)]
+    merges: List[MergeRule] = []
+    for _ in range(n_merges):
+        if not pair_counts:
+            break
+        best = max(pair_counts.items(), key=lambda kv: (kv[1], -kv[0][0], -kv[0][1]))
+        (a, b), c = best
+        if c <= 0:
+            break
+        new_id = len(id_to_bytes)
+        id_to_bytes.append(id_to_bytes[a] + id_to_bytes[b])
+        merges.append(MergeRule(a, b, new_id))
+        for wi in list(where.get((a, b), ())):
+            s, f = seqs[wi], freqs[wi]
+            for x, y in zip(s, s[1:]):
+                pair_counts[(x, y)] -= f
+                if pair_counts[(x, y)] <= 0:
+                    del pair_counts[(x, y)]
+            out, i = [], 0
+            while i < len(s):
+                if i < len(s) - 1 and s[i] == a and s[i + 1] == b:
+                    out.append(new_id)
+                    i += 2
+                else:
+                    out.append(s[i])
+                    i += 1
+            seqs[wi] = out
+            for x, y in zip(out, out[1:]):
+                pair_counts[(x, y)] += f
+                where.setdefault((x, y), set()).add(wi)
+        where.pop((a, b), None)
+    special_map = {s: len(id_to_bytes) + i for i, s in enumerate(specials)}
+    return BPETokenizer(id_to_bytes, merges, special_map, pattern)
