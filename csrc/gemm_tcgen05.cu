@@ -35,9 +35,15 @@ struct GemmParams {
   const __nv_bfloat16* aux;
   long long ldc, ldaux, sC, sAux;
   float alpha, beta;
-  int act;        // 0 none, 1 relu(x)^2, 2 relu, 3 acc * 2*sqrt(aux)
+  int act;        // 0 none, 1 relu(x)^2, 2 relu, 3 acc * 2*sqrt(aux), 4 SwiGLU of column halves
   int out_mode;   // 0 bf16 store, 1 fp32 store, 2 fp32 atomic add (stream-K)
   int* err;
+  // Grouped mode (MoE): batch = number of groups, A and C are packed [rows, *] with group g owning
+  // rows [group_offsets[g], group_offsets[g+1]).  group_tiles[g] is the exclusive prefix sum of
+  // ceil(rows_g / 128) (batch + 1 entries): the kernel walks exactly the non-empty m-tiles without
+  // the host ever reading the counts.
+  const int* group_offsets;
+  const int* group_tiles;
 };
 
 template <int BN, int STAGES>
@@ -76,7 +82,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
   const int tiles_m = (p.M + BM - 1) / BM;
   const int tiles_n = (p.N + BN - 1) / BN;
   const int num_kb = (p.K + BK - 1) / BK;
-  const long long tiles = static_cast<long long>(tiles_m) * tiles_n * p.batch;
+  const bool grouped = p.group_offsets != nullptr;
+  const long long tiles = grouped ? static_cast<long long>(p.group_tiles[p.batch]) * tiles_n
+                                  : static_cast<long long>(tiles_m) * tiles_n * p.batch;
 
   // Work range for this CTA, in (tile, k-block) units.
   long long unit_begin, unit_end;
@@ -133,6 +141,19 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     }
   };
   auto decode_tile = [&](long long tile, int& bi, int& m0, int& n0) {
+    if (grouped) {
+      // m-tile index over all groups -> owning group by binary search in the prefix table
+      const int mt = static_cast<int>(tile / tiles_n);
+      int lo = 0, hi = p.batch;                       // invariant: group_tiles[lo] <= mt < group_tiles[hi]
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (p.group_tiles[mid] <= mt) lo = mid; else hi = mid;
+      }
+      bi = lo;
+      m0 = (mt - p.group_tiles[lo]) * BM;
+      n0 = static_cast<int>(tile % tiles_n) * BN;
+      return;
+    }
     const int per_batch = tiles_m * tiles_n;
     bi = static_cast<int>(tile / per_batch);
     const int r = static_cast<int>(tile % per_batch);
@@ -164,7 +185,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           mbar_expect_tx(&s.full[st], kStageBytes);
           const int k0 = kb * BK;
           if (!A_MN) {
-            tma_load_3d(s.a[st], &tmA, &s.full[st], k0, m0, bi);
+            if (p.group_offsets != nullptr)
+              tma_load_3d(s.a[st], &tmA, &s.full[st], k0, p.group_offsets[bi] + m0, 0);
+            else
+              tma_load_3d(s.a[st], &tmA, &s.full[st], k0, m0, bi);
           } else {
 #pragma unroll
             for (int c = 0; c < BM / 64; ++c)
@@ -250,12 +274,61 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
         break;
       }
       tc_fence_after();
-      const int row = m0 + quarter * 32 + lane;
+      int row = m0 + quarter * 32 + lane;
       const uint32_t t_row = tmem_base + buf * BN + (static_cast<uint32_t>(quarter * 32) << 16);
-      const bool row_ok = row < p.M;
-      const long long c_off = static_cast<long long>(bi) * p.sC + static_cast<long long>(row) * p.ldc;
-      const long long x_off =
-          static_cast<long long>(bi) * p.sAux + static_cast<long long>(row) * p.ldaux;
+      bool row_ok = row < p.M;
+      long long c_off, x_off;
+      if (p.group_offsets != nullptr) {
+        const int g0 = p.group_offsets[bi];
+        row_ok = row < p.group_offsets[bi + 1] - g0;
+        row += g0;
+        c_off = static_cast<long long>(row) * p.ldc;
+        x_off = static_cast<long long>(row) * p.ldaux;
+      } else {
+        c_off = static_cast<long long>(bi) * p.sC + static_cast<long long>(row) * p.ldc;
+        x_off = static_cast<long long>(bi) * p.sAux + static_cast<long long>(row) * p.ldaux;
+      }
+      if (p.act == 4) {
+        // SwiGLU over column halves of the tile: out[:, n0/2 + j] = silu(acc[:, j]) * acc[:, BN/2 + j]
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; ++c) {
+          uint32_t rg[32], ru[32];
+          tmem_ld_32x32(t_row + c * 32, rg);
+          tmem_ld_32x32(t_row + BN / 2 + c * 32, ru);
+          tmem_wait_ld();
+          if (c == BN / 64 - 1) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&s.acc_empty[buf]);
+          }
+          const int col = n0 / 2 + c * 32;
+          if (!row_ok || col >= p.N / 2) continue;
+          __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.C) + c_off + col;
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float g = p.alpha * __uint_as_float(rg[j]);
+            v[j] = g / (1.f + __expf(-g)) * (p.beta * __uint_as_float(ru[j]));
+          }
+          if (col + 32 <= p.N / 2) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 u;
+              u.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
+              u.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
+              u.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
+              u.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
+              *reinterpret_cast<uint4*>(out + q * 8) = u;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col + j < p.N / 2) out[j] = __float2bfloat16(v[j]);
+          }
+        }
+        ++seg;
+        continue;
+      }
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -417,6 +490,8 @@ struct TyrGemmArgs {
   int sm_count;                     // CTAs to launch (0 = all SMs)
   int* err;
   void* stream;
+  const int* group_offsets;         // grouped (MoE) mode, see GemmParams
+  const int* group_tiles;
 };
 
 }  // extern "C"
@@ -440,7 +515,11 @@ static int launch_gemm(const TyrGemmArgs& a, const CUtensorMap& tmA, const CUten
   p.C = a.C; p.aux = reinterpret_cast<const __nv_bfloat16*>(a.aux);
   p.ldc = a.ldc; p.ldaux = a.ldaux; p.sC = a.sC; p.sAux = a.sAux;
   p.alpha = a.alpha; p.beta = a.beta; p.act = a.act; p.out_mode = a.out_mode; p.err = a.err;
-  const long long tiles = static_cast<long long>((a.M + BM - 1) / BM) * ((a.N + BN - 1) / BN) * a.batch;
+  p.group_offsets = a.group_offsets;
+  p.group_tiles = a.group_tiles;
+  long long tiles = static_cast<long long>((a.M + BM - 1) / BM) * ((a.N + BN - 1) / BN) * a.batch;
+  if (a.group_offsets != nullptr)   // host-side bound: every group may add one partial m-tile
+    tiles = ((a.sA + BM - 1) / BM + (a.batch < a.sA ? a.batch : a.sA)) * ((a.N + BN - 1) / BN);
   int grid = a.sm_count > 0 ? a.sm_count : g_sm_count;
   if (a.out_mode != 2 && tiles < grid) grid = static_cast<int>(tiles);
   if (a.out_mode == 2) {
@@ -487,7 +566,10 @@ extern "C" TYR_EXPORT int tyr_gemm_bf16(const TyrGemmArgs* args) {
   if (bn == 0) bn = (a.N <= 128) ? 128 : 256;
   CUtensorMap tmA, tmB;
   int r;
-  if (!a.a_mn)
+  if (a.group_offsets != nullptr) {
+    if (a.a_mn || a.out_mode == 2 || a.sA <= 0 || a.group_tiles == nullptr) return -9;   // packed rows: K-major A, sA = total rows
+    r = make_tmap_bf16_3d(&tmA, a.A, a.K, static_cast<uint64_t>(a.sA), 1, a.lda, 0, BM);
+  } else if (!a.a_mn)
     r = make_tmap_bf16_3d(&tmA, a.A, a.K, a.M, a.batch, a.lda, a.sA, BM);
   else
     r = make_tmap_bf16_3d(&tmA, a.A, a.M, a.K, a.batch, a.lda, a.sA, BK);

@@ -1,0 +1,510 @@
+// NVFP4 mixture-of-experts kernels.
+//
+// Weight format (the reference's, Tyr/Model/Laguna/NvFp4.lean:44-72): e2m1 values packed two per
+// byte (low nibble = even element), one e4m3 scale per 16 elements, one fp32 global scale per
+// expert;  w = e2m1(nibble) * (e4m3(scale) / global).
+//
+//  * nvfp4_quantize / nvfp4_dequant: bf16 <-> packed banks (dequant is exact: fp32 product rounded
+//    once to bf16, like the reference's LUT + embedding graph).
+//  * moe_route: softcap -> sigmoid | softmax -> selection bias -> top-k -> renormalise -> scale, plus
+//    per-expert counts; moe_layout: offsets + expert-major pair order.  No host synchronisation
+//    (the reference's sm_12x path reads a row count back to the host,
+//    cc/src/tyr_laguna_moe.cu:1054-1068; its SIMT path builds the layout with a <<<1,1>>> kernel).
+//  * moe_fp4_stage_a / stage_b: weight-streaming grouped GEMV for decode-sized batches.  A CTA owns
+//    (expert, row tile) and walks that expert's (token, slot) pairs eight at a time, so every
+//    packed weight row is read once per eight pairs and decoded in registers; the reference's
+//    stage_a/stage_b (:175-335) read the row once per pair.
+//  * Prefill-sized batches dequantise the banks of the experts in use into a bf16 scratch and run
+//    the grouped tcgen05 GEMM (gemm_tcgen05.cu, group offsets) with the SwiGLU in its epilogue.
+#include "common.cuh"
+#include <cuda_fp8.h>
+
+namespace tyr {
+
+__constant__ float kE2M1[16] = {0.f, 0.5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f,
+                                -0.f, -0.5f, -1.f, -1.5f, -2.f, -3.f, -4.f, -6.f};
+
+__device__ __forceinline__ float e4m3_to_float(uint8_t b) {
+  __half_raw h = __nv_cvt_fp8_to_halfraw(b, __NV_E4M3);
+  return __half2float(*reinterpret_cast<__half*>(&h));
+}
+__device__ __forceinline__ uint8_t float_to_e4m3(float v) {
+  return __nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3);
+}
+// round-to-nearest-even onto the e2m1 grid {0, .5, 1, 1.5, 2, 3, 4, 6} (saturating)
+__device__ __forceinline__ uint8_t float_to_e2m1(float v) {
+  const float a = fabsf(v);
+  uint8_t m;
+  if (a <= 0.25f) m = 0;
+  else if (a < 0.75f) m = 1;
+  else if (a <= 1.25f) m = 2;
+  else if (a < 1.75f) m = 3;
+  else if (a <= 2.5f) m = 4;
+  else if (a < 3.5f) m = 5;
+  else if (a <= 5.0f) m = 6;
+  else m = 7;
+  return m | (v < 0.f ? 8 : 0);
+}
+
+// ---------------------------------------------------------------------------------------------
+// quantise: one thread per 16-element block
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+nvfp4_quantize_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ packed,
+                      uint8_t* __restrict__ scales, const float* __restrict__ global_scale,
+                      long long blocks_per_mat, long long total_blocks) {
+  for (long long b = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; b < total_blocks;
+       b += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const float G = global_scale[b / blocks_per_mat];
+    const __nv_bfloat16* src = x + b * 16;
+    float v[16];
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      uint4 u = *reinterpret_cast<const uint4*>(src + i * 8);
+      float2 p0 = unpack_bf16x2(u.x), p1 = unpack_bf16x2(u.y), p2 = unpack_bf16x2(u.z), p3 = unpack_bf16x2(u.w);
+      v[i * 8 + 0] = p0.x; v[i * 8 + 1] = p0.y; v[i * 8 + 2] = p1.x; v[i * 8 + 3] = p1.y;
+      v[i * 8 + 4] = p2.x; v[i * 8 + 5] = p2.y; v[i * 8 + 6] = p3.x; v[i * 8 + 7] = p3.y;
+    }
+#pragma unroll
+    for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    const uint8_t sb = float_to_e4m3(amax / 6.f * G);
+    const float s = e4m3_to_float(sb);
+    scales[b] = sb;
+    const float inv = s > 0.f ? G / s : 0.f;
+    uint8_t out[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      out[i] = float_to_e2m1(v[2 * i] * inv) | (float_to_e2m1(v[2 * i + 1] * inv) << 4);
+    *reinterpret_cast<uint2*>(packed + b * 8) = *reinterpret_cast<uint2*>(out);
+  }
+}
+
+// dequantise: one thread per 16-element block; `expert_map` (nullable) selects source experts
+__global__ void __launch_bounds__(256)
+nvfp4_dequant_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ scales,
+                     const float* __restrict__ global_scale, __nv_bfloat16* __restrict__ out,
+                     long long blocks_per_mat, long long total_blocks) {
+  for (long long b = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; b < total_blocks;
+       b += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const float sd = e4m3_to_float(scales[b]) / global_scale[b / blocks_per_mat];
+    uint2 raw = *reinterpret_cast<const uint2*>(packed + b * 8);
+    const uint8_t* by = reinterpret_cast<const uint8_t*>(&raw);
+    uint32_t w[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) w[i] = pack_bf16x2(sd * kE2M1[by[i] & 15], sd * kE2M1[by[i] >> 4]);
+    uint4* dst = reinterpret_cast<uint4*>(out + b * 16);
+    dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+    dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// routing: one warp per token, E <= 512
+// ---------------------------------------------------------------------------------------------
+struct RouteArgs {
+  const float* logits;   // [T, E]
+  const float* bias;     // [E] selection bias (nullable)
+  int* ids;              // [T, k]
+  float* weights;        // [T, k]
+  int* counts;           // [E] (zero on entry)
+  int T, E, k;
+  int softmax;           // 0 = sigmoid scores, 1 = softmax scores
+  int renorm;
+  float softcap, scale;
+};
+
+__global__ void __launch_bounds__(256) moe_route_kernel(RouteArgs a) {
+  const int lane = threadIdx.x & 31;
+  const int tok = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (tok >= a.T) return;
+  constexpr int kMaxPer = 16;   // E <= 512
+  float score[kMaxPer], sel[kMaxPer];
+  const int per = (a.E + 31) / 32;
+  float mx = -INFINITY;
+  for (int j = 0; j < kMaxPer; ++j) {
+    const int e = lane + 32 * j;
+    float l = (j < per && e < a.E) ? a.logits[static_cast<long long>(tok) * a.E + e] : -INFINITY;
+    if (a.softcap > 0.f && l != -INFINITY) l = a.softcap * tanhf(l / a.softcap);
+    score[j] = l;
+    mx = fmaxf(mx, l);
+  }
+  if (a.softmax) {
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int j = 0; j < kMaxPer; ++j) {
+      score[j] = score[j] == -INFINITY ? 0.f : __expf(score[j] - mx);
+      sum += score[j];
+    }
+    sum = warp_sum(sum);
+    for (int j = 0; j < kMaxPer; ++j) score[j] /= sum;
+  } else {
+    for (int j = 0; j < kMaxPer; ++j) score[j] = score[j] == -INFINITY ? 0.f : 1.f / (1.f + __expf(-score[j]));
+  }
+  for (int j = 0; j < kMaxPer; ++j) {
+    const int e = lane + 32 * j;
+    sel[j] = (j < per && e < a.E) ? score[j] + (a.bias ? a.bias[e] : 0.f) : -INFINITY;
+  }
+  float wsum = 0.f;
+  float my_w = 0.f;
+  int my_id = 0;
+  for (int s = 0; s < a.k; ++s) {
+    // warp argmax (ties -> lowest expert index, like a stable top-k)
+    float best = -INFINITY;
+    int best_e = 0x7fffffff;
+    for (int j = 0; j < kMaxPer; ++j) {
+      const int e = lane + 32 * j;
+      if (sel[j] > best || (sel[j] == best && e < best_e)) { best = sel[j]; best_e = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+      if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+    }
+    // owner lane fetches the unbiased score and retires the entry
+    float sc = 0.f;
+    if ((best_e & 31) == lane) {
+      const int j = best_e >> 5;
+      for (int q = 0; q < kMaxPer; ++q)
+        if (q == j) { sc = score[q]; sel[q] = -INFINITY; }
+    }
+    sc = __shfl_sync(0xffffffffu, sc, best_e & 31);
+    wsum += sc;
+    if (lane == s) { my_w = sc; my_id = best_e; }
+  }
+  if (lane < a.k) {
+    const float w = (a.renorm ? my_w / wsum : my_w) * a.scale;
+    a.ids[static_cast<long long>(tok) * a.k + lane] = my_id;
+    a.weights[static_cast<long long>(tok) * a.k + lane] = w;
+    if (a.counts) atomicAdd(a.counts + my_id, 1);
+  }
+}
+
+// offsets[E+1] from counts[E]; cursors[E] zeroed; tiles[E+1] (nullable) = prefix sum of
+// ceil(count / 128), the m-tile table of the grouped GEMM.  One block.
+__global__ void moe_offsets_kernel(const int* counts, int* offsets, int* cursors, int* tiles, int E) {
+  __shared__ int s[1024];
+  __shared__ int s2[1024];
+  const int t = threadIdx.x;
+  const int v = t < E ? counts[t] : 0;
+  s[t] = v;
+  s2[t] = (v + 127) >> 7;
+  __syncthreads();
+  for (int o = 1; o < blockDim.x; o <<= 1) {
+    const int add = t >= o ? s[t - o] : 0;
+    const int add2 = t >= o ? s2[t - o] : 0;
+    __syncthreads();
+    s[t] += add;
+    s2[t] += add2;
+    __syncthreads();
+  }
+  if (t < E) {
+    offsets[t + 1] = s[t];
+    if (tiles) tiles[t + 1] = s2[t];
+    cursors[t] = 0;
+  }
+  if (t == 0) {
+    offsets[0] = 0;
+    if (tiles) tiles[0] = 0;
+  }
+}
+
+// pair_order[offsets[e] + slot] = pair index (expert-major); slot order within an expert is arbitrary
+__global__ void moe_scatter_kernel(const int* ids, const int* offsets, int* cursors, int* pair_order,
+                                   int* pair_pos, int pairs, int E) {
+  for (int p = blockIdx.x * blockDim.x + threadIdx.x; p < pairs; p += gridDim.x * blockDim.x) {
+    int e = ids[p];
+    e = e < 0 ? 0 : (e >= E ? E - 1 : e);
+    const int slot = atomicAdd(cursors + e, 1);
+    const int pos = offsets[e] + slot;
+    pair_order[pos] = p;
+    if (pair_pos) pair_pos[p] = pos;
+  }
+}
+
+// gather rows: dst[pos] = src[pair_order[pos] / k]   (bf16 [pairs, h])
+__global__ void __launch_bounds__(256)
+moe_gather_rows_kernel(const __nv_bfloat16* src, const int* pair_order, __nv_bfloat16* dst, int pairs, int k, int h) {
+  const int vec = h >> 3;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+       i < static_cast<long long>(pairs) * vec; i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int pos = static_cast<int>(i / vec), c = static_cast<int>(i % vec);
+    const int tok = pair_order[pos] / k;
+    reinterpret_cast<uint4*>(dst + static_cast<long long>(pos) * h)[c] =
+        reinterpret_cast<const uint4*>(src + static_cast<long long>(tok) * h)[c];
+  }
+}
+
+// combine: out[tok] = sum over its k slots of w * y[pair_pos[pair]]   (+ optional residual add-in)
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(const __nv_bfloat16* y, const int* pair_pos, const float* weights, const __nv_bfloat16* add,
+                   __nv_bfloat16* out, int T, int k, int h) {
+  const int vec = h >> 3;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+       i < static_cast<long long>(T) * vec; i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int tok = static_cast<int>(i / vec), c = static_cast<int>(i % vec);
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int s = 0; s < k; ++s) {
+      const int pair = tok * k + s;
+      const float w = weights[pair];
+      uint4 u = reinterpret_cast<const uint4*>(y + static_cast<long long>(pair_pos[pair]) * h)[c];
+      float2 a0 = unpack_bf16x2(u.x), a1 = unpack_bf16x2(u.y), a2 = unpack_bf16x2(u.z), a3 = unpack_bf16x2(u.w);
+      acc[0] += w * a0.x; acc[1] += w * a0.y; acc[2] += w * a1.x; acc[3] += w * a1.y;
+      acc[4] += w * a2.x; acc[5] += w * a2.y; acc[6] += w * a3.x; acc[7] += w * a3.y;
+    }
+    if (add) {
+      uint4 u = reinterpret_cast<const uint4*>(add + static_cast<long long>(tok) * h)[c];
+      float2 a0 = unpack_bf16x2(u.x), a1 = unpack_bf16x2(u.y), a2 = unpack_bf16x2(u.z), a3 = unpack_bf16x2(u.w);
+      acc[0] += a0.x; acc[1] += a0.y; acc[2] += a1.x; acc[3] += a1.y;
+      acc[4] += a2.x; acc[5] += a2.y; acc[6] += a3.x; acc[7] += a3.y;
+    }
+    uint4 o;
+    o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
+    o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+    reinterpret_cast<uint4*>(out + static_cast<long long>(tok) * h)[c] = o;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// weight-streaming grouped GEMV (decode).  Block = 256 threads = 8 warps; CTA = (row tile, expert).
+// ---------------------------------------------------------------------------------------------
+constexpr int kP = 8;          // pairs per pass
+constexpr int kRowsA = 32;     // output rows per CTA (4 per warp)
+
+struct StageArgs {
+  const __nv_bfloat16* x;      // stage A: [T, h] activations; stage B: unused
+  const float* hid_in;         // stage B: [pairs, mi] fp32 (expert-major positions)
+  const uint8_t* w0;           // stage A: gate packed; stage B: down packed
+  const uint8_t* s0;
+  const float* g0;
+  const uint8_t* w1;           // stage A: up packed
+  const uint8_t* s1;
+  const float* g1;
+  const int* offsets;          // [E+1]
+  const int* pair_order;       // [pairs] pair index at each expert-major position
+  const float* pair_weight;    // [pairs] routing weight by pair index (stage B)
+  float* hid_out;              // stage A: [pairs, mi] fp32
+  float* out;                  // stage B: [T, h] fp32, atomically accumulated
+  int k, in_dim, out_dim;      // stage A: in = h, out = mi; stage B: in = mi, out = h
+};
+
+// decode 16 weights of one scale group and accumulate against P activation vectors held in smem
+template <typename XT>
+__device__ __forceinline__ void fma_group(const uint8_t* by, float sd, const XT* xs, int xstride, int col,
+                                          int np, float (&acc)[kP]) {
+  float w[16];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    w[2 * i] = sd * kE2M1[by[i] & 15];
+    w[2 * i + 1] = sd * kE2M1[by[i] >> 4];
+  }
+#pragma unroll
+  for (int p = 0; p < kP; ++p) {
+    if (p < np) {
+      const XT* xp = xs + p * xstride + col;
+      float a = 0.f;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) a += w[i] * static_cast<float>(xp[i]);
+      acc[p] += a;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) moe_fp4_stage_a_kernel(StageArgs a) {
+  extern __shared__ float xs[];          // [kP][in_dim] fp32
+  const int e = blockIdx.y;
+  const int begin = a.offsets[e], end = a.offsets[e + 1];
+  if (begin >= end) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row0 = blockIdx.x * kRowsA + warp * (kRowsA / 8);
+  const int groups = a.in_dim >> 4;                         // 16-element scale groups per row
+  const float inv_g = 1.f / a.g0[e], inv_u = 1.f / a.g1[e];
+  for (int base = begin; base < end; base += kP) {
+    const int np = min(kP, end - base);
+    __syncthreads();
+    for (int i = threadIdx.x; i < np * a.in_dim; i += blockDim.x) {
+      const int p = i / a.in_dim, c = i % a.in_dim;
+      const int tok = a.pair_order[base + p] / a.k;
+      xs[p * a.in_dim + c] = __bfloat162float(a.x[static_cast<long long>(tok) * a.in_dim + c]);
+    }
+    __syncthreads();
+    for (int r = 0; r < kRowsA / 8; ++r) {
+      const int row = row0 + r;
+      if (row >= a.out_dim) break;
+      float ag[kP], au[kP];
+#pragma unroll
+      for (int p = 0; p < kP; ++p) ag[p] = au[p] = 0.f;
+      const long long wrow = (static_cast<long long>(e) * a.out_dim + row) * (a.in_dim >> 1);
+      const long long srow = (static_cast<long long>(e) * a.out_dim + row) * groups;
+      for (int g = lane; g < groups; g += 32) {
+        uint2 bg = *reinterpret_cast<const uint2*>(a.w0 + wrow + g * 8);
+        uint2 bu = *reinterpret_cast<const uint2*>(a.w1 + wrow + g * 8);
+        fma_group(reinterpret_cast<const uint8_t*>(&bg), e4m3_to_float(a.s0[srow + g]), xs, a.in_dim, g * 16, np, ag);
+        fma_group(reinterpret_cast<const uint8_t*>(&bu), e4m3_to_float(a.s1[srow + g]), xs, a.in_dim, g * 16, np, au);
+      }
+#pragma unroll
+      for (int p = 0; p < kP; ++p) {
+        const float gsum = warp_sum(ag[p]) * inv_g;
+        const float usum = warp_sum(au[p]) * inv_u;
+        if (lane == 0 && p < np)
+          a.hid_out[static_cast<long long>(base + p) * a.out_dim + row] = gsum / (1.f + __expf(-gsum)) * usum;
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) moe_fp4_stage_b_kernel(StageArgs a) {
+  extern __shared__ float hs[];          // [kP][in_dim] fp32
+  const int e = blockIdx.y;
+  const int begin = a.offsets[e], end = a.offsets[e + 1];
+  if (begin >= end) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row0 = blockIdx.x * kRowsA + warp * (kRowsA / 8);
+  const int groups = a.in_dim >> 4;
+  const float inv_d = 1.f / a.g0[e];
+  for (int base = begin; base < end; base += kP) {
+    const int np = min(kP, end - base);
+    __syncthreads();
+    for (int i = threadIdx.x; i < np * a.in_dim; i += blockDim.x)
+      hs[i] = a.hid_in[static_cast<long long>(base) * a.in_dim + i];
+    __syncthreads();
+    for (int r = 0; r < kRowsA / 8; ++r) {
+      const int row = row0 + r;
+      if (row >= a.out_dim) break;
+      float ad[kP];
+#pragma unroll
+      for (int p = 0; p < kP; ++p) ad[p] = 0.f;
+      const long long wrow = (static_cast<long long>(e) * a.out_dim + row) * (a.in_dim >> 1);
+      const long long srow = (static_cast<long long>(e) * a.out_dim + row) * groups;
+      for (int g = lane; g < groups; g += 32) {
+        uint2 bd = *reinterpret_cast<const uint2*>(a.w0 + wrow + g * 8);
+        fma_group(reinterpret_cast<const uint8_t*>(&bd), e4m3_to_float(a.s0[srow + g]), hs, a.in_dim, g * 16, np, ad);
+      }
+#pragma unroll
+      for (int p = 0; p < kP; ++p) {
+        const float d = warp_sum(ad[p]) * inv_d;
+        if (lane == 0 && p < np) {
+          const int pair = a.pair_order[base + p];
+          atomicAdd(a.out + static_cast<long long>(pair / a.k) * a.out_dim + row, a.pair_weight[pair] * d);
+        }
+      }
+    }
+  }
+}
+
+// routed fp32 -> bf16 with optional add-in:  out = bf16(routed + add)
+__global__ void __launch_bounds__(256)
+moe_finalize_kernel(const float* routed, const __nv_bfloat16* add, __nv_bfloat16* out, long long n) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float v = routed[i];
+    if (add) v += __bfloat162float(add[i]);
+    out[i] = __float2bfloat16(v);
+  }
+}
+
+static int blocks_for(long long items, int cap = 148 * 8) {
+  long long b = (items + 255) / 256;
+  return static_cast<int>(b < 1 ? 1 : (b > cap ? cap : b));
+}
+
+}  // namespace tyr
+
+using namespace tyr;
+
+extern "C" TYR_EXPORT int tyr_nvfp4_quantize(const void* x, void* packed, void* scales, const float* global_scale,
+                                             long long mats, long long elems_per_mat, void* stream) {
+  if (mats <= 0 || elems_per_mat <= 0 || (elems_per_mat & 15)) return -1;
+  const long long bpm = elems_per_mat / 16;
+  nvfp4_quantize_kernel<<<blocks_for(mats * bpm), 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)x, (uint8_t*)packed, (uint8_t*)scales, global_scale, bpm, mats * bpm);
+  return (int)cudaGetLastError();
+}
+
+extern "C" TYR_EXPORT int tyr_nvfp4_dequant(const void* packed, const void* scales, const float* global_scale,
+                                            void* out, long long mats, long long elems_per_mat, void* stream) {
+  if (mats <= 0 || elems_per_mat <= 0 || (elems_per_mat & 15)) return -1;
+  const long long bpm = elems_per_mat / 16;
+  nvfp4_dequant_kernel<<<blocks_for(mats * bpm), 256, 0, (cudaStream_t)stream>>>(
+      (const uint8_t*)packed, (const uint8_t*)scales, global_scale, (__nv_bfloat16*)out, bpm, mats * bpm);
+  return (int)cudaGetLastError();
+}
+
+extern "C" TYR_EXPORT int tyr_moe_route(const float* logits, const float* bias, int* ids, float* weights, int* counts,
+                                        int T, int E, int k, int softmax, int renorm, float softcap, float scale,
+                                        void* stream) {
+  if (T <= 0 || E <= 0 || E > 512 || k <= 0 || k > 32 || k > E) return -1;
+  RouteArgs a{logits, bias, ids, weights, counts, T, E, k, softmax, renorm, softcap, scale};
+  moe_route_kernel<<<(T + 7) / 8, 256, 0, (cudaStream_t)stream>>>(a);
+  return (int)cudaGetLastError();
+}
+
+extern "C" TYR_EXPORT int tyr_moe_layout(const int* ids, const int* counts, int* offsets, int* cursors,
+                                         int* tiles, int* pair_order, int* pair_pos, int pairs, int E,
+                                         void* stream) {
+  if (pairs <= 0 || E <= 0 || E > 1024) return -1;
+  int threads = 32;
+  while (threads < E) threads <<= 1;
+  moe_offsets_kernel<<<1, threads, 0, (cudaStream_t)stream>>>(counts, offsets, cursors, tiles, E);
+  moe_scatter_kernel<<<blocks_for(pairs), 256, 0, (cudaStream_t)stream>>>(ids, offsets, cursors, pair_order,
+                                                                         pair_pos, pairs, E);
+  return (int)cudaGetLastError();
+}
+
+extern "C" TYR_EXPORT int tyr_moe_gather_rows(const void* src, const int* pair_order, void* dst, int pairs, int k,
+                                              int h, void* stream) {
+  if (pairs <= 0 || (h & 7)) return -1;
+  moe_gather_rows_kernel<<<blocks_for(1LL * pairs * (h / 8)), 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)src, pair_order, (__nv_bfloat16*)dst, pairs, k, h);
+  return (int)cudaGetLastError();
+}
+
+extern "C" TYR_EXPORT int tyr_moe_combine(const void* y, const int* pair_pos, const float* weights, const void* add,
+                                          void* out, int T, int k, int h, void* stream) {
+  if (T <= 0 || (h & 7)) return -1;
+  moe_combine_kernel<<<blocks_for(1LL * T * (h / 8)), 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)y, pair_pos, weights, (const __nv_bfloat16*)add, (__nv_bfloat16*)out, T, k, h);
+  return (int)cudaGetLastError();
+}
+
+// Decode path: routed[T, h] (fp32, zero on entry) += sum_k w * down(silu(gate x) * up x)
+extern "C" TYR_EXPORT int tyr_moe_fp4_gemv(const void* x, const void* gate_p, const void* gate_s, const float* gate_g,
+                                           const void* up_p, const void* up_s, const float* up_g,
+                                           const void* down_p, const void* down_s, const float* down_g,
+                                           const int* offsets, const int* pair_order, const float* pair_weight,
+                                           float* hid, float* routed, int E, int k, int h, int mi, void* stream) {
+  if ((h & 15) || (mi & 15) || E <= 0 || E > 65535) return -1;
+  cudaStream_t st = (cudaStream_t)stream;
+  StageArgs a{};
+  a.x = (const __nv_bfloat16*)x;
+  a.w0 = (const uint8_t*)gate_p; a.s0 = (const uint8_t*)gate_s; a.g0 = gate_g;
+  a.w1 = (const uint8_t*)up_p; a.s1 = (const uint8_t*)up_s; a.g1 = up_g;
+  a.offsets = offsets; a.pair_order = pair_order; a.pair_weight = pair_weight;
+  a.hid_out = hid; a.k = k; a.in_dim = h; a.out_dim = mi;
+  const size_t smem_a = sizeof(float) * kP * h;
+  static int cfg_a = 0, cfg_b = 0;
+  if (smem_a > 48 * 1024 && cfg_a < (int)smem_a) {
+    cudaFuncSetAttribute(moe_fp4_stage_a_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_a);
+    cfg_a = (int)smem_a;
+  }
+  moe_fp4_stage_a_kernel<<<dim3((mi + kRowsA - 1) / kRowsA, E), 256, smem_a, st>>>(a);
+  StageArgs b{};
+  b.hid_in = hid;
+  b.w0 = (const uint8_t*)down_p; b.s0 = (const uint8_t*)down_s; b.g0 = down_g;
+  b.offsets = offsets; b.pair_order = pair_order; b.pair_weight = pair_weight;
+  b.out = routed; b.k = k; b.in_dim = mi; b.out_dim = h;
+  const size_t smem_b = sizeof(float) * kP * mi;
+  if (smem_b > 48 * 1024 && cfg_b < (int)smem_b) {
+    cudaFuncSetAttribute(moe_fp4_stage_b_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_b);
+    cfg_b = (int)smem_b;
+  }
+  moe_fp4_stage_b_kernel<<<dim3((h + kRowsA - 1) / kRowsA, E), 256, smem_b, st>>>(b);
+  return (int)cudaGetLastError();
+}
+
+extern "C" TYR_EXPORT int tyr_moe_finalize(const float* routed, const void* add, void* out, long long n, void* stream) {
+  moe_finalize_kernel<<<blocks_for(n), 256, 0, (cudaStream_t)stream>>>(routed, (const __nv_bfloat16*)add,
+                                                                       (__nv_bfloat16*)out, n);
+  return (int)cudaGetLastError();
+}

@@ -1,0 +1,154 @@
+"""Laguna: config validation, rotary tables, cached vs uncached parity, ring caches, weight
+round trip, generation (mirrors Tests/RunLaguna{Rope,Moe,Model,Parity}.lean)."""
+import math
+
+import pytest
+import torch
+
+from tyr_b200.io import safetensors as st
+from tyr_b200.models import common as C
+from tyr_b200.models import generation as G
+from tyr_b200.models import laguna as L
+
+
+def tiny_cfg(**kw):
+    base = dict(vocab_size=97, hidden_size=64, intermediate_size=128, num_hidden_layers=5, num_attention_heads=4,
+                num_attention_heads_sliding=6, num_key_value_heads=2, head_dim=32, sliding_window=6,
+                half_rotary_dim_sliding=16, half_rotary_dim_full=8, num_experts=8, num_experts_per_tok=2,
+                moe_intermediate_size=32, shared_expert_intermediate_size=32,
+                yarn_original_max_position_embeddings=16, eos_token_ids=(2,))
+    base.update(kw)
+    return L.LagunaConfig(**base)
+
+
+def test_config_defaults_and_selectors():
+    cfg = L.LagunaConfig()
+    assert cfg.heads(0) == 48 and cfg.heads(1) == 72 and cfg.is_full(4) and not cfg.is_full(5)
+    assert not cfg.is_moe_layer(0) and cfg.is_moe_layer(1)
+    assert C.yarn_correction_range(64, cfg.rope_theta_full, 8192, 32.0, 1.0) == (9, 18)
+    with pytest.raises(ValueError, match="must be divisible by num_key_value_heads"):
+        tiny_cfg(num_attention_heads=5)
+    with pytest.raises(ValueError, match="layer_types has 2 entries"):
+        tiny_cfg(layer_types=[L.FULL, L.SLIDING])
+    with pytest.raises(ValueError, match="num_experts_per_tok=9"):
+        tiny_cfg(num_experts_per_tok=9)
+
+
+def test_config_from_json():
+    j = {"num_hidden_layers": 4, "hidden_size": 64, "vocab_size": 50, "head_dim": 32, "num_attention_heads": 4,
+         "num_attention_heads_per_layer": [4, 6, 6, 6], "num_key_value_heads": 2, "eos_token_id": 3,
+         "rope_parameters": {"full_attention": {"partial_rotary_factor": 0.5, "rope_theta": 1000.0, "factor": 4.0},
+                             "sliding_attention": {"partial_rotary_factor": 1.0}},
+         "num_experts": 4, "num_experts_per_tok": 2, "mlp_only_layers": [0]}
+    cfg = L.LagunaConfig.from_json(j)
+    assert cfg.num_attention_heads_sliding == 6 and cfg.half_rotary_dim_full == 8 and cfg.half_rotary_dim_sliding == 16
+    assert cfg.rope_theta_full == 1000.0 and cfg.yarn_factor == 4.0 and cfg.eos_token_ids == (3,)
+    j["num_attention_heads_per_layer"] = [4, 6, 8, 6]
+    with pytest.raises(ValueError, match="varies within sliding_attention layers"):
+        L.LagunaConfig.from_json(j)
+    with pytest.raises(ValueError, match="attention_bias"):
+        L.LagunaConfig.from_json({"attention_bias": True})
+
+
+def test_rotary_tables_and_partial_application():
+    cfg = L.LagunaConfig()
+    t = L.precompute_rotary_tables(cfg, 64)
+    assert t.full_cos.shape == (64, 32) and t.sliding_cos.shape == (64, 64)
+    assert abs(t.full_cos[0, 0].item() - cfg.yarn_attention_factor) < 1e-6       # scaled by the attention factor
+    inv = C.yarn_inv_freq(32, cfg.rope_theta_full, 32.0, 8192, 32.0, 1.0)
+    assert inv[0] == 1.0 and abs(inv[31] - cfg.rope_theta_full ** (-62 / 64) / 32.0) < 1e-12
+    assert abs(t.sliding_sin[3, 1].item() - math.sin(3 * 10000.0 ** (-2 / 128))) < 1e-6
+    x = torch.randn(1, 4, 2, 128)
+    y = C.apply_rotary_partial(x, t.full_cos[:4], t.full_sin[:4])
+    assert torch.equal(y[..., 64:], x[..., 64:])
+    c, s = t.full_cos[2, 5], t.full_sin[2, 5]
+    assert torch.allclose(y[0, 2, 1, 5], x[0, 2, 1, 5] * c - x[0, 2, 1, 37] * s, atol=1e-6)
+    assert torch.allclose(y[0, 2, 1, 37], x[0, 2, 1, 37] * c + x[0, 2, 1, 5] * s, atol=1e-6)
+
+
+def test_cached_matches_uncached_with_ring_wraparound():
+    m = L.init(tiny_cfg())
+    ids = torch.randint(3, 97, (2, 14))
+    logits = L.forward(m, ids)
+    sess = L.CacheSession(m, 2, 20)
+    assert sess.capacities() == [20, 6, 6, 6, 20]
+    assert torch.allclose(sess.prefill(ids[:, :9]), logits[:, 8], atol=1e-4)       # prompt longer than the window
+    snap = sess.fork()
+    for t in range(9, 14):
+        assert torch.allclose(sess.step(ids[:, t]), logits[:, t], atol=1e-4), t
+    assert snap.pos == 9 and torch.allclose(snap.step(ids[:, 9]), logits[:, 9], atol=1e-4)
+    with pytest.raises(ValueError, match="chunked prefill"):
+        sess.prefill(ids[:, :3])
+
+
+def test_fused_and_eager_expert_paths_agree_and_dense_experts_run():
+    cfg = tiny_cfg()
+    m = L.init(cfg)
+    ids = torch.randint(3, 97, (1, 7))
+    assert torch.allclose(L.forward(m, ids, use_fused=True), L.forward(m, ids, use_fused=False), atol=1e-5)
+    md = L.init(cfg, dense_experts=True)
+    assert L.forward(md, ids).shape == (1, 7, 97)
+
+
+def test_state_dict_roundtrip_through_safetensors(tmp_path):
+    cfg = tiny_cfg(num_hidden_layers=2)
+    m = L.init(cfg, dtype=torch.bfloat16)
+    path = str(tmp_path / "model.safetensors")
+    st.save_file({k: v.contiguous() for k, v in L.state_dict(m).items()}, path)
+    m2 = L.load(cfg, path, dtype=torch.bfloat16)
+    ids = torch.randint(3, 97, (1, 5))
+    assert torch.equal(L.forward(m, ids), L.forward(m2, ids))
+    assert L.name_candidates("model.norm.weight")[:3] == ["model.norm.weight", "language_model.model.norm.weight",
+                                                          "model.language_model.model.norm.weight"]
+
+
+def test_generation_eos_padding_and_stream():
+    cfg = tiny_cfg()
+    m = L.init(cfg)
+    ids = torch.randint(3, 97, (2, 4))
+    seen = []
+    out = L.generate(m, ids, 5, on_step=lambda i, t: seen.append((i, t.clone())))
+    assert out.shape[1] <= 9 and torch.equal(out[:, :4], ids) and len(seen) == out.shape[1] - 4
+    greedy_first = L.forward(m, ids)[:, -1].argmax(-1)
+    assert torch.equal(out[:, 4], greedy_first)
+    # declare the first greedy token of row 0 an eos: row 0 then pads with the first eos id
+    eos = (int(greedy_first[0]), 1)
+    out2 = L.generate(m, ids, 4, eos_token_ids=eos)
+    assert (out2[0, 5:] == eos[0]).all()
+    assert torch.equal(L.generate(m, ids, 0), ids)
+    with pytest.raises(ValueError, match="non-empty prompt"):
+        L.generate(m, ids[:, :0], 3)
+
+
+def test_sampling_strategies():
+    logits = torch.tensor([[0.0, 5.0, 1.0, 4.0], [3.0, 0.0, 0.0, 0.0]])
+    assert G.sample_from_logits(logits, G.SamplingStrategy.greedy()).tolist() == [1, 0]
+    assert torch.isinf(G.top_k_filter(logits, 2)[0, [0, 2]]).all()
+    f = G.top_p_filter(logits, 0.5)
+    assert torch.isfinite(f[0, 1]) and torch.isinf(f[0, 0]) and torch.isfinite(f[1, 0])
+    g = torch.Generator().manual_seed(0)
+    draws = torch.stack([G.sample_from_logits(logits, G.SamplingStrategy.multinomial(0.7, top_k=2), g) for _ in range(50)])
+    assert set(draws[:, 0].tolist()) <= {1, 3}
+    with pytest.raises(ValueError, match="temperature > 0"):
+        G.sample_from_logits(logits, G.SamplingStrategy.multinomial(0.0))
+    t = torch.tensor([5, 2, 9])
+    assert G.token_in_set(t, [2, 9]).tolist() == [False, True, True]
+    assert G.apply_finished_eos(t, torch.tensor([True, False, False]), 7).tolist() == [7, 2, 9]
+
+
+@pytest.mark.gpu
+def test_gpu_laguna_bf16_fused_decode_matches_eager():
+    cfg = tiny_cfg(hidden_size=256, head_dim=128, half_rotary_dim_sliding=64, half_rotary_dim_full=32, num_experts=16,
+                   num_experts_per_tok=4, moe_intermediate_size=128, shared_expert_intermediate_size=128,
+                   intermediate_size=512, sliding_window=128)
+    m = L.init(cfg, device="cuda", dtype=torch.bfloat16)
+    ids = torch.randint(3, 97, (2, 200), device="cuda")
+    with torch.no_grad():
+        ref = L.forward(m, ids, use_fused=False).float()
+        sess = L.CacheSession(m, 2, 260)
+        lp = sess.prefill(ids[:, :190]).float()
+        scale = ref.abs().max().item()
+        assert (lp - ref[:, 189]).abs().max().item() < 0.05 * scale
+        for t in range(190, 200):
+            lt = sess.step(ids[:, t]).float()
+            assert (lt - ref[:, t]).abs().max().item() < 0.05 * scale, t

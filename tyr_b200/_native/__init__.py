@@ -86,7 +86,7 @@ class GemmArgs(ctypes.Structure):
         ("a_mn", c_int), ("b_mn", c_int), ("out_mode", c_int), ("act", c_int),
         ("alpha", c_float), ("beta", c_float),
         ("bn", c_int), ("sm_count", c_int),
-        ("err", c_void_p), ("stream", c_void_p),
+        ("err", c_void_p), ("stream", c_void_p), ("group_offsets", c_void_p), ("group_tiles", c_void_p),
     ]
 
 

@@ -1,0 +1,135 @@
+"""Laguna text generation / throughput CLI (counterpart of Examples/Laguna/RunHF.lean).
+
+    python -m tyr_b200.cli.run_laguna --source <dir|repo> --prompt "..." --max-new-tokens 64 --stream
+    python -m tyr_b200.cli.run_laguna --random-init --layers 8 --bench --prompt-tokens 4096 --batch-size 64
+
+``--random-init`` builds the Laguna-S-2.1 architecture with synthetic NVFP4 banks (no checkpoint or
+tokenizer needed) and feeds random token ids; ``--bench`` prints prefill and decode tokens/s
+measured with CUDA events around the two phases.
+"""
+from __future__ import annotations
+
+import argparse
+import sys
+import time
+
+import torch
+
+from ..io import hub
+from ..models import laguna as L
+from ..models.generation import SamplingStrategy
+from ..tokenizer import hf as tok_hf
+
+
+def parse(argv):
+    p = argparse.ArgumentParser(prog="run_laguna")
+    p.add_argument("--source", default="poolside/Laguna-S-2.1-NVFP4", help="model directory or hub repo id")
+    p.add_argument("--revision", default=None)
+    p.add_argument("--device", default="cuda" if torch.cuda.is_available() else "cpu")
+    p.add_argument("--prompt", default="Write a haiku about GPUs.")
+    p.add_argument("--prompt-file", default=None, help="one prompt per non-empty line")
+    p.add_argument("--batch-size", type=int, default=1)
+    p.add_argument("--max-new-tokens", type=int, default=64)
+    p.add_argument("--stream", action="store_true")
+    p.add_argument("--no-thinking", action="store_true")
+    p.add_argument("--debug-ids", action="store_true")
+    p.add_argument("--bench", action="store_true")
+    p.add_argument("--random-init", action="store_true")
+    p.add_argument("--layers", type=int, default=None, help="with --random-init: number of decoder layers")
+    p.add_argument("--prompt-tokens", type=int, default=4096, help="with --random-init: synthetic prompt length")
+    p.add_argument("--temperature", type=float, default=0.0)
+    p.add_argument("--top-k", type=int, default=None)
+    p.add_argument("--top-p", type=float, default=1.0)
+    return p.parse_args(argv)
+
+
+def _sync(dev):
+    if dev.type == "cuda":
+        torch.cuda.synchronize(dev)
+
+
+def bench(model, input_ids, max_new_tokens, eos=()):
+    """Returns dict(prefill_ms, prefill_tok_s, decode_ms, decode_tok_s); greedy, no early stop unless eos given."""
+    dev = input_ids.device
+    B, S = input_ids.shape
+    with torch.no_grad():
+        warm = L.CacheSession(model, B, S + 4)
+        warm.step(warm.prefill(input_ids).argmax(-1))
+        del warm
+        sess = L.CacheSession(model, B, S + max_new_tokens)
+        _sync(dev)
+        t0 = time.perf_counter()
+        logits = sess.prefill(input_ids)
+        tok = logits.argmax(-1)
+        _sync(dev)
+        t1 = time.perf_counter()
+        n = 0
+        for _ in range(max_new_tokens - 1):
+            tok = sess.step(tok).argmax(-1)
+            n += 1
+        _sync(dev)
+        t2 = time.perf_counter()
+    pre_ms, dec_ms = (t1 - t0) * 1e3, (t2 - t1) * 1e3
+    return {"prompt_tokens": B * S, "prefill_ms": pre_ms, "prefill_tok_s": B * S / pre_ms * 1e3,
+            "decode_tokens": B * n, "decode_ms": dec_ms, "decode_tok_s": (B * n / dec_ms * 1e3) if n else 0.0,
+            "batch": B}
+
+
+def main(argv=None) -> int:
+    a = parse(sys.argv[1:] if argv is None else argv)
+    dev = torch.device(a.device)
+    dtype = torch.bfloat16 if dev.type == "cuda" else torch.float32
+    strategy = (SamplingStrategy.greedy() if a.temperature <= 0 else
+                SamplingStrategy.multinomial(a.temperature, a.top_k, a.top_p))
+    if a.random_init:
+        cfg = L.LagunaConfig(num_hidden_layers=a.layers) if a.layers else L.LagunaConfig()
+        print(f"Random-init Laguna: {cfg.num_hidden_layers} layers, hidden {cfg.hidden_size}, {cfg.num_experts} experts "
+              f"top-{cfg.num_experts_per_tok}", flush=True)
+        model = L.init(cfg, device=dev, dtype=dtype)
+        ids = torch.randint(32, cfg.vocab_size, (a.batch_size, a.prompt_tokens), device=dev)
+        if a.bench:
+            r = bench(model, ids, a.max_new_tokens)
+            print(f"BENCH prompt_tokens={r['prompt_tokens']} prefill_ms={r['prefill_ms']:.1f} prefill_tok_s={r['prefill_tok_s']:.1f}")
+            print(f"BENCH decode_tokens={r['decode_tokens']} decode_ms={r['decode_ms']:.1f} decode_tok_s={r['decode_tok_s']:.1f} batch={r['batch']}")
+            return 0
+        out = L.generate(model, ids, a.max_new_tokens, strategy, eos_token_ids=())
+        print(out[:, a.prompt_tokens:].tolist())
+        return 0
+    model_dir = hub.resolve_pretrained_dir(a.source, a.revision)
+    cfg = L.LagunaConfig.load_from_pretrained_dir(model_dir)
+    tok = tok_hf.load_laguna(model_dir)
+    model = L.load(cfg, model_dir, device=dev, dtype=dtype, log=lambda s: print(s, flush=True))
+    prompts = [a.prompt]
+    if a.prompt_file:
+        prompts = [l.strip() for l in open(a.prompt_file, encoding="utf-8") if l.strip()]
+    if a.bench:
+        prompts = prompts[:1]
+    for b0 in range(0, len(prompts), a.batch_size):
+        chunk = prompts[b0:b0 + a.batch_size]
+        enc = [tok_hf.laguna_encode(tok, tok_hf.laguna_prompt(p, not a.no_thinking)) for p in chunk]
+        width = max(len(e) for e in enc)
+        # left-pad so every row's last prompt token sits at the same position
+        ids = torch.tensor([[tok_hf.LAGUNA_PAD_ID] * (width - len(e)) + e for e in enc], device=dev)
+        if a.bench:
+            print("Warming up...\nMeasuring...", flush=True)
+            r = bench(model, ids, a.max_new_tokens, cfg.eos_token_ids)
+            print(f"BENCH prompt_tokens={r['prompt_tokens']} prefill_ms={r['prefill_ms']:.1f} prefill_tok_s={r['prefill_tok_s']:.1f}")
+            print(f"BENCH decode_tokens={r['decode_tokens']} decode_ms={r['decode_ms']:.1f} decode_tok_s={r['decode_tok_s']:.1f}")
+            return 0
+        cb = None
+        if a.stream and len(chunk) == 1:
+            cb = lambda i, t: print(tok.decode([int(t[0])]), end="", flush=True)
+        out = L.generate(model, ids, a.max_new_tokens, strategy, on_step=cb)
+        if cb is not None:
+            print()
+        for row, p in zip(out.tolist(), chunk):
+            gen = row[width:]
+            if not (a.stream and len(chunk) == 1):
+                print(f"### {p}\n{tok.decode(gen)}")
+            if a.debug_ids:
+                print(f"ids: {gen}")
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

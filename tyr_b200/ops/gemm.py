@@ -176,3 +176,62 @@ def relu2_bwd(dy, y):
 def linear(x: torch.Tensor, w: torch.Tensor, act: Optional[str] = None) -> torch.Tensor:
     """Autograd linear ``act(x @ w^T)`` on the tcgen05 GEMM (weights ``[out, in]``)."""
     return _LinearFn.apply(x, w, act)
+
+
+def grouped_gemm(a: torch.Tensor, b: torch.Tensor, group_offsets: torch.Tensor,
+                 group_tiles: Optional[torch.Tensor] = None, *,
+                 act: Optional[str] = None, alpha: float = 1.0, beta: float = 1.0,
+                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Grouped (MoE) product on the tcgen05 kernel.
+
+    ``a``: packed rows ``[total_rows, K]``; group g owns rows ``[offsets[g], offsets[g+1])`` and is
+    multiplied by ``b[g]`` (``[G, N, K]``, K-major).  ``group_tiles`` (int32 ``[G+1]``, the prefix sum of
+    ``ceil(rows_g / 128)``) lets the kernel walk the non-empty row tiles without a device->host read
+    of the counts; it is derived on the device when not given.  ``act='swiglu'`` expects each 256-row
+    block of ``b[g]`` to hold 128 gate rows followed by the matching 128 up rows and returns
+    ``[total_rows, N/2]`` with ``silu(alpha*gate) * (beta*up)``."""
+    total, K = a.shape
+    G, N, K2 = b.shape
+    assert K == K2 and group_offsets.numel() == G + 1
+    swiglu = act == "swiglu"
+    n_out = N // 2 if swiglu else N
+    if not a.is_cuda:
+        offs = group_offsets.tolist()
+        res = torch.zeros(total, n_out, dtype=a.dtype)
+        for g in range(G):
+            lo, hi = offs[g], offs[g + 1]
+            if hi <= lo:
+                continue
+            acc = a[lo:hi].float() @ b[g].float().T
+            if swiglu:
+                blk = acc.reshape(hi - lo, N // 256, 2, 128)
+                gate, up = alpha * blk[:, :, 0], beta * blk[:, :, 1]
+                acc = (torch.nn.functional.silu(gate) * up).reshape(hi - lo, n_out)
+            else:
+                acc = alpha * acc
+            res[lo:hi] = acc.to(a.dtype)
+        return res
+    if swiglu and N % 256 != 0:
+        raise ValueError("swiglu grouped gemm needs N to be a multiple of 256")
+    if out is None:
+        out = torch.empty((total, n_out), dtype=torch.bfloat16, device=a.device)
+    args = GemmArgs()
+    args.A, args.B, args.C = a.data_ptr(), b.data_ptr(), out.data_ptr()
+    if group_tiles is None:
+        cnt = group_offsets[1:] - group_offsets[:-1]
+        group_tiles = torch.cat([torch.zeros(1, dtype=torch.int32, device=a.device),
+                                 torch.cumsum((cnt + 127) // 128, 0).to(torch.int32)])
+    args.M, args.N, args.K, args.batch = max(1, total), N, K, G
+    args.lda, args.ldb, args.ldc = a.stride(0), b.stride(1), out.stride(0)
+    args.sA, args.sB = total, b.stride(0)
+    args.out_mode = 0
+    args.act = 4 if swiglu else _ACT[act]
+    args.alpha = alpha
+    args.beta = beta if swiglu else 0.0
+    args.bn = 256
+    args.err = err_word(a.device).data_ptr()
+    args.stream = cur_stream(a.device).value
+    args.group_offsets = group_offsets.data_ptr()
+    args.group_tiles = group_tiles.data_ptr()
+    check(lib().tyr_gemm_bf16(ctypes.byref(args)), "tyr_gemm_bf16(grouped)")
+    return out

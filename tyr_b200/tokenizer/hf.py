@@ -165,3 +165,22 @@ def load_gemma4(path: str) -> HFTokenizer:
     t = HFTokenizer.from_file(path)
     t.byte_level = False
     return t
+
+
+# ---- Laguna (Tyr/Tokenizer/Laguna.lean:29-50, 751-757) ---------------------------------------------------
+LAGUNA_EOS_ID, LAGUNA_PAD_ID, LAGUNA_CLS_ID, LAGUNA_ASSISTANT_END_ID = 2, 9, 10, 24
+LAGUNA_EOS_TOKEN, LAGUNA_PAD_TOKEN = "〈|EOS|〉", "〈|PAD|〉"
+LAGUNA_SYSTEM = ("You are a helpful, conversationally-fluent assistant made by Poolside. "
+                 "You are here to be helpful to users through natural language conversations.")
+
+
+def laguna_prompt(prompt: str, enable_thinking: bool = True, system: str = LAGUNA_SYSTEM) -> str:
+    """Single user turn; ends with ``<assistant><think>`` (thinking on) or ``<assistant></think>``."""
+    return (f"{LAGUNA_EOS_TOKEN}<system>{system}</system>\n<user>{prompt}</user>\n<assistant>"
+            + ("<think>" if enable_thinking else "</think>"))
+
+
+def laguna_encode(tok: HFTokenizer, text: str) -> List[int]:
+    """HF post-processor behaviour: the EOS token (id 2, doubling as BOS) is always prepended."""
+    bos = tok.token_id(LAGUNA_EOS_TOKEN)
+    return [LAGUNA_EOS_ID if bos is None else bos] + tok.encode(text)

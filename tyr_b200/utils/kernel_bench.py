@@ -1,4 +1,4 @@
-"""Kernel micro-benchmarks: `python -m tyr_b200.utils.kernel_bench [gemm|attention|all]`.
+"""Kernel micro-benchmarks: `python -m tyr_b200.utils.kernel_bench [gemm|attention|moe|all]`.
 
 Times the hand-written kernels with CUDA events (5 warm-up + 20 timed iterations, a 256 MB
 buffer written between iterations to flush the 126 MB L2) on the NanoChat d20 shapes and prints
@@ -88,6 +88,33 @@ def bench_attention(results):
         print(f"flash fwd B{B} H{H} T{T} causal={causal}: ours {ours:7.3f} ms {flops/ours/1e9:7.1f} TF/s | SDPA {lib:7.3f} ms {flops/lib/1e9:7.1f} TF/s", flush=True)
 
 
+def bench_moe(results):
+    """Fused NVFP4 MoE op at Laguna-S-2.1 shapes (hidden 3072, 256 experts, top-10, FFN 1024): effective
+    FP4 weight-read bandwidth for decode-sized batches (the reference's bar is >= 150 GB/s at one token,
+    Tests/RunLagunaFused.lean:373-386) and tokens/s for prefill-sized batches."""
+    from tyr_b200.models import laguna as L
+    from tyr_b200.ops import moe
+    dev = torch.device("cuda")
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    cfg = L.LagunaConfig()
+    gen = torch.Generator().manual_seed(0)
+    ex = L.random_packed_experts(cfg, dev, gen)
+    E, k, h, mi = cfg.num_experts, cfg.num_experts_per_tok, cfg.hidden_size, cfg.moe_intermediate_size
+    for T, path in ((1, "gemv"), (4, "gemv"), (16, "gemv"), (64, "gemv"), (64, "gemm"), (512, "gemm"), (4096, "gemm")):
+        x = torch.randn(T, h, device=dev).bfloat16()
+        ids, w, cnt = moe.route(torch.randn(T, E, device=dev), k)
+        fn = lambda: moe.moe_fp4_forward(x, ids, w, ex, counts=cnt, force_path=path)
+        ms = _time(fn, flush=flush)
+        active = int((cnt > 0).sum())
+        fp4_bytes = ex.weight_bytes_per_pair() * (T * k if path == "gemv" and T == 1 else active)
+        flops = 6.0 * T * k * h * mi
+        row = {"kernel": "moe_fp4_" + path, "tokens": T, "ms": ms, "active_experts": active,
+               "fp4_gbs": fp4_bytes / ms / 1e6, "tflops": flops / ms / 1e9, "tokens_per_s": T / ms * 1e3}
+        results.append(row)
+        print(f"moe {path} T={T:5d}: {ms:8.3f} ms  unique-expert FP4 read {row['fp4_gbs']:8.1f} GB/s  {row['tflops']:7.1f} TF/s  "
+              f"{row['tokens_per_s']:10.0f} tok/s", flush=True)
+
+
 def main(argv):
     what = argv[1] if len(argv) > 1 else "all"
     results = []
@@ -95,6 +122,8 @@ def main(argv):
         bench_gemm(results)
     if what in ("attention", "all"):
         bench_attention(results)
+    if what in ("moe", "all"):
+        bench_moe(results)
     print(json.dumps(results))
 
 
