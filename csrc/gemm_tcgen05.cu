@@ -554,7 +554,7 @@ extern "C" TYR_EXPORT int tyr_gemm_bf16(const TyrGemmArgs* args) {
   if ((reinterpret_cast<uintptr_t>(a.A) & 15) || (reinterpret_cast<uintptr_t>(a.B) & 15) ||
       (reinterpret_cast<uintptr_t>(a.C) & 15))
     return -2;
-  if ((a.lda & 7) || (a.ldb & 7) || (a.sA & 7) || (a.sB & 7)) return -3;
+  if ((a.lda & 7) || (a.ldb & 7) || (a.group_offsets == nullptr && (a.sA & 7)) || (a.sB & 7)) return -3;
   if (a.out_mode == 0 ? (a.ldc & 7) : (a.ldc & 3)) return -4;
   if (a.aux && ((a.ldaux & 7) || (reinterpret_cast<uintptr_t>(a.aux) & 15))) return -5;
   if (g_sm_count == 0) {

@@ -18,6 +18,8 @@
 //    the grouped tcgen05 GEMM (gemm_tcgen05.cu, group offsets) with the SwiGLU in its epilogue.
 #include "common.cuh"
 #include <cuda_fp8.h>
+#include <cuda_fp4.h>
+#include <cuda_fp16.h>
 
 namespace tyr {
 
@@ -183,31 +185,38 @@ __global__ void __launch_bounds__(256) moe_route_kernel(RouteArgs a) {
 
 // offsets[E+1] from counts[E]; cursors[E] zeroed; tiles[E+1] (nullable) = prefix sum of
 // ceil(count / 128), the m-tile table of the grouped GEMM.  One block.
-__global__ void moe_offsets_kernel(const int* counts, int* offsets, int* cursors, int* tiles, int E) {
+// active[E + 1] (nullable): compact list of the experts with rows, followed by their number in active[E].
+__global__ void moe_offsets_kernel(const int* counts, int* offsets, int* cursors, int* tiles, int* active, int E) {
   __shared__ int s[1024];
   __shared__ int s2[1024];
+  __shared__ int s3[1024];
   const int t = threadIdx.x;
   const int v = t < E ? counts[t] : 0;
   s[t] = v;
   s2[t] = (v + 127) >> 7;
+  s3[t] = v > 0 ? 1 : 0;
   __syncthreads();
   for (int o = 1; o < blockDim.x; o <<= 1) {
     const int add = t >= o ? s[t - o] : 0;
     const int add2 = t >= o ? s2[t - o] : 0;
+    const int add3 = t >= o ? s3[t - o] : 0;
     __syncthreads();
     s[t] += add;
     s2[t] += add2;
+    s3[t] += add3;
     __syncthreads();
   }
   if (t < E) {
     offsets[t + 1] = s[t];
     if (tiles) tiles[t + 1] = s2[t];
+    if (active && v > 0) active[s3[t] - 1] = t;
     cursors[t] = 0;
   }
   if (t == 0) {
     offsets[0] = 0;
     if (tiles) tiles[0] = 0;
   }
+  if (active && t == E - 1) active[E] = s3[t];
 }
 
 // pair_order[offsets[e] + slot] = pair index (expert-major); slot order within an expert is arbitrary
@@ -267,10 +276,23 @@ moe_combine_kernel(const __nv_bfloat16* y, const int* pair_pos, const float* wei
 }
 
 // ---------------------------------------------------------------------------------------------
-// weight-streaming grouped GEMV (decode).  Block = 256 threads = 8 warps; CTA = (row tile, expert).
+// Weight-streaming grouped GEMV (decode-sized batches).
+//
+// The op is bound by reading each active expert's FP4 rows once.  Up to 8 (token, slot) pairs of
+// one expert form the N = 8 side of m16n8k16 tensor-core tiles, so one pass over the weights serves
+// all of them (more pairs -> further passes that hit L2).  Every lane streams 16 contiguous bytes
+// (32 weights = two scale groups) per row straight from global memory into registers, converts
+// e2m1 -> f16 with the hardware cvt, multiplies by the e4m3 group scale (exact in f16: <= 6
+// significant bits) and feeds the A fragment; the k order inside a 128-column step is permuted
+// identically for A and B, which a dot product does not care about.  Activations are staged once
+// per CTA in shared memory as f16 (clamped to the f16 range).  Four warps x 16 rows per CTA keep
+// >= 148 CTAs busy even for a single token; each lane has 64-128 B of weights in flight.
+// The synchronous mma form is used on purpose: N is 8 and the kernel is bandwidth bound, there
+// is no operand reuse that shared-memory staging for tcgen05 could exploit.
 // ---------------------------------------------------------------------------------------------
-constexpr int kP = 8;          // pairs per pass
-constexpr int kRowsA = 32;     // output rows per CTA (4 per warp)
+constexpr int kP = 8;            // pairs per pass (mma N)
+constexpr int kWarps = 4;        // warps per CTA
+constexpr int kRowsCta = 16 * kWarps;
 
 struct StageArgs {
   const __nv_bfloat16* x;      // stage A: [T, h] activations; stage B: unused
@@ -282,6 +304,8 @@ struct StageArgs {
   const uint8_t* s1;
   const float* g1;
   const int* offsets;          // [E+1]
+  const int* active;           // [E] compact list of experts with at least one pair
+  const int* n_active;         // [1]
   const int* pair_order;       // [pairs] pair index at each expert-major position
   const float* pair_weight;    // [pairs] routing weight by pair index (stage B)
   float* hid_out;              // stage A: [pairs, mi] fp32
@@ -289,104 +313,146 @@ struct StageArgs {
   int k, in_dim, out_dim;      // stage A: in = h, out = mi; stage B: in = mi, out = h
 };
 
-// decode 16 weights of one scale group and accumulate against P activation vectors held in smem
-template <typename XT>
-__device__ __forceinline__ void fma_group(const uint8_t* by, float sd, const XT* xs, int xstride, int col,
-                                          int np, float (&acc)[kP]) {
-  float w[16];
+__device__ __forceinline__ uint32_t e2m1x2_to_f16x2(uint32_t byte) {
+  __half2_raw h = __nv_cvt_fp4x2_to_halfraw2(static_cast<__nv_fp4x2_storage_t>(byte), __NV_E2M1);
+  return static_cast<uint32_t>(h.x) | (static_cast<uint32_t>(h.y) << 16);
+}
+__device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
+  __half2 r = __hmul2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
+  return *reinterpret_cast<uint32_t*>(&r);
+}
+__device__ __forceinline__ uint32_t e4m3_to_f16x2(uint32_t byte) {
+  __half_raw h = __nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>(byte), __NV_E4M3);
+  return static_cast<uint32_t>(h.x) * 0x00010001u;
+}
+__device__ __forceinline__ void mma_f16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                              uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_f16x2_sat(float a, float b) {
+  a = fminf(fmaxf(a, -65504.f), 65504.f);
+  b = fminf(fmaxf(b, -65504.f), 65504.f);
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// One 128-column step of one 16-row tile: rows (g, g+8) of one matrix.
+//   wlo / whi: the lane's 16 bytes of row g / row g+8;  slo / shi: its two scale bytes per row.
+__device__ __forceinline__ void tile_step(float (&c)[4], const uint4& wlo, const uint4& whi, uint32_t slo, uint32_t shi,
+                                          const uint32_t (&b)[16]) {
+  const uint32_t lo[4] = {wlo.x, wlo.y, wlo.z, wlo.w};
+  const uint32_t hi[4] = {whi.x, whi.y, whi.z, whi.w};
+  const uint32_t sl[2] = {e4m3_to_f16x2(slo & 0xff), e4m3_to_f16x2(slo >> 8)};
+  const uint32_t sh[2] = {e4m3_to_f16x2(shi & 0xff), e4m3_to_f16x2(shi >> 8)};
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    w[2 * i] = sd * kE2M1[by[i] & 15];
-    w[2 * i + 1] = sd * kE2M1[by[i] >> 4];
-  }
-#pragma unroll
-  for (int p = 0; p < kP; ++p) {
-    if (p < np) {
-      const XT* xp = xs + p * xstride + col;
-      float a = 0.f;
-#pragma unroll
-      for (int i = 0; i < 16; ++i) a += w[i] * static_cast<float>(xp[i]);
-      acc[p] += a;
-    }
+  for (int s = 0; s < 8; ++s) {
+    // k-step s uses bytes 2s and 2s+1 of the lane's 16 (elements 4s..4s+3); bytes 0-7 are scale group 0
+    const uint32_t wl = lo[s >> 1] >> ((s & 1) * 16);
+    const uint32_t wh = hi[s >> 1] >> ((s & 1) * 16);
+    const uint32_t a0 = hmul2_u32(e2m1x2_to_f16x2(wl & 0xff), sl[s >> 2]);
+    const uint32_t a2 = hmul2_u32(e2m1x2_to_f16x2((wl >> 8) & 0xff), sl[s >> 2]);
+    const uint32_t a1 = hmul2_u32(e2m1x2_to_f16x2(wh & 0xff), sh[s >> 2]);
+    const uint32_t a3 = hmul2_u32(e2m1x2_to_f16x2((wh >> 8) & 0xff), sh[s >> 2]);
+    mma_f16_16816(c, a0, a1, a2, a3, b[2 * s], b[2 * s + 1]);
   }
 }
 
-__global__ void __launch_bounds__(256) moe_fp4_stage_a_kernel(StageArgs a) {
-  extern __shared__ float xs[];          // [kP][in_dim] fp32
-  const int e = blockIdx.y;
+template <bool STAGE_A>
+__global__ void __launch_bounds__(32 * kWarps) moe_fp4_gemv_kernel(StageArgs a) {
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  if (static_cast<int>(blockIdx.y) >= *a.n_active) return;
+  const int e = a.active[blockIdx.y];
   const int begin = a.offsets[e], end = a.offsets[e + 1];
-  if (begin >= end) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int row0 = blockIdx.x * kRowsA + warp * (kRowsA / 8);
-  const int groups = a.in_dim >> 4;                         // 16-element scale groups per row
-  const float inv_g = 1.f / a.g0[e], inv_u = 1.f / a.g1[e];
-  for (int base = begin; base < end; base += kP) {
-    const int np = min(kP, end - base);
-    __syncthreads();
-    for (int i = threadIdx.x; i < np * a.in_dim; i += blockDim.x) {
-      const int p = i / a.in_dim, c = i % a.in_dim;
-      const int tok = a.pair_order[base + p] / a.k;
-      xs[p * a.in_dim + c] = __bfloat162float(a.x[static_cast<long long>(tok) * a.in_dim + c]);
-    }
-    __syncthreads();
-    for (int r = 0; r < kRowsA / 8; ++r) {
-      const int row = row0 + r;
-      if (row >= a.out_dim) break;
-      float ag[kP], au[kP];
-#pragma unroll
-      for (int p = 0; p < kP; ++p) ag[p] = au[p] = 0.f;
-      const long long wrow = (static_cast<long long>(e) * a.out_dim + row) * (a.in_dim >> 1);
-      const long long srow = (static_cast<long long>(e) * a.out_dim + row) * groups;
-      for (int g = lane; g < groups; g += 32) {
-        uint2 bg = *reinterpret_cast<const uint2*>(a.w0 + wrow + g * 8);
-        uint2 bu = *reinterpret_cast<const uint2*>(a.w1 + wrow + g * 8);
-        fma_group(reinterpret_cast<const uint8_t*>(&bg), e4m3_to_float(a.s0[srow + g]), xs, a.in_dim, g * 16, np, ag);
-        fma_group(reinterpret_cast<const uint8_t*>(&bu), e4m3_to_float(a.s1[srow + g]), xs, a.in_dim, g * 16, np, au);
-      }
-#pragma unroll
-      for (int p = 0; p < kP; ++p) {
-        const float gsum = warp_sum(ag[p]) * inv_g;
-        const float usum = warp_sum(au[p]) * inv_u;
-        if (lane == 0 && p < np)
-          a.hid_out[static_cast<long long>(base + p) * a.out_dim + row] = gsum / (1.f + __expf(-gsum)) * usum;
-      }
-    }
-  }
-}
+  const int g = lane >> 2, t = lane & 3;
+  const int K = a.in_dim;
+  const int xstride = K + 8;                                  // halves; +16 B staggers rows across banks
+  __half* xs = reinterpret_cast<__half*>(smem_raw);           // [kP][xstride]
+  const int row0 = blockIdx.x * kRowsCta + warp * 16;
+  const bool rows_ok = row0 < a.out_dim;                      // out_dim is a multiple of 16
+  const int steps = K >> 7;                                   // 128 columns per step (K % 128 == 0)
+  const long long rbytes = K >> 1, sbytes = K >> 4;
+  const long long r_lo = static_cast<long long>(e) * a.out_dim + row0 + g;
+  const uint8_t* w0lo = a.w0 + r_lo * rbytes + t * 16;
+  const uint8_t* w0hi = w0lo + 8 * rbytes;
+  const uint8_t* s0lo = a.s0 + r_lo * sbytes + t * 2;
+  const uint8_t* s0hi = s0lo + 8 * sbytes;
+  const uint8_t* w1lo = STAGE_A ? a.w1 + r_lo * rbytes + t * 16 : nullptr;
+  const uint8_t* w1hi = STAGE_A ? w1lo + 8 * rbytes : nullptr;
+  const uint8_t* s1lo = STAGE_A ? a.s1 + r_lo * sbytes + t * 2 : nullptr;
+  const uint8_t* s1hi = STAGE_A ? s1lo + 8 * sbytes : nullptr;
 
-__global__ void __launch_bounds__(256) moe_fp4_stage_b_kernel(StageArgs a) {
-  extern __shared__ float hs[];          // [kP][in_dim] fp32
-  const int e = blockIdx.y;
-  const int begin = a.offsets[e], end = a.offsets[e + 1];
-  if (begin >= end) return;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int row0 = blockIdx.x * kRowsA + warp * (kRowsA / 8);
-  const int groups = a.in_dim >> 4;
-  const float inv_d = 1.f / a.g0[e];
   for (int base = begin; base < end; base += kP) {
     const int np = min(kP, end - base);
     __syncthreads();
-    for (int i = threadIdx.x; i < np * a.in_dim; i += blockDim.x)
-      hs[i] = a.hid_in[static_cast<long long>(base) * a.in_dim + i];
-    __syncthreads();
-    for (int r = 0; r < kRowsA / 8; ++r) {
-      const int row = row0 + r;
-      if (row >= a.out_dim) break;
-      float ad[kP];
-#pragma unroll
-      for (int p = 0; p < kP; ++p) ad[p] = 0.f;
-      const long long wrow = (static_cast<long long>(e) * a.out_dim + row) * (a.in_dim >> 1);
-      const long long srow = (static_cast<long long>(e) * a.out_dim + row) * groups;
-      for (int g = lane; g < groups; g += 32) {
-        uint2 bd = *reinterpret_cast<const uint2*>(a.w0 + wrow + g * 8);
-        fma_group(reinterpret_cast<const uint8_t*>(&bd), e4m3_to_float(a.s0[srow + g]), hs, a.in_dim, g * 16, np, ad);
+    // stage activations of this pass as f16
+    for (int i = threadIdx.x; i < np * (K >> 1); i += blockDim.x) {
+      const int p = i / (K >> 1), c = (i % (K >> 1)) * 2;
+      float v0, v1;
+      if (STAGE_A) {
+        const int tok = a.pair_order[base + p] / a.k;
+        const float2 f = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(a.x + static_cast<long long>(tok) * K + c));
+        v0 = f.x; v1 = f.y;
+      } else {
+        const float2 f = *reinterpret_cast<const float2*>(a.hid_in + static_cast<long long>(base + p) * K + c);
+        v0 = f.x; v1 = f.y;
       }
+      *reinterpret_cast<uint32_t*>(xs + p * xstride + c) = pack_f16x2_sat(v0, v1);
+    }
+    __syncthreads();
+    if (!rows_ok) continue;
+    float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
+    const __half* xrow = xs + g * xstride + t * 32;
+#pragma unroll 2
+    for (int st = 0; st < steps; ++st) {
+      const uint4 a_lo = __ldg(reinterpret_cast<const uint4*>(w0lo + st * 64));
+      const uint4 a_hi = __ldg(reinterpret_cast<const uint4*>(w0hi + st * 64));
+      const uint32_t sa_lo = __ldg(reinterpret_cast<const uint16_t*>(s0lo + st * 8));
+      const uint32_t sa_hi = __ldg(reinterpret_cast<const uint16_t*>(s0hi + st * 8));
+      uint4 b_lo, b_hi;
+      uint32_t sb_lo = 0, sb_hi = 0;
+      if (STAGE_A) {
+        b_lo = __ldg(reinterpret_cast<const uint4*>(w1lo + st * 64));
+        b_hi = __ldg(reinterpret_cast<const uint4*>(w1hi + st * 64));
+        sb_lo = __ldg(reinterpret_cast<const uint16_t*>(s1lo + st * 8));
+        sb_hi = __ldg(reinterpret_cast<const uint16_t*>(s1hi + st * 8));
+      }
+      uint32_t b[16];
+      if (g < np) {
+        const uint4* xp = reinterpret_cast<const uint4*>(xrow + st * 128);
 #pragma unroll
-      for (int p = 0; p < kP; ++p) {
-        const float d = warp_sum(ad[p]) * inv_d;
-        if (lane == 0 && p < np) {
-          const int pair = a.pair_order[base + p];
-          atomicAdd(a.out + static_cast<long long>(pair / a.k) * a.out_dim + row, a.pair_weight[pair] * d);
+        for (int j = 0; j < 4; ++j) {
+          const uint4 v = xp[j];
+          b[4 * j] = v.x; b[4 * j + 1] = v.y; b[4 * j + 2] = v.z; b[4 * j + 3] = v.w;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) b[j] = 0u;
+      }
+      tile_step(c0, a_lo, a_hi, sa_lo, sa_hi, b);
+      if (STAGE_A) tile_step(c1, b_lo, b_hi, sb_lo, sb_hi, b);
+    }
+    // c[0], c[1]: (row g, pairs 2t, 2t+1);  c[2], c[3]: (row g+8, pairs 2t, 2t+1)
+    if (STAGE_A) {
+      const float ig = 1.f / a.g0[e], iu = 1.f / a.g1[e];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int n = 2 * t + (q & 1), row = row0 + g + (q >> 1) * 8;
+        if (n < np) {
+          const float gv = c0[q] * ig, uv = c1[q] * iu;
+          a.hid_out[static_cast<long long>(base + n) * a.out_dim + row] = gv / (1.f + __expf(-gv)) * uv;
+        }
+      }
+    } else {
+      const float id = 1.f / a.g0[e];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int n = 2 * t + (q & 1), row = row0 + g + (q >> 1) * 8;
+        if (n < np) {
+          const int pair = a.pair_order[base + n];
+          atomicAdd(a.out + static_cast<long long>(pair / a.k) * a.out_dim + row, a.pair_weight[pair] * c0[q] * id);
         }
       }
     }
@@ -441,12 +507,12 @@ extern "C" TYR_EXPORT int tyr_moe_route(const float* logits, const float* bias, 
 }
 
 extern "C" TYR_EXPORT int tyr_moe_layout(const int* ids, const int* counts, int* offsets, int* cursors,
-                                         int* tiles, int* pair_order, int* pair_pos, int pairs, int E,
-                                         void* stream) {
+                                         int* tiles, int* active, int* pair_order, int* pair_pos, int pairs,
+                                         int E, void* stream) {
   if (pairs <= 0 || E <= 0 || E > 1024) return -1;
   int threads = 32;
   while (threads < E) threads <<= 1;
-  moe_offsets_kernel<<<1, threads, 0, (cudaStream_t)stream>>>(counts, offsets, cursors, tiles, E);
+  moe_offsets_kernel<<<1, threads, 0, (cudaStream_t)stream>>>(counts, offsets, cursors, tiles, active, E);
   moe_scatter_kernel<<<blocks_for(pairs), 256, 0, (cudaStream_t)stream>>>(ids, offsets, cursors, pair_order,
                                                                          pair_pos, pairs, E);
   return (int)cudaGetLastError();
@@ -468,38 +534,43 @@ extern "C" TYR_EXPORT int tyr_moe_combine(const void* y, const int* pair_pos, co
   return (int)cudaGetLastError();
 }
 
-// Decode path: routed[T, h] (fp32, zero on entry) += sum_k w * down(silu(gate x) * up x)
+// Decode path: routed[T, h] (fp32, zero on entry) += sum_k w * down(silu(gate x) * up x).
+// `active` / `n_active` come from tyr_moe_layout; h and mi must be multiples of 128.
 extern "C" TYR_EXPORT int tyr_moe_fp4_gemv(const void* x, const void* gate_p, const void* gate_s, const float* gate_g,
                                            const void* up_p, const void* up_s, const float* up_g,
                                            const void* down_p, const void* down_s, const float* down_g,
-                                           const int* offsets, const int* pair_order, const float* pair_weight,
-                                           float* hid, float* routed, int E, int k, int h, int mi, void* stream) {
-  if ((h & 15) || (mi & 15) || E <= 0 || E > 65535) return -1;
+                                           const int* offsets, const int* active, const int* n_active,
+                                           const int* pair_order, const float* pair_weight,
+                                           float* hid, float* routed, int pairs, int E, int k, int h, int mi, void* stream) {
+  if ((h & 127) || (mi & 127) || E <= 0 || pairs <= 0) return -1;
   cudaStream_t st = (cudaStream_t)stream;
+  const int slots = pairs < E ? pairs : E;
+  if (slots > 65535) return -1;
   StageArgs a{};
   a.x = (const __nv_bfloat16*)x;
   a.w0 = (const uint8_t*)gate_p; a.s0 = (const uint8_t*)gate_s; a.g0 = gate_g;
   a.w1 = (const uint8_t*)up_p; a.s1 = (const uint8_t*)up_s; a.g1 = up_g;
-  a.offsets = offsets; a.pair_order = pair_order; a.pair_weight = pair_weight;
+  a.offsets = offsets; a.active = active; a.n_active = n_active; a.pair_order = pair_order; a.pair_weight = pair_weight;
   a.hid_out = hid; a.k = k; a.in_dim = h; a.out_dim = mi;
-  const size_t smem_a = sizeof(float) * kP * h;
-  static int cfg_a = 0, cfg_b = 0;
-  if (smem_a > 48 * 1024 && cfg_a < (int)smem_a) {
-    cudaFuncSetAttribute(moe_fp4_stage_a_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_a);
-    cfg_a = (int)smem_a;
+  const size_t smem_a = sizeof(__half) * kP * (h + 8);
+  const size_t smem_b = sizeof(__half) * kP * (mi + 8);
+  if (smem_a > 200 * 1024 || smem_b > 200 * 1024) return -3;
+  static size_t cfg_a = 0, cfg_b = 0;
+  if (smem_a > 48 * 1024 && cfg_a < smem_a) {
+    cudaFuncSetAttribute(moe_fp4_gemv_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_a);
+    cfg_a = smem_a;
   }
-  moe_fp4_stage_a_kernel<<<dim3((mi + kRowsA - 1) / kRowsA, E), 256, smem_a, st>>>(a);
+  if (smem_b > 48 * 1024 && cfg_b < smem_b) {
+    cudaFuncSetAttribute(moe_fp4_gemv_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_b);
+    cfg_b = smem_b;
+  }
+  moe_fp4_gemv_kernel<true><<<dim3((mi + kRowsCta - 1) / kRowsCta, slots), 32 * kWarps, smem_a, st>>>(a);
   StageArgs b{};
   b.hid_in = hid;
   b.w0 = (const uint8_t*)down_p; b.s0 = (const uint8_t*)down_s; b.g0 = down_g;
-  b.offsets = offsets; b.pair_order = pair_order; b.pair_weight = pair_weight;
+  b.offsets = offsets; b.active = active; b.n_active = n_active; b.pair_order = pair_order; b.pair_weight = pair_weight;
   b.out = routed; b.k = k; b.in_dim = mi; b.out_dim = h;
-  const size_t smem_b = sizeof(float) * kP * mi;
-  if (smem_b > 48 * 1024 && cfg_b < (int)smem_b) {
-    cudaFuncSetAttribute(moe_fp4_stage_b_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_b);
-    cfg_b = (int)smem_b;
-  }
-  moe_fp4_stage_b_kernel<<<dim3((h + kRowsA - 1) / kRowsA, E), 256, smem_b, st>>>(b);
+  moe_fp4_gemv_kernel<false><<<dim3((h + kRowsCta - 1) / kRowsCta, slots), 32 * kWarps, smem_b, st>>>(b);
   return (int)cudaGetLastError();
 }
 

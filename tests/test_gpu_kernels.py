@@ -280,6 +280,10 @@ def test_nanochat_fused_vs_reference_gpu():
     (1, 2, 1, 300, 300, False, None),
     (1, 2, 2, 128, 640, True, None),
     (2, 3, 3, 1024, 1024, True, None),
+    (2, 6, 2, 1, 190, False, None),
+    (2, 4, 2, 1, 128, False, None),
+    (1, 8, 8, 1, 191, True, None),
+    (2, 6, 2, 16, 300, True, None),
 ])
 def test_flash_attention_forward(B, Hq, Hkv, Tq, Tk, causal, window):
     from tyr_b200.ops import flash

@@ -15,7 +15,7 @@ from typing import List, Optional, Sequence, Tuple
 import torch
 import torch.nn.functional as F
 
-from ..ops import gemm as _gemm
+from ..ops.gemm import gemm as _gemm
 from ..ops.attention import attention
 from ..ops.norm import rms_norm_weighted
 
@@ -27,7 +27,7 @@ def lin(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor] = None, act:
     rows = x.numel() // x.shape[-1]
     if (x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and rows >= TCGEN05_MIN_ROWS
             and not torch.is_grad_enabled() and w.shape[1] % 8 == 0 and w.shape[0] % 8 == 0 and w.is_contiguous()):
-        y = _gemm.gemm(x.reshape(rows, -1).contiguous(), w, a_layout="K", b_layout="K",
+        y = _gemm(x.reshape(rows, -1).contiguous(), w, a_layout="K", b_layout="K",
                        act=act if b is None else None).reshape(*x.shape[:-1], w.shape[0])
         if b is not None:
             y = y + b

@@ -1,0 +1,102 @@
+"""Gated delta rule (Qwen3.5 GatedDeltaNet core): chunked prefill, recurrent oracle, fused decode step.
+
+q, k: [B, S, H, dk]; v: [B, S, H, dv]; g (log decay, <= 0) and beta: [B, S, H]; state [B, H, dk, dv] fp32.
+Semantics: cc/src/tyr_qwen35.cpp:12-170 of the reference (L2-normalised q/k, q scaled by dk^-1/2).
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from .._native import register_signatures
+from ._common import check, cur_stream, lib, ptr
+
+
+@register_signatures
+def _sigs(lib_):
+    import ctypes
+    P, I, L = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
+    fn = getattr(lib_, "tyr_gdr_decode", None)
+    if fn is not None:
+        fn.argtypes = [P, P, P, P, P, P, P, I, I, I, I, I, L, L, P]
+        fn.restype = ctypes.c_int
+
+
+def l2norm(x: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    return x * torch.rsqrt((x * x).sum(-1, keepdim=True) + eps)
+
+
+def recurrent_gated_delta_rule(q, k, v, g, beta, state: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Token-by-token recurrence in fp32 (oracle and the multi-token fallback with an initial state)."""
+    dt = q.dtype
+    qf = l2norm(q.float()).transpose(1, 2) * (q.shape[-1] ** -0.5)
+    kf = l2norm(k.float()).transpose(1, 2)
+    vf, bf, gf = v.float().transpose(1, 2), beta.float().transpose(1, 2), g.float().transpose(1, 2)
+    B, H, S, dk = kf.shape
+    dv = vf.shape[-1]
+    st = torch.zeros(B, H, dk, dv, device=q.device) if state is None else state.float().clone()
+    out = torch.empty(B, H, S, dv, device=q.device)
+    for i in range(S):
+        st = st * gf[:, :, i].exp()[..., None, None]
+        kv = (st * kf[:, :, i].unsqueeze(-1)).sum(-2)
+        delta = (vf[:, :, i] - kv) * bf[:, :, i].unsqueeze(-1)
+        st = st + kf[:, :, i].unsqueeze(-1) * delta.unsqueeze(-2)
+        out[:, :, i] = (st * qf[:, :, i].unsqueeze(-1)).sum(-2)
+    return out.transpose(1, 2).contiguous().to(dt), st
+
+
+def chunk_gated_delta_rule(q, k, v, g, beta, chunk_size: int = 64, state: Optional[torch.Tensor] = None):
+    """Chunk-parallel form: the intra-chunk triangular system is solved with one batched
+    unit-lower-triangular solve; chunks are chained through the [dk, dv] state."""
+    dt = q.dtype
+    qf = l2norm(q.float()).transpose(1, 2) * (q.shape[-1] ** -0.5)
+    kf = l2norm(k.float()).transpose(1, 2)
+    vf, bf, gf = v.float().transpose(1, 2), beta.float().transpose(1, 2), g.float().transpose(1, 2)
+    B, H, S, dk = kf.shape
+    dv = vf.shape[-1]
+    pad = (-S) % chunk_size
+    if pad:
+        P = lambda t, d: torch.nn.functional.pad(t, (0, 0, 0, pad) if d else (0, pad))
+        qf, kf, vf, bf, gf = P(qf, 1), P(kf, 1), P(vf, 1), P(bf, 0), P(gf, 0)
+    n, C = (S + pad) // chunk_size, chunk_size
+    rs = lambda t: t.reshape(B, H, n, C, *t.shape[3:])
+    qf, kf, vf, bf, gf = rs(qf), rs(kf), rs(vf), rs(bf), rs(gf)
+    gc = gf.cumsum(-1)
+    decay = torch.tril((gc.unsqueeze(-1) - gc.unsqueeze(-2))).exp().tril()
+    kb, vb = kf * bf.unsqueeze(-1), vf * bf.unsqueeze(-1)
+    L = (kb @ kf.transpose(-1, -2) * decay).tril(-1)                           # strictly lower
+    eye = torch.eye(C, device=q.device)
+    rhs = torch.cat([vb, kb * gc.exp().unsqueeze(-1)], dim=-1)
+    sol = torch.linalg.solve_triangular(eye + L, rhs, upper=False, unitriangular=True)
+    u, w = sol[..., :dv], sol[..., dv:]                                          # "value" and "k_cumdecay"
+    intra = (qf @ kf.transpose(-1, -2) * decay).tril()
+    st = torch.zeros(B, H, dk, dv, device=q.device) if state is None else state.float().clone()
+    out = torch.empty(B, H, n, C, dv, device=q.device)
+    for i in range(n):
+        v_new = u[:, :, i] - w[:, :, i] @ st
+        out[:, :, i] = (qf[:, :, i] * gc[:, :, i].exp().unsqueeze(-1)) @ st + intra[:, :, i] @ v_new
+        g_last = gc[:, :, i, -1]
+        st = st * g_last.exp()[..., None, None] + (kf[:, :, i] * (g_last.unsqueeze(-1) - gc[:, :, i]).exp().unsqueeze(-1)).transpose(-1, -2) @ v_new
+    out = out.reshape(B, H, n * C, dv)[:, :, :S].transpose(1, 2).contiguous().to(dt)
+    return out, st
+
+
+def gdr_decode_step(q, k, v, g, beta, state: torch.Tensor) -> torch.Tensor:
+    """One token: q, k [B, 1, Hk, dk] (un-repeated key heads), v [B, 1, Hv, dv], g/beta [B, 1, Hv];
+    ``state`` fp32 [B, Hv, dk, dv] is updated IN PLACE.  Returns [B, 1, Hv, dv]."""
+    B, _, Hk, dk = q.shape
+    Hv, dv = v.shape[2], v.shape[3]
+    if (q.is_cuda and q.dtype == torch.bfloat16 and dk in (64, 128) and state.dtype == torch.float32
+            and state.is_contiguous() and q.stride(-1) == 1 and k.stride(-1) == 1 and v.stride(-1) == 1
+            and q.stride(2) == dk and k.stride(2) == dk and v.stride(2) == dv and q.stride(0) == k.stride(0)):
+        out = torch.empty((B, 1, Hv, dv), dtype=q.dtype, device=q.device)
+        gc, bc = g.float().contiguous(), beta.float().contiguous()
+        check(lib().tyr_gdr_decode(ptr(q), ptr(k), ptr(v), ptr(gc), ptr(bc), ptr(state), ptr(out), B, Hk, Hv, dk, dv,
+                                   q.stride(0), v.stride(0), cur_stream(q.device)), "gdr_decode")
+        return out
+    rep = Hv // Hk
+    qr, kr = q.repeat_interleave(rep, dim=2), k.repeat_interleave(rep, dim=2)
+    out, st = recurrent_gated_delta_rule(qr, kr, v, g, beta, state)
+    state.copy_(st)
+    return out

@@ -28,9 +28,9 @@ def _sigs(lib_):
     table = {
         "tyr_nvfp4_quantize": [P, P, P, P, L, L, P], "tyr_nvfp4_dequant": [P, P, P, P, L, L, P],
         "tyr_moe_route": [P, P, P, P, P, I, I, I, I, I, F, F, P],
-        "tyr_moe_layout": [P, P, P, P, P, P, P, I, I, P],
+        "tyr_moe_layout": [P, P, P, P, P, P, P, P, I, I, P],
         "tyr_moe_gather_rows": [P, P, P, I, I, I, P], "tyr_moe_combine": [P, P, P, P, P, I, I, I, P],
-        "tyr_moe_fp4_gemv": [P] * 15 + [I, I, I, I, P], "tyr_moe_finalize": [P, P, P, L, P],
+        "tyr_moe_fp4_gemv": [P] * 17 + [I, I, I, I, I, P], "tyr_moe_finalize": [P, P, P, L, P],
     }
     for name, args in table.items():
         fn = getattr(lib_, name, None)
@@ -135,17 +135,19 @@ def route(logits: torch.Tensor, k: int, *, softmax: bool = False, bias: Optional
     return ids, w * scale, counts
 
 
-def layout(ids: torch.Tensor, counts: torch.Tensor, want_tiles: bool = False):
+def layout(ids: torch.Tensor, counts: torch.Tensor, want_tiles: bool = False, want_active: bool = False):
     """(offsets int32 [E+1], pair_order int32 [pairs], pair_pos int32 [pairs]) - expert-major.
     With ``want_tiles`` a fourth result: the 128-row tile prefix table the grouped GEMM walks."""
     pairs, E = ids.numel(), counts.numel()
     if ids.is_cuda:
-        meta = torch.empty(3 * E + 2, dtype=torch.int32, device=ids.device)
-        offsets, tiles, cursors = meta[:E + 1], meta[E + 1:2 * E + 2], meta[2 * E + 2:]
+        meta = torch.empty(4 * E + 3, dtype=torch.int32, device=ids.device)
+        offsets, tiles, cursors, active = meta[:E + 1], meta[E + 1:2 * E + 2], meta[2 * E + 2:3 * E + 2], meta[3 * E + 2:]
         op = torch.empty(2 * pairs, dtype=torch.int32, device=ids.device)
         order, pos = op[:pairs], op[pairs:]
-        check(lib().tyr_moe_layout(ptr(ids.contiguous()), ptr(counts), ptr(offsets), ptr(cursors), ptr(tiles), ptr(order),
-                                   ptr(pos), pairs, E, cur_stream(ids.device)), "moe_layout")
+        check(lib().tyr_moe_layout(ptr(ids.contiguous()), ptr(counts), ptr(offsets), ptr(cursors), ptr(tiles), ptr(active),
+                                   ptr(order), ptr(pos), pairs, E, cur_stream(ids.device)), "moe_layout")
+        if want_active:
+            return offsets, order, pos, tiles, active       # active[:E] compact expert list, active[E] their number
         return (offsets, order, pos, tiles) if want_tiles else (offsets, order, pos)
     flat = ids.reshape(-1).long()
     order = torch.argsort(flat, stable=True).to(torch.int32)
@@ -252,7 +254,7 @@ def moe_eager(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, gate: t
     return out.to(x.dtype)
 
 
-GEMV_MAX_PAIRS_PER_EXPERT = 24
+GEMV_MAX_PAIRS_PER_EXPERT = 8
 
 
 def moe_fp4_forward(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, ex: PackedExperts,
@@ -270,9 +272,11 @@ def moe_fp4_forward(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, e
         return y + add if add is not None else y
     if counts is None:
         counts = torch.bincount(ids.reshape(-1).long(), minlength=E).to(torch.int32)
-    offsets, order, pos, tiles = layout(ids.to(torch.int32), counts, want_tiles=True)
+    offsets, order, pos, tiles, active = layout(ids.to(torch.int32), counts, want_active=True)
     wf = weights.float().contiguous()
     path = force_path or ("gemv" if T * k <= GEMV_MAX_PAIRS_PER_EXPERT * E else "gemm")
+    if h % 128 or mi % 128:
+        path = "gemm"
     st = cur_stream(x.device)
     if path == "gemv":
         hid = torch.empty((T * k, mi), dtype=torch.float32, device=x.device)
@@ -281,7 +285,8 @@ def moe_fp4_forward(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, e
         check(lib().tyr_moe_fp4_gemv(ptr(x.contiguous()), ptr(ex.gate_packed), ptr(sc(ex.gate_scale)), ptr(ex.gate_global),
                                      ptr(ex.up_packed), ptr(sc(ex.up_scale)), ptr(ex.up_global),
                                      ptr(ex.down_packed), ptr(sc(ex.down_scale)), ptr(ex.down_global),
-                                     ptr(offsets), ptr(order), ptr(wf), ptr(hid), ptr(routed), E, k, h, mi, st),
+                                     ptr(offsets), ptr(active), ptr(active[E:]), ptr(order), ptr(wf), ptr(hid), ptr(routed),
+                                     T * k, E, k, h, mi, st),
               "moe_fp4_gemv")
         out = torch.empty_like(x)
         check(lib().tyr_moe_finalize(ptr(routed), ptr(add.contiguous() if add is not None else None), ptr(out),
@@ -295,4 +300,56 @@ def moe_fp4_forward(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, e
     out = torch.empty_like(x)
     check(lib().tyr_moe_combine(ptr(y), ptr(pos), ptr(wf), ptr(add.contiguous() if add is not None else None), ptr(out),
                                 T, k, h, st), "moe_combine")
+    return out
+
+
+_gu_cache: Dict[int, torch.Tensor] = {}
+
+
+def interleave_gate_up(gate_up: torch.Tensor) -> torch.Tensor:
+    """[E, 2*mi, h] (gate rows then up rows) -> 128-row gate/up interleave expected by the grouped GEMM's
+    SwiGLU epilogue; mi is padded to a multiple of 128 with zero rows.  Cached per source tensor."""
+    key = gate_up.data_ptr()
+    hit = _gu_cache.get(key)
+    if hit is not None and hit.shape[0] == gate_up.shape[0]:
+        return hit
+    E, two_mi, h = gate_up.shape
+    mi = two_mi // 2
+    g, u = gate_up[:, :mi], gate_up[:, mi:]
+    pad = (-mi) % 128
+    if pad:
+        g, u = torch.nn.functional.pad(g, (0, 0, 0, pad)), torch.nn.functional.pad(u, (0, 0, 0, pad))
+    mp = mi + pad
+    out = torch.stack([g.reshape(E, mp // 128, 128, h), u.reshape(E, mp // 128, 128, h)], dim=2).reshape(E, 2 * mp, h).contiguous()
+    if len(_gu_cache) > 256:
+        _gu_cache.clear()
+    _gu_cache[key] = out
+    return out
+
+
+def moe_dense_forward(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor,
+                      counts: Optional[torch.Tensor] = None, add: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """bf16 expert banks: ``gate_up`` [E, 2*mi, h], ``down`` [E, h, mi].  Grouped tensor-core path on the
+    GPU for bf16; per-expert loop otherwise (Tyr/Model/Qwen35/Model.lean:200-248 computes the same sum
+    by gathering one expert matrix per (token, slot))."""
+    T, h = x.shape
+    E, two_mi, _ = gate_up.shape
+    mi = two_mi // 2
+    k = ids.shape[1]
+    if not (x.is_cuda and x.dtype == torch.bfloat16 and gate_up.dtype == torch.bfloat16 and h % 8 == 0 and mi % 8 == 0):
+        y = moe_eager(x, ids, weights, gate_up[:, :mi], gate_up[:, mi:], down)
+        return y if add is None else (y.float() + add.float()).to(x.dtype)
+    if counts is None:
+        counts = torch.bincount(ids.reshape(-1).long(), minlength=E).to(torch.int32)
+    offsets, order, pos, tiles = layout(ids.to(torch.int32), counts, want_tiles=True)
+    st = cur_stream(x.device)
+    gu = interleave_gate_up(gate_up)
+    dn = down if mi % 128 == 0 else torch.nn.functional.pad(down, (0, (-mi) % 128)).contiguous()
+    xs = torch.empty((T * k, h), dtype=x.dtype, device=x.device)
+    check(lib().tyr_moe_gather_rows(ptr(x.contiguous()), ptr(order), ptr(xs), T * k, k, h, st), "moe_gather_rows")
+    hid = grouped_gemm(xs, gu, offsets, tiles, act="swiglu")
+    y = grouped_gemm(hid, dn.contiguous(), offsets, tiles)
+    out = torch.empty_like(x)
+    check(lib().tyr_moe_combine(ptr(y), ptr(pos), ptr(weights.float().contiguous()), ptr(add.contiguous() if add is not None else None),
+                                ptr(out), T, k, h, st), "moe_combine")
     return out

@@ -1,4 +1,4 @@
-"""Kernel micro-benchmarks: `python -m tyr_b200.utils.kernel_bench [gemm|attention|moe|all]`.
+"""Kernel micro-benchmarks: `python -m tyr_b200.utils.kernel_bench [gemm|attention|moe|moe-decode|all]`.
 
 Times the hand-written kernels with CUDA events (5 warm-up + 20 timed iterations, a 256 MB
 buffer written between iterations to flush the 126 MB L2) on the NanoChat d20 shapes and prints
@@ -88,7 +88,7 @@ def bench_attention(results):
         print(f"flash fwd B{B} H{H} T{T} causal={causal}: ours {ours:7.3f} ms {flops/ours/1e9:7.1f} TF/s | SDPA {lib:7.3f} ms {flops/lib/1e9:7.1f} TF/s", flush=True)
 
 
-def bench_moe(results):
+def bench_moe(results, cases=None):
     """Fused NVFP4 MoE op at Laguna-S-2.1 shapes (hidden 3072, 256 experts, top-10, FFN 1024): effective
     FP4 weight-read bandwidth for decode-sized batches (the reference's bar is >= 150 GB/s at one token,
     Tests/RunLagunaFused.lean:373-386) and tokens/s for prefill-sized batches."""
@@ -100,7 +100,7 @@ def bench_moe(results):
     gen = torch.Generator().manual_seed(0)
     ex = L.random_packed_experts(cfg, dev, gen)
     E, k, h, mi = cfg.num_experts, cfg.num_experts_per_tok, cfg.hidden_size, cfg.moe_intermediate_size
-    for T, path in ((1, "gemv"), (4, "gemv"), (16, "gemv"), (64, "gemv"), (64, "gemm"), (512, "gemm"), (4096, "gemm")):
+    for T, path in cases or ((1, "gemv"), (4, "gemv"), (16, "gemv"), (64, "gemv"), (64, "gemm"), (512, "gemm"), (4096, "gemm")):
         x = torch.randn(T, h, device=dev).bfloat16()
         ids, w, cnt = moe.route(torch.randn(T, E, device=dev), k)
         fn = lambda: moe.moe_fp4_forward(x, ids, w, ex, counts=cnt, force_path=path)
@@ -124,6 +124,8 @@ def main(argv):
         bench_attention(results)
     if what in ("moe", "all"):
         bench_moe(results)
+    if what == "moe-decode":
+        bench_moe(results, ((1, "gemv"), (64, "gemv")))
     print(json.dumps(results))
 
 
