@@ -295,67 +295,79 @@ constexpr int kWarps = 4;        // warps per CTA
 constexpr int kRowsCta = 16 * kWarps;
 
 struct StageArgs {
-  const __nv_bfloat16* x;      // stage A: [T, h] activations; stage B: unused
-  const float* hid_in;         // stage B: [pairs, mi] fp32 (expert-major positions)
+  const __nv_bfloat16* x;      // stage A: [T, h] activations
+  const float* hid_g;          // stage B input / stage A output: raw gate sums [pairs, mi] (expert-major positions)
+  const float* hid_u;          //                                  raw up sums
   const uint8_t* w0;           // stage A: gate packed; stage B: down packed
   const uint8_t* s0;
-  const float* g0;
+  const float* g0;             // global scale of w0's bank
   const uint8_t* w1;           // stage A: up packed
   const uint8_t* s1;
   const float* g1;
+  const float* gg;             // stage B: gate / up global scales (to finish silu(g) * u while staging)
+  const float* gu;
   const int* offsets;          // [E+1]
   const int* active;           // [E] compact list of experts with at least one pair
   const int* n_active;         // [1]
   const int* pair_order;       // [pairs] pair index at each expert-major position
   const float* pair_weight;    // [pairs] routing weight by pair index (stage B)
-  float* hid_out;              // stage A: [pairs, mi] fp32
+  float* out_g;                // stage A outputs (plain store when gridDim.z == 1, atomic otherwise)
+  float* out_u;
   float* out;                  // stage B: [T, h] fp32, atomically accumulated
   int k, in_dim, out_dim;      // stage A: in = h, out = mi; stage B: in = mi, out = h
 };
 
-__device__ __forceinline__ uint32_t e2m1x2_to_f16x2(uint32_t byte) {
-  __half2_raw h = __nv_cvt_fp4x2_to_halfraw2(static_cast<__nv_fp4x2_storage_t>(byte), __NV_E2M1);
-  return static_cast<uint32_t>(h.x) | (static_cast<uint32_t>(h.y) << 16);
+// e2m1 -> f16 without a table: with the nibble at bits [15:12] of a half, the sign stays at bit 15
+// and the three magnitude bits move to [11:9] (low two exponent bits and the top mantissa bit).
+// Read as f16 that is value * 2^-14, subnormal codes included; the group scale is applied as
+// (scale * 2^7) in f16 (max 448 * 128 < 65504) and the missing 2^7 goes onto the fp32 accumulator.
+// One 32-bit word holds nibbles n0..n7; register j pairs (n_j, n_{j+4}).
+__device__ __forceinline__ void decode_word(uint32_t w, uint32_t scale2, uint32_t (&r)[4]) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const uint32_t tj = j == 3 ? w : (w << (12 - 4 * j));
+    const uint32_t v = (tj & 0x80008000u) | ((tj >> 3) & 0x0E000E00u);
+    __half2 h = __hmul2(*reinterpret_cast<const __half2*>(&v), *reinterpret_cast<const __half2*>(&scale2));
+    r[j] = *reinterpret_cast<uint32_t*>(&h);
+  }
 }
-__device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
-  __half2 r = __hmul2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
-  return *reinterpret_cast<uint32_t*>(&r);
-}
-__device__ __forceinline__ uint32_t e4m3_to_f16x2(uint32_t byte) {
+__device__ __forceinline__ uint32_t e4m3_x128_to_f16x2(uint32_t byte) {
   __half_raw h = __nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>(byte), __NV_E4M3);
-  return static_cast<uint32_t>(h.x) * 0x00010001u;
+  __half v = __hmul(*reinterpret_cast<__half*>(&h), __float2half(128.f));
+  return static_cast<uint32_t>(*reinterpret_cast<unsigned short*>(&v)) * 0x00010001u;
 }
+constexpr float kDecodeRebias = 128.f;     // 2^14 / 2^7 left to apply after the contraction
+
 __device__ __forceinline__ void mma_f16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                               uint32_t b0, uint32_t b1) {
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-__device__ __forceinline__ uint32_t pack_f16x2_sat(float a, float b) {
+__device__ __forceinline__ unsigned short f16_sat(float a) {
   a = fminf(fmaxf(a, -65504.f), 65504.f);
-  b = fminf(fmaxf(b, -65504.f), 65504.f);
-  __half2 h = __floats2half2_rn(a, b);
-  return *reinterpret_cast<uint32_t*>(&h);
+  __half h = __float2half_rn(a);
+  return *reinterpret_cast<unsigned short*>(&h);
 }
 
 // One 128-column step of one 16-row tile: rows (g, g+8) of one matrix.
 //   wlo / whi: the lane's 16 bytes of row g / row g+8;  slo / shi: its two scale bytes per row.
+// Word i of the 16 bytes feeds k-steps 2i and 2i+1; k-step s takes registers 2(s&1), 2(s&1)+1, i.e.
+// elements {8i+j, 8i+j+4} and {8i+j+1, 8i+j+5} with j = 2(s&1); the activations are staged in the
+// same order (position of element e inside its 8: ((e & 3) << 1) | (e >> 2)).
 __device__ __forceinline__ void tile_step(float (&c)[4], const uint4& wlo, const uint4& whi, uint32_t slo, uint32_t shi,
                                           const uint32_t (&b)[16]) {
   const uint32_t lo[4] = {wlo.x, wlo.y, wlo.z, wlo.w};
   const uint32_t hi[4] = {whi.x, whi.y, whi.z, whi.w};
-  const uint32_t sl[2] = {e4m3_to_f16x2(slo & 0xff), e4m3_to_f16x2(slo >> 8)};
-  const uint32_t sh[2] = {e4m3_to_f16x2(shi & 0xff), e4m3_to_f16x2(shi >> 8)};
+  const uint32_t sl[2] = {e4m3_x128_to_f16x2(slo & 0xff), e4m3_x128_to_f16x2(slo >> 8)};
+  const uint32_t sh[2] = {e4m3_x128_to_f16x2(shi & 0xff), e4m3_x128_to_f16x2(shi >> 8)};
 #pragma unroll
-  for (int s = 0; s < 8; ++s) {
-    // k-step s uses bytes 2s and 2s+1 of the lane's 16 (elements 4s..4s+3); bytes 0-7 are scale group 0
-    const uint32_t wl = lo[s >> 1] >> ((s & 1) * 16);
-    const uint32_t wh = hi[s >> 1] >> ((s & 1) * 16);
-    const uint32_t a0 = hmul2_u32(e2m1x2_to_f16x2(wl & 0xff), sl[s >> 2]);
-    const uint32_t a2 = hmul2_u32(e2m1x2_to_f16x2((wl >> 8) & 0xff), sl[s >> 2]);
-    const uint32_t a1 = hmul2_u32(e2m1x2_to_f16x2(wh & 0xff), sh[s >> 2]);
-    const uint32_t a3 = hmul2_u32(e2m1x2_to_f16x2((wh >> 8) & 0xff), sh[s >> 2]);
-    mma_f16_16816(c, a0, a1, a2, a3, b[2 * s], b[2 * s + 1]);
+  for (int i = 0; i < 4; ++i) {
+    uint32_t rl[4], rh[4];
+    decode_word(lo[i], sl[i >> 1], rl);
+    decode_word(hi[i], sh[i >> 1], rh);
+    mma_f16_16816(c, rl[0], rh[0], rl[1], rh[1], b[4 * i], b[4 * i + 1]);
+    mma_f16_16816(c, rl[2], rh[2], rl[3], rh[3], b[4 * i + 2], b[4 * i + 3]);
   }
 }
 
@@ -368,45 +380,66 @@ __global__ void __launch_bounds__(32 * kWarps) moe_fp4_gemv_kernel(StageArgs a) 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int K = a.in_dim;
-  const int xstride = K + 8;                                  // halves; +16 B staggers rows across banks
-  __half* xs = reinterpret_cast<__half*>(smem_raw);           // [kP][xstride]
+  // this CTA's slice of the contraction: steps [st0, st1) of 128 columns each
+  const int steps = K >> 7;
+  const int st0 = steps * blockIdx.z / gridDim.z, st1 = steps * (blockIdx.z + 1) / gridDim.z;
+  const int kc0 = st0 << 7, kcols = (st1 - st0) << 7;
+  const int xstride = kcols + 8;                              // halves; +16 B staggers rows across banks
+  unsigned short* xs = reinterpret_cast<unsigned short*>(smem_raw);   // [kP][xstride] f16 bits
   const int row0 = blockIdx.x * kRowsCta + warp * 16;
   const bool rows_ok = row0 < a.out_dim;                      // out_dim is a multiple of 16
-  const int steps = K >> 7;                                   // 128 columns per step (K % 128 == 0)
   const long long rbytes = K >> 1, sbytes = K >> 4;
   const long long r_lo = static_cast<long long>(e) * a.out_dim + row0 + g;
-  const uint8_t* w0lo = a.w0 + r_lo * rbytes + t * 16;
+  const uint8_t* w0lo = a.w0 + r_lo * rbytes + t * 16 + (kc0 >> 1);
   const uint8_t* w0hi = w0lo + 8 * rbytes;
-  const uint8_t* s0lo = a.s0 + r_lo * sbytes + t * 2;
+  const uint8_t* s0lo = a.s0 + r_lo * sbytes + t * 2 + (kc0 >> 4);
   const uint8_t* s0hi = s0lo + 8 * sbytes;
-  const uint8_t* w1lo = STAGE_A ? a.w1 + r_lo * rbytes + t * 16 : nullptr;
+  const uint8_t* w1lo = STAGE_A ? a.w1 + r_lo * rbytes + t * 16 + (kc0 >> 1) : nullptr;
   const uint8_t* w1hi = STAGE_A ? w1lo + 8 * rbytes : nullptr;
-  const uint8_t* s1lo = STAGE_A ? a.s1 + r_lo * sbytes + t * 2 : nullptr;
+  const uint8_t* s1lo = STAGE_A ? a.s1 + r_lo * sbytes + t * 2 + (kc0 >> 4) : nullptr;
   const uint8_t* s1hi = STAGE_A ? s1lo + 8 * sbytes : nullptr;
+  float ig = 0.f, iu = 0.f;
+  if (!STAGE_A) { ig = 1.f / a.gg[e]; iu = 1.f / a.gu[e]; }
 
   for (int base = begin; base < end; base += kP) {
     const int np = min(kP, end - base);
     __syncthreads();
-    // stage activations of this pass as f16
-    for (int i = threadIdx.x; i < np * (K >> 1); i += blockDim.x) {
-      const int p = i / (K >> 1), c = (i % (K >> 1)) * 2;
-      float v0, v1;
+    // stage this pass's activations as f16 in the k order of the decoded fragments, 8 at a time
+    for (int i = threadIdx.x; i < np * (kcols >> 3); i += blockDim.x) {
+      const int p = i / (kcols >> 3), c = (i % (kcols >> 3)) << 3;
+      float v[8];
       if (STAGE_A) {
         const int tok = a.pair_order[base + p] / a.k;
-        const float2 f = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(a.x + static_cast<long long>(tok) * K + c));
-        v0 = f.x; v1 = f.y;
+        const uint4 u = *reinterpret_cast<const uint4*>(a.x + static_cast<long long>(tok) * K + kc0 + c);
+        const float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y), f2 = unpack_bf16x2(u.z), f3 = unpack_bf16x2(u.w);
+        v[0] = f0.x; v[1] = f0.y; v[2] = f1.x; v[3] = f1.y; v[4] = f2.x; v[5] = f2.y; v[6] = f3.x; v[7] = f3.y;
       } else {
-        const float2 f = *reinterpret_cast<const float2*>(a.hid_in + static_cast<long long>(base + p) * K + c);
-        v0 = f.x; v1 = f.y;
+        const long long o = static_cast<long long>(base + p) * K + kc0 + c;
+        const float4 g0 = *reinterpret_cast<const float4*>(a.hid_g + o), g1 = *reinterpret_cast<const float4*>(a.hid_g + o + 4);
+        const float4 u0 = *reinterpret_cast<const float4*>(a.hid_u + o), u1 = *reinterpret_cast<const float4*>(a.hid_u + o + 4);
+        const float gv[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+        const float uv[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float gs = gv[j] * ig;
+          v[j] = gs / (1.f + __expf(-gs)) * (uv[j] * iu);
+        }
       }
-      *reinterpret_cast<uint32_t*>(xs + p * xstride + c) = pack_f16x2_sat(v0, v1);
+      // element e goes to position ((e & 3) << 1) | (e >> 2): order 0,4,1,5,2,6,3,7
+      uint4 o4;
+      o4.x = f16_sat(v[0]) | (static_cast<uint32_t>(f16_sat(v[4])) << 16);
+      o4.y = f16_sat(v[1]) | (static_cast<uint32_t>(f16_sat(v[5])) << 16);
+      o4.z = f16_sat(v[2]) | (static_cast<uint32_t>(f16_sat(v[6])) << 16);
+      o4.w = f16_sat(v[3]) | (static_cast<uint32_t>(f16_sat(v[7])) << 16);
+      *reinterpret_cast<uint4*>(xs + p * xstride + c) = o4;
     }
     __syncthreads();
     if (!rows_ok) continue;
     float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
-    const __half* xrow = xs + g * xstride + t * 32;
-#pragma unroll 2
-    for (int st = 0; st < steps; ++st) {
+    const unsigned short* xrow = xs + g * xstride + t * 32;
+    const int nst = st1 - st0;
+#pragma unroll 4
+    for (int st = 0; st < nst; ++st) {
       const uint4 a_lo = __ldg(reinterpret_cast<const uint4*>(w0lo + st * 64));
       const uint4 a_hi = __ldg(reinterpret_cast<const uint4*>(w0hi + st * 64));
       const uint32_t sa_lo = __ldg(reinterpret_cast<const uint16_t*>(s0lo + st * 8));
@@ -436,17 +469,22 @@ __global__ void __launch_bounds__(32 * kWarps) moe_fp4_gemv_kernel(StageArgs a) 
     }
     // c[0], c[1]: (row g, pairs 2t, 2t+1);  c[2], c[3]: (row g+8, pairs 2t, 2t+1)
     if (STAGE_A) {
-      const float ig = 1.f / a.g0[e], iu = 1.f / a.g1[e];
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
         const int n = 2 * t + (q & 1), row = row0 + g + (q >> 1) * 8;
         if (n < np) {
-          const float gv = c0[q] * ig, uv = c1[q] * iu;
-          a.hid_out[static_cast<long long>(base + n) * a.out_dim + row] = gv / (1.f + __expf(-gv)) * uv;
+          const long long o = static_cast<long long>(base + n) * a.out_dim + row;
+          if (gridDim.z == 1) {
+            a.out_g[o] = c0[q] * kDecodeRebias;
+            a.out_u[o] = c1[q] * kDecodeRebias;
+          } else {
+            atomicAdd(a.out_g + o, c0[q] * kDecodeRebias);
+            atomicAdd(a.out_u + o, c1[q] * kDecodeRebias);
+          }
         }
       }
     } else {
-      const float id = 1.f / a.g0[e];
+      const float id = kDecodeRebias / a.g0[e];
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
         const int n = 2 * t + (q & 1), row = row0 + g + (q >> 1) * 8;
@@ -534,8 +572,20 @@ extern "C" TYR_EXPORT int tyr_moe_combine(const void* y, const int* pair_pos, co
   return (int)cudaGetLastError();
 }
 
+static int pick_split(int ctas, int steps, int sm_count) {
+  // split the contraction until about four CTAs per SM exist; the split must divide the step count
+  int z = 1;
+  while (ctas * z < 4 * sm_count && z < steps) {
+    int nz = z + 1;
+    while (nz < steps && steps % nz) ++nz;
+    z = nz;
+  }
+  return z;
+}
+
 // Decode path: routed[T, h] (fp32, zero on entry) += sum_k w * down(silu(gate x) * up x).
 // `active` / `n_active` come from tyr_moe_layout; h and mi must be multiples of 128.
+// `hid` holds 2 * pairs * mi floats (raw gate sums, then raw up sums) and must be zero on entry.
 extern "C" TYR_EXPORT int tyr_moe_fp4_gemv(const void* x, const void* gate_p, const void* gate_s, const float* gate_g,
                                            const void* up_p, const void* up_s, const float* up_g,
                                            const void* down_p, const void* down_s, const float* down_g,
@@ -546,14 +596,25 @@ extern "C" TYR_EXPORT int tyr_moe_fp4_gemv(const void* x, const void* gate_p, co
   cudaStream_t st = (cudaStream_t)stream;
   const int slots = pairs < E ? pairs : E;
   if (slots > 65535) return -1;
+  static int sm_count = 0;
+  if (sm_count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+  }
+  float* hid_g = hid;
+  float* hid_u = hid + static_cast<long long>(pairs) * mi;
   StageArgs a{};
   a.x = (const __nv_bfloat16*)x;
   a.w0 = (const uint8_t*)gate_p; a.s0 = (const uint8_t*)gate_s; a.g0 = gate_g;
   a.w1 = (const uint8_t*)up_p; a.s1 = (const uint8_t*)up_s; a.g1 = up_g;
   a.offsets = offsets; a.active = active; a.n_active = n_active; a.pair_order = pair_order; a.pair_weight = pair_weight;
-  a.hid_out = hid; a.k = k; a.in_dim = h; a.out_dim = mi;
-  const size_t smem_a = sizeof(__half) * kP * (h + 8);
-  const size_t smem_b = sizeof(__half) * kP * (mi + 8);
+  a.out_g = hid_g; a.out_u = hid_u; a.k = k; a.in_dim = h; a.out_dim = mi;
+  const int rows_a = (mi + kRowsCta - 1) / kRowsCta, rows_b = (h + kRowsCta - 1) / kRowsCta;
+  const int za = pick_split(rows_a * slots, h >> 7, sm_count);
+  const int zb = pick_split(rows_b * slots, mi >> 7, sm_count);
+  const size_t smem_a = sizeof(unsigned short) * kP * (((h >> 7) + za - 1) / za * 128 + 8);
+  const size_t smem_b = sizeof(unsigned short) * kP * (((mi >> 7) + zb - 1) / zb * 128 + 8);
   if (smem_a > 200 * 1024 || smem_b > 200 * 1024) return -3;
   static size_t cfg_a = 0, cfg_b = 0;
   if (smem_a > 48 * 1024 && cfg_a < smem_a) {
@@ -564,13 +625,13 @@ extern "C" TYR_EXPORT int tyr_moe_fp4_gemv(const void* x, const void* gate_p, co
     cudaFuncSetAttribute(moe_fp4_gemv_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_b);
     cfg_b = smem_b;
   }
-  moe_fp4_gemv_kernel<true><<<dim3((mi + kRowsCta - 1) / kRowsCta, slots), 32 * kWarps, smem_a, st>>>(a);
+  moe_fp4_gemv_kernel<true><<<dim3(rows_a, slots, za), 32 * kWarps, smem_a, st>>>(a);
   StageArgs b{};
-  b.hid_in = hid;
+  b.hid_g = hid_g; b.hid_u = hid_u; b.gg = gate_g; b.gu = up_g;
   b.w0 = (const uint8_t*)down_p; b.s0 = (const uint8_t*)down_s; b.g0 = down_g;
   b.offsets = offsets; b.active = active; b.n_active = n_active; b.pair_order = pair_order; b.pair_weight = pair_weight;
   b.out = routed; b.k = k; b.in_dim = mi; b.out_dim = h;
-  moe_fp4_gemv_kernel<false><<<dim3((h + kRowsCta - 1) / kRowsCta, slots), 32 * kWarps, smem_b, st>>>(b);
+  moe_fp4_gemv_kernel<false><<<dim3(rows_b, slots, zb), 32 * kWarps, smem_b, st>>>(b);
   return (int)cudaGetLastError();
 }
 

@@ -279,7 +279,7 @@ def moe_fp4_forward(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, e
         path = "gemm"
     st = cur_stream(x.device)
     if path == "gemv":
-        hid = torch.empty((T * k, mi), dtype=torch.float32, device=x.device)
+        hid = torch.zeros((2, T * k, mi), dtype=torch.float32, device=x.device)
         routed = torch.zeros((T, h), dtype=torch.float32, device=x.device)
         sc = lambda t: t.view(torch.uint8)
         check(lib().tyr_moe_fp4_gemv(ptr(x.contiguous()), ptr(ex.gate_packed), ptr(sc(ex.gate_scale)), ptr(ex.gate_global),
