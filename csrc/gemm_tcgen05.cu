@@ -44,6 +44,21 @@ struct GemmParams {
   // the host ever reading the counts.
   const int* group_offsets;
   const int* group_tiles;
+  // Tensor-parallel fusion over peer memory (ranks of one NVLink domain, plain peer loads / stores):
+  //  tp_mode 1, GEMM -> reduce-scatter: row r of the product belongs to rank r / rows_per_rank; the
+  //    epilogue stores the bf16 partial straight into that rank's slot buffer peer_c[owner] at row
+  //    tp_rank * rows_per_rank + r % rows_per_rank (the owner sums its tp_world slots afterwards).
+  //  tp_mode 2, all-gather -> GEMM: rows [j * rows_per_rank, (j+1) * rows_per_rank) of A live on rank j;
+  //    the producer warp fetches each A tile from its owner with a TMA load through that rank's map
+  //    (no cluster multicast).
+  //  m_rot rotates the order of row tiles so that every rank starts with a different peer (mode 1)
+  //  or with its own rows (mode 2).
+  int tp_mode, tp_rank, tp_world, rows_per_rank, m_rot;
+  void* peer_c[8];
+};
+
+struct TmapPeers {
+  CUtensorMap m[8];
 };
 
 template <int BN, int STAGES>
@@ -71,7 +86,8 @@ __device__ __forceinline__ float apply_act(float v, int act) {
 template <int BN, int STAGES, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(192, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
-                         const __grid_constant__ CUtensorMap tmB, GemmParams p) {
+                         const __grid_constant__ CUtensorMap tmB,
+                         const __grid_constant__ TmapPeers tmP, GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   using Smem = GemmSmem<BN, STAGES>;
   Smem& s = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -158,7 +174,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     bi = static_cast<int>(tile / per_batch);
     const int r = static_cast<int>(tile % per_batch);
     // n fastest: concurrently resident tiles share A rows and keep B (weights) in L2.
-    m0 = (r / tiles_n) * BM;
+    m0 = ((r / tiles_n + p.m_rot) % tiles_m) * BM;
     n0 = (r % tiles_n) * BN;
   };
   const long long cursor0 = (p.out_mode == 2) ? unit_begin : static_cast<long long>(blockIdx.x);
@@ -187,7 +203,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           if (!A_MN) {
             if (p.group_offsets != nullptr)
               tma_load_3d(s.a[st], &tmA, &s.full[st], k0, p.group_offsets[bi] + m0, 0);
-            else
+            else if (p.tp_mode == 2) {
+              const int src = m0 / p.rows_per_rank;
+              tma_load_3d(s.a[st], &tmP.m[src], &s.full[st], k0, m0 - src * p.rows_per_rank, bi);
+            } else
               tma_load_3d(s.a[st], &tmA, &s.full[st], k0, m0, bi);
           } else {
 #pragma unroll
@@ -288,6 +307,12 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
         c_off = static_cast<long long>(bi) * p.sC + static_cast<long long>(row) * p.ldc;
         x_off = static_cast<long long>(bi) * p.sAux + static_cast<long long>(row) * p.ldaux;
       }
+      void* c_base = p.C;
+      if (p.tp_mode == 1 && row_ok) {
+        const int owner = row / p.rows_per_rank;
+        c_base = p.peer_c[owner];
+        c_off = (static_cast<long long>(p.tp_rank) * p.rows_per_rank + (row - owner * p.rows_per_rank)) * p.ldc;
+      }
       if (p.act == 4) {
         // SwiGLU over column halves of the tile: out[:, n0/2 + j] = silu(acc[:, j]) * acc[:, BN/2 + j]
 #pragma unroll 1
@@ -376,7 +401,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           }
         }
         if (p.out_mode == 0) {
-          __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.C) + c_off + col;
+          __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(c_base) + c_off + col;
           if (full) {
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
@@ -499,7 +524,8 @@ struct TyrGemmArgs {
 static int g_sm_count = 0;
 
 template <int BN, int STAGES, bool A_MN, bool B_MN>
-static int launch_gemm(const TyrGemmArgs& a, const CUtensorMap& tmA, const CUtensorMap& tmB) {
+static int launch_gemm(const TyrGemmArgs& a, const CUtensorMap& tmA, const CUtensorMap& tmB,
+                       const tyr::TmapPeers& tmP, const tyr::GemmParams& tp) {
   using namespace tyr;
   auto kern = gemm_bf16_tcgen05_kernel<BN, STAGES, A_MN, B_MN>;
   constexpr size_t smem = sizeof(GemmSmem<BN, STAGES>) + 1024;
@@ -517,6 +543,9 @@ static int launch_gemm(const TyrGemmArgs& a, const CUtensorMap& tmA, const CUten
   p.alpha = a.alpha; p.beta = a.beta; p.act = a.act; p.out_mode = a.out_mode; p.err = a.err;
   p.group_offsets = a.group_offsets;
   p.group_tiles = a.group_tiles;
+  p.tp_mode = tp.tp_mode; p.tp_rank = tp.tp_rank; p.tp_world = tp.tp_world;
+  p.rows_per_rank = tp.rows_per_rank; p.m_rot = tp.m_rot;
+  for (int i = 0; i < 8; ++i) p.peer_c[i] = tp.peer_c[i];
   long long tiles = static_cast<long long>((a.M + BM - 1) / BM) * ((a.N + BN - 1) / BN) * a.batch;
   if (a.group_offsets != nullptr)   // host-side bound: every group may add one partial m-tile
     tiles = ((a.sA + BM - 1) / BM + (a.batch < a.sA ? a.batch : a.sA)) * ((a.N + BN - 1) / BN);
@@ -527,7 +556,7 @@ static int launch_gemm(const TyrGemmArgs& a, const CUtensorMap& tmA, const CUten
     if (units < grid) grid = static_cast<int>(units);
   }
   if (grid < 1) grid = 1;
-  kern<<<grid, 192, smem, reinterpret_cast<cudaStream_t>(a.stream)>>>(tmA, tmB, p);
+  kern<<<grid, 192, smem, reinterpret_cast<cudaStream_t>(a.stream)>>>(tmA, tmB, tmP, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 2000 + static_cast<int>(e);
 }
@@ -546,10 +575,44 @@ extern "C" TYR_EXPORT int tyr_bind_device(int device) {
   return 0;
 }
 
-// Returns 0 on success; negative = invalid argument; positive = CUDA/driver error.
-extern "C" TYR_EXPORT int tyr_gemm_bf16(const TyrGemmArgs* args) {
+extern "C" {
+// Tensor-parallel fusion request for tyr_gemm_bf16_tp.
+struct TyrTpArgs {
+  int mode;            // 1: GEMM -> reduce-scatter slots, 2: all-gather -> GEMM
+  int world, rank;
+  int rows_per_rank;   // multiple of 128
+  void* peers[8];      // mode 1: slot buffers [world * rows_per_rank, N] bf16 of every rank (row stride ldc)
+                       // mode 2: A shards [rows_per_rank, K] bf16 of every rank (row stride lda)
+};
+}
+
+static int gemm_impl(const TyrGemmArgs& a, const TyrTpArgs* tpa) {
   using namespace tyr;
-  const TyrGemmArgs& a = *args;
+  GemmParams tp{};
+  TmapPeers tmP{};
+  if (tpa != nullptr) {
+    if (tpa->world < 1 || tpa->world > 8 || tpa->rank < 0 || tpa->rank >= tpa->world) return -10;
+    if (tpa->rows_per_rank <= 0 || (tpa->rows_per_rank % BM) != 0 || a.M != tpa->rows_per_rank * tpa->world) return -11;
+    if (a.a_mn || a.batch != 1 || a.out_mode != 0 || a.group_offsets != nullptr) return -12;
+    tp.tp_mode = tpa->mode; tp.tp_rank = tpa->rank; tp.tp_world = tpa->world; tp.rows_per_rank = tpa->rows_per_rank;
+    const int tiles_per_rank = tpa->rows_per_rank / BM;
+    if (tpa->mode == 1) {
+      tp.m_rot = ((tpa->rank + 1) % tpa->world) * tiles_per_rank;     // remote owners first, own rows last
+      for (int i = 0; i < tpa->world; ++i) {
+        if (tpa->peers[i] == nullptr || (reinterpret_cast<uintptr_t>(tpa->peers[i]) & 15)) return -13;
+        tp.peer_c[i] = tpa->peers[i];
+      }
+    } else if (tpa->mode == 2) {
+      tp.m_rot = tpa->rank * tiles_per_rank;                          // own rows first
+      for (int i = 0; i < tpa->world; ++i) {
+        if (tpa->peers[i] == nullptr || (reinterpret_cast<uintptr_t>(tpa->peers[i]) & 15)) return -13;
+        int r = make_tmap_bf16_3d(&tmP.m[i], tpa->peers[i], a.K, tpa->rows_per_rank, 1, a.lda, 0, BM);
+        if (r) return 5000 + r;
+      }
+    } else {
+      return -10;
+    }
+  }
   if (a.M <= 0 || a.N <= 0 || a.K <= 0 || a.batch <= 0) return -1;
   if ((reinterpret_cast<uintptr_t>(a.A) & 15) || (reinterpret_cast<uintptr_t>(a.B) & 15) ||
       (reinterpret_cast<uintptr_t>(a.C) & 15))
@@ -581,15 +644,24 @@ extern "C" TYR_EXPORT int tyr_gemm_bf16(const TyrGemmArgs* args) {
   if (r) return 4000 + r;
 #define TYR_DISPATCH(BNv, ST)                                                   \
   do {                                                                          \
-    if (!a.a_mn && !a.b_mn) return launch_gemm<BNv, ST, false, false>(a, tmA, tmB); \
-    if (!a.a_mn && a.b_mn) return launch_gemm<BNv, ST, false, true>(a, tmA, tmB);   \
-    if (a.a_mn && a.b_mn) return launch_gemm<BNv, ST, true, true>(a, tmA, tmB);     \
-    return launch_gemm<BNv, ST, true, false>(a, tmA, tmB);                      \
+    if (!a.a_mn && !a.b_mn) return launch_gemm<BNv, ST, false, false>(a, tmA, tmB, tmP, tp); \
+    if (!a.a_mn && a.b_mn) return launch_gemm<BNv, ST, false, true>(a, tmA, tmB, tmP, tp);   \
+    if (a.a_mn && a.b_mn) return launch_gemm<BNv, ST, true, true>(a, tmA, tmB, tmP, tp);     \
+    return launch_gemm<BNv, ST, true, false>(a, tmA, tmB, tmP, tp);                      \
   } while (0)
   if (bn == 256) TYR_DISPATCH(256, 4);
   if (bn == 128) TYR_DISPATCH(128, 6);
 #undef TYR_DISPATCH
   return -6;
+}
+
+// Returns 0 on success; negative = invalid argument; positive = CUDA/driver error.
+extern "C" TYR_EXPORT int tyr_gemm_bf16(const TyrGemmArgs* args) { return gemm_impl(*args, nullptr); }
+
+// The same product with its collective fused in (see GemmParams::tp_mode).  Mode 2 ignores args->A.
+extern "C" TYR_EXPORT int tyr_gemm_bf16_tp(const TyrGemmArgs* args, const TyrTpArgs* tp) {
+  if (tp == nullptr) return -10;
+  return gemm_impl(*args, tp);
 }
 
 // ----------------------------------------------------------------------------------------

@@ -25,3 +25,11 @@ def test_fused_data_parallel_matches_accumulation(nproc):
         pytest.skip(f"needs {nproc} GPUs")
     r = _run_torchrun(os.path.join(ROOT, "tests", "workers", "dp_worker.py"), nproc, port=29611 + nproc)
     assert "DP_WORKER_RESULT PASS" in r.stdout, (r.stdout[-3000:], r.stderr[-3000:])
+
+
+@pytest.mark.parametrize("nproc", [2, 4, 8])
+def test_tensor_parallel_fused_gemm_collectives(nproc):
+    if torch.cuda.device_count() < nproc:
+        pytest.skip(f"needs {nproc} GPUs")
+    r = _run_torchrun(os.path.join(ROOT, "tests", "workers", "tp_worker.py"), nproc, port=29631 + nproc)
+    assert "TP_WORKER_RESULT PASS" in r.stdout, (r.stdout[-3000:], r.stderr[-3000:])

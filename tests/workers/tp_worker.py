@@ -1,0 +1,63 @@
+"""Child process of the tensor-parallel tests: one rank; backend from TYR_TEST_BACKEND (nccl on GPUs, gloo on CPU)."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+
+from tyr_b200.parallel.tp import TensorParallel  # noqa: E402
+
+
+def main():
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    backend = os.environ.get("TYR_TEST_BACKEND", "nccl")
+    if backend == "nccl":
+        torch.cuda.set_device(local)
+        dev = torch.device("cuda", local)
+        dist.init_process_group("nccl", device_id=dev)
+        dtype, rows, K, N = torch.bfloat16, 256 * world, 512, 384
+    else:
+        dev = torch.device("cpu")
+        dist.init_process_group("gloo")
+        dtype, rows, K, N = torch.float32, 6 * world, 16, 10
+    tp = TensorParallel(rank, world, dev, max_rows=rows, max_cols=max(N, 512), max_k=world * K)
+    g = torch.Generator().manual_seed(5)
+    x_full = (torch.randn(rows, world * K, generator=g) * 0.5).to(dtype)
+    w_full = (torch.randn(N, world * K, generator=g) * 0.1).to(dtype)
+    add_full = torch.randn(rows, N, generator=g).to(dtype)
+    ok = True
+    for it in range(3):                                   # repeated calls exercise the double buffering
+        # row-parallel: K split over ranks, rows scattered
+        xs, ws = x_full[:, rank * K:(rank + 1) * K].to(dev).contiguous(), w_full[:, rank * K:(rank + 1) * K].to(dev).contiguous()
+        rpr = rows // world
+        y = tp.gemm_reduce_scatter(xs * (it + 1), ws, add=add_full[rank * rpr:(rank + 1) * rpr].to(dev))
+        ref = (x_full.float() * (it + 1)) @ w_full.float().T + add_full.float()
+        err = (y.float().cpu() - ref[rank * rpr:(rank + 1) * rpr]).abs().max().item()
+        ok &= err < (0.25 if dtype == torch.bfloat16 else 1e-4) * max(1.0, ref.abs().max().item() / 8)
+        # column-parallel over row shards: every rank gets all rows of its N slice
+        nl = N // world if N % world == 0 else N
+        wl = w_full[rank * nl:(rank + 1) * nl, :K].to(dev).contiguous() if N % world == 0 else w_full[:, :K].to(dev).contiguous()
+        z = tp.allgather_gemm((x_full[rank * rpr:(rank + 1) * rpr, :K] * (it + 1)).to(dev).contiguous(), wl, act="relu")
+        wref = w_full[rank * nl:(rank + 1) * nl, :K] if N % world == 0 else w_full[:, :K]
+        zref = torch.relu((x_full[:, :K].float() * (it + 1)) @ wref.float().T)
+        err2 = (z.float().cpu() - zref).abs().max().item()
+        ok &= err2 < (0.1 if dtype == torch.bfloat16 else 1e-4) * max(1.0, zref.abs().max().item() / 8)
+        if not ok:
+            print(f"rank {rank} it {it}: rs err {err} ag err {err2}", flush=True)
+            break
+    if dev.type == "cuda":
+        torch.cuda.synchronize()
+        from tyr_b200.ops._common import raise_on_device_error
+        raise_on_device_error(dev)
+    flag = torch.tensor([1.0 if ok else 0.0], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        print("TP_WORKER_RESULT", "PASS" if flag.item() == 1.0 else "FAIL", flush=True)
+    tp.close()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

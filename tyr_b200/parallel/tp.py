@@ -1,0 +1,157 @@
+"""Tensor parallelism with the collectives fused into the tcgen05 GEMM (one process per GPU, one
+NVLink domain, symmetric heap over CUDA IPC).
+
+* ``gemm_reduce_scatter``: row-parallel linear.  Every rank multiplies its K-slice; the GEMM epilogue
+  stores each bf16 partial tile straight into the slot buffer of the rank that owns those rows
+  (plain peer stores, remote owners first so the traffic overlaps the remaining tiles); after one
+  flag barrier the owner sums its ``world`` slots in fp32.
+* ``allgather_gemm``: column-parallel linear over row-sharded activations.  Shards are staged in
+  symmetric memory; the GEMM's producer warp TMA-loads each A tile from the rank that owns it (own rows
+  first, no cluster multicast), so the gather happens tile by tile inside the MMA pipeline.
+
+Without CUDA (tests on gloo) or for world size 1 the same results come from ``torch.distributed``
+collectives / a plain GEMM.  The reference has no tensor parallelism; these serve the Qwen3.5 TP model.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from .._native import GemmArgs, kernels
+from ..distributed.symm import FlagBarrier, SymmetricHeap
+from ..ops._common import check, cur_stream, err_word, ptr
+from ..ops.gemm import _ACT, gemm
+
+
+class TpArgs(ctypes.Structure):
+    _fields_ = [("mode", ctypes.c_int), ("world", ctypes.c_int), ("rank", ctypes.c_int), ("rows_per_rank", ctypes.c_int),
+                ("peers", ctypes.c_void_p * 8)]
+
+
+def _declare(lib):
+    if getattr(lib, "_tp_declared", False):
+        return
+    lib.tyr_gemm_bf16_tp.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
+    lib.tyr_gemm_bf16_tp.restype = ctypes.c_int
+    lib.tyr_slot_sum_bf16.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
+    lib.tyr_slot_sum_bf16.restype = ctypes.c_int
+    lib._tp_declared = True
+
+
+class TensorParallel:
+    """Buffers are sized once: ``max_rows`` total activation rows (all ranks), ``max_cols`` widest
+    reduce-scatter output, ``max_k`` widest gathered input."""
+
+    def __init__(self, rank: int, world: int, device, group=None, max_rows: int = 8192, max_cols: int = 8192, max_k: int = 8192):
+        self.rank, self.world, self.group = rank, world, group
+        self.device = torch.device(device)
+        self.fused = self.device.type == "cuda" and world > 1
+        self._seq = 0
+        self._parity = 0
+        if not self.fused:
+            return
+        if world > 8:
+            raise ValueError("tensor parallel groups span at most 8 GPUs of one NVLink domain")
+        _declare(kernels())
+        self.max_rows, self.max_cols, self.max_k = max_rows, max_cols, max_k
+        rpr = (max_rows + world - 1) // world
+        slot_bytes = world * rpr * max_cols * 2
+        stage_bytes = rpr * max_k * 2
+        self.heap = SymmetricHeap(2 * slot_bytes + 2 * stage_bytes + 65536, rank, world, self.device, group)
+        self._slots = [self.heap.alloc((world * rpr * max_cols,), torch.bfloat16) for _ in range(2)]
+        self._stage = [self.heap.alloc((rpr * max_k,), torch.bfloat16) for _ in range(2)]
+        self.barrier = FlagBarrier(self.heap, n_slots=2)
+
+    # -- helpers ----------------------------------------------------------------------------------------
+    def _sync(self, slot: int):
+        self._seq += 1
+        self.barrier.signal(slot, self._seq)
+        self.barrier.wait(slot, self._seq, ptr(err_word(self.device)))
+
+    def _peers(self, t: torch.Tensor):
+        off = self.heap.offset_bytes(t)
+        arr = (ctypes.c_void_p * 8)()
+        for r in range(self.world):
+            arr[r] = self.heap.peer_ptrs[r] + off
+        return arr
+
+    def close(self):
+        if self.fused:
+            self.heap.close()
+
+    # -- GEMM -> reduce-scatter ----------------------------------------------------------------------------
+    def gemm_reduce_scatter(self, x: torch.Tensor, w: torch.Tensor, add: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """x: [M, K_local] (all M rows, this rank's K slice); w: [N, K_local].  Returns this rank's
+        ``[M / world, N]`` rows of ``sum_ranks x @ w^T`` (+ ``add``)."""
+        M, N = x.shape[0], w.shape[0]
+        if self.world == 1:
+            y = gemm(x, w, a_layout="K", b_layout="K") if x.is_cuda else (x.float() @ w.float().T).to(x.dtype)
+            return y if add is None else y + add
+        if M % self.world:
+            raise ValueError(f"rows ({M}) must divide evenly over {self.world} ranks")
+        rpr = M // self.world
+        if not self.fused or rpr % 128 or N % 8 or x.dtype != torch.bfloat16:
+            y = (x.float() @ w.float().T) if not x.is_cuda else torch.matmul(x, w.T).float()
+            out = torch.empty((rpr, N), dtype=torch.float32, device=x.device)
+            dist.reduce_scatter_tensor(out, y.contiguous(), group=self.group)
+            return (out if add is None else out + add.float()).to(x.dtype)
+        if M * N > self._slots[0].numel():
+            raise ValueError("gemm_reduce_scatter: product exceeds the slot buffers this group was sized for")
+        slots = self._slots[self._parity]
+        self._parity ^= 1
+        args = GemmArgs()
+        x = x.contiguous()
+        args.A, args.B, args.C = x.data_ptr(), w.data_ptr(), slots.data_ptr()
+        args.M, args.N, args.K, args.batch = M, N, x.shape[1], 1
+        args.lda, args.ldb, args.ldc = x.stride(0), w.stride(0), N
+        args.alpha, args.bn = 1.0, 0
+        args.err = err_word(x.device).data_ptr()
+        args.stream = cur_stream(x.device).value
+        tp = TpArgs(1, self.world, self.rank, rpr, self._peers(slots))
+        check(kernels().tyr_gemm_bf16_tp(ctypes.byref(args), ctypes.byref(tp)), "gemm_bf16_tp(reduce-scatter)")
+        self._sync(0)
+        out = torch.empty((rpr, N), dtype=torch.bfloat16, device=x.device)
+        check(kernels().tyr_slot_sum_bf16(ptr(slots), self.world, rpr * N, ptr(add.contiguous() if add is not None else None),
+                                          ptr(out), cur_stream(x.device)), "slot_sum_bf16")
+        return out
+
+    # -- all-gather -> GEMM ------------------------------------------------------------------------------------
+    def allgather_gemm(self, x_shard: torch.Tensor, w: torch.Tensor, act: Optional[str] = None) -> torch.Tensor:
+        """x_shard: this rank's ``[M / world, K]`` rows; w: [N_local, K].  Returns ``[M, N_local]``."""
+        rpr, K = x_shard.shape
+        if self.world == 1:
+            return gemm(x_shard, w, a_layout="K", b_layout="K", act=act) if x_shard.is_cuda else _cpu_lin(x_shard, w, act)
+        if not self.fused or rpr % 128 or K % 8 or x_shard.dtype != torch.bfloat16:
+            full = torch.empty((rpr * self.world, K), dtype=x_shard.dtype, device=x_shard.device)
+            dist.all_gather_into_tensor(full, x_shard.contiguous(), group=self.group)
+            return gemm(full, w, a_layout="K", b_layout="K", act=act) if full.is_cuda and full.dtype == torch.bfloat16 else _cpu_lin(full, w, act)
+        if rpr * K > self._stage[0].numel():
+            raise ValueError("allgather_gemm: shard exceeds the staging buffers this group was sized for")
+        stage = self._stage[self._parity]
+        self._parity ^= 1
+        stage[:rpr * K].view(rpr, K).copy_(x_shard)
+        self._sync(1)
+        M, N = rpr * self.world, w.shape[0]
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=x_shard.device)
+        args = GemmArgs()
+        args.A, args.B, args.C = stage.data_ptr(), w.data_ptr(), out.data_ptr()
+        args.M, args.N, args.K, args.batch = M, N, K, 1
+        args.lda, args.ldb, args.ldc = K, w.stride(0), N
+        args.alpha, args.bn, args.act = 1.0, 0, _ACT[act]
+        args.err = err_word(out.device).data_ptr()
+        args.stream = cur_stream(out.device).value
+        tp = TpArgs(2, self.world, self.rank, rpr, self._peers(stage))
+        check(kernels().tyr_gemm_bf16_tp(ctypes.byref(args), ctypes.byref(tp)), "gemm_bf16_tp(all-gather)")
+        return out
+
+
+def _cpu_lin(x, w, act):
+    y = x.float() @ w.float().T
+    if act == "relu":
+        y = torch.relu(y)
+    elif act == "relu2":
+        y = torch.relu(y).square()
+    return y.to(x.dtype)
