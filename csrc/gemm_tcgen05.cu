@@ -6,7 +6,8 @@
 //   contiguous) or MN-major (row/column dimension contiguous), so the forward (X*W^T), the
 //   data-gradient (dY*W) and the weight-gradient (dY^T*X) products of a linear layer all run
 //   without a transpose pass.
-// * One CTA per SM, 192 threads: warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner,
+// * One CTA per SM, 256 threads: warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner,
+//   warps 6-7 = gather warps (only busy in tp_mode 2, see GemmParams),
 //   warps 2..5 = epilogue (one TMEM lane quarter each).  The fp32 accumulator lives in TMEM
 //   and is double buffered (2 x BN columns) so the epilogue of tile i overlaps the main loop
 //   of tile i+1.
@@ -48,13 +49,19 @@ struct GemmParams {
   //  tp_mode 1, GEMM -> reduce-scatter: row r of the product belongs to rank r / rows_per_rank; the
   //    epilogue stores the bf16 partial straight into that rank's slot buffer peer_c[owner] at row
   //    tp_rank * rows_per_rank + r % rows_per_rank (the owner sums its tp_world slots afterwards).
-  //  tp_mode 2, all-gather -> GEMM: rows [j * rows_per_rank, (j+1) * rows_per_rank) of A live on rank j;
-  //    the producer warp fetches each A tile from its owner with a TMA load through that rank's map
-  //    (no cluster multicast).
+  //  tp_mode 2, all-gather -> GEMM: rows [j * rows_per_rank, (j+1) * rows_per_rank) of A live on rank j
+  //    (peer_c[j] points at that shard).  Own rows are read in place.  Remote rows cross NVLink exactly
+  //    once: the gather warps of all CTAs copy them, row tile by row tile in the order the tiles are
+  //    consumed, into the local buffer `gather_buf` ([M, K], described by tmA) with plain peer loads and
+  //    bump tile_ready[row tile]; the producer warp waits (bounded) for 2 * gridDim.x arrivals before its
+  //    first TMA load of such a tile.  Gather warps never wait, so the kernel cannot deadlock.
   //  m_rot rotates the order of row tiles so that every rank starts with a different peer (mode 1)
   //  or with its own rows (mode 2).
   int tp_mode, tp_rank, tp_world, rows_per_rank, m_rot;
   void* peer_c[8];
+  __nv_bfloat16* gather_buf;
+  int* tile_ready;
+  long long lda;
 };
 
 struct TmapPeers {
@@ -65,6 +72,7 @@ template <int BN, int STAGES>
 struct __align__(1024) GemmSmem {
   uint8_t a[STAGES][BM * BK * 2];
   uint8_t b[STAGES][BN * BK * 2];
+  uint8_t out_stage[4][2][32 * 128];   // per epilogue warp: two 32-row x 128-byte tiles (128B swizzle) for TMA stores
   uint64_t full[STAGES];
   uint64_t empty[STAGES];
   uint64_t acc_full[2];
@@ -84,9 +92,10 @@ __device__ __forceinline__ float apply_act(float v, int act) {
 }
 
 template <int BN, int STAGES, bool A_MN, bool B_MN>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(256, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
                          const __grid_constant__ CUtensorMap tmB,
+                         const __grid_constant__ CUtensorMap tmC,
                          const __grid_constant__ TmapPeers tmP, GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   using Smem = GemmSmem<BN, STAGES>;
@@ -191,6 +200,26 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       while (ok && next_segment(cursor, tile, kb0, kb1)) {
         int bi, m0, n0;
         decode_tile(tile, bi, m0, n0);
+        const int a_src = p.tp_mode == 2 ? m0 / p.rows_per_rank : 0;
+        if (p.tp_mode == 2 && a_src != p.tp_rank) {
+          // rows of a peer: wait until every gather warp has copied its part of this row tile
+          const int* flag = p.tile_ready + m0 / BM;
+          const int target = 2 * static_cast<int>(gridDim.x);
+          const long long t0 = clock64();
+          int seen;
+          do {
+            asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
+            if (seen >= target) break;
+            if (clock64() - t0 > kWaitBudgetCycles) {
+              report_error(p.err, ERR_PEER_FLAG_TIMEOUT, m0 / BM);
+              ok = false;
+              break;
+            }
+            __nanosleep(100);
+          } while (true);
+          if (!ok) break;
+          asm volatile("fence.proxy.async;" ::: "memory");
+        }
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int st = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -203,10 +232,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           if (!A_MN) {
             if (p.group_offsets != nullptr)
               tma_load_3d(s.a[st], &tmA, &s.full[st], k0, p.group_offsets[bi] + m0, 0);
-            else if (p.tp_mode == 2) {
-              const int src = m0 / p.rows_per_rank;
-              tma_load_3d(s.a[st], &tmP.m[src], &s.full[st], k0, m0 - src * p.rows_per_rank, bi);
-            } else
+            else if (p.tp_mode == 2 && a_src == p.tp_rank)
+              tma_load_3d(s.a[st], &tmP.m[a_src], &s.full[st], k0, m0 - a_src * p.rows_per_rank, bi);
+            else
               tma_load_3d(s.a[st], &tmA, &s.full[st], k0, m0, bi);
           } else {
 #pragma unroll
@@ -276,6 +304,34 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       }
       if (!ok) s.abort_flag = 1;
     }
+  } else if (warp >= 6) {
+    // ------------------------------------------------------------------ gather warps (tp_mode 2)
+    if (p.tp_mode == 2) {
+      const long long nvec = static_cast<long long>(BM) * p.K / 8;       // 16-byte vectors per row tile (lda == K)
+      const long long gid = static_cast<long long>(blockIdx.x) * 64 + (threadIdx.x - 192);
+      const long long gstride = static_cast<long long>(gridDim.x) * 64;
+      for (int i = 0; i < tiles_m; ++i) {
+        const int mt = (i + p.m_rot) % tiles_m;
+        const int src = mt * BM / p.rows_per_rank;
+        if (src == p.tp_rank) continue;
+        const uint4* from = reinterpret_cast<const uint4*>(
+            reinterpret_cast<const __nv_bfloat16*>(p.peer_c[src]) + static_cast<long long>(mt * BM - src * p.rows_per_rank) * p.lda);
+        uint4* to = reinterpret_cast<uint4*>(p.gather_buf + static_cast<long long>(mt) * BM * p.lda);
+        for (long long v = gid; v < nvec; v += 8 * gstride) {
+          uint4 buf[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            if (v + j * gstride < nvec) buf[j] = from[v + j * gstride];
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            if (v + j * gstride < nvec) to[v + j * gstride] = buf[j];
+        }
+        __threadfence();
+        asm volatile("fence.proxy.async;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) asm volatile("red.release.gpu.global.add.s32 [%0], 1;" ::"l"(p.tile_ready + mt) : "memory");
+      }
+    }
   } else {
     // ------------------------------------------------------------------ epilogue warps
     const int quarter = warp & 3;  // TMEM lane quarter this warp may access
@@ -283,6 +339,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     int kb0, kb1;
     uint32_t seg = 0;
     bool ok = true;
+    // bf16 outputs leave through shared memory and TMA stores (full 128-byte rows; also the efficient
+    // packet size for stores that cross NVLink in tp_mode 1); grouped / SwiGLU outputs need row masks
+    // and keep the direct stores.
+    const bool tma_out = p.out_mode == 0 && p.group_offsets == nullptr && p.act != 4;
+    uint32_t n_stores = 0;
     while (ok && next_segment(cursor, tile, kb0, kb1)) {
       int bi, m0, n0;
       decode_tile(tile, bi, m0, n0);
@@ -366,10 +427,18 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           if (lane == 0) mbar_arrive(&s.acc_empty[buf]);
         }
         const int col = n0 + c * 32;
-        if (!row_ok || col >= p.N) continue;
+        if (tma_out) {
+          if (col >= p.N) continue;            // a tile that ends inside the last valid chunk was flushed there
+          if (!(c & 1)) {                      // about to refill a staging tile: its previous store must have read it
+            if (lane == 0) tma_store_wait_read<1>();
+            __syncwarp();
+          }
+        } else if (!row_ok || col >= p.N) {
+          continue;
+        }
         float v[32];
         const bool full = (col + 32 <= p.N);
-        const bool use_aux = p.aux != nullptr && (p.beta != 0.f || p.act == 3);
+        const bool use_aux = p.aux != nullptr && (p.beta != 0.f || p.act == 3) && row_ok;
         float ax[32];
         if (use_aux) {
           const __nv_bfloat16* axp = p.aux + x_off + col;
@@ -400,7 +469,35 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
             for (int j = 0; j < 32; ++j) v[j] += p.beta * ax[j];
           }
         }
-        if (p.out_mode == 0) {
+        if (tma_out) {
+          uint8_t* st = s.out_stage[quarter][n_stores & 1] + lane * 128;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint4 u;
+            u.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
+            u.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
+            u.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
+            u.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
+            const int chunk = (c & 1) * 4 + q;                       // 16-byte chunk of the 128-byte row
+            *reinterpret_cast<uint4*>(st + ((chunk ^ (lane & 7)) << 4)) = u;
+          }
+          if ((c & 1) || col + 32 >= p.N) {
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+              int y = m0 + quarter * 32;
+              const CUtensorMap* tm = &tmC;
+              if (p.tp_mode == 1) {
+                const int owner = m0 / p.rows_per_rank;
+                tm = &tmP.m[owner];
+                y = p.tp_rank * p.rows_per_rank + (y - owner * p.rows_per_rank);
+              }
+              tma_store_3d(tm, s.out_stage[quarter][n_stores & 1], col - (c & 1) * 32, y, bi);
+              tma_store_commit();
+            }
+            ++n_stores;
+          }
+        } else if (p.out_mode == 0) {
           __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(c_base) + c_off + col;
           if (full) {
 #pragma unroll
@@ -446,6 +543,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       }
       ++seg;
     }
+    if (tma_out && lane == 0) tma_store_wait_all();   // stores must have left shared memory before the CTA exits
   }
 
   tc_fence_before();
@@ -524,7 +622,7 @@ struct TyrGemmArgs {
 static int g_sm_count = 0;
 
 template <int BN, int STAGES, bool A_MN, bool B_MN>
-static int launch_gemm(const TyrGemmArgs& a, const CUtensorMap& tmA, const CUtensorMap& tmB,
+static int launch_gemm(const TyrGemmArgs& a, const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC,
                        const tyr::TmapPeers& tmP, const tyr::GemmParams& tp) {
   using namespace tyr;
   auto kern = gemm_bf16_tcgen05_kernel<BN, STAGES, A_MN, B_MN>;
@@ -546,6 +644,7 @@ static int launch_gemm(const TyrGemmArgs& a, const CUtensorMap& tmA, const CUten
   p.tp_mode = tp.tp_mode; p.tp_rank = tp.tp_rank; p.tp_world = tp.tp_world;
   p.rows_per_rank = tp.rows_per_rank; p.m_rot = tp.m_rot;
   for (int i = 0; i < 8; ++i) p.peer_c[i] = tp.peer_c[i];
+  p.gather_buf = tp.gather_buf; p.tile_ready = tp.tile_ready; p.lda = a.lda;
   long long tiles = static_cast<long long>((a.M + BM - 1) / BM) * ((a.N + BN - 1) / BN) * a.batch;
   if (a.group_offsets != nullptr)   // host-side bound: every group may add one partial m-tile
     tiles = ((a.sA + BM - 1) / BM + (a.batch < a.sA ? a.batch : a.sA)) * ((a.N + BN - 1) / BN);
@@ -556,7 +655,7 @@ static int launch_gemm(const TyrGemmArgs& a, const CUtensorMap& tmA, const CUten
     if (units < grid) grid = static_cast<int>(units);
   }
   if (grid < 1) grid = 1;
-  kern<<<grid, 192, smem, reinterpret_cast<cudaStream_t>(a.stream)>>>(tmA, tmB, tmP, p);
+  kern<<<grid, 256, smem, reinterpret_cast<cudaStream_t>(a.stream)>>>(tmA, tmB, tmC, tmP, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 2000 + static_cast<int>(e);
 }
@@ -582,7 +681,9 @@ struct TyrTpArgs {
   int world, rank;
   int rows_per_rank;   // multiple of 128
   void* peers[8];      // mode 1: slot buffers [world * rows_per_rank, N] bf16 of every rank (row stride ldc)
-                       // mode 2: A shards [rows_per_rank, K] bf16 of every rank (row stride lda)
+                       // mode 2: A shards [rows_per_rank, K] bf16 of every rank (contiguous rows, lda == K)
+  void* gather_buf;    // mode 2: local [world * rows_per_rank, K] bf16 landing buffer for the peers' rows
+  int* tile_ready;     // mode 2: world * rows_per_rank / 128 counters (zeroed by this call)
 };
 }
 
@@ -604,11 +705,20 @@ static int gemm_impl(const TyrGemmArgs& a, const TyrTpArgs* tpa) {
       }
     } else if (tpa->mode == 2) {
       tp.m_rot = tpa->rank * tiles_per_rank;                          // own rows first
+      if (a.lda != a.K || tpa->gather_buf == nullptr || tpa->tile_ready == nullptr ||
+          (reinterpret_cast<uintptr_t>(tpa->gather_buf) & 15))
+        return -14;
       for (int i = 0; i < tpa->world; ++i) {
         if (tpa->peers[i] == nullptr || (reinterpret_cast<uintptr_t>(tpa->peers[i]) & 15)) return -13;
-        int r = make_tmap_bf16_3d(&tmP.m[i], tpa->peers[i], a.K, tpa->rows_per_rank, 1, a.lda, 0, BM);
-        if (r) return 5000 + r;
+        tp.peer_c[i] = tpa->peers[i];
       }
+      int r = make_tmap_bf16_3d(&tmP.m[tpa->rank], tpa->peers[tpa->rank], a.K, tpa->rows_per_rank, 1, a.lda, 0, BM);
+      if (r) return 5000 + r;
+      tp.gather_buf = reinterpret_cast<__nv_bfloat16*>(tpa->gather_buf);
+      tp.tile_ready = tpa->tile_ready;
+      cudaError_t e = cudaMemsetAsync(tpa->tile_ready, 0, sizeof(int) * tpa->world * tiles_per_rank,
+                                      reinterpret_cast<cudaStream_t>(a.stream));
+      if (e != cudaSuccess) return 7000 + static_cast<int>(e);
     } else {
       return -10;
     }
@@ -633,7 +743,8 @@ static int gemm_impl(const TyrGemmArgs& a, const TyrTpArgs* tpa) {
     if (a.a_mn || a.out_mode == 2 || a.sA <= 0 || a.group_tiles == nullptr) return -9;   // packed rows: K-major A, sA = total rows
     r = make_tmap_bf16_3d(&tmA, a.A, a.K, static_cast<uint64_t>(a.sA), 1, a.lda, 0, BM);
   } else if (!a.a_mn)
-    r = make_tmap_bf16_3d(&tmA, a.A, a.K, a.M, a.batch, a.lda, a.sA, BM);
+    r = make_tmap_bf16_3d(&tmA, (tpa != nullptr && tpa->mode == 2) ? tpa->gather_buf : a.A, a.K, a.M, a.batch, a.lda,
+                          a.sA, BM);
   else
     r = make_tmap_bf16_3d(&tmA, a.A, a.M, a.K, a.batch, a.lda, a.sA, BK);
   if (r) return 3000 + r;
@@ -642,12 +753,26 @@ static int gemm_impl(const TyrGemmArgs& a, const TyrTpArgs* tpa) {
   else
     r = make_tmap_bf16_3d(&tmB, a.B, a.N, a.K, a.batch, a.ldb, a.sB, BK);
   if (r) return 4000 + r;
+  CUtensorMap tmC{};
+  if (a.out_mode == 0 && a.group_offsets == nullptr && a.act != 4) {
+    if (tpa != nullptr && tpa->mode == 1) {
+      for (int i = 0; i < tpa->world; ++i) {
+        r = make_tmap_bf16_3d(&tmP.m[i], tpa->peers[i], a.N, static_cast<uint64_t>(tpa->world) * tpa->rows_per_rank, 1,
+                              a.ldc, 0, 32);
+        if (r) return 6000 + r;
+      }
+      tmC = tmP.m[tpa->rank];
+    } else {
+      r = make_tmap_bf16_3d(&tmC, a.C, a.N, a.M, a.batch, a.ldc, a.sC, 32);
+      if (r) return 6000 + r;
+    }
+  }
 #define TYR_DISPATCH(BNv, ST)                                                   \
   do {                                                                          \
-    if (!a.a_mn && !a.b_mn) return launch_gemm<BNv, ST, false, false>(a, tmA, tmB, tmP, tp); \
-    if (!a.a_mn && a.b_mn) return launch_gemm<BNv, ST, false, true>(a, tmA, tmB, tmP, tp);   \
-    if (a.a_mn && a.b_mn) return launch_gemm<BNv, ST, true, true>(a, tmA, tmB, tmP, tp);     \
-    return launch_gemm<BNv, ST, true, false>(a, tmA, tmB, tmP, tp);                      \
+    if (!a.a_mn && !a.b_mn) return launch_gemm<BNv, ST, false, false>(a, tmA, tmB, tmC, tmP, tp); \
+    if (!a.a_mn && a.b_mn) return launch_gemm<BNv, ST, false, true>(a, tmA, tmB, tmC, tmP, tp);   \
+    if (a.a_mn && a.b_mn) return launch_gemm<BNv, ST, true, true>(a, tmA, tmB, tmC, tmP, tp);     \
+    return launch_gemm<BNv, ST, true, false>(a, tmA, tmB, tmC, tmP, tp);                      \
   } while (0)
   if (bn == 256) TYR_DISPATCH(256, 4);
   if (bn == 128) TYR_DISPATCH(128, 6);

@@ -6,8 +6,10 @@ NVLink domain, symmetric heap over CUDA IPC).
   (plain peer stores, remote owners first so the traffic overlaps the remaining tiles); after one
   flag barrier the owner sums its ``world`` slots in fp32.
 * ``allgather_gemm``: column-parallel linear over row-sharded activations.  Shards are staged in
-  symmetric memory; the GEMM's producer warp TMA-loads each A tile from the rank that owns it (own rows
-  first, no cluster multicast), so the gather happens tile by tile inside the MMA pipeline.
+  symmetric memory; inside the GEMM kernel two gather warps per CTA pull the peers' rows over NVLink
+  (plain peer loads, each row once, in the order the row tiles are consumed) into a local landing buffer
+  and publish per-tile counters, while the MMA pipeline starts on the rank's own rows and picks up each
+  remote tile as soon as it has landed (bounded waits, no cluster multicast).
 
 Without CUDA (tests on gloo) or for world size 1 the same results come from ``torch.distributed``
 collectives / a plain GEMM.  The reference has no tensor parallelism; these serve the Qwen3.5 TP model.
@@ -28,7 +30,7 @@ from ..ops.gemm import _ACT, gemm
 
 class TpArgs(ctypes.Structure):
     _fields_ = [("mode", ctypes.c_int), ("world", ctypes.c_int), ("rank", ctypes.c_int), ("rows_per_rank", ctypes.c_int),
-                ("peers", ctypes.c_void_p * 8)]
+                ("peers", ctypes.c_void_p * 8), ("gather_buf", ctypes.c_void_p), ("tile_ready", ctypes.c_void_p)]
 
 
 def _declare(lib):
@@ -64,6 +66,9 @@ class TensorParallel:
         self._slots = [self.heap.alloc((world * rpr * max_cols,), torch.bfloat16) for _ in range(2)]
         self._stage = [self.heap.alloc((rpr * max_k,), torch.bfloat16) for _ in range(2)]
         self.barrier = FlagBarrier(self.heap, n_slots=2)
+        # landing buffer of the all-gather GEMM (peers' rows cross NVLink once) and its per-row-tile counters
+        self._gather = torch.empty((world * rpr * max_k,), dtype=torch.bfloat16, device=self.device)
+        self._tile_ready = torch.zeros((world * rpr + 127) // 128, dtype=torch.int32, device=self.device)
 
     # -- helpers ----------------------------------------------------------------------------------------
     def _sync(self, slot: int):
@@ -110,7 +115,7 @@ class TensorParallel:
         args.alpha, args.bn = 1.0, 0
         args.err = err_word(x.device).data_ptr()
         args.stream = cur_stream(x.device).value
-        tp = TpArgs(1, self.world, self.rank, rpr, self._peers(slots))
+        tp = TpArgs(1, self.world, self.rank, rpr, self._peers(slots), None, None)
         check(kernels().tyr_gemm_bf16_tp(ctypes.byref(args), ctypes.byref(tp)), "gemm_bf16_tp(reduce-scatter)")
         self._sync(0)
         out = torch.empty((rpr, N), dtype=torch.bfloat16, device=x.device)
@@ -143,7 +148,7 @@ class TensorParallel:
         args.alpha, args.bn, args.act = 1.0, 0, _ACT[act]
         args.err = err_word(out.device).data_ptr()
         args.stream = cur_stream(out.device).value
-        tp = TpArgs(2, self.world, self.rank, rpr, self._peers(stage))
+        tp = TpArgs(2, self.world, self.rank, rpr, self._peers(stage), self._gather.data_ptr(), self._tile_ready.data_ptr())
         check(kernels().tyr_gemm_bf16_tp(ctypes.byref(args), ctypes.byref(tp)), "gemm_bf16_tp(all-gather)")
         return out
 
