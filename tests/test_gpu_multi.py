@@ -33,3 +33,11 @@ def test_tensor_parallel_fused_gemm_collectives(nproc):
         pytest.skip(f"needs {nproc} GPUs")
     r = _run_torchrun(os.path.join(ROOT, "tests", "workers", "tp_worker.py"), nproc, port=29631 + nproc)
     assert "TP_WORKER_RESULT PASS" in r.stdout, (r.stdout[-3000:], r.stderr[-3000:])
+
+
+@pytest.mark.parametrize("nproc", [2, 4, 8])
+def test_expert_parallel_pull_dispatch_and_combine(nproc):
+    if torch.cuda.device_count() < nproc:
+        pytest.skip(f"needs {nproc} GPUs")
+    r = _run_torchrun(os.path.join(ROOT, "tests", "workers", "ep_worker.py"), nproc, port=29651 + nproc)
+    assert "EP_WORKER_RESULT PASS" in r.stdout, (r.stdout[-3000:], r.stderr[-3000:])

@@ -22,3 +22,11 @@ def test_world_one_is_a_plain_product():
     x, w = torch.randn(4, 8), torch.randn(3, 8)
     assert torch.allclose(tp.gemm_reduce_scatter(x, w), x @ w.T, atol=1e-5)
     assert torch.allclose(tp.allgather_gemm(x, w, act="relu"), torch.relu(x @ w.T), atol=1e-5)
+
+
+def test_expert_parallel_collective_path_two_gloo_ranks():
+    env = dict(os.environ, TYR_TEST_BACKEND="gloo", MASTER_ADDR="127.0.0.1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29673", os.path.join(ROOT, "tests", "workers", "ep_worker.py")]
+    r = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=240)
+    assert "EP_WORKER_RESULT PASS" in r.stdout, (r.stdout[-2000:], r.stderr[-2000:])
