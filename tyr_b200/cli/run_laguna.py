@@ -40,6 +40,8 @@ def parse(argv):
     p.add_argument("--temperature", type=float, default=0.0)
     p.add_argument("--top-k", type=int, default=None)
     p.add_argument("--top-p", type=float, default=1.0)
+    p.add_argument("--ep", action="store_true",
+                   help="under torchrun: split the experts over the ranks (expert parallel), every rank decodes its own batch")
     return p.parse_args(argv)
 
 
@@ -77,20 +79,52 @@ def bench(model, input_ids, max_new_tokens, eos=()):
 
 def main(argv=None) -> int:
     a = parse(sys.argv[1:] if argv is None else argv)
+    import os
+    world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
+    ep = None
+    if a.ep and world > 1:
+        import torch.distributed as dist
+        local = int(os.environ.get("LOCAL_RANK", "0"))
+        if a.device.startswith("cuda"):
+            torch.cuda.set_device(local)
+            a.device = f"cuda:{local}"
+            dist.init_process_group("nccl", device_id=torch.device(a.device))
+        else:
+            dist.init_process_group("gloo")
     dev = torch.device(a.device)
     dtype = torch.bfloat16 if dev.type == "cuda" else torch.float32
     strategy = (SamplingStrategy.greedy() if a.temperature <= 0 else
                 SamplingStrategy.multinomial(a.temperature, a.top_k, a.top_p))
     if a.random_init:
         cfg = L.LagunaConfig(num_hidden_layers=a.layers) if a.layers else L.LagunaConfig()
-        print(f"Random-init Laguna: {cfg.num_hidden_layers} layers, hidden {cfg.hidden_size}, {cfg.num_experts} experts "
-              f"top-{cfg.num_experts_per_tok}", flush=True)
-        model = L.init(cfg, device=dev, dtype=dtype)
-        ids = torch.randint(32, cfg.vocab_size, (a.batch_size, a.prompt_tokens), device=dev)
+        if a.ep and world > 1:
+            from ..parallel.ep import ExpertParallel
+            ep = ExpertParallel(rank, world, dev, cfg.num_experts, cfg.hidden_size, a.batch_size * a.prompt_tokens,
+                                cfg.num_experts_per_tok, capacity_factor=min(world, 2))
+        if rank == 0:
+            print(f"Random-init Laguna: {cfg.num_hidden_layers} layers, hidden {cfg.hidden_size}, {cfg.num_experts} experts "
+                  f"top-{cfg.num_experts_per_tok}" + (f", expert parallel over {world} ranks" if ep else ""), flush=True)
+        model = L.init(cfg, device=dev, dtype=dtype, ep=ep)
+        ids = torch.randint(32, cfg.vocab_size, (a.batch_size, a.prompt_tokens), device=dev,
+                            generator=torch.Generator(device=dev).manual_seed(rank))
         if a.bench:
             r = bench(model, ids, a.max_new_tokens)
-            print(f"BENCH prompt_tokens={r['prompt_tokens']} prefill_ms={r['prefill_ms']:.1f} prefill_tok_s={r['prefill_tok_s']:.1f}")
-            print(f"BENCH decode_tokens={r['decode_tokens']} decode_ms={r['decode_ms']:.1f} decode_tok_s={r['decode_tok_s']:.1f} batch={r['batch']}")
+            if ep is not None:
+                import torch.distributed as dist
+                t = torch.tensor([r["prefill_ms"], r["decode_ms"]], device=dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                r["prefill_ms"], r["decode_ms"] = t.tolist()
+                r["prompt_tokens"] *= world
+                r["decode_tokens"] *= world
+                r["prefill_tok_s"] = r["prompt_tokens"] / r["prefill_ms"] * 1e3
+                r["decode_tok_s"] = r["decode_tokens"] / r["decode_ms"] * 1e3 if r["decode_ms"] else 0.0
+            if rank == 0:
+                print(f"BENCH prompt_tokens={r['prompt_tokens']} prefill_ms={r['prefill_ms']:.1f} prefill_tok_s={r['prefill_tok_s']:.1f}")
+                print(f"BENCH decode_tokens={r['decode_tokens']} decode_ms={r['decode_ms']:.1f} decode_tok_s={r['decode_tok_s']:.1f} "
+                      f"batch={r['batch']} ranks={world}")
+            if ep is not None:
+                ep.close()
+                dist.destroy_process_group()
             return 0
         out = L.generate(model, ids, a.max_new_tokens, strategy, eos_token_ids=())
         print(out[:, a.prompt_tokens:].tolist())

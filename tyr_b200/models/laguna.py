@@ -268,6 +268,7 @@ class LagunaForCausalLM:
     norm: torch.Tensor
     lm_head: torch.Tensor
     tie_word_embeddings: bool = False
+    ep: Optional[object] = None      # parallel.ep.ExpertParallel: experts split over the ranks, banks hold the local slice
 
     @property
     def device(self):
@@ -282,10 +283,11 @@ def _w(shape, fan_in, device, dtype, gen):
     return (torch.randn(shape, generator=gen, dtype=torch.float32) * (fan_in ** -0.5)).to(device=device, dtype=dtype)
 
 
-def random_packed_experts(cfg: LagunaConfig, device, gen, dense_std: Optional[float] = None) -> moe_ops.PackedExperts:
+def random_packed_experts(cfg: LagunaConfig, device, gen, dense_std: Optional[float] = None,
+                          num_local: Optional[int] = None) -> moe_ops.PackedExperts:
     """Synthetic NVFP4 banks: quantised gaussian weights, real U8 / e4m3 tensors (the fused op needs
-    those, Tyr/Model/Laguna/MoE.lean:209-216)."""
-    E, mi, h = cfg.num_experts, cfg.moe_intermediate_size, cfg.hidden_size
+    those, Tyr/Model/Laguna/MoE.lean:209-216).  ``num_local`` builds only that many experts (one EP rank's slice)."""
+    E, mi, h = num_local or cfg.num_experts, cfg.moe_intermediate_size, cfg.hidden_size
 
     def bank(rows, cols):
         packed = torch.empty((E, rows, cols // 2), dtype=torch.uint8, device=device)
@@ -305,8 +307,11 @@ def random_packed_experts(cfg: LagunaConfig, device, gen, dense_std: Optional[fl
 
 
 def init(cfg: LagunaConfig, device="cpu", dtype=torch.float32, tie_word_embeddings: bool = False, seed: int = 0,
-         dense_experts: bool = False) -> LagunaForCausalLM:
+         dense_experts: bool = False, ep=None) -> LagunaForCausalLM:
+    """Random-init model.  With ``ep`` (an ``ExpertParallel`` group) every rank draws the same dense weights and
+    only its own slice of each expert bank."""
     gen = torch.Generator().manual_seed(seed)
+    egen = torch.Generator().manual_seed(seed + 7919 * (1 + (ep.rank if ep is not None else 0)))
     h, D = cfg.hidden_size, cfg.head_dim
     mk = lambda shape, fan: _w(shape, fan, device, dtype, gen)
     ones = lambda n: torch.ones(n, device=device, dtype=dtype)
@@ -322,13 +327,15 @@ def init(cfg: LagunaConfig, device="cpu", dtype=torch.float32, tie_word_embeddin
                 de = DenseExperts(mk((E, mi, h), h), mk((E, mi, h), h), mk((E, h, mi), mi))
                 ffn = SparseMoeBlock(router, None, mk((si, h), h), mk((si, h), h), mk((h, si), si), de)
             else:
-                ffn = SparseMoeBlock(router, random_packed_experts(cfg, device, gen), mk((si, h), h), mk((si, h), h), mk((h, si), si))
+                n_loc = ep.E_local if ep is not None else None
+                ffn = SparseMoeBlock(router, random_packed_experts(cfg, device, egen if ep is not None else gen, num_local=n_loc),
+                                     mk((si, h), h), mk((si, h), h), mk((h, si), si))
         else:
             ffn = DenseMLP(mk((cfg.intermediate_size, h), h), mk((cfg.intermediate_size, h), h), mk((h, cfg.intermediate_size), cfg.intermediate_size))
         layers.append(Layer(ones(h), attn, ones(h), ffn))
     emb = (torch.randn((cfg.vocab_size, h), generator=gen) * 0.02).to(device=device, dtype=dtype)
     head = emb if tie_word_embeddings else mk((cfg.vocab_size, h), h)
-    return LagunaForCausalLM(cfg, emb, layers, ones(h), head, tie_word_embeddings)
+    return LagunaForCausalLM(cfg, emb, layers, ones(h), head, tie_word_embeddings, ep)
 
 
 # ---- blocks ------------------------------------------------------------------------------------------------------
@@ -340,10 +347,16 @@ def route(cfg: LagunaConfig, r: Router, x2: torch.Tensor):
                          scale=cfg.moe_routed_scaling_factor)
 
 
-def moe_forward(cfg: LagunaConfig, m: SparseMoeBlock, x2: torch.Tensor, use_fused: bool = True) -> torch.Tensor:
-    """``scale * sum_k w_k expert_k(x) + shared(x)`` over [tokens, hidden] (MoE.lean:267-356)."""
+def moe_forward(cfg: LagunaConfig, m: SparseMoeBlock, x2: torch.Tensor, use_fused: bool = True, ep=None) -> torch.Tensor:
+    """``scale * sum_k w_k expert_k(x) + shared(x)`` over [tokens, hidden] (MoE.lean:267-356).  With ``ep`` the
+    routed part runs expert-parallel: rows are pulled by the rank that owns the expert and the results pulled back."""
     ids, w, counts = route(cfg, m.router, x2)
     shared = swiglu_mlp(x2, m.shared_gate_proj, m.shared_up_proj, m.shared_down_proj)
+    if ep is not None:
+        from ..parallel.ep import local_expert_fn
+        banks = m.experts if m.dense_experts is None else (
+            torch.cat([m.dense_experts.gate_proj, m.dense_experts.up_proj], 1), m.dense_experts.down_proj)
+        return ep.forward(x2, ids, w, local_expert_fn(banks), add=shared, counts=counts)
     if m.dense_experts is not None:
         de = m.dense_experts
         return (moe_ops.moe_eager(x2, ids, w, de.gate_proj, de.up_proj, de.down_proj).float() + shared.float()).to(x2.dtype)
@@ -373,7 +386,7 @@ def attention_forward(cfg: LagunaConfig, i: int, a: Attention, x: torch.Tensor, 
 
 
 def layer_forward(cfg: LagunaConfig, i: int, layer: Layer, x: torch.Tensor, tables: RotaryTables, position: int,
-                  cache: Optional[KVCache], use_fused: bool = True) -> torch.Tensor:
+                  cache: Optional[KVCache], use_fused: bool = True, ep=None) -> torch.Tensor:
     B, S, h = x.shape
     cos, sin = tables.rows(cfg.is_full(i), position, S)
     h1 = norm_w(x, layer.input_layernorm, cfg.rms_norm_eps)
@@ -382,7 +395,7 @@ def layer_forward(cfg: LagunaConfig, i: int, layer: Layer, x: torch.Tensor, tabl
     if isinstance(layer.ffn, DenseMLP):
         f = swiglu_mlp(h3, layer.ffn.gate_proj, layer.ffn.up_proj, layer.ffn.down_proj)
     else:
-        f = moe_forward(cfg, layer.ffn, h3.reshape(B * S, h), use_fused).reshape(B, S, h)
+        f = moe_forward(cfg, layer.ffn, h3.reshape(B * S, h), use_fused, ep).reshape(B, S, h)
     return h2 + f
 
 
@@ -392,7 +405,7 @@ def forward_hidden(m: LagunaForCausalLM, input_ids: torch.Tensor, use_fused: boo
     x = F.embedding(input_ids, m.embed_tokens)
     tables = precompute_rotary_tables(cfg, input_ids.shape[1], x.device)
     for i, layer in enumerate(m.layers):
-        x = layer_forward(cfg, i, layer, x, tables, 0, None, use_fused)
+        x = layer_forward(cfg, i, layer, x, tables, 0, None, use_fused, m.ep)
     return norm_w(x, m.norm, cfg.rms_norm_eps)
 
 
@@ -437,7 +450,7 @@ class CacheSession:
         if self.pos > 0 and S != 1:
             raise ValueError("chunked prefill is not supported; prefill a fresh session")
         for i, layer in enumerate(self.m.layers):
-            x = layer_forward(cfg, i, layer, x, self.tables, self.pos, self.caches[i], use_fused)
+            x = layer_forward(cfg, i, layer, x, self.tables, self.pos, self.caches[i], use_fused, self.m.ep)
         self.pos += S
         return norm_w(x, self.m.norm, cfg.rms_norm_eps)
 
