@@ -207,6 +207,39 @@ class FusedDataParallel:
                 dist.broadcast(buf, src=owner, group=self.group)
                 mast[b].copy_(buf)
 
+    def scatter_master(self, trainer):
+        """Inverse of ``gather_master``: refresh the owned fp32 shards from the (restored) full master tensors.
+        The bf16 working copies were already refreshed on every rank by ``load_named``."""
+        p = trainer.params
+        for name, st in self.adam.items():
+            full = p.master[name].reshape(-1)
+            n = st["master"].numel()
+            st["master"].copy_(full[self.rank * n:(self.rank + 1) * n])
+        for name, st in self.muon.items():
+            mast = p.master[name].reshape(-1, *st["shape"])
+            if st["own"]:
+                st["master"].copy_(mast[st["own"]])
+
+    def state_dict(self):
+        """This rank's optimizer shards (Adam moments of its slice, Muon momentum of its matrices)."""
+        out = {}
+        for name, st in self.adam.items():
+            out[f"dp.adam.{name}.m"], out[f"dp.adam.{name}.v"] = st["m"], st["v"]
+            out[f"dp.adam.{name}.step"] = torch.tensor([st["step"]], dtype=torch.int64)
+        for name, st in self.muon.items():
+            out[f"dp.muon.{name}.mom"] = st["mom"]
+        out["dp.step_no"] = torch.tensor([self.step_no], dtype=torch.int64)
+        return out
+
+    def load_state_dict(self, sd):
+        for name, st in self.adam.items():
+            st["m"].copy_(sd[f"dp.adam.{name}.m"].reshape(st["m"].shape))
+            st["v"].copy_(sd[f"dp.adam.{name}.v"].reshape(st["v"].shape))
+            st["step"] = int(sd[f"dp.adam.{name}.step"][0])
+        for name, st in self.muon.items():
+            if st["mom"].numel():
+                st["mom"].copy_(sd[f"dp.muon.{name}.mom"].reshape(st["mom"].shape))
+
     def close(self):
         if self.heap is not None:
             self.heap.close()

@@ -298,6 +298,8 @@ class NanoChatTrainer:
         for k, g in self.muon_groups.items():
             out[f"muon.{k}.momentum"] = g.momentum
         out["muon.smear_gate.momentum"] = self.smear_momentum
+        if self.dp is not None and self.world_size > 1:
+            out.update(self.dp.state_dict())
         return out
 
     def load_optimizer_state_dict(self, sd: Dict[str, torch.Tensor]):
@@ -308,3 +310,5 @@ class NanoChatTrainer:
         for k, g in self.muon_groups.items():
             g.momentum.copy_(sd[f"muon.{k}.momentum"].reshape(g.momentum.shape))
         self.smear_momentum.copy_(sd["muon.smear_gate.momentum"])
+        if self.dp is not None and self.world_size > 1:
+            self.dp.load_state_dict(sd)
