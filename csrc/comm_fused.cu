@@ -426,3 +426,48 @@ extern "C" TYR_EXPORT int tyr_slot_sum_bf16(const void* slots, int world, long l
                                                                           (const __nv_bfloat16*)add, (__nv_bfloat16*)out);
   return (int)cudaGetLastError();
 }
+
+// ---------------------------------------------------------------------------------------------
+// One-shot all-reduce for the small activations of tensor-parallel decode: every rank has published
+// its bf16 partial [n] in symmetric memory; each rank reads all of them over NVLink (plain peer
+// loads, 16 B per thread), sums in fp32 (plus an optional residual) and rounds once.
+// ---------------------------------------------------------------------------------------------
+namespace tyr {
+__global__ void __launch_bounds__(256)
+peer_sum_bf16_kernel(PeerPtrs src, int world, long long n, const __nv_bfloat16* __restrict__ add, __nv_bfloat16* __restrict__ out) {
+  const long long nvec = n >> 3;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    uint4 u[kMaxRanks];
+#pragma unroll
+    for (int r = 0; r < kMaxRanks; ++r)
+      if (r < world) u[r] = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(src.p[r]) + i * 8);
+#pragma unroll
+    for (int r = 0; r < kMaxRanks; ++r)
+      if (r < world) {
+        const float2 a = unpack_bf16x2(u[r].x), b = unpack_bf16x2(u[r].y), c = unpack_bf16x2(u[r].z), d = unpack_bf16x2(u[r].w);
+        acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y; acc[4] += c.x; acc[5] += c.y; acc[6] += d.x; acc[7] += d.y;
+      }
+    if (add) {
+      const uint4 v = *reinterpret_cast<const uint4*>(add + i * 8);
+      const float2 a = unpack_bf16x2(v.x), b = unpack_bf16x2(v.y), c = unpack_bf16x2(v.z), d = unpack_bf16x2(v.w);
+      acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y; acc[4] += c.x; acc[5] += c.y; acc[6] += d.x; acc[7] += d.y;
+    }
+    uint4 o;
+    o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
+    o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+    *reinterpret_cast<uint4*>(out + i * 8) = o;
+  }
+}
+}  // namespace tyr
+
+extern "C" TYR_EXPORT int tyr_peer_sum_bf16(void* const* src_ptrs, int world, long long n, const void* add, void* out,
+                                            void* stream) {
+  if (world < 1 || world > tyr::kMaxRanks || n <= 0 || (n & 7)) return -1;
+  long long blocks = (n / 8 + 255) / 256;
+  if (blocks > 148 * 4) blocks = 148 * 4;
+  tyr::peer_sum_bf16_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>(make_peers(src_ptrs, world), world, n,
+                                                                          (const __nv_bfloat16*)add, (__nv_bfloat16*)out);
+  return (int)cudaGetLastError();
+}

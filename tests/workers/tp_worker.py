@@ -10,6 +10,29 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspa
 from tyr_b200.parallel.tp import TensorParallel  # noqa: E402
 
 
+def qwen35_tp_matches_single_gpu(rank, world, dev, dtype, group):
+    """Sequence-parallel prefill and replicated decode of the sharded model against the whole model on one device."""
+    from tyr_b200.models import qwen35 as Q, qwen35_tp as QT
+    cfg = Q.Qwen35Config(vocab_size=128, hidden_size=64, intermediate_size=128, num_hidden_layers=4, num_attention_heads=8, num_key_value_heads=2,
+                         head_dim=16, half_rotary_dim=4, linear_key_head_dim=16, linear_value_head_dim=16, linear_num_key_heads=8, linear_num_value_heads=16)
+    full = Q.init(cfg, device=dev, dtype=dtype, seed=3)
+    B, S = 2, 64 * world
+    tp = TensorParallel(rank, world, dev, group=group, max_rows=B * S, max_cols=64, max_k=64)
+    m = QT.shard(full, rank, world, tp)
+    ids = torch.randint(0, 128, (B, S + 3), generator=torch.Generator().manual_seed(11)).to(dev)
+    ref_cache, cache = Q.HybridCache(full, B, S + 8), QT.TPCache(m, B, S + 8)
+    tol = 0.08 if dtype == torch.bfloat16 else 2e-3
+    ok = True
+    for t, chunk in enumerate([ids[:, :S], ids[:, S:S + 1], ids[:, S + 1:S + 2], ids[:, S + 2:S + 3]]):
+        ref, got = ref_cache.run(torch.nn.functional.embedding(chunk, full.embed_tokens)).float(), cache.run(chunk).float()
+        err = (ref - got).abs().max().item()
+        if got.shape != ref.shape or not err < tol * max(1.0, ref.abs().max().item()):
+            print(f"rank {rank} qwen35 tp chunk {t}: err {err} of {ref.abs().max().item()}", flush=True)
+            ok = False
+    tp.close()
+    return ok
+
+
 def main():
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     backend = os.environ.get("TYR_TEST_BACKEND", "nccl")
@@ -47,6 +70,7 @@ def main():
         if not ok:
             print(f"rank {rank} it {it}: rs err {err} ag err {err2}", flush=True)
             break
+    ok &= qwen35_tp_matches_single_gpu(rank, world, dev, dtype, tp.group)
     if dev.type == "cuda":
         torch.cuda.synchronize()
         from tyr_b200.ops._common import raise_on_device_error

@@ -97,6 +97,11 @@ class Qwen35Config:
                             num_key_value_heads=2, rope_theta=10000000.0, linear_num_value_heads=16, tie_word_embeddings=True)
 
     @staticmethod
+    def qwen35_27b():
+        return Qwen35Config(hidden_size=5120, intermediate_size=17408, num_hidden_layers=64, num_attention_heads=24, num_key_value_heads=4,
+                            linear_num_value_heads=48)
+
+    @staticmethod
     def qwen35_35b_a3b():
         return Qwen35Config(hidden_size=2048, intermediate_size=0, num_hidden_layers=40, num_key_value_heads=2, num_experts=256)
 
@@ -238,22 +243,29 @@ def rms(x, w, eps):
     return norm_w(x, w, eps, one_plus_w=True)
 
 
-def attention_forward(cfg: Qwen35Config, a: Attention, x, cos, sin, cache: Optional[KVCache], attn_mask=None):
-    B, S, _ = x.shape
+def attention_core(cfg: Qwen35Config, q_norm, k_norm, qg, k, v, cos, sin, cache: Optional[KVCache], attn_mask=None):
+    """Everything between the input and output projections of a gated full-attention layer.  ``qg``: [B, S, H*2D]
+    (per head q then gate), ``k``/``v``: [B, S, Hkv*D]; head counts come from ``cfg`` (a tensor-parallel rank passes
+    its local counts).  Returns [B, S, H*D]."""
+    B, S, _ = qg.shape
     H, Hkv, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
-    qg = lin(x, a.q_proj).reshape(B, S, H, 2 * D)
+    qg = qg.reshape(B, S, H, 2 * D)
     q, gate = qg[..., :D], qg[..., D:].reshape(B, S, H * D)
-    k = lin(x, a.k_proj).reshape(B, S, Hkv, D)
-    v = lin(x, a.v_proj).reshape(B, S, Hkv, D).transpose(1, 2)
-    q = head_norm(q.contiguous(), a.q_norm, cfg.rms_norm_eps, one_plus_w=True)
-    k = head_norm(k, a.k_norm, cfg.rms_norm_eps, one_plus_w=True)
+    k = k.reshape(B, S, Hkv, D)
+    v = v.reshape(B, S, Hkv, D).transpose(1, 2)
+    q = head_norm(q.contiguous(), q_norm, cfg.rms_norm_eps, one_plus_w=True)
+    k = head_norm(k, k_norm, cfg.rms_norm_eps, one_plus_w=True)
     q = apply_rotary_partial(q, cos, sin).transpose(1, 2)
     k = apply_rotary_partial(k, cos, sin).transpose(1, 2)
     if attn_mask is not None:
         o = attention(q, k, v, causal=True, key_padding_mask=attn_mask.bool())
     else:
         o = cached_attention(q, k, v, cache, None)
-    o = o.transpose(1, 2).reshape(B, S, H * D) * torch.sigmoid(gate)
+    return o.transpose(1, 2).reshape(B, S, H * D) * torch.sigmoid(gate)
+
+
+def attention_forward(cfg: Qwen35Config, a: Attention, x, cos, sin, cache: Optional[KVCache], attn_mask=None):
+    o = attention_core(cfg, a.q_norm, a.k_norm, lin(x, a.q_proj), lin(x, a.k_proj), lin(x, a.v_proj), cos, sin, cache, attn_mask)
     return lin(o, a.o_proj)
 
 
@@ -269,17 +281,15 @@ def rms_norm_gated(x, gate, w, eps):
     return (y * F.silu(gate.float())).to(x.dtype)
 
 
-def gated_delta_net_forward(cfg: Qwen35Config, m: GatedDeltaNet, x, state: Optional[LinearState] = None, attn_mask=None):
-    """Returns the mixed hidden states; ``state`` (if given) is advanced in place.  A one-token call on
-    a state that already holds context takes the recurrent kernel (Model.lean:642-779)."""
-    B, S, _ = x.shape
-    if attn_mask is not None:
-        x = x * attn_mask.to(x.dtype).unsqueeze(-1)
+def gated_delta_net_core(cfg: Qwen35Config, m, mixed, z, b, a, state: Optional[LinearState] = None):
+    """Causal depthwise conv + SiLU, gated delta rule and gated RMSNorm of one GatedDeltaNet layer, between its input
+    and output projections.  ``mixed``: [B, S, conv_dim] (q | k | v channels), ``z``: [B, S, Hv*dv], ``b``/``a``: [B, S, Hv];
+    head counts come from ``cfg``.  ``state`` (if given) is advanced in place; a one-token call on a state that already
+    holds context takes the recurrent kernel (Model.lean:642-779).  Returns [B, S, Hv*dv]."""
+    B, S, _ = mixed.shape
     K, cd = cfg.linear_conv_kernel_dim, cfg.linear_conv_dim
     Hk, Hv, dk, dv = cfg.linear_num_key_heads, cfg.linear_num_value_heads, cfg.linear_key_head_dim, cfg.linear_value_head_dim
-    mixed = lin(x, m.in_proj_qkv)                                   # [B, S, cd]
-    z = lin(x, m.in_proj_z).reshape(B, S, Hv, dv)
-    b, a = lin(x, m.in_proj_b), lin(x, m.in_proj_a)
+    z = z.reshape(B, S, Hv, dv)
     step = state is not None and state.conv is not None and S == 1
     w = m.conv1d_weight.reshape(cd, K).to(mixed.dtype)
     if step:
@@ -310,7 +320,14 @@ def gated_delta_net_forward(cfg: Qwen35Config, m: GatedDeltaNet, x, state: Optio
         if state is not None:
             state.rec = rec.contiguous()
     core = rms_norm_gated(core.reshape(B * S * Hv, dv), z.reshape(B * S * Hv, dv), m.norm_weight, cfg.rms_norm_eps)
-    return lin(core.reshape(B, S, Hv * dv), m.out_proj)
+    return core.reshape(B, S, Hv * dv)
+
+
+def gated_delta_net_forward(cfg: Qwen35Config, m: GatedDeltaNet, x, state: Optional[LinearState] = None, attn_mask=None):
+    if attn_mask is not None:
+        x = x * attn_mask.to(x.dtype).unsqueeze(-1)
+    core = gated_delta_net_core(cfg, m, lin(x, m.in_proj_qkv), lin(x, m.in_proj_z), lin(x, m.in_proj_b), lin(x, m.in_proj_a), state)
+    return lin(core, m.out_proj)
 
 
 def moe_forward(cfg: Qwen35Config, m: SparseMoeBlock, x2: torch.Tensor) -> torch.Tensor:

@@ -40,6 +40,8 @@ def _declare(lib):
     lib.tyr_gemm_bf16_tp.restype = ctypes.c_int
     lib.tyr_slot_sum_bf16.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
     lib.tyr_slot_sum_bf16.restype = ctypes.c_int
+    lib.tyr_peer_sum_bf16.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
+    lib.tyr_peer_sum_bf16.restype = ctypes.c_int
     lib._tp_declared = True
 
 
@@ -122,6 +124,36 @@ class TensorParallel:
         check(kernels().tyr_slot_sum_bf16(ptr(slots), self.world, rpr * N, ptr(add.contiguous() if add is not None else None),
                                           ptr(out), cur_stream(x.device)), "slot_sum_bf16")
         return out
+
+    # -- small-M linear -> one-shot all-reduce (decode) ---------------------------------------------------------
+    def linear_all_reduce(self, x: torch.Tensor, w: torch.Tensor, add: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """x: [M, K_local] replicated rows with this rank's K slice; w: [N, K_local].  Every rank returns the full
+        ``[M, N]`` sum (+ ``add``).  The partial product lands in this rank's symmetric buffer; after one flag barrier
+        each rank sums all peers' partials with plain peer loads (one launch, no ring)."""
+        M, N = x.shape[0], w.shape[0]
+        if self.world == 1:
+            y = torch.matmul(x, w.T)
+            return y if add is None else y + add
+        if not self.fused or (M * N) % 8 or x.dtype != torch.bfloat16 or M * N > self._slots[0].numel():
+            y = torch.matmul(x, w.T).float()
+            dist.all_reduce(y, group=self.group)
+            return (y if add is None else y + add.float()).to(x.dtype)
+        part = self._slots[self._parity]
+        self._parity ^= 1
+        torch.matmul(x, w.T, out=part[:M * N].view(M, N))
+        self._sync(0)
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+        check(kernels().tyr_peer_sum_bf16(self._peers(part), self.world, M * N, ptr(add.contiguous() if add is not None else None),
+                                          ptr(out), cur_stream(x.device)), "peer_sum_bf16")
+        return out
+
+    def all_gather_cols(self, y_local: torch.Tensor) -> torch.Tensor:
+        """[M, N_local] per rank -> [M, N_local * world] (rank-major columns); used for vocabulary-parallel logits."""
+        if self.world == 1:
+            return y_local
+        parts = [torch.empty_like(y_local) for _ in range(self.world)]
+        dist.all_gather(parts, y_local.contiguous(), group=self.group)
+        return torch.cat(parts, dim=-1)
 
     # -- all-gather -> GEMM ------------------------------------------------------------------------------------
     def allgather_gemm(self, x_shard: torch.Tensor, w: torch.Tensor, act: Optional[str] = None) -> torch.Tensor:
