@@ -186,3 +186,16 @@ def test_sharding_arithmetic_and_tensor():
     assert st.cache_is_stale
     with pytest.raises(ValueError):
         sd.ShardedTensor(full.shape, 0, 4, torch.zeros(5, 2))
+
+
+def test_native_registry_and_apple_stubs():
+    from tyr_b200 import distributed as D
+    from tyr_b200.audio import apple
+    init, rank, world = D.registry_state()
+    assert isinstance(init, bool) and rank >= 0 and world >= 0
+    assert apple.mps_is_available() is False
+    import pytest
+    with pytest.raises(IOError, match="macOS"):
+        apple.start_microphone()
+    with pytest.raises(IOError, match="macOS"):
+        apple.beep()

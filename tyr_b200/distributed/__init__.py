@@ -170,6 +170,13 @@ def is_initialized() -> bool:
     return _backend is not None
 
 
+def registry_state():
+    """(initialised, rank, world) as recorded by the native registry that survives Python-side resets; the
+    counterpart of the globals in cc/src/tyr_distributed.cpp:49-58."""
+    lib = _lib()
+    return bool(lib.tyr_pg_is_initialized()), int(lib.tyr_pg_rank()), int(lib.tyr_pg_world())
+
+
 def get_rank() -> int:
     return _require().rank()
 

@@ -161,10 +161,11 @@ class TensorParallel:
         rpr, K = x_shard.shape
         if self.world == 1:
             return gemm(x_shard, w, a_layout="K", b_layout="K", act=act) if x_shard.is_cuda else _cpu_lin(x_shard, w, act)
-        if not self.fused or rpr % 128 or K % 8 or x_shard.dtype != torch.bfloat16:
+        if not self.fused or rpr % 128 or K % 8 or w.shape[0] % 8 or x_shard.dtype != torch.bfloat16:
             full = torch.empty((rpr * self.world, K), dtype=x_shard.dtype, device=x_shard.device)
             dist.all_gather_into_tensor(full, x_shard.contiguous(), group=self.group)
-            return gemm(full, w, a_layout="K", b_layout="K", act=act) if full.is_cuda and full.dtype == torch.bfloat16 else _cpu_lin(full, w, act)
+            tc = full.is_cuda and full.dtype == torch.bfloat16 and K % 8 == 0 and w.shape[0] % 8 == 0
+            return gemm(full, w, a_layout="K", b_layout="K", act=act) if tc else _cpu_lin(full, w, act)
         if rpr * K > self._stage[0].numel():
             raise ValueError("allgather_gemm: shard exceeds the staging buffers this group was sized for")
         stage = self._stage[self._parity]
