@@ -390,7 +390,8 @@ struct RopeNormArgs {
   const float* cosT;           // [P, rot/2]
   const float* sinT;
   const int* pos;              // [rows] (nullable)
-  long long row_stride;        // elements between rows of x / y
+  long long row_stride;        // elements between rows of x
+  long long y_row_stride;      // elements between rows of y
   int rows, T, H, D, rot;
   float eps;
   int one_plus_w;
@@ -406,7 +407,7 @@ __global__ void __launch_bounds__(256) rope_norm_kernel(RopeNormArgs a) {
     const long long row = u / a.H;
     const int head = static_cast<int>(u % a.H);
     const __nv_bfloat16* x = a.x + row * a.row_stride + static_cast<long long>(head) * a.D;
-    __nv_bfloat16* y = a.y + row * a.row_stride + static_cast<long long>(head) * a.D;
+    __nv_bfloat16* y = a.y + row * a.y_row_stride + static_cast<long long>(head) * a.D;
     float rstd = 1.f;
     if (a.w) {
       float ss = 0.f;
@@ -486,11 +487,11 @@ extern "C" TYR_EXPORT int tyr_qkv_post_bwd(const void* qkv, const void* ve, cons
 
 extern "C" TYR_EXPORT int tyr_rope_norm(const void* x, void* y, const void* w, const float* cosT,
                                         const float* sinT, const int* pos, long long row_stride,
-                                        int rows, int T, int H, int D, int rot, float eps,
+                                        long long y_row_stride, int rows, int T, int H, int D, int rot, float eps,
                                         int one_plus_w, void* stream) {
   if (rot > D || (rot & 1)) return -1;
   RopeNormArgs a{(const __nv_bfloat16*)x, (__nv_bfloat16*)y, (const __nv_bfloat16*)w, cosT, sinT,
-                 pos, row_stride, rows, T, H, D, rot, eps, one_plus_w};
+                 pos, row_stride, y_row_stride, rows, T, H, D, rot, eps, one_plus_w};
   rope_norm_kernel<<<grid_for_units(1LL * rows * H, 8), 256, 0, (cudaStream_t)stream>>>(a);
   return (int)cudaGetLastError();
 }

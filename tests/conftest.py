@@ -18,3 +18,14 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+@pytest.fixture(autouse=True)
+def _seed_every_test():
+    """Random inputs are drawn from the global generator in many tests; a fixed seed keeps discrete choices
+    (router top-k near ties, greedy argmax) reproducible from run to run."""
+    import torch
+    torch.manual_seed(1234)
+    if torch.cuda.is_available():
+        torch.cuda.manual_seed_all(1234)
+    yield

@@ -311,3 +311,27 @@ def test_flash_attention_forward(B, Hq, Hkv, Tq, Tk, causal, window):
         m &= ki > qi - window
     s = s.masked_fill(~m, float("-inf"))
     assert torch.allclose(lse, torch.logsumexp(s, -1), rtol=1e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,D,cap,pos,ring,window,splits", [
+    (2, 6, 1, 128, 700, 513, False, None, None), (3, 8, 2, 256, 300, 299, False, 100, 4), (2, 4, 4, 64, 64, 200, True, None, 2),
+    (64, 48, 8, 128, 1100, 1024, False, None, None), (1, 8, 1, 128, 96, 5, True, None, 3), (2, 12, 2, 128, 50, 0, False, None, 1)])
+def test_decode_attention_matches_reference(B, Hq, Hkv, D, cap, pos, ring, window, splits):
+    from tyr_b200.ops.decode_attention import decode_attention
+    g = torch.Generator().manual_seed(pos + D)
+    mk = lambda *s: torch.randn(*s, generator=g).to(torch.bfloat16)
+    q, kn, vn, kc, vc = mk(B, Hq, D), mk(B, Hkv, D), mk(B, Hkv, D), mk(B, Hkv, cap, D), mk(B, Hkv, cap, D)
+    pt = torch.tensor([pos], dtype=torch.int32)
+    kc_ref, vc_ref = kc.clone(), vc.clone()
+    ref = decode_attention(q, kn, vn, kc_ref, vc_ref, pt, ring=ring, window=window)
+    kd, vd = kc.cuda(), vc.cuda()
+    wide = torch.randn(B, (Hq + 2 * Hkv) * D + 8, generator=g).to(torch.bfloat16).cuda()      # q / k / v as column slices of one projection
+    wide[:, :Hq * D], wide[:, Hq * D:(Hq + Hkv) * D], wide[:, (Hq + Hkv) * D:(Hq + 2 * Hkv) * D] = q.reshape(B, -1).cuda(), kn.reshape(B, -1).cuda(), vn.reshape(B, -1).cuda()
+    qv = wide[:, :Hq * D].view(B, Hq, D)
+    kv = wide[:, Hq * D:(Hq + Hkv) * D].view(B, Hkv, D)
+    vv = wide[:, (Hq + Hkv) * D:(Hq + 2 * Hkv) * D].view(B, Hkv, D)
+    for _ in range(2):                                   # a second launch checks that the ticket counters were reset
+        out = decode_attention(qv, kv, vv, kd, vd, pt.cuda(), ring=ring, window=window, splits=splits)
+    torch.cuda.synchronize()
+    assert torch.equal(kd.cpu(), kc_ref) and torch.equal(vd.cpu(), vc_ref)
+    assert (out.float().cpu() - ref.float()).abs().max() < 2e-2

@@ -81,6 +81,24 @@ def test_cached_matches_uncached_with_ring_wraparound():
         sess.prefill(ids[:, :3])
 
 
+def test_device_position_decode_step_matches_host_position_step():
+    """The graph body (position in a tensor, fused append in the attention op) against the sliced-cache step."""
+    m = L.init(tiny_cfg())
+    ids = torch.randint(3, 97, (2, 14))
+    a, b = L.CacheSession(m, 2, 20), L.CacheSession(m, 2, 20)
+    a.prefill(ids[:, :9]), b.prefill(ids[:, :9])
+    b.pos_t = torch.tensor([b.pos], dtype=torch.int32)
+    for t in range(9, 14):                                   # runs past the window, so the ring stores wrap
+        want = a.step(ids[:, t])
+        with torch.no_grad():
+            got = b._device_step(ids[:, t])
+        b._advance_host()
+        assert int(b.pos_t) == b.pos == a.pos
+        assert torch.allclose(got, want, atol=2e-4), t
+    for ca, cb in zip(a.caches, b.caches):
+        assert torch.allclose(ca.k, cb.k, atol=1e-5) and torch.allclose(ca.v, cb.v, atol=1e-5)
+
+
 def test_fused_and_eager_expert_paths_agree_and_dense_experts_run():
     cfg = tiny_cfg()
     m = L.init(cfg)

@@ -116,3 +116,34 @@ def test_gpu_qwen35_moe_bf16_cached_matches_full_forward():
         assert (c.prefill(ids[:, :130]).float() - full[:, 129]).abs().max().item() < 0.06 * scale
         for t in range(130, 140):
             assert (c.step(ids[:, t]).float() - full[:, t]).abs().max().item() < 0.06 * scale, t
+
+
+def test_device_position_decode_step_matches_host_position_step():
+    m = Q.init(tiny())
+    ids = torch.randint(0, 80, (2, 12))
+    a, b = Q.HybridCache(m, 2, 16), Q.HybridCache(m, 2, 16)
+    a.prefill(ids[:, :7]), b.prefill(ids[:, :7])
+    b.pos_t = torch.tensor([b.pos], dtype=torch.int32)
+    for t in range(7, 12):
+        want = a.step(ids[:, t])
+        with torch.no_grad():
+            got = b._device_step(ids[:, t])
+        b._advance_host()
+        assert int(b.pos_t) == b.pos == a.pos and torch.allclose(got, want, atol=2e-4), t
+
+
+@pytest.mark.gpu
+def test_gpu_qwen35_dense_graph_decode_matches_full_forward():
+    cfg = tiny(0, hidden_size=256, intermediate_size=512, head_dim=128, half_rotary_dim=32, linear_key_head_dim=128, linear_value_head_dim=128,
+               num_attention_heads=4, num_key_value_heads=1)
+    m = Q.init(cfg, device="cuda", dtype=torch.bfloat16)
+    ids = torch.randint(0, 80, (2, 140), device="cuda")
+    with torch.no_grad():
+        full = Q.forward(m, ids).float()
+        c = Q.HybridCache(m, 2, 160)
+        scale = full.abs().max().item()
+        assert c.device_step_supported()
+        assert (c.prefill(ids[:, :130]).float() - full[:, 129]).abs().max().item() < 0.06 * scale
+        for t in range(130, 140):
+            assert (c.step(ids[:, t]).float() - full[:, t]).abs().max().item() < 0.06 * scale, t
+        assert c._graph.replays == 10 and int(c.pos_t) == 140

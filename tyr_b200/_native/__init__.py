@@ -112,7 +112,7 @@ def _declare_kernels(lib):
     _sig(lib, "tyr_qkv_post_bwd",
          [P, P, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_float, P])
     _sig(lib, "tyr_rope_norm",
-         [P, P, P, P, P, P, c_ll, c_int, c_int, c_int, c_int, c_int, c_float, c_int, P])
+         [P, P, P, P, P, P, c_ll, c_ll, c_int, c_int, c_int, c_int, c_int, c_float, c_int, P])
     _sig(lib, "tyr_softcap_ce", [P, P, P, P, c_int, c_int, c_ll, c_float, c_float, P, c_ll, c_int, P])
     _sig(lib, "tyr_adamw_step",
          [P, P, P, P, P, c_ll, c_float, c_float, c_float, c_float, c_float, c_float, c_float,

@@ -17,6 +17,9 @@ import torch.nn.functional as F
 
 from ..io import safetensors as st
 from ..ops import moe as moe_ops
+from ..ops import decode_attention as da
+from ..ops.decode_attention import decode_attention
+from ..ops.rope import rope_norm
 from .common import (KVCache, apply_rotary_partial, cached_attention, cos_sin_tables, head_norm, lin, norm_w,
                      plain_inv_freq, swiglu_mlp, yarn_inv_freq)
 from .generation import SamplingStrategy, StreamCallback, generate_cached
@@ -385,6 +388,38 @@ def attention_forward(cfg: LagunaConfig, i: int, a: Attention, x: torch.Tensor, 
     return lin(gated, a.o_proj)
 
 
+def attention_decode(cfg: LagunaConfig, i: int, a: Attention, x: torch.Tensor, tables: RotaryTables, pos_t: torch.Tensor,
+                     cache: KVCache) -> torch.Tensor:
+    """One new token per row with the position on the device: fused q/k/v/g projection, RMSNorm+RoPE kernel on the q and k
+    slices, split-KV attention kernel that also appends to the store.  x: [B, 1, hidden]."""
+    B = x.shape[0]
+    H, Hkv, D = cfg.heads(i), cfg.num_key_value_heads, cfg.head_dim
+    y = lin(x, a.fused()).reshape(B, -1)
+    q, k, v = y[:, :H * D].view(B, H, D), y[:, H * D:(H + Hkv) * D].view(B, Hkv, D), y[:, (H + Hkv) * D:(H + 2 * Hkv) * D].view(B, Hkv, D)
+    g = y[:, (H + 2 * Hkv) * D:(H + 2 * Hkv) * D + H]
+    cos, sin = (tables.full_cos, tables.full_sin) if cfg.is_full(i) else (tables.sliding_cos, tables.sliding_sin)
+    positions = pos_t.expand(B)
+    rot = 2 * cos.shape[1]
+    q = rope_norm(q, cos, sin, weight=a.q_norm, positions=positions, rot=rot, eps=cfg.rms_norm_eps)
+    k = rope_norm(k, cos, sin, weight=a.k_norm, positions=positions, rot=rot, eps=cfg.rms_norm_eps)
+    o = decode_attention(q, k, v, cache.k, cache.v, pos_t, ring=cache.ring, window=None if cfg.is_full(i) else cfg.sliding_window)
+    gated = (o * F.softplus(g.float()).to(x.dtype).unsqueeze(-1)).reshape(B, 1, H * D)
+    return lin(gated, a.o_proj)
+
+
+def layer_decode(cfg: LagunaConfig, i: int, layer: Layer, x: torch.Tensor, tables: RotaryTables, pos_t: torch.Tensor,
+                 cache: KVCache, use_fused: bool = True, ep=None) -> torch.Tensor:
+    B, S, h = x.shape
+    h1 = norm_w(x, layer.input_layernorm, cfg.rms_norm_eps)
+    h2 = x + attention_decode(cfg, i, layer.attn, h1, tables, pos_t, cache)
+    h3 = norm_w(h2, layer.post_attention_layernorm, cfg.rms_norm_eps)
+    if isinstance(layer.ffn, DenseMLP):
+        f = swiglu_mlp(h3, layer.ffn.gate_proj, layer.ffn.up_proj, layer.ffn.down_proj)
+    else:
+        f = moe_forward(cfg, layer.ffn, h3.reshape(B * S, h), use_fused, ep).reshape(B, S, h)
+    return h2 + f
+
+
 def layer_forward(cfg: LagunaConfig, i: int, layer: Layer, x: torch.Tensor, tables: RotaryTables, position: int,
                   cache: Optional[KVCache], use_fused: bool = True, ep=None) -> torch.Tensor:
     B, S, h = x.shape
@@ -425,6 +460,7 @@ class CacheSession:
         if cfg.num_hidden_layers == 0:
             raise ValueError("Laguna cache session requires at least one layer")
         self.m, self.batch, self.max_len, self.pos = m, batch, max_len, 0
+        self.pos_t, self._graph, self._pos_t_host = None, None, -1
         self.tables = tables or precompute_rotary_tables(cfg, max_len, m.device)
         self.caches = [KVCache.allocate(batch, cfg.num_key_value_heads,
                                         max_len if cfg.is_full(i) else min(max_len, cfg.sliding_window),
@@ -438,6 +474,7 @@ class CacheSession:
         other = object.__new__(CacheSession)
         other.m, other.batch, other.max_len, other.pos, other.tables = self.m, self.batch, self.max_len, self.pos, self.tables
         other.caches = [c.clone() for c in self.caches]
+        other.pos_t, other._graph, other._pos_t_host = None, None, -1
         return other
 
     @torch.no_grad()
@@ -459,9 +496,48 @@ class CacheSession:
         h = self._run(F.embedding(input_ids, self.m.embed_tokens), use_fused)
         return lin(h[:, -1], self.m.lm_head)
 
+    # -- decode with the position on the device --------------------------------------------------------------------
+    def device_step_supported(self) -> bool:
+        cfg, m = self.m.cfg, self.m
+        if m.ep is not None or not m.embed_tokens.is_cuda or m.dtype != torch.bfloat16 or os.environ.get("TYR_DECODE_GRAPH", "1") == "0":
+            return False
+        return cfg.head_dim in (64, 128, 256) and all(cfg.heads(i) % cfg.num_key_value_heads == 0 and cfg.heads(i) // cfg.num_key_value_heads <= 8
+                                                       for i in range(cfg.num_hidden_layers))
+
+    def _device_step(self, tokens: torch.Tensor, use_fused: bool = True) -> torch.Tensor:
+        """One decode step whose only position input is ``self.pos_t``; advances ``pos_t`` (graph body)."""
+        cfg = self.m.cfg
+        x = F.embedding(tokens.reshape(self.batch, 1), self.m.embed_tokens)
+        for i, layer in enumerate(self.m.layers):
+            x = layer_decode(cfg, i, layer, x, self.tables, self.pos_t, self.caches[i], use_fused, self.m.ep)
+        logits = lin(norm_w(x, self.m.norm, cfg.rms_norm_eps)[:, -1], self.m.lm_head)
+        self.pos_t += 1
+        return logits
+
+    def _advance_host(self):
+        self.pos += 1
+        for c in self.caches:
+            c.length += 1
+
     def step(self, tokens: torch.Tensor, use_fused: bool = True) -> torch.Tensor:
-        h = self._run(F.embedding(tokens.reshape(self.batch, 1), self.m.embed_tokens), use_fused)
-        return lin(h[:, -1], self.m.lm_head)
+        if self.pos == 0 or not use_fused or not self.device_step_supported():
+            h = self._run(F.embedding(tokens.reshape(self.batch, 1), self.m.embed_tokens), use_fused)
+            return lin(h[:, -1], self.m.lm_head)
+        if self.pos + 1 > self.max_len:
+            raise ValueError("Laguna cache overflow")
+        if getattr(self, "pos_t", None) is None:
+            self.pos_t = torch.zeros(1, dtype=torch.int32, device=self.m.device)
+            self._graph = None
+        if self._graph is None:
+            from ..utils.graph import GraphedStep
+            self.pos_t.fill_(self.pos)
+            self._graph = GraphedStep(self._device_step, (tokens.reshape(self.batch).clone(),), advancing_state=(self.pos_t,))
+        elif self._pos_t_host != self.pos:
+            self.pos_t.fill_(self.pos)
+        out = self._graph(tokens.reshape(self.batch))
+        self._advance_host()
+        self._pos_t_host = self.pos
+        return out
 
 
 def generate(m: LagunaForCausalLM, input_ids: torch.Tensor, max_new_tokens: int = 256,

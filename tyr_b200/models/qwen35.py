@@ -19,6 +19,8 @@ from ..io import safetensors as st
 from ..ops import delta_rule as dr
 from ..ops import moe as moe_ops
 from ..ops.attention import attention
+from ..ops.decode_attention import decode_attention
+from ..ops.rope import rope_norm
 from .common import KVCache, apply_rotary_partial, cached_attention, cos_sin_tables, head_norm, lin, norm_w, plain_inv_freq, swiglu_mlp
 from .generation import SamplingStrategy, generate_cached
 from .laguna import name_candidates
@@ -264,6 +266,20 @@ def attention_core(cfg: Qwen35Config, q_norm, k_norm, qg, k, v, cos, sin, cache:
     return o.transpose(1, 2).reshape(B, S, H * D) * torch.sigmoid(gate)
 
 
+def attention_core_decode(cfg: Qwen35Config, q_norm, k_norm, qg, k, v, cos_table, sin_table, pos_t, cache: KVCache):
+    """``attention_core`` for one new token per row with the position in the device tensor ``pos_t``: RMSNorm+RoPE kernel,
+    then the split-KV kernel that also appends to the store.  ``cos_table`` / ``sin_table`` are the whole tables."""
+    B = qg.shape[0]
+    H, Hkv, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+    qg = qg.reshape(B, H, 2 * D)
+    positions = pos_t.expand(B)
+    rot = 2 * cos_table.shape[1]
+    q = rope_norm(qg[..., :D], cos_table, sin_table, weight=q_norm, positions=positions, rot=rot, eps=cfg.rms_norm_eps, one_plus_w=True)
+    kn = rope_norm(k.reshape(B, Hkv, D), cos_table, sin_table, weight=k_norm, positions=positions, rot=rot, eps=cfg.rms_norm_eps, one_plus_w=True)
+    o = decode_attention(q, kn, v.reshape(B, Hkv, D), cache.k, cache.v, pos_t)
+    return (o.reshape(B, 1, H * D) * torch.sigmoid(qg[..., D:].reshape(B, 1, H * D)))
+
+
 def attention_forward(cfg: Qwen35Config, a: Attention, x, cos, sin, cache: Optional[KVCache], attn_mask=None):
     o = attention_core(cfg, a.q_norm, a.k_norm, lin(x, a.q_proj), lin(x, a.k_proj), lin(x, a.v_proj), cos, sin, cache, attn_mask)
     return lin(o, a.o_proj)
@@ -298,7 +314,7 @@ def gated_delta_net_core(cfg: Qwen35Config, m, mixed, z, b, a, state: Optional[L
         if m.conv1d_bias is not None:
             y = y + m.conv1d_bias.float()
         conv_out = F.silu(y).to(mixed.dtype).unsqueeze(1)                                 # [B, 1, cd]
-        state.conv = window
+        state.conv.copy_(window)                                                          # in place: the step is graph-replayable
     else:
         xc = mixed.transpose(1, 2)
         y = F.conv1d(F.pad(xc, (K - 1, 0)), m.conv1d_weight.to(xc.dtype), None if m.conv1d_bias is None else m.conv1d_bias.to(xc.dtype), groups=cd)
@@ -402,7 +418,53 @@ class HybridCache:
         return lin(rms(x[:, -1], self.m.norm, cfg.rms_norm_eps), self.m.lm_head)
 
     def prefill(self, ids): return self.run(F.embedding(ids, self.m.embed_tokens))
-    def step(self, tok): return self.run(F.embedding(tok.reshape(-1, 1), self.m.embed_tokens))
+
+    # -- decode with the position on the device (CUDA-graph body) ---------------------------------------------------
+    def device_step_supported(self) -> bool:
+        cfg, m = self.m.cfg, self.m
+        return (m.embed_tokens.is_cuda and m.dtype == torch.bfloat16 and os.environ.get("TYR_DECODE_GRAPH", "1") != "0" and not cfg.is_moe
+                and cfg.head_dim in (64, 128, 256) and cfg.num_attention_heads // cfg.num_key_value_heads <= 8)
+
+    def _device_step(self, tok: torch.Tensor) -> torch.Tensor:
+        m, cfg = self.m, self.m.cfg
+        eps = cfg.rms_norm_eps
+        x = F.embedding(tok.reshape(-1, 1), m.embed_tokens)
+        for i, l in enumerate(m.layers):
+            h1 = rms(x, l.input_layernorm, eps)
+            if cfg.is_full(i):
+                a = l.mixer
+                o = attention_core_decode(cfg, a.q_norm, a.k_norm, lin(h1, a.q_proj), lin(h1, a.k_proj), lin(h1, a.v_proj), self.cos, self.sin,
+                                          self.pos_t, self.kv[i])
+                mixed = lin(o, a.o_proj)
+            else:
+                mixed = gated_delta_net_forward(cfg, l.mixer, h1, self.lin[i])
+            h2 = x + mixed
+            h3 = rms(h2, l.post_attention_layernorm, eps)
+            f = swiglu_mlp(h3, l.ffn.gate_proj, l.ffn.up_proj, l.ffn.down_proj) if isinstance(l.ffn, MLP) else \
+                moe_forward(cfg, l.ffn, h3.reshape(-1, cfg.hidden_size)).reshape(h3.shape)
+            x = h2 + f
+        self.pos_t += 1
+        return lin(rms(x[:, -1], m.norm, eps), m.lm_head)
+
+    def _advance_host(self):
+        self.pos += 1
+        for c in self.kv:
+            if c is not None:
+                c.length += 1
+
+    def step(self, tok):
+        if self.pos == 0 or not self.device_step_supported():
+            return self.run(F.embedding(tok.reshape(-1, 1), self.m.embed_tokens))
+        if self.pos + 1 > self.max_len:
+            raise ValueError("Qwen3.5 cache overflow")
+        if getattr(self, "_graph", None) is None:
+            from ..utils.graph import GraphedStep
+            self.pos_t = torch.full((1,), self.pos, dtype=torch.int32, device=self.m.device)
+            state = [self.pos_t] + [t for s in self.lin if s is not None for t in (s.conv, s.rec)]
+            self._graph = GraphedStep(self._device_step, (tok.reshape(-1).clone(),), advancing_state=state)
+        out = self._graph(tok.reshape(-1))
+        self._advance_host()
+        return out
 
 
 def generate(m: Qwen35ForCausalLM, input_ids, max_new_tokens=64, strategy=SamplingStrategy(), eos_token_ids=None, on_step=None):

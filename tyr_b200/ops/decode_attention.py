@@ -1,0 +1,88 @@
+"""One-token attention over a K/V store with the append fused in and the position read on the device
+(csrc/decode_attention.cu), so that a decode step has no host-dependent shapes and can be replayed from a CUDA graph.
+
+The CPU path states the same contract in plain PyTorch and is the oracle of the numerics tests."""
+from __future__ import annotations
+
+import ctypes
+import math
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from .._native import register_signatures
+from ._common import check, cur_stream, err_word, lib, ptr
+
+_workspaces: Dict[Tuple, torch.Tensor] = {}
+
+
+@register_signatures
+def _sigs(lib_):
+    P, I, L, F = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
+    fn = getattr(lib_, "tyr_decode_attention", None)
+    if fn is not None:
+        fn.argtypes = [P, P, P, P, P, P, P, P, L, L, L, I, I, I, I, I, I, I, I, I, F, P, P]
+        fn.restype = I
+        lib_.tyr_decode_attention_workspace_bytes.argtypes = [I, I, I, I, I]
+        lib_.tyr_decode_attention_workspace_bytes.restype = L
+
+
+def pick_splits(B: int, Hkv: int, keys: int) -> int:
+    """Enough CTAs to fill 148 SMs a few times over, but at least 256 keys per split."""
+    want = -(-592 // max(1, B * Hkv))
+    return max(1, min(want, 32, -(-keys // 256)))
+
+
+def supported(q: torch.Tensor, Hkv: int) -> bool:
+    B, Hq, D = q.shape
+    return q.is_cuda and q.dtype == torch.bfloat16 and D in (64, 128, 256) and Hq % Hkv == 0 and Hq // Hkv <= 8
+
+
+def _rows_ok(t: torch.Tensor, D: int) -> bool:
+    return t.stride(2) == 1 and t.stride(1) == D and t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0
+
+
+def decode_attention(q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                     pos: torch.Tensor, *, ring: bool = False, window: Optional[int] = None, scale: Optional[float] = None,
+                     append: bool = True, splits: Optional[int] = None) -> torch.Tensor:
+    """q: [B, Hq, D]; k_new, v_new: [B, Hkv, D] (the new position, RoPE applied); stores ``[B, Hkv, cap, D]``;
+    ``pos``: int32 tensor holding the absolute position of the new token.  Writes the new K/V at slot ``pos`` (``pos % cap``
+    for a ring store) when ``append`` and returns the attention of the new query over the retained keys (all of a ring
+    store; the last ``window`` positions of a plain one), ``[B, Hq, D]``."""
+    B, Hq, D = q.shape
+    Hkv, cap = k_cache.shape[1], k_cache.shape[2]
+    sc = scale if scale is not None else 1.0 / math.sqrt(D)
+    if not q.is_cuda:
+        p = int(pos.reshape(-1)[0])
+        if p < 0 or (not ring and p >= cap):
+            raise ValueError(f"decode position {p} outside a store of {cap} slots")
+        slot = p % cap if ring else p
+        if append:
+            k_cache[:, :, slot] = k_new
+            v_cache[:, :, slot] = v_new
+        if ring:
+            lo, hi = 0, min(p + 1, cap)
+        else:
+            lo, hi = (max(0, p + 1 - window) if window else 0), p + 1
+        k, v = k_cache[:, :, lo:hi].float().clone(), v_cache[:, :, lo:hi].float().clone()
+        k[:, :, slot - lo], v[:, :, slot - lo] = k_new.float(), v_new.float()
+        G = Hq // Hkv
+        s = torch.einsum("bhgd,bhkd->bhgk", q.float().reshape(B, Hkv, G, D), k) * sc
+        return torch.einsum("bhgk,bhkd->bhgd", torch.softmax(s, -1), v).reshape(B, Hq, D).to(q.dtype)
+    if not supported(q, Hkv):
+        raise ValueError(f"decode_attention: unsupported geometry Hq={Hq} Hkv={Hkv} D={D} dtype={q.dtype}")
+    if not k_cache.is_contiguous() or not v_cache.is_contiguous():
+        raise ValueError("decode_attention: K/V stores must be contiguous")
+    q, k_new, v_new = (t if _rows_ok(t, D) else t.contiguous() for t in (q, k_new, v_new))
+    keys = cap if ring or not window else min(cap, window)
+    if splits is None:
+        splits = pick_splits(B, Hkv, keys)
+    key = (q.device.index, B, Hq, Hkv, D, splits)
+    ws = _workspaces.get(key)
+    if ws is None:
+        ws = _workspaces[key] = torch.zeros(lib().tyr_decode_attention_workspace_bytes(B, Hq, Hkv, D, splits) // 4, dtype=torch.int32, device=q.device)
+    out = torch.empty((B, Hq, D), dtype=q.dtype, device=q.device)
+    check(lib().tyr_decode_attention(ptr(q), ptr(k_new), ptr(v_new), ptr(k_cache), ptr(v_cache), ptr(pos), ptr(out), ptr(ws),
+                                     q.stride(0), k_new.stride(0), v_new.stride(0), B, Hq, Hkv, D, cap, 1 if ring else 0, int(window or 0),
+                                     splits, 1 if append else 0, sc, ptr(err_word(q.device)), cur_stream(q.device)), "decode_attention")
+    return out

@@ -106,15 +106,13 @@ def rope_norm(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, *, weight=N
     rows, H, D = x.shape
     rot = D if rot is None else rot
     if x.is_cuda and x.dtype == torch.bfloat16:
-        xc = x if x.stride(2) == 1 and x.stride(1) == D else x.contiguous()
+        xc = x if x.stride(2) == 1 and x.stride(1) == D else x.contiguous()      # rows may be slices of a wider projection
         y = torch.empty((rows, H, D), dtype=x.dtype, device=x.device)
-        if xc.stride(0) != H * D:
-            xc = xc.contiguous()
         pos = positions.to(torch.int32).contiguous() if positions is not None else None
         w = weight.to(torch.bfloat16).contiguous() if weight is not None else None
         T = cos.shape[0]
         check(lib().tyr_rope_norm(ptr(xc), ptr(y), ptr(w), ptr(cos.float().contiguous()),
-                                  ptr(sin.float().contiguous()), ptr(pos), H * D, rows, T, H, D, rot,
+                                  ptr(sin.float().contiguous()), ptr(pos), xc.stride(0), H * D, rows, T, H, D, rot,
                                   eps, 1 if one_plus_w else 0, cur_stream(x.device)), "rope_norm")
         return y
     xf = x.float()

@@ -1,4 +1,4 @@
-"""Kernel micro-benchmarks: `python -m tyr_b200.utils.kernel_bench [gemm|attention|moe|moe-decode|all]`.
+"""Kernel micro-benchmarks: `python -m tyr_b200.utils.kernel_bench [gemm|attention|moe|moe-decode|decode-attn|all]`.
 
 Times the hand-written kernels with CUDA events (5 warm-up + 20 timed iterations, a 256 MB
 buffer written between iterations to flush the 126 MB L2) on the NanoChat d20 shapes and prints
@@ -115,6 +115,31 @@ def bench_moe(results, cases=None):
               f"{row['tokens_per_s']:10.0f} tok/s", flush=True)
 
 
+def bench_decode_attention(results):
+    """Split-KV decode attention with fused append against the library SDPA over the sliced store: Laguna-S-2.1
+    (48 q / 8 kv heads x 128) and Qwen3.5-27B (24 q / 4 kv heads x 256) geometries; bandwidth counts the K/V bytes read."""
+    import torch.nn.functional as F
+    from tyr_b200.ops.decode_attention import decode_attention
+    dev = torch.device("cuda")
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    for name, B, Hq, Hkv, D, pos in (("laguna b64", 64, 48, 8, 128, 4096), ("laguna b1", 1, 48, 8, 128, 4096), ("qwen27b b32", 32, 24, 4, 256, 2048),
+                                     ("laguna b64 long", 64, 48, 8, 128, 16384)):
+        cap = pos + 64
+        q, kn, vn = (torch.randn(B, n, D, device=dev).bfloat16() for n in (Hq, Hkv, Hkv))
+        kc, vc = torch.randn(B, Hkv, cap, D, device=dev).bfloat16(), torch.randn(B, Hkv, cap, D, device=dev).bfloat16()
+        pt = torch.tensor([pos], dtype=torch.int32, device=dev)
+        ours = _time(lambda: decode_attention(q, kn, vn, kc, vc, pt), flush=flush)
+
+        def lib_path():
+            kc[:, :, pos] = kn
+            vc[:, :, pos] = vn
+            return F.scaled_dot_product_attention(q.unsqueeze(2), kc[:, :, :pos + 1], vc[:, :, :pos + 1], enable_gqa=True)
+        libms = _time(lib_path, flush=flush)
+        gb = 2.0 * B * Hkv * (pos + 1) * D * 2 / 1e9
+        results.append({"kernel": "decode_attention", "case": name, "ms": ours, "gbs": gb / ours * 1e3, "sdpa_ms": libms, "sdpa_gbs": gb / libms * 1e3})
+        print(f"decode attention {name:16s}: ours {ours:7.3f} ms {gb / ours * 1e3:7.0f} GB/s | append+SDPA {libms:7.3f} ms {gb / libms * 1e3:7.0f} GB/s", flush=True)
+
+
 def main(argv):
     what = argv[1] if len(argv) > 1 else "all"
     results = []
@@ -124,6 +149,8 @@ def main(argv):
         bench_attention(results)
     if what in ("moe", "all"):
         bench_moe(results)
+    if what in ("decode-attn", "all"):
+        bench_decode_attention(results)
     if what == "moe-decode":
         bench_moe(results, ((1, "gemv"), (64, "gemv")))
     print(json.dumps(results))
