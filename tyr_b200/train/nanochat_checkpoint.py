@@ -28,7 +28,7 @@ def _cursor_file(rank: int) -> str:
 
 
 def save(root: str, trainer: NanoChatTrainer, data: Optional[DistributedDataGenerator], loss: float,
-         barrier=None) -> str:
+         barrier=None, extra: Optional[dict] = None) -> str:
     """All ranks call this.  Rank 0 creates the snapshot and writes the weights; every rank writes its optimizer
     sidecar and cursor; rank 0 publishes after a barrier."""
     rank, world = trainer.rank, trainer.world_size
@@ -46,6 +46,8 @@ def save(root: str, trainer: NanoChatTrainer, data: Optional[DistributedDataGene
         st.save_file(named, os.path.join(snap, MODEL_FILE))
         meta = {"step": trainer.step_index, "loss": float(loss), "world_size": world, "config": trainer.cfg.to_json(),
                 "hyperparameters": trainer.hp.to_json()}
+        if extra:
+            meta["extra"] = extra
         with open(os.path.join(snap, META_FILE), "w") as f:
             json.dump(meta, f, indent=2)
     sd = {k: v.detach().cpu().contiguous() for k, v in trainer.optimizer_state_dict().items()}
@@ -60,12 +62,19 @@ def save(root: str, trainer: NanoChatTrainer, data: Optional[DistributedDataGene
     return snap
 
 
-def load(root: str, trainer: NanoChatTrainer, data: Optional[DistributedDataGenerator] = None) -> dict:
-    """Restore weights, this rank's optimizer state and data cursor from the published snapshot; returns the meta."""
+def load(root: str, trainer: NanoChatTrainer, data: Optional[DistributedDataGenerator] = None, weights_only: bool = False) -> dict:
+    """Restore weights, this rank's optimizer state and data cursor from the published snapshot; returns the meta.
+    ``weights_only`` takes just the parameters (the next stage of a recipe starts its own optimizer and step count)."""
     snap = ckpt.resolve_snapshot(root)
     meta = json.load(open(os.path.join(snap, META_FILE)))
     if meta["config"] != trainer.cfg.to_json():
         raise ckpt.CheckpointError("checkpoint was written for a different model configuration")
+    if weights_only:
+        src = st.Source.open(os.path.join(snap, MODEL_FILE))
+        trainer.params.load_named({n: src.load(n) for n in src.names()})
+        if trainer.dp is not None and trainer.world_size > 1 and hasattr(trainer.dp, "scatter_master"):
+            trainer.dp.scatter_master(trainer)
+        return meta
     if meta["world_size"] != trainer.world_size:
         raise ckpt.CheckpointError(f"checkpoint was written by {meta['world_size']} ranks, this run has {trainer.world_size}")
     src = st.Source.open(os.path.join(snap, MODEL_FILE))
