@@ -2,12 +2,12 @@
 // whole decode step can be replayed from a CUDA graph.
 //
 // One new query row per (batch, head); K/V stores [B, Hkv, cap, D] bf16 (plain or ring).  Grid (splits, Hkv, B): a CTA
-// owns the G = Hq / Hkv query heads of one K/V head over one slice of the retained keys (split-KV, 4 warps).  Scores
-// are computed lane-per-key (the key row streams through registers 16 B at a time, the queries sit in shared memory
-// as fp32 pre-scaled by scale * log2 e), probabilities are then broadcast by shuffle and the value rows are consumed
-// lane-per-channel (coalesced).  The key at the new position is taken from k_new / v_new rather than from the store,
-// so the append (done by split 0) cannot race with readers.  Split partials {m, l, acc} go to a workspace; the last
-// CTA to arrive for a (batch, K/V head) combines them (atomic ticket, counter reset for the next launch).
+// owns the G = Hq / Hkv <= 8 query heads of one K/V head over one slice of the retained keys (split-KV, 4 warps, 16 keys
+// per warp step).  Both products run on mma.sync m16n8k16 with the operand fragments loaded straight from global
+// memory, 16 bytes per lane (see the kernel's comment for the channel / key permutations that make this possible).
+// The key at the new position is taken from k_new / v_new rather than from the store, so the append (done by split 0)
+// cannot race with readers.  Split partials {m, l, acc} go to a workspace; the last CTA to arrive for a
+// (batch, K/V head) combines them (atomic ticket, counter reset for the next launch).
 //
 // The reference takes the library SDPA over a sliced cache for this step (cc/include/tyr_attention.h:58-130,
 // Tyr/Inference/KVCache.lean:41-215).
@@ -39,32 +39,39 @@ struct DecodeAttnArgs {
   int* err;
 };
 
-template <int D>
-__device__ __forceinline__ void load_row_chunk(const __nv_bfloat16* row, int lane, float (&v)[D / 32]) {
-  if constexpr (D == 64) {
-    const float2 a = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(row + lane * 2));
-    v[0] = a.x; v[1] = a.y;
-  } else if constexpr (D == 128) {
-    const uint2 u = *reinterpret_cast<const uint2*>(row + lane * 4);
-    const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y);
-    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
-  } else {
-    const uint4 u = *reinterpret_cast<const uint4*>(row + lane * 8);
-    const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
-    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y; v[4] = c.x; v[5] = c.y; v[6] = d.x; v[7] = d.y;
-  }
+__device__ __forceinline__ void mma_bf16_16816(float& d0, float& d1, uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+  // Rows 8..15 of the 16-row tile are padding (at most 8 query heads share a K/V head): their A registers are zero and
+  // their accumulators are scratch.
+  float z0 = 0.f, z1 = 0.f;
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(d0), "+f"(d1), "+f"(z0), "+f"(z1)
+               : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
 }
 
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t r;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+  return r;
+}
+
+// Tensor-core formulation (mma.sync m16n8k16, bf16 in, fp32 accumulate); one warp consumes 16 keys per step.
+//   S = Q K^T : M = query heads of the group (<= 8 real rows), N = 8 keys, K = 16 channels.  The reduction over channels
+//   is order-free, so lane (g, t) feeds the B fragment straight from one 16-byte load of key row g (channels
+//   32j + 8t .. +8) and Q is loaded once with the same addressing.
+//   O += P V  : M = heads, N = 8 channels, K = 16 keys.  Lane (g, t) loads 16 bytes (8 channels) of the four key rows
+//   {2t, 2t+1, 2t+8, 2t+9}; byte permutes pair the rows per channel.  The channel order of the accumulators is permuted
+//   (undone when they are written out): accumulator (c, e, u) of lane (g, t) is channel 64c + 16t + 8u + e of head g.
 template <int D>
 __global__ void __launch_bounds__(kDecWarps * 32) decode_attention_kernel(DecodeAttnArgs a) {
-  constexpr int E = D / 32;                      // channels per lane in the value phase
-  __shared__ __align__(16) float sq[kDecGMax * D];
+  constexpr int NJ = D / 32;                     // 16-byte chunks per lane of a K (or Q) row
+  constexpr int NC = D / 64;                     // 64-channel blocks of a V row
   __shared__ float s_m[kDecWarps][kDecGMax], s_l[kDecWarps][kDecGMax];
   __shared__ float s_acc[kDecWarps][kDecGMax][D];
   __shared__ int s_ticket;
 
   const int split = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
   const int G = a.Hq / a.Hkv;
   const int pos = *a.pos;
   if (pos < 0 || (!a.ring && pos >= a.cap)) {    // position outside the store: report, leave the output untouched
@@ -82,7 +89,7 @@ __global__ void __launch_bounds__(kDecWarps * 32) decode_attention_kernel(Decode
     slot_new = pos;
   }
   int chunk = (n_keys + a.splits - 1) / a.splits;
-  chunk = (chunk + 31) & ~31;
+  chunk = (chunk + 63) & ~63;
   const int lo = start + split * chunk;
   int hi = lo + chunk;
   if (hi > start + n_keys) hi = start + n_keys;
@@ -99,86 +106,103 @@ __global__ void __launch_bounds__(kDecWarps * 32) decode_attention_kernel(Decode
       reinterpret_cast<uint4*>(a.v_cache + kv_base + static_cast<long long>(slot_new) * D)[i] = reinterpret_cast<const uint4*>(vn)[i];
     }
   }
-  for (int i = tid; i < G * D; i += kDecWarps * 32) {
-    const int g = i / D, d = i - g * D;
-    sq[i] = __bfloat162float(a.q[b * a.q_bs + static_cast<long long>(hkv * G + g) * D + d]) * a.scale_log2;
-  }
-  __syncthreads();
 
-  float m[kDecGMax], l[kDecGMax], acc[kDecGMax][E];
+  uint4 qf[NJ];                                  // A fragments of head g (zero rows when g >= G)
+  {
+    const __nv_bfloat16* qrow = a.q + b * a.q_bs + static_cast<long long>(hkv * G + (g < G ? g : 0)) * D;
 #pragma unroll
-  for (int g = 0; g < kDecGMax; ++g) {
-    m[g] = -INFINITY;
-    l[g] = 0.f;
+    for (int j = 0; j < NJ; ++j) qf[j] = g < G ? *reinterpret_cast<const uint4*>(qrow + 32 * j + 8 * t) : make_uint4(0u, 0u, 0u, 0u);
+  }
+  float m = -INFINITY, l = 0.f;                  // running max (same in the four lanes of a head) and per-lane partial sum
+  float o[NC][8][2];
 #pragma unroll
-    for (int e = 0; e < E; ++e) acc[g][e] = 0.f;
+  for (int c = 0; c < NC; ++c)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) o[c][e][0] = o[c][e][1] = 0.f;
+
+  for (int base = lo + warp * 16; base < hi; base += kDecWarps * 16) {
+    // ---- S for 16 keys: key tiles base + [0, 8) and base + [8, 16) ----
+    float s[2][2];
+#pragma unroll
+    for (int tile = 0; tile < 2; ++tile) {
+      int row = base + 8 * tile + g;
+      row = row < hi ? row : hi - 1;             // clamped rows are masked below
+      const __nv_bfloat16* krow = (row == slot_new) ? kn : kc + static_cast<long long>(row) * D;
+      uint4 kf[NJ];
+#pragma unroll
+      for (int j = 0; j < NJ; ++j) kf[j] = *reinterpret_cast<const uint4*>(krow + 32 * j + 8 * t);
+      float c0 = 0.f, c1 = 0.f;
+#pragma unroll
+      for (int j = 0; j < NJ; ++j) {
+        mma_bf16_16816(c0, c1, qf[j].x, qf[j].y, kf[j].x, kf[j].y);
+        mma_bf16_16816(c0, c1, qf[j].z, qf[j].w, kf[j].z, kf[j].w);
+      }
+      const int key0 = base + 8 * tile + 2 * t;
+      s[tile][0] = key0 < hi ? c0 * a.scale_log2 : -INFINITY;
+      s[tile][1] = key0 + 1 < hi ? c1 * a.scale_log2 : -INFINITY;
+    }
+    // ---- V rows of this lane's four keys (issued before the softmax arithmetic so the loads overlap it) ----
+    const __nv_bfloat16* vrow[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      int row = base + 2 * t + (i & 1) + 8 * (i >> 1);
+      row = row < hi ? row : hi - 1;
+      vrow[i] = (row == slot_new) ? vn : vc + static_cast<long long>(row) * D;
+    }
+    uint4 vf[NC][4];
+#pragma unroll
+    for (int c = 0; c < NC; ++c)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) vf[c][i] = *reinterpret_cast<const uint4*>(vrow[i] + 64 * c + 8 * g);
+
+    // ---- online softmax for head g (its 16 scores live in the four lanes t = 0..3) ----
+    float mx = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float m_new = fmaxf(m, mx);            // finite: key `base` is always in range
+    const float alpha = exp2f(m - m_new);
+    const float p00 = exp2f(s[0][0] - m_new), p01 = exp2f(s[0][1] - m_new);
+    const float p10 = exp2f(s[1][0] - m_new), p11 = exp2f(s[1][1] - m_new);
+    l = l * alpha + (p00 + p01) + (p10 + p11);
+    if (__any_sync(0xffffffffu, m_new > m)) {
+#pragma unroll
+      for (int c = 0; c < NC; ++c)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) { o[c][e][0] *= alpha; o[c][e][1] *= alpha; }
+    }
+    m = m_new;
+    const uint32_t pa0 = pack_bf16x2(p00, p01), pa2 = pack_bf16x2(p10, p11);
+
+    // ---- O += P V ----
+#pragma unroll
+    for (int c = 0; c < NC; ++c) {
+      const uint32_t v0[4] = {vf[c][0].x, vf[c][0].y, vf[c][0].z, vf[c][0].w};
+      const uint32_t v1[4] = {vf[c][1].x, vf[c][1].y, vf[c][1].z, vf[c][1].w};
+      const uint32_t v2[4] = {vf[c][2].x, vf[c][2].y, vf[c][2].z, vf[c][2].w};
+      const uint32_t v3[4] = {vf[c][3].x, vf[c][3].y, vf[c][3].z, vf[c][3].w};
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const uint32_t sel = (e & 1) ? 0x7632u : 0x5410u;
+        mma_bf16_16816(o[c][e][0], o[c][e][1], pa0, pa2, prmt(v0[e >> 1], v1[e >> 1], sel), prmt(v2[e >> 1], v3[e >> 1], sel));
+      }
+    }
   }
 
-  for (int base = lo + warp * 32; base < hi; base += kDecWarps * 32) {
-    const int slot = base + lane;
-    const bool valid = slot < hi;
-    float s[kDecGMax];
+  // publish this warp's state: head g, channels as laid out above
+  l += __shfl_xor_sync(0xffffffffu, l, 1);
+  l += __shfl_xor_sync(0xffffffffu, l, 2);
+  if (g < G) {
+    if (t == 0) { s_m[warp][g] = m; s_l[warp][g] = l; }
 #pragma unroll
-    for (int g = 0; g < kDecGMax; ++g) s[g] = 0.f;
-    if (valid) {
-      const __nv_bfloat16* krow = (slot == slot_new) ? kn : kc + static_cast<long long>(slot) * D;
-#pragma unroll 4
-      for (int c = 0; c < D / 8; ++c) {
-        const uint4 u = *reinterpret_cast<const uint4*>(krow + c * 8);
-        const float2 k0 = unpack_bf16x2(u.x), k1 = unpack_bf16x2(u.y), k2 = unpack_bf16x2(u.z), k3 = unpack_bf16x2(u.w);
+    for (int c = 0; c < NC; ++c)
 #pragma unroll
-        for (int g = 0; g < kDecGMax; ++g) {
-          if (g < G) {
-            const float4 qa = *reinterpret_cast<const float4*>(&sq[g * D + c * 8]);
-            const float4 qb = *reinterpret_cast<const float4*>(&sq[g * D + c * 8 + 4]);
-            s[g] += qa.x * k0.x + qa.y * k0.y + qa.z * k1.x + qa.w * k1.y + qb.x * k2.x + qb.y * k2.y + qb.z * k3.x + qb.w * k3.y;
-          }
-        }
+      for (int e = 0; e < 8; ++e) {
+        s_acc[warp][g][64 * c + 16 * t + e] = o[c][e][0];
+        s_acc[warp][g][64 * c + 16 * t + 8 + e] = o[c][e][1];
       }
-    }
-    float p[kDecGMax];
-#pragma unroll
-    for (int g = 0; g < kDecGMax; ++g) {
-      p[g] = 0.f;
-      if (g < G) {
-        const float sv = valid ? s[g] : -INFINITY;
-        const float mx = fmaxf(m[g], warp_max(sv));          // finite: the chunk holds at least one key
-        const float alpha = exp2f(m[g] - mx);
-        p[g] = valid ? exp2f(sv - mx) : 0.f;
-        l[g] = l[g] * alpha + p[g];                          // per-lane partial sum, reduced at the end
-        m[g] = mx;
-#pragma unroll
-        for (int e = 0; e < E; ++e) acc[g][e] *= alpha;
-      }
-    }
-    const int n_here = (hi - base) < 32 ? (hi - base) : 32;
-#pragma unroll 4
-    for (int j = 0; j < n_here; ++j) {
-      const int sj = base + j;
-      const __nv_bfloat16* vrow = (sj == slot_new) ? vn : vc + static_cast<long long>(sj) * D;
-      float v[E];
-      load_row_chunk<D>(vrow, lane, v);
-#pragma unroll
-      for (int g = 0; g < kDecGMax; ++g) {
-        if (g < G) {
-          const float pj = __shfl_sync(0xffffffffu, p[g], j);
-#pragma unroll
-          for (int e = 0; e < E; ++e) acc[g][e] += pj * v[e];
-        }
-      }
-    }
   }
 
   // ---- combine the four warps -------------------------------------------------------------------------------
-#pragma unroll
-  for (int g = 0; g < kDecGMax; ++g) {
-    if (g < G) {
-      const float lw = warp_sum(l[g]);
-      if (lane == 0) { s_m[warp][g] = m[g]; s_l[warp][g] = lw; }
-#pragma unroll
-      for (int e = 0; e < E; ++e) s_acc[warp][g][lane * E + e] = acc[g][e];
-    }
-  }
   __syncthreads();
   const int hq0 = hkv * G;
   for (int i = tid; i < G * D; i += kDecWarps * 32) {

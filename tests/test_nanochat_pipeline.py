@@ -102,6 +102,15 @@ def test_quick_pipeline_runs_every_stage_and_resumes(tmp_path):
     assert np_.eval_base_model(p, cfg) > 0.0
     acc = np_.eval_chat(p, cfg, "sft", max_problems=2)
     assert 0.0 <= acc <= 1.0
+    # the chat CLI answers from the SFT checkpoint with the trained tokenizer
+    from tyr_b200.cli import run_chat
+    import io, contextlib
+    buf = io.StringIO()
+    with contextlib.redirect_stdout(buf):
+        rc = run_chat.main(["--base-dir", base, "--stage", "sft", "--prompt", "2+2?", "--chat-markers", "--max-new-tokens", "6", "--temperature", "0",
+                            "--show-tokens", "--device", "cpu"])
+    assert rc == 0 and "[tokens]" in buf.getvalue()
+    assert run_chat.main(["--base-dir", base, "--stage", "rl", "--prompt", "x", "--device", "cpu"]) == 1        # no such checkpoint yet
     # one GRPO update from the SFT checkpoint
     cfg.env.rl = np_.RLEnv(num_samples=2, max_new_tokens=4, examples_per_step_global=1, max_prompts=2)
     reward = np_.reinforcement_learning(p, cfg)

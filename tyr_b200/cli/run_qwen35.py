@@ -73,8 +73,11 @@ def bench(make_cache, ids, new_tokens, dev, group=None):
     cache = make_cache(S + new_tokens + 1)
     logits, pre_ms = _time_phase(lambda: cache.prefill(ids), dev)
 
+    first = cache.step(logits.argmax(-1)).argmax(-1)          # untimed: the first step of a cache captures its CUDA graph
+    new_tokens = max(1, new_tokens - 1)
+
     def decode():
-        tok = logits.argmax(-1)
+        tok = first
         for _ in range(new_tokens):
             tok = cache.step(tok).argmax(-1)
         return tok
