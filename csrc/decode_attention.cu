@@ -2,7 +2,7 @@
 // whole decode step can be replayed from a CUDA graph.
 //
 // One new query row per (batch, head); K/V stores [B, Hkv, cap, D] bf16 (plain or ring).  Grid (splits, Hkv, B): a CTA
-// owns the G = Hq / Hkv <= 8 query heads of one K/V head over one slice of the retained keys (split-KV, 4 warps, 16 keys
+// owns the G = Hq / Hkv <= 16 query heads of one K/V head over one slice of the retained keys (split-KV, 4 warps, 16 keys
 // per warp step).  Both products run on mma.sync m16n8k16 with the operand fragments loaded straight from global
 // memory, 16 bytes per lane (see the kernel's comment for the channel / key permutations that make this possible).
 // The key at the new position is taken from k_new / v_new rather than from the store, so the append (done by split 0)
@@ -20,7 +20,6 @@
 namespace tyr {
 
 constexpr int kDecWarps = 4;
-constexpr int kDecGMax = 8;
 
 struct DecodeAttnArgs {
   const __nv_bfloat16* q;        // [B, Hq, D], batch stride q_bs, head stride D
@@ -39,13 +38,22 @@ struct DecodeAttnArgs {
   int* err;
 };
 
-__device__ __forceinline__ void mma_bf16_16816(float& d0, float& d1, uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
-  // Rows 8..15 of the 16-row tile are padding (at most 8 query heads share a K/V head): their A registers are zero and
-  // their accumulators are scratch.
-  float z0 = 0.f, z1 = 0.f;
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-               : "+f"(d0), "+f"(d1), "+f"(z0), "+f"(z1)
-               : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+// One m16n8k16 step.  `lo` accumulates the tile's rows 0..7 (query head g of the lane), `hi` rows 8..15 (head g + 8).
+// With at most 8 query heads per K/V head the upper rows are padding: their A registers are zero and their accumulators
+// scratch, which halves the live registers.
+template <bool WIDE>
+__device__ __forceinline__ void mma_bf16_16816(float (&lo)[2], float (&hi)[2], uint32_t a_lo0, uint32_t a_lo2, uint32_t a_hi0, uint32_t a_hi2,
+                                               uint32_t b0, uint32_t b1) {
+  if constexpr (WIDE) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(lo[0]), "+f"(lo[1]), "+f"(hi[0]), "+f"(hi[1])
+                 : "r"(a_lo0), "r"(a_hi0), "r"(a_lo2), "r"(a_hi2), "r"(b0), "r"(b1));
+  } else {
+    float z0 = 0.f, z1 = 0.f;
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(lo[0]), "+f"(lo[1]), "+f"(z0), "+f"(z1)
+                 : "r"(a_lo0), "r"(0u), "r"(a_lo2), "r"(0u), "r"(b0), "r"(b1));
+  }
 }
 
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
@@ -61,12 +69,14 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
 //   O += P V  : M = heads, N = 8 channels, K = 16 keys.  Lane (g, t) loads 16 bytes (8 channels) of the four key rows
 //   {2t, 2t+1, 2t+8, 2t+9}; byte permutes pair the rows per channel.  The channel order of the accumulators is permuted
 //   (undone when they are written out): accumulator (c, e, u) of lane (g, t) is channel 64c + 16t + 8u + e of head g.
-template <int D>
+template <int D, bool WIDE>
 __global__ void __launch_bounds__(kDecWarps * 32) decode_attention_kernel(DecodeAttnArgs a) {
   constexpr int NJ = D / 32;                     // 16-byte chunks per lane of a K (or Q) row
   constexpr int NC = D / 64;                     // 64-channel blocks of a V row
-  __shared__ float s_m[kDecWarps][kDecGMax], s_l[kDecWarps][kDecGMax];
-  __shared__ float s_acc[kDecWarps][kDecGMax][D];
+  constexpr int R = WIDE ? 2 : 1;                // query heads per lane: g, and g + 8 when more than 8 heads share a K/V head
+  constexpr int GM = 8 * R;
+  __shared__ float s_m[kDecWarps][GM], s_l[kDecWarps][GM];
+  __shared__ float s_acc[kDecWarps][GM][D];
   __shared__ int s_ticket;
 
   const int split = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
@@ -107,22 +117,29 @@ __global__ void __launch_bounds__(kDecWarps * 32) decode_attention_kernel(Decode
     }
   }
 
-  uint4 qf[NJ];                                  // A fragments of head g (zero rows when g >= G)
-  {
-    const __nv_bfloat16* qrow = a.q + b * a.q_bs + static_cast<long long>(hkv * G + (g < G ? g : 0)) * D;
+  uint4 qf[R][NJ];                               // A fragments of heads g (and g + 8); zero rows beyond G
 #pragma unroll
-    for (int j = 0; j < NJ; ++j) qf[j] = g < G ? *reinterpret_cast<const uint4*>(qrow + 32 * j + 8 * t) : make_uint4(0u, 0u, 0u, 0u);
+  for (int r = 0; r < R; ++r) {
+    const int head = g + 8 * r;
+    const __nv_bfloat16* qrow = a.q + b * a.q_bs + static_cast<long long>(hkv * G + (head < G ? head : 0)) * D;
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) qf[r][j] = head < G ? *reinterpret_cast<const uint4*>(qrow + 32 * j + 8 * t) : make_uint4(0u, 0u, 0u, 0u);
   }
-  float m = -INFINITY, l = 0.f;                  // running max (same in the four lanes of a head) and per-lane partial sum
-  float o[NC][8][2];
+  float m[R], l[R];                              // running max (same in the four lanes of a head) and per-lane partial sum
+  float o[R][NC][8][2];
 #pragma unroll
-  for (int c = 0; c < NC; ++c)
+  for (int r = 0; r < R; ++r) {
+    m[r] = -INFINITY;
+    l[r] = 0.f;
 #pragma unroll
-    for (int e = 0; e < 8; ++e) o[c][e][0] = o[c][e][1] = 0.f;
+    for (int c = 0; c < NC; ++c)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[r][c][e][0] = o[r][c][e][1] = 0.f;
+  }
 
   for (int base = lo + warp * 16; base < hi; base += kDecWarps * 16) {
     // ---- S for 16 keys: key tiles base + [0, 8) and base + [8, 16) ----
-    float s[2][2];
+    float s[R][2][2];
 #pragma unroll
     for (int tile = 0; tile < 2; ++tile) {
       int row = base + 8 * tile + g;
@@ -131,15 +148,19 @@ __global__ void __launch_bounds__(kDecWarps * 32) decode_attention_kernel(Decode
       uint4 kf[NJ];
 #pragma unroll
       for (int j = 0; j < NJ; ++j) kf[j] = *reinterpret_cast<const uint4*>(krow + 32 * j + 8 * t);
-      float c0 = 0.f, c1 = 0.f;
+      float c_lo[2] = {0.f, 0.f}, c_hi[2] = {0.f, 0.f};
 #pragma unroll
       for (int j = 0; j < NJ; ++j) {
-        mma_bf16_16816(c0, c1, qf[j].x, qf[j].y, kf[j].x, kf[j].y);
-        mma_bf16_16816(c0, c1, qf[j].z, qf[j].w, kf[j].z, kf[j].w);
+        mma_bf16_16816<WIDE>(c_lo, c_hi, qf[0][j].x, qf[0][j].y, qf[R - 1][j].x, qf[R - 1][j].y, kf[j].x, kf[j].y);
+        mma_bf16_16816<WIDE>(c_lo, c_hi, qf[0][j].z, qf[0][j].w, qf[R - 1][j].z, qf[R - 1][j].w, kf[j].z, kf[j].w);
       }
       const int key0 = base + 8 * tile + 2 * t;
-      s[tile][0] = key0 < hi ? c0 * a.scale_log2 : -INFINITY;
-      s[tile][1] = key0 + 1 < hi ? c1 * a.scale_log2 : -INFINITY;
+      s[0][tile][0] = key0 < hi ? c_lo[0] * a.scale_log2 : -INFINITY;
+      s[0][tile][1] = key0 + 1 < hi ? c_lo[1] * a.scale_log2 : -INFINITY;
+      if constexpr (WIDE) {
+        s[1][tile][0] = key0 < hi ? c_hi[0] * a.scale_log2 : -INFINITY;
+        s[1][tile][1] = key0 + 1 < hi ? c_hi[1] * a.scale_log2 : -INFINITY;
+      }
     }
     // ---- V rows of this lane's four keys (issued before the softmax arithmetic so the loads overlap it) ----
     const __nv_bfloat16* vrow[4];
@@ -155,23 +176,28 @@ __global__ void __launch_bounds__(kDecWarps * 32) decode_attention_kernel(Decode
 #pragma unroll
       for (int i = 0; i < 4; ++i) vf[c][i] = *reinterpret_cast<const uint4*>(vrow[i] + 64 * c + 8 * g);
 
-    // ---- online softmax for head g (its 16 scores live in the four lanes t = 0..3) ----
-    float mx = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-    const float m_new = fmaxf(m, mx);            // finite: key `base` is always in range
-    const float alpha = exp2f(m - m_new);
-    const float p00 = exp2f(s[0][0] - m_new), p01 = exp2f(s[0][1] - m_new);
-    const float p10 = exp2f(s[1][0] - m_new), p11 = exp2f(s[1][1] - m_new);
-    l = l * alpha + (p00 + p01) + (p10 + p11);
-    if (__any_sync(0xffffffffu, m_new > m)) {
+    // ---- online softmax per head (its 16 scores live in the four lanes t = 0..3) ----
+    uint32_t pa0[R], pa2[R];
 #pragma unroll
-      for (int c = 0; c < NC; ++c)
+    for (int r = 0; r < R; ++r) {
+      float mx = fmaxf(fmaxf(s[r][0][0], s[r][0][1]), fmaxf(s[r][1][0], s[r][1][1]));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      const float m_new = fmaxf(m[r], mx);       // finite: key `base` is always in range
+      const float alpha = exp2f(m[r] - m_new);
+      const float p00 = exp2f(s[r][0][0] - m_new), p01 = exp2f(s[r][0][1] - m_new);
+      const float p10 = exp2f(s[r][1][0] - m_new), p11 = exp2f(s[r][1][1] - m_new);
+      l[r] = l[r] * alpha + (p00 + p01) + (p10 + p11);
+      if (__any_sync(0xffffffffu, m_new > m[r])) {
 #pragma unroll
-        for (int e = 0; e < 8; ++e) { o[c][e][0] *= alpha; o[c][e][1] *= alpha; }
+        for (int c = 0; c < NC; ++c)
+#pragma unroll
+          for (int e = 0; e < 8; ++e) { o[r][c][e][0] *= alpha; o[r][c][e][1] *= alpha; }
+      }
+      m[r] = m_new;
+      pa0[r] = pack_bf16x2(p00, p01);
+      pa2[r] = pack_bf16x2(p10, p11);
     }
-    m = m_new;
-    const uint32_t pa0 = pack_bf16x2(p00, p01), pa2 = pack_bf16x2(p10, p11);
 
     // ---- O += P V ----
 #pragma unroll
@@ -183,23 +209,29 @@ __global__ void __launch_bounds__(kDecWarps * 32) decode_attention_kernel(Decode
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
         const uint32_t sel = (e & 1) ? 0x7632u : 0x5410u;
-        mma_bf16_16816(o[c][e][0], o[c][e][1], pa0, pa2, prmt(v0[e >> 1], v1[e >> 1], sel), prmt(v2[e >> 1], v3[e >> 1], sel));
+        mma_bf16_16816<WIDE>(o[0][c][e], o[R - 1][c][e], pa0[0], pa2[0], pa0[R - 1], pa2[R - 1],
+                             prmt(v0[e >> 1], v1[e >> 1], sel), prmt(v2[e >> 1], v3[e >> 1], sel));
       }
     }
   }
 
-  // publish this warp's state: head g, channels as laid out above
-  l += __shfl_xor_sync(0xffffffffu, l, 1);
-  l += __shfl_xor_sync(0xffffffffu, l, 2);
-  if (g < G) {
-    if (t == 0) { s_m[warp][g] = m; s_l[warp][g] = l; }
+  // publish this warp's state: heads g (and g + 8), channels as laid out above
 #pragma unroll
-    for (int c = 0; c < NC; ++c)
+  for (int r = 0; r < R; ++r) {
+    float lr = l[r];
+    lr += __shfl_xor_sync(0xffffffffu, lr, 1);
+    lr += __shfl_xor_sync(0xffffffffu, lr, 2);
+    const int head = g + 8 * r;
+    if (head < G) {
+      if (t == 0) { s_m[warp][head] = m[r]; s_l[warp][head] = lr; }
 #pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        s_acc[warp][g][64 * c + 16 * t + e] = o[c][e][0];
-        s_acc[warp][g][64 * c + 16 * t + 8 + e] = o[c][e][1];
-      }
+      for (int c = 0; c < NC; ++c)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          s_acc[warp][head][64 * c + 16 * t + e] = o[r][c][e][0];
+          s_acc[warp][head][64 * c + 16 * t + 8 + e] = o[r][c][e][1];
+        }
+    }
   }
 
   // ---- combine the four warps -------------------------------------------------------------------------------
@@ -270,8 +302,10 @@ extern "C" TYR_EXPORT int tyr_decode_attention(const void* q, const void* k_new,
                                                long long vn_bs, int B, int Hq, int Hkv, int D, int cap, int ring, int window,
                                                int splits, int append, float scale, void* err, void* stream) {
   using namespace tyr;
-  if (B <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv != 0 || Hq / Hkv > kDecGMax || cap <= 0 || splits < 1 || splits > 64) return -1;
+  if (B <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv != 0 || Hq / Hkv > 16 || cap <= 0 || splits < 1 || splits > 64) return -1;
   if (D != 64 && D != 128 && D != 256) return -2;
+  const bool wide = Hq / Hkv > 8;
+  if (wide && D == 256) return -4;                                  // 16 heads x 256 channels of accumulators do not fit a warp
   if ((q_bs | kn_bs | vn_bs) & 7) return -3;                       // 16-byte rows
   DecodeAttnArgs a;
   a.q = (const __nv_bfloat16*)q; a.k_new = (const __nv_bfloat16*)k_new; a.v_new = (const __nv_bfloat16*)v_new;
@@ -285,8 +319,11 @@ extern "C" TYR_EXPORT int tyr_decode_attention(const void* q, const void* k_new,
   a.scale_log2 = scale * 1.4426950408889634f;
   a.err = (int*)err;
   const dim3 grid(splits, Hkv, B);
-  if (D == 64) decode_attention_kernel<64><<<grid, kDecWarps * 32, 0, (cudaStream_t)stream>>>(a);
-  else if (D == 128) decode_attention_kernel<128><<<grid, kDecWarps * 32, 0, (cudaStream_t)stream>>>(a);
-  else decode_attention_kernel<256><<<grid, kDecWarps * 32, 0, (cudaStream_t)stream>>>(a);
+  const cudaStream_t st = (cudaStream_t)stream;
+  if (D == 64 && !wide) decode_attention_kernel<64, false><<<grid, kDecWarps * 32, 0, st>>>(a);
+  else if (D == 64) decode_attention_kernel<64, true><<<grid, kDecWarps * 32, 0, st>>>(a);
+  else if (D == 128 && !wide) decode_attention_kernel<128, false><<<grid, kDecWarps * 32, 0, st>>>(a);
+  else if (D == 128) decode_attention_kernel<128, true><<<grid, kDecWarps * 32, 0, st>>>(a);
+  else decode_attention_kernel<256, false><<<grid, kDecWarps * 32, 0, st>>>(a);
   return (int)cudaGetLastError();
 }

@@ -315,7 +315,8 @@ def test_flash_attention_forward(B, Hq, Hkv, Tq, Tk, causal, window):
 
 @pytest.mark.parametrize("B,Hq,Hkv,D,cap,pos,ring,window,splits", [
     (2, 6, 1, 128, 700, 513, False, None, None), (3, 8, 2, 256, 300, 299, False, 100, 4), (2, 4, 4, 64, 64, 200, True, None, 2),
-    (64, 48, 8, 128, 1100, 1024, False, None, None), (1, 8, 1, 128, 96, 5, True, None, 3), (2, 12, 2, 128, 50, 0, False, None, 1)])
+    (64, 48, 8, 128, 1100, 1024, False, None, None), (1, 8, 1, 128, 96, 5, True, None, 3), (2, 12, 2, 128, 50, 0, False, None, 1),
+    (4, 72, 8, 128, 512, 777, True, None, None), (2, 16, 1, 64, 200, 150, False, 64, 2), (1, 9, 1, 128, 40, 17, False, None, 1)])
 def test_decode_attention_matches_reference(B, Hq, Hkv, D, cap, pos, ring, window, splits):
     from tyr_b200.ops.decode_attention import decode_attention
     g = torch.Generator().manual_seed(pos + D)

@@ -501,8 +501,7 @@ class CacheSession:
         cfg, m = self.m.cfg, self.m
         if m.ep is not None or not m.embed_tokens.is_cuda or m.dtype != torch.bfloat16 or os.environ.get("TYR_DECODE_GRAPH", "1") == "0":
             return False
-        return cfg.head_dim in (64, 128, 256) and all(cfg.heads(i) % cfg.num_key_value_heads == 0 and cfg.heads(i) // cfg.num_key_value_heads <= 8
-                                                       for i in range(cfg.num_hidden_layers))
+        return all(da.geometry_supported(cfg.heads(i), cfg.num_key_value_heads, cfg.head_dim) for i in range(cfg.num_hidden_layers))
 
     def _device_step(self, tokens: torch.Tensor, use_fused: bool = True) -> torch.Tensor:
         """One decode step whose only position input is ``self.pos_t``; advances ``pos_t`` (graph body)."""

@@ -19,7 +19,7 @@ from ..io import safetensors as st
 from ..ops import delta_rule as dr
 from ..ops import moe as moe_ops
 from ..ops.attention import attention
-from ..ops.decode_attention import decode_attention
+from ..ops.decode_attention import decode_attention, geometry_supported
 from ..ops.rope import rope_norm
 from .common import KVCache, apply_rotary_partial, cached_attention, cos_sin_tables, head_norm, lin, norm_w, plain_inv_freq, swiglu_mlp
 from .generation import SamplingStrategy, generate_cached
@@ -423,7 +423,7 @@ class HybridCache:
     def device_step_supported(self) -> bool:
         cfg, m = self.m.cfg, self.m
         return (m.embed_tokens.is_cuda and m.dtype == torch.bfloat16 and os.environ.get("TYR_DECODE_GRAPH", "1") != "0" and not cfg.is_moe
-                and cfg.head_dim in (64, 128, 256) and cfg.num_attention_heads // cfg.num_key_value_heads <= 8)
+                and geometry_supported(cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim))
 
     def _device_step(self, tok: torch.Tensor) -> torch.Tensor:
         m, cfg = self.m, self.m.cfg

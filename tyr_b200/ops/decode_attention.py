@@ -33,9 +33,14 @@ def pick_splits(B: int, Hkv: int, keys: int) -> int:
     return max(1, min(want, 32, -(-keys // 256)))
 
 
+def geometry_supported(Hq: int, Hkv: int, D: int) -> bool:
+    """Up to 16 query heads per K/V head at head dim 64 / 128, up to 8 at head dim 256."""
+    return D in (64, 128, 256) and Hkv > 0 and Hq % Hkv == 0 and Hq // Hkv <= (8 if D == 256 else 16)
+
+
 def supported(q: torch.Tensor, Hkv: int) -> bool:
     B, Hq, D = q.shape
-    return q.is_cuda and q.dtype == torch.bfloat16 and D in (64, 128, 256) and Hq % Hkv == 0 and Hq // Hkv <= 8
+    return q.is_cuda and q.dtype == torch.bfloat16 and geometry_supported(Hq, Hkv, D)
 
 
 def _rows_ok(t: torch.Tensor, D: int) -> bool:
