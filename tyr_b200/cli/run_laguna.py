@@ -36,6 +36,9 @@ def parse(argv):
     p.add_argument("--bench", action="store_true")
     p.add_argument("--random-init", action="store_true")
     p.add_argument("--layers", type=int, default=None, help="with --random-init: number of decoder layers")
+    p.add_argument("--shape", default="laguna-s", choices=["laguna-s", "moe-24x2048"],
+                   help="with --random-init: Laguna-S-2.1 (hidden 3072, 256 experts top-10, FFN 1024) or the 24-layer benchmark shape "
+                        "(hidden 2048, 16 q / 4 kv heads x 128, 64 experts top-8 + shared, FFN 768)")
     p.add_argument("--prompt-tokens", type=int, default=4096, help="with --random-init: synthetic prompt length")
     p.add_argument("--temperature", type=float, default=0.0)
     p.add_argument("--top-k", type=int, default=None)
@@ -99,7 +102,12 @@ def main(argv=None) -> int:
     strategy = (SamplingStrategy.greedy() if a.temperature <= 0 else
                 SamplingStrategy.multinomial(a.temperature, a.top_k, a.top_p))
     if a.random_init:
-        cfg = L.LagunaConfig(num_hidden_layers=a.layers) if a.layers else L.LagunaConfig()
+        if a.shape == "moe-24x2048":
+            cfg = L.LagunaConfig(hidden_size=2048, intermediate_size=8192, num_hidden_layers=a.layers or 24, num_attention_heads=16,
+                                 num_attention_heads_sliding=16, num_key_value_heads=4, num_experts=64, num_experts_per_tok=8,
+                                 moe_intermediate_size=768, shared_expert_intermediate_size=768)
+        else:
+            cfg = L.LagunaConfig(num_hidden_layers=a.layers) if a.layers else L.LagunaConfig()
         if a.ep and world > 1:
             from ..parallel.ep import ExpertParallel
             ep = ExpertParallel(rank, world, dev, cfg.num_experts, cfg.hidden_size, a.batch_size * a.prompt_tokens,
