@@ -1,0 +1,102 @@
+// y[M, N] = x[M, K] @ W[N, K]^T (+ bias) for decode-sized M (1..16 rows): a weight-streaming kernel.  The product is bound
+// by reading W once from HBM, so a CTA owns 16 weight rows and its 8 warps split K; every lane streams 16 bytes of two
+// weight rows per step straight into mma.sync m16n8k16 A fragments (W rows are the M dimension of the tile, the tokens the
+// N dimension; the reduction over K is order-free, so a lane's 8 consecutive channels serve as the fragment's k-slots and
+// the activations are loaded with the same addressing).  Tokens beyond M load nothing.  Warp partials meet in shared memory.
+//
+// The reference sends these products to the library GEMM (cc/src/tyr.cpp:1003-1036).
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "common.cuh"
+
+namespace tyr {
+
+constexpr int kSkWarps = 8;
+
+struct SkinnyArgs {
+  const __nv_bfloat16* x;      // [M, K], row stride ldx
+  const __nv_bfloat16* w;      // [N, K], row stride ldw
+  const __nv_bfloat16* bias;   // [N] or null
+  __nv_bfloat16* y;            // [M, N], row stride ldy
+  long long ldx, ldw, ldy;
+  int M, N, K;
+};
+
+__device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int TILES>                               // token tiles of 8: M <= 8 * TILES
+__global__ void __launch_bounds__(kSkWarps * 32) skinny_gemm_kernel(SkinnyArgs a) {
+  __shared__ float part[kSkWarps][TILES][16][8];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int row0 = blockIdx.x * 16;
+  int r_lo = row0 + g, r_hi = row0 + g + 8;
+  r_lo = r_lo < a.N ? r_lo : a.N - 1;            // clamped rows are not written
+  r_hi = r_hi < a.N ? r_hi : a.N - 1;
+  const __nv_bfloat16* w_lo = a.w + r_lo * a.ldw + 8 * t;
+  const __nv_bfloat16* w_hi = a.w + r_hi * a.ldw + 8 * t;
+  const __nv_bfloat16* xr[TILES];
+  bool live[TILES];
+#pragma unroll
+  for (int i = 0; i < TILES; ++i) {
+    const int tok = 8 * i + g;
+    live[i] = tok < a.M;
+    xr[i] = a.x + (live[i] ? tok : 0) * a.ldx + 8 * t;
+  }
+  float acc[TILES][4];
+#pragma unroll
+  for (int i = 0; i < TILES; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+
+  const int chunks = a.K >> 5;                   // 32 channels per warp step
+#pragma unroll 4
+  for (int c = warp; c < chunks; c += kSkWarps) {
+    const uint4 lo = __ldcs(reinterpret_cast<const uint4*>(w_lo + 32 * c));    // streamed once: do not keep in cache
+    const uint4 hi = __ldcs(reinterpret_cast<const uint4*>(w_hi + 32 * c));
+#pragma unroll
+    for (int i = 0; i < TILES; ++i) {
+      const uint4 xv = live[i] ? __ldg(reinterpret_cast<const uint4*>(xr[i] + 32 * c)) : make_uint4(0u, 0u, 0u, 0u);
+      mma_16816(acc[i], lo.x, hi.x, lo.y, hi.y, xv.x, xv.y);
+      mma_16816(acc[i], lo.z, hi.z, lo.w, hi.w, xv.z, xv.w);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < TILES; ++i) {
+    part[warp][i][g][2 * t] = acc[i][0];
+    part[warp][i][g][2 * t + 1] = acc[i][1];
+    part[warp][i][g + 8][2 * t] = acc[i][2];
+    part[warp][i][g + 8][2 * t + 1] = acc[i][3];
+  }
+  __syncthreads();
+  for (int idx = tid; idx < TILES * 8 * 16; idx += kSkWarps * 32) {
+    const int tok = idx >> 4, r = idx & 15;        // consecutive threads write consecutive output columns
+    const int row = row0 + r;
+    if (tok < a.M && row < a.N) {
+      float s = 0.f;
+#pragma unroll
+      for (int wp = 0; wp < kSkWarps; ++wp) s += part[wp][tok >> 3][r][tok & 7];
+      if (a.bias) s += __bfloat162float(a.bias[row]);
+      a.y[tok * a.ldy + row] = __float2bfloat16(s);
+    }
+  }
+}
+
+}  // namespace tyr
+
+extern "C" TYR_EXPORT int tyr_skinny_gemm_bf16(const void* x, const void* w, const void* bias, void* y, long long ldx, long long ldw,
+                                               long long ldy, int M, int N, int K, void* stream) {
+  using namespace tyr;
+  if (M < 1 || M > 16 || N < 1 || K < 32 || (K & 31)) return -1;
+  if ((ldx | ldw) & 7) return -2;                                    // 16-byte loads
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) return -3;
+  SkinnyArgs a{(const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)bias, (__nv_bfloat16*)y, ldx, ldw, ldy, M, N, K};
+  const int grid = (N + 15) / 16;
+  if (M <= 8) skinny_gemm_kernel<1><<<grid, kSkWarps * 32, 0, (cudaStream_t)stream>>>(a);
+  else skinny_gemm_kernel<2><<<grid, kSkWarps * 32, 0, (cudaStream_t)stream>>>(a);
+  return (int)cudaGetLastError();
+}

@@ -336,3 +336,18 @@ def test_decode_attention_matches_reference(B, Hq, Hkv, D, cap, pos, ring, windo
     torch.cuda.synchronize()
     assert torch.equal(kd.cpu(), kc_ref) and torch.equal(vd.cpu(), vc_ref)
     assert (out.float().cpu() - ref.float()).abs().max() < 2e-2
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 3072, 9216), (3, 100, 64), (8, 4096, 1024), (9, 1000, 2048), (16, 272, 3072)])
+def test_skinny_gemm_matches_reference(M, N, K):
+    from tyr_b200.ops.skinny import skinny_linear, supported
+    g = torch.Generator().manual_seed(M * 7 + N)
+    wide = (torch.randn(N, K + 64, generator=g) * K ** -0.5).to(torch.bfloat16).cuda()
+    w = wide[:, 32:32 + K]                                   # strided rows, 16-byte aligned start
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
+    b = torch.randn(N, generator=g).to(torch.bfloat16).cuda()
+    assert supported(x, w)
+    for bias in (None, b):
+        y = skinny_linear(x, w, bias).float()
+        ref = x.float() @ w.float().T + (0 if bias is None else bias.float())
+        assert (y - ref).abs().max() < 2e-2 * max(1.0, ref.abs().max().item())

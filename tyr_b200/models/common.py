@@ -1,7 +1,7 @@
 """Shared inference building blocks for the decoder families (Laguna, Qwen3, Qwen3.5, Gemma4, ...).
 
-* ``lin``: bias-free/biased projection; prefill-sized bf16 batches go to the tcgen05 GEMM, decode-sized
-  batches to the library GEMV (weight streaming).
+* ``lin``: bias-free/biased projection; prefill-sized bf16 batches go to the tcgen05 GEMM, batches of up to 16 rows
+  to the weight-streaming kernel, the sizes in between to the library GEMM.
 * rotary tables (plain / YaRN / partial), HF rotate-half application.
 * ``KVCache``: static and ring (sliding-window) stores with in-place writes; the session owns the
   tensors (Tyr/Model/Laguna/Model.lean:351-406, Tyr/Model/Qwen/Model.lean KVCache).
@@ -16,6 +16,7 @@ import torch
 import torch.nn.functional as F
 
 from ..ops.gemm import gemm as _gemm
+from ..ops import skinny as _skinny
 from ..ops.attention import attention
 from ..ops.norm import rms_norm_weighted
 
@@ -34,6 +35,11 @@ def lin(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor] = None, act:
             if act == "relu":
                 y = F.relu(y)
         return y
+    if rows <= _skinny.MAX_ROWS and x.is_cuda and not torch.is_grad_enabled():
+        x2 = x.reshape(rows, -1)
+        if _skinny.supported(x2, w):
+            y = _skinny.skinny_linear(x2, w, b).reshape(*x.shape[:-1], w.shape[0])
+            return F.relu(y) if act == "relu" else (F.relu(y).square() if act == "relu2" else y)
     y = F.linear(x, w.to(x.dtype), None if b is None else b.to(x.dtype))
     if act == "relu":
         y = F.relu(y)

@@ -1,0 +1,41 @@
+"""Decode-sized linear layers (1..16 rows) on the weight-streaming kernel (csrc/skinny_gemm.cu)."""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .._native import register_signatures
+from ._common import check, cur_stream, lib, ptr
+
+MAX_ROWS = 16
+
+
+@register_signatures
+def _sigs(lib_):
+    P, I, L = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
+    fn = getattr(lib_, "tyr_skinny_gemm_bf16", None)
+    if fn is not None:
+        fn.argtypes = [P, P, P, P, L, L, L, I, I, I, P]
+        fn.restype = I
+
+
+def supported(x2: torch.Tensor, w: torch.Tensor) -> bool:
+    M, K = x2.shape
+    return (x2.is_cuda and x2.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and 1 <= M <= MAX_ROWS and K >= 32 and K % 32 == 0
+            and x2.stride(1) == 1 and w.stride(1) == 1 and x2.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and x2.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def skinny_linear(x2: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x2: [M <= 16, K] bf16, w: [N, K] bf16 (rows may be strided) -> [M, N] bf16 with fp32 accumulation."""
+    M, K = x2.shape
+    N = w.shape[0]
+    if not x2.is_cuda:
+        y = x2.float() @ w.float().T
+        return (y if bias is None else y + bias.float()).to(x2.dtype)
+    y = torch.empty((M, N), dtype=torch.bfloat16, device=x2.device)
+    b = None if bias is None else bias.to(torch.bfloat16).contiguous()
+    check(lib().tyr_skinny_gemm_bf16(ptr(x2), ptr(w), ptr(b), ptr(y), x2.stride(0), w.stride(0), N, M, N, K, cur_stream(x2.device)), "skinny_gemm_bf16")
+    return y

@@ -1,4 +1,4 @@
-"""Kernel micro-benchmarks: `python -m tyr_b200.utils.kernel_bench [gemm|attention|moe|moe-decode|decode-attn|all]`.
+"""Kernel micro-benchmarks: `python -m tyr_b200.utils.kernel_bench [gemm|attention|moe|moe-decode|decode-attn|skinny|all]`.
 
 Times the hand-written kernels with CUDA events (5 warm-up + 20 timed iterations, a 256 MB
 buffer written between iterations to flush the 126 MB L2) on the NanoChat d20 shapes and prints
@@ -140,6 +140,23 @@ def bench_decode_attention(results):
         print(f"decode attention {name:16s}: ours {ours:7.3f} ms {gb / ours * 1e3:7.0f} GB/s | append+SDPA {libms:7.3f} ms {gb / libms * 1e3:7.0f} GB/s", flush=True)
 
 
+def bench_skinny(results):
+    """Weight-streaming linear for decode-sized batches against the library GEMM: Laguna / Qwen3.5 projection shapes and
+    the Laguna lm_head; bandwidth counts the weight bytes."""
+    import torch.nn.functional as F
+    from tyr_b200.ops.skinny import skinny_linear
+    dev = torch.device("cuda")
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    for M, N, K in ((1, 11336, 3072), (1, 3072, 9216), (1, 100352, 3072), (8, 11336, 3072), (8, 34816, 5120), (16, 5120, 17408)):
+        w = (torch.randn(N, K, device=dev) * K ** -0.5).bfloat16()
+        x = torch.randn(M, K, device=dev).bfloat16()
+        ours = _time(lambda: skinny_linear(x, w), flush=flush)
+        libms = _time(lambda: F.linear(x, w), flush=flush)
+        gb = N * K * 2 / 1e9
+        results.append({"kernel": "skinny_gemm", "M": M, "N": N, "K": K, "ms": ours, "gbs": gb / ours * 1e3, "lib_ms": libms, "lib_gbs": gb / libms * 1e3})
+        print(f"skinny M={M:2d} N={N:6d} K={K:5d}: ours {ours * 1e3:7.1f} us {gb / ours * 1e3:6.0f} GB/s | library {libms * 1e3:7.1f} us {gb / libms * 1e3:6.0f} GB/s", flush=True)
+
+
 def main(argv):
     what = argv[1] if len(argv) > 1 else "all"
     results = []
@@ -151,6 +168,8 @@ def main(argv):
         bench_moe(results)
     if what in ("decode-attn", "all"):
         bench_decode_attention(results)
+    if what in ("skinny", "all"):
+        bench_skinny(results)
     if what == "moe-decode":
         bench_moe(results, ((1, "gemv"), (64, "gemv")))
     print(json.dumps(results))
