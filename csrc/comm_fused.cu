@@ -60,13 +60,13 @@ __global__ void signal_kernel(PeerPtrs flags, int world, int my_rank, int slot_b
 
 // Waits until every slot [slot_base + r] of the LOCAL flag array is >= value.
 __global__ void wait_all_kernel(const unsigned long long* local_flags, int world, int slot_base,
-                                unsigned long long value, int* err) {
+                                unsigned long long value, int* err, long long budget_cycles) {
   const int r = threadIdx.x;
   if (r < world) {
     const unsigned long long* f = local_flags + slot_base + r;
     long long start = clock64();
     while (ld_acquire_sys(f) < value) {
-      if (clock64() - start > kWaitBudgetCycles * 4) {
+      if (clock64() - start > budget_cycles) {
         report_error(err, ERR_PEER_FLAG_TIMEOUT, slot_base + r);
         break;
       }
@@ -310,7 +310,17 @@ extern "C" TYR_EXPORT int tyr_wait_all(const void* local_flags, int world, int s
                                        unsigned long long value, int* err, void* stream) {
   if (world < 1 || world > kMaxRanks) return -1;
   wait_all_kernel<<<1, 32, 0, (cudaStream_t)stream>>>((const unsigned long long*)local_flags, world,
-                                                      slot_base, value, err);
+                                                      slot_base, value, err, kWaitBudgetCycles * 4);
+  return (int)cudaGetLastError();
+}
+
+// Same wait with a caller-chosen cycle budget (health checks and tests use a short one): on expiry the
+// kernel records ERR_PEER_FLAG_TIMEOUT with the slot in the error record and returns; the context stays usable.
+extern "C" TYR_EXPORT int tyr_wait_all_budget(const void* local_flags, int world, int slot_base, unsigned long long value,
+                                              int* err, long long budget_cycles, void* stream) {
+  if (world < 1 || world > kMaxRanks || budget_cycles <= 0) return -1;
+  wait_all_kernel<<<1, 32, 0, (cudaStream_t)stream>>>((const unsigned long long*)local_flags, world,
+                                                      slot_base, value, err, budget_cycles);
   return (int)cudaGetLastError();
 }
 

@@ -351,3 +351,23 @@ def test_skinny_gemm_matches_reference(M, N, K):
         y = skinny_linear(x, w, bias).float()
         ref = x.float() @ w.float().T + (0 if bias is None else bias.float())
         assert (y - ref).abs().max() < 2e-2 * max(1.0, ref.abs().max().item())
+
+
+def test_flag_wait_runs_out_and_reports_without_losing_the_context():
+    """A wait on a flag that nothing sets ends after its cycle budget (about 0.1 s here), records the timeout in the
+    device error record, and leaves the device usable."""
+    from tyr_b200.distributed.symm import wait_flags_bounded
+    from tyr_b200.ops._common import err_word, ptr, raise_on_device_error
+    dev = torch.device("cuda", 0)
+    flags = torch.zeros(8, dtype=torch.int64, device=dev)
+    flags[0] = 5                                            # rank 0 signalled, rank 1 never does
+    err = err_word(dev)
+    err.zero_()
+    wait_flags_bounded(flags, 2, 0, 5, ptr(err), 200_000_000)
+    with pytest.raises(RuntimeError, match="code=2 .*detail=1"):
+        raise_on_device_error(dev)
+    assert err.tolist()[0] == 0                             # the record was cleared by the read
+    flags[1] = 5
+    wait_flags_bounded(flags, 2, 0, 5, ptr(err), 200_000_000)
+    raise_on_device_error(dev)                              # satisfied wait: no error
+    assert float((torch.ones(4, device=dev) * 2).sum()) == 8.0

@@ -28,7 +28,7 @@ def _sigs(lib):
     table = {
         "tyr_symm_alloc": [PP, L], "tyr_symm_free": [P], "tyr_ipc_export": [P, P],
         "tyr_ipc_open": [P, PP], "tyr_ipc_close": [P],
-        "tyr_signal": [PP, I, I, I, U, P], "tyr_wait_all": [P, I, I, U, P, P],
+        "tyr_signal": [PP, I, I, I, U, P], "tyr_wait_all": [P, I, I, U, P, P], "tyr_wait_all_budget": [P, I, I, U, P, L, P],
         "tyr_dp_adam_shard": [PP, PP, I, L, L, P, P, P, L] + [F] * 8 + [P, I, U, P, I, P],
         "tyr_dp_muon_gather": [PP, I, P, P, P, P, L, I, F, F, P, I, U, P, I, P],
         "tyr_dp_muon_apply_push": [PP, I, P, P, P, L, I, F, F, I, P],
@@ -152,3 +152,10 @@ class FlagBarrier:
 
     def local_ptr(self):
         return ctypes.c_void_p(self.flags.data_ptr())
+
+
+def wait_flags_bounded(flags: torch.Tensor, world: int, slot_base: int, value: int, err_ptr, budget_cycles: int, stream=None) -> None:
+    """Enqueue the flag wait on a plain local int64 tensor with an explicit cycle budget.  When the budget runs out the
+    kernel writes {2 = peer flag timeout, slot} into the device error record and returns."""
+    check(kernels().tyr_wait_all_budget(ctypes.c_void_p(flags.data_ptr()), world, slot_base, value, err_ptr, budget_cycles,
+                                        stream or cur_stream(flags.device)), "wait_all_budget")
