@@ -293,6 +293,30 @@ extern "C" TYR_EXPORT int tyr_ipc_open(const void* handle64, void** out) {
 }
 extern "C" TYR_EXPORT int tyr_ipc_close(void* p) { return (int)cudaIpcCloseMemHandle(p); }
 
+// Signal + wait in one launch with the sequence number in device memory (`*seq` holds the number of barriers completed on
+// this slot), so the launch has no host-dependent argument and can be replayed from a CUDA graph: every rank publishes
+// seq + 1 to all peers, waits (bounded) until all peers published it, then advances the counter.
+__global__ void barrier_dev_kernel(PeerPtrs flags, const unsigned long long* local_flags, int world, int my_rank,
+                                   int slot_base, unsigned long long* seq, int* err) {
+  const int r = threadIdx.x;
+  const unsigned long long value = *seq + 1;
+  if (r < world) {
+    __threadfence_system();
+    st_release_sys(reinterpret_cast<unsigned long long*>(flags.p[r]) + slot_base + my_rank, value);
+    const unsigned long long* f = local_flags + slot_base + r;
+    const long long start = clock64();
+    while (ld_acquire_sys(f) < value) {
+      if (clock64() - start > kWaitBudgetCycles * 4) {
+        report_error(err, ERR_PEER_FLAG_TIMEOUT, slot_base + r);
+        break;
+      }
+      __nanosleep(100);
+    }
+  }
+  __syncwarp();
+  if (r == 0) *seq = value;
+}
+
 static PeerPtrs make_peers(void* const* ptrs, int world) {
   PeerPtrs pp;
   for (int i = 0; i < kMaxRanks; ++i) pp.p[i] = i < world ? ptrs[i] : nullptr;
@@ -304,6 +328,13 @@ extern "C" TYR_EXPORT int tyr_signal(void* const* flag_ptrs, int world, int my_r
   if (world < 1 || world > kMaxRanks) return -1;
   signal_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(make_peers(flag_ptrs, world), world, my_rank,
                                                     slot_base, value);
+  return (int)cudaGetLastError();
+}
+extern "C" TYR_EXPORT int tyr_barrier_dev(void* const* flag_ptrs, const void* local_flags, int world, int my_rank, int slot_base,
+                                          void* seq, int* err, void* stream) {
+  if (world < 1 || world > kMaxRanks) return -1;
+  barrier_dev_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(make_peers(flag_ptrs, world), (const unsigned long long*)local_flags,
+                                                         world, my_rank, slot_base, (unsigned long long*)seq, err);
   return (int)cudaGetLastError();
 }
 extern "C" TYR_EXPORT int tyr_wait_all(const void* local_flags, int world, int slot_base,

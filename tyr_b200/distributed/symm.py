@@ -28,7 +28,7 @@ def _sigs(lib):
     table = {
         "tyr_symm_alloc": [PP, L], "tyr_symm_free": [P], "tyr_ipc_export": [P, P],
         "tyr_ipc_open": [P, PP], "tyr_ipc_close": [P],
-        "tyr_signal": [PP, I, I, I, U, P], "tyr_wait_all": [P, I, I, U, P, P], "tyr_wait_all_budget": [P, I, I, U, P, L, P],
+        "tyr_signal": [PP, I, I, I, U, P], "tyr_wait_all": [P, I, I, U, P, P], "tyr_wait_all_budget": [P, I, I, U, P, L, P], "tyr_barrier_dev": [PP, P, I, I, I, P, P, P],
         "tyr_dp_adam_shard": [PP, PP, I, L, L, P, P, P, L] + [F] * 8 + [P, I, U, P, I, P],
         "tyr_dp_muon_gather": [PP, I, P, P, P, P, L, I, F, F, P, I, U, P, I, P],
         "tyr_dp_muon_apply_push": [PP, I, P, P, P, L, I, F, F, I, P],
@@ -152,6 +152,16 @@ class FlagBarrier:
 
     def local_ptr(self):
         return ctypes.c_void_p(self.flags.data_ptr())
+
+    def barrier_device_seq(self, slot: int, err_ptr, stream=None):
+        """Signal and wait in one launch, the sequence number kept in device memory (one counter per slot): nothing in
+        the launch depends on the host, so it can sit inside a CUDA graph.  A slot must not mix this with
+        ``signal`` / ``wait``."""
+        h = self.heap
+        if getattr(self, "_seq_dev", None) is None:
+            self._seq_dev = torch.zeros(self.n_slots, dtype=torch.int64, device=h.device)
+        check(kernels().tyr_barrier_dev(self._table, ctypes.c_void_p(self.flags.data_ptr()), h.world_size, h.rank, slot * h.world_size,
+                                        ctypes.c_void_p(self._seq_dev.data_ptr() + 8 * slot), err_ptr, stream or cur_stream(h.device)), "barrier_dev")
 
 
 def wait_flags_bounded(flags: torch.Tensor, world: int, slot_base: int, value: int, err_ptr, budget_cycles: int, stream=None) -> None:

@@ -16,6 +16,7 @@ reference has no tensor parallelism.
 from __future__ import annotations
 
 import dataclasses
+import os
 from dataclasses import dataclass
 from typing import List, Optional
 
@@ -25,6 +26,7 @@ import torch.nn.functional as F
 
 from ..parallel.tp import TensorParallel
 from . import qwen35 as Q
+from ..ops.decode_attention import geometry_supported
 from .common import KVCache, lin
 from .generation import SamplingStrategy, generate_cached
 
@@ -222,7 +224,52 @@ class TPCache:
         return tp.all_gather_cols(lin(Q.rms(x_last, m.norm, eps), m.lm_head))
 
     def prefill(self, ids): return self.run(ids)
-    def step(self, tok): return self.run(tok.reshape(-1, 1))
+
+    # -- replicated decode with the position on the device (CUDA-graph body) ---------------------------------------------
+    def device_step_supported(self) -> bool:
+        m, loc = self.m, self.m.local
+        return (m.tp.fused and m.dtype == torch.bfloat16 and os.environ.get("TYR_DECODE_GRAPH", "1") != "0"
+                and geometry_supported(loc.num_attention_heads, loc.num_key_value_heads, loc.head_dim))
+
+    def _device_step(self, tok: torch.Tensor) -> torch.Tensor:
+        """Final normed hidden state [B, hidden] of the new token on every rank; the vocabulary-parallel head and its
+        gather stay outside the graph."""
+        m, cfg, loc, tp = self.m, self.m.cfg, self.m.local, self.m.tp
+        eps, B = cfg.rms_norm_eps, tok.numel()
+        x = F.embedding(tok.reshape(-1), m.embed_tokens)
+        for i, l in enumerate(m.layers):
+            proj = lin(Q.rms(x, l.input_layernorm, eps), l.mixer.in_proj).reshape(B, 1, -1)
+            if isinstance(l.mixer, TPAttention):
+                nq, nkv = loc.num_attention_heads * 2 * loc.head_dim, loc.num_key_value_heads * loc.head_dim
+                core = Q.attention_core_decode(loc, l.mixer.q_norm, l.mixer.k_norm, proj[..., :nq], proj[..., nq:nq + nkv], proj[..., nq + nkv:],
+                                               self.cos, self.sin, self.pos_t, self.kv[i])
+                w_out = l.mixer.o_proj
+            else:
+                cd, vd, Hv = loc.linear_conv_dim, loc.linear_value_dim, loc.linear_num_value_heads
+                core = Q.gated_delta_net_core(loc, l.mixer, proj[..., :cd], proj[..., cd:cd + vd], proj[..., cd + vd:cd + vd + Hv], proj[..., cd + vd + Hv:], self.lin[i])
+                w_out = l.mixer.out_proj
+            x = tp.linear_all_reduce(core.reshape(B, -1), w_out, add=x)
+            gu = lin(Q.rms(x, l.post_attention_layernorm, eps), l.ffn.gate_up)
+            x = tp.linear_all_reduce(self._swiglu(gu), l.ffn.down, add=x)
+        self.pos_t += 1
+        return Q.rms(x, m.norm, eps)
+
+    def step(self, tok):
+        if self.pos == 0 or not self.device_step_supported():
+            return self.run(tok.reshape(-1, 1))
+        if self.pos + 1 > self.max_len:
+            raise ValueError("Qwen3.5 cache overflow")
+        if getattr(self, "_graph", None) is None:
+            from ..utils.graph import GraphedStep
+            self.pos_t = torch.full((1,), self.pos, dtype=torch.int32, device=self.m.device)
+            state = [self.pos_t] + [t for s in self.lin if s is not None for t in (s.conv, s.rec)]
+            self._graph = GraphedStep(self._device_step, (tok.reshape(-1).clone(),), advancing_state=state)
+        h = self._graph(tok.reshape(-1))
+        self.pos += 1
+        for c in self.kv:
+            if c is not None:
+                c.length += 1
+        return self.m.tp.all_gather_cols(lin(h, self.m.lm_head))
 
 
 def generate(m: Qwen35TP, input_ids, max_new_tokens=64, strategy=SamplingStrategy.greedy(), eos_token_ids=None, on_step=None):

@@ -74,9 +74,7 @@ class TensorParallel:
 
     # -- helpers ----------------------------------------------------------------------------------------
     def _sync(self, slot: int):
-        self._seq += 1
-        self.barrier.signal(slot, self._seq)
-        self.barrier.wait(slot, self._seq, ptr(err_word(self.device)))
+        self.barrier.barrier_device_seq(slot, ptr(err_word(self.device)))
 
     def _peers(self, t: torch.Tensor):
         off = self.heap.offset_bytes(t)
