@@ -20,6 +20,7 @@ struct SkinnyArgs {
   const __nv_bfloat16* w;      // [N, K], row stride ldw
   const __nv_bfloat16* bias;   // [N] or null
   __nv_bfloat16* y;            // [M, N], row stride ldy
+  float* ws;                   // [M, N] fp32, zero on entry and exit; used when the reduction is split over gridDim.y CTAs
   long long ldx, ldw, ldy;
   int M, N, K;
 };
@@ -54,8 +55,10 @@ __global__ void __launch_bounds__(kSkWarps * 32) skinny_gemm_kernel(SkinnyArgs a
   for (int i = 0; i < TILES; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
 
   const int chunks = a.K >> 5;                   // 32 channels per warp step
+  const int c_lo = static_cast<int>(static_cast<long long>(chunks) * blockIdx.y / gridDim.y);
+  const int c_hi = static_cast<int>(static_cast<long long>(chunks) * (blockIdx.y + 1) / gridDim.y);
 #pragma unroll 4
-  for (int c = warp; c < chunks; c += kSkWarps) {
+  for (int c = c_lo + warp; c < c_hi; c += kSkWarps) {
     const uint4 lo = __ldcs(reinterpret_cast<const uint4*>(w_lo + 32 * c));    // streamed once: do not keep in cache
     const uint4 hi = __ldcs(reinterpret_cast<const uint4*>(w_hi + 32 * c));
 #pragma unroll
@@ -80,23 +83,56 @@ __global__ void __launch_bounds__(kSkWarps * 32) skinny_gemm_kernel(SkinnyArgs a
       float s = 0.f;
 #pragma unroll
       for (int wp = 0; wp < kSkWarps; ++wp) s += part[wp][tok >> 3][r][tok & 7];
-      if (a.bias) s += __bfloat162float(a.bias[row]);
-      a.y[tok * a.ldy + row] = __float2bfloat16(s);
+      if (gridDim.y == 1) {
+        if (a.bias) s += __bfloat162float(a.bias[row]);
+        a.y[tok * a.ldy + row] = __float2bfloat16(s);
+      } else {
+        atomicAdd(a.ws + static_cast<long long>(tok) * a.N + row, s);
+      }
     }
+  }
+}
+
+// Second pass of a split reduction: round the fp32 sums (+ bias) and leave the workspace zeroed for the next call.
+__global__ void __launch_bounds__(256) skinny_finish_kernel(SkinnyArgs a) {
+  const long long n = static_cast<long long>(a.M) * a.N;
+  for (long long i = blockIdx.x * 256LL + threadIdx.x; i < n; i += static_cast<long long>(gridDim.x) * 256) {
+    const int tok = static_cast<int>(i / a.N), row = static_cast<int>(i - static_cast<long long>(tok) * a.N);
+    float s = a.ws[i];
+    a.ws[i] = 0.f;
+    if (a.bias) s += __bfloat162float(a.bias[row]);
+    a.y[tok * a.ldy + row] = __float2bfloat16(s);
   }
 }
 
 }  // namespace tyr
 
-extern "C" TYR_EXPORT int tyr_skinny_gemm_bf16(const void* x, const void* w, const void* bias, void* y, long long ldx, long long ldw,
-                                               long long ldy, int M, int N, int K, void* stream) {
+// Number of CTAs the reduction should be split over for this shape (1 = no workspace needed): enough CTAs to cover the
+// SMs about three times, at least 1024 channels per split.
+extern "C" TYR_EXPORT int tyr_skinny_gemm_splits(int N, int K) {
+  const int row_ctas = (N + 15) / 16;
+  int splits = (3 * 148 + row_ctas - 1) / row_ctas;
+  const int max_by_k = K / 1024 > 0 ? K / 1024 : 1;
+  if (splits > max_by_k) splits = max_by_k;
+  if (splits > 8) splits = 8;
+  return splits < 1 ? 1 : splits;
+}
+
+extern "C" TYR_EXPORT int tyr_skinny_gemm_bf16(const void* x, const void* w, const void* bias, void* y, void* ws, long long ldx,
+                                               long long ldw, long long ldy, int M, int N, int K, void* stream) {
   using namespace tyr;
   if (M < 1 || M > 16 || N < 1 || K < 32 || (K & 31)) return -1;
   if ((ldx | ldw) & 7) return -2;                                    // 16-byte loads
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) return -3;
-  SkinnyArgs a{(const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)bias, (__nv_bfloat16*)y, ldx, ldw, ldy, M, N, K};
-  const int grid = (N + 15) / 16;
+  SkinnyArgs a{(const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)bias, (__nv_bfloat16*)y, (float*)ws, ldx, ldw, ldy, M, N, K};
+  const int splits = ws != nullptr ? tyr_skinny_gemm_splits(N, K) : 1;
+  const dim3 grid((N + 15) / 16, splits);
   if (M <= 8) skinny_gemm_kernel<1><<<grid, kSkWarps * 32, 0, (cudaStream_t)stream>>>(a);
   else skinny_gemm_kernel<2><<<grid, kSkWarps * 32, 0, (cudaStream_t)stream>>>(a);
+  if (splits > 1) {
+    long long blocks = (static_cast<long long>(M) * N + 255) / 256;
+    if (blocks > 592) blocks = 592;
+    skinny_finish_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>(a);
+  }
   return (int)cudaGetLastError();
 }

@@ -10,6 +10,16 @@ from .._native import register_signatures
 from ._common import check, cur_stream, lib, ptr
 
 MAX_ROWS = 16
+_workspaces = {}
+
+
+def _workspace(device, M: int, N: int) -> torch.Tensor:
+    """fp32 [M * N] scratch of the split reduction; zero between calls (the finishing kernel re-zeroes what it read)."""
+    key = (device.index, M * N)
+    ws = _workspaces.get(key)
+    if ws is None:
+        ws = _workspaces[key] = torch.zeros(M * N, dtype=torch.float32, device=device)
+    return ws
 
 
 @register_signatures
@@ -17,8 +27,10 @@ def _sigs(lib_):
     P, I, L = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
     fn = getattr(lib_, "tyr_skinny_gemm_bf16", None)
     if fn is not None:
-        fn.argtypes = [P, P, P, P, L, L, L, I, I, I, P]
+        fn.argtypes = [P, P, P, P, P, L, L, L, I, I, I, P]
         fn.restype = I
+        lib_.tyr_skinny_gemm_splits.argtypes = [I, I]
+        lib_.tyr_skinny_gemm_splits.restype = I
 
 
 def supported(x2: torch.Tensor, w: torch.Tensor) -> bool:
@@ -37,5 +49,6 @@ def skinny_linear(x2: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor
         return (y if bias is None else y + bias.float()).to(x2.dtype)
     y = torch.empty((M, N), dtype=torch.bfloat16, device=x2.device)
     b = None if bias is None else bias.to(torch.bfloat16).contiguous()
-    check(lib().tyr_skinny_gemm_bf16(ptr(x2), ptr(w), ptr(b), ptr(y), x2.stride(0), w.stride(0), N, M, N, K, cur_stream(x2.device)), "skinny_gemm_bf16")
+    ws = _workspace(x2.device, M, N) if lib().tyr_skinny_gemm_splits(N, K) > 1 else None
+    check(lib().tyr_skinny_gemm_bf16(ptr(x2), ptr(w), ptr(b), ptr(y), ptr(ws), x2.stride(0), w.stride(0), N, M, N, K, cur_stream(x2.device)), "skinny_gemm_bf16")
     return y
