@@ -121,6 +121,8 @@ def main(argv=None) -> int:
     ckpt_root = os.path.join(a.checkpoint_dir, "checkpoints")
     if a.resume:
         meta = nck.load(a.resume if os.path.isdir(os.path.join(a.resume, "snapshots")) else os.path.join(a.resume, "checkpoints"), trainer, gen)
+        if a.synthetic:
+            train.i = trainer.step_index * accum           # the synthetic stream is a function of the batch index
         log.on_info(f"Resumed from step {meta['step']} (loss {meta['loss']:.4f})")
     barrier = (lambda: torch.distributed.barrier()) if world > 1 else None
     B, T = hp.device_batch_size, hp.max_seq_len
