@@ -115,6 +115,20 @@ def bench_moe(results, cases=None):
               f"{row['tokens_per_s']:10.0f} tok/s", flush=True)
 
 
+def bench_decode_attention_small(results):
+    """One small case for profiler captures: K/V of 134 MB (larger than L2), two warm-up and three timed launches."""
+    from tyr_b200.ops.decode_attention import decode_attention
+    dev = torch.device("cuda")
+    B, Hq, Hkv, D, pos = 8, 48, 8, 128, 4096
+    q, kn, vn = (torch.randn(B, n, D, device=dev).bfloat16() for n in (Hq, Hkv, Hkv))
+    kc, vc = torch.randn(B, Hkv, pos + 64, D, device=dev).bfloat16(), torch.randn(B, Hkv, pos + 64, D, device=dev).bfloat16()
+    pt = torch.tensor([pos], dtype=torch.int32, device=dev)
+    ms = _time(lambda: decode_attention(q, kn, vn, kc, vc, pt), iters=3, warmup=2)
+    gb = 2.0 * B * Hkv * (pos + 1) * D * 2 / 1e9
+    results.append({"kernel": "decode_attention", "case": "small b8", "ms": ms, "gbs": gb / ms * 1e3})
+    print(f"decode attention small b8: {ms:7.3f} ms {gb / ms * 1e3:7.0f} GB/s", flush=True)
+
+
 def bench_decode_attention(results):
     """Split-KV decode attention with fused append against the library SDPA over the sliced store: Laguna-S-2.1
     (48 q / 8 kv heads x 128) and Qwen3.5-27B (24 q / 4 kv heads x 256) geometries; bandwidth counts the K/V bytes read."""
@@ -168,6 +182,8 @@ def main(argv):
         bench_moe(results)
     if what in ("decode-attn", "all"):
         bench_decode_attention(results)
+    if what == "decode-attn-small":
+        bench_decode_attention_small(results)
     if what in ("skinny", "all"):
         bench_skinny(results)
     if what == "moe-decode":
