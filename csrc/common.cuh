@@ -37,6 +37,34 @@ __device__ __forceinline__ void report_error(int* err, int code, int detail) {
   }
 }
 
+// Checked builds (-DTYR_BOUNDS_CHECK, library libtyr_kernels_checked.so): data-dependent indices (token ids, positions,
+// expert ids, pair maps) are tested before use.  A violation is written once into a per-translation-unit record
+// {ERR_BOUNDS, tag, index, limit} that `tyr_bounds_status_<unit>` copies out and clears, and the access is skipped or
+// clamped; nothing traps.  Release builds compile the test away.
+#ifdef TYR_BOUNDS_CHECK
+static __device__ int g_bounds_record[4];
+__device__ __forceinline__ bool index_ok(long long i, long long n, int tag) {
+  if (i >= 0 && i < n) return true;
+  if (atomicCAS(&g_bounds_record[0], 0, static_cast<int>(ERR_BOUNDS)) == 0) {
+    g_bounds_record[1] = tag;
+    g_bounds_record[2] = static_cast<int>(i);
+    g_bounds_record[3] = static_cast<int>(n);
+  }
+  return false;
+}
+#define TYR_INDEX_OK(i, n, tag) ::tyr::index_ok((i), (n), (tag))
+#define TYR_DEFINE_BOUNDS_STATUS(unit)                                                                   \
+  extern "C" TYR_EXPORT int tyr_bounds_status_##unit(int* out4) {                                        \
+    int zero[4] = {0, 0, 0, 0};                                                                          \
+    cudaError_t e = cudaMemcpyFromSymbol(out4, ::tyr::g_bounds_record, sizeof(zero));                    \
+    if (e == cudaSuccess) e = cudaMemcpyToSymbol(::tyr::g_bounds_record, zero, sizeof(zero));            \
+    return static_cast<int>(e);                                                                          \
+  }
+#else
+#define TYR_INDEX_OK(i, n, tag) true
+#define TYR_DEFINE_BOUNDS_STATUS(unit)
+#endif
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }

@@ -224,6 +224,7 @@ __global__ void moe_scatter_kernel(const int* ids, const int* offsets, int* curs
                                    int* pair_pos, int pairs, int E) {
   for (int p = blockIdx.x * blockDim.x + threadIdx.x; p < pairs; p += gridDim.x * blockDim.x) {
     int e = ids[p];
+    (void)TYR_INDEX_OK(e, E, 11);                    // checked builds record the first bad expert id; it is clamped either way
     e = e < 0 ? 0 : (e >= E ? E - 1 : e);
     const int slot = atomicAdd(cursors + e, 1);
     const int pos = offsets[e] + slot;
@@ -240,6 +241,7 @@ moe_gather_rows_kernel(const __nv_bfloat16* src, const int* pair_order, __nv_bfl
        i < static_cast<long long>(pairs) * vec; i += static_cast<long long>(gridDim.x) * blockDim.x) {
     const int pos = static_cast<int>(i / vec), c = static_cast<int>(i % vec);
     const int tok = pair_order[pos] / k;
+    if (!TYR_INDEX_OK(pair_order[pos], pairs, 12)) continue;
     reinterpret_cast<uint4*>(dst + static_cast<long long>(pos) * h)[c] =
         reinterpret_cast<const uint4*>(src + static_cast<long long>(tok) * h)[c];
   }
@@ -257,6 +259,7 @@ moe_combine_kernel(const __nv_bfloat16* y, const int* pair_pos, const float* wei
     for (int s = 0; s < k; ++s) {
       const int pair = tok * k + s;
       const float w = weights[pair];
+      if (!TYR_INDEX_OK(pair_pos[pair], static_cast<long long>(T) * k, 13)) continue;
       uint4 u = reinterpret_cast<const uint4*>(y + static_cast<long long>(pair_pos[pair]) * h)[c];
       float2 a0 = unpack_bf16x2(u.x), a1 = unpack_bf16x2(u.y), a2 = unpack_bf16x2(u.z), a3 = unpack_bf16x2(u.w);
       acc[0] += w * a0.x; acc[1] += w * a0.y; acc[2] += w * a1.x; acc[3] += w * a1.y;
@@ -640,3 +643,5 @@ extern "C" TYR_EXPORT int tyr_moe_finalize(const float* routed, const void* add,
                                                                        (__nv_bfloat16*)out, n);
   return (int)cudaGetLastError();
 }
+
+TYR_DEFINE_BOUNDS_STATUS(moe)

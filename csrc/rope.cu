@@ -418,7 +418,8 @@ __global__ void __launch_bounds__(256) rope_norm_kernel(RopeNormArgs a) {
       ss = warp_sum(ss);
       rstd = rsqrtf(ss / a.D + a.eps);
     }
-    const int pos = a.pos ? a.pos[row] : static_cast<int>(row % a.T);
+    int pos = a.pos ? a.pos[row] : static_cast<int>(row % a.T);
+    if (!TYR_INDEX_OK(pos, a.T, 21)) pos = 0;      // checked builds record a position outside the tables and rotate by position 0
     const float* c = a.cosT + static_cast<long long>(pos) * hr;
     const float* s = a.sinT + static_cast<long long>(pos) * hr;
     auto nrm = [&](int i) -> float {
@@ -495,3 +496,5 @@ extern "C" TYR_EXPORT int tyr_rope_norm(const void* x, void* y, const void* w, c
   rope_norm_kernel<<<grid_for_units(1LL * rows * H, 8), 256, 0, (cudaStream_t)stream>>>(a);
   return (int)cudaGetLastError();
 }
+
+TYR_DEFINE_BOUNDS_STATUS(rope)

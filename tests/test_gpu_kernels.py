@@ -371,3 +371,33 @@ def test_flag_wait_runs_out_and_reports_without_losing_the_context():
     wait_flags_bounded(flags, 2, 0, 5, ptr(err), 200_000_000)
     raise_on_device_error(dev)                              # satisfied wait: no error
     assert float((torch.ones(4, device=dev) * 2).sum()) == 8.0
+
+
+def test_checked_build_records_a_bad_index_and_skips_it():
+    """The -DTYR_BOUNDS_CHECK library: a rotary position outside the table and a pair index outside the batch are
+    recorded (tag, index, limit) without faulting; clean inputs leave the record empty."""
+    import ctypes
+    from tyr_b200._native.checked import bounds_status, checked
+    lib = checked()
+    dev = torch.device("cuda", 0)
+    st = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+    x = torch.randn(4, 2, 32, device=dev).bfloat16()
+    y = torch.empty_like(x)
+    cos, sin = torch.ones(16, 8, device=dev), torch.zeros(16, 8, device=dev)
+    assert bounds_status("rope")[0] == 0
+    pos = torch.tensor([0, 3, 15, 7], dtype=torch.int32, device=dev)
+    assert lib.tyr_rope_norm(p(x), p(y), None, p(cos), p(sin), p(pos), 64, 64, 4, 16, 2, 32, 16, 1e-6, 0, st) == 0
+    torch.cuda.synchronize()
+    assert bounds_status("rope") == (0, 0, 0, 0) and torch.equal(x, y)              # cos 1 / sin 0: identity rotation
+    pos[2] = 99
+    assert lib.tyr_rope_norm(p(x), p(y), None, p(cos), p(sin), p(pos), 64, 64, 4, 16, 2, 32, 16, 1e-6, 0, st) == 0
+    torch.cuda.synchronize()
+    assert bounds_status("rope") == (3, 21, 99, 16) and bounds_status("rope")[0] == 0   # read clears
+    src = torch.randn(3, 16, device=dev).bfloat16()
+    dst = torch.zeros(6, 16, device=dev).bfloat16()
+    order = torch.tensor([0, 1, 2, 77, 4, 5], dtype=torch.int32, device=dev)
+    assert lib.tyr_moe_gather_rows(p(src), p(order), p(dst), 6, 2, 16, st) == 0
+    torch.cuda.synchronize()
+    assert bounds_status("moe") == (3, 12, 77, 6)
+    assert torch.equal(dst[0], src[0]) and torch.equal(dst[4], src[2]) and bool((dst[3] == 0).all())     # the bad row was skipped

@@ -32,7 +32,9 @@ def _exported(lib_name):
 
 def test_every_bound_symbol_is_exported_and_every_export_is_bound():
     _native.kernels(), _native.host()          # builds the libraries when missing
-    exported = _exported("libtyr_kernels.so") | _exported("libtyr_host.so")
+    from tyr_b200._native import checked
+    checked.checked()
+    exported = _exported("libtyr_kernels.so") | _exported("libtyr_host.so") | _exported("libtyr_kernels_checked.so")
     named = _python_names()
     missing = sorted(n for n in named if n not in exported and n not in OPTIONAL)
     assert not missing, f"Python names native symbols that no library exports: {missing}"

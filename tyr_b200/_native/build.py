@@ -59,18 +59,26 @@ def _run(cmd):
     return r.stdout + r.stderr
 
 
-def build_kernels(verbose: bool = False, force: bool = False) -> Path:
+CHECKED_UNITS = ("moe_nvfp4", "rope")       # translation units with index checks; the checked library holds only these
+
+
+def build_kernels(verbose: bool = False, force: bool = False, checked: bool = False) -> Path:
+    """``checked=True`` builds ``libtyr_kernels_checked.so``: the units listed in ``CHECKED_UNITS`` compiled with
+    ``-DTYR_BOUNDS_CHECK`` (data-dependent indices are tested and violations recorded, see csrc/common.cuh)."""
     srcs = sorted(CSRC.glob("*.cu"))
+    if checked:
+        srcs = [s for s in srcs if s.stem in CHECKED_UNITS]
     hdrs = sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h"))
-    out = OUT_DIR / "libtyr_kernels.so"
+    out = OUT_DIR / ("libtyr_kernels_checked.so" if checked else "libtyr_kernels.so")
     OBJ_DIR.mkdir(parents=True, exist_ok=True)
-    hdr_digest = _digest(hdrs, " ".join(NVCC_FLAGS))
+    base_flags = NVCC_FLAGS + (["-DTYR_BOUNDS_CHECK"] if checked else [])
+    hdr_digest = _digest(hdrs, " ".join(base_flags))
     nvcc = _nvcc()
     jobs = []
     objs = []
     for s in srcs:
-        obj = OBJ_DIR / (s.stem + ".o")
-        stamp = OBJ_DIR / (s.stem + ".sha")
+        obj = OBJ_DIR / (s.stem + (".checked.o" if checked else ".o"))
+        stamp = OBJ_DIR / (s.stem + (".checked.sha" if checked else ".sha"))
         dig = _digest([s], hdr_digest)
         objs.append(obj)
         if force or not obj.exists() or not stamp.exists() or stamp.read_text() != dig:
@@ -78,7 +86,7 @@ def build_kernels(verbose: bool = False, force: bool = False) -> Path:
 
     def compile_one(job):
         s, obj, stamp, dig = job
-        flags = list(NVCC_FLAGS)
+        flags = list(base_flags)
         if verbose:
             flags += ["-Xptxas", "-v"]
         log = _run([nvcc, *flags, "-I", str(CSRC), "-c", str(s), "-o", str(obj)])
@@ -111,6 +119,7 @@ def build_host(force: bool = False) -> Path:
 
 
 def build_all(verbose: bool = False, force: bool = False):
+    build_kernels(verbose=verbose, force=force, checked=True)
     return build_kernels(verbose=verbose, force=force), build_host(force=force)
 
 
