@@ -63,7 +63,7 @@ def bench_distributed(sizes: Sequence[int], args: Sequence[str], log_dir: str, e
     for i, n in enumerate(sizes):
         if n < 1:
             raise ValueError(f"invalid process count '{n}'")
-        ck = tempfile.mkdtemp(prefix=f"tyr_bench_{n}gpu_")
+        ck = tempfile.mkdtemp(prefix=f"bench_{n}gpu_")
         log = runner(torchrun_command("tyr_b200.cli.train_nanochat", n, [*args, "--checkpoint-dir", ck], 29540 + i),
                      log_file=os.path.join(log_dir, f"tyr_nanochat_{n}gpu.log"), echo=echo)
         if "Finished at step" not in log:
@@ -84,7 +84,7 @@ def bench_distributed(sizes: Sequence[int], args: Sequence[str], log_dir: str, e
 def test_resume(nproc: int, args: Sequence[str], steps: int = 6, echo: bool = True, runner=run) -> bool:
     """Train ``steps`` straight through, then ``steps / 2`` + resume; the final logged losses must agree."""
     half = steps // 2
-    a, b = tempfile.mkdtemp(prefix="tyr_resume_a_"), tempfile.mkdtemp(prefix="tyr_resume_b_")
+    a, b = tempfile.mkdtemp(prefix="resume_a_"), tempfile.mkdtemp(prefix="resume_b_")
     common = [*args, "--log-every", "1"]
     full = runner(torchrun_command("tyr_b200.cli.train_nanochat", nproc, [*common, "--iterations", str(steps), "--checkpoint-dir", a], 29560), echo=echo)
     runner(torchrun_command("tyr_b200.cli.train_nanochat", nproc, [*common, "--iterations", str(half), "--checkpoint-dir", b], 29561), echo=echo)
