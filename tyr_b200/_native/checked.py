@@ -8,7 +8,8 @@ from pathlib import Path
 from typing import Tuple
 
 _lib = None
-UNITS = ("moe", "rope")
+STATUS_FNS = {"moe": "tyr_bounds_status_moe", "rope": "tyr_bounds_status_rope"}
+UNITS = tuple(STATUS_FNS)
 
 
 def checked():
@@ -23,13 +24,13 @@ def checked():
         _lib.tyr_rope_norm.argtypes = [P, P, P, P, P, P, L, L, I, I, I, I, I, F, I, P]
         _lib.tyr_moe_gather_rows.argtypes = [P, P, P, I, I, I, P]
         for u in UNITS:
-            getattr(_lib, f"tyr_bounds_status_{u}").argtypes = [ctypes.POINTER(ctypes.c_int)]
+            getattr(_lib, STATUS_FNS[u]).argtypes = [ctypes.POINTER(ctypes.c_int)]
     return _lib
 
 
 def bounds_status(unit: str) -> Tuple[int, int, int, int]:
     out = (ctypes.c_int * 4)()
-    rc = getattr(checked(), f"tyr_bounds_status_{unit}")(out)
+    rc = getattr(checked(), STATUS_FNS[unit])(out)
     if rc != 0:
-        raise RuntimeError(f"tyr_bounds_status_{unit} failed with CUDA error {rc}")
+        raise RuntimeError(f"{STATUS_FNS[unit]} failed with CUDA error {rc}")
     return tuple(out)
