@@ -288,7 +288,10 @@ def attention_forward(cfg: Gemma4Config, i: int, a: Attention, x, rot, cache: Op
 
 
 def layer_forward(cfg, i, l: Layer, x, rot, cache, shared, per_layer_input=None, edge_mask=None):
+    """``edge_mask``: one [B, S, S] mask for every layer, or a ``(sliding, full)`` pair chosen by the layer's kind."""
     B, S, h = x.shape
+    if isinstance(edge_mask, (tuple, list)):
+        edge_mask = edge_mask[1] if cfg.is_full(i) else edge_mask[0]
     eps = cfg.rms_norm_eps
     h2 = x + rms(attention_forward(cfg, i, l.self_attn, rms(x, l.input_layernorm, eps), rot, cache, shared, edge_mask), l.post_attention_layernorm, eps)
     h3 = rms(h2, l.pre_feedforward_layernorm, eps)
@@ -345,8 +348,12 @@ class Gemma4Cache:
                 self.caches.append(KVCache.allocate(batch, Hkv, max_len, D, m.device, m.dtype))
 
     @torch.no_grad()
-    def run(self, ids: torch.Tensor, embeds: Optional[torch.Tensor] = None, per_layer=None) -> torch.Tensor:
+    def run(self, ids: torch.Tensor, embeds: Optional[torch.Tensor] = None, per_layer=None, edge_mask=None) -> torch.Tensor:
+        """``edge_mask`` (prefill of an empty cache only) replaces the causal / window masks, e.g. to let the tokens of one
+        image attend to each other in both directions."""
         m, cfg = self.m, self.m.cfg
+        if edge_mask is not None and self.pos != 0:
+            raise ValueError("edge masks apply to the prefill of an empty cache")
         x = embed_tokens(m, ids) if embeds is None else embeds
         S = x.shape[1]
         if self.pos + S > self.max_len:
@@ -358,7 +365,7 @@ class Gemma4Cache:
             rot = (fc[sl], fs[sl]) if cfg.is_full(i) else (sc[sl], ss[sl])
             src = cfg.shared_source_layer(i)
             x = layer_forward(cfg, i, l, x, rot, self.caches[i], self.caches[src] if src is not None else None,
-                              pli[:, :, i] if pli is not None else None)
+                              pli[:, :, i] if pli is not None else None, edge_mask)
         self.pos += S
         return cap_logits(cfg, lin(rms(x[:, -1], m.norm, cfg.rms_norm_eps), m.lm_head))
 
