@@ -1,0 +1,571 @@
+// Flash-attention backward for sm_100a on tcgen05 / TMEM / TMA (head dim 128, bf16).
+//
+// One CTA owns one 128-key block of one (batch, KV head): K_j and V_j stay in shared memory, dK_j
+// and dV_j accumulate in TMEM over every query block (and every query head of the GQA group) that
+// sees the block, and are written once at the end.  Scores are produced TRANSPOSED (keys on the
+// TMEM lanes, query rows on the columns), so P^T and dS^T are directly the A operands of the
+// dV / dK products:
+//
+//   S^T  = K Q_i^T                 (SS)      TMEM columns   0..127
+//   dP^T = V dO_i^T                (SS)      TMEM columns 256..383
+//   P^T  = exp2(S^T * c - lse_i)             bf16, packed over the S^T columns it came from
+//   dS^T = P^T o (dP^T - delta_i)            bf16 -> shared memory, [keys][query rows], 128B swizzle
+//   dV  += P^T dO_i                (TS)      TMEM columns 128..255
+//   dK  += dS^T Q_i                (SS)      TMEM columns 384..511
+//   dQ_i = dS K                    (SS, both operands MN-major)  TMEM columns 256..383 (over dP^T)
+//
+// dQ_i is drained by its own warpgroup with vector fp32 reductions into a [B, Hq, Tpad, 128] fp32
+// accumulator (several key blocks add into the same rows); a small kernel before this one computes
+// delta = rowsum(dO o O), rescales the log-sum-exp to base 2 and zeroes the accumulator, and one
+// after it scales and converts dQ to bf16.
+//
+//   warps 0-3   scores: query-row columns  0..63  of the block (one thread per key / TMEM lane)
+//   warps 4-7   scores: query-row columns 64..127
+//   warps 8-11  dQ drain
+//   warp 12     MMA issuer, warp 13 TMA producer (Q_i, dO_i, lse_i, delta_i into a 2-stage ring)
+//
+// Masks are those of the forward kernel: causal with offset, sliding window, key length.  Query rows
+// past Tq carry lse = +inf in the padded statistics, so their probabilities are exactly zero.
+//
+// The reference differentiates at::scaled_dot_product_attention through autograd
+// (cc/include/tyr_attention.h:58-130).
+#include "common.cuh"
+
+#include <climits>
+
+namespace tyr {
+
+constexpr int BW_T = 128;                       // rows of a query block == keys of a key block == head dim
+constexpr uint32_t BW_CHUNK = BW_T * 64 * 2;    // one [128 x 64] bf16 swizzled chunk
+constexpr uint32_t BW_TILE = 2 * BW_CHUNK;      // 32 KB
+
+struct BwdParams {
+  int B, Hq, Hkv, Tq, Tk, Tpad;
+  int q_offset, causal, window;
+  float scale, scale_log2;
+  const float* lse2;      // [B, Hq, Tpad], base-2, +inf on padded / empty rows
+  const float* delta;     // [B, Hq, Tpad]
+  float* dq_acc;          // [B, Hq, Tpad, 128] fp32, zeroed
+  __nv_bfloat16* dK;
+  __nv_bfloat16* dV;
+  long long dk_sb, dk_st, dk_sh, dv_sb, dv_st, dv_sh;
+  int* err;
+};
+
+struct __align__(1024) BwdSmem {
+  uint8_t k[BW_TILE];
+  uint8_t v[BW_TILE];
+  uint8_t q[2][BW_TILE];
+  uint8_t dout[2][BW_TILE];
+  uint8_t ds[BW_TILE];
+  float lse[2][BW_T];
+  float delta[2][BW_T];
+  uint64_t kv_full;
+  uint64_t q_full[2];      // Q_i + lse_i
+  uint64_t do_full[2];     // dO_i + delta_i
+  uint64_t qdo_empty[2];
+  uint64_t s_ready, dp_ready, p_ready, ds_ready, dq_ready, dq_free, acc_done;
+  uint32_t tmem_base;
+};
+
+static_assert(sizeof(BwdSmem) <= 227 * 1024, "backward tiles exceed the shared memory of one CTA");
+
+__device__ __forceinline__ void bulk_load_1d(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(dst)),
+               "l"(src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void red_add_v4(float* dst, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+// Query blocks [lo, hi) that see at least one key of block j.
+__device__ __forceinline__ void q_range(const BwdParams& p, int j, int& lo, int& hi) {
+  const int nq = (p.Tq + BW_T - 1) / BW_T;
+  lo = 0;
+  hi = nq;
+  if (p.causal) lo = max(0, j * BW_T - p.q_offset) / BW_T;
+  if (p.window > 0) {
+    const int kmax = min(p.Tk - 1, j * BW_T + BW_T - 1);
+    const int last_row = kmax - p.q_offset + p.window - 1;
+    hi = last_row < 0 ? 0 : min(nq, last_row / BW_T + 1);
+  }
+  if (hi < lo) hi = lo;
+}
+
+__global__ void __launch_bounds__(512, 1)
+flash_bwd_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                      const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
+                      BwdParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  BwdSmem& s = *reinterpret_cast<BwdSmem*>(smem_raw);
+  if ((smem_u32(smem_raw) & 1023u) != 0) {       // the swizzled tiles need a 1024-byte aligned base
+    if (threadIdx.x == 0) report_error(p.err, ERR_TMEM, 800);
+    return;
+  }
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int j = blockIdx.x;
+  const int kvh = blockIdx.y;
+  const int batch = blockIdx.z;
+  const int G = p.Hq / p.Hkv;
+  int ilo, ihi;
+  q_range(p, j, ilo, ihi);
+  const int ni = ihi - ilo;
+  const int n_it = ni * G;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&s.kv_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s.q_full[i], 1);
+      mbar_init(&s.do_full[i], 1);
+      mbar_init(&s.qdo_empty[i], 1);
+    }
+    mbar_init(&s.s_ready, 1);
+    mbar_init(&s.dp_ready, 1);
+    mbar_init(&s.p_ready, 256);
+    mbar_init(&s.ds_ready, 256);
+    mbar_init(&s.dq_ready, 1);
+    mbar_init(&s.dq_free, 128);
+    mbar_init(&s.acc_done, 1);
+    mbar_fence_init();
+  }
+  if (warp == 12) {
+    tmem_alloc(&s.tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = s.tmem_base;
+  constexpr uint32_t COL_S = 0, COL_DV = 128, COL_DPQ = 256, COL_DK = 384;
+
+  if (warp >= 12) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
+    if (warp == 13) {
+      // ---------------------------------------------------------------- TMA producer
+      if (elect_one() && n_it > 0) {
+        tma_prefetch_desc(&tmQ);
+        tma_prefetch_desc(&tmK);
+        tma_prefetch_desc(&tmV);
+        tma_prefetch_desc(&tmDO);
+        mbar_expect_tx(&s.kv_full, 2 * BW_TILE);
+        for (int c = 0; c < 2; ++c) {
+          tma_load_4d(s.k + c * BW_CHUNK, &tmK, &s.kv_full, c * 64, kvh, j * BW_T, batch);
+          tma_load_4d(s.v + c * BW_CHUNK, &tmV, &s.kv_full, c * 64, kvh, j * BW_T, batch);
+        }
+        bool ok = true;
+        int it = 0;
+        for (; it < n_it; ++it) {
+          const int st = it & 1;
+          const uint32_t ph = (it >> 1) & 1;
+          const int head = kvh * G + it / ni;
+          const int i = ilo + it % ni;
+          if (!mbar_wait(&s.qdo_empty[st], ph ^ 1, p.err, 810 + st)) { ok = false; break; }
+          const long long stat = (static_cast<long long>(batch) * p.Hq + head) * p.Tpad + i * BW_T;
+          mbar_expect_tx(&s.q_full[st], BW_TILE + BW_T * 4);
+          for (int c = 0; c < 2; ++c)
+            tma_load_4d(s.q[st] + c * BW_CHUNK, &tmQ, &s.q_full[st], c * 64, head, i * BW_T, batch);
+          bulk_load_1d(s.lse[st], p.lse2 + stat, BW_T * 4, &s.q_full[st]);
+          mbar_expect_tx(&s.do_full[st], BW_TILE + BW_T * 4);
+          for (int c = 0; c < 2; ++c)
+            tma_load_4d(s.dout[st] + c * BW_CHUNK, &tmDO, &s.do_full[st], c * 64, head, i * BW_T, batch);
+          bulk_load_1d(s.delta[st], p.delta + stat, BW_T * 4, &s.do_full[st]);
+        }
+        if (!ok) {   // let the copies in flight land before the CTA unwinds
+          mbar_wait(&s.kv_full, 0, nullptr, 0);
+          for (int q = max(0, it - 2); q < it; ++q) {
+            mbar_wait(&s.q_full[q & 1], (q >> 1) & 1, nullptr, 0);
+            mbar_wait(&s.do_full[q & 1], (q >> 1) & 1, nullptr, 0);
+          }
+        }
+      }
+    } else if (warp == 12) {
+      // ---------------------------------------------------------------- MMA issuer
+      if (elect_one() && n_it > 0) {
+        constexpr uint32_t idesc_kk = make_idesc_f16(1, BW_T, BW_T, 0, 0);   // both operands K-major
+        constexpr uint32_t idesc_kn = make_idesc_f16(1, BW_T, BW_T, 0, 1);   // B MN-major
+        constexpr uint32_t idesc_nn = make_idesc_f16(1, BW_T, BW_T, 1, 1);   // A and B MN-major
+        const uint32_t ka = smem_u32(s.k), va = smem_u32(s.v), dsa = smem_u32(s.ds);
+        // D = A[128 x 128, K-major] * B[128 x 128, K-major]^T
+        auto mma_kk = [&](uint32_t d_col, uint32_t a, uint32_t b) {
+#pragma unroll
+          for (int k = 0; k < BW_T / 16; ++k) {
+            const uint32_t off = (k >> 2) * BW_CHUNK + (k & 3) * 32;
+            umma_f16_ss(tmem_base + d_col, make_smem_desc_sw128(a + off, 16, 1024),
+                        make_smem_desc_sw128(b + off, 16, 1024), idesc_kk, k > 0 ? 1u : 0u);
+          }
+        };
+        bool ok = mbar_wait(&s.kv_full, 0, p.err, 820);
+        ok = ok && mbar_wait(&s.q_full[0], 0, p.err, 821);
+        if (ok) {
+          tc_fence_after();
+          mma_kk(COL_S, ka, smem_u32(s.q[0]));
+          umma_commit(&s.s_ready);
+          ok = mbar_wait(&s.do_full[0], 0, p.err, 822);
+        }
+        if (ok) {
+          tc_fence_after();
+          mma_kk(COL_DPQ, va, smem_u32(s.dout[0]));
+          umma_commit(&s.dp_ready);
+        }
+        for (int it = 0; it < n_it && ok; ++it) {
+          const int st = it & 1;
+          const uint32_t par = it & 1;
+          const uint32_t qa = smem_u32(s.q[st]), doa = smem_u32(s.dout[st]);
+          // dV += P^T dO_i : A from TMEM (16 bf16 per K step = 8 columns; the two score warpgroups
+          // packed their halves at columns 0 and 64), B = dO_i [rows][d] MN-major
+          if (!mbar_wait(&s.p_ready, par, p.err, 830)) { ok = false; break; }
+          tc_fence_after();
+#pragma unroll
+          for (int k = 0; k < BW_T / 16; ++k)
+            umma_f16_ts(tmem_base + COL_DV, tmem_base + COL_S + (k >> 2) * 64 + (k & 3) * 8,
+                        make_smem_desc_sw128(doa + k * 2048, BW_CHUNK, 1024), idesc_kn,
+                        (it == 0 && k == 0) ? 0u : 1u);
+          if (it + 1 < n_it) {
+            const int sn = (it + 1) & 1;
+            if (!mbar_wait(&s.q_full[sn], ((it + 1) >> 1) & 1, p.err, 831)) { ok = false; break; }
+            tc_fence_after();
+            mma_kk(COL_S, ka, smem_u32(s.q[sn]));
+            umma_commit(&s.s_ready);
+          }
+          if (!mbar_wait(&s.ds_ready, par, p.err, 832)) { ok = false; break; }
+          tc_fence_after();
+          // dK += dS^T Q_i : A = dS^T [keys][rows] K-major, B = Q_i [rows][d] MN-major
+#pragma unroll
+          for (int k = 0; k < BW_T / 16; ++k)
+            umma_f16_ss(tmem_base + COL_DK, make_smem_desc_sw128(dsa + (k >> 2) * BW_CHUNK + (k & 3) * 32, 16, 1024),
+                        make_smem_desc_sw128(qa + k * 2048, BW_CHUNK, 1024), idesc_kn, (it == 0 && k == 0) ? 0u : 1u);
+          // dQ_i = dS K : A = dS read MN-major out of the same buffer, B = K [keys][d] MN-major
+#pragma unroll
+          for (int k = 0; k < BW_T / 16; ++k)
+            umma_f16_ss(tmem_base + COL_DPQ, make_smem_desc_sw128(dsa + k * 2048, BW_CHUNK, 1024),
+                        make_smem_desc_sw128(ka + k * 2048, BW_CHUNK, 1024), idesc_nn, k > 0 ? 1u : 0u);
+          umma_commit(&s.dq_ready);
+          umma_commit(&s.qdo_empty[st]);
+          if (it + 1 < n_it) {
+            const int sn = (it + 1) & 1;
+            if (!mbar_wait(&s.do_full[sn], ((it + 1) >> 1) & 1, p.err, 833)) { ok = false; break; }
+            if (!mbar_wait(&s.dq_free, par, p.err, 834)) { ok = false; break; }
+            tc_fence_after();
+            mma_kk(COL_DPQ, va, smem_u32(s.dout[sn]));
+            umma_commit(&s.dp_ready);
+          }
+        }
+        if (ok) umma_commit(&s.acc_done);
+      }
+    }
+  } else if (warp >= 8) {
+    // ------------------------------------------------------------------ dQ drain
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 96;");
+    const int lrow = (warp & 3) * 32 + lane;
+    const uint32_t addr = tmem_base + COL_DPQ + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+    for (int it = 0; it < n_it; ++it) {
+      const int head = kvh * G + it / ni;
+      const int i = ilo + it % ni;
+      if (!mbar_wait(&s.dq_ready, it & 1, p.err, 840)) break;
+      tc_fence_after();
+      float* dst = p.dq_acc + ((static_cast<long long>(batch) * p.Hq + head) * p.Tpad + i * BW_T + lrow) * BW_T;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(addr + c * 32, r);
+        tmem_wait_ld();
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          red_add_v4(dst + c * 32 + q * 4, __uint_as_float(r[q * 4]), __uint_as_float(r[q * 4 + 1]),
+                     __uint_as_float(r[q * 4 + 2]), __uint_as_float(r[q * 4 + 3]));
+      }
+      tc_fence_before();
+      mbar_arrive(&s.dq_free);
+    }
+  } else {
+    // ------------------------------------------------------------------ score warps
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 168;");
+    const int wg = warp >> 2;
+    const int r = (warp & 3) * 32 + lane;                // key row of this thread inside the block
+    const int key = j * BW_T + r;
+    const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t s_addr = tmem_base + COL_S + wg * 64 + lane_addr;
+    const uint32_t dp_addr = tmem_base + COL_DPQ + wg * 64 + lane_addr;
+    const int rmin = p.causal ? key - p.q_offset : INT_MIN;                 // rows that see this key: [rmin, rmax)
+    const int rmax = p.window > 0 ? key - p.q_offset + p.window : INT_MAX;
+    const bool key_ok = key < p.Tk;
+    uint8_t* ds_row = s.ds + wg * BW_CHUNK + r * 128;
+    bool ok = true;
+    for (int it = 0; it < n_it && ok; ++it) {
+      const int st = it & 1;
+      const uint32_t ph = (it >> 1) & 1;
+      const int i = ilo + it % ni;
+      const int row0 = i * BW_T + wg * 64;               // first query row of this thread's columns
+      if (!mbar_wait(&s.q_full[st], ph, p.err, 850)) { ok = false; break; }
+      if (!mbar_wait(&s.s_ready, it & 1, p.err, 851)) { ok = false; break; }
+      tc_fence_after();
+      float pr[64];
+      {
+        uint32_t t[64];
+        tmem_ld_32x32(s_addr, *reinterpret_cast<uint32_t(*)[32]>(t));
+        tmem_ld_32x32(s_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(t + 32));
+        tmem_wait_ld();
+        const int blk_lo = i * BW_T, blk_hi = i * BW_T + BW_T - 1;
+        const bool full = (j * BW_T + BW_T <= p.Tk) && (!p.causal || j * BW_T + BW_T - 1 <= blk_lo + p.q_offset) &&
+                          (p.window <= 0 || j * BW_T > blk_hi + p.q_offset - p.window);
+        const float4* l4 = reinterpret_cast<const float4*>(&s.lse[st][wg * 64]);
+        if (full) {
+#pragma unroll
+          for (int c = 0; c < 16; ++c) {
+            const float4 l = l4[c];
+            pr[4 * c + 0] = exp2f(fmaf(__uint_as_float(t[4 * c + 0]), p.scale_log2, -l.x));
+            pr[4 * c + 1] = exp2f(fmaf(__uint_as_float(t[4 * c + 1]), p.scale_log2, -l.y));
+            pr[4 * c + 2] = exp2f(fmaf(__uint_as_float(t[4 * c + 2]), p.scale_log2, -l.z));
+            pr[4 * c + 3] = exp2f(fmaf(__uint_as_float(t[4 * c + 3]), p.scale_log2, -l.w));
+          }
+        } else {
+#pragma unroll
+          for (int c = 0; c < 16; ++c) {
+            const float4 l = l4[c];
+            const float lv[4] = {l.x, l.y, l.z, l.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int row = row0 + 4 * c + e;
+              const bool keep = key_ok && row >= rmin && row < rmax;
+              pr[4 * c + e] = keep ? exp2f(fmaf(__uint_as_float(t[4 * c + e]), p.scale_log2, -lv[e])) : 0.f;
+            }
+          }
+        }
+      }
+      // P^T as packed bf16 over this warpgroup's own score columns
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int q = 0; q < 16; ++q) pk[q] = pack_bf16x2(pr[c * 32 + 2 * q], pr[c * 32 + 2 * q + 1]);
+        tmem_st_32x16(s_addr + c * 16, pk);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(&s.p_ready);
+      if (!mbar_wait(&s.do_full[st], ph, p.err, 852)) { ok = false; break; }
+      if (!mbar_wait(&s.dp_ready, it & 1, p.err, 853)) { ok = false; break; }
+      if (it > 0 && !mbar_wait(&s.dq_ready, (it - 1) & 1, p.err, 854)) { ok = false; break; }   // dS buffer drained
+      tc_fence_after();
+      const float4* d4 = reinterpret_cast<const float4*>(&s.delta[st][wg * 64]);
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t t[32];
+        tmem_ld_32x32(dp_addr + c * 32, t);
+        tmem_wait_ld();
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const float4 da = d4[c * 8 + u * 2], db = d4[c * 8 + u * 2 + 1];
+          const float* pp = pr + c * 32 + u * 8;
+          uint4 w;
+          w.x = pack_bf16x2(pp[0] * (__uint_as_float(t[u * 8 + 0]) - da.x), pp[1] * (__uint_as_float(t[u * 8 + 1]) - da.y));
+          w.y = pack_bf16x2(pp[2] * (__uint_as_float(t[u * 8 + 2]) - da.z), pp[3] * (__uint_as_float(t[u * 8 + 3]) - da.w));
+          w.z = pack_bf16x2(pp[4] * (__uint_as_float(t[u * 8 + 4]) - db.x), pp[5] * (__uint_as_float(t[u * 8 + 5]) - db.y));
+          w.w = pack_bf16x2(pp[6] * (__uint_as_float(t[u * 8 + 6]) - db.z), pp[7] * (__uint_as_float(t[u * 8 + 7]) - db.w));
+          const int unit = c * 4 + u;
+          *reinterpret_cast<uint4*>(ds_row + ((unit ^ (r & 7)) << 4)) = w;
+        }
+      }
+      fence_proxy_async();
+      tc_fence_before();
+      mbar_arrive(&s.ds_ready);
+    }
+    // ---------------------------------------------------------------- dK / dV epilogue
+    if (ok && n_it > 0) ok = mbar_wait(&s.acc_done, 0, p.err, 860);
+    tc_fence_after();
+    if (ok) {
+      // warpgroup 0 writes dV, warpgroup 1 writes dK (scaled)
+      const uint32_t src = tmem_base + (wg == 0 ? COL_DV : COL_DK) + lane_addr;
+      const float f = wg == 0 ? 1.f : p.scale;
+      __nv_bfloat16* out = wg == 0 ? p.dV + batch * p.dv_sb + static_cast<long long>(key) * p.dv_st + kvh * p.dv_sh
+                                   : p.dK + batch * p.dk_sb + static_cast<long long>(key) * p.dk_st + kvh * p.dk_sh;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t o[32];
+        if (n_it > 0) {
+          tmem_ld_32x32(src + c * 32, o);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int q = 0; q < 32; ++q) o[q] = 0u;
+        }
+        if (key_ok) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint4 u;
+            u.x = pack_bf16x2(__uint_as_float(o[q * 8 + 0]) * f, __uint_as_float(o[q * 8 + 1]) * f);
+            u.y = pack_bf16x2(__uint_as_float(o[q * 8 + 2]) * f, __uint_as_float(o[q * 8 + 3]) * f);
+            u.z = pack_bf16x2(__uint_as_float(o[q * 8 + 4]) * f, __uint_as_float(o[q * 8 + 5]) * f);
+            u.w = pack_bf16x2(__uint_as_float(o[q * 8 + 6]) * f, __uint_as_float(o[q * 8 + 7]) * f);
+            *reinterpret_cast<uint4*>(out + c * 32 + q * 8) = u;
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 12) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// One warp per (batch, head, padded row): delta = sum_d dO*O, lse in base 2 (+inf where the row is
+// padding or saw no key), and the row of the fp32 dQ accumulator cleared.
+__global__ void flash_bwd_prepare_kernel(const __nv_bfloat16* __restrict__ dO, const __nv_bfloat16* __restrict__ O,
+                                         const float* __restrict__ lse, float* __restrict__ lse2,
+                                         float* __restrict__ delta, float* __restrict__ dq_acc, int B, int H, int Tq,
+                                         int Tpad, long long do_sb, long long do_st, long long do_sh, long long o_sb,
+                                         long long o_st, long long o_sh) {
+  const long long w = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long total = static_cast<long long>(B) * H * Tpad;
+  if (w >= total) return;
+  const int row = static_cast<int>(w % Tpad);
+  const int h = static_cast<int>((w / Tpad) % H);
+  const int b = static_cast<int>(w / (static_cast<long long>(Tpad) * H));
+  reinterpret_cast<float4*>(dq_acc + w * BW_T)[lane] = make_float4(0.f, 0.f, 0.f, 0.f);
+  float acc = 0.f, l2 = INFINITY;
+  if (row < Tq) {
+    const uint2 a = *reinterpret_cast<const uint2*>(dO + b * do_sb + static_cast<long long>(row) * do_st + h * do_sh + lane * 4);
+    const uint2 c = *reinterpret_cast<const uint2*>(O + b * o_sb + static_cast<long long>(row) * o_st + h * o_sh + lane * 4);
+    const float2 a0 = unpack_bf16x2(a.x), a1 = unpack_bf16x2(a.y), c0 = unpack_bf16x2(c.x), c1 = unpack_bf16x2(c.y);
+    acc = warp_sum(a0.x * c0.x + a0.y * c0.y + a1.x * c1.x + a1.y * c1.y);
+    const float l = lse[(static_cast<long long>(b) * H + h) * Tq + row];
+    l2 = (l == -INFINITY) ? INFINITY : l * 1.4426950408889634f;
+  }
+  if (lane == 0) {
+    delta[w] = acc;
+    lse2[w] = l2;
+  }
+}
+
+// One warp per (batch, head, row): dQ = bf16(scale * accumulator).
+__global__ void flash_bwd_finish_kernel(const float* __restrict__ dq_acc, __nv_bfloat16* __restrict__ dQ, int B, int H,
+                                        int Tq, int Tpad, long long sb, long long st, long long sh, float scale) {
+  const long long w = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long total = static_cast<long long>(B) * H * Tq;
+  if (w >= total) return;
+  const int row = static_cast<int>(w % Tq);
+  const int h = static_cast<int>((w / Tq) % H);
+  const int b = static_cast<int>(w / (static_cast<long long>(Tq) * H));
+  const float4 v = reinterpret_cast<const float4*>(dq_acc + ((static_cast<long long>(b) * H + h) * Tpad + row) * BW_T)[lane];
+  uint2 u;
+  u.x = pack_bf16x2(v.x * scale, v.y * scale);
+  u.y = pack_bf16x2(v.z * scale, v.w * scale);
+  *reinterpret_cast<uint2*>(dQ + b * sb + static_cast<long long>(row) * st + h * sh + lane * 4) = u;
+}
+
+}  // namespace tyr
+
+using namespace tyr;
+
+namespace {
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+// [B, T, H, 128] bf16 given by element strides; box = 64 channels x 1 head x 128 positions.
+int make_map(CUtensorMap* tm, const void* base, int B, int T, int H, long long sb, long long st, long long sh) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return -1;
+  cuuint64_t dims[4] = {(cuuint64_t)BW_T, (cuuint64_t)H, (cuuint64_t)T, (cuuint64_t)B};
+  cuuint64_t strides[3] = {(cuuint64_t)sh * 2, (cuuint64_t)st * 2, (cuuint64_t)sb * 2};
+  if (H == 1) strides[0] = (cuuint64_t)BW_T * 2;
+  if (B == 1) strides[2] = (cuuint64_t)st * 2 * T;
+  cuuint32_t box[4] = {64, 1, (cuuint32_t)BW_T, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)r;
+}
+}  // namespace
+
+// Bytes of scratch the backward needs: the fp32 dQ accumulator followed by the padded lse / delta rows.
+extern "C" TYR_EXPORT long long tyr_flash_bwd_workspace_bytes(int B, int Hq, int Tq) {
+  const long long tpad = (Tq + BW_T - 1) / BW_T * BW_T;
+  return static_cast<long long>(B) * Hq * tpad * (BW_T + 2) * 4;
+}
+
+// Every tensor is a [B, T, H, 128] view given by (batch, row, head) element strides; lse is the
+// forward's [B, Hq, Tq] fp32 natural-log statistics.  strides: q, k, v, o, do, dq, dk, dv (3 each).
+extern "C" TYR_EXPORT int tyr_flash_bwd(const void* dout, const void* q, const void* k, const void* v, const void* o,
+                                        const float* lse, void* dq, void* dk, void* dv, void* workspace, int B,
+                                        int Hq, int Hkv, int Tq, int Tk, int D, const long long* strides, int causal,
+                                        int window, int q_offset, float scale, int* err, void* stream) {
+  if (D != BW_T) return -1;
+  if (Hq % Hkv != 0 || B <= 0 || Tq <= 0 || Tk <= 0 || !workspace) return -2;
+  for (int i = 0; i < 24; ++i)
+    if (strides[i] & 7) return -3;
+  if (((uintptr_t)dout | (uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)o | (uintptr_t)dq | (uintptr_t)dk |
+       (uintptr_t)dv | (uintptr_t)workspace) & 15)
+    return -4;
+  const long long* sq = strides;
+  const long long* sk = strides + 3;
+  const long long* sv = strides + 6;
+  const long long* so = strides + 9;
+  const long long* sdo = strides + 12;
+  const long long* sdq = strides + 15;
+  const long long* sdk = strides + 18;
+  const long long* sdv = strides + 21;
+  const int tpad = (Tq + BW_T - 1) / BW_T * BW_T;
+  const long long rows = static_cast<long long>(B) * Hq * tpad;
+  float* acc = static_cast<float*>(workspace);
+  float* lse2 = acc + rows * BW_T;
+  float* delta = lse2 + rows;
+  CUtensorMap tq, tk, tv, tdo;
+  int r;
+  if ((r = make_map(&tq, q, B, Tq, Hq, sq[0], sq[1], sq[2]))) return 3000 + r;
+  if ((r = make_map(&tk, k, B, Tk, Hkv, sk[0], sk[1], sk[2]))) return 4000 + r;
+  if ((r = make_map(&tv, v, B, Tk, Hkv, sv[0], sv[1], sv[2]))) return 5000 + r;
+  if ((r = make_map(&tdo, dout, B, Tq, Hq, sdo[0], sdo[1], sdo[2]))) return 6000 + r;
+  constexpr size_t smem = sizeof(BwdSmem);
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(flash_bwd_d128_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return 1000 + (int)e;
+    configured = true;
+  }
+  cudaStream_t cs = (cudaStream_t)stream;
+  {
+    const long long threads = rows * 32;
+    flash_bwd_prepare_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, cs>>>(
+        (const __nv_bfloat16*)dout, (const __nv_bfloat16*)o, lse, lse2, delta, acc, B, Hq, Tq, tpad, sdo[0], sdo[1],
+        sdo[2], so[0], so[1], so[2]);
+  }
+  BwdParams p;
+  p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.Tq = Tq; p.Tk = Tk; p.Tpad = tpad;
+  p.q_offset = q_offset; p.causal = causal; p.window = window;
+  p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
+  p.lse2 = lse2; p.delta = delta; p.dq_acc = acc;
+  p.dK = (__nv_bfloat16*)dk; p.dV = (__nv_bfloat16*)dv;
+  p.dk_sb = sdk[0]; p.dk_st = sdk[1]; p.dk_sh = sdk[2];
+  p.dv_sb = sdv[0]; p.dv_st = sdv[1]; p.dv_sh = sdv[2];
+  p.err = err;
+  dim3 grid((Tk + BW_T - 1) / BW_T, Hkv, B);
+  flash_bwd_d128_kernel<<<grid, 512, smem, cs>>>(tq, tk, tv, tdo, p);
+  {
+    const long long threads = static_cast<long long>(B) * Hq * Tq * 32;
+    flash_bwd_finish_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, cs>>>(acc, (__nv_bfloat16*)dq, B, Hq, Tq, tpad,
+                                                                                sdq[0], sdq[1], sdq[2], scale);
+  }
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 2000 + (int)e;
+}

@@ -313,6 +313,41 @@ def test_flash_attention_forward(B, Hq, Hkv, Tq, Tk, causal, window):
     assert torch.allclose(lse, torch.logsumexp(s, -1), rtol=1e-2, atol=2e-2)
 
 
+@pytest.mark.parametrize("B,Hq,Hkv,Tq,Tk,causal,window", [
+    (2, 2, 2, 256, 256, True, None),
+    (1, 4, 2, 384, 384, True, None),
+    (2, 2, 2, 512, 512, True, 200),
+    (1, 2, 2, 200, 200, True, None),
+    (1, 2, 1, 300, 300, False, None),
+    (1, 2, 2, 128, 640, True, None),
+    (1, 3, 3, 1024, 1024, True, None),
+    (2, 6, 2, 16, 300, True, None),
+])
+def test_flash_attention_backward(B, Hq, Hkv, Tq, Tk, causal, window):
+    """dQ, dK, dV of the tcgen05 backward against fp32 autograd through the explicit masked softmax."""
+    from tyr_b200.ops import flash
+    from tyr_b200.ops._common import err_word
+    from tyr_b200.ops.attention import attention_ref
+    if not (flash.has_fwd() and flash.has_bwd()):
+        pytest.skip("flash kernels not built")
+    g = torch.Generator(device="cuda").manual_seed(5)
+    D = 128
+    q = torch.randn(B, Tq, Hq, D, device=_dev(), generator=g).bfloat16()
+    k = torch.randn(B, Tk, Hkv, D, device=_dev(), generator=g).bfloat16()
+    v = torch.randn(B, Tk, Hkv, D, device=_dev(), generator=g).bfloat16()
+    do = torch.randn(B, Tq, Hq, D, device=_dev(), generator=g).bfloat16()
+    o, lse = flash.flash_fwd_bthd(q, k, v, causal=causal, window=window, scale=None)
+    dq, dk, dv, _ = flash.flash_bwd_bthd(do, q, k, v, o, lse, causal=causal, window=window, scale=None)
+    torch.cuda.synchronize()
+    assert err_word(_dev()).tolist()[0] == 0, err_word(_dev()).tolist()
+    qf, kf, vf = (t.float().transpose(1, 2).requires_grad_() for t in (q, k, v))
+    ref = attention_ref(qf, kf, vf, causal=causal, window=window)
+    ref.backward(do.float().transpose(1, 2))
+    for name, got, want in (("dq", dq, qf.grad), ("dk", dk, kf.grad), ("dv", dv, vf.grad)):
+        e = _rel_err(got, want.transpose(1, 2))
+        assert e < 3e-2, (name, e)
+
+
 @pytest.mark.parametrize("B,Hq,Hkv,D,cap,pos,ring,window,splits", [
     (2, 6, 1, 128, 700, 513, False, None, None), (3, 8, 2, 256, 300, 299, False, 100, 4), (2, 4, 4, 64, 64, 200, True, None, 2),
     (64, 48, 8, 128, 1100, 1024, False, None, None), (1, 8, 1, 128, 96, 5, True, None, 3), (2, 12, 2, 128, 50, 0, False, None, 1),

@@ -9,7 +9,7 @@ from tyr_b200 import _native
 
 ROOT = Path(__file__).resolve().parent.parent
 SYMBOL = re.compile(r"\b(tyr_[a-z0-9_]+)\b")
-OPTIONAL = {"tyr_flash_bwd"}      # probed with hasattr(); the training path takes the library backward until it is built
+OPTIONAL = set()                 # symbols probed with hasattr() that a build may leave out
 
 
 def _python_names():
@@ -21,7 +21,8 @@ def _python_names():
             if f.name == "test_native_exports.py":
                 continue
             text = f.read_text()
-            names.update(m for m in SYMBOL.findall(text) if f"lib.{m}" in text or f"().{m}" in text or f'"{m}"' in text or f".{m}(" in text)
+            names.update(m for m in set(SYMBOL.findall(text))
+                         if re.search(r'(?:lib\.|\(\)\.)' + re.escape(m) + r'(?![a-z0-9_])', text) or f'"{m}"' in text or f".{m}(" in text)
     return {n for n in names if not n.startswith("tyr_b200")}
 
 
@@ -35,6 +36,10 @@ def test_every_bound_symbol_is_exported_and_every_export_is_bound():
     from tyr_b200._native import checked
     checked.checked()
     exported = _exported("libtyr_kernels.so") | _exported("libtyr_host.so") | _exported("libtyr_kernels_checked.so")
+    if _native.parquet() is not None:
+        exported |= _exported("libtyr_parquet.so")
+    else:
+        exported |= {n for n in _python_names() if n.startswith("tyr_parquet_")}
     named = _python_names()
     missing = sorted(n for n in named if n not in exported and n not in OPTIONAL)
     assert not missing, f"Python names native symbols that no library exports: {missing}"

@@ -30,6 +30,8 @@ def _load(name: str):
             try:
                 if name == "libtyr_kernels.so":
                     _b.build_kernels()
+                elif name == "libtyr_parquet.so":
+                    _b.build_parquet()
                 else:
                     _b.build_host()
             except Exception as e:  # pragma: no cover - build environment specific
@@ -60,6 +62,34 @@ def host():
                 _declare_host(lib)
                 _host = lib
     return _host
+
+
+_parquet = None
+
+
+def parquet():
+    """``libtyr_parquet.so`` (native parquet reader) or None when it was not built (no pyarrow at build time)."""
+    global _parquet
+    if _parquet is None:
+        with _lock:
+            if _parquet is None:
+                try:
+                    lib = _load("libtyr_parquet.so")
+                except Exception:
+                    _parquet = False
+                    return None
+                P, I, L, C = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_char_p
+                PP, PL = ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_longlong)
+                lib.tyr_parquet_open.argtypes, lib.tyr_parquet_open.restype = [C, PP, C, I], I
+                lib.tyr_parquet_close.argtypes, lib.tyr_parquet_close.restype = [P], None
+                lib.tyr_parquet_info.argtypes, lib.tyr_parquet_info.restype = [P, PL], I
+                lib.tyr_parquet_row_group_rows.argtypes, lib.tyr_parquet_row_group_rows.restype = [P, I], L
+                lib.tyr_parquet_column.argtypes, lib.tyr_parquet_column.restype = [P, I, C, I], I
+                lib.tyr_parquet_read_text.argtypes, lib.tyr_parquet_read_text.restype = [P, I, C, PP, PP, PP, PL, C, I], I
+                lib.tyr_parquet_to_json_lines.argtypes, lib.tyr_parquet_to_json_lines.restype = [P, I, PP, PL, C, I], I
+                lib.tyr_parquet_free.argtypes, lib.tyr_parquet_free.restype = [P], None
+                _parquet = lib
+    return _parquet or None
 
 
 def kernels_available() -> bool:

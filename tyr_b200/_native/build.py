@@ -1,6 +1,6 @@
 """In-tree build of the native libraries.
 
-Two shared objects are produced next to this file:
+Shared objects produced next to this file (plus ``libtyr_parquet.so``, see :func:`build_parquet`):
 
 * ``libtyr_kernels.so`` - every ``csrc/*.cu`` file, compiled by nvcc for ``sm_100a`` only
   (``-gencode arch=compute_100a,code=sm_100a -lineinfo``).  The kernels are exported as plain
@@ -118,8 +118,36 @@ def build_host(force: bool = False) -> Path:
     return out
 
 
+def build_parquet(force: bool = False):
+    """``libtyr_parquet.so``: csrc/parquet/*.cpp against the Arrow C++ / parquet-cpp libraries inside the pyarrow wheel (the
+    reference links the same ones, cc/Makefile:37-44).  Returns None when pyarrow is not installed."""
+    try:
+        import pyarrow as pa
+    except Exception:
+        return None
+    srcs = sorted((CSRC / "parquet").glob("*.cpp"))
+    libdir = Path(pa.get_library_dirs()[0])
+    arrow = sorted(libdir.glob("libarrow.so.*"), key=lambda q: len(q.name))
+    parquet = sorted(libdir.glob("libparquet.so.*"), key=lambda q: len(q.name))
+    if not srcs or not arrow or not parquet:
+        return None
+    out = OUT_DIR / "libtyr_parquet.so"
+    stamp = OBJ_DIR / "parquet.sha"
+    OBJ_DIR.mkdir(parents=True, exist_ok=True)
+    flags = ["-O2", "-std=c++20", "-fPIC", "-Wall", "-fvisibility=hidden"]
+    dig = _digest(srcs, " ".join(flags) + pa.__version__)
+    if not force and out.exists() and stamp.exists() and stamp.read_text() == dig:
+        return out
+    cxx = shutil.which("g++") or "g++"
+    _run([cxx, *flags, "-shared", "-I", pa.get_include(), "-o", str(out), *map(str, srcs), "-L", str(libdir),
+          "-l:" + parquet[0].name, "-l:" + arrow[0].name, "-Wl,-rpath," + str(libdir)])
+    stamp.write_text(dig)
+    return out
+
+
 def build_all(verbose: bool = False, force: bool = False):
     build_kernels(verbose=verbose, force=force, checked=True)
+    build_parquet(force=force)
     return build_kernels(verbose=verbose, force=force), build_host(force=force)
 
 

@@ -25,12 +25,16 @@ def _sigs(lib_):
     P, I, L, F = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
     for name, args in (
         ("tyr_flash_fwd", [P, P, P, P, P, I, I, I, I, I, I] + [L] * 12 + [I, I, I, F, P, P]),
-        ("tyr_flash_bwd", [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I] + [L] * 12 + [I, I, I, F, P, P]),
+        ("tyr_flash_bwd", [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, ctypes.POINTER(L), I, I, I, F, P, P]),
     ):
         fn = getattr(lib_, name, None)
         if fn is not None:
             fn.argtypes = args
             fn.restype = ctypes.c_int
+    fn = getattr(lib_, "tyr_flash_bwd_workspace_bytes", None)
+    if fn is not None:
+        fn.argtypes = [I, I, I]
+        fn.restype = L
 
 
 def has_fwd() -> bool:
@@ -71,8 +75,9 @@ def flash_fwd_bthd(q, k, v, *, causal: bool, window: Optional[int], scale: Optio
 
 
 def flash_bwd_bthd(do, q, k, v, o, lse, *, causal, window, scale, q_offset=None):
-    """Gradients (dq, dk, dv) as [B, T, H, D] tensors packed into one [B, T, 3, H, D] buffer when
-    Hq == Hkv, else three separate buffers."""
+    """Gradients (dq, dk, dv) as [B, T, H, D] views, packed into one [B, T, 3, H, D] buffer (returned fourth) when
+    Hq == Hkv and Tq == Tk, else three separate buffers.  Every operand is a strided [B, T, H, D] view."""
+    import ctypes
     B, Tq, Hq, D = q.shape
     Tk, Hkv = k.shape[1], k.shape[2]
     if q_offset is None:
@@ -86,10 +91,10 @@ def flash_bwd_bthd(do, q, k, v, o, lse, *, causal, window, scale, q_offset=None)
         dq = torch.empty((B, Tq, Hq, D), dtype=q.dtype, device=q.device)
         dk = torch.empty((B, Tk, Hkv, D), dtype=q.dtype, device=q.device)
         dv = torch.empty((B, Tk, Hkv, D), dtype=q.dtype, device=q.device)
-    check(lib().tyr_flash_bwd(ptr(do), ptr(q), ptr(k), ptr(v), ptr(o), ptr(lse), ptr(dq), ptr(dk), ptr(dv),
-                              None, B, Hq, Hkv, Tq, Tk, D,
-                              *_bthd_strides(q), *_bthd_strides(k), *_bthd_strides(do),
-                              *_bthd_strides(dq), 1 if causal else 0, int(window or 0), q_offset, sc,
+    ws = torch.empty(int(lib().tyr_flash_bwd_workspace_bytes(B, Hq, Tq)), dtype=torch.uint8, device=q.device)
+    strides = (ctypes.c_longlong * 24)(*[x for t in (q, k, v, o, do, dq, dk, dv) for x in _bthd_strides(t)])
+    check(lib().tyr_flash_bwd(ptr(do), ptr(q), ptr(k), ptr(v), ptr(o), ptr(lse), ptr(dq), ptr(dk), ptr(dv), ptr(ws),
+                              B, Hq, Hkv, Tq, Tk, D, strides, 1 if causal else 0, int(window or 0), q_offset, sc,
                               ptr(err_word(q.device)), cur_stream(q.device)), "flash_bwd")
     return dq, dk, dv, buf
 
@@ -110,8 +115,13 @@ def flash_attention(q, k, v, *, causal=True, window=None, scale=None):
     return o.transpose(1, 2)
 
 
+_TRAIN = os.environ.get("TYR_FLASH_TRAIN", "0") == "1"
+
+
 def supported_packed(H, D, T, causal, window) -> bool:
-    return has_fwd() and has_bwd() and D == 128
+    """Training path (forward + backward through these kernels).  Opt-in (TYR_FLASH_TRAIN=1): at head dim 128 the library's
+    fused attention is currently the faster pair, so the default training step keeps it."""
+    return _TRAIN and has_fwd() and has_bwd() and D == 128
 
 
 class _FlashPackedFn(torch.autograd.Function):

@@ -88,6 +88,30 @@ def bench_attention(results):
         print(f"flash fwd B{B} H{H} T{T} causal={causal}: ours {ours:7.3f} ms {flops/ours/1e9:7.1f} TF/s | SDPA {lib:7.3f} ms {flops/lib/1e9:7.1f} TF/s", flush=True)
 
 
+def bench_attention_bwd(results):
+    """Backward of causal / joint attention: the tcgen05 kernel (with its prepare and finish launches) against the
+    library's backward, both through their public entry points."""
+    import torch.nn.functional as F
+    from tyr_b200.ops import flash
+    dev = torch.device("cuda")
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    for B, H, T, causal in ((32, 10, 2048, True), (4, 24, 4608, False), (8, 16, 4096, True)):
+        D = 128
+        qkv = torch.randn(B, T, 3, H, D, device=dev).bfloat16()
+        q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
+        do = torch.randn(B, T, H, D, device=dev).bfloat16()
+        flops = 10.0 * B * H * T * T * D * (0.5 if causal else 1.0)
+        o, lse = flash.flash_fwd_bthd(q, k, v, causal=causal, window=None, scale=None)
+        ours = _time(lambda: flash.flash_bwd_bthd(do, q, k, v, o, lse, causal=causal, window=None, scale=None), flush=flush)
+        qt, kt, vt = (t.transpose(1, 2).detach().requires_grad_() for t in (q, k, v))
+        ol = F.scaled_dot_product_attention(qt, kt, vt, is_causal=causal)
+        dot = do.transpose(1, 2)
+        lib = _time(lambda: torch.autograd.grad(ol, (qt, kt, vt), dot, retain_graph=True), flush=flush)
+        results.append({"kernel": "flash_bwd", "shape": f"B{B} H{H} T{T} D{D} causal={causal}", "ours_ms": ours,
+                        "ours_tflops": flops / ours / 1e9, "sdpa_ms": lib, "sdpa_tflops": flops / lib / 1e9})
+        print(f"flash bwd B{B} H{H} T{T} causal={causal}: ours {ours:7.3f} ms {flops/ours/1e9:7.1f} TF/s | SDPA {lib:7.3f} ms {flops/lib/1e9:7.1f} TF/s", flush=True)
+
+
 def bench_moe(results, cases=None):
     """Fused NVFP4 MoE op at Laguna-S-2.1 shapes (hidden 3072, 256 experts, top-10, FFN 1024): effective
     FP4 weight-read bandwidth for decode-sized batches (the reference's bar is >= 150 GB/s at one token,
@@ -178,6 +202,8 @@ def main(argv):
         bench_gemm(results)
     if what in ("attention", "all"):
         bench_attention(results)
+    if what in ("attention-bwd", "all"):
+        bench_attention_bwd(results)
     if what in ("moe", "all"):
         bench_moe(results)
     if what in ("decode-attn", "all"):
