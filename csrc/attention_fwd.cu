@@ -281,7 +281,9 @@ flash_fwd_d128_kernel(const __grid_constant__ CUtensorMap tmQ,
         const int qi = row + p.q_offset;
         const bool need_mask = (col0 + ATT_BN > p.Tk) || (p.causal && col0 + ATT_BN - 1 > row0 + t * ATT_BM + p.q_offset) ||
                                (p.window > 0 && col0 < row0 + t * ATT_BM + ATT_BM - 1 + p.q_offset - p.window + 1);
-        float mx = -INFINITY;
+        // Row maximum on the raw scores (the softmax scale is positive, so it commutes with max); four
+        // independent chains keep the dependent-issue latency off the critical path.
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
         if (need_mask) {
 #pragma unroll
           for (int c = 0; c < 128; ++c) {
@@ -289,18 +291,15 @@ flash_fwd_d128_kernel(const __grid_constant__ CUtensorMap tmQ,
             bool keep = col < p.Tk;
             if (p.causal) keep = keep && (col <= qi);
             if (p.window > 0) keep = keep && (col > qi - p.window);
-            float v = keep ? __uint_as_float(r[c]) * p.scale_log2 : -INFINITY;
+            const float v = keep ? __uint_as_float(r[c]) : -INFINITY;
             r[c] = __float_as_uint(v);
-            mx = fmaxf(mx, v);
+            mx4[c & 3] = fmaxf(mx4[c & 3], v);
           }
         } else {
 #pragma unroll
-          for (int c = 0; c < 128; ++c) {
-            float v = __uint_as_float(r[c]) * p.scale_log2;
-            r[c] = __float_as_uint(v);
-            mx = fmaxf(mx, v);
-          }
+          for (int c = 0; c < 128; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(r[c]));
         }
+        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
         // lazy rescale: move the reference maximum only when it grew by more than 8 (log2 units)
         const bool first = (j == lo[t]);
         float m_new = fmaxf(m_used, mx);
@@ -321,22 +320,23 @@ flash_fwd_d128_kernel(const __grid_constant__ CUtensorMap tmQ,
           if (want) l_sum *= f;
         }
         if (want) m_used = (m_new == -INFINITY) ? 0.f : m_new;
-        // probabilities -> bf16 -> TMEM (over the first 64 columns of S)
-        float ls = 0.f;
+        // probabilities exp2(s * scale - m) -> bf16 -> TMEM (over the first 64 columns of S); the row sum is
+        // taken in fp32 over four chains
+        float ls4[4] = {0.f, 0.f, 0.f, 0.f};
+        const float neg_m = -m_used;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t pk[16];
 #pragma unroll
           for (int q = 0; q < 16; ++q) {
-            const float p0 = exp2f(__uint_as_float(r[c * 32 + 2 * q]) - m_used);
-            const float p1 = exp2f(__uint_as_float(r[c * 32 + 2 * q + 1]) - m_used);
+            const float p0 = exp2f(fmaf(__uint_as_float(r[c * 32 + 2 * q]), p.scale_log2, neg_m));
+            const float p1 = exp2f(fmaf(__uint_as_float(r[c * 32 + 2 * q + 1]), p.scale_log2, neg_m));
             pk[q] = pack_bf16x2(p0, p1);
-            // sum what the tensor core will actually see
-            float2 rr = unpack_bf16x2(pk[q]);
-            ls += rr.x + rr.y;
+            ls4[q & 3] += p0 + p1;
           }
           tmem_st_32x16(s_addr + c * 16, pk);
         }
+        const float ls = (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
         l_sum += ls;
         tmem_wait_st();
         tc_fence_before();

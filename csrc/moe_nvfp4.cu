@@ -116,17 +116,15 @@ struct RouteArgs {
   float softcap, scale;
 };
 
-__global__ void __launch_bounds__(256) moe_route_kernel(RouteArgs a) {
-  const int lane = threadIdx.x & 31;
-  const int tok = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (tok >= a.T) return;
+// One warp routes one token from its row of logits (global or shared memory).
+__device__ __forceinline__ void route_token(const RouteArgs& a, const float* __restrict__ row, int tok, int lane) {
   constexpr int kMaxPer = 16;   // E <= 512
   float score[kMaxPer], sel[kMaxPer];
   const int per = (a.E + 31) / 32;
   float mx = -INFINITY;
   for (int j = 0; j < kMaxPer; ++j) {
     const int e = lane + 32 * j;
-    float l = (j < per && e < a.E) ? a.logits[static_cast<long long>(tok) * a.E + e] : -INFINITY;
+    float l = (j < per && e < a.E) ? row[e] : -INFINITY;
     if (a.softcap > 0.f && l != -INFINITY) l = a.softcap * tanhf(l / a.softcap);
     score[j] = l;
     mx = fmaxf(mx, l);
@@ -181,6 +179,49 @@ __global__ void __launch_bounds__(256) moe_route_kernel(RouteArgs a) {
     a.weights[static_cast<long long>(tok) * a.k + lane] = w;
     if (a.counts) atomicAdd(a.counts + my_id, 1);
   }
+}
+
+__global__ void __launch_bounds__(256) moe_route_kernel(RouteArgs a) {
+  const int lane = threadIdx.x & 31;
+  const int tok = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (tok >= a.T) return;
+  route_token(a, a.logits + static_cast<long long>(tok) * a.E, tok, lane);
+}
+
+// Decode-sized batches: one CTA per token computes the fp32 router logits itself (bf16 activations, fp32 router
+// weight, fp32 accumulation; warp w takes experts w, w + 8, ...) into shared memory and warp 0 routes from there, so the
+// logits never go through global memory and no separate cast / GEMM launches precede the routing.
+__global__ void __launch_bounds__(256) moe_route_fused_kernel(RouteArgs a, const __nv_bfloat16* __restrict__ x,
+                                                              const float* __restrict__ wr, int h) {
+  extern __shared__ __align__(16) float route_smem[];
+  float* xs = route_smem;          // [h]
+  float* lg = route_smem + h;      // [E]
+  const int tok = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const __nv_bfloat16* xr = x + static_cast<long long>(tok) * h;
+  for (int i = threadIdx.x * 8; i < h; i += blockDim.x * 8) {
+    const uint4 u = *reinterpret_cast<const uint4*>(xr + i);
+    const float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y), f2 = unpack_bf16x2(u.z), f3 = unpack_bf16x2(u.w);
+    *reinterpret_cast<float4*>(xs + i) = make_float4(f0.x, f0.y, f1.x, f1.y);
+    *reinterpret_cast<float4*>(xs + i + 4) = make_float4(f2.x, f2.y, f3.x, f3.y);
+  }
+  __syncthreads();
+  for (int e = warp; e < a.E; e += 8) {
+    const float4* w4 = reinterpret_cast<const float4*>(wr + static_cast<long long>(e) * h);
+    const float4* x4 = reinterpret_cast<const float4*>(xs);
+    float acc0 = 0.f, acc1 = 0.f;
+    for (int i = lane; i < (h >> 2); i += 64) {
+      const float4 w0 = __ldg(w4 + i), v0 = x4[i];
+      acc0 += w0.x * v0.x + w0.y * v0.y + w0.z * v0.z + w0.w * v0.w;
+      if (i + 32 < (h >> 2)) {
+        const float4 w1 = __ldg(w4 + i + 32), v1 = x4[i + 32];
+        acc1 += w1.x * v1.x + w1.y * v1.y + w1.z * v1.z + w1.w * v1.w;
+      }
+    }
+    const float acc = warp_sum(acc0 + acc1);
+    if (lane == 0) lg[e] = acc;
+  }
+  __syncthreads();
+  if (warp == 0) route_token(a, lg, tok, lane);
 }
 
 // offsets[E+1] from counts[E]; cursors[E] zeroed; tiles[E+1] (nullable) = prefix sum of
@@ -544,6 +585,24 @@ extern "C" TYR_EXPORT int tyr_moe_route(const float* logits, const float* bias, 
   if (T <= 0 || E <= 0 || E > 512 || k <= 0 || k > 32 || k > E) return -1;
   RouteArgs a{logits, bias, ids, weights, counts, T, E, k, softmax, renorm, softcap, scale};
   moe_route_kernel<<<(T + 7) / 8, 256, 0, (cudaStream_t)stream>>>(a);
+  return (int)cudaGetLastError();
+}
+
+// Router GEMV + routing in one launch: x bf16 [T, h] (h a multiple of 8), router weight fp32 [E, h].
+extern "C" TYR_EXPORT int tyr_moe_route_fused(const void* x, const float* router_w, const float* bias, int* ids,
+                                              float* weights, int* counts, int T, int E, int k, int h, int softmax,
+                                              int renorm, float softcap, float scale, void* stream) {
+  if (T <= 0 || E <= 0 || E > 512 || k <= 0 || k > 32 || k > E || h <= 0 || (h & 7)) return -1;
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(router_w)) & 15) return -2;
+  const size_t smem = sizeof(float) * (static_cast<size_t>(h) + E);
+  if (smem > 96 * 1024) return -3;
+  static size_t configured = 0;
+  if (smem > 48 * 1024 && configured < smem) {
+    cudaFuncSetAttribute(moe_route_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    configured = smem;
+  }
+  RouteArgs a{nullptr, bias, ids, weights, counts, T, E, k, softmax, renorm, softcap, scale};
+  moe_route_fused_kernel<<<T, 256, smem, (cudaStream_t)stream>>>(a, (const __nv_bfloat16*)x, router_w, h);
   return (int)cudaGetLastError();
 }
 

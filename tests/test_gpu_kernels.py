@@ -436,3 +436,22 @@ def test_checked_build_records_a_bad_index_and_skips_it():
     torch.cuda.synchronize()
     assert bounds_status("moe") == (3, 12, 77, 6)
     assert torch.equal(dst[0], src[0]) and torch.equal(dst[4], src[2]) and bool((dst[3] == 0).all())     # the bad row was skipped
+
+
+@pytest.mark.parametrize("T,E,k,h,softmax", [(1, 256, 10, 3072, False), (64, 256, 10, 3072, False), (7, 64, 8, 2048, True), (33, 512, 4, 1024, False)])
+def test_moe_route_fused_matches_separate_gemm_and_route(T, E, k, h, softmax):
+    """Router GEMV + routing in one launch against fp32 logits from a library GEMM fed to the plain routing kernel."""
+    from tyr_b200.ops import moe
+    g = torch.Generator(device="cuda").manual_seed(T + E)
+    x = torch.randn(T, h, device=_dev(), generator=g).bfloat16()
+    wr = torch.randn(E, h, device=_dev(), generator=g) * h ** -0.5
+    bias = torch.randn(E, device=_dev(), generator=g) * 0.01
+    assert moe.route_fused_supported(x, wr)
+    ids, w, counts = moe.route_fused(x, wr, k, softmax=softmax, bias=bias, renorm=True, softcap=0.0, scale=2.5)
+    logits = x.double() @ wr.double().t()
+    rid, rw, rc = moe.route(logits.float(), k, softmax=softmax, bias=bias, renorm=True, softcap=0.0, scale=2.5)
+    same = (ids.sort(1).values == rid.sort(1).values).all(1)
+    assert float(same.float().mean()) >= 0.95                      # a near-tie at the k-th place may resolve differently
+    rows = same.nonzero().flatten()
+    assert torch.allclose(w[rows].sort(1).values, rw[rows].sort(1).values, rtol=2e-3, atol=1e-5)
+    assert int(counts.sum()) == T * k and torch.equal(counts, torch.bincount(ids.flatten().long(), minlength=E).int())

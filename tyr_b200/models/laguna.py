@@ -344,6 +344,9 @@ def init(cfg: LagunaConfig, device="cpu", dtype=torch.float32, tie_word_embeddin
 # ---- blocks ------------------------------------------------------------------------------------------------------
 def route(cfg: LagunaConfig, r: Router, x2: torch.Tensor):
     """fp32 router logits -> (ids int32 [T,k], weights fp32 [T,k] including the routed scale, counts)."""
+    if moe_ops.route_fused_supported(x2, r.weight):
+        return moe_ops.route_fused(x2, r.weight, cfg.num_experts_per_tok, softmax=False, bias=r.e_score_correction_bias, renorm=cfg.norm_topk_prob,
+                                   softcap=cfg.moe_router_logit_softcapping, scale=cfg.moe_routed_scaling_factor)
     logits = F.linear(x2.float(), r.weight.float())
     return moe_ops.route(logits, cfg.num_experts_per_tok, softmax=False, bias=r.e_score_correction_bias,
                          renorm=cfg.norm_topk_prob, softcap=cfg.moe_router_logit_softcapping,

@@ -28,6 +28,7 @@ def _sigs(lib_):
     table = {
         "tyr_nvfp4_quantize": [P, P, P, P, L, L, P], "tyr_nvfp4_dequant": [P, P, P, P, L, L, P],
         "tyr_moe_route": [P, P, P, P, P, I, I, I, I, I, F, F, P],
+        "tyr_moe_route_fused": [P, P, P, P, P, P, I, I, I, I, I, I, F, F, P],
         "tyr_moe_layout": [P, P, P, P, P, P, P, P, I, I, P],
         "tyr_moe_gather_rows": [P, P, P, I, I, I, P], "tyr_moe_combine": [P, P, P, P, P, I, I, I, P],
         "tyr_moe_fp4_gemv": [P] * 17 + [I, I, I, I, I, P], "tyr_moe_finalize": [P, P, P, L, P],
@@ -133,6 +134,30 @@ def route(logits: torch.Tensor, k: int, *, softmax: bool = False, bias: Optional
     ids = order.to(torch.int32)
     counts = torch.bincount(ids.reshape(-1).long(), minlength=E).to(torch.int32)
     return ids, w * scale, counts
+
+
+ROUTE_FUSED_MAX_TOKENS = 256
+
+
+def route_fused_supported(x: torch.Tensor, router_w: torch.Tensor) -> bool:
+    """Decode-sized bf16 batches with an fp32 router: logits and routing in one launch."""
+    return (x.is_cuda and x.dtype == torch.bfloat16 and router_w.dtype == torch.float32 and x.dim() == 2 and x.shape[0] <= ROUTE_FUSED_MAX_TOKENS
+            and x.shape[1] % 8 == 0 and router_w.shape[0] <= 512 and 4 * (x.shape[1] + router_w.shape[0]) <= 96 * 1024
+            and x.is_contiguous() and router_w.is_contiguous() and hasattr(lib(), "tyr_moe_route_fused"))
+
+
+def route_fused(x: torch.Tensor, router_w: torch.Tensor, k: int, *, softmax: bool = False, bias: Optional[torch.Tensor] = None,
+                renorm: bool = True, softcap: float = 0.0, scale: float = 1.0):
+    """x bf16 [T, h], router_w fp32 [E, h] -> (ids, weights, counts) as :func:`route` of ``x.float() @ router_w.T`` (fp32
+    accumulation inside the kernel; the logits are never written out)."""
+    T, E = x.shape[0], router_w.shape[0]
+    ids = torch.empty((T, k), dtype=torch.int32, device=x.device)
+    w = torch.empty((T, k), dtype=torch.float32, device=x.device)
+    counts = torch.zeros(E, dtype=torch.int32, device=x.device)
+    b = bias.float().contiguous() if bias is not None else None
+    check(lib().tyr_moe_route_fused(ptr(x), ptr(router_w), ptr(b), ptr(ids), ptr(w), ptr(counts), T, E, k, x.shape[1], 1 if softmax else 0,
+                                    1 if renorm else 0, softcap, scale, cur_stream(x.device)), "moe_route_fused")
+    return ids, w, counts
 
 
 def layout(ids: torch.Tensor, counts: torch.Tensor, want_tiles: bool = False, want_active: bool = False):
