@@ -116,15 +116,16 @@ struct RouteArgs {
   float softcap, scale;
 };
 
-// One warp routes one token from its row of logits (global or shared memory).
-__device__ __forceinline__ void route_token(const RouteArgs& a, const float* __restrict__ row, int tok, int lane) {
+// One warp routes one token from its row of logits.  The row may have been written by other CTAs of the same launch, so it is
+// read with L2-coherent loads.
+__device__ __forceinline__ void route_token(const RouteArgs& a, const float* row, int tok, int lane) {
   constexpr int kMaxPer = 16;   // E <= 512
   float score[kMaxPer], sel[kMaxPer];
   const int per = (a.E + 31) / 32;
   float mx = -INFINITY;
   for (int j = 0; j < kMaxPer; ++j) {
     const int e = lane + 32 * j;
-    float l = (j < per && e < a.E) ? row[e] : -INFINITY;
+    float l = (j < per && e < a.E) ? __ldcg(row + e) : -INFINITY;
     if (a.softcap > 0.f && l != -INFINITY) l = a.softcap * tanhf(l / a.softcap);
     score[j] = l;
     mx = fmaxf(mx, l);
@@ -188,40 +189,55 @@ __global__ void __launch_bounds__(256) moe_route_kernel(RouteArgs a) {
   route_token(a, a.logits + static_cast<long long>(tok) * a.E, tok, lane);
 }
 
-// Decode-sized batches: one CTA per token computes the fp32 router logits itself (bf16 activations, fp32 router
-// weight, fp32 accumulation; warp w takes experts w, w + 8, ...) into shared memory and warp 0 routes from there, so the
-// logits never go through global memory and no separate cast / GEMM launches precede the routing.
+// Decode-sized batches: router logits and routing in one launch.  CTA (token group, expert group) takes kRouteTok
+// tokens and 8 experts (one per warp): each warp streams its expert's fp32 weight row once and dots it with the
+// group's bf16 activation rows staged in shared memory (fp32 accumulation), so the router matrix is read once per
+// token group.  Logits go to a small global scratch; the last CTA of a token group to finish (atomic ticket) routes the
+// group's tokens, one warp per token.  `tickets` holds one zeroed counter per token group.
+constexpr int kRouteTok = 8;
+
 __global__ void __launch_bounds__(256) moe_route_fused_kernel(RouteArgs a, const __nv_bfloat16* __restrict__ x,
-                                                              const float* __restrict__ wr, int h) {
-  extern __shared__ __align__(16) float route_smem[];
-  float* xs = route_smem;          // [h]
-  float* lg = route_smem + h;      // [E]
-  const int tok = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const __nv_bfloat16* xr = x + static_cast<long long>(tok) * h;
-  for (int i = threadIdx.x * 8; i < h; i += blockDim.x * 8) {
-    const uint4 u = *reinterpret_cast<const uint4*>(xr + i);
-    const float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y), f2 = unpack_bf16x2(u.z), f3 = unpack_bf16x2(u.w);
-    *reinterpret_cast<float4*>(xs + i) = make_float4(f0.x, f0.y, f1.x, f1.y);
-    *reinterpret_cast<float4*>(xs + i + 4) = make_float4(f2.x, f2.y, f3.x, f3.y);
-  }
+                                                              const float* __restrict__ wr, float* __restrict__ logits,
+                                                              int* __restrict__ tickets, int h) {
+  extern __shared__ __align__(16) uint8_t route_smem[];
+  __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(route_smem);     // [kRouteTok][h]
+  __shared__ int s_last;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tok0 = blockIdx.x * kRouteTok;
+  const int nt = min(kRouteTok, a.T - tok0);
+  for (int i = threadIdx.x * 8; i < nt * h; i += blockDim.x * 8)
+    *reinterpret_cast<uint4*>(xs + i) = *reinterpret_cast<const uint4*>(x + static_cast<long long>(tok0) * h + i);
   __syncthreads();
-  for (int e = warp; e < a.E; e += 8) {
+  const int e = blockIdx.y * 8 + warp;
+  if (e < a.E) {
+    float acc[kRouteTok];
+#pragma unroll
+    for (int t = 0; t < kRouteTok; ++t) acc[t] = 0.f;
     const float4* w4 = reinterpret_cast<const float4*>(wr + static_cast<long long>(e) * h);
-    const float4* x4 = reinterpret_cast<const float4*>(xs);
-    float acc0 = 0.f, acc1 = 0.f;
-    for (int i = lane; i < (h >> 2); i += 64) {
-      const float4 w0 = __ldg(w4 + i), v0 = x4[i];
-      acc0 += w0.x * v0.x + w0.y * v0.y + w0.z * v0.z + w0.w * v0.w;
-      if (i + 32 < (h >> 2)) {
-        const float4 w1 = __ldg(w4 + i + 32), v1 = x4[i + 32];
-        acc1 += w1.x * v1.x + w1.y * v1.y + w1.z * v1.z + w1.w * v1.w;
+    for (int i = lane; i < (h >> 2); i += 32) {
+      const float4 w = __ldg(w4 + i);
+#pragma unroll
+      for (int t = 0; t < kRouteTok; ++t) {
+        if (t < nt) {
+          const uint2 u = *reinterpret_cast<const uint2*>(xs + t * h + 4 * i);
+          const float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y);
+          acc[t] += w.x * f0.x + w.y * f0.y + w.z * f1.x + w.w * f1.y;
+        }
       }
     }
-    const float acc = warp_sum(acc0 + acc1);
-    if (lane == 0) lg[e] = acc;
+#pragma unroll
+    for (int t = 0; t < kRouteTok; ++t) {
+      const float v = warp_sum(acc[t]);
+      if (lane == 0 && t < nt) logits[static_cast<long long>(tok0 + t) * a.E + e] = v;
+    }
   }
+  __threadfence();
   __syncthreads();
-  if (warp == 0) route_token(a, lg, tok, lane);
+  if (threadIdx.x == 0) s_last = (atomicAdd(tickets + blockIdx.x, 1) == static_cast<int>(gridDim.y) - 1);
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  if (warp < nt) route_token(a, logits + static_cast<long long>(tok0 + warp) * a.E, tok0 + warp, lane);
 }
 
 // offsets[E+1] from counts[E]; cursors[E] zeroed; tiles[E+1] (nullable) = prefix sum of
@@ -588,21 +604,24 @@ extern "C" TYR_EXPORT int tyr_moe_route(const float* logits, const float* bias, 
   return (int)cudaGetLastError();
 }
 
-// Router GEMV + routing in one launch: x bf16 [T, h] (h a multiple of 8), router weight fp32 [E, h].
-extern "C" TYR_EXPORT int tyr_moe_route_fused(const void* x, const float* router_w, const float* bias, int* ids,
-                                              float* weights, int* counts, int T, int E, int k, int h, int softmax,
-                                              int renorm, float softcap, float scale, void* stream) {
+// Router GEMV + routing in one launch: x bf16 [T, h] (h a multiple of 8), router weight fp32 [E, h], `logits` a scratch of
+// T * E floats, `tickets` ceil(T / 8) zeroed ints.
+extern "C" TYR_EXPORT int tyr_moe_route_fused(const void* x, const float* router_w, const float* bias, float* logits,
+                                              int* tickets, int* ids, float* weights, int* counts, int T, int E, int k,
+                                              int h, int softmax, int renorm, float softcap, float scale, void* stream) {
   if (T <= 0 || E <= 0 || E > 512 || k <= 0 || k > 32 || k > E || h <= 0 || (h & 7)) return -1;
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(router_w)) & 15) return -2;
-  const size_t smem = sizeof(float) * (static_cast<size_t>(h) + E);
-  if (smem > 96 * 1024) return -3;
+  const size_t smem = sizeof(__nv_bfloat16) * static_cast<size_t>(h) * kRouteTok;
+  if (smem > 160 * 1024) return -3;
   static size_t configured = 0;
   if (smem > 48 * 1024 && configured < smem) {
     cudaFuncSetAttribute(moe_route_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     configured = smem;
   }
   RouteArgs a{nullptr, bias, ids, weights, counts, T, E, k, softmax, renorm, softcap, scale};
-  moe_route_fused_kernel<<<T, 256, smem, (cudaStream_t)stream>>>(a, (const __nv_bfloat16*)x, router_w, h);
+  dim3 grid((T + kRouteTok - 1) / kRouteTok, (E + 7) / 8);
+  moe_route_fused_kernel<<<grid, 256, smem, (cudaStream_t)stream>>>(a, (const __nv_bfloat16*)x, router_w, logits,
+                                                                    tickets, h);
   return (int)cudaGetLastError();
 }
 

@@ -9,6 +9,7 @@ The eager paths ``moe_eager`` (per-expert loop) is the CPU oracle.
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import Dict, Optional, Tuple
 
@@ -28,7 +29,7 @@ def _sigs(lib_):
     table = {
         "tyr_nvfp4_quantize": [P, P, P, P, L, L, P], "tyr_nvfp4_dequant": [P, P, P, P, L, L, P],
         "tyr_moe_route": [P, P, P, P, P, I, I, I, I, I, F, F, P],
-        "tyr_moe_route_fused": [P, P, P, P, P, P, I, I, I, I, I, I, F, F, P],
+        "tyr_moe_route_fused": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, F, P],
         "tyr_moe_layout": [P, P, P, P, P, P, P, P, I, I, P],
         "tyr_moe_gather_rows": [P, P, P, I, I, I, P], "tyr_moe_combine": [P, P, P, P, P, I, I, I, P],
         "tyr_moe_fp4_gemv": [P] * 17 + [I, I, I, I, I, P], "tyr_moe_finalize": [P, P, P, L, P],
@@ -137,12 +138,13 @@ def route(logits: torch.Tensor, k: int, *, softmax: bool = False, bias: Optional
 
 
 ROUTE_FUSED_MAX_TOKENS = 256
+_ROUTE_FUSED = os.environ.get("TYR_ROUTE_FUSED", "1") != "0"
 
 
 def route_fused_supported(x: torch.Tensor, router_w: torch.Tensor) -> bool:
     """Decode-sized bf16 batches with an fp32 router: logits and routing in one launch."""
-    return (x.is_cuda and x.dtype == torch.bfloat16 and router_w.dtype == torch.float32 and x.dim() == 2 and x.shape[0] <= ROUTE_FUSED_MAX_TOKENS
-            and x.shape[1] % 8 == 0 and router_w.shape[0] <= 512 and 4 * (x.shape[1] + router_w.shape[0]) <= 96 * 1024
+    return (_ROUTE_FUSED and x.is_cuda and x.dtype == torch.bfloat16 and router_w.dtype == torch.float32 and x.dim() == 2
+            and x.shape[0] <= ROUTE_FUSED_MAX_TOKENS and x.shape[1] % 8 == 0 and router_w.shape[0] <= 512 and 16 * x.shape[1] <= 160 * 1024
             and x.is_contiguous() and router_w.is_contiguous() and hasattr(lib(), "tyr_moe_route_fused"))
 
 
@@ -153,9 +155,11 @@ def route_fused(x: torch.Tensor, router_w: torch.Tensor, k: int, *, softmax: boo
     T, E = x.shape[0], router_w.shape[0]
     ids = torch.empty((T, k), dtype=torch.int32, device=x.device)
     w = torch.empty((T, k), dtype=torch.float32, device=x.device)
-    counts = torch.zeros(E, dtype=torch.int32, device=x.device)
+    zeros = torch.zeros(E + (T + 7) // 8, dtype=torch.int32, device=x.device)       # expert counts, then one ticket per token group
+    counts, tickets = zeros[:E], zeros[E:]
+    logits = torch.empty((T, E), dtype=torch.float32, device=x.device)
     b = bias.float().contiguous() if bias is not None else None
-    check(lib().tyr_moe_route_fused(ptr(x), ptr(router_w), ptr(b), ptr(ids), ptr(w), ptr(counts), T, E, k, x.shape[1], 1 if softmax else 0,
+    check(lib().tyr_moe_route_fused(ptr(x), ptr(router_w), ptr(b), ptr(logits), ptr(tickets), ptr(ids), ptr(w), ptr(counts), T, E, k, x.shape[1], 1 if softmax else 0,
                                     1 if renorm else 0, softcap, scale, cur_stream(x.device)), "moe_route_fused")
     return ids, w, counts
 
