@@ -9,19 +9,20 @@
 //   S^T  = K Q_i^T                 (SS)      TMEM columns   0..127
 //   dP^T = V dO_i^T                (SS)      TMEM columns 256..383
 //   P^T  = exp2(S^T * c - lse_i)             bf16, packed over the S^T columns it came from
-//   dS^T = P^T o (dP^T - delta_i)            bf16 -> shared memory, [keys][query rows], 128B swizzle
+//   dS^T = P^T o (dP^T - delta_i)            bf16 -> shared memory, [keys][query rows], 128B swizzle, K-major A of dK
 //   dV  += P^T dO_i                (TS)      TMEM columns 128..255
 //   dK  += dS^T Q_i                (SS)      TMEM columns 384..511
-//   dQ_i = dS K                    (SS, both operands MN-major)  TMEM columns 256..383 (over dP^T)
 //
-// dQ_i is drained by its own warpgroup with vector fp32 reductions into a [B, Hq, Tpad, 128] fp32
-// accumulator (several key blocks add into the same rows); a small kernel before this one computes
-// delta = rowsum(dO o O), rescales the log-sum-exp to base 2 and zeroes the accumulator, and one
-// after it scales and converts dQ to bf16.
+// dQ comes from a second kernel with the loops the other way round (one CTA per 128-row query block, walking the key
+// blocks): S = Q_i K_j^T and dP = dO_i V_j^T are recomputed, dS goes to shared memory and dQ_i += dS K_j accumulates in
+// TMEM, so no partial dQ tile ever leaves the SM.  Seven products per (query block, key block) pair instead of five, but
+// the first version, which reduced the dQ tiles of all key blocks into an fp32 accumulator with vector atomics, was bound by
+// the L2 atomic rate (about 1.5 TB/s) at less than a quarter of the tensor throughput.  A small kernel before the two computes
+// delta = rowsum(dO o O) and rescales the log-sum-exp to base 2 into padded rows.
 //
+// dK / dV kernel:
 //   warps 0-3   scores: query-row columns  0..63  of the block (one thread per key / TMEM lane)
 //   warps 4-7   scores: query-row columns 64..127
-//   warps 8-11  dQ drain
 //   warp 12     MMA issuer, warp 13 TMA producer (Q_i, dO_i, lse_i, delta_i into a 2-stage ring)
 //
 // Masks are those of the forward kernel: causal with offset, sliding window, key length.  Query rows
@@ -45,10 +46,10 @@ struct BwdParams {
   float scale, scale_log2;
   const float* lse2;      // [B, Hq, Tpad], base-2, +inf on padded / empty rows
   const float* delta;     // [B, Hq, Tpad]
-  float* dq_acc;          // [B, Hq, Tpad, 128] fp32, zeroed
   __nv_bfloat16* dK;
   __nv_bfloat16* dV;
-  long long dk_sb, dk_st, dk_sh, dv_sb, dv_st, dv_sh;
+  __nv_bfloat16* dQ;
+  long long dk_sb, dk_st, dk_sh, dv_sb, dv_st, dv_sh, dq_sb, dq_st, dq_sh;
   int* err;
 };
 
@@ -64,7 +65,7 @@ struct __align__(1024) BwdSmem {
   uint64_t q_full[2];      // Q_i + lse_i
   uint64_t do_full[2];     // dO_i + delta_i
   uint64_t qdo_empty[2];
-  uint64_t s_ready, dp_ready, p_ready, ds_ready, dq_ready, dq_free, acc_done;
+  uint64_t s_ready, dp_ready, p_ready, ds_ready, ds_free, acc_done;
   uint32_t tmem_base;
 };
 
@@ -76,10 +77,6 @@ __device__ __forceinline__ void bulk_load_1d(void* dst, const void* src, uint32_
                "l"(src), "r"(bytes), "r"(smem_u32(bar))
                : "memory");
 }
-__device__ __forceinline__ void red_add_v4(float* dst, float a, float b, float c, float d) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
-}
-
 // Query blocks [lo, hi) that see at least one key of block j.
 __device__ __forceinline__ void q_range(const BwdParams& p, int j, int& lo, int& hi) {
   const int nq = (p.Tq + BW_T - 1) / BW_T;
@@ -126,8 +123,7 @@ flash_bwd_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     mbar_init(&s.dp_ready, 1);
     mbar_init(&s.p_ready, 256);
     mbar_init(&s.ds_ready, 256);
-    mbar_init(&s.dq_ready, 1);
-    mbar_init(&s.dq_free, 128);
+    mbar_init(&s.ds_free, 1);
     mbar_init(&s.acc_done, 1);
     mbar_fence_init();
   }
@@ -139,7 +135,7 @@ flash_bwd_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = s.tmem_base;
-  constexpr uint32_t COL_S = 0, COL_DV = 128, COL_DPQ = 256, COL_DK = 384;
+  constexpr uint32_t COL_S = 0, COL_DV = 128, COL_DP = 256, COL_DK = 384;
 
   if (warp >= 12) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
@@ -186,7 +182,6 @@ flash_bwd_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       if (elect_one() && n_it > 0) {
         constexpr uint32_t idesc_kk = make_idesc_f16(1, BW_T, BW_T, 0, 0);   // both operands K-major
         constexpr uint32_t idesc_kn = make_idesc_f16(1, BW_T, BW_T, 0, 1);   // B MN-major
-        constexpr uint32_t idesc_nn = make_idesc_f16(1, BW_T, BW_T, 1, 1);   // A and B MN-major
         const uint32_t ka = smem_u32(s.k), va = smem_u32(s.v), dsa = smem_u32(s.ds);
         // D = A[128 x 128, K-major] * B[128 x 128, K-major]^T
         auto mma_kk = [&](uint32_t d_col, uint32_t a, uint32_t b) {
@@ -207,7 +202,7 @@ flash_bwd_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         }
         if (ok) {
           tc_fence_after();
-          mma_kk(COL_DPQ, va, smem_u32(s.dout[0]));
+          mma_kk(COL_DP, va, smem_u32(s.dout[0]));
           umma_commit(&s.dp_ready);
         }
         for (int it = 0; it < n_it && ok; ++it) {
@@ -232,54 +227,27 @@ flash_bwd_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           }
           if (!mbar_wait(&s.ds_ready, par, p.err, 832)) { ok = false; break; }
           tc_fence_after();
+          // dP^T of the next block first (the score warps are done with this one), then
           // dK += dS^T Q_i : A = dS^T [keys][rows] K-major, B = Q_i [rows][d] MN-major
+          if (it + 1 < n_it) {
+            const int sn = (it + 1) & 1;
+            if (!mbar_wait(&s.do_full[sn], ((it + 1) >> 1) & 1, p.err, 833)) { ok = false; break; }
+            tc_fence_after();
+            mma_kk(COL_DP, va, smem_u32(s.dout[sn]));
+            umma_commit(&s.dp_ready);
+          }
 #pragma unroll
           for (int k = 0; k < BW_T / 16; ++k)
             umma_f16_ss(tmem_base + COL_DK, make_smem_desc_sw128(dsa + (k >> 2) * BW_CHUNK + (k & 3) * 32, 16, 1024),
                         make_smem_desc_sw128(qa + k * 2048, BW_CHUNK, 1024), idesc_kn, (it == 0 && k == 0) ? 0u : 1u);
-          // dQ_i = dS K : A = dS read MN-major out of the same buffer, B = K [keys][d] MN-major
-#pragma unroll
-          for (int k = 0; k < BW_T / 16; ++k)
-            umma_f16_ss(tmem_base + COL_DPQ, make_smem_desc_sw128(dsa + k * 2048, BW_CHUNK, 1024),
-                        make_smem_desc_sw128(ka + k * 2048, BW_CHUNK, 1024), idesc_nn, k > 0 ? 1u : 0u);
-          umma_commit(&s.dq_ready);
+          umma_commit(&s.ds_free);
           umma_commit(&s.qdo_empty[st]);
-          if (it + 1 < n_it) {
-            const int sn = (it + 1) & 1;
-            if (!mbar_wait(&s.do_full[sn], ((it + 1) >> 1) & 1, p.err, 833)) { ok = false; break; }
-            if (!mbar_wait(&s.dq_free, par, p.err, 834)) { ok = false; break; }
-            tc_fence_after();
-            mma_kk(COL_DPQ, va, smem_u32(s.dout[sn]));
-            umma_commit(&s.dp_ready);
-          }
         }
         if (ok) umma_commit(&s.acc_done);
       }
     }
   } else if (warp >= 8) {
-    // ------------------------------------------------------------------ dQ drain
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 96;");
-    const int lrow = (warp & 3) * 32 + lane;
-    const uint32_t addr = tmem_base + COL_DPQ + (static_cast<uint32_t>((warp & 3) * 32) << 16);
-    for (int it = 0; it < n_it; ++it) {
-      const int head = kvh * G + it / ni;
-      const int i = ilo + it % ni;
-      if (!mbar_wait(&s.dq_ready, it & 1, p.err, 840)) break;
-      tc_fence_after();
-      float* dst = p.dq_acc + ((static_cast<long long>(batch) * p.Hq + head) * p.Tpad + i * BW_T + lrow) * BW_T;
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(addr + c * 32, r);
-        tmem_wait_ld();
-#pragma unroll
-        for (int q = 0; q < 8; ++q)
-          red_add_v4(dst + c * 32 + q * 4, __uint_as_float(r[q * 4]), __uint_as_float(r[q * 4 + 1]),
-                     __uint_as_float(r[q * 4 + 2]), __uint_as_float(r[q * 4 + 3]));
-      }
-      tc_fence_before();
-      mbar_arrive(&s.dq_free);
-    }
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 96;");      // idle warpgroup: hands its registers to the score warps
   } else {
     // ------------------------------------------------------------------ score warps
     asm volatile("setmaxnreg.inc.sync.aligned.u32 168;");
@@ -288,7 +256,7 @@ flash_bwd_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     const int key = j * BW_T + r;
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t s_addr = tmem_base + COL_S + wg * 64 + lane_addr;
-    const uint32_t dp_addr = tmem_base + COL_DPQ + wg * 64 + lane_addr;
+    const uint32_t dp_addr = tmem_base + COL_DP + wg * 64 + lane_addr;
     const int rmin = p.causal ? key - p.q_offset : INT_MIN;                 // rows that see this key: [rmin, rmax)
     const int rmax = p.window > 0 ? key - p.q_offset + p.window : INT_MAX;
     const bool key_ok = key < p.Tk;
@@ -348,7 +316,7 @@ flash_bwd_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       mbar_arrive(&s.p_ready);
       if (!mbar_wait(&s.do_full[st], ph, p.err, 852)) { ok = false; break; }
       if (!mbar_wait(&s.dp_ready, it & 1, p.err, 853)) { ok = false; break; }
-      if (it > 0 && !mbar_wait(&s.dq_ready, (it - 1) & 1, p.err, 854)) { ok = false; break; }   // dS buffer drained
+      if (it > 0 && !mbar_wait(&s.ds_free, (it - 1) & 1, p.err, 854)) { ok = false; break; }   // dK of the previous block has read dS
       tc_fence_after();
       const float4* d4 = reinterpret_cast<const float4*>(&s.delta[st][wg * 64]);
 #pragma unroll
@@ -415,11 +383,11 @@ flash_bwd_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   }
 }
 
-// One warp per (batch, head, padded row): delta = sum_d dO*O, lse in base 2 (+inf where the row is
-// padding or saw no key), and the row of the fp32 dQ accumulator cleared.
+// One warp per (batch, head, padded row): delta = sum_d dO*O and lse in base 2 (+inf where the row is
+// padding or saw no key).
 __global__ void flash_bwd_prepare_kernel(const __nv_bfloat16* __restrict__ dO, const __nv_bfloat16* __restrict__ O,
                                          const float* __restrict__ lse, float* __restrict__ lse2,
-                                         float* __restrict__ delta, float* __restrict__ dq_acc, int B, int H, int Tq,
+                                         float* __restrict__ delta, int B, int H, int Tq,
                                          int Tpad, long long do_sb, long long do_st, long long do_sh, long long o_sb,
                                          long long o_st, long long o_sh) {
   const long long w = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
@@ -429,7 +397,6 @@ __global__ void flash_bwd_prepare_kernel(const __nv_bfloat16* __restrict__ dO, c
   const int row = static_cast<int>(w % Tpad);
   const int h = static_cast<int>((w / Tpad) % H);
   const int b = static_cast<int>(w / (static_cast<long long>(Tpad) * H));
-  reinterpret_cast<float4*>(dq_acc + w * BW_T)[lane] = make_float4(0.f, 0.f, 0.f, 0.f);
   float acc = 0.f, l2 = INFINITY;
   if (row < Tq) {
     const uint2 a = *reinterpret_cast<const uint2*>(dO + b * do_sb + static_cast<long long>(row) * do_st + h * do_sh + lane * 4);
@@ -445,21 +412,268 @@ __global__ void flash_bwd_prepare_kernel(const __nv_bfloat16* __restrict__ dO, c
   }
 }
 
-// One warp per (batch, head, row): dQ = bf16(scale * accumulator).
-__global__ void flash_bwd_finish_kernel(const float* __restrict__ dq_acc, __nv_bfloat16* __restrict__ dQ, int B, int H,
-                                        int Tq, int Tpad, long long sb, long long st, long long sh, float scale) {
-  const long long w = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+// ------------------------------------------------------------------------------------------------------------------
+// dQ: one CTA per 128-row query block of one (batch, head).  Q_i and dO_i stay in shared memory, K_j / V_j stream through a
+// 2-stage ring; per key block:  S = Q_i K_j^T (TMEM columns 0..127), dP = dO_i V_j^T (128..255), the score warps turn them
+// into dS = P o (dP - delta) in shared memory ([rows][keys], K-major A), and dQ_i += dS K_j accumulates at columns 256..383.
+//   warps 0-3   scores: key columns 0..63 (one thread per query row / TMEM lane), warps 4-7: key columns 64..127
+//   warp 8      MMA issuer, warp 9 TMA producer
+// ------------------------------------------------------------------------------------------------------------------
+struct __align__(1024) DqSmem {
+  uint8_t q[BW_TILE];
+  uint8_t dout[BW_TILE];
+  uint8_t k[2][BW_TILE];
+  uint8_t v[2][BW_TILE];
+  uint8_t ds[BW_TILE];
+  uint64_t qdo_full;
+  uint64_t k_full[2], v_full[2], kv_empty[2];
+  uint64_t s_ready, dp_ready, ds_ready, ds_free, acc_done;
+  uint32_t tmem_base;
+};
+static_assert(sizeof(DqSmem) <= 227 * 1024, "dQ tiles exceed the shared memory of one CTA");
+
+// Key blocks [lo, hi) that the query rows [r0, r0 + 128) see.
+__device__ __forceinline__ void k_range(const BwdParams& p, int r0, int& lo, int& hi) {
+  int last_key = p.Tk - 1;
+  if (p.causal) last_key = min(last_key, r0 + BW_T - 1 + p.q_offset);
+  int first_key = 0;
+  if (p.window > 0) first_key = max(0, r0 + p.q_offset - p.window + 1);
+  lo = first_key / BW_T;
+  hi = last_key < 0 ? lo : last_key / BW_T + 1;
+  if (hi < lo) hi = lo;
+}
+
+__global__ void __launch_bounds__(320, 1)
+flash_bwd_dq_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                         const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO, BwdParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  DqSmem& s = *reinterpret_cast<DqSmem*>(smem_raw);
+  if ((smem_u32(smem_raw) & 1023u) != 0) {
+    if (threadIdx.x == 0) report_error(p.err, ERR_TMEM, 900);
+    return;
+  }
+  const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const long long total = static_cast<long long>(B) * H * Tq;
-  if (w >= total) return;
-  const int row = static_cast<int>(w % Tq);
-  const int h = static_cast<int>((w / Tq) % H);
-  const int b = static_cast<int>(w / (static_cast<long long>(Tq) * H));
-  const float4 v = reinterpret_cast<const float4*>(dq_acc + ((static_cast<long long>(b) * H + h) * Tpad + row) * BW_T)[lane];
-  uint2 u;
-  u.x = pack_bf16x2(v.x * scale, v.y * scale);
-  u.y = pack_bf16x2(v.z * scale, v.w * scale);
-  *reinterpret_cast<uint2*>(dQ + b * sb + static_cast<long long>(row) * st + h * sh + lane * 4) = u;
+  const int i = gridDim.x - 1 - blockIdx.x;      // late query blocks see the most keys: start them first
+  const int head = blockIdx.y;
+  const int batch = blockIdx.z;
+  const int kvh = head / (p.Hq / p.Hkv);
+  int jlo, jhi;
+  k_range(p, i * BW_T, jlo, jhi);
+  const int n_it = jhi - jlo;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&s.qdo_full, 1);
+    for (int q = 0; q < 2; ++q) {
+      mbar_init(&s.k_full[q], 1);
+      mbar_init(&s.v_full[q], 1);
+      mbar_init(&s.kv_empty[q], 1);
+    }
+    mbar_init(&s.s_ready, 1);
+    mbar_init(&s.dp_ready, 1);
+    mbar_init(&s.ds_ready, 256);
+    mbar_init(&s.ds_free, 1);
+    mbar_init(&s.acc_done, 1);
+    mbar_fence_init();
+  }
+  if (warp == 8) {
+    tmem_alloc(&s.tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = s.tmem_base;
+  constexpr uint32_t COL_S = 0, COL_DP = 128, COL_DQ = 256;
+
+  if (warp == 9) {
+    // ------------------------------------------------------------------ TMA producer
+    if (elect_one() && n_it > 0) {
+      tma_prefetch_desc(&tmQ);
+      tma_prefetch_desc(&tmK);
+      tma_prefetch_desc(&tmV);
+      tma_prefetch_desc(&tmDO);
+      mbar_expect_tx(&s.qdo_full, 2 * BW_TILE);
+      for (int c = 0; c < 2; ++c) {
+        tma_load_4d(s.q + c * BW_CHUNK, &tmQ, &s.qdo_full, c * 64, head, i * BW_T, batch);
+        tma_load_4d(s.dout + c * BW_CHUNK, &tmDO, &s.qdo_full, c * 64, head, i * BW_T, batch);
+      }
+      bool ok = true;
+      int it = 0;
+      for (; it < n_it; ++it) {
+        const int st = it & 1;
+        const uint32_t ph = (it >> 1) & 1;
+        if (!mbar_wait(&s.kv_empty[st], ph ^ 1, p.err, 910 + st)) { ok = false; break; }
+        mbar_expect_tx(&s.k_full[st], BW_TILE);
+        for (int c = 0; c < 2; ++c)
+          tma_load_4d(s.k[st] + c * BW_CHUNK, &tmK, &s.k_full[st], c * 64, kvh, (jlo + it) * BW_T, batch);
+        mbar_expect_tx(&s.v_full[st], BW_TILE);
+        for (int c = 0; c < 2; ++c)
+          tma_load_4d(s.v[st] + c * BW_CHUNK, &tmV, &s.v_full[st], c * 64, kvh, (jlo + it) * BW_T, batch);
+      }
+      if (!ok) {   // let the copies in flight land before the CTA unwinds
+        mbar_wait(&s.qdo_full, 0, nullptr, 0);
+        for (int q = max(0, it - 2); q < it; ++q) {
+          mbar_wait(&s.k_full[q & 1], (q >> 1) & 1, nullptr, 0);
+          mbar_wait(&s.v_full[q & 1], (q >> 1) & 1, nullptr, 0);
+        }
+      }
+    }
+  } else if (warp == 8) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (elect_one() && n_it > 0) {
+      constexpr uint32_t idesc_kk = make_idesc_f16(1, BW_T, BW_T, 0, 0);
+      constexpr uint32_t idesc_kn = make_idesc_f16(1, BW_T, BW_T, 0, 1);
+      const uint32_t qa = smem_u32(s.q), doa = smem_u32(s.dout), dsa = smem_u32(s.ds);
+      auto mma_kk = [&](uint32_t d_col, uint32_t a, uint32_t b) {
+#pragma unroll
+        for (int k = 0; k < BW_T / 16; ++k) {
+          const uint32_t off = (k >> 2) * BW_CHUNK + (k & 3) * 32;
+          umma_f16_ss(tmem_base + d_col, make_smem_desc_sw128(a + off, 16, 1024), make_smem_desc_sw128(b + off, 16, 1024),
+                      idesc_kk, k > 0 ? 1u : 0u);
+        }
+      };
+      bool ok = mbar_wait(&s.qdo_full, 0, p.err, 920);
+      ok = ok && mbar_wait(&s.k_full[0], 0, p.err, 921);
+      if (ok) {
+        tc_fence_after();
+        mma_kk(COL_S, qa, smem_u32(s.k[0]));
+        umma_commit(&s.s_ready);
+        ok = mbar_wait(&s.v_full[0], 0, p.err, 922);
+      }
+      if (ok) {
+        tc_fence_after();
+        mma_kk(COL_DP, doa, smem_u32(s.v[0]));
+        umma_commit(&s.dp_ready);
+      }
+      for (int it = 0; it < n_it && ok; ++it) {
+        const int st = it & 1;
+        // the score warps have read S_j and dP_j and written dS_j
+        if (!mbar_wait(&s.ds_ready, it & 1, p.err, 930)) { ok = false; break; }
+        tc_fence_after();
+        if (it + 1 < n_it) {
+          const int sn = (it + 1) & 1;
+          const uint32_t phn = ((it + 1) >> 1) & 1;
+          if (!mbar_wait(&s.k_full[sn], phn, p.err, 931)) { ok = false; break; }
+          tc_fence_after();
+          mma_kk(COL_S, qa, smem_u32(s.k[sn]));
+          umma_commit(&s.s_ready);
+          if (!mbar_wait(&s.v_full[sn], phn, p.err, 932)) { ok = false; break; }
+          tc_fence_after();
+          mma_kk(COL_DP, doa, smem_u32(s.v[sn]));
+          umma_commit(&s.dp_ready);
+        }
+        // dQ_i += dS K_j : A = dS [rows][keys] K-major, B = K_j [keys][d] MN-major
+        const uint32_t ka = smem_u32(s.k[st]);
+#pragma unroll
+        for (int k = 0; k < BW_T / 16; ++k)
+          umma_f16_ss(tmem_base + COL_DQ, make_smem_desc_sw128(dsa + (k >> 2) * BW_CHUNK + (k & 3) * 32, 16, 1024),
+                      make_smem_desc_sw128(ka + k * 2048, BW_CHUNK, 1024), idesc_kn, (it == 0 && k == 0) ? 0u : 1u);
+        umma_commit(&s.ds_free);
+        umma_commit(&s.kv_empty[st]);
+      }
+      if (ok) umma_commit(&s.acc_done);
+    }
+  } else {
+    // ------------------------------------------------------------------ score warps
+    const int wg = warp >> 2;
+    const int r = (warp & 3) * 32 + lane;                 // query row of this thread inside the block
+    const int row = i * BW_T + r;
+    const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t s_addr = tmem_base + COL_S + wg * 64 + lane_addr;
+    const uint32_t dp_addr = tmem_base + COL_DP + wg * 64 + lane_addr;
+    const long long stat = (static_cast<long long>(batch) * p.Hq + head) * p.Tpad + row;
+    const float lse2 = p.lse2[stat];                      // +inf on padded / empty rows: their probabilities are 0
+    const float delta = p.delta[stat];
+    const int kmin = p.window > 0 ? row + p.q_offset - p.window + 1 : INT_MIN;      // keys this row sees: [kmin, kmax]
+    const int kmax = min(p.Tk - 1, p.causal ? row + p.q_offset : INT_MAX);
+    uint8_t* ds_row = s.ds + wg * BW_CHUNK + r * 128;
+    bool ok = true;
+    for (int it = 0; it < n_it && ok; ++it) {
+      const int j = jlo + it;
+      const int key0 = j * BW_T + wg * 64;
+      if (!mbar_wait(&s.s_ready, it & 1, p.err, 950)) { ok = false; break; }
+      tc_fence_after();
+      float pr[64];
+      {
+        uint32_t t[64];
+        tmem_ld_32x32(s_addr, *reinterpret_cast<uint32_t(*)[32]>(t));
+        tmem_ld_32x32(s_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(t + 32));
+        tmem_wait_ld();
+        const bool full = (j * BW_T + BW_T <= p.Tk) && (!p.causal || j * BW_T + BW_T - 1 <= i * BW_T + p.q_offset) &&
+                          (p.window <= 0 || j * BW_T > i * BW_T + BW_T - 1 + p.q_offset - p.window);
+        if (full) {
+#pragma unroll
+          for (int c = 0; c < 64; ++c) pr[c] = exp2f(fmaf(__uint_as_float(t[c]), p.scale_log2, -lse2));
+        } else {
+#pragma unroll
+          for (int c = 0; c < 64; ++c) {
+            const int key = key0 + c;
+            pr[c] = (key >= kmin && key <= kmax) ? exp2f(fmaf(__uint_as_float(t[c]), p.scale_log2, -lse2)) : 0.f;
+          }
+        }
+      }
+      if (!mbar_wait(&s.dp_ready, it & 1, p.err, 951)) { ok = false; break; }
+      if (it > 0 && !mbar_wait(&s.ds_free, (it - 1) & 1, p.err, 952)) { ok = false; break; }   // dQ of the previous block has read dS
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t t[32];
+        tmem_ld_32x32(dp_addr + c * 32, t);
+        tmem_wait_ld();
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const float* pp = pr + c * 32 + u * 8;
+          uint4 w;
+          w.x = pack_bf16x2(pp[0] * (__uint_as_float(t[u * 8 + 0]) - delta), pp[1] * (__uint_as_float(t[u * 8 + 1]) - delta));
+          w.y = pack_bf16x2(pp[2] * (__uint_as_float(t[u * 8 + 2]) - delta), pp[3] * (__uint_as_float(t[u * 8 + 3]) - delta));
+          w.z = pack_bf16x2(pp[4] * (__uint_as_float(t[u * 8 + 4]) - delta), pp[5] * (__uint_as_float(t[u * 8 + 5]) - delta));
+          w.w = pack_bf16x2(pp[6] * (__uint_as_float(t[u * 8 + 6]) - delta), pp[7] * (__uint_as_float(t[u * 8 + 7]) - delta));
+          const int unit = c * 4 + u;
+          *reinterpret_cast<uint4*>(ds_row + ((unit ^ (r & 7)) << 4)) = w;
+        }
+      }
+      fence_proxy_async();
+      tc_fence_before();
+      mbar_arrive(&s.ds_ready);
+    }
+    // ---------------------------------------------------------------- dQ epilogue: each warpgroup writes 64 channels
+    if (ok && n_it > 0) ok = mbar_wait(&s.acc_done, 0, p.err, 960);
+    tc_fence_after();
+    if (ok) {
+      const uint32_t src = tmem_base + COL_DQ + wg * 64 + lane_addr;
+      __nv_bfloat16* out = p.dQ + batch * p.dq_sb + static_cast<long long>(row) * p.dq_st + head * p.dq_sh + wg * 64;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t o[32];
+        if (n_it > 0) {
+          tmem_ld_32x32(src + c * 32, o);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int q = 0; q < 32; ++q) o[q] = 0u;
+        }
+        if (row < p.Tq) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint4 u;
+            u.x = pack_bf16x2(__uint_as_float(o[q * 8 + 0]) * p.scale, __uint_as_float(o[q * 8 + 1]) * p.scale);
+            u.y = pack_bf16x2(__uint_as_float(o[q * 8 + 2]) * p.scale, __uint_as_float(o[q * 8 + 3]) * p.scale);
+            u.z = pack_bf16x2(__uint_as_float(o[q * 8 + 4]) * p.scale, __uint_as_float(o[q * 8 + 5]) * p.scale);
+            u.w = pack_bf16x2(__uint_as_float(o[q * 8 + 6]) * p.scale, __uint_as_float(o[q * 8 + 7]) * p.scale);
+            *reinterpret_cast<uint4*>(out + c * 32 + q * 8) = u;
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 8) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
 }
 
 }  // namespace tyr
@@ -498,10 +712,10 @@ int make_map(CUtensorMap* tm, const void* base, int B, int T, int H, long long s
 }
 }  // namespace
 
-// Bytes of scratch the backward needs: the fp32 dQ accumulator followed by the padded lse / delta rows.
+// Bytes of scratch the backward needs: the padded base-2 lse and delta rows.
 extern "C" TYR_EXPORT long long tyr_flash_bwd_workspace_bytes(int B, int Hq, int Tq) {
   const long long tpad = (Tq + BW_T - 1) / BW_T * BW_T;
-  return static_cast<long long>(B) * Hq * tpad * (BW_T + 2) * 4;
+  return static_cast<long long>(B) * Hq * tpad * 2 * 4;
 }
 
 // Every tensor is a [B, T, H, 128] view given by (batch, row, head) element strides; lse is the
@@ -527,8 +741,7 @@ extern "C" TYR_EXPORT int tyr_flash_bwd(const void* dout, const void* q, const v
   const long long* sdv = strides + 21;
   const int tpad = (Tq + BW_T - 1) / BW_T * BW_T;
   const long long rows = static_cast<long long>(B) * Hq * tpad;
-  float* acc = static_cast<float*>(workspace);
-  float* lse2 = acc + rows * BW_T;
+  float* lse2 = static_cast<float*>(workspace);
   float* delta = lse2 + rows;
   CUtensorMap tq, tk, tv, tdo;
   int r;
@@ -536,10 +749,12 @@ extern "C" TYR_EXPORT int tyr_flash_bwd(const void* dout, const void* q, const v
   if ((r = make_map(&tk, k, B, Tk, Hkv, sk[0], sk[1], sk[2]))) return 4000 + r;
   if ((r = make_map(&tv, v, B, Tk, Hkv, sv[0], sv[1], sv[2]))) return 5000 + r;
   if ((r = make_map(&tdo, dout, B, Tq, Hq, sdo[0], sdo[1], sdo[2]))) return 6000 + r;
-  constexpr size_t smem = sizeof(BwdSmem);
+  constexpr size_t smem = sizeof(BwdSmem), smem_dq = sizeof(DqSmem);
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(flash_bwd_d128_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(flash_bwd_dq_d128_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dq);
     if (e != cudaSuccess) return 1000 + (int)e;
     configured = true;
   }
@@ -547,25 +762,23 @@ extern "C" TYR_EXPORT int tyr_flash_bwd(const void* dout, const void* q, const v
   {
     const long long threads = rows * 32;
     flash_bwd_prepare_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, cs>>>(
-        (const __nv_bfloat16*)dout, (const __nv_bfloat16*)o, lse, lse2, delta, acc, B, Hq, Tq, tpad, sdo[0], sdo[1],
+        (const __nv_bfloat16*)dout, (const __nv_bfloat16*)o, lse, lse2, delta, B, Hq, Tq, tpad, sdo[0], sdo[1],
         sdo[2], so[0], so[1], so[2]);
   }
   BwdParams p;
   p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.Tq = Tq; p.Tk = Tk; p.Tpad = tpad;
   p.q_offset = q_offset; p.causal = causal; p.window = window;
   p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
-  p.lse2 = lse2; p.delta = delta; p.dq_acc = acc;
+  p.lse2 = lse2; p.delta = delta;
   p.dK = (__nv_bfloat16*)dk; p.dV = (__nv_bfloat16*)dv;
   p.dk_sb = sdk[0]; p.dk_st = sdk[1]; p.dk_sh = sdk[2];
   p.dv_sb = sdv[0]; p.dv_st = sdv[1]; p.dv_sh = sdv[2];
+  p.dQ = (__nv_bfloat16*)dq;
+  p.dq_sb = sdq[0]; p.dq_st = sdq[1]; p.dq_sh = sdq[2];
   p.err = err;
   dim3 grid((Tk + BW_T - 1) / BW_T, Hkv, B);
   flash_bwd_d128_kernel<<<grid, 512, smem, cs>>>(tq, tk, tv, tdo, p);
-  {
-    const long long threads = static_cast<long long>(B) * Hq * Tq * 32;
-    flash_bwd_finish_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, cs>>>(acc, (__nv_bfloat16*)dq, B, Hq, Tq, tpad,
-                                                                                sdq[0], sdq[1], sdq[2], scale);
-  }
+  flash_bwd_dq_d128_kernel<<<dim3((Tq + BW_T - 1) / BW_T, Hq, B), 320, smem_dq, cs>>>(tq, tk, tv, tdo, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 2000 + (int)e;
 }

@@ -280,13 +280,24 @@ __global__ void moe_offsets_kernel(const int* counts, int* offsets, int* cursors
 __global__ void moe_scatter_kernel(const int* ids, const int* offsets, int* cursors, int* pair_order,
                                    int* pair_pos, int pairs, int E) {
   for (int p = blockIdx.x * blockDim.x + threadIdx.x; p < pairs; p += gridDim.x * blockDim.x) {
-    int e = ids[p];
-    (void)TYR_INDEX_OK(e, E, 11);                    // checked builds record the first bad expert id; it is clamped either way
-    e = e < 0 ? 0 : (e >= E ? E - 1 : e);
+    const int e = ids[p];
+    if (e < 0 || e >= E) {                           // not routed (expert-parallel padding rows carry id E): takes no slot
+      (void)TYR_INDEX_OK(e, E + 1, 11);              // checked builds record ids beyond the padding marker
+      if (pair_pos) pair_pos[p] = 0;
+      continue;
+    }
     const int slot = atomicAdd(cursors + e, 1);
     const int pos = offsets[e] + slot;
     pair_order[pos] = p;
     if (pair_pos) pair_pos[p] = pos;
+  }
+}
+
+// counts[e] += number of pairs routed to expert e; ids outside [0, E) are not counted (counts zero on entry)
+__global__ void moe_count_kernel(const int* ids, int* counts, int pairs, int E) {
+  for (int p = blockIdx.x * blockDim.x + threadIdx.x; p < pairs; p += gridDim.x * blockDim.x) {
+    const int e = ids[p];
+    if (e >= 0 && e < E) atomicAdd(counts + e, 1);
   }
 }
 
@@ -351,8 +362,8 @@ moe_combine_kernel(const __nv_bfloat16* y, const int* pair_pos, const float* wei
 // is no operand reuse that shared-memory staging for tcgen05 could exploit.
 // ---------------------------------------------------------------------------------------------
 constexpr int kP = 8;            // pairs per pass (mma N)
-constexpr int kWarps = 4;        // warps per CTA
-constexpr int kRowsCta = 16 * kWarps;
+constexpr int kWarpsA = 8;       // warps per CTA, stage A (eight warps share one staged activation block: 3 CTAs x 8 warps per SM)
+constexpr int kWarpsB = 4;       // warps per CTA, stage B
 
 struct StageArgs {
   const __nv_bfloat16* x;      // stage A: [T, h] activations
@@ -432,7 +443,8 @@ __device__ __forceinline__ void tile_step(float (&c)[4], const uint4& wlo, const
 }
 
 template <bool STAGE_A>
-__global__ void __launch_bounds__(32 * kWarps) moe_fp4_gemv_kernel(StageArgs a) {
+__global__ void __launch_bounds__(32 * (STAGE_A ? kWarpsA : kWarpsB), STAGE_A ? 3 : 8) moe_fp4_gemv_kernel(StageArgs a) {
+  constexpr int kRowsCta = 16 * (STAGE_A ? kWarpsA : kWarpsB);
   extern __shared__ __align__(16) uint8_t smem_raw[];
   if (static_cast<int>(blockIdx.y) >= *a.n_active) return;
   const int e = a.active[blockIdx.y];
@@ -637,6 +649,12 @@ extern "C" TYR_EXPORT int tyr_moe_layout(const int* ids, const int* counts, int*
   return (int)cudaGetLastError();
 }
 
+extern "C" TYR_EXPORT int tyr_moe_count(const int* ids, int* counts, int pairs, int E, void* stream) {
+  if (pairs <= 0 || E <= 0) return -1;
+  moe_count_kernel<<<blocks_for(pairs), 256, 0, (cudaStream_t)stream>>>(ids, counts, pairs, E);
+  return (int)cudaGetLastError();
+}
+
 extern "C" TYR_EXPORT int tyr_moe_gather_rows(const void* src, const int* pair_order, void* dst, int pairs, int k,
                                               int h, void* stream) {
   if (pairs <= 0 || (h & 7)) return -1;
@@ -691,7 +709,7 @@ extern "C" TYR_EXPORT int tyr_moe_fp4_gemv(const void* x, const void* gate_p, co
   a.w1 = (const uint8_t*)up_p; a.s1 = (const uint8_t*)up_s; a.g1 = up_g;
   a.offsets = offsets; a.active = active; a.n_active = n_active; a.pair_order = pair_order; a.pair_weight = pair_weight;
   a.out_g = hid_g; a.out_u = hid_u; a.k = k; a.in_dim = h; a.out_dim = mi;
-  const int rows_a = (mi + kRowsCta - 1) / kRowsCta, rows_b = (h + kRowsCta - 1) / kRowsCta;
+  const int rows_a = (mi + 16 * kWarpsA - 1) / (16 * kWarpsA), rows_b = (h + 16 * kWarpsB - 1) / (16 * kWarpsB);
   const int za = pick_split(rows_a * slots, h >> 7, sm_count);
   const int zb = pick_split(rows_b * slots, mi >> 7, sm_count);
   const size_t smem_a = sizeof(unsigned short) * kP * (((h >> 7) + za - 1) / za * 128 + 8);
@@ -706,13 +724,13 @@ extern "C" TYR_EXPORT int tyr_moe_fp4_gemv(const void* x, const void* gate_p, co
     cudaFuncSetAttribute(moe_fp4_gemv_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_b);
     cfg_b = smem_b;
   }
-  moe_fp4_gemv_kernel<true><<<dim3(rows_a, slots, za), 32 * kWarps, smem_a, st>>>(a);
+  moe_fp4_gemv_kernel<true><<<dim3(rows_a, slots, za), 32 * kWarpsA, smem_a, st>>>(a);
   StageArgs b{};
   b.hid_g = hid_g; b.hid_u = hid_u; b.gg = gate_g; b.gu = up_g;
   b.w0 = (const uint8_t*)down_p; b.s0 = (const uint8_t*)down_s; b.g0 = down_g;
   b.offsets = offsets; b.active = active; b.n_active = n_active; b.pair_order = pair_order; b.pair_weight = pair_weight;
   b.out = routed; b.k = k; b.in_dim = mi; b.out_dim = h;
-  moe_fp4_gemv_kernel<false><<<dim3(rows_b, slots, zb), 32 * kWarps, smem_b, st>>>(b);
+  moe_fp4_gemv_kernel<false><<<dim3(rows_b, slots, zb), 32 * kWarpsB, smem_b, st>>>(b);
   return (int)cudaGetLastError();
 }
 

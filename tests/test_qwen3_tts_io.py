@@ -85,3 +85,29 @@ def test_checkpoint_roundtrip_and_identity_projection(tmp_path):
     del tensors["talker.codec_head.weight"]
     with pytest.raises(st.SafeTensorsError, match="codec_head"):
         IO.load_sharded(variant("no_head", tensors))
+
+
+def test_cli_text_to_codes_and_wav(tmp_path, capsys):
+    """run_tts qwen3tts: token ids -> codes file -> wav through a tiny speech decoder stored next to the model."""
+    from tyr_b200.cli import run_tts
+    from tyr_b200.models import qwen3_tts_bridge as B
+    cfg = IO.config_from_json(tiny_json())
+    m = T.init(cfg, seed=1)
+    d = tmp_path / "model"
+    (d / "speech_tokenizer").mkdir(parents=True)
+    json.dump(tiny_json(), open(d / "config.json", "w"))
+    st.save_file({k: v.contiguous() for k, v in IO.state_dict(m).items()}, str(d / "model.safetensors"))
+    ids = tmp_path / "ids.txt"
+    ids.write_text("3 5 7 9 11")
+    codes = tmp_path / "out" / "codes.txt"
+    rc = run_tts.main(["qwen3tts", "--model-dir", str(d), "--token-ids-path", str(ids), "--speaker", "vivian", "--max-frames", "5", "--codes-path", str(codes),
+                       "--skip-decode", "--device", "cpu", "--seed", "3"])
+    assert rc == 0 and B.parse_code_rows(codes.read_text()).shape[1] == 3
+    assert "saved_codes=" in capsys.readouterr().out
+    with pytest.raises(SystemExit):
+        run_tts.main(["qwen3tts", "--model-dir", str(d), "--encode-only"])
+    with pytest.raises(SystemExit, match="no speech_tokenizer"):
+        run_tts.main(["qwen3tts", "--model-dir", str(d), "--token-ids-path", str(ids), "--max-frames", "3", "--codes-path", str(codes), "--device", "cpu"])
+    with pytest.raises(ValueError, match="Unsupported speaker"):
+        run_tts.main(["qwen3tts", "--model-dir", str(d), "--token-ids-path", str(ids), "--speaker", "nobody", "--skip-decode", "--device", "cpu",
+                      "--codes-path", str(codes)])

@@ -59,6 +59,13 @@ def _run(cmd):
     return r.stdout + r.stderr
 
 
+def _link(cmd, out: Path):
+    """Links into a sibling temporary file and renames it over ``out``, so a reader never sees a half-written library."""
+    tmp = out.with_name(out.name + ".tmp")
+    _run([*cmd, "-o", str(tmp)])
+    os.replace(tmp, out)
+
+
 CHECKED_UNITS = ("moe_nvfp4", "rope")       # translation units with index checks; the checked library holds only these
 
 
@@ -99,7 +106,7 @@ def build_kernels(verbose: bool = False, force: bool = False, checked: bool = Fa
                 if verbose and log.strip():
                     print("[%s]\n%s" % (name, log))
     if jobs or not out.exists():
-        _run([nvcc, "-shared", "-o", str(out), *map(str, objs), "-lcudart"])
+        _link([nvcc, "-shared", *map(str, objs), "-lcudart"], out)
     return out
 
 
@@ -113,7 +120,7 @@ def build_host(force: bool = False) -> Path:
     if not force and out.exists() and stamp.exists() and stamp.read_text() == dig:
         return out
     cxx = shutil.which("g++") or "g++"
-    _run([cxx, *CXX_FLAGS, "-shared", "-o", str(out), *map(str, srcs), "-ldl"])
+    _link([cxx, *CXX_FLAGS, "-shared", *map(str, srcs), "-ldl"], out)
     stamp.write_text(dig)
     return out
 
@@ -139,8 +146,8 @@ def build_parquet(force: bool = False):
     if not force and out.exists() and stamp.exists() and stamp.read_text() == dig:
         return out
     cxx = shutil.which("g++") or "g++"
-    _run([cxx, *flags, "-shared", "-I", pa.get_include(), "-o", str(out), *map(str, srcs), "-L", str(libdir),
-          "-l:" + parquet[0].name, "-l:" + arrow[0].name, "-Wl,-rpath," + str(libdir)])
+    _link([cxx, *flags, "-shared", "-I", pa.get_include(), *map(str, srcs), "-L", str(libdir),
+           "-l:" + parquet[0].name, "-l:" + arrow[0].name, "-Wl,-rpath," + str(libdir)], out)
     stamp.write_text(dig)
     return out
 

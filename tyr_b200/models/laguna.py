@@ -502,14 +502,18 @@ class CacheSession:
     # -- decode with the position on the device --------------------------------------------------------------------
     def device_step_supported(self) -> bool:
         cfg, m = self.m.cfg, self.m
-        if m.ep is not None or not m.embed_tokens.is_cuda or m.dtype != torch.bfloat16 or os.environ.get("TYR_DECODE_GRAPH", "1") == "0":
+        if not m.embed_tokens.is_cuda or m.dtype != torch.bfloat16 or os.environ.get("TYR_DECODE_GRAPH", "1") == "0":
             return False
+        if m.ep is not None and not (m.ep.fused and self.batch * cfg.num_experts_per_tok * m.ep.world <= 4096):
+            return False          # the collective fallback and the row-count read-back of large batches need the host
         return all(da.geometry_supported(cfg.heads(i), cfg.num_key_value_heads, cfg.head_dim) for i in range(cfg.num_hidden_layers))
 
     def _device_step(self, tokens: torch.Tensor, use_fused: bool = True) -> torch.Tensor:
         """One decode step whose only position input is ``self.pos_t``; advances ``pos_t`` (graph body)."""
         cfg = self.m.cfg
         x = F.embedding(tokens.reshape(self.batch, 1), self.m.embed_tokens)
+        if self.m.ep is not None and len(self.m.layers) % 2:
+            self.m.ep._sync(0)    # odd depth: the first layer of a replay reuses the exchange buffers of the last layer before it
         for i, layer in enumerate(self.m.layers):
             x = layer_decode(cfg, i, layer, x, self.tables, self.pos_t, self.caches[i], use_fused, self.m.ep)
         logits = lin(norm_w(x, self.m.norm, cfg.rms_norm_eps)[:, -1], self.m.lm_head)

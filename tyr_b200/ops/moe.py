@@ -30,7 +30,7 @@ def _sigs(lib_):
         "tyr_nvfp4_quantize": [P, P, P, P, L, L, P], "tyr_nvfp4_dequant": [P, P, P, P, L, L, P],
         "tyr_moe_route": [P, P, P, P, P, I, I, I, I, I, F, F, P],
         "tyr_moe_route_fused": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, F, P],
-        "tyr_moe_layout": [P, P, P, P, P, P, P, P, I, I, P],
+        "tyr_moe_layout": [P, P, P, P, P, P, P, P, I, I, P], "tyr_moe_count": [P, P, I, I, P],
         "tyr_moe_gather_rows": [P, P, P, I, I, I, P], "tyr_moe_combine": [P, P, P, P, P, I, I, I, P],
         "tyr_moe_fp4_gemv": [P] * 17 + [I, I, I, I, I, P], "tyr_moe_finalize": [P, P, P, L, P],
     }
@@ -135,6 +135,18 @@ def route(logits: torch.Tensor, k: int, *, softmax: bool = False, bias: Optional
     ids = order.to(torch.int32)
     counts = torch.bincount(ids.reshape(-1).long(), minlength=E).to(torch.int32)
     return ids, w * scale, counts
+
+
+def count_experts(ids: torch.Tensor, E: int) -> torch.Tensor:
+    """int32 [E] histogram of the expert ids; ids outside [0, E) (padding rows) are not counted.  No host synchronisation on CUDA."""
+    flat = ids.reshape(-1)
+    if not ids.is_cuda:
+        flat = flat.long()
+        return torch.bincount(flat[(flat >= 0) & (flat < E)], minlength=E).to(torch.int32)
+    counts = torch.zeros(E, dtype=torch.int32, device=ids.device)
+    flat = flat.to(torch.int32).contiguous()
+    check(lib().tyr_moe_count(ptr(flat), ptr(counts), flat.numel(), E, cur_stream(ids.device)), "moe_count")
+    return counts
 
 
 ROUTE_FUSED_MAX_TOKENS = 256
@@ -300,7 +312,7 @@ def moe_fp4_forward(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, e
         y = moe_eager(x, ids, weights, g, u, d)
         return y + add if add is not None else y
     if counts is None:
-        counts = torch.bincount(ids.reshape(-1).long(), minlength=E).to(torch.int32)
+        counts = count_experts(ids, E)
     offsets, order, pos, tiles, active = layout(ids.to(torch.int32), counts, want_active=True)
     wf = weights.float().contiguous()
     path = force_path or ("gemv" if T * k <= GEMV_MAX_PAIRS_PER_EXPERT * E else "gemm")
@@ -369,7 +381,7 @@ def moe_dense_forward(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
         y = moe_eager(x, ids, weights, gate_up[:, :mi], gate_up[:, mi:], down)
         return y if add is None else (y.float() + add.float()).to(x.dtype)
     if counts is None:
-        counts = torch.bincount(ids.reshape(-1).long(), minlength=E).to(torch.int32)
+        counts = count_experts(ids, E)
     offsets, order, pos, tiles = layout(ids.to(torch.int32), counts, want_tiles=True)
     st = cur_stream(x.device)
     gu = interleave_gate_up(gate_up)

@@ -71,9 +71,8 @@ class ExpertParallel:
             self.heap.close()
 
     def _sync(self, slot):
-        self._seq += 1
-        self.barrier.signal(slot, self._seq)
-        self.barrier.wait(slot, self._seq, ptr(err_word(self.device)))
+        # signal + wait in one launch with the sequence number in device memory: replayable from a CUDA graph
+        self.barrier.barrier_device_seq(slot, ptr(err_word(self.device)))
 
     def _table(self, t):
         off = self.heap.offset_bytes(t)
@@ -98,24 +97,25 @@ class ExpertParallel:
         par = self._parity
         self._parity ^= 1
         if counts is None:
-            counts = torch.bincount(ids.reshape(-1).long(), minlength=self.E).to(torch.int32)
+            counts = moe_ops.count_experts(ids, self.E)
         ids32 = ids.to(torch.int32).contiguous()
         offsets, order, pos = moe_ops.layout(ids32, counts)
         self._offsets[par].copy_(offsets)
         xs = self._xs[par]
         check(lib.tyr_moe_gather_rows(ptr(x.contiguous()), ptr(order), ptr(xs), T * k, k, h, st), "moe_gather_rows")
+        R = min(self.capacity, self.world * T * k)     # host-known upper bound of the rows this rank can receive
+        self._row_expert[:R].fill_(self.E_local)       # rows the pull does not fill stay marked as padding
         self._sync(0)
         check(lib.tyr_ep_pull(self._table(self._offsets[par]), self._table(xs), self.world, self.rank, self.E_local, h,
                               ptr(self._seg_rows), ptr(self._seg_src), ptr(self._dest_base[par]), ptr(self._exp_off),
                               ptr(self._exp_tiles), ptr(self._total), ptr(self._rows), ptr(self._row_expert), self.capacity,
                               self.max_pairs, ptr(err_word(x.device)), st), "ep_pull")
-        # the owner evaluates its experts on a host-known upper bound of rows; rows past the device-side
-        # total carry stale data and are never read back
-        R = min(self.capacity, self.world * T * k)
+        # the owner evaluates its experts on that upper bound; rows past the device-side total keep the padding id, take no
+        # slot in the expert layout and are never read back
         total = int(self._total.item()) if R > 4096 else R           # large batches: trim to the real row count
         R = max(1, min(R, total))
         rows = self._rows[:R]
-        row_e = self._row_expert[:R].clamp_(0, self.E_local - 1).reshape(R, 1)
+        row_e = self._row_expert[:R].reshape(R, 1)
         y_local = expert_fn(rows, row_e, torch.ones(R, 1, device=x.device))
         self._y[par][:R].copy_(y_local)
         self._sync(1)

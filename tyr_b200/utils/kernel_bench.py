@@ -112,6 +112,22 @@ def bench_attention_bwd(results):
         print(f"flash bwd B{B} H{H} T{T} causal={causal}: ours {ours:7.3f} ms {flops/ours/1e9:7.1f} TF/s | SDPA {lib:7.3f} ms {flops/lib/1e9:7.1f} TF/s", flush=True)
 
 
+def bench_attention_bwd_small(results):
+    """One small backward case for profiler captures: B 8, H 10, T 2048 causal (q, k, v, o, dO and the gradients hold about
+    0.3 GB), two warm-up and three timed calls."""
+    from tyr_b200.ops import flash
+    dev = torch.device("cuda")
+    B, H, T, D = 8, 10, 2048, 128
+    qkv = torch.randn(B, T, 3, H, D, device=dev).bfloat16()
+    q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
+    do = torch.randn(B, T, H, D, device=dev).bfloat16()
+    o, lse = flash.flash_fwd_bthd(q, k, v, causal=True, window=None, scale=None)
+    ms = _time(lambda: flash.flash_bwd_bthd(do, q, k, v, o, lse, causal=True, window=None, scale=None), iters=3, warmup=2)
+    flops = 5.0 * B * H * T * T * D
+    results.append({"kernel": "flash_bwd_small", "ms": ms, "tflops": flops / ms / 1e9})
+    print(f"flash bwd small B{B} H{H} T{T}: {ms:7.3f} ms {flops / ms / 1e9:7.1f} TF/s", flush=True)
+
+
 def bench_moe(results, cases=None):
     """Fused NVFP4 MoE op at Laguna-S-2.1 shapes (hidden 3072, 256 experts, top-10, FFN 1024): effective
     FP4 weight-read bandwidth for decode-sized batches (the reference's bar is >= 150 GB/s at one token,
@@ -204,6 +220,8 @@ def main(argv):
         bench_attention(results)
     if what in ("attention-bwd", "all"):
         bench_attention_bwd(results)
+    if what == "attention-bwd-small":
+        bench_attention_bwd_small(results)
     if what in ("moe", "all"):
         bench_moe(results)
     if what in ("decode-attn", "all"):
