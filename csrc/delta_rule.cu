@@ -1,4 +1,7 @@
-// Gated delta rule, single-token recurrent step (Qwen3.5 GatedDeltaNet decode).
+// Gated delta rule (Qwen3.5 GatedDeltaNet): the single-token recurrent step for decode, and further down the sequential chunk
+// pass of the chunked prefill form.
+//
+// Single-token step.
 //
 // Per (batch, value head) the state S is [dk, dv] fp32.  One step is
 //   S <- exp(g) * S;  kv = S^T k;  delta = beta * (v - kv);  S <- S + k delta^T;  out = S^T q
@@ -63,7 +66,536 @@ gdr_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __re
   }
 }
 
+// ------------------------------------------------------------------------------------------------------------------
+// Chunked prefill: the sequential pass over the chunks of one (batch, value head).
+//
+// The chunk-local quantities (u = "value" and w = "k_cumdecay" of the unit-lower-triangular solve, the decayed
+// q K^T matrix `intra`, qg = q * exp(gc), kd = k * exp(g_last - gc)) are batched matrix work over all chunks at once and
+// come in as fp32.  What is left is a recurrence over the chunks through the [dk, dv] state S,
+//     v_new = u_i - w_i S;   out_i = qg_i S + intra_i v_new;   S <- exp(g_last_i) S + kd_i^T v_new,
+// which the reference runs as a host loop of five small launches per chunk (cc/src/tyr_qwen35.cpp:89-110).  Here one CTA
+// walks all chunks of one (batch, head, 64-column slice of dv): S lives in registers as the accumulator of the last product
+// (each of the 4 warps owns 32 of the 128 state rows) and is mirrored into shared memory as the B operand of the first two;
+// all five products run on tensor cores in TF32 (mma.sync m16n8k8, fp32 accumulate).  The chunk inputs are staged with
+// cp.async in two groups so that the loads of w / qg for the next chunk overlap the last two products of this one.
+// ------------------------------------------------------------------------------------------------------------------
+constexpr int GC_C = 64;       // chunk length
+constexpr int GC_DK = 128;     // key dim
+constexpr int GC_DVS = 64;     // dv columns per CTA
+constexpr int GC_LDW = GC_DK + 4;    // row-major A operands: 4 g + t hits 32 distinct banks
+constexpr int GC_LDT = GC_DK + 8;    // kd is read transposed:  8 t + g
+constexpr int GC_LDI = GC_C + 4;
+constexpr int GC_LDS = GC_DVS + 8;   // B operands:              8 t + g
+
+struct GdrChunkSmem {
+  float w[GC_C * GC_LDW];
+  float q[GC_C * GC_LDW];
+  float kd[GC_C * GC_LDT];
+  float intra[GC_C * GC_LDI];
+  float s[GC_DK * GC_LDS];
+  float v[GC_C * GC_LDS];
+};
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void mma_tf32(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// rows x cols floats from global (row stride = cols) into shared memory rows of `ld` floats, 16 bytes per copy
+__device__ __forceinline__ void stage_tile(float* dst, const float* src, int rows, int cols, int ld) {
+  const int per_row = cols >> 2;
+  for (int i = threadIdx.x; i < rows * per_row; i += blockDim.x) {
+    const int r = i / per_row, c = (i % per_row) << 2;
+    cp_async16(dst + r * ld + c, src + static_cast<long long>(r) * cols + c);
+  }
+}
+
+__global__ void __launch_bounds__(128, 1)
+gdr_chunk_scan_kernel(const float* __restrict__ u, const float* __restrict__ w, const float* __restrict__ qg,
+                      const float* __restrict__ kd, const float* __restrict__ intra, const float* __restrict__ glast,
+                      const float* __restrict__ state_in, float* __restrict__ state_out, float* __restrict__ out, int n,
+                      int dv) {
+  extern __shared__ __align__(16) uint8_t gdr_smem_raw[];
+  GdrChunkSmem& sm = *reinterpret_cast<GdrChunkSmem*>(gdr_smem_raw);
+  const int bh = blockIdx.y;
+  const int col0 = blockIdx.x * GC_DVS;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const long long chunk_k = static_cast<long long>(GC_C) * GC_DK;      // floats per chunk of w / qg / kd
+  const float* w_p = w + static_cast<long long>(bh) * n * chunk_k;
+  const float* q_p = qg + static_cast<long long>(bh) * n * chunk_k;
+  const float* kd_p = kd + static_cast<long long>(bh) * n * chunk_k;
+  const float* in_p = intra + static_cast<long long>(bh) * n * GC_C * GC_C;
+  const float* u_p = u + static_cast<long long>(bh) * n * GC_C * dv + col0;
+  float* o_p = out + static_cast<long long>(bh) * n * GC_C * dv + col0;
+
+  // state rows [32 warp, 32 warp + 32) x 64 columns as two m-tiles x eight n-tiles of accumulators
+  float S[2][8][4];
+  {
+    const float* si = state_in ? state_in + (static_cast<long long>(bh) * GC_DK) * dv + col0 : nullptr;
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+        for (int h2 = 0; h2 < 2; ++h2) {
+          const int r = warp * 32 + mt * 16 + g + h2 * 8, c = nt * 8 + 2 * t;
+          float2 v = make_float2(0.f, 0.f);
+          if (si) v = *reinterpret_cast<const float2*>(si + static_cast<long long>(r) * dv + c);
+          S[mt][nt][2 * h2] = v.x;
+          S[mt][nt][2 * h2 + 1] = v.y;
+          *reinterpret_cast<float2*>(&sm.s[r * GC_LDS + c]) = v;
+        }
+  }
+  stage_tile(sm.w, w_p, GC_C, GC_DK, GC_LDW);
+  stage_tile(sm.q, q_p, GC_C, GC_DK, GC_LDW);
+  cp_async_commit();
+
+  for (int i = 0; i < n; ++i) {
+    stage_tile(sm.kd, kd_p + i * chunk_k, GC_C, GC_DK, GC_LDT);
+    stage_tile(sm.intra, in_p + static_cast<long long>(i) * GC_C * GC_C, GC_C, GC_C, GC_LDI);
+    cp_async_commit();
+    cp_async_wait<1>();            // w_i, qg_i landed (this thread's copies); the barrier publishes everyone's and S
+    __syncthreads();
+    // ---- X = w_i S, Y = qg_i S : warp rows [16 warp, +16), K = dk
+    float X[8][4], Y[8][4];
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) X[nt][e] = Y[nt][e] = 0.f;
+    const int ar = warp * 16 + g;
+#pragma unroll 4
+    for (int kk = 0; kk < GC_DK / 8; ++kk) {
+      const int kc = kk * 8 + t;
+      const uint32_t wa0 = __float_as_uint(sm.w[ar * GC_LDW + kc]), wa1 = __float_as_uint(sm.w[(ar + 8) * GC_LDW + kc]);
+      const uint32_t wa2 = __float_as_uint(sm.w[ar * GC_LDW + kc + 4]), wa3 = __float_as_uint(sm.w[(ar + 8) * GC_LDW + kc + 4]);
+      const uint32_t qa0 = __float_as_uint(sm.q[ar * GC_LDW + kc]), qa1 = __float_as_uint(sm.q[(ar + 8) * GC_LDW + kc]);
+      const uint32_t qa2 = __float_as_uint(sm.q[ar * GC_LDW + kc + 4]), qa3 = __float_as_uint(sm.q[(ar + 8) * GC_LDW + kc + 4]);
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) {
+        const uint32_t b0 = __float_as_uint(sm.s[kc * GC_LDS + nt * 8 + g]), b1 = __float_as_uint(sm.s[(kc + 4) * GC_LDS + nt * 8 + g]);
+        mma_tf32(X[nt], wa0, wa1, wa2, wa3, b0, b1);
+        mma_tf32(Y[nt], qa0, qa1, qa2, qa3, b0, b1);
+      }
+    }
+    // ---- v_new = u_i - X  -> shared memory (B operand of the next two products)
+    {
+      const float* ui = u_p + static_cast<long long>(i) * GC_C * dv;
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+        for (int h2 = 0; h2 < 2; ++h2) {
+          const int r = ar + h2 * 8, c = nt * 8 + 2 * t;
+          const float2 uu = *reinterpret_cast<const float2*>(ui + static_cast<long long>(r) * dv + c);
+          *reinterpret_cast<float2*>(&sm.v[r * GC_LDS + c]) = make_float2(uu.x - X[nt][2 * h2], uu.y - X[nt][2 * h2 + 1]);
+        }
+    }
+    cp_async_wait<0>();            // kd_i, intra_i
+    __syncthreads();               // v_new complete; every warp is done with w, qg and the old S in shared memory
+    if (i + 1 < n) {               // next chunk's first group overlaps the two products below
+      stage_tile(sm.w, w_p + (i + 1) * chunk_k, GC_C, GC_DK, GC_LDW);
+      stage_tile(sm.q, q_p + (i + 1) * chunk_k, GC_C, GC_DK, GC_LDW);
+    }
+    cp_async_commit();
+    // ---- out_i = Y + intra_i v_new : K = chunk
+#pragma unroll 2
+    for (int kk = 0; kk < GC_C / 8; ++kk) {
+      const int kc = kk * 8 + t;
+      const uint32_t a0 = __float_as_uint(sm.intra[ar * GC_LDI + kc]), a1 = __float_as_uint(sm.intra[(ar + 8) * GC_LDI + kc]);
+      const uint32_t a2 = __float_as_uint(sm.intra[ar * GC_LDI + kc + 4]), a3 = __float_as_uint(sm.intra[(ar + 8) * GC_LDI + kc + 4]);
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) {
+        const uint32_t b0 = __float_as_uint(sm.v[kc * GC_LDS + nt * 8 + g]), b1 = __float_as_uint(sm.v[(kc + 4) * GC_LDS + nt * 8 + g]);
+        mma_tf32(Y[nt], a0, a1, a2, a3, b0, b1);
+      }
+    }
+    {
+      float* oi = o_p + static_cast<long long>(i) * GC_C * dv;
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+        for (int h2 = 0; h2 < 2; ++h2)
+          *reinterpret_cast<float2*>(oi + static_cast<long long>(ar + h2 * 8) * dv + nt * 8 + 2 * t) =
+              make_float2(Y[nt][2 * h2], Y[nt][2 * h2 + 1]);
+    }
+    // ---- S <- exp(g_last) S + kd_i^T v_new : this warp's 32 state rows, K = chunk
+    const float e = glast[static_cast<long long>(bh) * n + i];
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) S[mt][nt][q4] *= e;
+#pragma unroll 2
+    for (int kk = 0; kk < GC_C / 8; ++kk) {
+      const int kc = kk * 8 + t;
+      uint32_t a[2][4];
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt) {
+        const int m = warp * 32 + mt * 16 + g;          // A[m][k] = kd[k][m]
+        a[mt][0] = __float_as_uint(sm.kd[kc * GC_LDT + m]);
+        a[mt][1] = __float_as_uint(sm.kd[kc * GC_LDT + m + 8]);
+        a[mt][2] = __float_as_uint(sm.kd[(kc + 4) * GC_LDT + m]);
+        a[mt][3] = __float_as_uint(sm.kd[(kc + 4) * GC_LDT + m + 8]);
+      }
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) {
+        const uint32_t b0 = __float_as_uint(sm.v[kc * GC_LDS + nt * 8 + g]), b1 = __float_as_uint(sm.v[(kc + 4) * GC_LDS + nt * 8 + g]);
+        mma_tf32(S[0][nt], a[0][0], a[0][1], a[0][2], a[0][3], b0, b1);
+        mma_tf32(S[1][nt], a[1][0], a[1][1], a[1][2], a[1][3], b0, b1);
+      }
+    }
+    // mirror the new state for the next chunk's first products (nobody reads sm.s between the barrier above and the next one)
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+        for (int h2 = 0; h2 < 2; ++h2)
+          *reinterpret_cast<float2*>(&sm.s[(warp * 32 + mt * 16 + g + h2 * 8) * GC_LDS + nt * 8 + 2 * t]) =
+              make_float2(S[mt][nt][2 * h2], S[mt][nt][2 * h2 + 1]);
+    __syncthreads();               // kd, intra, v free for the next chunk's copies; S mirror complete
+  }
+  float* so = state_out + (static_cast<long long>(bh) * GC_DK) * dv + col0;
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+      for (int h2 = 0; h2 < 2; ++h2)
+        *reinterpret_cast<float2*>(so + static_cast<long long>(warp * 32 + mt * 16 + g + h2 * 8) * dv + nt * 8 + 2 * t) =
+            make_float2(S[mt][nt][2 * h2], S[mt][nt][2 * h2 + 1]);
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// Chunked prefill: everything that is local to one chunk, in one launch per layer.
+//
+// One CTA per (chunk of 64 tokens, batch, value head), 256 threads:
+//   1. q, k rows -> fp32 shared memory, L2-normalised (q also scaled by dk^-1/2); gc = inclusive cumulative sum of g.
+//   2. k k^T and q k^T (64 x 64, K = 128) on tensor cores with the 3-term TF32 split (hi*hi + hi*lo + lo*hi, close to fp32:
+//      the first matrix feeds a triangular solve), then A = beta_i (k_i.k_j) exp(gc_i - gc_j) for j < i and
+//      intra = (q_i.k_j) exp(gc_i - gc_j) for j <= i.
+//   3. (I + A) X = [v beta | k beta exp(gc)] by forward substitution in fp32: one thread per right-hand-side column keeps
+//      its 64 unknowns in registers; the rows of A are broadcast from shared memory.  X = [u | w].
+//   4. qg = q exp(gc), kd = k exp(gc_last - gc), glast = exp(gc_last).
+// The reference builds the same quantities as a graph of library ops over all chunks with a 63-step loop for the solve
+// (cc/src/tyr_qwen35.cpp:21-88).  Rows past the sequence end behave as g = 0, beta = 0, q = k = v = 0.
+// ------------------------------------------------------------------------------------------------------------------
+constexpr int GP_LDA = GC_C + 4;
+
+struct GdrPrepSmem {
+  float k[GC_C * GC_LDW];
+  float q[GC_C * GC_LDW];
+  float a[GC_C * GP_LDA];
+  float gc[GC_C];
+  float beta[GC_C];
+  float eg[GC_C];        // exp(gc_i)
+};
+
+struct GdrPrepArgs {
+  const __nv_bfloat16 *q, *k, *v;
+  const float *g, *beta;               // [B, S, Hv] contiguous
+  float *u, *w, *qg, *kd, *intra, *glast;
+  long long q_sb, q_ss, q_sh, k_sb, k_ss, k_sh, v_sb, v_ss, v_sh;
+  int S, n, Hk, Hv, dv;
+};
+
+__device__ __forceinline__ uint32_t to_tf32(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return r;
+}
+
+__global__ void __launch_bounds__(256, 2) gdr_chunk_prepare_kernel(GdrPrepArgs a) {
+  extern __shared__ __align__(16) uint8_t gdr_smem_raw[];
+  GdrPrepSmem& sm = *reinterpret_cast<GdrPrepSmem*>(gdr_smem_raw);
+  const int c = blockIdx.x, bh = blockIdx.y;
+  const int b = bh / a.Hv, hv = bh % a.Hv, hk = hv / (a.Hv / a.Hk);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int row0 = c * GC_C;
+  // ---- 1. stage q, k (fp32), g, beta
+  for (int i = tid; i < GC_C * (GC_DK / 8); i += 256) {
+    const int r = i / (GC_DK / 8), d = (i % (GC_DK / 8)) * 8;
+    const int tok = row0 + r;
+    uint4 uq = make_uint4(0, 0, 0, 0), uk = make_uint4(0, 0, 0, 0);
+    if (tok < a.S) {
+      uq = *reinterpret_cast<const uint4*>(a.q + b * a.q_sb + static_cast<long long>(tok) * a.q_ss + hk * a.q_sh + d);
+      uk = *reinterpret_cast<const uint4*>(a.k + b * a.k_sb + static_cast<long long>(tok) * a.k_ss + hk * a.k_sh + d);
+    }
+    const uint32_t qq[4] = {uq.x, uq.y, uq.z, uq.w}, kk[4] = {uk.x, uk.y, uk.z, uk.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 fq = unpack_bf16x2(qq[e]), fk = unpack_bf16x2(kk[e]);
+      sm.q[r * GC_LDW + d + 2 * e] = fq.x; sm.q[r * GC_LDW + d + 2 * e + 1] = fq.y;
+      sm.k[r * GC_LDW + d + 2 * e] = fk.x; sm.k[r * GC_LDW + d + 2 * e + 1] = fk.y;
+    }
+  }
+  if (tid < GC_C) {
+    const int tok = row0 + tid;
+    const long long gi = (static_cast<long long>(b) * a.S + tok) * a.Hv + hv;
+    sm.gc[tid] = tok < a.S ? a.g[gi] : 0.f;
+    sm.beta[tid] = tok < a.S ? a.beta[gi] : 0.f;
+  }
+  __syncthreads();
+  // inclusive scan of g over the chunk (warp 0: two elements per lane)
+  if (warp == 0) {
+    float x0 = sm.gc[2 * lane], x1 = sm.gc[2 * lane + 1];
+    float s = x0 + x1;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float t = __shfl_up_sync(0xffffffffu, s, o);
+      if (lane >= o) s += t;
+    }
+    const float base = s - (x0 + x1);
+    sm.gc[2 * lane] = base + x0;
+    sm.gc[2 * lane + 1] = base + x0 + x1;
+  }
+  // L2 normalisation: 4 threads per row
+  {
+    const int r = tid >> 2, part = tid & 3;
+    float sq = 0.f, sk = 0.f;
+    for (int d = part * 32; d < part * 32 + 32; ++d) {
+      const float x = sm.q[r * GC_LDW + d], y = sm.k[r * GC_LDW + d];
+      sq += x * x; sk += y * y;
+    }
+    sq += __shfl_xor_sync(0xffffffffu, sq, 1); sq += __shfl_xor_sync(0xffffffffu, sq, 2);
+    sk += __shfl_xor_sync(0xffffffffu, sk, 1); sk += __shfl_xor_sync(0xffffffffu, sk, 2);
+    const float qn = rsqrtf(sq + 1e-6f) * rsqrtf(static_cast<float>(GC_DK)), kn = rsqrtf(sk + 1e-6f);
+    for (int d = part * 32; d < part * 32 + 32; ++d) {
+      sm.q[r * GC_LDW + d] *= qn;
+      sm.k[r * GC_LDW + d] *= kn;
+    }
+  }
+  __syncthreads();
+  if (tid < GC_C) sm.eg[tid] = __expf(sm.gc[tid]);
+  // ---- 2. warps 0-3: k k^T strips, warps 4-7: q k^T strips (16 rows each), 3-term TF32
+  {
+    const int g8 = lane >> 2, t = lane & 3;
+    const bool is_q = warp >= 4;
+    const float* A = is_q ? sm.q : sm.k;
+    const int ar = (warp & 3) * 16 + g8;
+    float acc[8][4];
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[nt][e] = 0.f;
+#pragma unroll 2
+    for (int kk = 0; kk < GC_DK / 8; ++kk) {
+      const int kc = kk * 8 + t;
+      const float af[4] = {A[ar * GC_LDW + kc], A[(ar + 8) * GC_LDW + kc], A[ar * GC_LDW + kc + 4], A[(ar + 8) * GC_LDW + kc + 4]};
+      uint32_t ah[4], al[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        ah[e] = to_tf32(af[e]);
+        al[e] = to_tf32(af[e] - __uint_as_float(ah[e]));
+      }
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) {
+        const float b0f = sm.k[(nt * 8 + g8) * GC_LDW + kc], b1f = sm.k[(nt * 8 + g8) * GC_LDW + kc + 4];
+        const uint32_t b0h = to_tf32(b0f), b1h = to_tf32(b1f);
+        const uint32_t b0l = to_tf32(b0f - __uint_as_float(b0h)), b1l = to_tf32(b1f - __uint_as_float(b1h));
+        mma_tf32(acc[nt], al[0], al[1], al[2], al[3], b0h, b1h);
+        mma_tf32(acc[nt], ah[0], ah[1], ah[2], ah[3], b0l, b1l);
+        mma_tf32(acc[nt], ah[0], ah[1], ah[2], ah[3], b0h, b1h);
+      }
+    }
+    __syncthreads();          // eg ready (written above by other threads)
+    float* intra_o = a.intra + (static_cast<long long>(bh) * a.n + c) * GC_C * GC_C;
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+      for (int h2 = 0; h2 < 2; ++h2) {
+        const int i = ar + h2 * 8, j = nt * 8 + 2 * t;
+        const float gi = sm.gc[i];
+        float v0 = acc[nt][2 * h2] * __expf(gi - sm.gc[j]), v1 = acc[nt][2 * h2 + 1] * __expf(gi - sm.gc[j + 1]);
+        if (is_q) {
+          v0 = j <= i ? v0 : 0.f;
+          v1 = j + 1 <= i ? v1 : 0.f;
+          *reinterpret_cast<float2*>(intra_o + i * GC_C + j) = make_float2(v0, v1);
+        } else {
+          const float bi = sm.beta[i];
+          sm.a[i * GP_LDA + j] = j < i ? v0 * bi : 0.f;
+          sm.a[i * GP_LDA + j + 1] = j + 1 < i ? v1 * bi : 0.f;
+        }
+      }
+  }
+  __syncthreads();
+  // ---- 3. forward substitution, one right-hand-side column per thread
+  {
+    const int col = tid;
+    const int ncol = a.dv + GC_DK;
+    if (col < ncol) {
+      float x[GC_C];
+      const bool is_v = col < a.dv;
+      if (is_v) {
+        const __nv_bfloat16* vp = a.v + b * a.v_sb + hv * a.v_sh + col;
+#pragma unroll
+        for (int i = 0; i < GC_C; ++i) {
+          const int tok = row0 + i;
+          x[i] = tok < a.S ? __bfloat162float(vp[static_cast<long long>(tok) * a.v_ss]) * sm.beta[i] : 0.f;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < GC_C; ++i) x[i] = sm.k[i * GC_LDW + (col - a.dv)] * sm.beta[i] * sm.eg[i];
+      }
+#pragma unroll
+      for (int i = 1; i < GC_C; ++i) {
+        float acc = x[i];
+#pragma unroll
+        for (int j4 = 0; j4 < (i + 3) / 4; ++j4) {
+          const float4 r4 = *reinterpret_cast<const float4*>(&sm.a[i * GP_LDA + 4 * j4]);     // entries at j >= i are zero
+          acc -= r4.x * x[4 * j4];
+          if (4 * j4 + 1 < i) acc -= r4.y * x[4 * j4 + 1];
+          if (4 * j4 + 2 < i) acc -= r4.z * x[4 * j4 + 2];
+          if (4 * j4 + 3 < i) acc -= r4.w * x[4 * j4 + 3];
+        }
+        x[i] = acc;
+      }
+      float* dst = is_v ? a.u + (static_cast<long long>(bh) * a.n + c) * GC_C * a.dv + col
+                        : a.w + (static_cast<long long>(bh) * a.n + c) * GC_C * GC_DK + (col - a.dv);
+      const int ld = is_v ? a.dv : GC_DK;
+#pragma unroll
+      for (int i = 0; i < GC_C; ++i) dst[static_cast<long long>(i) * ld] = x[i];
+    }
+  }
+  // ---- 4. qg, kd, glast
+  {
+    const float g_last = sm.gc[GC_C - 1];
+    float* qg_o = a.qg + (static_cast<long long>(bh) * a.n + c) * GC_C * GC_DK;
+    float* kd_o = a.kd + (static_cast<long long>(bh) * a.n + c) * GC_C * GC_DK;
+    for (int i = tid; i < GC_C * (GC_DK / 4); i += 256) {
+      const int r = i / (GC_DK / 4), d = (i % (GC_DK / 4)) * 4;
+      const float eq = sm.eg[r], ek = __expf(g_last - sm.gc[r]);
+      const float4 fq = *reinterpret_cast<const float4*>(&sm.q[r * GC_LDW + d]);
+      const float4 fk = *reinterpret_cast<const float4*>(&sm.k[r * GC_LDW + d]);
+      *reinterpret_cast<float4*>(qg_o + r * GC_DK + d) = make_float4(fq.x * eq, fq.y * eq, fq.z * eq, fq.w * eq);
+      *reinterpret_cast<float4*>(kd_o + r * GC_DK + d) = make_float4(fk.x * ek, fk.y * ek, fk.z * ek, fk.w * ek);
+    }
+    if (tid == 0) a.glast[static_cast<long long>(bh) * a.n + c] = __expf(g_last);
+  }
+}
+
 }  // namespace tyr
+
+// Causal depthwise conv1d (kernel taps K <= 8, zero history) + bias + SiLU on channels-last activations:
+//   y[b, s, c] = silu(bias[c] + sum_j w[c, j] * x[b, s - (K - 1) + j, c]).
+// One thread per (token, 8 channels); the taps of neighbouring tokens hit L1 / L2.  The reference transposes to channels-first
+// and calls the library's grouped convolution (Tyr/Model/Qwen35/Model.lean:642-700).
+namespace tyr {
+__global__ void __launch_bounds__(256) causal_conv1d_silu_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ w,
+                                                                 const float* __restrict__ bias, __nv_bfloat16* __restrict__ y,
+                                                                 long long total, int S, int C, int K, long long x_sb,
+                                                                 long long x_ss) {
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int c8 = C >> 3;
+  const int c = static_cast<int>(i % c8) * 8;
+  const long long bs = i / c8;
+  const int s = static_cast<int>(bs % S);
+  const long long b = bs / S;
+  float acc[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) acc[e] = bias ? bias[c + e] : 0.f;
+  for (int j = 0; j < K; ++j) {
+    const int t = s - (K - 1) + j;
+    if (t < 0) continue;
+    const uint4 u = *reinterpret_cast<const uint4*>(x + b * x_sb + static_cast<long long>(t) * x_ss + c);
+    const uint32_t uu[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 f = unpack_bf16x2(uu[e]);
+      acc[2 * e] += f.x * w[(c + 2 * e) * K + j];
+      acc[2 * e + 1] += f.y * w[(c + 2 * e + 1) * K + j];
+    }
+  }
+  uint4 o;
+  uint32_t* oo = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float a0 = acc[2 * e], a1 = acc[2 * e + 1];
+    oo[e] = pack_bf16x2(a0 / (1.f + __expf(-a0)), a1 / (1.f + __expf(-a1)));
+  }
+  *reinterpret_cast<uint4*>(y + (b * S + s) * C + c) = o;
+}
+}  // namespace tyr
+
+// x: bf16 [B, S, C] with (batch, token) element strides and contiguous channels; w: fp32 [C, K]; bias: fp32 [C] or null;
+// y: bf16 [B, S, C] contiguous.  C must be a multiple of 8.
+extern "C" TYR_EXPORT int tyr_causal_conv1d_silu(const void* x, const float* w, const float* bias, void* y, int B, int S, int C,
+                                                 int K, long long x_sb, long long x_ss, void* stream) {
+  if (B <= 0 || S <= 0 || C <= 0 || (C & 7) || K <= 0 || K > 8 || (x_sb & 7) || (x_ss & 7)) return -1;
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) return -2;
+  const long long total = static_cast<long long>(B) * S * (C >> 3);
+  tyr::causal_conv1d_silu_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(x), w, bias, reinterpret_cast<__nv_bfloat16*>(y), total, S, C, K, x_sb, x_ss);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Chunk-local quantities of the gated delta rule (chunk 64, dk 128, dv 64 or 128).  q, k: bf16 [B, S, Hk, 128] and
+// v: bf16 [B, S, Hv, dv] given by (batch, token, head) element strides; g, beta: fp32 [B, S, Hv] contiguous.  Outputs (fp32,
+// n = ceil(S / 64) chunks): u [B*Hv, n, 64, dv], w / qg / kd [B*Hv, n, 64, 128], intra [B*Hv, n, 64, 64], glast [B*Hv, n].
+extern "C" TYR_EXPORT int tyr_gdr_chunk_prepare(const void* q, const void* k, const void* v, const float* g,
+                                                const float* beta, float* u, float* w, float* qg, float* kd,
+                                                float* intra, float* glast, const long long* strides, int B, int S,
+                                                int Hk, int Hv, int dk, int dv, void* stream) {
+  using namespace tyr;
+  if (B <= 0 || S <= 0 || Hk <= 0 || Hv <= 0 || Hv % Hk || dk != GC_DK || (dv != 64 && dv != 128)) return -1;
+  for (int i = 0; i < 6; ++i)
+    if (strides[i] & 7) return -3;
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k)) & 15) return -4;
+  GdrPrepArgs a;
+  a.q = reinterpret_cast<const __nv_bfloat16*>(q);
+  a.k = reinterpret_cast<const __nv_bfloat16*>(k);
+  a.v = reinterpret_cast<const __nv_bfloat16*>(v);
+  a.g = g; a.beta = beta; a.u = u; a.w = w; a.qg = qg; a.kd = kd; a.intra = intra; a.glast = glast;
+  a.q_sb = strides[0]; a.q_ss = strides[1]; a.q_sh = strides[2];
+  a.k_sb = strides[3]; a.k_ss = strides[4]; a.k_sh = strides[5];
+  a.v_sb = strides[6]; a.v_ss = strides[7]; a.v_sh = strides[8];
+  a.S = S; a.n = (S + GC_C - 1) / GC_C; a.Hk = Hk; a.Hv = Hv; a.dv = dv;
+  constexpr size_t smem = sizeof(GdrPrepSmem);
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gdr_chunk_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return 1000 + (int)e;
+    configured = true;
+  }
+  gdr_chunk_prepare_kernel<<<dim3(a.n, B * Hv), 256, smem, reinterpret_cast<cudaStream_t>(stream)>>>(a);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Sequential chunk pass of the gated delta rule (chunk 64, dk 128, dv a multiple of 64), all tensors fp32 and contiguous:
+// u [BH, n, 64, dv], w / qg / kd [BH, n, 64, 128], intra [BH, n, 64, 64], glast [BH, n] (= exp of the chunk's last cumulative
+// log decay), state_in [BH, 128, dv] (nullable = zeros), state_out [BH, 128, dv], out [BH, n, 64, dv].
+extern "C" TYR_EXPORT int tyr_gdr_chunk_scan(const float* u, const float* w, const float* qg, const float* kd,
+                                             const float* intra, const float* glast, const float* state_in,
+                                             float* state_out, float* out, int BH, int n, int dk, int dv, int chunk,
+                                             void* stream) {
+  using namespace tyr;
+  if (BH <= 0 || n <= 0 || dk != GC_DK || chunk != GC_C || dv <= 0 || dv % GC_DVS) return -1;
+  if ((reinterpret_cast<uintptr_t>(u) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(qg) |
+       reinterpret_cast<uintptr_t>(kd) | reinterpret_cast<uintptr_t>(intra) | reinterpret_cast<uintptr_t>(out) |
+       reinterpret_cast<uintptr_t>(state_out) | reinterpret_cast<uintptr_t>(state_in)) & 15)
+    return -2;
+  constexpr size_t smem = sizeof(GdrChunkSmem);
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gdr_chunk_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return 1000 + (int)e;
+    configured = true;
+  }
+  gdr_chunk_scan_kernel<<<dim3(dv / GC_DVS, BH), 128, smem, reinterpret_cast<cudaStream_t>(stream)>>>(
+      u, w, qg, kd, intra, glast, state_in, state_out, out, n, dv);
+  return static_cast<int>(cudaGetLastError());
+}
 
 // q, k: bf16 [B, Hk, dk] (rows may be strided by q_bstride elements between batches); v: bf16 [B, Hv, dv]
 // (v_bstride); g, beta: fp32 [B, Hv]; state: fp32 [B, Hv, dk, dv] updated in place; out: bf16 [B, Hv, dv].

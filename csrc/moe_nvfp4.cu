@@ -626,7 +626,7 @@ extern "C" TYR_EXPORT int tyr_moe_route_fused(const void* x, const float* router
   const size_t smem = sizeof(__nv_bfloat16) * static_cast<size_t>(h) * kRouteTok;
   if (smem > 160 * 1024) return -3;
   static size_t configured = 0;
-  if (smem > 48 * 1024 && configured < smem) {
+  if (smem + 1024 > 48 * 1024 && configured < smem) {       // the kernel also holds a few bytes of static shared memory
     cudaFuncSetAttribute(moe_route_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     configured = smem;
   }

@@ -455,3 +455,48 @@ def test_moe_route_fused_matches_separate_gemm_and_route(T, E, k, h, softmax):
     rows = same.nonzero().flatten()
     assert torch.allclose(w[rows].sort(1).values, rw[rows].sort(1).values, rtol=2e-3, atol=1e-5)
     assert int(counts.sum()) == T * k and torch.equal(counts, torch.bincount(ids.flatten().long(), minlength=E).int())
+
+
+@pytest.mark.parametrize("B,S,Hk,Hv,dv,with_state", [(2, 256, 2, 4, 128, False), (1, 200, 1, 2, 64, True), (1, 64, 2, 2, 128, True)])
+def test_gated_delta_rule_chunk_scan_kernel_matches_recurrence(B, S, Hk, Hv, dv, with_state):
+    """Chunked prefill with the chunk recurrence in one launch (TF32 tensor cores) against the token-by-token fp32 recurrence."""
+    from tyr_b200.ops import delta_rule as DR
+    g = torch.Generator(device="cuda").manual_seed(S + dv)
+    dk = 128
+    rn = lambda *s: torch.randn(*s, device=_dev(), generator=g)
+    q, k = rn(B, S, Hk, dk).bfloat16(), rn(B, S, Hk, dk).bfloat16()
+    rep = Hv // Hk
+    qr, kr = q.repeat_interleave(rep, dim=2), k.repeat_interleave(rep, dim=2)
+    v = rn(B, S, Hv, dv).bfloat16()
+    gl = -torch.nn.functional.softplus(rn(B, S, Hv)) * 0.3
+    beta = torch.sigmoid(rn(B, S, Hv))
+    st0 = rn(B, Hv, dk, dv) * 0.1 if with_state else None
+    assert DR.chunk_kernels_supported(q, k, v)
+    out, st = DR.chunk_gated_delta_rule(q, k, v, gl, beta, 64, st0)                 # grouped keys: both chunk kernels
+    ref, rst = DR.recurrent_gated_delta_rule(qr, kr, v, gl, beta, st0)
+    torch.cuda.synchronize()
+    assert out.shape == ref.shape and _rel_err(out, ref) < 2e-2, _rel_err(out, ref)
+    assert _rel_err(st, rst) < 2e-2, _rel_err(st, rst)
+    import os
+    os.environ["TYR_GDR_CHUNK_KERNEL"] = "0"
+    try:
+        DR._CHUNK_KERNEL = False
+        lib_out, lib_st = DR.chunk_gated_delta_rule(q, k, v, gl, beta, 64, st0)     # library-op form of the same algorithm
+    finally:
+        DR._CHUNK_KERNEL = True
+        os.environ.pop("TYR_GDR_CHUNK_KERNEL", None)
+    assert _rel_err(out, lib_out) < 2e-2 and _rel_err(st, lib_st) < 2e-2
+
+
+@pytest.mark.parametrize("B,S,C,K,bias", [(2, 300, 256, 4, True), (1, 5, 64, 4, False), (3, 64, 10240, 4, True), (1, 2, 8, 2, True)])
+def test_causal_conv1d_silu_matches_library(B, S, C, K, bias):
+    from tyr_b200.ops import delta_rule as DR
+    g = torch.Generator(device="cuda").manual_seed(C + S)
+    wide = torch.randn(B, S, C + 16, device=_dev(), generator=g).bfloat16()
+    x = wide[:, :, 8:8 + C]                                  # strided rows, 16-byte aligned
+    w = torch.randn(C, K, device=_dev(), generator=g) * 0.5
+    b = torch.randn(C, device=_dev(), generator=g) if bias else None
+    y = DR.causal_conv1d_silu(x, w, b)
+    xc = x.float().transpose(1, 2)
+    ref = torch.nn.functional.silu(torch.nn.functional.conv1d(torch.nn.functional.pad(xc, (K - 1, 0)), w.reshape(C, 1, K), b, groups=C)).transpose(1, 2)
+    assert y.shape == (B, S, C) and (y.float() - ref).abs().max() < 3e-2

@@ -45,6 +45,27 @@ def main():
         if err > tol:
             ok = False
             print(f"rank {rank} it {it}: err {err} tol {tol}", flush=True)
+    if dev.type == "cuda" and ep.fused:
+        # the exchange replayed from a CUDA graph (two layers per step, fresh inputs per replay) against the eager result
+        from tyr_b200.utils.graph import GraphedStep
+        fn_e = local_expert_fn(mine)
+
+        def two_layers(x, logits):
+            for _ in range(2):
+                ids, w, cnt = moe.route(logits, k)
+                x = ep.forward(x, ids, w, fn_e, counts=cnt)
+            return x
+        gi = torch.Generator().manual_seed(500 + rank)
+        xs = [torch.randn(T, h, generator=gi).to(dtype).to(dev) * 0.5 for _ in range(3)]
+        ls = [torch.randn(T, E, generator=gi).to(dev) for _ in range(3)]
+        step = GraphedStep(two_layers, (xs[0], ls[0]))
+        for x, l in zip(xs, ls):
+            got = step(x, l).clone()
+            want = two_layers(x, l)
+            err = (got.float() - want.float()).abs().max().item()
+            if err > 0.05 * max(1.0, want.float().abs().max().item()):
+                ok = False
+                print(f"rank {rank} graph replay: err {err}", flush=True)
     if dev.type == "cuda":
         torch.cuda.synchronize()
         from tyr_b200.ops._common import raise_on_device_error

@@ -317,8 +317,7 @@ def gated_delta_net_core(cfg: Qwen35Config, m, mixed, z, b, a, state: Optional[L
         state.conv.copy_(window)                                                          # in place: the step is graph-replayable
     else:
         xc = mixed.transpose(1, 2)
-        y = F.conv1d(F.pad(xc, (K - 1, 0)), m.conv1d_weight.to(xc.dtype), None if m.conv1d_bias is None else m.conv1d_bias.to(xc.dtype), groups=cd)
-        conv_out = F.silu(y).transpose(1, 2)
+        conv_out = dr.causal_conv1d_silu(mixed, m.conv1d_weight.reshape(cd, K), m.conv1d_bias)
         if state is not None:
             state.conv = (xc[:, :, S - K:] if S >= K else F.pad(xc, (K - S, 0))).contiguous()
     kd = cfg.linear_key_dim
@@ -331,8 +330,7 @@ def gated_delta_net_core(cfg: Qwen35Config, m, mixed, z, b, a, state: Optional[L
     if step and state.rec is not None:
         core = dr.gdr_decode_step(q.contiguous(), k.contiguous(), v.contiguous(), g, beta, state.rec)
     else:
-        qr, kr = q.repeat_interleave(rep, dim=2), k.repeat_interleave(rep, dim=2)
-        core, rec = dr.chunk_gated_delta_rule(qr, kr, v, g, beta, state=state.rec if state is not None else None)
+        core, rec = dr.chunk_gated_delta_rule(q, k, v, g, beta, state=state.rec if state is not None else None)    # keys stay grouped
         if state is not None:
             state.rec = rec.contiguous()
     core = rms_norm_gated(core.reshape(B * S * Hv, dv), z.reshape(B * S * Hv, dv), m.norm_weight, cfg.rms_norm_eps)

@@ -5,6 +5,7 @@ Semantics: cc/src/tyr_qwen35.cpp:12-170 of the reference (L2-normalised q/k, q s
 """
 from __future__ import annotations
 
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -21,6 +22,21 @@ def _sigs(lib_):
     if fn is not None:
         fn.argtypes = [P, P, P, P, P, P, P, I, I, I, I, I, L, L, P]
         fn.restype = ctypes.c_int
+    fn = getattr(lib_, "tyr_gdr_chunk_scan", None)
+    if fn is not None:
+        fn.argtypes = [P] * 9 + [I, I, I, I, I, P]
+        fn.restype = ctypes.c_int
+    fn = getattr(lib_, "tyr_gdr_chunk_prepare", None)
+    if fn is not None:
+        fn.argtypes = [P] * 11 + [ctypes.POINTER(L), I, I, I, I, I, I, P]
+        fn.restype = ctypes.c_int
+    fn = getattr(lib_, "tyr_causal_conv1d_silu", None)
+    if fn is not None:
+        fn.argtypes = [P, P, P, P, I, I, I, I, L, L, P]
+        fn.restype = ctypes.c_int
+
+
+_CHUNK_KERNEL = os.environ.get("TYR_GDR_CHUNK_KERNEL", "1") != "0"
 
 
 def l2norm(x: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
@@ -46,9 +62,61 @@ def recurrent_gated_delta_rule(q, k, v, g, beta, state: Optional[torch.Tensor] =
     return out.transpose(1, 2).contiguous().to(dt), st
 
 
+def chunk_kernels_supported(q, k, v, chunk_size: int = 64) -> bool:
+    """Both chunk kernels (csrc/delta_rule.cu) apply: bf16 on CUDA, dk 128, dv 64 or 128, chunk 64, 16-byte aligned q / k rows;
+    q and k may carry fewer heads than v (grouped keys)."""
+    ok_view = lambda t: t.stride(3) == 1 and all(x % 8 == 0 for x in t.stride()[:3]) and t.data_ptr() % 16 == 0
+    return (_CHUNK_KERNEL and q.is_cuda and q.dtype == k.dtype == v.dtype == torch.bfloat16 and q.shape[-1] == 128 and v.shape[-1] in (64, 128)
+            and chunk_size == 64 and v.shape[2] % q.shape[2] == 0 and q.shape[2] == k.shape[2] and ok_view(q) and ok_view(k) and v.stride(3) == 1
+            and hasattr(lib(), "tyr_gdr_chunk_prepare") and hasattr(lib(), "tyr_gdr_chunk_scan"))
+
+
+def chunk_gated_delta_rule_fused(q, k, v, g, beta, state: Optional[torch.Tensor] = None):
+    """Two launches: the chunk-local quantities (normalisation, decay, the two 64 x 64 products, the triangular solve) and the
+    recurrence over the chunks.  q, k: [B, S, Hk, 128] with Hk dividing Hv (keys are not repeated); see :func:`chunk_kernels_supported`."""
+    import ctypes
+    B, S, Hk, dk = q.shape
+    Hv, dv = v.shape[2], v.shape[3]
+    n, BH, dev = (S + 63) // 64, B * Hv, q.device
+    f32 = lambda *shape: torch.empty(shape, dtype=torch.float32, device=dev)
+    u, w, qg, kd, intra, glast = f32(BH, n, 64, dv), f32(BH, n, 64, dk), f32(BH, n, 64, dk), f32(BH, n, 64, dk), f32(BH, n, 64, 64), f32(BH, n)
+    strides = (ctypes.c_longlong * 9)(*[t.stride(i) for t in (q, k, v) for i in range(3)])
+    gc, bc = g.float().contiguous(), beta.float().contiguous()
+    st = cur_stream(dev)
+    check(lib().tyr_gdr_chunk_prepare(ptr(q), ptr(k), ptr(v), ptr(gc), ptr(bc), ptr(u), ptr(w), ptr(qg), ptr(kd), ptr(intra), ptr(glast), strides,
+                                      B, S, Hk, Hv, dk, dv, st), "gdr_chunk_prepare")
+    st_in = None if state is None else state.float().contiguous()
+    st_out = f32(B, Hv, dk, dv)
+    out = f32(B, Hv, n * 64, dv)
+    check(lib().tyr_gdr_chunk_scan(ptr(u), ptr(w), ptr(qg), ptr(kd), ptr(intra), ptr(glast), ptr(st_in), ptr(st_out), ptr(out), BH, n, dk, dv, 64, st),
+          "gdr_chunk_scan")
+    return out[:, :, :S].transpose(1, 2).to(q.dtype), st_out
+
+
+def causal_conv1d_silu(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x: [B, S, C] (channels last), weight: [C, K] -> silu(causal depthwise conv + bias) as [B, S, C], zero history."""
+    B, S, C = x.shape
+    K = weight.shape[-1]
+    if (x.is_cuda and x.dtype == torch.bfloat16 and C % 8 == 0 and K <= 8 and x.stride(2) == 1 and x.stride(0) % 8 == 0 and x.stride(1) % 8 == 0
+            and x.data_ptr() % 16 == 0 and hasattr(lib(), "tyr_causal_conv1d_silu")):
+        y = torch.empty((B, S, C), dtype=x.dtype, device=x.device)
+        wf = weight.reshape(C, K).float().contiguous()
+        bf = None if bias is None else bias.float().contiguous()
+        check(lib().tyr_causal_conv1d_silu(ptr(x), ptr(wf), ptr(bf), ptr(y), B, S, C, K, x.stride(0), x.stride(1), cur_stream(x.device)), "causal_conv1d_silu")
+        return y
+    xc = x.transpose(1, 2)
+    y = torch.nn.functional.conv1d(torch.nn.functional.pad(xc, (K - 1, 0)), weight.reshape(C, 1, K).to(xc.dtype), None if bias is None else bias.to(xc.dtype), groups=C)
+    return torch.nn.functional.silu(y).transpose(1, 2)
+
+
 def chunk_gated_delta_rule(q, k, v, g, beta, chunk_size: int = 64, state: Optional[torch.Tensor] = None):
     """Chunk-parallel form: the intra-chunk triangular system is solved with one batched
     unit-lower-triangular solve; chunks are chained through the [dk, dv] state."""
+    if chunk_kernels_supported(q, k, v, chunk_size):
+        return chunk_gated_delta_rule_fused(q, k, v, g, beta, state)
+    if q.shape[2] != v.shape[2]:
+        rep = v.shape[2] // q.shape[2]
+        q, k = q.repeat_interleave(rep, dim=2), k.repeat_interleave(rep, dim=2)
     dt = q.dtype
     qf = l2norm(q.float()).transpose(1, 2) * (q.shape[-1] ** -0.5)
     kf = l2norm(k.float()).transpose(1, 2)
@@ -71,6 +139,19 @@ def chunk_gated_delta_rule(q, k, v, g, beta, chunk_size: int = 64, state: Option
     sol = torch.linalg.solve_triangular(eye + L, rhs, upper=False, unitriangular=True)
     u, w = sol[..., :dv], sol[..., dv:]                                          # "value" and "k_cumdecay"
     intra = (qf @ kf.transpose(-1, -2) * decay).tril()
+    if q.is_cuda and dk == 128 and dv % 64 == 0 and C == 64 and _CHUNK_KERNEL and hasattr(lib(), "tyr_gdr_chunk_scan"):
+        # the recurrence over the chunks in one launch (csrc/delta_rule.cu: gdr_chunk_scan_kernel)
+        g_last = gc[..., -1:]
+        c32 = lambda t: t.float().contiguous()
+        qg, kd = c32(qf * gc.exp().unsqueeze(-1)), c32(kf * (g_last - gc).exp().unsqueeze(-1))
+        u, w, intra, glast = c32(u), c32(w), c32(intra), c32(g_last.squeeze(-1).exp())
+        st_in = None if state is None else c32(state)
+        st = torch.empty(B, H, dk, dv, dtype=torch.float32, device=q.device)
+        out = torch.empty(B, H, n, C, dv, dtype=torch.float32, device=q.device)
+        check(lib().tyr_gdr_chunk_scan(ptr(u), ptr(w), ptr(qg), ptr(kd), ptr(intra), ptr(glast), ptr(st_in), ptr(st), ptr(out), B * H, n, dk, dv, C,
+                                       cur_stream(q.device)), "gdr_chunk_scan")
+        out = out.reshape(B, H, n * C, dv)[:, :, :S].transpose(1, 2).contiguous().to(dt)
+        return out, st
     st = torch.zeros(B, H, dk, dv, device=q.device) if state is None else state.float().clone()
     out = torch.empty(B, H, n, C, dv, device=q.device)
     for i in range(n):

@@ -112,6 +112,19 @@ def bench_attention_bwd(results):
         print(f"flash bwd B{B} H{H} T{T} causal={causal}: ours {ours:7.3f} ms {flops/ours/1e9:7.1f} TF/s | SDPA {lib:7.3f} ms {flops/lib/1e9:7.1f} TF/s", flush=True)
 
 
+def bench_attention_fwd_small(results):
+    """One small forward case for profiler captures: B 8, H 10, T 2048 causal, two warm-up and three timed calls."""
+    from tyr_b200.ops import flash
+    dev = torch.device("cuda")
+    B, H, T, D = 8, 10, 2048, 128
+    qkv = torch.randn(B, T, 3, H, D, device=dev).bfloat16()
+    q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
+    ms = _time(lambda: flash.flash_fwd_bthd(q, k, v, causal=True, window=None, scale=None), iters=3, warmup=2)
+    flops = 2.0 * B * H * T * T * D
+    results.append({"kernel": "flash_fwd_small", "ms": ms, "tflops": flops / ms / 1e9})
+    print(f"flash fwd small B{B} H{H} T{T}: {ms:7.3f} ms {flops / ms / 1e9:7.1f} TF/s", flush=True)
+
+
 def bench_attention_bwd_small(results):
     """One small backward case for profiler captures: B 8, H 10, T 2048 causal (q, k, v, o, dO and the gradients hold about
     0.3 GB), two warm-up and three timed calls."""
@@ -220,6 +233,8 @@ def main(argv):
         bench_attention(results)
     if what in ("attention-bwd", "all"):
         bench_attention_bwd(results)
+    if what == "attention-fwd-small":
+        bench_attention_fwd_small(results)
     if what == "attention-bwd-small":
         bench_attention_bwd_small(results)
     if what in ("moe", "all"):
