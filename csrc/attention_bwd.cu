@@ -285,9 +285,9 @@ flash_bwd_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           for (int c = 0; c < 16; ++c) {
             const float4 l = l4[c];
             pr[4 * c + 0] = exp2f(fmaf(__uint_as_float(t[4 * c + 0]), p.scale_log2, -l.x));
-            pr[4 * c + 1] = exp2f(fmaf(__uint_as_float(t[4 * c + 1]), p.scale_log2, -l.y));
+            pr[4 * c + 1] = exp2_poly(fmaf(__uint_as_float(t[4 * c + 1]), p.scale_log2, -l.y));
             pr[4 * c + 2] = exp2f(fmaf(__uint_as_float(t[4 * c + 2]), p.scale_log2, -l.z));
-            pr[4 * c + 3] = exp2f(fmaf(__uint_as_float(t[4 * c + 3]), p.scale_log2, -l.w));
+            pr[4 * c + 3] = exp2_poly(fmaf(__uint_as_float(t[4 * c + 3]), p.scale_log2, -l.w));
           }
         } else {
 #pragma unroll
@@ -604,7 +604,10 @@ flash_bwd_dq_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
                           (p.window <= 0 || j * BW_T > i * BW_T + BW_T - 1 + p.q_offset - p.window);
         if (full) {
 #pragma unroll
-          for (int c = 0; c < 64; ++c) pr[c] = exp2f(fmaf(__uint_as_float(t[c]), p.scale_log2, -lse2));
+          for (int c = 0; c < 64; c += 2) {           // every other exponential on the FMA pipe
+            pr[c] = exp2f(fmaf(__uint_as_float(t[c]), p.scale_log2, -lse2));
+            pr[c + 1] = exp2_poly(fmaf(__uint_as_float(t[c + 1]), p.scale_log2, -lse2));
+          }
         } else {
 #pragma unroll
           for (int c = 0; c < 64; ++c) {

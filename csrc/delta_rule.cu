@@ -6,63 +6,78 @@
 // Per (batch, value head) the state S is [dk, dv] fp32.  One step is
 //   S <- exp(g) * S;  kv = S^T k;  delta = beta * (v - kv);  S <- S + k delta^T;  out = S^T q
 // with q, k L2-normalised over dk and q scaled by dk^-1/2.  The step is bound by one read and one
-// write of S (2 * dk * dv * 4 bytes); the kernel below does exactly that: each thread owns one
-// state column, keeps its dk values in registers between the two reductions, and the CTA's accesses
-// to a state row are contiguous.  Semantics follow cc/src/tyr_qwen35.cpp:121-170 of the reference.
+// write of S (2 * dk * dv * 4 bytes); the kernel below does exactly that: a thread owns a quarter of one
+// state column, keeps those values in registers between the two reductions (finished across the four row
+// groups through shared memory), and the CTA's accesses to a state row are contiguous.  Semantics follow cc/src/tyr_qwen35.cpp:121-170 of the reference.
 #include "common.cuh"
 
 namespace tyr {
 
 template <int DK>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(512)
 gdr_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
                   const __nv_bfloat16* __restrict__ v, const float* __restrict__ g,
                   const float* __restrict__ beta, float* __restrict__ state, __nv_bfloat16* __restrict__ out,
                   int Hk, int Hv, int dv, long long q_bstride, long long v_bstride) {
+  // 128 state columns x 4 row groups per CTA: a thread keeps DK / 4 values of one column in registers; the two column
+  // reductions (S^T k and S^T q) are finished across the row groups through shared memory.
+  constexpr int RPT = DK / 4;
   __shared__ float sq[DK], sk[DK];
-  __shared__ float red[2][4];
+  __shared__ float red[2][16];
+  __shared__ float part[4][128];
   const int bh = blockIdx.x;
   const int b = bh / Hv, hv = bh % Hv;
   const int hk = hv / (Hv / Hk);
   const int tid = threadIdx.x;
+  const int cl = tid & 127, rg = tid >> 7;
   const __nv_bfloat16* qp = q + b * q_bstride + static_cast<long long>(hk) * DK;
   const __nv_bfloat16* kp = k + b * q_bstride + static_cast<long long>(hk) * DK;
-  // L2 norms of q and k (DK <= 128 * ceil: each thread takes DK/128 elements)
   float qs = 0.f, ks = 0.f;
-  for (int i = tid; i < DK; i += 128) {
-    const float a = __bfloat162float(qp[i]), c = __bfloat162float(kp[i]);
-    sq[i] = a; sk[i] = c;
-    qs += a * a; ks += c * c;
+  if (tid < DK) {
+    const float a = __bfloat162float(qp[tid]), c = __bfloat162float(kp[tid]);
+    sq[tid] = a; sk[tid] = c;
+    qs = a * a; ks = c * c;
   }
   qs = warp_sum(qs); ks = warp_sum(ks);
   if ((tid & 31) == 0) { red[0][tid >> 5] = qs; red[1][tid >> 5] = ks; }
   __syncthreads();
-  qs = red[0][0] + red[0][1] + red[0][2] + red[0][3];
-  ks = red[1][0] + red[1][1] + red[1][2] + red[1][3];
+  qs = 0.f; ks = 0.f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) { qs += red[0][i]; ks += red[1][i]; }
   const float qn = rsqrtf(qs + 1e-6f) * rsqrtf(static_cast<float>(DK));
   const float kn = rsqrtf(ks + 1e-6f);
   const float decay = __expf(g[bh]);
   const float bt = beta[bh];
   float* S = state + static_cast<long long>(bh) * DK * dv;
-  for (int col = blockIdx.y * 128 + tid; col < dv; col += gridDim.y * 128) {
-    float s[DK];
+  const int r0 = rg * RPT;
+  for (int col0 = blockIdx.y * 128; col0 < dv; col0 += gridDim.y * 128) {
+    const int col = col0 + cl;
+    const bool live = col < dv;
+    float s[RPT];
     float kv = 0.f;
 #pragma unroll
-    for (int r = 0; r < DK; ++r) {
-      s[r] = S[static_cast<long long>(r) * dv + col] * decay;
-      kv += s[r] * sk[r];
+    for (int r = 0; r < RPT; ++r) {
+      s[r] = live ? S[static_cast<long long>(r0 + r) * dv + col] * decay : 0.f;
+      kv += s[r] * sk[r0 + r];
     }
-    kv *= kn;
-    const float vt = __bfloat162float(v[b * v_bstride + static_cast<long long>(hv) * dv + col]);
+    part[rg][cl] = kv;
+    __syncthreads();
+    kv = (part[0][cl] + part[1][cl] + part[2][cl] + part[3][cl]) * kn;
+    __syncthreads();
+    const float vt = live ? __bfloat162float(v[b * v_bstride + static_cast<long long>(hv) * dv + col]) : 0.f;
     const float delta = (vt - kv) * bt * kn;       // k enters normalised: k_hat = kn * k
     float o = 0.f;
 #pragma unroll
-    for (int r = 0; r < DK; ++r) {
-      s[r] += sk[r] * delta;
-      o += s[r] * sq[r];
-      S[static_cast<long long>(r) * dv + col] = s[r];
+    for (int r = 0; r < RPT; ++r) {
+      s[r] += sk[r0 + r] * delta;
+      o += s[r] * sq[r0 + r];
+      if (live) S[static_cast<long long>(r0 + r) * dv + col] = s[r];
     }
-    out[(static_cast<long long>(bh)) * dv + col] = __float2bfloat16(o * qn);
+    part[rg][cl] = o;
+    __syncthreads();
+    if (rg == 0 && live)
+      out[(static_cast<long long>(bh)) * dv + col] = __float2bfloat16((part[0][cl] + part[1][cl] + part[2][cl] + part[3][cl]) * qn);
+    __syncthreads();
   }
 }
 
@@ -299,6 +314,7 @@ struct GdrPrepSmem {
   float gc[GC_C];
   float beta[GC_C];
   float eg[GC_C];        // exp(gc_i)
+  __nv_bfloat16 v[GC_C * 128];   // the chunk's value rows (dv <= 128), staged with 16-byte loads
 };
 
 struct GdrPrepArgs {
@@ -339,6 +355,13 @@ __global__ void __launch_bounds__(256, 2) gdr_chunk_prepare_kernel(GdrPrepArgs a
       sm.k[r * GC_LDW + d + 2 * e] = fk.x; sm.k[r * GC_LDW + d + 2 * e + 1] = fk.y;
     }
   }
+  for (int i = tid; i < GC_C * (a.dv / 8); i += 256) {
+    const int r = i / (a.dv / 8), d = (i % (a.dv / 8)) * 8;
+    const int tok = row0 + r;
+    uint4 uv = make_uint4(0, 0, 0, 0);
+    if (tok < a.S) uv = *reinterpret_cast<const uint4*>(a.v + b * a.v_sb + static_cast<long long>(tok) * a.v_ss + hv * a.v_sh + d);
+    *reinterpret_cast<uint4*>(&sm.v[r * a.dv + d]) = uv;
+  }
   if (tid < GC_C) {
     const int tok = row0 + tid;
     const long long gi = (static_cast<long long>(b) * a.S + tok) * a.Hv + hv;
@@ -363,14 +386,14 @@ __global__ void __launch_bounds__(256, 2) gdr_chunk_prepare_kernel(GdrPrepArgs a
   {
     const int r = tid >> 2, part = tid & 3;
     float sq = 0.f, sk = 0.f;
-    for (int d = part * 32; d < part * 32 + 32; ++d) {
+    for (int d = part; d < GC_DK; d += 4) {            // bank (4 r + part + 4 i): the 32 lanes hit 32 banks
       const float x = sm.q[r * GC_LDW + d], y = sm.k[r * GC_LDW + d];
       sq += x * x; sk += y * y;
     }
     sq += __shfl_xor_sync(0xffffffffu, sq, 1); sq += __shfl_xor_sync(0xffffffffu, sq, 2);
     sk += __shfl_xor_sync(0xffffffffu, sk, 1); sk += __shfl_xor_sync(0xffffffffu, sk, 2);
     const float qn = rsqrtf(sq + 1e-6f) * rsqrtf(static_cast<float>(GC_DK)), kn = rsqrtf(sk + 1e-6f);
-    for (int d = part * 32; d < part * 32 + 32; ++d) {
+    for (int d = part; d < GC_DK; d += 4) {
       sm.q[r * GC_LDW + d] *= qn;
       sm.k[r * GC_LDW + d] *= kn;
     }
@@ -437,12 +460,8 @@ __global__ void __launch_bounds__(256, 2) gdr_chunk_prepare_kernel(GdrPrepArgs a
       float x[GC_C];
       const bool is_v = col < a.dv;
       if (is_v) {
-        const __nv_bfloat16* vp = a.v + b * a.v_sb + hv * a.v_sh + col;
 #pragma unroll
-        for (int i = 0; i < GC_C; ++i) {
-          const int tok = row0 + i;
-          x[i] = tok < a.S ? __bfloat162float(vp[static_cast<long long>(tok) * a.v_ss]) * sm.beta[i] : 0.f;
-        }
+        for (int i = 0; i < GC_C; ++i) x[i] = __bfloat162float(sm.v[i * a.dv + col]) * sm.beta[i];
       } else {
 #pragma unroll
         for (int i = 0; i < GC_C; ++i) x[i] = sm.k[i * GC_LDW + (col - a.dv)] * sm.beta[i] * sm.eg[i];
@@ -486,45 +505,73 @@ __global__ void __launch_bounds__(256, 2) gdr_chunk_prepare_kernel(GdrPrepArgs a
 
 }  // namespace tyr
 
-// Causal depthwise conv1d (kernel taps K <= 8, zero history) + bias + SiLU on channels-last activations:
+// Causal depthwise conv1d (kernel taps K <= 4, zero history) + bias + SiLU on channels-last activations:
 //   y[b, s, c] = silu(bias[c] + sum_j w[c, j] * x[b, s - (K - 1) + j, c]).
-// One thread per (token, 8 channels); the taps of neighbouring tokens hit L1 / L2.  The reference transposes to channels-first
+// One thread per (32 tokens, 8 channels): its taps and a sliding window of K rows stay in registers, so every input row is
+// loaded once and a warp's accesses are 512 contiguous bytes.  The reference transposes to channels-first
 // and calls the library's grouped convolution (Tyr/Model/Qwen35/Model.lean:642-700).
 namespace tyr {
+constexpr int CONV_TOK = 32;      // tokens per thread: the taps and the sliding window stay in registers
+template <int K>
 __global__ void __launch_bounds__(256) causal_conv1d_silu_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ w,
                                                                  const float* __restrict__ bias, __nv_bfloat16* __restrict__ y,
-                                                                 long long total, int S, int C, int K, long long x_sb,
-                                                                 long long x_ss) {
+                                                                 long long total, int S, int C, long long x_sb, long long x_ss) {
   const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i >= total) return;
   const int c8 = C >> 3;
   const int c = static_cast<int>(i % c8) * 8;
-  const long long bs = i / c8;
-  const int s = static_cast<int>(bs % S);
-  const long long b = bs / S;
-  float acc[8];
+  const long long bt = i / c8;
+  const int nblk = (S + CONV_TOK - 1) / CONV_TOK;
+  const int s0 = static_cast<int>(bt % nblk) * CONV_TOK;
+  const long long b = bt / nblk;
+  float wt[8][K], bs[8];
 #pragma unroll
-  for (int e = 0; e < 8; ++e) acc[e] = bias ? bias[c + e] : 0.f;
-  for (int j = 0; j < K; ++j) {
-    const int t = s - (K - 1) + j;
-    if (t < 0) continue;
-    const uint4 u = *reinterpret_cast<const uint4*>(x + b * x_sb + static_cast<long long>(t) * x_ss + c);
+  for (int e = 0; e < 8; ++e) {
+    bs[e] = bias ? bias[c + e] : 0.f;
+#pragma unroll
+    for (int j = 0; j < K; ++j) wt[e][j] = w[(c + e) * K + j];
+  }
+  float win[K][8];                                   // win[j] = x[s - (K - 1) + j]
+  const __nv_bfloat16* xb = x + b * x_sb + c;
+  auto load_row = [&](int t, float (&dst)[8]) {
+    if (t < 0 || t >= S) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) dst[e] = 0.f;
+      return;
+    }
+    const uint4 u = *reinterpret_cast<const uint4*>(xb + static_cast<long long>(t) * x_ss);
     const uint32_t uu[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       const float2 f = unpack_bf16x2(uu[e]);
-      acc[2 * e] += f.x * w[(c + 2 * e) * K + j];
-      acc[2 * e + 1] += f.y * w[(c + 2 * e + 1) * K + j];
+      dst[2 * e] = f.x;
+      dst[2 * e + 1] = f.y;
     }
-  }
-  uint4 o;
-  uint32_t* oo = reinterpret_cast<uint32_t*>(&o);
+  };
 #pragma unroll
-  for (int e = 0; e < 4; ++e) {
-    const float a0 = acc[2 * e], a1 = acc[2 * e + 1];
-    oo[e] = pack_bf16x2(a0 / (1.f + __expf(-a0)), a1 / (1.f + __expf(-a1)));
+  for (int j = 0; j < K - 1; ++j) load_row(s0 - (K - 1) + j, win[j]);
+  for (int s = s0; s < min(S, s0 + CONV_TOK); ++s) {
+    load_row(s, win[K - 1]);
+    uint4 o;
+    uint32_t* oo = reinterpret_cast<uint32_t*>(&o);
+    float acc[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      acc[e] = bs[e];
+#pragma unroll
+      for (int j = 0; j < K; ++j) acc[e] += win[j][e] * wt[e][j];
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float a0 = acc[2 * e], a1 = acc[2 * e + 1];
+      oo[e] = pack_bf16x2(a0 / (1.f + __expf(-a0)), a1 / (1.f + __expf(-a1)));
+    }
+    *reinterpret_cast<uint4*>(y + (b * S + s) * C + c) = o;
+#pragma unroll
+    for (int j = 0; j < K - 1; ++j)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) win[j][e] = win[j + 1][e];
   }
-  *reinterpret_cast<uint4*>(y + (b * S + s) * C + c) = o;
 }
 }  // namespace tyr
 
@@ -532,11 +579,20 @@ __global__ void __launch_bounds__(256) causal_conv1d_silu_kernel(const __nv_bflo
 // y: bf16 [B, S, C] contiguous.  C must be a multiple of 8.
 extern "C" TYR_EXPORT int tyr_causal_conv1d_silu(const void* x, const float* w, const float* bias, void* y, int B, int S, int C,
                                                  int K, long long x_sb, long long x_ss, void* stream) {
-  if (B <= 0 || S <= 0 || C <= 0 || (C & 7) || K <= 0 || K > 8 || (x_sb & 7) || (x_ss & 7)) return -1;
+  if (B <= 0 || S <= 0 || C <= 0 || (C & 7) || K <= 0 || K > 4 || (x_sb & 7) || (x_ss & 7)) return -1;
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) return -2;
-  const long long total = static_cast<long long>(B) * S * (C >> 3);
-  tyr::causal_conv1d_silu_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      reinterpret_cast<const __nv_bfloat16*>(x), w, bias, reinterpret_cast<__nv_bfloat16*>(y), total, S, C, K, x_sb, x_ss);
+  const long long total = static_cast<long long>(B) * ((S + tyr::CONV_TOK - 1) / tyr::CONV_TOK) * (C >> 3);
+  const unsigned blocks = static_cast<unsigned>((total + 255) / 256);
+  auto* xx = reinterpret_cast<const __nv_bfloat16*>(x);
+  auto* yy = reinterpret_cast<__nv_bfloat16*>(y);
+  cudaStream_t cs = reinterpret_cast<cudaStream_t>(stream);
+  switch (K) {
+    case 1: tyr::causal_conv1d_silu_kernel<1><<<blocks, 256, 0, cs>>>(xx, w, bias, yy, total, S, C, x_sb, x_ss); break;
+    case 2: tyr::causal_conv1d_silu_kernel<2><<<blocks, 256, 0, cs>>>(xx, w, bias, yy, total, S, C, x_sb, x_ss); break;
+    case 3: tyr::causal_conv1d_silu_kernel<3><<<blocks, 256, 0, cs>>>(xx, w, bias, yy, total, S, C, x_sb, x_ss); break;
+    case 4: tyr::causal_conv1d_silu_kernel<4><<<blocks, 256, 0, cs>>>(xx, w, bias, yy, total, S, C, x_sb, x_ss); break;
+    default: return -3;
+  }
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -549,9 +605,9 @@ extern "C" TYR_EXPORT int tyr_gdr_chunk_prepare(const void* q, const void* k, co
                                                 int Hk, int Hv, int dk, int dv, void* stream) {
   using namespace tyr;
   if (B <= 0 || S <= 0 || Hk <= 0 || Hv <= 0 || Hv % Hk || dk != GC_DK || (dv != 64 && dv != 128)) return -1;
-  for (int i = 0; i < 6; ++i)
+  for (int i = 0; i < 9; ++i)
     if (strides[i] & 7) return -3;
-  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k)) & 15) return -4;
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15) return -4;
   GdrPrepArgs a;
   a.q = reinterpret_cast<const __nv_bfloat16*>(q);
   a.k = reinterpret_cast<const __nv_bfloat16*>(k);
@@ -611,9 +667,9 @@ extern "C" TYR_EXPORT int tyr_gdr_decode(const void* q, const void* k, const voi
   auto* vv = reinterpret_cast<const __nv_bfloat16*>(v);
   auto* oo = reinterpret_cast<__nv_bfloat16*>(out);
   if (dk == 128)
-    gdr_decode_kernel<128><<<grid, 128, 0, st>>>(qq, kk, vv, g, beta, state, oo, Hk, Hv, dv, q_bstride, v_bstride);
+    gdr_decode_kernel<128><<<grid, 512, 0, st>>>(qq, kk, vv, g, beta, state, oo, Hk, Hv, dv, q_bstride, v_bstride);
   else if (dk == 64)
-    gdr_decode_kernel<64><<<grid, 128, 0, st>>>(qq, kk, vv, g, beta, state, oo, Hk, Hv, dv, q_bstride, v_bstride);
+    gdr_decode_kernel<64><<<grid, 512, 0, st>>>(qq, kk, vv, g, beta, state, oo, Hk, Hv, dv, q_bstride, v_bstride);
   else
     return -2;
   return static_cast<int>(cudaGetLastError());

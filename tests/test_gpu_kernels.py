@@ -499,4 +499,4 @@ def test_causal_conv1d_silu_matches_library(B, S, C, K, bias):
     y = DR.causal_conv1d_silu(x, w, b)
     xc = x.float().transpose(1, 2)
     ref = torch.nn.functional.silu(torch.nn.functional.conv1d(torch.nn.functional.pad(xc, (K - 1, 0)), w.reshape(C, 1, K), b, groups=C)).transpose(1, 2)
-    assert y.shape == (B, S, C) and (y.float() - ref).abs().max() < 3e-2
+    assert y.shape == (B, S, C) and (y.float() - ref).abs().max() < 1e-2 * max(1.0, ref.abs().max().item())

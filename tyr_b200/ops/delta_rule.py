@@ -67,7 +67,7 @@ def chunk_kernels_supported(q, k, v, chunk_size: int = 64) -> bool:
     q and k may carry fewer heads than v (grouped keys)."""
     ok_view = lambda t: t.stride(3) == 1 and all(x % 8 == 0 for x in t.stride()[:3]) and t.data_ptr() % 16 == 0
     return (_CHUNK_KERNEL and q.is_cuda and q.dtype == k.dtype == v.dtype == torch.bfloat16 and q.shape[-1] == 128 and v.shape[-1] in (64, 128)
-            and chunk_size == 64 and v.shape[2] % q.shape[2] == 0 and q.shape[2] == k.shape[2] and ok_view(q) and ok_view(k) and v.stride(3) == 1
+            and chunk_size == 64 and v.shape[2] % q.shape[2] == 0 and q.shape[2] == k.shape[2] and ok_view(q) and ok_view(k) and ok_view(v)
             and hasattr(lib(), "tyr_gdr_chunk_prepare") and hasattr(lib(), "tyr_gdr_chunk_scan"))
 
 
@@ -97,7 +97,7 @@ def causal_conv1d_silu(x: torch.Tensor, weight: torch.Tensor, bias: Optional[tor
     """x: [B, S, C] (channels last), weight: [C, K] -> silu(causal depthwise conv + bias) as [B, S, C], zero history."""
     B, S, C = x.shape
     K = weight.shape[-1]
-    if (x.is_cuda and x.dtype == torch.bfloat16 and C % 8 == 0 and K <= 8 and x.stride(2) == 1 and x.stride(0) % 8 == 0 and x.stride(1) % 8 == 0
+    if (x.is_cuda and x.dtype == torch.bfloat16 and C % 8 == 0 and K <= 4 and x.stride(2) == 1 and x.stride(0) % 8 == 0 and x.stride(1) % 8 == 0
             and x.data_ptr() % 16 == 0 and hasattr(lib(), "tyr_causal_conv1d_silu")):
         y = torch.empty((B, S, C), dtype=x.dtype, device=x.device)
         wf = weight.reshape(C, K).float().contiguous()
