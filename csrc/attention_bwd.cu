@@ -21,9 +21,9 @@
 // delta = rowsum(dO o O) and rescales the log-sum-exp to base 2 into padded rows.
 //
 // dK / dV kernel:
-//   warps 0-3   scores: query-row columns  0..63  of the block (one thread per key / TMEM lane)
-//   warps 4-7   scores: query-row columns 64..127
-//   warp 12     MMA issuer, warp 13 TMA producer (Q_i, dO_i, lse_i, delta_i into a 2-stage ring)
+//   warps 0-15  scores: four warpgroups, each 32 of the block's 128 query-row columns (one thread per key / TMEM lane);
+//               four score warps per scheduler hide each other's TMEM-load, exp2 and packing latencies
+//   warp 16     MMA issuer, warp 17 TMA producer (Q_i, dO_i, lse_i, delta_i into a 2-stage ring)
 //
 // Masks are those of the forward kernel: causal with offset, sliding window, key length.  Query rows
 // past Tq carry lse = +inf in the padded statistics, so their probabilities are exactly zero.
@@ -91,7 +91,7 @@ __device__ __forceinline__ void q_range(const BwdParams& p, int j, int& lo, int&
   if (hi < lo) hi = lo;
 }
 
-__global__ void __launch_bounds__(512, 1)
+__global__ void __launch_bounds__(640, 1)
 flash_bwd_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                       const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                       BwdParams p) {
@@ -121,13 +121,13 @@ flash_bwd_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     }
     mbar_init(&s.s_ready, 1);
     mbar_init(&s.dp_ready, 1);
-    mbar_init(&s.p_ready, 256);
-    mbar_init(&s.ds_ready, 256);
+    mbar_init(&s.p_ready, 512);
+    mbar_init(&s.ds_ready, 512);
     mbar_init(&s.ds_free, 1);
     mbar_init(&s.acc_done, 1);
     mbar_fence_init();
   }
-  if (warp == 12) {
+  if (warp == 16) {
     tmem_alloc(&s.tmem_base, 512);
     tmem_relinquish();
   }
@@ -137,9 +137,9 @@ flash_bwd_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   const uint32_t tmem_base = s.tmem_base;
   constexpr uint32_t COL_S = 0, COL_DV = 128, COL_DP = 256, COL_DK = 384;
 
-  if (warp >= 12) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
-    if (warp == 13) {
+  if (warp >= 16) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+    if (warp == 17) {
       // ---------------------------------------------------------------- TMA producer
       if (elect_one() && n_it > 0) {
         tma_prefetch_desc(&tmQ);
@@ -177,7 +177,7 @@ flash_bwd_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           }
         }
       }
-    } else if (warp == 12) {
+    } else if (warp == 16) {
       // ---------------------------------------------------------------- MMA issuer
       if (elect_one() && n_it > 0) {
         constexpr uint32_t idesc_kk = make_idesc_f16(1, BW_T, BW_T, 0, 0);   // both operands K-major
@@ -209,13 +209,13 @@ flash_bwd_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           const int st = it & 1;
           const uint32_t par = it & 1;
           const uint32_t qa = smem_u32(s.q[st]), doa = smem_u32(s.dout[st]);
-          // dV += P^T dO_i : A from TMEM (16 bf16 per K step = 8 columns; the two score warpgroups
-          // packed their halves at columns 0 and 64), B = dO_i [rows][d] MN-major
+          // dV += P^T dO_i : A from TMEM (16 bf16 per K step = 8 columns; the four score warpgroups
+          // packed their quarters at columns 0, 32, 64 and 96), B = dO_i [rows][d] MN-major
           if (!mbar_wait(&s.p_ready, par, p.err, 830)) { ok = false; break; }
           tc_fence_after();
 #pragma unroll
           for (int k = 0; k < BW_T / 16; ++k)
-            umma_f16_ts(tmem_base + COL_DV, tmem_base + COL_S + (k >> 2) * 64 + (k & 3) * 8,
+            umma_f16_ts(tmem_base + COL_DV, tmem_base + COL_S + (k >> 1) * 32 + (k & 1) * 8,
                         make_smem_desc_sw128(doa + k * 2048, BW_CHUNK, 1024), idesc_kn,
                         (it == 0 && k == 0) ? 0u : 1u);
           if (it + 1 < n_it) {
@@ -246,52 +246,49 @@ flash_bwd_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         if (ok) umma_commit(&s.acc_done);
       }
     }
-  } else if (warp >= 8) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 96;");      // idle warpgroup: hands its registers to the score warps
   } else {
-    // ------------------------------------------------------------------ score warps
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 168;");
+    // ------------------------------------------------------------------ score warps: 4 warpgroups x 32 query-row columns
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 104;");
     const int wg = warp >> 2;
     const int r = (warp & 3) * 32 + lane;                // key row of this thread inside the block
     const int key = j * BW_T + r;
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const uint32_t s_addr = tmem_base + COL_S + wg * 64 + lane_addr;
-    const uint32_t dp_addr = tmem_base + COL_DP + wg * 64 + lane_addr;
+    const uint32_t s_addr = tmem_base + COL_S + wg * 32 + lane_addr;
+    const uint32_t dp_addr = tmem_base + COL_DP + wg * 32 + lane_addr;
     const int rmin = p.causal ? key - p.q_offset : INT_MIN;                 // rows that see this key: [rmin, rmax)
     const int rmax = p.window > 0 ? key - p.q_offset + p.window : INT_MAX;
     const bool key_ok = key < p.Tk;
-    uint8_t* ds_row = s.ds + wg * BW_CHUNK + r * 128;
+    uint8_t* ds_row = s.ds + (wg >> 1) * BW_CHUNK + r * 128;
     bool ok = true;
     for (int it = 0; it < n_it && ok; ++it) {
       const int st = it & 1;
       const uint32_t ph = (it >> 1) & 1;
       const int i = ilo + it % ni;
-      const int row0 = i * BW_T + wg * 64;               // first query row of this thread's columns
+      const int row0 = i * BW_T + wg * 32;               // first query row of this thread's columns
       if (!mbar_wait(&s.q_full[st], ph, p.err, 850)) { ok = false; break; }
       if (!mbar_wait(&s.s_ready, it & 1, p.err, 851)) { ok = false; break; }
       tc_fence_after();
-      float pr[64];
+      float pr[32];
       {
-        uint32_t t[64];
-        tmem_ld_32x32(s_addr, *reinterpret_cast<uint32_t(*)[32]>(t));
-        tmem_ld_32x32(s_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(t + 32));
+        uint32_t t[32];
+        tmem_ld_32x32(s_addr, t);
         tmem_wait_ld();
         const int blk_lo = i * BW_T, blk_hi = i * BW_T + BW_T - 1;
         const bool full = (j * BW_T + BW_T <= p.Tk) && (!p.causal || j * BW_T + BW_T - 1 <= blk_lo + p.q_offset) &&
                           (p.window <= 0 || j * BW_T > blk_hi + p.q_offset - p.window);
-        const float4* l4 = reinterpret_cast<const float4*>(&s.lse[st][wg * 64]);
+        const float4* l4 = reinterpret_cast<const float4*>(&s.lse[st][wg * 32]);
         if (full) {
 #pragma unroll
-          for (int c = 0; c < 16; ++c) {
+          for (int c = 0; c < 8; ++c) {
             const float4 l = l4[c];
             pr[4 * c + 0] = exp2f(fmaf(__uint_as_float(t[4 * c + 0]), p.scale_log2, -l.x));
-            pr[4 * c + 1] = exp2_poly(fmaf(__uint_as_float(t[4 * c + 1]), p.scale_log2, -l.y));
+            pr[4 * c + 1] = exp2f(fmaf(__uint_as_float(t[4 * c + 1]), p.scale_log2, -l.y));
             pr[4 * c + 2] = exp2f(fmaf(__uint_as_float(t[4 * c + 2]), p.scale_log2, -l.z));
-            pr[4 * c + 3] = exp2_poly(fmaf(__uint_as_float(t[4 * c + 3]), p.scale_log2, -l.w));
+            pr[4 * c + 3] = exp2f(fmaf(__uint_as_float(t[4 * c + 3]), p.scale_log2, -l.w));
           }
         } else {
 #pragma unroll
-          for (int c = 0; c < 16; ++c) {
+          for (int c = 0; c < 8; ++c) {
             const float4 l = l4[c];
             const float lv[4] = {l.x, l.y, l.z, l.w};
 #pragma unroll
@@ -303,13 +300,12 @@ flash_bwd_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           }
         }
       }
-      // P^T as packed bf16 over this warpgroup's own score columns
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      // P^T as packed bf16 over the first 16 of this warpgroup's own 32 score columns
+      {
         uint32_t pk[16];
 #pragma unroll
-        for (int q = 0; q < 16; ++q) pk[q] = pack_bf16x2(pr[c * 32 + 2 * q], pr[c * 32 + 2 * q + 1]);
-        tmem_st_32x16(s_addr + c * 16, pk);
+        for (int q = 0; q < 16; ++q) pk[q] = pack_bf16x2(pr[2 * q], pr[2 * q + 1]);
+        tmem_st_32x16(s_addr, pk);
       }
       tmem_wait_st();
       tc_fence_before();
@@ -318,22 +314,21 @@ flash_bwd_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       if (!mbar_wait(&s.dp_ready, it & 1, p.err, 853)) { ok = false; break; }
       if (it > 0 && !mbar_wait(&s.ds_free, (it - 1) & 1, p.err, 854)) { ok = false; break; }   // dK of the previous block has read dS
       tc_fence_after();
-      const float4* d4 = reinterpret_cast<const float4*>(&s.delta[st][wg * 64]);
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      const float4* d4 = reinterpret_cast<const float4*>(&s.delta[st][wg * 32]);
+      {
         uint32_t t[32];
-        tmem_ld_32x32(dp_addr + c * 32, t);
+        tmem_ld_32x32(dp_addr, t);
         tmem_wait_ld();
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
-          const float4 da = d4[c * 8 + u * 2], db = d4[c * 8 + u * 2 + 1];
-          const float* pp = pr + c * 32 + u * 8;
+          const float4 da = d4[u * 2], db = d4[u * 2 + 1];
+          const float* pp = pr + u * 8;
           uint4 w;
           w.x = pack_bf16x2(pp[0] * (__uint_as_float(t[u * 8 + 0]) - da.x), pp[1] * (__uint_as_float(t[u * 8 + 1]) - da.y));
           w.y = pack_bf16x2(pp[2] * (__uint_as_float(t[u * 8 + 2]) - da.z), pp[3] * (__uint_as_float(t[u * 8 + 3]) - da.w));
           w.z = pack_bf16x2(pp[4] * (__uint_as_float(t[u * 8 + 4]) - db.x), pp[5] * (__uint_as_float(t[u * 8 + 5]) - db.y));
           w.w = pack_bf16x2(pp[6] * (__uint_as_float(t[u * 8 + 6]) - db.z), pp[7] * (__uint_as_float(t[u * 8 + 7]) - db.w));
-          const int unit = c * 4 + u;
+          const int unit = (wg & 1) * 4 + u;
           *reinterpret_cast<uint4*>(ds_row + ((unit ^ (r & 7)) << 4)) = w;
         }
       }
@@ -345,13 +340,14 @@ flash_bwd_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     if (ok && n_it > 0) ok = mbar_wait(&s.acc_done, 0, p.err, 860);
     tc_fence_after();
     if (ok) {
-      // warpgroup 0 writes dV, warpgroup 1 writes dK (scaled)
-      const uint32_t src = tmem_base + (wg == 0 ? COL_DV : COL_DK) + lane_addr;
-      const float f = wg == 0 ? 1.f : p.scale;
-      __nv_bfloat16* out = wg == 0 ? p.dV + batch * p.dv_sb + static_cast<long long>(key) * p.dv_st + kvh * p.dv_sh
-                                   : p.dK + batch * p.dk_sb + static_cast<long long>(key) * p.dk_st + kvh * p.dk_sh;
+      // warpgroups 0, 1 write the two channel halves of dV, warpgroups 2, 3 those of dK (scaled)
+      const bool is_dv = wg < 2;
+      const uint32_t src = tmem_base + (is_dv ? COL_DV : COL_DK) + (wg & 1) * 64 + lane_addr;
+      const float f = is_dv ? 1.f : p.scale;
+      __nv_bfloat16* out = (is_dv ? p.dV + batch * p.dv_sb + static_cast<long long>(key) * p.dv_st + kvh * p.dv_sh
+                                  : p.dK + batch * p.dk_sb + static_cast<long long>(key) * p.dk_st + kvh * p.dk_sh) + (wg & 1) * 64;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t o[32];
         if (n_it > 0) {
           tmem_ld_32x32(src + c * 32, o);
@@ -377,7 +373,7 @@ flash_bwd_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 12) {
+  if (warp == 16) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
@@ -416,8 +412,8 @@ __global__ void flash_bwd_prepare_kernel(const __nv_bfloat16* __restrict__ dO, c
 // dQ: one CTA per 128-row query block of one (batch, head).  Q_i and dO_i stay in shared memory, K_j / V_j stream through a
 // 2-stage ring; per key block:  S = Q_i K_j^T (TMEM columns 0..127), dP = dO_i V_j^T (128..255), the score warps turn them
 // into dS = P o (dP - delta) in shared memory ([rows][keys], K-major A), and dQ_i += dS K_j accumulates at columns 256..383.
-//   warps 0-3   scores: key columns 0..63 (one thread per query row / TMEM lane), warps 4-7: key columns 64..127
-//   warp 8      MMA issuer, warp 9 TMA producer
+//   warps 0-15  scores: four warpgroups of 32 key columns each (one thread per query row / TMEM lane)
+//   warp 16     MMA issuer, warp 17 TMA producer
 // ------------------------------------------------------------------------------------------------------------------
 struct __align__(1024) DqSmem {
   uint8_t q[BW_TILE];
@@ -443,7 +439,7 @@ __device__ __forceinline__ void k_range(const BwdParams& p, int r0, int& lo, int
   if (hi < lo) hi = lo;
 }
 
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(576, 1)
 flash_bwd_dq_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                          const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO, BwdParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -471,12 +467,12 @@ flash_bwd_dq_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
     }
     mbar_init(&s.s_ready, 1);
     mbar_init(&s.dp_ready, 1);
-    mbar_init(&s.ds_ready, 256);
+    mbar_init(&s.ds_ready, 512);
     mbar_init(&s.ds_free, 1);
     mbar_init(&s.acc_done, 1);
     mbar_fence_init();
   }
-  if (warp == 8) {
+  if (warp == 16) {
     tmem_alloc(&s.tmem_base, 512);
     tmem_relinquish();
   }
@@ -486,7 +482,7 @@ flash_bwd_dq_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
   const uint32_t tmem_base = s.tmem_base;
   constexpr uint32_t COL_S = 0, COL_DP = 128, COL_DQ = 256;
 
-  if (warp == 9) {
+  if (warp == 17) {
     // ------------------------------------------------------------------ TMA producer
     if (elect_one() && n_it > 0) {
       tma_prefetch_desc(&tmQ);
@@ -519,7 +515,7 @@ flash_bwd_dq_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
         }
       }
     }
-  } else if (warp == 8) {
+  } else if (warp == 16) {
     // ------------------------------------------------------------------ MMA issuer
     if (elect_one() && n_it > 0) {
       constexpr uint32_t idesc_kk = make_idesc_f16(1, BW_T, BW_T, 0, 0);
@@ -575,42 +571,41 @@ flash_bwd_dq_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
       if (ok) umma_commit(&s.acc_done);
     }
   } else {
-    // ------------------------------------------------------------------ score warps
+    // ------------------------------------------------------------------ score warps: 4 warpgroups x 32 key columns
     const int wg = warp >> 2;
     const int r = (warp & 3) * 32 + lane;                 // query row of this thread inside the block
     const int row = i * BW_T + r;
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const uint32_t s_addr = tmem_base + COL_S + wg * 64 + lane_addr;
-    const uint32_t dp_addr = tmem_base + COL_DP + wg * 64 + lane_addr;
+    const uint32_t s_addr = tmem_base + COL_S + wg * 32 + lane_addr;
+    const uint32_t dp_addr = tmem_base + COL_DP + wg * 32 + lane_addr;
     const long long stat = (static_cast<long long>(batch) * p.Hq + head) * p.Tpad + row;
     const float lse2 = p.lse2[stat];                      // +inf on padded / empty rows: their probabilities are 0
     const float delta = p.delta[stat];
     const int kmin = p.window > 0 ? row + p.q_offset - p.window + 1 : INT_MIN;      // keys this row sees: [kmin, kmax]
     const int kmax = min(p.Tk - 1, p.causal ? row + p.q_offset : INT_MAX);
-    uint8_t* ds_row = s.ds + wg * BW_CHUNK + r * 128;
+    uint8_t* ds_row = s.ds + (wg >> 1) * BW_CHUNK + r * 128;
     bool ok = true;
     for (int it = 0; it < n_it && ok; ++it) {
       const int j = jlo + it;
-      const int key0 = j * BW_T + wg * 64;
+      const int key0 = j * BW_T + wg * 32;
       if (!mbar_wait(&s.s_ready, it & 1, p.err, 950)) { ok = false; break; }
       tc_fence_after();
-      float pr[64];
+      float pr[32];
       {
-        uint32_t t[64];
-        tmem_ld_32x32(s_addr, *reinterpret_cast<uint32_t(*)[32]>(t));
-        tmem_ld_32x32(s_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(t + 32));
+        uint32_t t[32];
+        tmem_ld_32x32(s_addr, t);
         tmem_wait_ld();
         const bool full = (j * BW_T + BW_T <= p.Tk) && (!p.causal || j * BW_T + BW_T - 1 <= i * BW_T + p.q_offset) &&
                           (p.window <= 0 || j * BW_T > i * BW_T + BW_T - 1 + p.q_offset - p.window);
         if (full) {
 #pragma unroll
-          for (int c = 0; c < 64; c += 2) {           // every other exponential on the FMA pipe
+          for (int c = 0; c < 32; c += 2) {           
             pr[c] = exp2f(fmaf(__uint_as_float(t[c]), p.scale_log2, -lse2));
-            pr[c + 1] = exp2_poly(fmaf(__uint_as_float(t[c + 1]), p.scale_log2, -lse2));
+            pr[c + 1] = exp2f(fmaf(__uint_as_float(t[c + 1]), p.scale_log2, -lse2));
           }
         } else {
 #pragma unroll
-          for (int c = 0; c < 64; ++c) {
+          for (int c = 0; c < 32; ++c) {
             const int key = key0 + c;
             pr[c] = (key >= kmin && key <= kmax) ? exp2f(fmaf(__uint_as_float(t[c]), p.scale_log2, -lse2)) : 0.f;
           }
@@ -619,20 +614,19 @@ flash_bwd_dq_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
       if (!mbar_wait(&s.dp_ready, it & 1, p.err, 951)) { ok = false; break; }
       if (it > 0 && !mbar_wait(&s.ds_free, (it - 1) & 1, p.err, 952)) { ok = false; break; }   // dQ of the previous block has read dS
       tc_fence_after();
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      {
         uint32_t t[32];
-        tmem_ld_32x32(dp_addr + c * 32, t);
+        tmem_ld_32x32(dp_addr, t);
         tmem_wait_ld();
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
-          const float* pp = pr + c * 32 + u * 8;
+          const float* pp = pr + u * 8;
           uint4 w;
           w.x = pack_bf16x2(pp[0] * (__uint_as_float(t[u * 8 + 0]) - delta), pp[1] * (__uint_as_float(t[u * 8 + 1]) - delta));
           w.y = pack_bf16x2(pp[2] * (__uint_as_float(t[u * 8 + 2]) - delta), pp[3] * (__uint_as_float(t[u * 8 + 3]) - delta));
           w.z = pack_bf16x2(pp[4] * (__uint_as_float(t[u * 8 + 4]) - delta), pp[5] * (__uint_as_float(t[u * 8 + 5]) - delta));
           w.w = pack_bf16x2(pp[6] * (__uint_as_float(t[u * 8 + 6]) - delta), pp[7] * (__uint_as_float(t[u * 8 + 7]) - delta));
-          const int unit = c * 4 + u;
+          const int unit = (wg & 1) * 4 + u;
           *reinterpret_cast<uint4*>(ds_row + ((unit ^ (r & 7)) << 4)) = w;
         }
       }
@@ -640,14 +634,14 @@ flash_bwd_dq_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
       tc_fence_before();
       mbar_arrive(&s.ds_ready);
     }
-    // ---------------------------------------------------------------- dQ epilogue: each warpgroup writes 64 channels
+    // ---------------------------------------------------------------- dQ epilogue: each warpgroup writes 32 channels
     if (ok && n_it > 0) ok = mbar_wait(&s.acc_done, 0, p.err, 960);
     tc_fence_after();
     if (ok) {
-      const uint32_t src = tmem_base + COL_DQ + wg * 64 + lane_addr;
-      __nv_bfloat16* out = p.dQ + batch * p.dq_sb + static_cast<long long>(row) * p.dq_st + head * p.dq_sh + wg * 64;
+      const uint32_t src = tmem_base + COL_DQ + wg * 32 + lane_addr;
+      __nv_bfloat16* out = p.dQ + batch * p.dq_sb + static_cast<long long>(row) * p.dq_st + head * p.dq_sh + wg * 32;
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      for (int c = 0; c < 1; ++c) {
         uint32_t o[32];
         if (n_it > 0) {
           tmem_ld_32x32(src + c * 32, o);
@@ -673,7 +667,7 @@ flash_bwd_dq_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 8) {
+  if (warp == 16) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
@@ -780,8 +774,8 @@ extern "C" TYR_EXPORT int tyr_flash_bwd(const void* dout, const void* q, const v
   p.dq_sb = sdq[0]; p.dq_st = sdq[1]; p.dq_sh = sdq[2];
   p.err = err;
   dim3 grid((Tk + BW_T - 1) / BW_T, Hkv, B);
-  flash_bwd_d128_kernel<<<grid, 512, smem, cs>>>(tq, tk, tv, tdo, p);
-  flash_bwd_dq_d128_kernel<<<dim3((Tq + BW_T - 1) / BW_T, Hq, B), 320, smem_dq, cs>>>(tq, tk, tv, tdo, p);
+  flash_bwd_d128_kernel<<<grid, 640, smem, cs>>>(tq, tk, tv, tdo, p);
+  flash_bwd_dq_d128_kernel<<<dim3((Tq + BW_T - 1) / BW_T, Hq, B), 576, smem_dq, cs>>>(tq, tk, tv, tdo, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 2000 + (int)e;
 }

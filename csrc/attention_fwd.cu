@@ -330,7 +330,7 @@ flash_fwd_d128_kernel(const __grid_constant__ CUtensorMap tmQ,
 #pragma unroll
           for (int q = 0; q < 16; ++q) {
             const float p0 = exp2f(fmaf(__uint_as_float(r[c * 32 + 2 * q]), p.scale_log2, neg_m));
-            const float p1 = exp2_poly(fmaf(__uint_as_float(r[c * 32 + 2 * q + 1]), p.scale_log2, neg_m));
+            const float p1 = exp2f(fmaf(__uint_as_float(r[c * 32 + 2 * q + 1]), p.scale_log2, neg_m));
             pk[q] = pack_bf16x2(p0, p1);
             ls4[q & 3] += p0 + p1;
           }

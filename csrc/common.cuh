@@ -320,20 +320,6 @@ __device__ __forceinline__ float warp_max(float v) {
   for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
   return v;
 }
-// exp2 for x <= 0 on the FMA / ALU pipes: x = n + f with n the nearest integer, 2^f by a degree-4 polynomial on [-0.5, 0.5]
-// (relative error 7e-6, far below bf16 resolution), 2^n added into the exponent field.  Half of the probabilities take this
-// path so that the special-function unit (ex2 and the bf16 conversions, 16 lanes per SM) stops being the bound.
-__device__ __forceinline__ float exp2_poly(float x) {
-  x = fmaxf(x, -126.f);
-  const float t = x + 12582912.f;                    // 1.5 * 2^23: n lands in the low mantissa bits
-  const float f = x - (t - 12582912.f);
-  float p = fmaf(f, 0.00966725f, 0.0558755f);
-  p = fmaf(p, f, 0.24022309f);
-  p = fmaf(p, f, 0.69312727f);
-  p = fmaf(p, f, 1.f);
-  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
-}
-
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
