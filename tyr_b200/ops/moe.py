@@ -183,7 +183,7 @@ def layout(ids: torch.Tensor, counts: torch.Tensor, want_tiles: bool = False, wa
     if ids.is_cuda:
         meta = torch.empty(4 * E + 3, dtype=torch.int32, device=ids.device)
         offsets, tiles, cursors, active = meta[:E + 1], meta[E + 1:2 * E + 2], meta[2 * E + 2:3 * E + 2], meta[3 * E + 2:]
-        op = torch.empty(2 * pairs, dtype=torch.int32, device=ids.device)
+        op = torch.zeros(2 * pairs, dtype=torch.int32, device=ids.device)     # positions no routed pair fills (padding ids) must stay valid indices
         order, pos = op[:pairs], op[pairs:]
         check(lib().tyr_moe_layout(ptr(ids.contiguous()), ptr(counts), ptr(offsets), ptr(cursors), ptr(tiles), ptr(active),
                                    ptr(order), ptr(pos), pairs, E, cur_stream(ids.device)), "moe_layout")
