@@ -36,7 +36,7 @@ struct GemmParams {
   const __nv_bfloat16* aux;
   long long ldc, ldaux, sC, sAux;
   float alpha, beta;
-  int act;        // 0 none, 1 relu(x)^2, 2 relu, 3 acc * 2*sqrt(aux), 4 SwiGLU of column halves
+  int act;        // 0 none, 1 relu(x)^2, 2 relu, 3 acc * 2*sqrt(aux), 4 SwiGLU of column halves, 5 GELU(tanh)-gate of column halves
   int out_mode;   // 0 bf16 store, 1 fp32 store, 2 fp32 atomic add (stream-K)
   int* err;
   // Grouped mode (MoE): batch = number of groups, A and C are packed [rows, *] with group g owning
@@ -342,7 +342,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     // bf16 outputs leave through shared memory and TMA stores (full 128-byte rows; also the efficient
     // packet size for stores that cross NVLink in tp_mode 1); grouped / SwiGLU outputs need row masks
     // and keep the direct stores.
-    const bool tma_out = p.out_mode == 0 && p.group_offsets == nullptr && p.act != 4;
+    const bool tma_out = p.out_mode == 0 && p.group_offsets == nullptr && p.act != 4 && p.act != 5;
     uint32_t n_stores = 0;
     while (ok && next_segment(cursor, tile, kb0, kb1)) {
       int bi, m0, n0;
@@ -374,8 +374,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
         c_base = p.peer_c[owner];
         c_off = (static_cast<long long>(p.tp_rank) * p.rows_per_rank + (row - owner * p.rows_per_rank)) * p.ldc;
       }
-      if (p.act == 4) {
-        // SwiGLU over column halves of the tile: out[:, n0/2 + j] = silu(acc[:, j]) * acc[:, BN/2 + j]
+      if (p.act == 4 || p.act == 5) {
+        // gated MLP over column halves of the tile: out[:, n0/2 + j] = act(acc[:, j]) * acc[:, BN/2 + j], act = SiLU (4) or
+        // tanh-GELU (5)
 #pragma unroll 1
         for (int c = 0; c < BN / 64; ++c) {
           uint32_t rg[32], ru[32];
@@ -394,7 +395,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             const float g = p.alpha * __uint_as_float(rg[j]);
-            v[j] = g / (1.f + __expf(-g)) * (p.beta * __uint_as_float(ru[j]));
+            const float a = p.act == 4 ? g / (1.f + __expf(-g))
+                                       : 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+            v[j] = a * (p.beta * __uint_as_float(ru[j]));
           }
           if (col + 32 <= p.N / 2) {
 #pragma unroll
@@ -754,7 +757,7 @@ static int gemm_impl(const TyrGemmArgs& a, const TyrTpArgs* tpa) {
     r = make_tmap_bf16_3d(&tmB, a.B, a.N, a.K, a.batch, a.ldb, a.sB, BK);
   if (r) return 4000 + r;
   CUtensorMap tmC{};
-  if (a.out_mode == 0 && a.group_offsets == nullptr && a.act != 4) {
+  if (a.out_mode == 0 && a.group_offsets == nullptr && a.act != 4 && a.act != 5) {
     if (tpa != nullptr && tpa->mode == 1) {
       for (int i = 0; i < tpa->world; ++i) {
         r = make_tmap_bf16_3d(&tmP.m[i], tpa->peers[i], a.N, static_cast<uint64_t>(tpa->world) * tpa->rows_per_rank, 1,

@@ -500,3 +500,18 @@ def test_causal_conv1d_silu_matches_library(B, S, C, K, bias):
     xc = x.float().transpose(1, 2)
     ref = torch.nn.functional.silu(torch.nn.functional.conv1d(torch.nn.functional.pad(xc, (K - 1, 0)), w.reshape(C, 1, K), b, groups=C)).transpose(1, 2)
     assert y.shape == (B, S, C) and (y.float() - ref).abs().max() < 1e-2 * max(1.0, ref.abs().max().item())
+
+
+@pytest.mark.parametrize("act", ["swiglu", "geglu"])
+def test_moe_dense_grouped_gemm_gate_epilogues(act):
+    """Dense expert banks through the grouped tcgen05 GEMM with the SiLU / tanh-GELU gate in the epilogue against the fp32 expert loop."""
+    from tyr_b200.ops import moe
+    g = torch.Generator(device="cuda").manual_seed(3)
+    T, E, k, h, mi = 200, 8, 2, 256, 384
+    x = torch.randn(T, h, device=_dev(), generator=g).bfloat16()
+    gate_up = (torch.randn(E, 2 * mi, h, device=_dev(), generator=g) * h ** -0.5).bfloat16()
+    down = (torch.randn(E, h, mi, device=_dev(), generator=g) * mi ** -0.5).bfloat16()
+    ids, w, cnt = moe.route(torch.randn(T, E, device=_dev(), generator=g), k)
+    y = moe.moe_dense_forward(x, ids, w, gate_up, down, counts=cnt, act=act)
+    ref = moe.moe_eager(x, ids.cpu().to(_dev()), w, gate_up[:, :mi], gate_up[:, mi:], down, act=act)
+    assert _rel_err(y, ref) < 3e-2, _rel_err(y, ref)

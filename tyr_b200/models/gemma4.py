@@ -245,6 +245,10 @@ def route(cfg: Gemma4Config, m: MoeBranch, hidden2: torch.Tensor):
 def experts_forward(m: MoeBranch, x2: torch.Tensor, idx: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     """GELU-gated routed experts: per unique expert, ``down(gelu_tanh(gate x) * up x)`` weighted into the token rows
     (the reference's fused expert loop, cc/src/tyr.cpp:1468-1546)."""
+    if x2.is_cuda and x2.dtype == torch.bfloat16 and m.gate_up_proj.dtype == torch.bfloat16 and x2.shape[1] % 8 == 0 and (m.gate_up_proj.shape[1] // 2) % 8 == 0:
+        # grouped tcgen05 GEMMs with the GELU gate in the epilogue; no host read of the expert ids
+        from ..ops import moe as moe_ops
+        return moe_ops.moe_dense_forward(x2, idx.to(torch.int32), w.float(), m.gate_up_proj, m.down_proj, act="geglu")
     out = torch.zeros_like(x2, dtype=torch.float32)
     mi = m.gate_up_proj.shape[1] // 2
     for e in torch.unique(idx).tolist():

@@ -189,11 +189,11 @@ def grouped_gemm(a: torch.Tensor, b: torch.Tensor, group_offsets: torch.Tensor,
     ``ceil(rows_g / 128)``) lets the kernel walk the non-empty row tiles without a device->host read
     of the counts; it is derived on the device when not given.  ``act='swiglu'`` expects each 256-row
     block of ``b[g]`` to hold 128 gate rows followed by the matching 128 up rows and returns
-    ``[total_rows, N/2]`` with ``silu(alpha*gate) * (beta*up)``."""
+    ``[total_rows, N/2]`` with ``silu(alpha*gate) * (beta*up)``; ``act='geglu'`` is the same with tanh-GELU on the gate."""
     total, K = a.shape
     G, N, K2 = b.shape
     assert K == K2 and group_offsets.numel() == G + 1
-    swiglu = act == "swiglu"
+    swiglu = act in ("swiglu", "geglu")          # gated pairs: SiLU or tanh-GELU on the gate half
     n_out = N // 2 if swiglu else N
     if not a.is_cuda:
         offs = group_offsets.tolist()
@@ -206,7 +206,8 @@ def grouped_gemm(a: torch.Tensor, b: torch.Tensor, group_offsets: torch.Tensor,
             if swiglu:
                 blk = acc.reshape(hi - lo, N // 256, 2, 128)
                 gate, up = alpha * blk[:, :, 0], beta * blk[:, :, 1]
-                acc = (torch.nn.functional.silu(gate) * up).reshape(hi - lo, n_out)
+                fn = torch.nn.functional.silu if act == "swiglu" else (lambda t: torch.nn.functional.gelu(t, approximate="tanh"))
+                acc = (fn(gate) * up).reshape(hi - lo, n_out)
             else:
                 acc = alpha * acc
             res[lo:hi] = acc.to(a.dtype)
@@ -225,7 +226,7 @@ def grouped_gemm(a: torch.Tensor, b: torch.Tensor, group_offsets: torch.Tensor,
     args.lda, args.ldb, args.ldc = a.stride(0), b.stride(1), out.stride(0)
     args.sA, args.sB = total, b.stride(0)
     args.out_mode = 0
-    args.act = 4 if swiglu else _ACT[act]
+    args.act = (4 if act == "swiglu" else 5) if swiglu else _ACT[act]
     args.alpha = alpha
     args.beta = beta if swiglu else 0.0
     args.bn = 256

@@ -9,6 +9,7 @@ The eager paths ``moe_eager`` (per-expert loop) is the CPU oracle.
 """
 from __future__ import annotations
 
+import collections
 import os
 from dataclasses import dataclass
 from typing import Dict, Optional, Tuple
@@ -258,14 +259,21 @@ class PackedExperts:
         return 2 * (mi * h // 2 + mi * h // 16) + (h * mi // 2 + h * mi // 16)
 
 
-_dense_cache: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = {}
+_dense_cache: "collections.OrderedDict" = collections.OrderedDict()      # (bank address, size) -> (gate|up interleaved, down) in bf16
+_dense_cache_bytes = [0]
+_dense_pinned = set()                 # banks a captured CUDA graph reads: never evicted
+DENSE_CACHE_BUDGET_BYTES = int(float(os.environ.get("TYR_MOE_DENSE_CACHE_GB", "24")) * (1 << 30))
 
 
 def _interleaved_gate_up(ex: PackedExperts) -> Tuple[torch.Tensor, torch.Tensor]:
     """bf16 [E, 2*mi_pad, h] with 128 gate rows then 128 up rows per 256-row block, and down [E, h, mi_pad]."""
-    key = ex.gate_packed.data_ptr()
+    key = (ex.gate_packed.data_ptr(), ex.gate_packed.numel())
     hit = _dense_cache.get(key)
+    capturing = ex.gate_packed.is_cuda and torch.cuda.is_current_stream_capturing()
     if hit is not None:
+        _dense_cache.move_to_end(key)
+        if capturing:
+            _dense_pinned.add(key)
         return hit
     g, u, d = ex.dense()
     E, mi, h = g.shape
@@ -276,21 +284,36 @@ def _interleaved_gate_up(ex: PackedExperts) -> Tuple[torch.Tensor, torch.Tensor]
         d = torch.nn.functional.pad(d, (0, pad))
     mp = mi + pad
     gu = torch.stack([g.reshape(E, mp // 128, 128, h), u.reshape(E, mp // 128, 128, h)], dim=2).reshape(E, 2 * mp, h)
-    _dense_cache.clear()
-    _dense_cache[key] = (gu.contiguous(), d.contiguous())
-    return _dense_cache[key]
+    entry = (gu.contiguous(), d.contiguous())
+    size = sum(t.numel() * t.element_size() for t in entry)
+    # least-recently-used entries go first; one entry is always kept, so a bank larger than the budget still works (and is
+    # dequantised again on its next use, which is what a prefill over many large layers wants)
+    for old_key in [k for k in _dense_cache if k not in _dense_pinned]:
+        if _dense_cache_bytes[0] + size <= DENSE_CACHE_BUDGET_BYTES:
+            break
+        old_entry = _dense_cache.pop(old_key)
+        _dense_cache_bytes[0] -= sum(t.numel() * t.element_size() for t in old_entry)
+    _dense_cache[key] = entry
+    _dense_cache_bytes[0] += size
+    if capturing:
+        _dense_pinned.add(key)
+    return entry
 
 
 def moe_eager(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, gate: torch.Tensor, up: torch.Tensor,
-              down: torch.Tensor) -> torch.Tensor:
-    """Per-unique-expert loop on dense banks (the reference's eager path, MoE.lean:313-356); fp32 math."""
+              down: torch.Tensor, act: str = "swiglu") -> torch.Tensor:
+    """Per-unique-expert loop on dense banks (the reference's eager path, MoE.lean:313-356); fp32 math.  ``act``: "swiglu"
+    or "geglu" (tanh-GELU gate, Gemma 4); ids outside the bank are skipped."""
     T, h = x.shape
     out = torch.zeros(T, h, dtype=torch.float32, device=x.device)
     xf = x.float()
+    fn = torch.nn.functional.silu if act == "swiglu" else (lambda t: torch.nn.functional.gelu(t, approximate="tanh"))
     for e in torch.unique(ids).tolist():
+        if e < 0 or e >= gate.shape[0]:
+            continue
         tok, slot = torch.nonzero(ids == e, as_tuple=True)
         xe = xf[tok]
-        hdn = torch.nn.functional.silu(xe @ gate[e].float().T) * (xe @ up[e].float().T)
+        hdn = fn(xe @ gate[e].float().T) * (xe @ up[e].float().T)
         out.index_add_(0, tok, (hdn @ down[e].float().T) * weights[tok, slot].float().unsqueeze(-1))
     return out.to(x.dtype)
 
@@ -369,7 +392,7 @@ def interleave_gate_up(gate_up: torch.Tensor) -> torch.Tensor:
 
 
 def moe_dense_forward(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor,
-                      counts: Optional[torch.Tensor] = None, add: Optional[torch.Tensor] = None) -> torch.Tensor:
+                      counts: Optional[torch.Tensor] = None, add: Optional[torch.Tensor] = None, act: str = "swiglu") -> torch.Tensor:
     """bf16 expert banks: ``gate_up`` [E, 2*mi, h], ``down`` [E, h, mi].  Grouped tensor-core path on the
     GPU for bf16; per-expert loop otherwise (Tyr/Model/Qwen35/Model.lean:200-248 computes the same sum
     by gathering one expert matrix per (token, slot))."""
@@ -378,7 +401,7 @@ def moe_dense_forward(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
     mi = two_mi // 2
     k = ids.shape[1]
     if not (x.is_cuda and x.dtype == torch.bfloat16 and gate_up.dtype == torch.bfloat16 and h % 8 == 0 and mi % 8 == 0):
-        y = moe_eager(x, ids, weights, gate_up[:, :mi], gate_up[:, mi:], down)
+        y = moe_eager(x, ids, weights, gate_up[:, :mi], gate_up[:, mi:], down, act=act)
         return y if add is None else (y.float() + add.float()).to(x.dtype)
     if counts is None:
         counts = count_experts(ids, E)
@@ -388,7 +411,7 @@ def moe_dense_forward(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
     dn = down if mi % 128 == 0 else torch.nn.functional.pad(down, (0, (-mi) % 128)).contiguous()
     xs = torch.empty((T * k, h), dtype=x.dtype, device=x.device)
     check(lib().tyr_moe_gather_rows(ptr(x.contiguous()), ptr(order), ptr(xs), T * k, k, h, st), "moe_gather_rows")
-    hid = grouped_gemm(xs, gu, offsets, tiles, act="swiglu")
+    hid = grouped_gemm(xs, gu, offsets, tiles, act=act)
     y = grouped_gemm(hid, dn.contiguous(), offsets, tiles)
     out = torch.empty_like(x)
     check(lib().tyr_moe_combine(ptr(y), ptr(pos), ptr(weights.float().contiguous()), ptr(add.contiguous() if add is not None else None),
