@@ -18,6 +18,7 @@ constexpr int kSkWarps = 8;
 struct SkinnyArgs {
   const __nv_bfloat16* x;      // [M, K], row stride ldx
   const __nv_bfloat16* w;      // [N, K], row stride ldw
+  const __nv_bfloat16* w2;     // gated form only: the second matrix [N, K]; y = silu(x w^T) * (x w2^T)
   const __nv_bfloat16* bias;   // [N] or null
   __nv_bfloat16* y;            // [M, N], row stride ldy
   float* ws;                   // [M, N] fp32, zero on entry and exit; used when the reduction is split over gridDim.y CTAs
@@ -31,9 +32,9 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-template <int TILES>                               // token tiles of 8: M <= 8 * TILES
+template <int TILES, bool GATED>                   // token tiles of 8: M <= 8 * TILES; GATED: two matrices, SwiGLU epilogue
 __global__ void __launch_bounds__(kSkWarps * 32) skinny_gemm_kernel(SkinnyArgs a) {
-  __shared__ float part[kSkWarps][TILES][16][8];
+  __shared__ float part[GATED ? 2 : 1][kSkWarps][TILES][16][8];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
   const int row0 = blockIdx.x * 16;
@@ -42,6 +43,8 @@ __global__ void __launch_bounds__(kSkWarps * 32) skinny_gemm_kernel(SkinnyArgs a
   r_hi = r_hi < a.N ? r_hi : a.N - 1;
   const __nv_bfloat16* w_lo = a.w + r_lo * a.ldw + 8 * t;
   const __nv_bfloat16* w_hi = a.w + r_hi * a.ldw + 8 * t;
+  const __nv_bfloat16* v_lo = GATED ? a.w2 + r_lo * a.ldw + 8 * t : nullptr;
+  const __nv_bfloat16* v_hi = GATED ? a.w2 + r_hi * a.ldw + 8 * t : nullptr;
   const __nv_bfloat16* xr[TILES];
   bool live[TILES];
 #pragma unroll
@@ -50,9 +53,12 @@ __global__ void __launch_bounds__(kSkWarps * 32) skinny_gemm_kernel(SkinnyArgs a
     live[i] = tok < a.M;
     xr[i] = a.x + (live[i] ? tok : 0) * a.ldx + 8 * t;
   }
-  float acc[TILES][4];
+  float acc[TILES][4], acc2[TILES][4];
 #pragma unroll
-  for (int i = 0; i < TILES; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+  for (int i = 0; i < TILES; ++i) {
+    acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+    acc2[i][0] = acc2[i][1] = acc2[i][2] = acc2[i][3] = 0.f;
+  }
 
   const int chunks = a.K >> 5;                   // 32 channels per warp step
   const int c_lo = static_cast<int>(static_cast<long long>(chunks) * blockIdx.y / gridDim.y);
@@ -61,19 +67,34 @@ __global__ void __launch_bounds__(kSkWarps * 32) skinny_gemm_kernel(SkinnyArgs a
   for (int c = c_lo + warp; c < c_hi; c += kSkWarps) {
     const uint4 lo = __ldcs(reinterpret_cast<const uint4*>(w_lo + 32 * c));    // streamed once: do not keep in cache
     const uint4 hi = __ldcs(reinterpret_cast<const uint4*>(w_hi + 32 * c));
+    uint4 lo2 = make_uint4(0u, 0u, 0u, 0u), hi2 = lo2;
+    if (GATED) {
+      lo2 = __ldcs(reinterpret_cast<const uint4*>(v_lo + 32 * c));
+      hi2 = __ldcs(reinterpret_cast<const uint4*>(v_hi + 32 * c));
+    }
 #pragma unroll
     for (int i = 0; i < TILES; ++i) {
       const uint4 xv = live[i] ? __ldg(reinterpret_cast<const uint4*>(xr[i] + 32 * c)) : make_uint4(0u, 0u, 0u, 0u);
       mma_16816(acc[i], lo.x, hi.x, lo.y, hi.y, xv.x, xv.y);
       mma_16816(acc[i], lo.z, hi.z, lo.w, hi.w, xv.z, xv.w);
+      if (GATED) {
+        mma_16816(acc2[i], lo2.x, hi2.x, lo2.y, hi2.y, xv.x, xv.y);
+        mma_16816(acc2[i], lo2.z, hi2.z, lo2.w, hi2.w, xv.z, xv.w);
+      }
     }
   }
 #pragma unroll
   for (int i = 0; i < TILES; ++i) {
-    part[warp][i][g][2 * t] = acc[i][0];
-    part[warp][i][g][2 * t + 1] = acc[i][1];
-    part[warp][i][g + 8][2 * t] = acc[i][2];
-    part[warp][i][g + 8][2 * t + 1] = acc[i][3];
+    part[0][warp][i][g][2 * t] = acc[i][0];
+    part[0][warp][i][g][2 * t + 1] = acc[i][1];
+    part[0][warp][i][g + 8][2 * t] = acc[i][2];
+    part[0][warp][i][g + 8][2 * t + 1] = acc[i][3];
+    if (GATED) {
+      part[1][warp][i][g][2 * t] = acc2[i][0];
+      part[1][warp][i][g][2 * t + 1] = acc2[i][1];
+      part[1][warp][i][g + 8][2 * t] = acc2[i][2];
+      part[1][warp][i][g + 8][2 * t + 1] = acc2[i][3];
+    }
   }
   __syncthreads();
   for (int idx = tid; idx < TILES * 8 * 16; idx += kSkWarps * 32) {
@@ -82,8 +103,13 @@ __global__ void __launch_bounds__(kSkWarps * 32) skinny_gemm_kernel(SkinnyArgs a
     if (tok < a.M && row < a.N) {
       float s = 0.f;
 #pragma unroll
-      for (int wp = 0; wp < kSkWarps; ++wp) s += part[wp][tok >> 3][r][tok & 7];
-      if (gridDim.y == 1) {
+      for (int wp = 0; wp < kSkWarps; ++wp) s += part[0][wp][tok >> 3][r][tok & 7];
+      if (GATED) {
+        float u = 0.f;
+#pragma unroll
+        for (int wp = 0; wp < kSkWarps; ++wp) u += part[1][wp][tok >> 3][r][tok & 7];
+        a.y[tok * a.ldy + row] = __float2bfloat16(s / (1.f + __expf(-s)) * u);
+      } else if (gridDim.y == 1) {
         if (a.bias) s += __bfloat162float(a.bias[row]);
         a.y[tok * a.ldy + row] = __float2bfloat16(s);
       } else {
@@ -124,15 +150,30 @@ extern "C" TYR_EXPORT int tyr_skinny_gemm_bf16(const void* x, const void* w, con
   if (M < 1 || M > 16 || N < 1 || K < 32 || (K & 31)) return -1;
   if ((ldx | ldw) & 7) return -2;                                    // 16-byte loads
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) return -3;
-  SkinnyArgs a{(const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)bias, (__nv_bfloat16*)y, (float*)ws, ldx, ldw, ldy, M, N, K};
+  SkinnyArgs a{(const __nv_bfloat16*)x, (const __nv_bfloat16*)w, nullptr, (const __nv_bfloat16*)bias, (__nv_bfloat16*)y, (float*)ws, ldx, ldw, ldy, M, N, K};
   const int splits = ws != nullptr ? tyr_skinny_gemm_splits(N, K) : 1;
   const dim3 grid((N + 15) / 16, splits);
-  if (M <= 8) skinny_gemm_kernel<1><<<grid, kSkWarps * 32, 0, (cudaStream_t)stream>>>(a);
-  else skinny_gemm_kernel<2><<<grid, kSkWarps * 32, 0, (cudaStream_t)stream>>>(a);
+  if (M <= 8) skinny_gemm_kernel<1, false><<<grid, kSkWarps * 32, 0, (cudaStream_t)stream>>>(a);
+  else skinny_gemm_kernel<2, false><<<grid, kSkWarps * 32, 0, (cudaStream_t)stream>>>(a);
   if (splits > 1) {
     long long blocks = (static_cast<long long>(M) * N + 255) / 256;
     if (blocks > 592) blocks = 592;
     skinny_finish_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>(a);
   }
+  return (int)cudaGetLastError();
+}
+
+// y[M, N] = silu(x wg^T) * (x wu^T): the gate and up projections of a SwiGLU MLP for decode-sized M in one pass over both
+// matrices (same row stride ldw), no intermediate tensors.
+extern "C" TYR_EXPORT int tyr_skinny_swiglu_bf16(const void* x, const void* wg, const void* wu, void* y, long long ldx,
+                                                 long long ldw, long long ldy, int M, int N, int K, void* stream) {
+  using namespace tyr;
+  if (M < 1 || M > 16 || N < 1 || K < 32 || (K & 31)) return -1;
+  if ((ldx | ldw) & 7) return -2;
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(wg) | reinterpret_cast<uintptr_t>(wu)) & 15) return -3;
+  SkinnyArgs a{(const __nv_bfloat16*)x, (const __nv_bfloat16*)wg, (const __nv_bfloat16*)wu, nullptr, (__nv_bfloat16*)y, nullptr, ldx, ldw, ldy, M, N, K};
+  const dim3 grid((N + 15) / 16, 1);
+  if (M <= 8) skinny_gemm_kernel<1, true><<<grid, kSkWarps * 32, 0, (cudaStream_t)stream>>>(a);
+  else skinny_gemm_kernel<2, true><<<grid, kSkWarps * 32, 0, (cudaStream_t)stream>>>(a);
   return (int)cudaGetLastError();
 }

@@ -515,3 +515,16 @@ def test_moe_dense_grouped_gemm_gate_epilogues(act):
     y = moe.moe_dense_forward(x, ids, w, gate_up, down, counts=cnt, act=act)
     ref = moe.moe_eager(x, ids.cpu().to(_dev()), w, gate_up[:, :mi], gate_up[:, mi:], down, act=act)
     assert _rel_err(y, ref) < 3e-2, _rel_err(y, ref)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 1024, 512), (8, 17408, 5120), (13, 272, 2048)])
+def test_skinny_swiglu_matches_reference(M, N, K):
+    from tyr_b200.ops.skinny import skinny_swiglu, swiglu_supported
+    g = torch.Generator(device="cuda").manual_seed(M + N)
+    x = torch.randn(M, K, device=_dev(), generator=g).bfloat16()
+    wg = (torch.randn(N, K, device=_dev(), generator=g) * K ** -0.5).bfloat16()
+    wu = (torch.randn(N, K, device=_dev(), generator=g) * K ** -0.5).bfloat16()
+    assert swiglu_supported(x, wg, wu)
+    y = skinny_swiglu(x, wg, wu).float()
+    ref = torch.nn.functional.silu(x.float() @ wg.float().T) * (x.float() @ wu.float().T)
+    assert (y - ref).abs().max() < 2e-2 * max(1.0, ref.abs().max().item())

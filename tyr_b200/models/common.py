@@ -49,6 +49,11 @@ def lin(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor] = None, act:
 
 
 def swiglu_mlp(x, gate_w, up_w, down_w):
+    rows = x.numel() // x.shape[-1]
+    if rows <= _skinny.MAX_ROWS and x.is_cuda and not torch.is_grad_enabled():
+        x2 = x.reshape(rows, -1)
+        if _skinny.swiglu_supported(x2, gate_w, up_w):          # decode: gate and up in one pass, SwiGLU in the epilogue
+            return lin(_skinny.skinny_swiglu(x2, gate_w, up_w).reshape(*x.shape[:-1], gate_w.shape[0]), down_w)
     return lin(F.silu(lin(x, gate_w)) * lin(x, up_w), down_w)
 
 

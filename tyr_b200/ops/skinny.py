@@ -2,6 +2,7 @@
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -31,6 +32,10 @@ def _sigs(lib_):
         fn.restype = I
         lib_.tyr_skinny_gemm_splits.argtypes = [I, I]
         lib_.tyr_skinny_gemm_splits.restype = I
+    fn = getattr(lib_, "tyr_skinny_swiglu_bf16", None)
+    if fn is not None:
+        fn.argtypes = [P, P, P, P, L, L, L, I, I, I, P]
+        fn.restype = I
 
 
 def supported(x2: torch.Tensor, w: torch.Tensor) -> bool:
@@ -52,4 +57,24 @@ def skinny_linear(x2: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor
     b = None if bias is None else bias.to(torch.bfloat16).contiguous()
     ws = _workspace(x2.device, M, N) if lib().tyr_skinny_gemm_splits(N, K) > 1 else None
     check(lib().tyr_skinny_gemm_bf16(ptr(x2), ptr(w), ptr(b), ptr(y), ptr(ws), x2.stride(0), w.stride(0), N, M, N, K, cur_stream(x2.device)), "skinny_gemm_bf16")
+    return y
+
+
+_SWIGLU = os.environ.get("TYR_SKINNY_SWIGLU", "1") != "0"
+
+
+def swiglu_supported(x2: torch.Tensor, gate_w: torch.Tensor, up_w: torch.Tensor) -> bool:
+    return (_SWIGLU and supported(x2, gate_w) and supported(x2, up_w) and gate_w.shape == up_w.shape and gate_w.stride(0) == up_w.stride(0)
+            and hasattr(lib(), "tyr_skinny_swiglu_bf16"))
+
+
+def skinny_swiglu(x2: torch.Tensor, gate_w: torch.Tensor, up_w: torch.Tensor) -> torch.Tensor:
+    """x2: [M <= 16, K] bf16 -> silu(x2 gate_w^T) * (x2 up_w^T) as [M, N] bf16: both matrices streamed once, one launch."""
+    M, K = x2.shape
+    N = gate_w.shape[0]
+    if not x2.is_cuda:
+        return (torch.nn.functional.silu(x2.float() @ gate_w.float().T) * (x2.float() @ up_w.float().T)).to(x2.dtype)
+    y = torch.empty((M, N), dtype=torch.bfloat16, device=x2.device)
+    check(lib().tyr_skinny_swiglu_bf16(ptr(x2), ptr(gate_w), ptr(up_w), ptr(y), x2.stride(0), gate_w.stride(0), N, M, N, K, cur_stream(x2.device)),
+          "skinny_swiglu")
     return y
