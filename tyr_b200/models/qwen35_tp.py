@@ -123,7 +123,10 @@ def shard(m: Q.Qwen35ForCausalLM, rank: int, world: int, tp: TensorParallel) -> 
                                 x.o_proj.chunk(world, dim=1)[rank].contiguous(), x.q_norm, x.k_norm)
         else:
             seg = lambda t: torch.cat([_rows(t[:kd], rank, world), _rows(t[kd:2 * kd], rank, world), _rows(t[2 * kd:], rank, world)])
-            mixer = TPGatedDeltaNet(torch.cat([seg(x.in_proj_qkv), _rows(x.in_proj_z, rank, world), _rows(x.in_proj_b, rank, world), _rows(x.in_proj_a, rank, world)]).contiguous(),
+            merged = torch.cat([seg(x.in_proj_qkv), _rows(x.in_proj_z, rank, world), _rows(x.in_proj_b, rank, world), _rows(x.in_proj_a, rank, world)])
+            if merged.shape[0] % 8:      # zero rows up to a multiple of 8 output columns: keeps the merged projection on the tensor-core / fused path
+                merged = F.pad(merged, (0, 0, 0, (-merged.shape[0]) % 8))
+            mixer = TPGatedDeltaNet(merged.contiguous(),
                                     seg(x.conv1d_weight).contiguous(), None if x.conv1d_bias is None else seg(x.conv1d_bias).contiguous(),
                                     _rows(x.dt_bias, rank, world), _rows(x.a_log, rank, world), x.norm_weight, x.out_proj.chunk(world, dim=1)[rank].contiguous())
         f = l.ffn
@@ -149,7 +152,8 @@ def init_sharded(cfg: Q.Qwen35Config, rank: int, world: int, tp: TensorParallel,
         else:
             Hv, cd, vd, K = loc.linear_num_value_heads, loc.linear_conv_dim, loc.linear_value_dim, cfg.linear_conv_kernel_dim
             a = torch.rand(Hv, generator=mine, device=device) * 16.0 + 1e-6
-            mixer = TPGatedDeltaNet(mk((cd + vd + 2 * Hv, h), h), mk((cd, 1, K), K), (torch.rand(cd, generator=mine, device=device) * 0.2 - 0.1).to(dtype),
+            mixer = TPGatedDeltaNet(mk((-(-(cd + vd + 2 * Hv) // 8) * 8, h), h), mk((cd, 1, K), K),      # width rounded up to 8 columns (the extra ones are unused)
+                                    (torch.rand(cd, generator=mine, device=device) * 0.2 - 0.1).to(dtype),
                                     torch.ones(Hv, device=device), torch.log(a), torch.ones(cfg.linear_value_head_dim, device=device, dtype=dtype),
                                     mk((h, vd), cfg.linear_value_dim))
         I = loc.intermediate_size
@@ -178,7 +182,7 @@ class TPCache:
             nq, nkv = loc.num_attention_heads * 2 * loc.head_dim, loc.num_key_value_heads * loc.head_dim
             return Q.attention_core(loc, l.mixer.q_norm, l.mixer.k_norm, proj[..., :nq], proj[..., nq:nq + nkv], proj[..., nq + nkv:], cos, sin, self.kv[i])
         cd, vd, Hv = loc.linear_conv_dim, loc.linear_value_dim, loc.linear_num_value_heads
-        return Q.gated_delta_net_core(loc, l.mixer, proj[..., :cd], proj[..., cd:cd + vd], proj[..., cd + vd:cd + vd + Hv], proj[..., cd + vd + Hv:], self.lin[i])
+        return Q.gated_delta_net_core(loc, l.mixer, proj[..., :cd], proj[..., cd:cd + vd], proj[..., cd + vd:cd + vd + Hv], proj[..., cd + vd + Hv:cd + vd + 2 * Hv], self.lin[i])
 
     @staticmethod
     def _swiglu(gu):
@@ -246,7 +250,7 @@ class TPCache:
                 w_out = l.mixer.o_proj
             else:
                 cd, vd, Hv = loc.linear_conv_dim, loc.linear_value_dim, loc.linear_num_value_heads
-                core = Q.gated_delta_net_core(loc, l.mixer, proj[..., :cd], proj[..., cd:cd + vd], proj[..., cd + vd:cd + vd + Hv], proj[..., cd + vd + Hv:], self.lin[i])
+                core = Q.gated_delta_net_core(loc, l.mixer, proj[..., :cd], proj[..., cd:cd + vd], proj[..., cd + vd:cd + vd + Hv], proj[..., cd + vd + Hv:cd + vd + 2 * Hv], self.lin[i])
                 w_out = l.mixer.out_proj
             x = tp.linear_all_reduce(core.reshape(B, -1), w_out, add=x)
             gu = lin(Q.rms(x, l.post_attention_layernorm, eps), l.ffn.gate_up)

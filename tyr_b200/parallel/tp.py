@@ -185,7 +185,10 @@ class TensorParallel:
 
 
 def _cpu_lin(x, w, act):
-    y = x.float() @ w.float().T
+    if x.is_cuda and x.dtype == torch.bfloat16:      # odd widths on the GPU: the library's bf16 GEMM, not an fp32 product
+        y = torch.nn.functional.linear(x, w.to(x.dtype)).float()
+    else:
+        y = x.float() @ w.float().T
     if act == "relu":
         y = torch.relu(y)
     elif act == "relu2":
