@@ -101,7 +101,7 @@ class ClockSampler:
 
 def reference_arm(args):
     """The reference is a Lean 4 project (lakefile.lean + a C++ FFI library built by Lake); it has
-    no Python packaging, so `pip install /root/reference` cannot produce anything runnable and the
+    no Python packaging, so a `pip install` of its source tree cannot produce anything runnable and the
     Lean toolchain is not in this image."""
     ref_dir = os.path.join(ROOT, "baseline", "_ref")
     why = ("reference is a Lean 4 + LibTorch FFI project (no setup.py/pyproject; needs elan/Lean 4.29 "

@@ -137,8 +137,8 @@ __device__ __forceinline__ void stage_tile(float* dst, const float* src, int row
 __global__ void __launch_bounds__(128, 1)
 gdr_chunk_scan_kernel(const float* __restrict__ u, const float* __restrict__ w, const float* __restrict__ qg,
                       const float* __restrict__ kd, const float* __restrict__ intra, const float* __restrict__ glast,
-                      const float* __restrict__ state_in, float* __restrict__ state_out, float* __restrict__ out, int n,
-                      int dv) {
+                      const float* __restrict__ state_in, float* __restrict__ state_out, __nv_bfloat16* __restrict__ out, int n,
+                      int dv, int seq, int Hv) {
   extern __shared__ __align__(16) uint8_t gdr_smem_raw[];
   GdrChunkSmem& sm = *reinterpret_cast<GdrChunkSmem*>(gdr_smem_raw);
   const int bh = blockIdx.y;
@@ -151,7 +151,8 @@ gdr_chunk_scan_kernel(const float* __restrict__ u, const float* __restrict__ w, 
   const float* kd_p = kd + static_cast<long long>(bh) * n * chunk_k;
   const float* in_p = intra + static_cast<long long>(bh) * n * GC_C * GC_C;
   const float* u_p = u + static_cast<long long>(bh) * n * GC_C * dv + col0;
-  float* o_p = out + static_cast<long long>(bh) * n * GC_C * dv + col0;
+  // output rows go straight to the [B, S, Hv, dv] bf16 layout of the layer (rows past the sequence end are dropped)
+  __nv_bfloat16* o_p = out + (static_cast<long long>(bh / Hv) * seq * Hv + (bh % Hv)) * dv + col0;
 
   // state rows [32 warp, 32 warp + 32) x 64 columns as two m-tiles x eight n-tiles of accumulators
   float S[2][8][4];
@@ -234,13 +235,16 @@ gdr_chunk_scan_kernel(const float* __restrict__ u, const float* __restrict__ w, 
       }
     }
     {
-      float* oi = o_p + static_cast<long long>(i) * GC_C * dv;
 #pragma unroll
-      for (int nt = 0; nt < 8; ++nt)
+      for (int h2 = 0; h2 < 2; ++h2) {
+        const int tok = i * GC_C + ar + h2 * 8;
+        if (tok < seq) {
+          __nv_bfloat16* oi = o_p + static_cast<long long>(tok) * Hv * dv;
 #pragma unroll
-        for (int h2 = 0; h2 < 2; ++h2)
-          *reinterpret_cast<float2*>(oi + static_cast<long long>(ar + h2 * 8) * dv + nt * 8 + 2 * t) =
-              make_float2(Y[nt][2 * h2], Y[nt][2 * h2 + 1]);
+          for (int nt = 0; nt < 8; ++nt)
+            *reinterpret_cast<uint32_t*>(oi + nt * 8 + 2 * t) = pack_bf16x2(Y[nt][2 * h2], Y[nt][2 * h2 + 1]);
+        }
+      }
     }
     // ---- S <- exp(g_last) S + kd_i^T v_new : this warp's 32 state rows, K = chunk
     const float e = glast[static_cast<long long>(bh) * n + i];
@@ -630,13 +634,14 @@ extern "C" TYR_EXPORT int tyr_gdr_chunk_prepare(const void* q, const void* k, co
 
 // Sequential chunk pass of the gated delta rule (chunk 64, dk 128, dv a multiple of 64), all tensors fp32 and contiguous:
 // u [BH, n, 64, dv], w / qg / kd [BH, n, 64, 128], intra [BH, n, 64, 64], glast [BH, n] (= exp of the chunk's last cumulative
-// log decay), state_in [BH, 128, dv] (nullable = zeros), state_out [BH, 128, dv], out [BH, n, 64, dv].
+// log decay), state_in [BH, 128, dv] (nullable = zeros), state_out [BH, 128, dv]; out: bf16 [B, S, Hv, dv] with BH = B * Hv and
+// n = ceil(S / 64).
 extern "C" TYR_EXPORT int tyr_gdr_chunk_scan(const float* u, const float* w, const float* qg, const float* kd,
                                              const float* intra, const float* glast, const float* state_in,
-                                             float* state_out, float* out, int BH, int n, int dk, int dv, int chunk,
-                                             void* stream) {
+                                             float* state_out, void* out, int BH, int n, int dk, int dv, int chunk, int S,
+                                             int Hv, void* stream) {
   using namespace tyr;
-  if (BH <= 0 || n <= 0 || dk != GC_DK || chunk != GC_C || dv <= 0 || dv % GC_DVS) return -1;
+  if (BH <= 0 || n <= 0 || dk != GC_DK || chunk != GC_C || dv <= 0 || dv % GC_DVS || Hv <= 0 || BH % Hv || S <= 0 || S > n * GC_C) return -1;
   if ((reinterpret_cast<uintptr_t>(u) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(qg) |
        reinterpret_cast<uintptr_t>(kd) | reinterpret_cast<uintptr_t>(intra) | reinterpret_cast<uintptr_t>(out) |
        reinterpret_cast<uintptr_t>(state_out) | reinterpret_cast<uintptr_t>(state_in)) & 15)
@@ -649,7 +654,7 @@ extern "C" TYR_EXPORT int tyr_gdr_chunk_scan(const float* u, const float* w, con
     configured = true;
   }
   gdr_chunk_scan_kernel<<<dim3(dv / GC_DVS, BH), 128, smem, reinterpret_cast<cudaStream_t>(stream)>>>(
-      u, w, qg, kd, intra, glast, state_in, state_out, out, n, dv);
+      u, w, qg, kd, intra, glast, state_in, state_out, reinterpret_cast<__nv_bfloat16*>(out), n, dv, S, Hv);
   return static_cast<int>(cudaGetLastError());
 }
 

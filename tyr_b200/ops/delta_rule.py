@@ -24,7 +24,7 @@ def _sigs(lib_):
         fn.restype = ctypes.c_int
     fn = getattr(lib_, "tyr_gdr_chunk_scan", None)
     if fn is not None:
-        fn.argtypes = [P] * 9 + [I, I, I, I, I, P]
+        fn.argtypes = [P] * 9 + [I, I, I, I, I, I, I, P]
         fn.restype = ctypes.c_int
     fn = getattr(lib_, "tyr_gdr_chunk_prepare", None)
     if fn is not None:
@@ -87,10 +87,10 @@ def chunk_gated_delta_rule_fused(q, k, v, g, beta, state: Optional[torch.Tensor]
                                       B, S, Hk, Hv, dk, dv, st), "gdr_chunk_prepare")
     st_in = None if state is None else state.float().contiguous()
     st_out = f32(B, Hv, dk, dv)
-    out = f32(B, Hv, n * 64, dv)
-    check(lib().tyr_gdr_chunk_scan(ptr(u), ptr(w), ptr(qg), ptr(kd), ptr(intra), ptr(glast), ptr(st_in), ptr(st_out), ptr(out), BH, n, dk, dv, 64, st),
+    out = torch.empty((B, S, Hv, dv), dtype=torch.bfloat16, device=dev)          # written in the layer's layout by the scan kernel
+    check(lib().tyr_gdr_chunk_scan(ptr(u), ptr(w), ptr(qg), ptr(kd), ptr(intra), ptr(glast), ptr(st_in), ptr(st_out), ptr(out), BH, n, dk, dv, 64, S, Hv, st),
           "gdr_chunk_scan")
-    return out[:, :, :S].transpose(1, 2).to(q.dtype), st_out
+    return out, st_out
 
 
 def causal_conv1d_silu(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -139,19 +139,6 @@ def chunk_gated_delta_rule(q, k, v, g, beta, chunk_size: int = 64, state: Option
     sol = torch.linalg.solve_triangular(eye + L, rhs, upper=False, unitriangular=True)
     u, w = sol[..., :dv], sol[..., dv:]                                          # "value" and "k_cumdecay"
     intra = (qf @ kf.transpose(-1, -2) * decay).tril()
-    if q.is_cuda and dk == 128 and dv % 64 == 0 and C == 64 and _CHUNK_KERNEL and hasattr(lib(), "tyr_gdr_chunk_scan"):
-        # the recurrence over the chunks in one launch (csrc/delta_rule.cu: gdr_chunk_scan_kernel)
-        g_last = gc[..., -1:]
-        c32 = lambda t: t.float().contiguous()
-        qg, kd = c32(qf * gc.exp().unsqueeze(-1)), c32(kf * (g_last - gc).exp().unsqueeze(-1))
-        u, w, intra, glast = c32(u), c32(w), c32(intra), c32(g_last.squeeze(-1).exp())
-        st_in = None if state is None else c32(state)
-        st = torch.empty(B, H, dk, dv, dtype=torch.float32, device=q.device)
-        out = torch.empty(B, H, n, C, dv, dtype=torch.float32, device=q.device)
-        check(lib().tyr_gdr_chunk_scan(ptr(u), ptr(w), ptr(qg), ptr(kd), ptr(intra), ptr(glast), ptr(st_in), ptr(st), ptr(out), B * H, n, dk, dv, C,
-                                       cur_stream(q.device)), "gdr_chunk_scan")
-        out = out.reshape(B, H, n * C, dv)[:, :, :S].transpose(1, 2).contiguous().to(dt)
-        return out, st
     st = torch.zeros(B, H, dk, dv, device=q.device) if state is None else state.float().clone()
     out = torch.empty(B, H, n, C, dv, device=q.device)
     for i in range(n):
