@@ -141,6 +141,34 @@ def bench_attention_bwd_small(results):
     print(f"flash bwd small B{B} H{H} T{T}: {ms:7.3f} ms {flops / ms / 1e9:7.1f} TF/s", flush=True)
 
 
+def _gdr_inputs(B, S, Hk, Hv, dv, dev):
+    g = torch.Generator(device=dev).manual_seed(0)
+    rn = lambda *shape: torch.randn(*shape, device=dev, generator=g)
+    q, k, v = rn(B, S, Hk, 128).bfloat16(), rn(B, S, Hk, 128).bfloat16(), rn(B, S, Hv, dv).bfloat16()
+    return q, k, v, -torch.nn.functional.softplus(rn(B, S, Hv)) * 0.3, torch.sigmoid(rn(B, S, Hv))
+
+
+def bench_gdr(results, small=False):
+    """Gated delta rule prefill (chunk 64): the two chunk kernels against the library-op form of the same algorithm
+    (Qwen3.5-27B head counts: 16 key / 48 value heads of 128).  ``small``: one case for profiler captures."""
+    from tyr_b200.ops import delta_rule as DR
+    dev = torch.device("cuda")
+    flush = None if small else torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    for B, S in (((2, 2048),) if small else ((8, 2048), (1, 8192))):
+        q, k, v, gl, beta = _gdr_inputs(B, S, 16, 48, 128, dev)
+        iters, warm = (3, 2) if small else (10, 3)
+        ours = _time(lambda: DR.chunk_gated_delta_rule(q, k, v, gl, beta), iters=iters, warmup=warm, flush=flush)
+        row = {"kernel": "gdr_chunk", "B": B, "S": S, "ours_ms": ours}
+        if not small:
+            DR._CHUNK_KERNEL = False
+            try:
+                row["library_ms"] = _time(lambda: DR.chunk_gated_delta_rule(q, k, v, gl, beta), iters=5, warmup=2, flush=flush)
+            finally:
+                DR._CHUNK_KERNEL = True
+        results.append(row)
+        print(f"gated delta rule prefill B{B} S{S} 16/48 heads x 128: ours {ours:7.3f} ms" + (f" | library ops {row['library_ms']:7.3f} ms" if "library_ms" in row else ""), flush=True)
+
+
 def bench_moe(results, cases=None):
     """Fused NVFP4 MoE op at Laguna-S-2.1 shapes (hidden 3072, 256 experts, top-10, FFN 1024): effective
     FP4 weight-read bandwidth for decode-sized batches (the reference's bar is >= 150 GB/s at one token,
@@ -233,6 +261,10 @@ def main(argv):
         bench_attention(results)
     if what in ("attention-bwd", "all"):
         bench_attention_bwd(results)
+    if what in ("gdr", "all"):
+        bench_gdr(results)
+    if what == "gdr-small":
+        bench_gdr(results, small=True)
     if what == "attention-fwd-small":
         bench_attention_fwd_small(results)
     if what == "attention-bwd-small":
