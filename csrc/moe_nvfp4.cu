@@ -205,6 +205,7 @@ __global__ void __launch_bounds__(256) moe_route_fused_kernel(RouteArgs a, const
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tok0 = blockIdx.x * kRouteTok;
   const int nt = min(kRouteTok, a.T - tok0);
+#pragma unroll 4
   for (int i = threadIdx.x * 8; i < nt * h; i += blockDim.x * 8)
     *reinterpret_cast<uint4*>(xs + i) = *reinterpret_cast<const uint4*>(x + static_cast<long long>(tok0) * h + i);
   __syncthreads();
@@ -214,7 +215,8 @@ __global__ void __launch_bounds__(256) moe_route_fused_kernel(RouteArgs a, const
 #pragma unroll
     for (int t = 0; t < kRouteTok; ++t) acc[t] = 0.f;
     const float4* w4 = reinterpret_cast<const float4*>(wr + static_cast<long long>(e) * h);
-    for (int i = lane; i < (h >> 2); i += 32) {
+#pragma unroll 4
+    for (int i = lane; i < (h >> 2); i += 32) {          // four weight loads in flight per lane
       const float4 w = __ldg(w4 + i);
 #pragma unroll
       for (int t = 0; t < kRouteTok; ++t) {

@@ -457,7 +457,7 @@ def test_moe_route_fused_matches_separate_gemm_and_route(T, E, k, h, softmax):
     assert int(counts.sum()) == T * k and torch.equal(counts, torch.bincount(ids.flatten().long(), minlength=E).int())
 
 
-@pytest.mark.parametrize("B,S,Hk,Hv,dv,with_state", [(2, 256, 2, 4, 128, False), (1, 200, 1, 2, 64, True), (1, 64, 2, 2, 128, True)])
+@pytest.mark.parametrize("B,S,Hk,Hv,dv,with_state", [(2, 256, 2, 4, 128, False), (1, 200, 1, 2, 64, True), (1, 64, 2, 2, 128, True), (4, 128, 16, 48, 128, False)])
 def test_gated_delta_rule_chunk_scan_kernel_matches_recurrence(B, S, Hk, Hv, dv, with_state):
     """Chunked prefill with the chunk recurrence in one launch (TF32 tensor cores) against the token-by-token fp32 recurrence."""
     from tyr_b200.ops import delta_rule as DR
