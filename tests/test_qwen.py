@@ -73,3 +73,24 @@ def test_loader_roundtrip_fp8_blocks_and_omni_names(tmp_path):
     got = Q._load_linear(st.Source.open(src_p), "x", 128, 256, "cpu", torch.float32)
     ref = w.to(torch.float8_e4m3fn).float()
     assert torch.equal(got[:, :128], ref[:, :128] * 2.0) and torch.equal(got[:, 128:], ref[:, 128:] * 0.5)
+
+
+@pytest.mark.gpu
+def test_gpu_qwen3_graph_decode_step_matches_eager_session(monkeypatch):
+    """Decode steps replayed from one CUDA graph (device-side position, fused KV append) against the eager cached step."""
+    from tyr_b200.models import qwen as Q
+    cfg = Q.QwenConfig(vocab_size=200, hidden_size=256, intermediate_size=512, num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=2,
+                       half_head_dim=64, rope_theta=10000.0, rms_norm_eps=1e-6)
+    lm = Q.Qwen3ForCausalLM.init(cfg, device="cuda", dtype=torch.bfloat16, seed=3)
+    ids = torch.randint(0, 200, (3, 37), device="cuda")
+    toks = torch.randint(0, 200, (6, 3), device="cuda")
+    graph = Q.Qwen3Session(lm, 3, 64)
+    assert graph.device_step_supported()
+    outs = [graph.prefill(ids)] + [graph.step(t) for t in toks]
+    assert graph._graph.replays == 6 and graph.pos == 43
+    monkeypatch.setenv("TYR_DECODE_GRAPH", "0")
+    eager = Q.Qwen3Session(lm, 3, 64)
+    refs = [eager.prefill(ids)] + [eager.step(t) for t in toks]
+    for a, b in zip(outs, refs):
+        assert (a.float() - b.float()).abs().max() < 0.06 * max(1.0, b.float().abs().max().item())
+    assert torch.equal(outs[-1].argmax(-1), refs[-1].argmax(-1)) or (outs[-1].float() - refs[-1].float()).abs().max() < 0.05

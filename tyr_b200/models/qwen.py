@@ -255,8 +255,53 @@ class Qwen3Session:
     def prefill(self, ids):
         return self.run_embeds(self.lm.embed_tokens(ids))
 
+    # -- decode with the position on the device: one CUDA graph replayed per token ------------------------------------
+    def device_step_supported(self) -> bool:
+        from ..ops.decode_attention import geometry_supported
+        cfg, e = self.lm.cfg, self.lm.model.embed_tokens
+        return (e.is_cuda and e.dtype == torch.bfloat16 and os.environ.get("TYR_DECODE_GRAPH", "1") != "0"
+                and geometry_supported(cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim))
+
+    def _device_step(self, tok: torch.Tensor) -> torch.Tensor:
+        """One token per row; the only position input is ``self.pos_t`` (advanced here).  Per layer: RMSNorm(+RoPE) kernel on q and
+        k, split-KV attention that also appends to the store, decode-sized linears."""
+        from ..ops.decode_attention import decode_attention
+        from ..ops.rope import rope_norm
+        cfg, m = self.lm.cfg, self.lm.model
+        H, Hkv, D, eps = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.rms_norm_eps
+        x = self.lm.embed_tokens(tok.reshape(-1, 1))
+        B = x.shape[0]
+        positions = self.pos_t.expand(B)
+        rot = 2 * self.rope.cos.shape[1]
+        for l, c in zip(m.layers, self.caches):
+            a = l.self_attn
+            h1 = norm_w(x, l.input_layernorm, eps)
+            q = rope_norm(lin(h1, a.q_proj, a.q_bias).reshape(B, H, D), self.rope.cos, self.rope.sin, weight=a.q_norm, positions=positions, rot=rot, eps=eps)
+            k = rope_norm(lin(h1, a.k_proj, a.k_bias).reshape(B, Hkv, D), self.rope.cos, self.rope.sin, weight=a.k_norm, positions=positions, rot=rot, eps=eps)
+            v = lin(h1, a.v_proj, a.v_bias).reshape(B, Hkv, D)
+            o = decode_attention(q, k, v, c.k, c.v, self.pos_t)
+            h = x + lin(o.reshape(B, 1, H * D), a.o_proj)
+            x = h + swiglu_mlp(norm_w(h, l.post_attention_layernorm, eps), l.mlp.gate_proj, l.mlp.up_proj, l.mlp.down_proj)
+        self.pos_t += 1
+        return lin(norm_w(x[:, -1], m.norm, eps), self.lm.lm_head)
+
     def step(self, tok):
-        return self.run_embeds(self.lm.embed_tokens(tok.reshape(-1, 1)))
+        if self.pos == 0 or not self.device_step_supported():
+            return self.run_embeds(self.lm.embed_tokens(tok.reshape(-1, 1)))
+        if self.pos + 1 > self.max_len:
+            raise ValueError("Qwen3 cache overflow")
+        if getattr(self, "_graph", None) is None:
+            from ..utils.graph import GraphedStep
+            self.pos_t = torch.full((1,), self.pos, dtype=torch.int32, device=self.lm.model.embed_tokens.device)
+            self._graph = GraphedStep(self._device_step, (tok.reshape(-1).clone(),), advancing_state=(self.pos_t,))
+        elif self._pos_t_host != self.pos:               # a multi-token run moved the position since the last replay
+            self.pos_t.fill_(self.pos)
+        out = self._graph(tok.reshape(-1))
+        self.pos += 1
+        self._pos_t_host = self.pos
+        for c in self.caches:
+            c.length += 1
+        return out
 
 
 def generate(lm: Qwen3ForCausalLM, input_ids, max_new_tokens=64, strategy=SamplingStrategy(), eos_token_ids=None, on_step=None):
