@@ -22,6 +22,7 @@
 // (cc/src/tyr.cpp:1003-1036, 1267-1300) followed by separate elementwise kernels.
 #include "common.cuh"
 #include <cstdio>
+#include <cstdlib>
 #include <mutex>
 
 namespace tyr {
@@ -38,6 +39,11 @@ struct GemmParams {
   float alpha, beta;
   int act;        // 0 none, 1 relu(x)^2, 2 relu, 3 acc * 2*sqrt(aux), 4 SwiGLU of column halves, 5 GELU(tanh)-gate of column halves
   int out_mode;   // 0 bf16 store, 1 fp32 store, 2 fp32 atomic add (stream-K)
+  // out_mode 2 only.  > 0: the first (tiles / grid) * grid tiles are reduced whole, one per CTA and round, and every
+  // remaining tile is cut into sk_slabs equal k ranges that are dealt round-robin, slab by slab.  All CTAs then sweep the
+  // same k blocks at the same time, so a k slab of both operands is read from HBM once and served to the other CTAs from
+  // L2.  0: an even split of the linear (tile, k-block) sequence (grouped mode, where the tile count lives on the device).
+  int sk_slabs;
   int* err;
   // Grouped mode (MoE): batch = number of groups, A and C are packed [rows, *] with group g owning
   // rows [group_offsets[g], group_offsets[g+1]).  group_tiles[g] is the exclusive prefix sum of
@@ -147,8 +153,24 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
   constexpr uint32_t kStageBytes = BM * BK * 2 + BN * BK * 2;
 
   // Segment iterator shared by the three roles (identical sequence in each).
+  const long long whole_tiles = (tiles / gridDim.x) * gridDim.x;
   auto next_segment = [&](long long& cursor, long long& tile, int& kb0, int& kb1) -> bool {
-    if (p.out_mode == 2) {
+    if (p.out_mode == 2 && p.sk_slabs > 0) {
+      if (cursor < whole_tiles) {
+        tile = cursor;
+        kb0 = 0;
+        kb1 = num_kb;
+      } else {
+        const long long rest = tiles - whole_tiles, v = cursor - whole_tiles;
+        if (v >= rest * p.sk_slabs) return false;
+        const int slab = static_cast<int>(v / rest);
+        tile = whole_tiles + v % rest;
+        kb0 = static_cast<int>(static_cast<long long>(num_kb) * slab / p.sk_slabs);
+        kb1 = static_cast<int>(static_cast<long long>(num_kb) * (slab + 1) / p.sk_slabs);
+      }
+      cursor += gridDim.x;
+      return true;
+    } else if (p.out_mode == 2) {
       if (cursor >= unit_end) return false;
       tile = cursor / num_kb;
       kb0 = static_cast<int>(cursor % num_kb);
@@ -186,7 +208,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     m0 = ((r / tiles_n + p.m_rot) % tiles_m) * BM;
     n0 = (r % tiles_n) * BN;
   };
-  const long long cursor0 = (p.out_mode == 2) ? unit_begin : static_cast<long long>(blockIdx.x);
+  const long long cursor0 = (p.out_mode == 2 && p.sk_slabs == 0) ? unit_begin : static_cast<long long>(blockIdx.x);
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -623,6 +645,7 @@ struct TyrGemmArgs {
 }  // extern "C"
 
 static int g_sm_count = 0;
+static const bool g_aligned_split = [] { const char* e = getenv("TYR_GEMM_ALIGNED_SPLIT"); return e == nullptr || e[0] != '0'; }();
 
 template <int BN, int STAGES, bool A_MN, bool B_MN>
 static int launch_gemm(const TyrGemmArgs& a, const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC,
@@ -653,9 +676,25 @@ static int launch_gemm(const TyrGemmArgs& a, const CUtensorMap& tmA, const CUten
     tiles = ((a.sA + BM - 1) / BM + (a.batch < a.sA ? a.batch : a.sA)) * ((a.N + BN - 1) / BN);
   int grid = a.sm_count > 0 ? a.sm_count : g_sm_count;
   if (a.out_mode != 2 && tiles < grid) grid = static_cast<int>(tiles);
+  p.sk_slabs = 0;
   if (a.out_mode == 2) {
-    const long long units = tiles * ((a.K + BK - 1) / BK);
+    const int num_kb = (a.K + BK - 1) / BK;
+    const long long units = tiles * num_kb;
     if (units < grid) grid = static_cast<int>(units);
+    if (grid < 1) grid = 1;
+    if (a.group_offsets == nullptr && g_aligned_split) {
+      // Slab count for the tiles that do not fill a whole round: fewest k-block times over all rounds, an accumulate
+      // epilogue counted as kEpilogueBlocks of them.
+      const long long rest = tiles - (tiles / grid) * grid;
+      constexpr int kEpilogueBlocks = 8;
+      long long best = -1;
+      p.sk_slabs = 1;
+      for (int sl = 1; rest > 0 && sl <= num_kb && sl <= 128; ++sl) {
+        const long long rounds = (rest * sl + grid - 1) / grid;
+        const long long cost = rounds * ((num_kb + sl - 1) / sl + kEpilogueBlocks);
+        if (best < 0 || cost < best) { best = cost; p.sk_slabs = sl; }
+      }
+    }
   }
   if (grid < 1) grid = 1;
   kern<<<grid, 256, smem, reinterpret_cast<cudaStream_t>(a.stream)>>>(tmA, tmB, tmC, tmP, p);

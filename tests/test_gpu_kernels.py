@@ -62,10 +62,11 @@ def test_gemm_epilogues_and_batch(bn):
     assert _rel_err(outg, refg) < 1e-2
 
 
-def test_gemm_stream_k_accumulate():
+@pytest.mark.parametrize("Kt,M,N", [(4096, 384, 256), (1024, 2048, 2560), (704, 1344, 520), (64, 19072, 256)])
+def test_gemm_stream_k_accumulate(Kt, M, N):
+    """Fewer tiles than SMs, a whole round of tiles plus a remainder, ragged edges, and a single k block."""
     from tyr_b200.ops.gemm import gemm
     g = torch.Generator(device="cuda").manual_seed(3)
-    Kt, M, N = 4096, 384, 256
     dy = torch.randn(Kt, M, device=_dev(), generator=g).bfloat16()
     x = torch.randn(Kt, N, device=_dev(), generator=g).bfloat16()
     acc = torch.ones(M, N, device=_dev(), dtype=torch.float32)

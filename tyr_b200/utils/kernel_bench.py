@@ -1,4 +1,4 @@
-"""Kernel micro-benchmarks: `python -m tyr_b200.utils.kernel_bench [gemm|attention|moe|moe-decode|decode-attn|skinny|all]`.
+"""Kernel micro-benchmarks: `python -m tyr_b200.utils.kernel_bench [gemm|attention|moe|moe-decode|decode-attn|skinny|qwen3-decode|all]`.
 
 Times the hand-written kernels with CUDA events (5 warm-up + 20 timed iterations, a 256 MB
 buffer written between iterations to flush the 126 MB L2) on the NanoChat d20 shapes and prints
@@ -252,9 +252,48 @@ def bench_skinny(results):
         print(f"skinny M={M:2d} N={N:6d} K={K:5d}: ours {ours * 1e3:7.1f} us {gb / ours * 1e3:6.0f} GB/s | library {libms * 1e3:7.1f} us {gb / libms * 1e3:6.0f} GB/s", flush=True)
 
 
+def bench_qwen3_decode(results):
+    """Greedy decode through ``Qwen3Session`` (random-init Qwen3-4B shape, 1024-token prompt, 64 timed steps) for
+    batch 1 and 8, once replaying the captured step graph and once launching the same kernels eagerly."""
+    import os
+    from tyr_b200.models import qwen as Q
+    dev = torch.device("cuda")
+    cfg = Q.QwenConfig.qwen3_4b()
+    lm = Q.Qwen3ForCausalLM.init(cfg, device=dev, dtype=torch.bfloat16, seed=0)
+    saved = os.environ.get("TYR_DECODE_GRAPH")
+    try:
+        for B in (1, 8):
+            ids = torch.randint(0, cfg.vocab_size, (B, 1024), device=dev)
+            for graph in ("1", "0"):
+                os.environ["TYR_DECODE_GRAPH"] = graph
+                with torch.no_grad():
+                    s = Q.Qwen3Session(lm, B, 1024 + 80)
+                    tok = s.prefill(ids).argmax(-1)
+                    for _ in range(3):                       # the first step of a session captures its graph
+                        tok = s.step(tok).argmax(-1)
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    torch.cuda.synchronize()
+                    e0.record()
+                    for _ in range(64):
+                        tok = s.step(tok).argmax(-1)
+                    e1.record()
+                    torch.cuda.synchronize()
+                ms = e0.elapsed_time(e1) / 64
+                results.append({"kernel": "qwen3_4b_decode", "batch": B, "graph": graph == "1", "ms_per_step": ms, "tok_s": B / ms * 1e3})
+                print(f"qwen3-4b decode batch {B} graph={graph}: {B / ms * 1e3:8.1f} tok/s, {ms:.2f} ms/step", flush=True)
+                del s
+    finally:
+        if saved is None:
+            os.environ.pop("TYR_DECODE_GRAPH", None)
+        else:
+            os.environ["TYR_DECODE_GRAPH"] = saved
+
+
 def main(argv):
     what = argv[1] if len(argv) > 1 else "all"
     results = []
+    if what == "qwen3-decode":
+        bench_qwen3_decode(results)
     if what in ("gemm", "all"):
         bench_gemm(results)
     if what in ("attention", "all"):
