@@ -44,6 +44,10 @@ struct GemmParams {
   // same k blocks at the same time, so a k slab of both operands is read from HBM once and served to the other CTAs from
   // L2.  0: an even split of the linear (tile, k-block) sequence (grouped mode, where the tile count lives on the device).
   int sk_slabs;
+  // Tile order of the non-grouped walk: 0 = column tiles fastest (the tiles in flight share a few A row tiles and keep all
+  // of B in L2: right while B is the smaller operand), 1 = row tiles fastest (A stays in L2 and B streams once: an lm_head
+  // whose vocabulary matrix is larger than L2).
+  int raster_m;
   int* err;
   // Grouped mode (MoE): batch = number of groups, A and C are packed [rows, *] with group g owning
   // rows [group_offsets[g], group_offsets[g+1]).  group_tiles[g] is the exclusive prefix sum of
@@ -205,8 +209,13 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     bi = static_cast<int>(tile / per_batch);
     const int r = static_cast<int>(tile % per_batch);
     // n fastest: concurrently resident tiles share A rows and keep B (weights) in L2.
-    m0 = ((r / tiles_n + p.m_rot) % tiles_m) * BM;
-    n0 = (r % tiles_n) * BN;
+    if (p.raster_m) {
+      m0 = (r % tiles_m) * BM;
+      n0 = (r / tiles_m) * BN;
+    } else {
+      m0 = ((r / tiles_n + p.m_rot) % tiles_m) * BM;
+      n0 = (r % tiles_n) * BN;
+    }
   };
   const long long cursor0 = (p.out_mode == 2 && p.sk_slabs == 0) ? unit_begin : static_cast<long long>(blockIdx.x);
 
@@ -645,6 +654,7 @@ struct TyrGemmArgs {
 }  // extern "C"
 
 static int g_sm_count = 0;
+static const bool g_raster_m = [] { const char* e = getenv("TYR_GEMM_RASTER_M"); return e == nullptr || e[0] != '0'; }();
 static const bool g_aligned_split = [] { const char* e = getenv("TYR_GEMM_ALIGNED_SPLIT"); return e == nullptr || e[0] != '0'; }();
 
 template <int BN, int STAGES, bool A_MN, bool B_MN>
@@ -676,6 +686,7 @@ static int launch_gemm(const TyrGemmArgs& a, const CUtensorMap& tmA, const CUten
     tiles = ((a.sA + BM - 1) / BM + (a.batch < a.sA ? a.batch : a.sA)) * ((a.N + BN - 1) / BN);
   int grid = a.sm_count > 0 ? a.sm_count : g_sm_count;
   if (a.out_mode != 2 && tiles < grid) grid = static_cast<int>(tiles);
+  p.raster_m = (a.group_offsets == nullptr && tp.tp_mode == 0 && a.M < a.N && g_raster_m) ? 1 : 0;
   p.sk_slabs = 0;
   if (a.out_mode == 2) {
     const int num_kb = (a.K + BK - 1) / BK;

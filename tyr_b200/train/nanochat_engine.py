@@ -20,6 +20,7 @@ Differences that are deliberate and B200-specific:
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass, asdict
 from typing import Dict, List, Optional, Sequence, Tuple
 
@@ -28,6 +29,8 @@ import torch
 from ..models import nanochat as nc
 from ..ops import optim_kernels as ok
 from ..ops import polar
+
+DEFAULT_CE_CHUNK_ROWS = 8192
 
 
 @dataclass
@@ -187,7 +190,7 @@ class NanoChatTrainer:
 
     def __init__(self, cfg: nc.Config, hp: Optional[Hyperparameters] = None, device="cpu",
                  compute_dtype=torch.bfloat16, seed: Optional[int] = 0, world_size: int = 1,
-                 rank: int = 0, dp=None, ce_chunk_rows: int = 8192):
+                 rank: int = 0, dp=None, ce_chunk_rows: Optional[int] = None):
         self.cfg = cfg
         self.hp = hp or Hyperparameters()
         self.device = torch.device(device)
@@ -200,7 +203,8 @@ class NanoChatTrainer:
             alloc = dp.alloc
         self.params = nc.ModdedGPTParams(cfg, device=device, compute_dtype=compute_dtype, seed=seed, alloc=alloc)
         self.step_index = 0
-        self.ce_chunk_rows = ce_chunk_rows
+        # rows of logits alive at once in the fused lm_head + loss (bf16 [rows, vocab]); TYR_CE_CHUNK_ROWS overrides the default
+        self.ce_chunk_rows = ce_chunk_rows if ce_chunk_rows is not None else int(os.environ.get("TYR_CE_CHUNK_ROWS", DEFAULT_CE_CHUNK_ROWS))
         self.dp = dp
         p = self.params
         sharded = dp is not None and world_size > 1
