@@ -518,7 +518,7 @@ def test_moe_dense_grouped_gemm_gate_epilogues(act):
     assert _rel_err(y, ref) < 3e-2, _rel_err(y, ref)
 
 
-@pytest.mark.parametrize("M,N,K", [(1, 1024, 512), (8, 17408, 5120), (13, 272, 2048)])
+@pytest.mark.parametrize("M,N,K", [(1, 1024, 512), (8, 17408, 5120), (13, 272, 2048), (2, 128, 64), (2, 64, 64), (16, 48, 32)])
 def test_skinny_swiglu_matches_reference(M, N, K):
     from tyr_b200.ops.skinny import skinny_swiglu, swiglu_supported
     g = torch.Generator(device="cuda").manual_seed(M + N)

@@ -26,9 +26,10 @@ def qwen35_tp_matches_single_gpu(rank, world, dev, dtype, group):
     for t, chunk in enumerate([ids[:, :S], ids[:, S:S + 1], ids[:, S + 1:S + 2], ids[:, S + 2:S + 3]]):
         ref, got = ref_cache.run(torch.nn.functional.embedding(chunk, full.embed_tokens)).float(), cache.run(chunk).float()
         err = (ref - got).abs().max().item()
-        if got.shape != ref.shape or not err < tol * max(1.0, ref.abs().max().item()):
-            print(f"rank {rank} qwen35 tp chunk {t}: err {err} of {ref.abs().max().item()}", flush=True)
-            ok = False
+        bad = got.shape != ref.shape or not err < tol * max(1.0, ref.abs().max().item())
+        if bad or rank == 0:
+            print(f"rank {rank} qwen35 tp chunk {t}: err {err} of {ref.abs().max().item()}{' FAIL' if bad else ''}", flush=True)
+        ok = ok and not bad
     tp.close()
     return ok
 

@@ -185,6 +185,15 @@ class TPCache:
         return Q.gated_delta_net_core(loc, l.mixer, proj[..., :cd], proj[..., cd:cd + vd], proj[..., cd + vd:cd + vd + Hv], proj[..., cd + vd + Hv:cd + vd + 2 * Hv], self.lin[i])
 
     @staticmethod
+    def _mlp_hidden(h, gate_up):
+        """silu(h gate^T) * (h up^T) for the local column slice; decode-sized rows take the one-pass weight-streaming kernel."""
+        from ..ops import skinny
+        I = gate_up.shape[0] // 2
+        if h.shape[0] <= skinny.MAX_ROWS and h.is_cuda and skinny.swiglu_supported(h, gate_up[:I], gate_up[I:]):
+            return skinny.skinny_swiglu(h, gate_up[:I], gate_up[I:])
+        return TPCache._swiglu(lin(h, gate_up))
+
+    @staticmethod
     def _swiglu(gu):
         I = gu.shape[-1] // 2
         return (F.silu(gu[..., :I].float()) * gu[..., I:].float()).to(gu.dtype)
@@ -221,8 +230,7 @@ class TPCache:
                 proj = lin(Q.rms(x, l.input_layernorm, eps), l.mixer.in_proj)
                 core = self._mixer(i, l, proj, B, S, cos, sin).reshape(rows, -1)
                 x = tp.linear_all_reduce(core, l.mixer.o_proj if isinstance(l.mixer, TPAttention) else l.mixer.out_proj, add=x)
-                gu = lin(Q.rms(x, l.post_attention_layernorm, eps), l.ffn.gate_up)
-                x = tp.linear_all_reduce(self._swiglu(gu), l.ffn.down, add=x)
+                x = tp.linear_all_reduce(self._mlp_hidden(Q.rms(x, l.post_attention_layernorm, eps), l.ffn.gate_up), l.ffn.down, add=x)
             x_last = x.reshape(B, S, -1)[:, -1]
         self.pos += S
         return tp.all_gather_cols(lin(Q.rms(x_last, m.norm, eps), m.lm_head))
@@ -253,8 +261,7 @@ class TPCache:
                 core = Q.gated_delta_net_core(loc, l.mixer, proj[..., :cd], proj[..., cd:cd + vd], proj[..., cd + vd:cd + vd + Hv], proj[..., cd + vd + Hv:cd + vd + 2 * Hv], self.lin[i])
                 w_out = l.mixer.out_proj
             x = tp.linear_all_reduce(core.reshape(B, -1), w_out, add=x)
-            gu = lin(Q.rms(x, l.post_attention_layernorm, eps), l.ffn.gate_up)
-            x = tp.linear_all_reduce(self._swiglu(gu), l.ffn.down, add=x)
+            x = tp.linear_all_reduce(self._mlp_hidden(Q.rms(x, l.post_attention_layernorm, eps), l.ffn.gate_up), l.ffn.down, add=x)
         self.pos_t += 1
         return Q.rms(x, m.norm, eps)
 
