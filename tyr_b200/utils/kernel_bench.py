@@ -252,6 +252,17 @@ def bench_skinny(results):
         print(f"skinny M={M:2d} N={N:6d} K={K:5d}: ours {ours * 1e3:7.1f} us {gb / ours * 1e3:6.0f} GB/s | library {libms * 1e3:7.1f} us {gb / libms * 1e3:6.0f} GB/s", flush=True)
 
 
+def bench_gemm_fwd_small(results):
+    """The forward qkv projection of NanoChat d20 alone, few launches: the case to put under a profiler."""
+    from tyr_b200.ops.gemm import gemm
+    dev = torch.device("cuda")
+    a = torch.randn(65536, 1280, device=dev).bfloat16()
+    b = torch.randn(3840, 1280, device=dev).bfloat16()
+    ms = _time(lambda: gemm(a, b, a_layout="K", b_layout="K"), iters=3, warmup=2)
+    results.append({"kernel": "gemm", "shape": "fwd qkv [65536x1280]x[3840x1280]^T", "ours_ms": ms, "ours_tflops": 2.0 * 65536 * 3840 * 1280 / ms / 1e9})
+    print(f"fwd qkv: {ms:.3f} ms", flush=True)
+
+
 def bench_qwen3_decode(results):
     """Greedy decode through ``Qwen3Session`` (random-init Qwen3-4B shape, 1024-token prompt, 64 timed steps) for
     batch 1 and 8, once replaying the captured step graph and once launching the same kernels eagerly."""
@@ -292,6 +303,8 @@ def bench_qwen3_decode(results):
 def main(argv):
     what = argv[1] if len(argv) > 1 else "all"
     results = []
+    if what == "gemm-fwd-small":
+        bench_gemm_fwd_small(results)
     if what == "qwen3-decode":
         bench_qwen3_decode(results)
     if what in ("gemm", "all"):
