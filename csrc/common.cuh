@@ -155,6 +155,10 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const void* tmap, uint64_
       : "r"(smem_u32(dst)), "l"(tmap), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
+// Asks for a tile to be brought into L2; completes nothing and signals nothing.
+__device__ __forceinline__ void tma_prefetch_l2_3d(const void* tmap, int x, int y, int z) {
+  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];" : : "l"(tmap), "r"(x), "r"(y), "r"(z) : "memory");
+}
 __device__ __forceinline__ void tma_load_4d(void* dst, const void* tmap, uint64_t* bar, int x,
                                             int y, int z, int w) {
   asm volatile(

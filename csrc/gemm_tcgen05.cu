@@ -48,6 +48,10 @@ struct GemmParams {
   // of B in L2: right while B is the smaller operand), 1 = row tiles fastest (A stays in L2 and B streams once: an lm_head
   // whose vocabulary matrix is larger than L2).
   int raster_m;
+  // > 0 (plain mode only; TYR_GEMM_L2_PREFETCH, off by default): the producer asks L2 for the operand tiles of the k block
+  // this many steps ahead of the one it loads, across tile boundaries.  Measured at 8 and 16 steps it made every NanoChat
+  // shape slower (forward qkv 1248 -> 1108 TFLOP/s): all CTAs that share a tile repeat the request.
+  int l2_prefetch;
   int* err;
   // Grouped mode (MoE): batch = number of groups, A and C are packed [rows, *] with group g owning
   // rows [group_offsets[g], group_offsets[g+1]).  group_tiles[g] is the exclusive prefix sum of
@@ -228,6 +232,35 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       int kb0, kb1;
       uint32_t it = 0;
       bool ok = true;
+      // second walk over the same segments, p.l2_prefetch k blocks ahead of the loads
+      long long pf_cursor = cursor0, pf_tile;
+      int pf_kb = 0, pf_kb1 = 0, pf_bi = 0, pf_m0 = 0, pf_n0 = 0;
+      bool pf_live = p.l2_prefetch > 0;
+      auto pf_step = [&]() {
+        if (!pf_live) return;
+        if (pf_kb >= pf_kb1) {
+          if (!next_segment(pf_cursor, pf_tile, pf_kb, pf_kb1)) {
+            pf_live = false;
+            return;
+          }
+          decode_tile(pf_tile, pf_bi, pf_m0, pf_n0);
+        }
+        const int k0 = pf_kb * BK;
+        if (!A_MN) {
+          tma_prefetch_l2_3d(&tmA, k0, pf_m0, pf_bi);
+        } else {
+#pragma unroll
+          for (int c = 0; c < BM / 64; ++c) tma_prefetch_l2_3d(&tmA, pf_m0 + c * 64, k0, pf_bi);
+        }
+        if (!B_MN) {
+          tma_prefetch_l2_3d(&tmB, k0, pf_n0, pf_bi);
+        } else {
+#pragma unroll
+          for (int c = 0; c < BN / 64; ++c) tma_prefetch_l2_3d(&tmB, pf_n0 + c * 64, k0, pf_bi);
+        }
+        ++pf_kb;
+      };
+      for (int i = 0; i < p.l2_prefetch; ++i) pf_step();
       while (ok && next_segment(cursor, tile, kb0, kb1)) {
         int bi, m0, n0;
         decode_tile(tile, bi, m0, n0);
@@ -258,6 +291,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
             ok = false;
             break;
           }
+          pf_step();
           mbar_expect_tx(&s.full[st], kStageBytes);
           const int k0 = kb * BK;
           if (!A_MN) {
@@ -654,6 +688,7 @@ struct TyrGemmArgs {
 }  // extern "C"
 
 static int g_sm_count = 0;
+static const int g_l2_prefetch = [] { const char* e = getenv("TYR_GEMM_L2_PREFETCH"); const int v = e ? atoi(e) : 0; return v < 0 ? 0 : (v > 64 ? 64 : v); }();
 static const bool g_raster_m = [] { const char* e = getenv("TYR_GEMM_RASTER_M"); return e == nullptr || e[0] != '0'; }();
 static const bool g_aligned_split = [] { const char* e = getenv("TYR_GEMM_ALIGNED_SPLIT"); return e == nullptr || e[0] != '0'; }();
 
@@ -687,6 +722,7 @@ static int launch_gemm(const TyrGemmArgs& a, const CUtensorMap& tmA, const CUten
   int grid = a.sm_count > 0 ? a.sm_count : g_sm_count;
   if (a.out_mode != 2 && tiles < grid) grid = static_cast<int>(tiles);
   p.raster_m = (a.group_offsets == nullptr && tp.tp_mode == 0 && a.M < a.N && g_raster_m) ? 1 : 0;
+  p.l2_prefetch = (a.group_offsets == nullptr && tp.tp_mode == 0) ? g_l2_prefetch : 0;
   p.sk_slabs = 0;
   if (a.out_mode == 2) {
     const int num_kb = (a.K + BK - 1) / BK;
