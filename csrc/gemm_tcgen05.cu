@@ -11,10 +11,11 @@
 //   warps 2..5 = epilogue (one TMEM lane quarter each).  The fp32 accumulator lives in TMEM
 //   and is double buffered (2 x BN columns) so the epilogue of tile i overlaps the main loop
 //   of tile i+1.
-// * Work is either split at tile granularity (plain stores) or as an even stream-K partition of
-//   all (tile, k-block) units with fp32 `red.global.add` accumulation into a zero-initialised
-//   (or gradient-accumulating) output, which removes wave quantisation for the weight-gradient
-//   shapes (few output tiles, very long K).
+// * Work is either split at tile granularity (plain stores) or, for the weight-gradient shapes
+//   (few output tiles, very long K), along K with fp32 `red.global.add` accumulation into a
+//   zero-initialised (or gradient-accumulating) output: whole tiles for as many full rounds as
+//   there are, the remaining tiles cut into k slabs dealt round-robin.  All CTAs then sweep the
+//   same k blocks at the same time, so operand slabs are shared through L2 (see GemmParams).
 // * Every mbarrier wait is bounded; a timeout records an error and unwinds through the normal
 //   teardown (TMEM is released).
 //
