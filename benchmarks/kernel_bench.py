@@ -1,4 +1,4 @@
-"""Kernel micro-benchmarks: `python -m tyr_b200.utils.kernel_bench [gemm|attention|moe|moe-decode|decode-attn|skinny|qwen3-decode|all]`.
+"""Kernel micro-benchmarks: `python -m benchmarks.kernel_bench [gemm|attention|moe|moe-decode|decode-attn|skinny|qwen3-decode|all]`.
 
 Times the hand-written kernels with CUDA events (5 warm-up + 20 timed iterations, a 256 MB
 buffer written between iterations to flush the 126 MB L2) on the NanoChat d20 shapes and prints

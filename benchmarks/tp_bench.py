@@ -1,6 +1,6 @@
 """Fused tensor-parallel GEMMs against the NCCL formulation of the same ops.
 
-    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 -m tyr_b200.parallel.tp_bench
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 -m benchmarks.tp_bench
 
 Shapes: Qwen3.5-27B-like row-parallel projections (hidden 5120; attention output 24*256 and FFN 17408
 input channels split over the ranks) and the matching column-parallel projections, for a prefill batch

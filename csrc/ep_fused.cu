@@ -95,9 +95,12 @@ ep_pull_kernel(EpPeers xs, const int* seg_rows, const int* seg_src_row, const in
 }
 
 // out[t] = sum_s w[t,s] * y_owner[dest_base_owner[e_local][me] + (pos - offsets[e])] (+ add[t])
+// A row index outside [0, capacity) (the owner received more rows than its buffers hold: ep_layout recorded the overflow
+// and ep_pull skipped the segment) contributes nothing and records ERR_BOUNDS; the owner's y is never read past its end.
 __global__ void __launch_bounds__(256)
 ep_combine_kernel(EpPeers y, EpPeers dest_base, const int* ids, const float* weights, const int* pair_pos, const int* offsets,
-                  const __nv_bfloat16* add, __nv_bfloat16* out, int T, int k, int h, int E_local, int world, int my_rank) {
+                  const __nv_bfloat16* add, __nv_bfloat16* out, int T, int k, int h, int E_local, int world, int my_rank,
+                  int capacity, int* err) {
   const int vec = h >> 3;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < static_cast<long long>(T) * vec;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
@@ -109,6 +112,10 @@ ep_combine_kernel(EpPeers y, EpPeers dest_base, const int* ids, const float* wei
       const int owner = e / E_local, el = e - owner * E_local;
       const int q = pair_pos[pair] - offsets[e];
       const int row = reinterpret_cast<const int*>(dest_base.p[owner])[el * world + my_rank] + q;
+      if (e < 0 || owner >= world || row < 0 || row >= capacity) {
+        if (c == 0) report_error(err, ERR_BOUNDS, row);
+        continue;
+      }
       const float w = weights[pair];
       const uint4 u = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(y.p[owner]) +
                                                      static_cast<long long>(row) * h)[c];
@@ -163,12 +170,13 @@ extern "C" TYR_EXPORT int tyr_ep_pull(void* const* src_offsets, void* const* xs,
 
 extern "C" TYR_EXPORT int tyr_ep_combine(void* const* y, void* const* dest_base, const int* ids, const float* weights,
                                          const int* pair_pos, const int* offsets, const void* add, void* out, int T, int k,
-                                         int h, int E_local, int world, int my_rank, void* stream) {
-  if (world < 1 || world > kEpMaxRanks || T <= 0 || (h & 7)) return -1;
+                                         int h, int E_local, int world, int my_rank, int capacity, int* err, void* stream) {
+  if (world < 1 || world > kEpMaxRanks || T <= 0 || (h & 7) || capacity <= 0) return -1;
   long long blocks = (static_cast<long long>(T) * (h / 8) + 255) / 256;
   if (blocks > 148 * 8) blocks = 148 * 8;
   ep_combine_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>(make_ep_peers(y, world), make_ep_peers(dest_base, world), ids,
                                                                   weights, pair_pos, offsets, (const __nv_bfloat16*)add,
-                                                                  (__nv_bfloat16*)out, T, k, h, E_local, world, my_rank);
+                                                                  (__nv_bfloat16*)out, T, k, h, E_local, world, my_rank,
+                                                                  capacity, err);
   return (int)cudaGetLastError();
 }

@@ -106,20 +106,33 @@ __device__ __forceinline__ float apply_act(float v, int act) {
   return v;
 }
 
-template <int BN, int STAGES, bool A_MN, bool B_MN>
+// PAIR = true: the grid is launched as clusters of two CTAs that share one 256 x BN output tile through
+// tcgen05.mma.cta_group::2.  Each CTA loads its own 128 rows of A and its own half (BN / 2 columns) of B with plain TMA
+// loads whose completion is counted on the leader's `full` barrier; the leader (cluster rank 0) issues every MMA and
+// commits to the `empty` / `acc_full` barriers of both CTAs; each CTA's epilogue drains its own 128 accumulator rows
+// and arrives on the leader's `acc_empty`.  A stage costs 32 KB instead of 48 KB and every operand byte in shared
+// memory feeds twice the tensor-core work, which is what the single-CTA form runs short of.  Plain mode only (no
+// grouped rows, no K split, no tensor-parallel fusion, K-major A).
+template <int BN, int STAGES, bool A_MN, bool B_MN, bool PAIR>
 __global__ void __launch_bounds__(256, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
                          const __grid_constant__ CUtensorMap tmB,
                          const __grid_constant__ CUtensorMap tmC,
                          const __grid_constant__ TmapPeers tmP, GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
-  using Smem = GemmSmem<BN, STAGES>;
+  constexpr int BNL = PAIR ? BN / 2 : BN;          // columns of B this CTA keeps in shared memory
+  constexpr int TILE_M = PAIR ? 2 * BM : BM;       // rows of the tile one scheduler unit covers
+  using Smem = GemmSmem<BNL, STAGES>;
   Smem& s = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                      ~static_cast<uintptr_t>(1023));
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const uint32_t cta_rank = PAIR ? cluster_ctarank() : 0u;
+  // scheduler units: CTAs, or CTA pairs
+  const int n_workers = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
+  const int worker = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
 
-  const int tiles_m = (p.M + BM - 1) / BM;
+  const int tiles_m = (p.M + TILE_M - 1) / TILE_M;
   const int tiles_n = (p.N + BN - 1) / BN;
   const int num_kb = (p.K + BK - 1) / BK;
   const bool grouped = p.group_offsets != nullptr;
@@ -130,8 +143,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
   long long unit_begin, unit_end;
   if (p.out_mode == 2) {
     const long long units = tiles * num_kb;
-    unit_begin = units * blockIdx.x / gridDim.x;
-    unit_end = units * (blockIdx.x + 1) / gridDim.x;
+    unit_begin = units * worker / n_workers;
+    unit_end = units * (worker + 1) / n_workers;
   } else {
     // tile-granular, strided assignment expressed in the same unit space
     unit_begin = 0;
@@ -145,24 +158,33 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s.acc_full[i], 1);
-      mbar_init(&s.acc_empty[i], 4);  // one arrival per epilogue warp
+      mbar_init(&s.acc_empty[i], PAIR ? 8 : 4);  // one arrival per epilogue warp (of both CTAs of a pair)
     }
     s.abort_flag = 0;
     mbar_fence_init();
   }
   if (warp == 1) {
-    tmem_alloc(&s.tmem_base, 2 * BN);
-    tmem_relinquish();
+    if (PAIR) {
+      tmem_alloc_pair(&s.tmem_base, 2 * BN);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(&s.tmem_base, 2 * BN);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if (PAIR) {   // the peer's barriers must exist before anything arrives on them
+    cluster_arrive();
+    cluster_wait();
+  }
   tc_fence_after();
   const uint32_t tmem_base = s.tmem_base;
 
-  constexpr uint32_t kStageBytes = BM * BK * 2 + BN * BK * 2;
+  constexpr uint32_t kStageBytes = BM * BK * 2 + BNL * BK * 2;
 
   // Segment iterator shared by the three roles (identical sequence in each).
-  const long long whole_tiles = (tiles / gridDim.x) * gridDim.x;
+  const long long whole_tiles = (tiles / n_workers) * n_workers;
   auto next_segment = [&](long long& cursor, long long& tile, int& kb0, int& kb1) -> bool {
     if (p.out_mode == 2 && p.sk_slabs > 0) {
       if (cursor < whole_tiles) {
@@ -177,7 +199,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
         kb0 = static_cast<int>(static_cast<long long>(num_kb) * slab / p.sk_slabs);
         kb1 = static_cast<int>(static_cast<long long>(num_kb) * (slab + 1) / p.sk_slabs);
       }
-      cursor += gridDim.x;
+      cursor += n_workers;
       return true;
     } else if (p.out_mode == 2) {
       if (cursor >= unit_end) return false;
@@ -192,7 +214,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       tile = cursor;
       kb0 = 0;
       kb1 = num_kb;
-      cursor += gridDim.x;
+      cursor += n_workers;
       return true;
     }
   };
@@ -215,14 +237,15 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     const int r = static_cast<int>(tile % per_batch);
     // n fastest: concurrently resident tiles share A rows and keep B (weights) in L2.
     if (p.raster_m) {
-      m0 = (r % tiles_m) * BM;
+      m0 = (r % tiles_m) * TILE_M;
       n0 = (r / tiles_m) * BN;
     } else {
-      m0 = ((r / tiles_n + p.m_rot) % tiles_m) * BM;
+      m0 = ((r / tiles_n + p.m_rot) % tiles_m) * TILE_M;
       n0 = (r % tiles_n) * BN;
     }
+    if (PAIR) m0 += static_cast<int>(cta_rank) * BM;   // this CTA's half of the pair's rows
   };
-  const long long cursor0 = (p.out_mode == 2 && p.sk_slabs == 0) ? unit_begin : static_cast<long long>(blockIdx.x);
+  const long long cursor0 = (p.out_mode == 2 && p.sk_slabs == 0) ? unit_begin : static_cast<long long>(worker);
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -293,8 +316,23 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
             break;
           }
           pf_step();
-          mbar_expect_tx(&s.full[st], kStageBytes);
           const int k0 = kb * BK;
+          if (PAIR) {
+            // both CTAs' bytes are counted on the leader's barrier; only the leader arms it
+            const uint32_t bar = mapa_shared(smem_u32(&s.full[st]), 0);
+            if (cta_rank == 0) mbar_expect_tx(&s.full[st], 2 * kStageBytes);
+            tma_load_3d_pair(s.a[st], &tmA, bar, k0, m0, bi);
+            const int nb = n0 + static_cast<int>(cta_rank) * BNL;
+            if (!B_MN) {
+              tma_load_3d_pair(s.b[st], &tmB, bar, k0, nb, bi);
+            } else {
+#pragma unroll
+              for (int c = 0; c < BNL / 64; ++c)
+                tma_load_3d_pair(s.b[st] + c * (64 * BK * 2), &tmB, bar, nb + c * 64, k0, bi);
+            }
+            continue;
+          }
+          mbar_expect_tx(&s.full[st], kStageBytes);
           if (!A_MN) {
             if (p.group_offsets != nullptr)
               tma_load_3d(s.a[st], &tmA, &s.full[st], k0, p.group_offsets[bi] + m0, 0);
@@ -325,8 +363,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (elect_one()) {
-      constexpr uint32_t idesc = make_idesc_f16(1, BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+    if ((!PAIR || cta_rank == 0) && elect_one()) {
+      constexpr uint32_t idesc = make_idesc_f16(1, TILE_M, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
       long long cursor = cursor0, tile;
       int kb0, kb1;
       uint32_t it = 0, seg = 0;
@@ -334,7 +372,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       while (ok && next_segment(cursor, tile, kb0, kb1)) {
         const uint32_t buf = seg & 1;
         const uint32_t acc_ph = (seg >> 1) & 1;
-        if (!mbar_wait(&s.acc_empty[buf], acc_ph ^ 1, p.err, 200 + buf)) {
+        if (!(PAIR ? mbar_wait_cluster(&s.acc_empty[buf], acc_ph ^ 1, p.err, 200 + buf)
+                   : mbar_wait(&s.acc_empty[buf], acc_ph ^ 1, p.err, 200 + buf))) {
           ok = false;
           break;
         }
@@ -361,11 +400,27 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
               db = make_smem_desc_sw128(b_addr + k * (UMMA_K * 2), 16, 1024);
             else
               db = make_smem_desc_sw128(b_addr + k * (UMMA_K * 128), 64 * BK * 2, 1024);
-            umma_f16_ss(d_tmem, da, db, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+            if (PAIR)
+              umma_f16_ss_pair(d_tmem, da, db, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+            else
+              umma_f16_ss(d_tmem, da, db, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           }
-          umma_commit(&s.empty[st]);  // frees the smem stage once these MMAs retire
+          // frees the smem stage (in both CTAs of a pair) once these MMAs retire
+          if (PAIR) {
+            umma_commit_pair(smem_u32(&s.empty[st]));
+            umma_commit_pair(mapa_shared(smem_u32(&s.empty[st]), 1));
+          } else {
+            umma_commit(&s.empty[st]);
+          }
         }
-        if (ok) umma_commit(&s.acc_full[buf]);
+        if (ok) {
+          if (PAIR) {
+            umma_commit_pair(smem_u32(&s.acc_full[buf]));
+            umma_commit_pair(mapa_shared(smem_u32(&s.acc_full[buf]), 1));
+          } else {
+            umma_commit(&s.acc_full[buf]);
+          }
+        }
         ++seg;
       }
       if (!ok) s.abort_flag = 1;
@@ -452,7 +507,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           if (c == BN / 64 - 1) {
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&s.acc_empty[buf]);
+            if (lane == 0) {
+            if (PAIR) mbar_arrive_cluster(mapa_shared(smem_u32(&s.acc_empty[buf]), 0));
+            else mbar_arrive(&s.acc_empty[buf]);
+          }
           }
           const int col = n0 / 2 + c * 32;
           if (!row_ok || col >= p.N / 2) continue;
@@ -493,7 +551,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           // accumulator fully read: hand the TMEM buffer back to the MMA warp
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(&s.acc_empty[buf]);
+          if (lane == 0) {
+            if (PAIR) mbar_arrive_cluster(mapa_shared(smem_u32(&s.acc_empty[buf]), 0));
+            else mbar_arrive(&s.acc_empty[buf]);
+          }
         }
         const int col = n0 + c * 32;
         if (tma_out) {
@@ -553,7 +614,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           if ((c & 1) || col + 32 >= p.N) {
             fence_proxy_async();
             __syncwarp();
-            if (lane == 0) {
+            if (lane == 0 && m0 + quarter * 32 < p.M) {
               int y = m0 + quarter * 32;
               const CUtensorMap* tm = &tmC;
               if (p.tp_mode == 1) {
@@ -617,9 +678,14 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
 
   tc_fence_before();
   __syncthreads();
+  if (PAIR) {   // neither CTA may leave (or free TMEM) while its peer can still touch its shared memory or TMEM
+    cluster_arrive();
+    cluster_wait();
+  }
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, 2 * BN);
+    if (PAIR) tmem_dealloc_pair(tmem_base, 2 * BN);
+    else tmem_dealloc(tmem_base, 2 * BN);
   }
 }
 
@@ -688,23 +754,61 @@ struct TyrGemmArgs {
 
 }  // extern "C"
 
-static int g_sm_count = 0;
+// Per-device launch state: SM count, and which kernel instantiations already had their dynamic shared-memory limit
+// raised on that device (the attribute is per device, so a second GPU used from the same process needs its own call).
+constexpr int kMaxGemmDevices = 64;
+static int g_sm_count_dev[kMaxGemmDevices] = {0};
+static int g_pair_clusters_dev[kMaxGemmDevices] = {0};
+static std::mutex g_gemm_mu;
+static int current_device() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxGemmDevices) return 0;
+  return dev;
+}
+static int device_sm_count() {
+  const int dev = current_device();
+  if (g_sm_count_dev[dev] == 0) {
+    int n = 0;
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    g_sm_count_dev[dev] = n > 0 ? n : 1;
+  }
+  return g_sm_count_dev[dev];
+}
+static const bool g_pair_enabled = [] { const char* e = getenv("TYR_GEMM_PAIR"); return e == nullptr || e[0] != '0'; }();
 static const int g_l2_prefetch = [] { const char* e = getenv("TYR_GEMM_L2_PREFETCH"); const int v = e ? atoi(e) : 0; return v < 0 ? 0 : (v > 64 ? 64 : v); }();
 static const bool g_raster_m = [] { const char* e = getenv("TYR_GEMM_RASTER_M"); return e == nullptr || e[0] != '0'; }();
 static const bool g_aligned_split = [] { const char* e = getenv("TYR_GEMM_ALIGNED_SPLIT"); return e == nullptr || e[0] != '0'; }();
 
-template <int BN, int STAGES, bool A_MN, bool B_MN>
+template <int BN, int STAGES, bool A_MN, bool B_MN, bool PAIR = false>
 static int launch_gemm(const TyrGemmArgs& a, const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC,
                        const tyr::TmapPeers& tmP, const tyr::GemmParams& tp) {
   using namespace tyr;
-  auto kern = gemm_bf16_tcgen05_kernel<BN, STAGES, A_MN, B_MN>;
-  constexpr size_t smem = sizeof(GemmSmem<BN, STAGES>) + 1024;
-  static bool configured = false;
-  if (!configured) {
+  auto kern = gemm_bf16_tcgen05_kernel<BN, STAGES, A_MN, B_MN, PAIR>;
+  constexpr size_t smem = sizeof(GemmSmem<PAIR ? BN / 2 : BN, STAGES>) + 1024;
+  static bool configured[kMaxGemmDevices] = {false};
+  const int dev = current_device();
+  const int g_sm_count = device_sm_count();
+  if (!configured[dev]) {
+    std::lock_guard<std::mutex> lock(g_gemm_mu);
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(smem));
     if (e != cudaSuccess) return 1000 + static_cast<int>(e);
-    configured = true;
+    if (PAIR && g_pair_clusters_dev[dev] == 0) {
+      // how many CTA pairs the device can keep resident at once (one CTA per SM, pairs within a TPC)
+      cudaLaunchConfig_t qc = {};
+      qc.gridDim = dim3(static_cast<unsigned>(g_sm_count & ~1));
+      qc.blockDim = dim3(256);
+      qc.dynamicSmemBytes = smem;
+      cudaLaunchAttribute qa[1];
+      qa[0].id = cudaLaunchAttributeClusterDimension;
+      qa[0].val.clusterDim.x = 2; qa[0].val.clusterDim.y = 1; qa[0].val.clusterDim.z = 1;
+      qc.attrs = qa; qc.numAttrs = 1;
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, kern, &qc) != cudaSuccess || n <= 0) n = g_sm_count / 2;
+      if (n > g_sm_count / 2) n = g_sm_count / 2;
+      g_pair_clusters_dev[dev] = n;
+    }
+    configured[dev] = true;
   }
   GemmParams p;
   p.M = a.M; p.N = a.N; p.K = a.K; p.batch = a.batch;
@@ -717,7 +821,8 @@ static int launch_gemm(const TyrGemmArgs& a, const CUtensorMap& tmA, const CUten
   p.rows_per_rank = tp.rows_per_rank; p.m_rot = tp.m_rot;
   for (int i = 0; i < 8; ++i) p.peer_c[i] = tp.peer_c[i];
   p.gather_buf = tp.gather_buf; p.tile_ready = tp.tile_ready; p.lda = a.lda;
-  long long tiles = static_cast<long long>((a.M + BM - 1) / BM) * ((a.N + BN - 1) / BN) * a.batch;
+  constexpr int TILE_M = PAIR ? 2 * BM : BM;
+  long long tiles = static_cast<long long>((a.M + TILE_M - 1) / TILE_M) * ((a.N + BN - 1) / BN) * a.batch;
   if (a.group_offsets != nullptr)   // host-side bound: every group may add one partial m-tile
     tiles = ((a.sA + BM - 1) / BM + (a.batch < a.sA ? a.batch : a.sA)) * ((a.N + BN - 1) / BN);
   int grid = a.sm_count > 0 ? a.sm_count : g_sm_count;
@@ -745,6 +850,23 @@ static int launch_gemm(const TyrGemmArgs& a, const CUtensorMap& tmA, const CUten
     }
   }
   if (grid < 1) grid = 1;
+  if (PAIR) {
+    int pairs = g_pair_clusters_dev[dev];
+    if (a.sm_count > 0 && a.sm_count / 2 < pairs) pairs = a.sm_count / 2;
+    if (pairs < 1) pairs = 1;
+    if (tiles < pairs) pairs = static_cast<int>(tiles);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));
+    cfg.blockDim = dim3(256);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = reinterpret_cast<cudaStream_t>(a.stream);
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+    cfg.attrs = at; cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmC, tmP, p);
+    return e == cudaSuccess ? 0 : 2000 + static_cast<int>(e);
+  }
   kern<<<grid, 256, smem, reinterpret_cast<cudaStream_t>(a.stream)>>>(tmA, tmB, tmC, tmP, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 2000 + static_cast<int>(e);
@@ -820,11 +942,6 @@ static int gemm_impl(const TyrGemmArgs& a, const TyrTpArgs* tpa) {
   if ((a.lda & 7) || (a.ldb & 7) || (a.group_offsets == nullptr && (a.sA & 7)) || (a.sB & 7)) return -3;
   if (a.out_mode == 0 ? (a.ldc & 7) : (a.ldc & 3)) return -4;
   if (a.aux && ((a.ldaux & 7) || (reinterpret_cast<uintptr_t>(a.aux) & 15))) return -5;
-  if (g_sm_count == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
-  }
   int bn = a.bn;
   if (bn == 0) bn = (a.N <= 128) ? 128 : 256;
   CUtensorMap tmA, tmB;
@@ -838,8 +955,11 @@ static int gemm_impl(const TyrGemmArgs& a, const TyrTpArgs* tpa) {
   else
     r = make_tmap_bf16_3d(&tmA, a.A, a.M, a.K, a.batch, a.lda, a.sA, BK);
   if (r) return 3000 + r;
+  // CTA pairs: plain products with a K-major A whose tiles are 256 columns wide
+  const bool pair = g_pair_enabled && tpa == nullptr && a.group_offsets == nullptr && a.out_mode != 2 && !a.a_mn &&
+                    bn == 256 && a.act != 4 && a.act != 5;
   if (!a.b_mn)
-    r = make_tmap_bf16_3d(&tmB, a.B, a.K, a.N, a.batch, a.ldb, a.sB, bn);
+    r = make_tmap_bf16_3d(&tmB, a.B, a.K, a.N, a.batch, a.ldb, a.sB, pair ? bn / 2 : bn);
   else
     r = make_tmap_bf16_3d(&tmB, a.B, a.N, a.K, a.batch, a.ldb, a.sB, BK);
   if (r) return 4000 + r;
@@ -864,6 +984,10 @@ static int gemm_impl(const TyrGemmArgs& a, const TyrTpArgs* tpa) {
     if (a.a_mn && a.b_mn) return launch_gemm<BNv, ST, true, true>(a, tmA, tmB, tmC, tmP, tp);     \
     return launch_gemm<BNv, ST, true, false>(a, tmA, tmB, tmC, tmP, tp);                      \
   } while (0)
+  if (pair) {
+    if (!a.b_mn) return launch_gemm<256, 6, false, false, true>(a, tmA, tmB, tmC, tmP, tp);
+    return launch_gemm<256, 6, false, true, true>(a, tmA, tmB, tmC, tmP, tp);
+  }
   if (bn == 256) TYR_DISPATCH(256, 4);
   if (bn == 128) TYR_DISPATCH(128, 6);
 #undef TYR_DISPATCH

@@ -62,6 +62,51 @@ def test_gemm_epilogues_and_batch(bn):
     assert _rel_err(outg, refg) < 1e-2
 
 
+def _assert_elementwise(out, ref, K, what=""):
+    """Per-element bound: the bf16 (or fp32) rounding of the result plus an accumulation term that grows like sqrt(K).
+    One wrong output tile breaks it by orders of magnitude, which a norm ratio over a large matrix does not show."""
+    out, ref = out.float(), ref.float()
+    err = (out - ref).abs()
+    bound = 2.0 ** -7 * ref.abs() + 4e-3 * math.sqrt(K) + 1e-3
+    bad = err > bound
+    assert not bool(bad.any()), (what, int(bad.sum()), float(err.max()), bad.nonzero()[:4].tolist())
+
+
+@pytest.mark.parametrize("M,N,K,b_layout", [
+    (65536, 3840, 1280, "K"),      # forward qkv projection of the d20 model (CTA pairs, 52 rounds of 256 x 256 tiles)
+    (65536, 1280, 5120, "MN"),     # data gradient of the MLP up-projection
+    (8192, 65536, 1280, "K"),      # lm_head chunk: row-fastest tile order
+    (1000, 2000, 328, "K"),        # ragged edges in every dimension, second CTA of the last pair partly out of range
+    (130, 384, 64, "MN"),          # the pair's second CTA holds 2 valid rows
+])
+def test_gemm_production_shapes_elementwise(M, N, K, b_layout):
+    from tyr_b200.ops.gemm import gemm
+    g = torch.Generator(device="cuda").manual_seed(11)
+    a = torch.randn(M, K, device=_dev(), generator=g).bfloat16()
+    b = torch.randn((N, K) if b_layout == "K" else (K, N), device=_dev(), generator=g).bfloat16()
+    out = gemm(a, b, b_layout=b_layout)
+    step = 8192
+    for r0 in range(0, M, step):      # reference in row slabs: keeps the fp32 product small
+        ref = a[r0:r0 + step].float() @ (b.float().t() if b_layout == "K" else b.float())
+        _assert_elementwise(out[r0:r0 + step], ref, K, f"rows {r0}")
+    assert _rel_err(out[:4096], a[:4096].float() @ (b.float().t() if b_layout == "K" else b.float())) < 5e-3
+
+
+def test_gemm_wgrad_production_shape_elementwise():
+    """K = 65536 weight gradient (MN/MN, fp32 accumulate): whole-tile rounds plus a k-slab remainder on all SMs."""
+    from tyr_b200.ops.gemm import gemm
+    g = torch.Generator(device="cuda").manual_seed(12)
+    Kt, M, N = 65536, 5120, 1280
+    dy = torch.randn(Kt, M, device=_dev(), generator=g).bfloat16()
+    x = torch.randn(Kt, N, device=_dev(), generator=g).bfloat16()
+    acc = torch.zeros(M, N, device=_dev(), dtype=torch.float32)
+    gemm(dy, x, a_layout="MN", b_layout="MN", out=acc, accumulate=True)
+    ref = dy.float().t() @ x.float()
+    err = (acc - ref).abs()
+    assert float(err.max()) < 0.05 * math.sqrt(Kt) * 2.0 ** -8 + 1e-1, float(err.max())
+    assert _rel_err(acc, ref) < 1e-3
+
+
 @pytest.mark.parametrize("Kt,M,N", [(4096, 384, 256), (1024, 2048, 2560), (704, 1344, 520), (64, 19072, 256)])
 def test_gemm_stream_k_accumulate(Kt, M, N):
     """Fewer tiles than SMs, a whole round of tiles plus a remainder, ragged edges, and a single k block."""

@@ -369,8 +369,10 @@ def moe_forward(cfg: LagunaConfig, m: SparseMoeBlock, x2: torch.Tensor, use_fuse
     fused_ok = use_fused and x2.is_cuda and x2.dtype == torch.bfloat16
     if fused_ok:
         return moe_ops.moe_fp4_forward(x2, ids, w, m.experts, counts=counts, add=shared)
+    # eager path on the dequantised banks: model-dtype arithmetic in the reference's op order
     g, u, d = m.experts.dense()
-    return (moe_ops.moe_eager(x2, ids, w, g, u, d).float() + shared.float()).to(x2.dtype)
+    sc = cfg.moe_routed_scaling_factor
+    return moe_ops.moe_eager_model_dtype(x2, ids, w / sc, g, u, d, scale=sc) + shared
 
 
 def attention_forward(cfg: LagunaConfig, i: int, a: Attention, x: torch.Tensor, cos, sin,

@@ -318,6 +318,29 @@ def moe_eager(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, gate: t
     return out.to(x.dtype)
 
 
+def moe_eager_model_dtype(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, gate: torch.Tensor, up: torch.Tensor,
+                          down: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    """The same per-unique-expert loop with every operation in the model dtype and in the order of the reference's eager
+    path (MoE.lean:313-356): experts in ascending order, ``linear`` / SiLU / product / ``linear`` each rounded to ``x.dtype``,
+    routing weights (without the routed scale, rounded to ``x.dtype``) applied to the expert output, accumulator in
+    ``x.dtype``, the routed scale applied once after accumulation.  In bf16 this reproduces the rounding points of the
+    Hugging Face implementation that generated the reference's fixtures; in fp32 it equals :func:`moe_eager`."""
+    T, h = x.shape
+    dt = x.dtype
+    acc = torch.zeros(T, h, dtype=dt, device=x.device)
+    w = weights.to(dt)
+    lin = torch.nn.functional.linear
+    for e in torch.unique(ids).tolist():
+        if e < 0 or e >= gate.shape[0]:
+            continue
+        tok, slot = torch.nonzero(ids == e, as_tuple=True)
+        xe = x[tok]
+        hdn = torch.nn.functional.silu(lin(xe, gate[e].to(dt))) * lin(xe, up[e].to(dt))
+        oe = lin(hdn, down[e].to(dt)) * w[tok, slot].unsqueeze(-1)
+        acc.index_add_(0, tok, oe)
+    return acc * scale
+
+
 GEMV_MAX_PAIRS_PER_EXPERT = 8
 
 

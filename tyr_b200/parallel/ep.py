@@ -25,7 +25,7 @@ def _declare(lib):
     P, I = ctypes.c_void_p, ctypes.c_int
     lib.tyr_ep_pull.argtypes = [P, P, I, I, I, I, P, P, P, P, P, P, P, P, I, I, P, P]
     lib.tyr_ep_pull.restype = I
-    lib.tyr_ep_combine.argtypes = [P, P, P, P, P, P, P, P, I, I, I, I, I, I, P]
+    lib.tyr_ep_combine.argtypes = [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, P, P]
     lib.tyr_ep_combine.restype = I
     lib._ep_declared = True
 
@@ -110,10 +110,9 @@ class ExpertParallel:
                               ptr(self._seg_rows), ptr(self._seg_src), ptr(self._dest_base[par]), ptr(self._exp_off),
                               ptr(self._exp_tiles), ptr(self._total), ptr(self._rows), ptr(self._row_expert), self.capacity,
                               self.max_pairs, ptr(err_word(x.device)), st), "ep_pull")
-        # the owner evaluates its experts on that upper bound; rows past the device-side total keep the padding id, take no
-        # slot in the expert layout and are never read back
-        total = int(self._total.item()) if R > 4096 else R           # large batches: trim to the real row count
-        R = max(1, min(R, total))
+        # the owner evaluates its experts on that upper bound at every batch size (no host read of the received total): rows
+        # past the device-side total keep the padding id, take no slot in the expert layout, cost no tensor-core tile (the
+        # grouped GEMM walks the device-side tile table) and are never read back
         rows = self._rows[:R]
         row_e = self._row_expert[:R].reshape(R, 1)
         y_local = expert_fn(rows, row_e, torch.ones(R, 1, device=x.device))
@@ -123,7 +122,7 @@ class ExpertParallel:
         check(lib.tyr_ep_combine(self._table(self._y[par]), self._table(self._dest_base[par]), ptr(ids32),
                                  ptr(weights.float().contiguous()), ptr(pos), ptr(self._offsets[par]),
                                  ptr(add.contiguous() if add is not None else None), ptr(out), T, k, h, self.E_local, self.world,
-                                 self.rank, st), "ep_combine")
+                                 self.rank, self.capacity, ptr(err_word(x.device)), st), "ep_combine")
         return out
 
     # -- collective fallback (gloo / unsupported shapes) ----------------------------------------------------
