@@ -10,6 +10,10 @@ Model/config (the reference's d20: Examples/NanoChat/Pipeline.lean:167-244, Modd
 step, bf16 compute, Muon on matrices + AdamW on embeddings/head/scalars, synthetic Zipf(1.1)
 token ids, random-init weights.  One step = forward + backward + optimizer update.
 
+After the training half the same process measures the second half of the metric, Laguna MoE decode tokens/s
+(``laguna_decode`` object of the same line; see :func:`laguna_decode_bench`), and with N > 1 a ``dp_selfcheck``
+value (largest difference between any rank's parameters and rank 0's after the warm-up steps).
+
 Prints ONE JSON line on rank 0.  ``value`` is the whole-job tokens/s over all N GPUs, timed on
 the device with CUDA events around exactly K steps (max over ranks).  ``e2e`` repeats the
 measurement through the public trainer entry (`NanoChatTrainer.train_step_from_host`): every step
@@ -43,6 +47,9 @@ def parse_args():
     ap.add_argument("--seq-len", type=int, default=2048)
     ap.add_argument("--vocab", type=int, default=65536)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-laguna", action="store_true", help="skip the Laguna MoE decode half of the metric")
+    ap.add_argument("--laguna-steps", type=int, default=48)
+    ap.add_argument("--laguna-layers", type=int, default=24)
     return ap.parse_args()
 
 
@@ -110,6 +117,107 @@ def reference_arm(args):
         why = "baseline/_ref holds no runnable NanoChat trainer (Lean executable TrainNanoChat cannot be built offline)"
     print(json.dumps({"impl": "reference", "unavailable": why}))
     return 0
+
+
+def laguna_decode_bench(args, world, rank, device):
+    """Second half of the headline metric: decode tokens/s of the Laguna-style NVFP4 MoE decoder
+    (24 layers, d 2048, 16 q / 4 kv heads x 128, 64 routed experts top-8 + one shared expert, expert FFN 768;
+    reference entry Examples/Laguna/RunHF.lean:90-122).  Every rank prefills 64 sequences x 64 tokens (4096 tokens) and
+    then decodes with batch 64; with N > 1 ranks the experts are split over the ranks (expert parallel) and the rows
+    travel through the fused dispatch / combine kernels over peer memory.  Device-timed exactly like the training half
+    (CUDA events, max over ranks); the end-to-end figure copies each step's tokens from pinned host memory and reads the
+    sampled tokens back every step."""
+    import torch
+    import torch.distributed as dist
+    from tyr_b200.models import laguna as L
+    from tyr_b200.ops import _common as opc
+
+    B, S, K, W = 64, 64, args.laguna_steps, max(3, args.warmup)
+    cfg = L.LagunaConfig(hidden_size=2048, intermediate_size=8192, num_hidden_layers=args.laguna_layers,
+                         num_attention_heads=16, num_attention_heads_sliding=16, num_key_value_heads=4, num_experts=64,
+                         num_experts_per_tok=8, moe_intermediate_size=768, shared_expert_intermediate_size=768)
+    ep = None
+    if world > 1:
+        from tyr_b200.parallel.ep import ExpertParallel
+        ep = ExpertParallel(rank, world, device, cfg.num_experts, cfg.hidden_size, B * S, cfg.num_experts_per_tok,
+                            capacity_factor=min(world, 2))
+    model = L.init(cfg, device=device, dtype=torch.bfloat16, ep=ep)
+    ids = torch.randint(32, cfg.vocab_size, (B, S), device=device, generator=torch.Generator(device=device).manual_seed(rank))
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=device)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    with torch.no_grad():
+        sess = L.CacheSession(model, B, S + 2 * (K + W) + 8)
+        barrier()
+        p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        p0.record()
+        tok = sess.prefill(ids).argmax(-1)
+        p1.record()
+        for _ in range(W):                      # the first step captures the CUDA graph of the decode step
+            tok = sess.step(tok).argmax(-1)
+        barrier()
+        opc.raise_on_device_error(device)
+        launches0 = opc.LAUNCH_COUNT[0]
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(K):
+            flush.zero_()                       # L2 flush between steps: weights and caches come from HBM every step
+            tok = sess.step(tok).argmax(-1)
+        e1.record()
+        barrier()
+        launches = opc.LAUNCH_COUNT[0] - launches0
+        opc.raise_on_device_error(device)
+        # end to end: tokens come from pinned host memory, the sampled tokens go back to the host, every step
+        host_in = tok.cpu().pin_memory()
+        host_out = torch.empty_like(host_in).pin_memory()
+        barrier()
+        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        f0.record()
+        for _ in range(K):
+            flush.zero_()
+            t_dev = host_in.to(device, non_blocking=True)
+            nxt = sess.step(t_dev).argmax(-1)
+            host_out.copy_(nxt, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+            host_in.copy_(host_out)
+        f1.record()
+        barrier()
+    t = torch.tensor([e0.elapsed_time(e1), f0.elapsed_time(f1), p0.elapsed_time(p1)], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    dec_ms, e2e_ms, pre_ms = (float(x) for x in t.tolist())
+    out = {"metric": "laguna_moe_decode_tokens_per_s", "value": B * world * K / (dec_ms / 1e3), "unit": "tokens/s",
+           "ms_per_step": dec_ms / K, "steps": K, "warmup": W, "batch_per_gpu": B,
+           "prefill_tokens": B * S * world, "prefill_ms": pre_ms, "prefill_tokens_per_s": B * S * world / (pre_ms / 1e3),
+           "e2e": {"value": B * world * K / (e2e_ms / 1e3), "unit": "tokens/s",
+                   "h2d_bytes_per_step": int(host_in.numel() * host_in.element_size()),
+                   "d2h_bytes_per_step": int(host_out.numel() * host_out.element_size())},
+           "gpu_launches": launches,
+           "config": {"model": f"laguna-moe {cfg.num_hidden_layers} layers, d 2048, 16q/4kv x 128, 64 experts top-8 + shared, FFN 768, NVFP4",
+                      "parallelism": f"ep{world}" if world > 1 else "1 GPU", "decode_step": "CUDA graph" if sess._graph is not None else "eager",
+                      "l2": "256 MB buffer written between steps"}}
+    if ep is not None:
+        ep.close()
+    return out
+
+
+def dp_selfcheck(trainer, world, device):
+    """max over ranks and parameters of |working copy on this rank - working copy on rank 0| (0.0 = the replicas agree
+    bit for bit after the fused reduce-scatter / update / all-gather); run outside the timed region."""
+    import torch
+    import torch.distributed as dist
+    worst = torch.zeros((), dtype=torch.float32, device=device)
+    for name, w in trainer.params.work.items():
+        ref = w.detach().clone()
+        dist.broadcast(ref, src=0)
+        worst = torch.maximum(worst, (w.detach().float() - ref.float()).abs().max())
+        del ref
+    dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+    return float(worst.item())
 
 
 def zipf_tokens(n_batches, batch, seq_plus_one, vocab, seed):
@@ -222,6 +330,18 @@ def main():
                "h2d_bytes_per_step": int(host_tok[0].numel() * host_tok.element_size()),
                "d2h_bytes_per_step": 4, "final_loss": loss_f}
 
+    selfcheck = dp_selfcheck(trainer, world, device) if (world > 1 and args.impl == "ours") else None
+    laguna = None
+    if not args.no_laguna and args.impl == "ours":
+        del trainer, dp, dev_tok, flush
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+        try:
+            laguna = laguna_decode_bench(args, world, rank, device)
+        except Exception as e:                                   # the training half still reports
+            laguna = {"metric": "laguna_moe_decode_tokens_per_s", "error": f"{type(e).__name__}: {e}"[:300]}
+
     if rank == 0:
         out = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
@@ -235,6 +355,7 @@ def main():
                        "optimizer": "Muon(matrices)+AdamW(embeddings,head,scalars)",
                        "l2": "256 MB buffer written between iterations (L2 flush); per-step working set >> 126 MB"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "final_loss": final_loss,
+            "dp_selfcheck": selfcheck, "laguna_decode": laguna,
         }
         print(json.dumps(out))
     if world > 1:

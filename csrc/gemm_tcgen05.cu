@@ -83,11 +83,12 @@ struct TmapPeers {
   CUtensorMap m[8];
 };
 
-template <int BN, int STAGES>
+// EPI_WARPS epilogue warps with EPI_BUFS staging tiles each (32 rows x 128 bytes, 128B swizzle) for the TMA stores.
+template <int BN, int STAGES, int EPI_WARPS = 4, int EPI_BUFS = 2>
 struct __align__(1024) GemmSmem {
   uint8_t a[STAGES][BM * BK * 2];
   uint8_t b[STAGES][BN * BK * 2];
-  uint8_t out_stage[4][2][32 * 128];   // per epilogue warp: two 32-row x 128-byte tiles (128B swizzle) for TMA stores
+  uint8_t out_stage[EPI_WARPS][EPI_BUFS][32 * 128];
   uint64_t full[STAGES];
   uint64_t empty[STAGES];
   uint64_t acc_full[2];
@@ -106,6 +107,30 @@ __device__ __forceinline__ float apply_act(float v, int act) {
   return v;
 }
 
+// One 32-column chunk of the epilogue with the activation fixed at compile time (no per-element branches):
+//   ACT 0: v = alpha * acc (+ beta * aux)      1: alpha * relu(acc)^2 (+ ...)      2: alpha * relu(acc) (+ ...)
+//   ACT 3: v = alpha * acc * 2 * sqrt(aux)     (gradient of y = relu(z)^2 given aux = y)
+template <int ACT>
+__device__ __forceinline__ void epi_chunk(const uint32_t (&r)[32], const float (&ax)[32], bool use_aux, float alpha,
+                                          float beta, float (&v)[32]) {
+  if constexpr (ACT == 3) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = alpha * __uint_as_float(r[j]) * 2.f * sqrtf(fmaxf(ax[j], 0.f));
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      float a = __uint_as_float(r[j]);
+      if constexpr (ACT == 1) { a = fmaxf(a, 0.f); a = a * a; }
+      if constexpr (ACT == 2) a = fmaxf(a, 0.f);
+      v[j] = alpha * a;
+    }
+    if (use_aux) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = fmaf(beta, ax[j], v[j]);
+    }
+  }
+}
+
 // PAIR = true: the grid is launched as clusters of two CTAs that share one 256 x BN output tile through
 // tcgen05.mma.cta_group::2.  Each CTA loads its own 128 rows of A and its own half (BN / 2 columns) of B with plain TMA
 // loads whose completion is counted on the leader's `full` barrier; the leader (cluster rank 0) issues every MMA and
@@ -113,8 +138,12 @@ __device__ __forceinline__ float apply_act(float v, int act) {
 // and arrives on the leader's `acc_empty`.  A stage costs 32 KB instead of 48 KB and every operand byte in shared
 // memory feeds twice the tensor-core work, which is what the single-CTA form runs short of.  Plain mode only (no
 // grouped rows, no K split, no tensor-parallel fusion, K-major A).
+//
+// The pair form runs 320 threads: warps 2-5 drain the left half of the accumulator columns and warps 6-9 the right half
+// (two epilogue warps per scheduler partition hide each other's latencies; with one, a 128 x 256 tile took about
+// 15 000 cycles to drain, longer than its main loop at K = 1280).
 template <int BN, int STAGES, bool A_MN, bool B_MN, bool PAIR>
-__global__ void __launch_bounds__(256, 1)
+__global__ void __launch_bounds__(PAIR ? 320 : 256, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
                          const __grid_constant__ CUtensorMap tmB,
                          const __grid_constant__ CUtensorMap tmC,
@@ -122,7 +151,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
   extern __shared__ uint8_t smem_raw[];
   constexpr int BNL = PAIR ? BN / 2 : BN;          // columns of B this CTA keeps in shared memory
   constexpr int TILE_M = PAIR ? 2 * BM : BM;       // rows of the tile one scheduler unit covers
-  using Smem = GemmSmem<BNL, STAGES>;
+  constexpr int EPI_WARPS = PAIR ? 8 : 4;
+  constexpr int EPI_BUFS = PAIR ? 1 : 2;
+  constexpr int EPI_CHUNKS = BN / 32 / (EPI_WARPS / 4);   // 32-column chunks each epilogue warp drains per tile
+  using Smem = GemmSmem<BNL, STAGES, EPI_WARPS, EPI_BUFS>;
   Smem& s = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                      ~static_cast<uintptr_t>(1023));
   const int warp = threadIdx.x >> 5;
@@ -158,7 +190,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s.acc_full[i], 1);
-      mbar_init(&s.acc_empty[i], PAIR ? 8 : 4);  // one arrival per epilogue warp (of both CTAs of a pair)
+      mbar_init(&s.acc_empty[i], PAIR ? 2 * EPI_WARPS : EPI_WARPS);  // one arrival per epilogue warp (of both CTAs of a pair)
     }
     s.abort_flag = 0;
     mbar_fence_init();
@@ -425,7 +457,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       }
       if (!ok) s.abort_flag = 1;
     }
-  } else if (warp >= 6) {
+  } else if (!PAIR && warp >= 6) {
     // ------------------------------------------------------------------ gather warps (tp_mode 2)
     if (p.tp_mode == 2) {
       const long long nvec = static_cast<long long>(BM) * p.K / 8;       // 16-byte vectors per row tile (lda == K)
@@ -456,6 +488,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
   } else {
     // ------------------------------------------------------------------ epilogue warps
     const int quarter = warp & 3;  // TMEM lane quarter this warp may access
+    const int epi = warp - 2;      // staging slot
+    const int c_begin = (epi >> 2) * EPI_CHUNKS;
     long long cursor = cursor0, tile;
     int kb0, kb1;
     uint32_t seg = 0;
@@ -543,12 +577,12 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
         continue;
       }
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = c_begin; c < c_begin + EPI_CHUNKS; ++c) {
         uint32_t r[32];
         tmem_ld_32x32(t_row + c * 32, r);
         tmem_wait_ld();
-        if (c == BN / 32 - 1) {
-          // accumulator fully read: hand the TMEM buffer back to the MMA warp
+        if (c == c_begin + EPI_CHUNKS - 1) {
+          // this warp's part of the accumulator is read: hand the TMEM buffer back to the MMA warp
           tc_fence_before();
           __syncwarp();
           if (lane == 0) {
@@ -560,7 +594,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
         if (tma_out) {
           if (col >= p.N) continue;            // a tile that ends inside the last valid chunk was flushed there
           if (!(c & 1)) {                      // about to refill a staging tile: its previous store must have read it
-            if (lane == 0) tma_store_wait_read<1>();
+            if (lane == 0) tma_store_wait_read<EPI_BUFS - 1>();
             __syncwarp();
           }
         } else if (!row_ok || col >= p.N) {
@@ -585,22 +619,16 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
 #pragma unroll
             for (int j = 0; j < 32; ++j) ax[j] = (col + j < p.N) ? __bfloat162float(axp[j]) : 0.f;
           }
-        }
-        if (p.act == 3) {
-          // gradient of y = relu(z)^2 given aux = y:  dz = acc * 2*sqrt(y)
-#pragma unroll
-          for (int j = 0; j < 32; ++j)
-            v[j] = p.alpha * __uint_as_float(r[j]) * 2.f * sqrtf(fmaxf(ax[j], 0.f));
         } else {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = p.alpha * apply_act(__uint_as_float(r[j]), p.act);
-          if (use_aux) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] += p.beta * ax[j];
-          }
+          for (int j = 0; j < 32; ++j) ax[j] = 0.f;
         }
+        if (p.act == 0) epi_chunk<0>(r, ax, use_aux, p.alpha, p.beta, v);
+        else if (p.act == 1) epi_chunk<1>(r, ax, use_aux, p.alpha, p.beta, v);
+        else if (p.act == 2) epi_chunk<2>(r, ax, use_aux, p.alpha, p.beta, v);
+        else epi_chunk<3>(r, ax, use_aux, p.alpha, p.beta, v);
         if (tma_out) {
-          uint8_t* st = s.out_stage[quarter][n_stores & 1] + lane * 128;
+          uint8_t* st = s.out_stage[epi][n_stores % EPI_BUFS] + lane * 128;
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
             uint4 u;
@@ -622,7 +650,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
                 tm = &tmP.m[owner];
                 y = p.tp_rank * p.rows_per_rank + (y - owner * p.rows_per_rank);
               }
-              tma_store_3d(tm, s.out_stage[quarter][n_stores & 1], col - (c & 1) * 32, y, bi);
+              tma_store_3d(tm, s.out_stage[epi][n_stores % EPI_BUFS], col - (c & 1) * 32, y, bi);
               tma_store_commit();
             }
             ++n_stores;
@@ -784,7 +812,8 @@ static int launch_gemm(const TyrGemmArgs& a, const CUtensorMap& tmA, const CUten
                        const tyr::TmapPeers& tmP, const tyr::GemmParams& tp) {
   using namespace tyr;
   auto kern = gemm_bf16_tcgen05_kernel<BN, STAGES, A_MN, B_MN, PAIR>;
-  constexpr size_t smem = sizeof(GemmSmem<PAIR ? BN / 2 : BN, STAGES>) + 1024;
+  constexpr size_t smem = sizeof(GemmSmem<PAIR ? BN / 2 : BN, STAGES, PAIR ? 8 : 4, PAIR ? 1 : 2>) + 1024;
+  constexpr unsigned kThreads = PAIR ? 320 : 256;
   static bool configured[kMaxGemmDevices] = {false};
   const int dev = current_device();
   const int g_sm_count = device_sm_count();
@@ -797,7 +826,7 @@ static int launch_gemm(const TyrGemmArgs& a, const CUtensorMap& tmA, const CUten
       // how many CTA pairs the device can keep resident at once (one CTA per SM, pairs within a TPC)
       cudaLaunchConfig_t qc = {};
       qc.gridDim = dim3(static_cast<unsigned>(g_sm_count & ~1));
-      qc.blockDim = dim3(256);
+      qc.blockDim = dim3(kThreads);
       qc.dynamicSmemBytes = smem;
       cudaLaunchAttribute qa[1];
       qa[0].id = cudaLaunchAttributeClusterDimension;
@@ -857,7 +886,7 @@ static int launch_gemm(const TyrGemmArgs& a, const CUtensorMap& tmA, const CUten
     if (tiles < pairs) pairs = static_cast<int>(tiles);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));
-    cfg.blockDim = dim3(256);
+    cfg.blockDim = dim3(kThreads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = reinterpret_cast<cudaStream_t>(a.stream);
     cudaLaunchAttribute at[1];

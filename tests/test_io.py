@@ -111,6 +111,83 @@ def test_checkpoint_snapshot_protocol(tmp_path):
         ck.resolve_snapshot(root)
 
 
+def test_checkpoint_on_disk_forms_match_the_reference(tmp_path):
+    """Pointer = bare snapshot name, meta.txt = version-2 JSON with loss bits, flat directories, legacy key=value
+    metadata, a second pointer for optimizer state, and removal of a snapshot whose save failed
+    (Tyr/Checkpoint.lean:42-157)."""
+    import json
+    import struct as _struct
+    root = str(tmp_path / "ckpt")
+    os.makedirs(root)
+    tree = Tiny(torch.randn(2, 3), Frozen(torch.arange(4)), Static(None))
+    snap = ck.save_training_checkpoint(root, tree, None, None, ck.CheckpointMeta.with_loss(12, 0.75, best_val_loss=0.5, optim_count=12))
+    name = open(os.path.join(root, "CURRENT")).read()
+    assert name == os.path.basename(snap) and name.startswith("snapshot-") and "/" not in name and "." not in name
+    j = json.load(open(os.path.join(snap, "meta.txt")))
+    assert j == {"version": 2, "iteration": 12, "optimCount": 12,
+                 "trainLossBits": _struct.unpack("<Q", _struct.pack("<d", 0.75))[0],
+                 "bestValLossBits": _struct.unpack("<Q", _struct.pack("<d", 0.5))[0]}
+    m = ck.load_meta(snap)
+    assert (m.step, m.loss, m.best_val_loss, m.optim_count) == (12, 0.75, 0.5, 12)
+    assert ck.has_checkpoint(root)
+    # a pointer in the form earlier versions of this module wrote still resolves
+    with open(os.path.join(root, "CURRENT"), "w") as f:
+        f.write(".snapshots/" + name + "\n")
+    assert ck.resolve_snapshot(root) == snap
+    # flat legacy directory: no pointer -> the directory itself; key=value metadata
+    flat = str(tmp_path / "flat")
+    os.makedirs(flat)
+    assert ck.resolve_snapshot(flat) == flat
+    with open(os.path.join(flat, "meta.txt"), "w") as f:
+        f.write("iteration=40\nbestValLoss=1.5\ntrainLoss=2.25\n")
+    m = ck.load_meta(flat)
+    assert (m.step, m.best_val_loss, m.loss, m.optim_count) == (40, 1.5, 2.25, 0)
+    with open(os.path.join(flat, "meta.txt"), "w") as f:
+        f.write("iteration=40\niteration=41\nbestValLoss=1\ntrainLoss=2\n")
+    with pytest.raises(ck.CheckpointError, match="Duplicate"):
+        ck.load_meta(flat)
+    # a separate pointer for optimizer state
+    osnap = ck.write_snapshot(root, lambda d: ck.save_tree(d, "mu", tree), pointer="OPTIMIZER_CURRENT")
+    assert ck.resolve_snapshot(root, "OPTIMIZER_CURRENT") == osnap and ck.resolve_snapshot(root) == snap
+    # a failed save leaves no partial snapshot behind and does not move the pointer
+    before = set(os.listdir(os.path.join(root, ".snapshots")))
+
+    def boom(d):
+        ck.save_tree(d, "param", tree)
+        raise RuntimeError("disk full")
+    with pytest.raises(RuntimeError, match="disk full"):
+        ck.write_snapshot(root, boom)
+    assert set(os.listdir(os.path.join(root, ".snapshots"))) == before
+    assert ck.resolve_snapshot(root) == snap
+    for bad in ("snapshot-1.2", "snapshot-1/x", "other-1"):
+        with open(os.path.join(root, "CURRENT"), "w") as f:
+            f.write(bad)
+        with pytest.raises(ck.CheckpointError):
+            ck.resolve_snapshot(root)
+
+
+def test_checkpoint_reads_tensor_files_written_by_libtorch_vector_save():
+    """tests/fixtures/reference_pt/param_{0,1,2}.pt were written by a C++ program with the call the reference makes for
+    every leaf, ``torch::save(std::vector<torch::Tensor>{t}, path)`` (cc/src/tyr.cpp:2149-2151): arange(6).reshape(2, 3)
+    fp32, 0.5 * arange(4) fp32, 1.5 * ones(3, 2) bf16."""
+    d = os.path.join(os.path.dirname(__file__), "fixtures", "reference_pt")
+
+    @tensor_struct
+    class Three:
+        a: torch.Tensor
+        b: torch.Tensor
+        c: torch.Tensor
+    tmpl = Three(torch.zeros(2, 3), torch.zeros(4), torch.zeros(3, 2, dtype=torch.bfloat16))
+    got = ck.load_reference_pt_layout(d, "param", tmpl)
+    assert torch.equal(got.a, torch.arange(6.).reshape(2, 3))
+    assert torch.equal(got.b, torch.arange(4.) * 0.5)
+    assert got.c.dtype == torch.bfloat16 and torch.equal(got.c.float(), torch.full((3, 2), 1.5))
+    with pytest.raises(ck.CheckpointError, match="shape"):
+        ck.load_reference_pt_layout(d, "param", Three(torch.zeros(3, 2), torch.zeros(4), torch.zeros(3, 2, dtype=torch.bfloat16)))
+    with pytest.raises(ck.CheckpointError, match="dtype"):
+        ck.load_reference_pt_layout(d, "param", Three(torch.zeros(2, 3), torch.zeros(4), torch.zeros(3, 2)))
+
+
 def test_media_writers_and_float_buffer(tmp_path):
     img = torch.rand(3, 4, 5)
     p = str(tmp_path / "x.ppm")

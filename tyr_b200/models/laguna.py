@@ -506,8 +506,8 @@ class CacheSession:
         cfg, m = self.m.cfg, self.m
         if not m.embed_tokens.is_cuda or m.dtype != torch.bfloat16 or os.environ.get("TYR_DECODE_GRAPH", "1") == "0":
             return False
-        if m.ep is not None and not (m.ep.fused and self.batch * cfg.num_experts_per_tok * m.ep.world <= 4096):
-            return False          # the collective fallback and the row-count read-back of large batches need the host
+        if m.ep is not None and not m.ep.fused:
+            return False          # the collective fallback runs host-side collectives
         return all(da.geometry_supported(cfg.heads(i), cfg.num_key_value_heads, cfg.head_dim) for i in range(cfg.num_hidden_layers))
 
     def _device_step(self, tokens: torch.Tensor, use_fused: bool = True) -> torch.Tensor:

@@ -50,6 +50,8 @@ def save(root: str, trainer: NanoChatTrainer, data: Optional[DistributedDataGene
             meta["extra"] = extra
         with open(os.path.join(snap, META_FILE), "w") as f:
             json.dump(meta, f, indent=2)
+        # the reference's metadata file (iteration / loss bits / optimizer step count) beside the run description above
+        ckpt.save_meta(snap, ckpt.CheckpointMeta.with_loss(trainer.step_index, float(loss), optim_count=trainer.step_index))
     sd = {k: v.detach().cpu().contiguous() for k, v in trainer.optimizer_state_dict().items()}
     st.save_file(sd, os.path.join(snap, _opt_file(rank)))
     if data is not None:

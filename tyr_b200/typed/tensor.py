@@ -108,6 +108,16 @@ class Tensor:
     def __repr__(self):
         return f"Tensor(shape={list(self.shape)}, dtype={self.dtype}, device={self.device.kind!r})"
 
+    def _repr_html_(self):
+        """Notebook display: dtype / shape / device / statistics and a heat map for small tensors."""
+        from ..utils import widget
+        return widget.render_html(widget.to_module_node(self, "tensor"))
+
+    def describe(self) -> str:
+        """One line with dtype, shape, device and value statistics."""
+        from ..utils import widget
+        return widget.render_text(widget.to_module_node(self, "tensor"))
+
     # -- operator sugar (delegates to the typed ops so every result is spec-checked) -----------------
     def __add__(self, o):
         from . import ops
