@@ -121,8 +121,8 @@ flash_bwd_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     }
     mbar_init(&s.s_ready, 1);
     mbar_init(&s.dp_ready, 1);
-    mbar_init(&s.p_ready, 512);
-    mbar_init(&s.ds_ready, 512);
+    mbar_init(&s.p_ready, 16);      // one arrival per score warp (512 single-thread arrivals on one barrier serialise)
+    mbar_init(&s.ds_ready, 16);
     mbar_init(&s.ds_free, 1);
     mbar_init(&s.acc_done, 1);
     mbar_fence_init();
@@ -309,7 +309,8 @@ flash_bwd_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       }
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(&s.p_ready);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s.p_ready);
       if (!mbar_wait(&s.do_full[st], ph, p.err, 852)) { ok = false; break; }
       if (!mbar_wait(&s.dp_ready, it & 1, p.err, 853)) { ok = false; break; }
       if (it > 0 && !mbar_wait(&s.ds_free, (it - 1) & 1, p.err, 854)) { ok = false; break; }   // dK of the previous block has read dS
@@ -334,7 +335,8 @@ flash_bwd_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       }
       fence_proxy_async();
       tc_fence_before();
-      mbar_arrive(&s.ds_ready);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s.ds_ready);
     }
     // ---------------------------------------------------------------- dK / dV epilogue
     if (ok && n_it > 0) ok = mbar_wait(&s.acc_done, 0, p.err, 860);
@@ -423,7 +425,7 @@ struct __align__(1024) DqSmem {
   uint8_t ds[BW_TILE];
   uint64_t qdo_full;
   uint64_t k_full[2], v_full[2], kv_empty[2];
-  uint64_t s_ready, dp_ready, ds_ready, ds_free, acc_done;
+  uint64_t s_ready[2], s_free[2], dp_ready, ds_ready, ds_free, acc_done;
   uint32_t tmem_base;
 };
 static_assert(sizeof(DqSmem) <= 227 * 1024, "dQ tiles exceed the shared memory of one CTA");
@@ -465,9 +467,12 @@ flash_bwd_dq_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
       mbar_init(&s.v_full[q], 1);
       mbar_init(&s.kv_empty[q], 1);
     }
-    mbar_init(&s.s_ready, 1);
+    mbar_init(&s.s_ready[0], 1);
+    mbar_init(&s.s_ready[1], 1);
+    mbar_init(&s.s_free[0], 16);
+    mbar_init(&s.s_free[1], 16);
     mbar_init(&s.dp_ready, 1);
-    mbar_init(&s.ds_ready, 512);
+    mbar_init(&s.ds_ready, 16);
     mbar_init(&s.ds_free, 1);
     mbar_init(&s.acc_done, 1);
     mbar_fence_init();
@@ -480,7 +485,9 @@ flash_bwd_dq_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = s.tmem_base;
-  constexpr uint32_t COL_S = 0, COL_DP = 128, COL_DQ = 256;
+  // S is double buffered (columns 0..127 and 384..511): S_{j+1} is computed while the score warps still work on block j,
+  // so they go from dS_j straight to the exponentials of block j+1.
+  constexpr uint32_t COL_S0 = 0, COL_DP = 128, COL_DQ = 256, COL_S1 = 384;
 
   if (warp == 17) {
     // ------------------------------------------------------------------ TMA producer
@@ -533,14 +540,23 @@ flash_bwd_dq_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
       ok = ok && mbar_wait(&s.k_full[0], 0, p.err, 921);
       if (ok) {
         tc_fence_after();
-        mma_kk(COL_S, qa, smem_u32(s.k[0]));
-        umma_commit(&s.s_ready);
+        mma_kk(COL_S0, qa, smem_u32(s.k[0]));
+        umma_commit(&s.s_ready[0]);
         ok = mbar_wait(&s.v_full[0], 0, p.err, 922);
       }
       if (ok) {
         tc_fence_after();
         mma_kk(COL_DP, doa, smem_u32(s.v[0]));
         umma_commit(&s.dp_ready);
+      }
+      // S of the second block right away: its TMEM buffer is free and K_1 sits in the other ring stage
+      if (ok && n_it > 1) {
+        ok = mbar_wait(&s.k_full[1], 0, p.err, 923);
+        if (ok) {
+          tc_fence_after();
+          mma_kk(COL_S1, qa, smem_u32(s.k[1]));
+          umma_commit(&s.s_ready[1]);
+        }
       }
       for (int it = 0; it < n_it && ok; ++it) {
         const int st = it & 1;
@@ -550,10 +566,6 @@ flash_bwd_dq_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
         if (it + 1 < n_it) {
           const int sn = (it + 1) & 1;
           const uint32_t phn = ((it + 1) >> 1) & 1;
-          if (!mbar_wait(&s.k_full[sn], phn, p.err, 931)) { ok = false; break; }
-          tc_fence_after();
-          mma_kk(COL_S, qa, smem_u32(s.k[sn]));
-          umma_commit(&s.s_ready);
           if (!mbar_wait(&s.v_full[sn], phn, p.err, 932)) { ok = false; break; }
           tc_fence_after();
           mma_kk(COL_DP, doa, smem_u32(s.v[sn]));
@@ -567,6 +579,16 @@ flash_bwd_dq_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
                       make_smem_desc_sw128(ka + k * 2048, BW_CHUNK, 1024), idesc_kn, (it == 0 && k == 0) ? 0u : 1u);
         umma_commit(&s.ds_free);
         umma_commit(&s.kv_empty[st]);
+        // S of block it + 2 into the buffer block it used: the score warps released it after their exponentials, and its
+        // K tile lands in the ring stage that the commit above frees
+        if (it + 2 < n_it) {
+          const uint32_t ph2 = ((it + 2) >> 1) & 1;
+          if (!mbar_wait(&s.s_free[st], (it >> 1) & 1, p.err, 933)) { ok = false; break; }
+          if (!mbar_wait(&s.k_full[st], ph2, p.err, 931)) { ok = false; break; }
+          tc_fence_after();
+          mma_kk(st ? COL_S1 : COL_S0, qa, smem_u32(s.k[st]));
+          umma_commit(&s.s_ready[st]);
+        }
       }
       if (ok) umma_commit(&s.acc_done);
     }
@@ -576,7 +598,8 @@ flash_bwd_dq_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
     const int r = (warp & 3) * 32 + lane;                 // query row of this thread inside the block
     const int row = i * BW_T + r;
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const uint32_t s_addr = tmem_base + COL_S + wg * 32 + lane_addr;
+    const uint32_t s_addr0 = tmem_base + COL_S0 + wg * 32 + lane_addr;
+    const uint32_t s_addr1 = tmem_base + COL_S1 + wg * 32 + lane_addr;
     const uint32_t dp_addr = tmem_base + COL_DP + wg * 32 + lane_addr;
     const long long stat = (static_cast<long long>(batch) * p.Hq + head) * p.Tpad + row;
     const float lse2 = p.lse2[stat];                      // +inf on padded / empty rows: their probabilities are 0
@@ -588,13 +611,17 @@ flash_bwd_dq_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
     for (int it = 0; it < n_it && ok; ++it) {
       const int j = jlo + it;
       const int key0 = j * BW_T + wg * 32;
-      if (!mbar_wait(&s.s_ready, it & 1, p.err, 950)) { ok = false; break; }
+      if (!mbar_wait(&s.s_ready[it & 1], (it >> 1) & 1, p.err, 950)) { ok = false; break; }
       tc_fence_after();
       float pr[32];
       {
         uint32_t t[32];
-        tmem_ld_32x32(s_addr, t);
+        tmem_ld_32x32((it & 1) ? s_addr1 : s_addr0, t);
         tmem_wait_ld();
+        // the scores are in registers: the buffer may take S of block it + 2
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&s.s_free[it & 1]);
         const bool full = (j * BW_T + BW_T <= p.Tk) && (!p.causal || j * BW_T + BW_T - 1 <= i * BW_T + p.q_offset) &&
                           (p.window <= 0 || j * BW_T > i * BW_T + BW_T - 1 + p.q_offset - p.window);
         if (full) {
@@ -632,7 +659,8 @@ flash_bwd_dq_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
       }
       fence_proxy_async();
       tc_fence_before();
-      mbar_arrive(&s.ds_ready);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s.ds_ready);
     }
     // ---------------------------------------------------------------- dQ epilogue: each warpgroup writes 32 channels
     if (ok && n_it > 0) ok = mbar_wait(&s.acc_done, 0, p.err, 960);

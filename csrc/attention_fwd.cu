@@ -53,7 +53,7 @@ struct __align__(1024) AttnSmem {
   uint64_t v_full[ATT_STAGES];
   uint64_t kv_empty[ATT_STAGES];
   uint64_t s_ready[2];     // MMA -> softmax: S_t written
-  uint64_t p_ready[2];     // softmax -> MMA: P_t written (128 arrivals)
+  uint64_t p_ready[2];     // softmax -> MMA: P_t written (one arrival per softmax warp)
   uint64_t o_done[2];      // MMA -> softmax: all PV of tile t retired
   uint32_t tmem_base;
 };
@@ -130,7 +130,7 @@ flash_fwd_d128_kernel(const __grid_constant__ CUtensorMap tmQ,
     }
     for (int t = 0; t < 2; ++t) {
       mbar_init(&s.s_ready[t], 1);
-      mbar_init(&s.p_ready[t], ATT_BM);
+      mbar_init(&s.p_ready[t], ATT_BM / 32);   // one arrival per softmax warp
       mbar_init(&s.o_done[t], 1);
     }
     mbar_fence_init();
@@ -340,7 +340,8 @@ flash_fwd_d128_kernel(const __grid_constant__ CUtensorMap tmQ,
         l_sum += ls;
         tmem_wait_st();
         tc_fence_before();
-        mbar_arrive(&s.p_ready[t]);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&s.p_ready[t]);   // one arrival per warp: 128 arrivals on one barrier serialise
       }
       // ---------------------------------------------------------------- epilogue
       if (ok && hi[t] > lo[t]) ok = mbar_wait(&s.o_done[t], 0, p.err, 710 + t);

@@ -115,12 +115,12 @@ def flash_attention(q, k, v, *, causal=True, window=None, scale=None):
     return o.transpose(1, 2)
 
 
-_TRAIN = os.environ.get("TYR_FLASH_TRAIN", "0") == "1"
+_TRAIN = os.environ.get("TYR_FLASH_TRAIN", "1") != "0"
 
 
 def supported_packed(H, D, T, causal, window) -> bool:
-    """Training path (forward + backward through these kernels).  Opt-in (TYR_FLASH_TRAIN=1): at head dim 128 the library's
-    fused attention is currently the faster pair, so the default training step keeps it."""
+    """Training path (forward + backward through these kernels, reading q / k / v from the packed projection and writing
+    the three gradients into one packed buffer).  ``TYR_FLASH_TRAIN=0`` falls back to the library's fused attention."""
     return _TRAIN and has_fwd() and has_bwd() and D == 128
 
 

@@ -23,9 +23,13 @@ class GraphedStep:
                 fn(*self.static_in)
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
+        from ..ops import _common as opc
         self.graph = torch.cuda.CUDAGraph()
+        before = opc.LAUNCH_COUNT[0]
         with torch.no_grad(), torch.cuda.graph(self.graph):
             self.static_out = fn(*self.static_in)
+        # launches of this library's kernels recorded into the graph: every replay runs them again
+        self.kernel_launches_per_replay = opc.LAUNCH_COUNT[0] - before
         for t, s in zip(advancing_state, saved):
             t.copy_(s)
         self.replays = 0
@@ -35,4 +39,6 @@ class GraphedStep:
             dst.copy_(src)
         self.graph.replay()
         self.replays += 1
+        from ..ops import _common as opc
+        opc.LAUNCH_COUNT[0] += self.kernel_launches_per_replay
         return self.static_out
