@@ -1,0 +1,180 @@
+#!/usr/bin/env python
+"""One entry point for the checks a change has to pass (the role of the reference's CPU workflow and its test-inventory /
+qualification scripts: .github/workflows/cpu.yml:72-164, scripts/test_inventory.py, scripts/qualification/run.py:45).
+
+    python ci/run.py                 # build, source gates, test inventory, export check, CPU suite -> build/ci/report.json
+    python ci/run.py --gpu           # additionally the GPU suite (`-m gpu`), on a machine with a B200
+    python ci/run.py --only gates    # a single stage: build | gates | inventory | exports | cpu | gpu | distributed
+
+Stages
+  build        every CUDA source compiled for sm_100a and the host libraries, in-tree
+  gates        static source gates: no forbidden CUDA calls or load forms in sources that travel to a multi-GPU run, nothing
+               committed reads a scratch directory, every kernel launcher that waits has a bounded wait
+  inventory    every tests/test_*.py is collected by pytest and holds at least one test; every file under tests/workers/ is
+               launched by some test; every GPU test carries the `gpu` marker; the file that must run last is collected last
+  exports      ctypes declarations agree with the symbols the built libraries export
+  cpu          pytest -m "not gpu"
+  distributed  the two-rank gloo value checks alone (also part of cpu), with their logs kept
+  gpu          pytest -m gpu
+
+The report lists every stage with its status, duration and the tail of its output; the exit code is non-zero when a stage
+failed.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import re
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parents[1]
+OUT = ROOT / "build" / "ci"
+
+# CUDA entry points that are closed on the B200 pool, and the load form that must never reach another GPU's memory.
+FORBIDDEN = [
+    ("batched memcpy", re.compile(r"cu(?:da)?Memcpy(?:3D)?Batch" + r"Async")),
+    ("cluster-multicast bulk load", re.compile(r"cp\.async\.bulk[\w.:]*\.multicast" + r"::cluster")),
+    ("GPU clock / power setting", re.compile(r"nvidia-smi\s+(?:-lgc|-ac|-pl|-pm|--lock-gpu-clocks|-rgc|--gpu-reset)")),
+    ("device-side trap", re.compile(r"\b__trap\s*\(")),
+]
+SOURCE_SUFFIXES = {".py", ".cu", ".cuh", ".h", ".cpp", ".sh", ".yml", ".toml"}
+SKIP_DIRS = {".git", "_work", "gpurun_out", "build", "__pycache__", ".pytest_cache", "baseline"}
+
+
+def run(cmd, timeout, env=None):
+    t0 = time.time()
+    try:
+        r = subprocess.run(cmd, cwd=ROOT, capture_output=True, text=True, timeout=timeout, env=env)
+        rc, out = r.returncode, (r.stdout + r.stderr)
+    except subprocess.TimeoutExpired as e:
+        rc, out = 124, ((e.stdout or b"").decode(errors="replace") if isinstance(e.stdout, bytes) else (e.stdout or "")) + "\nTIMEOUT"
+    return {"rc": rc, "seconds": round(time.time() - t0, 1), "tail": out[-4000:]}
+
+
+def source_files():
+    for p in ROOT.rglob("*"):
+        if p.is_file() and p.suffix in SOURCE_SUFFIXES and not (set(p.relative_to(ROOT).parts[:-1]) & SKIP_DIRS):
+            yield p
+
+
+def stage_build():
+    return run([sys.executable, "-c", "import __graft_entry__ as g; g.build(); print('build ok')"], 1800)
+
+
+def stage_gates():
+    problems = []
+    for p in source_files():
+        rel = p.relative_to(ROOT).as_posix()
+        if rel == "ci/run.py":
+            continue
+        text = p.read_text(errors="replace")
+        for what, rx in FORBIDDEN:
+            m = rx.search(text)
+            if m:
+                problems.append(f"{rel}:{text.count(chr(10), 0, m.start()) + 1}: {what}")
+        if p.suffix == ".py" and re.search(r"""(?:open|import_module|run)\([^)]*['"]_work/""", text):
+            problems.append(f"{rel}: reads a scratch directory")
+    # every spin on a flag in the kernels goes through the bounded helpers
+    for p in (ROOT / "csrc").glob("*.cu"):
+        text = p.read_text()
+        for m in re.finditer(r"while\s*\(\s*(?:true|1)\s*\)", text):
+            body = text[m.end():m.end() + 1200]
+            if "kWaitBudgetCycles" not in body and "budget" not in body and "break" not in body:
+                problems.append(f"{p.relative_to(ROOT).as_posix()}:{text.count(chr(10), 0, m.start()) + 1}: unbounded loop")
+    return {"rc": 1 if problems else 0, "seconds": 0.0, "tail": "\n".join(problems) or "source gates clean"}
+
+
+def stage_inventory():
+    t0 = time.time()
+    listing = subprocess.run([sys.executable, "-m", "pytest", "tests", "--collect-only", "-q"], cwd=ROOT,
+                             capture_output=True, text=True, timeout=900)
+    r = {"rc": listing.returncode, "seconds": round(time.time() - t0, 1), "tail": (listing.stdout + listing.stderr)[-4000:]}
+    problems = []
+    if r["rc"] != 0:
+        return r
+    collected = {}
+    order = []
+    for line in listing.stdout.splitlines():
+        if "::" in line:
+            f = line.split("::")[0]
+            collected[f] = collected.get(f, 0) + 1
+            if not order or order[-1] != f:
+                order.append(f)
+    files = sorted(p.relative_to(ROOT).as_posix() for p in (ROOT / "tests").glob("test_*.py"))
+    for f in files:
+        if collected.get(f, 0) == 0:
+            problems.append(f"{f}: collected no test (unreachable test file)")
+    if order and order[-1] != "tests/test_zz_no_alloc.py" and (ROOT / "tests/test_zz_no_alloc.py").exists():
+        problems.append(f"tests/test_zz_no_alloc.py must be collected last, last is {order[-1]}")
+    tests_text = "\n".join(p.read_text() for p in (ROOT / "tests").glob("test_*.py"))
+    for w in sorted((ROOT / "tests" / "workers").glob("*.py")):
+        if w.name != "__init__.py" and w.stem not in tests_text:
+            problems.append(f"tests/workers/{w.name}: no test launches this worker")
+    # a test that touches a CUDA device must carry the gpu marker (module-level pytestmark or decorator)
+    for p in (ROOT / "tests").glob("test_*.py"):
+        text = p.read_text()
+        module_mark = re.search(r"^pytestmark\s*=.*gpu", text, re.MULTILINE) is not None
+        for m in re.finditer(r"^((?:@[^\n]+\n)*)def (test_\w+)\(", text, re.MULTILINE):
+            start = m.end()
+            nxt = re.search(r"^(?:@|def |class )", text[start:], re.MULTILINE)
+            body = text[start:start + (nxt.start() if nxt else len(text))]
+            if re.search(r"""['"]cuda|\.cuda\(\)|_dev\(\)|Device\.cuda""", body) and not module_mark and "mark.gpu" not in m.group(1) \
+                    and "skipif" not in m.group(1) and "is_available" not in body:
+                problems.append(f"{p.relative_to(ROOT).as_posix()}::{m.group(2)} uses CUDA without the gpu marker")
+    tail = "\n".join(problems) or f"{len(files)} test files, {sum(collected.values())} tests, all reachable"
+    return {"rc": 1 if problems else 0, "seconds": r["seconds"], "tail": tail}
+
+
+def stage_exports():
+    return run([sys.executable, "-m", "pytest", "tests/test_native_exports.py", "-q"], 900)
+
+
+def stage_cpu():
+    return run([sys.executable, "-m", "pytest", "tests", "-x", "-q", "-m", "not gpu"], 3600)
+
+
+def stage_distributed():
+    OUT.mkdir(parents=True, exist_ok=True)
+    env = dict(os.environ, TYR_DIST_LOG_DIR=str(OUT / "distributed"))
+    return run([sys.executable, "-m", "pytest", "tests/test_distributed.py", "-q", "-m", "not gpu"], 1800, env)
+
+
+def stage_gpu():
+    return run([sys.executable, "-m", "pytest", "tests", "-x", "-q", "-m", "gpu"], 5400)
+
+
+STAGES = {"build": stage_build, "gates": stage_gates, "inventory": stage_inventory, "exports": stage_exports,
+          "cpu": stage_cpu, "distributed": stage_distributed, "gpu": stage_gpu}
+DEFAULT = ["build", "gates", "inventory", "exports", "cpu"]
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpu", action="store_true")
+    ap.add_argument("--only", action="append", choices=sorted(STAGES))
+    ap.add_argument("--report", default=str(OUT / "report.json"))
+    a = ap.parse_args(argv)
+    names = a.only or (DEFAULT + (["gpu"] if a.gpu else []))
+    report = {"started": time.strftime("%Y-%m-%dT%H:%M:%SZ", time.gmtime()), "stages": {}}
+    failed = []
+    for n in names:
+        print(f"[ci] {n} ...", flush=True)
+        res = STAGES[n]()
+        report["stages"][n] = res
+        print(f"[ci] {n}: {'ok' if res['rc'] == 0 else 'FAILED rc=' + str(res['rc'])} in {res['seconds']} s", flush=True)
+        if res["rc"] != 0:
+            failed.append(n)
+            print(res["tail"][-1500:], flush=True)
+    report["failed"] = failed
+    Path(a.report).parent.mkdir(parents=True, exist_ok=True)
+    Path(a.report).write_text(json.dumps(report, indent=2))
+    print(f"[ci] report: {a.report}; {'all stages passed' if not failed else 'failed: ' + ', '.join(failed)}")
+    return 1 if failed else 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

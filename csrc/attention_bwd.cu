@@ -381,32 +381,37 @@ flash_bwd_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   }
 }
 
-// One warp per (batch, head, padded row): delta = sum_d dO*O and lse in base 2 (+inf where the row is
-// padding or saw no key).
-__global__ void flash_bwd_prepare_kernel(const __nv_bfloat16* __restrict__ dO, const __nv_bfloat16* __restrict__ O,
-                                         const float* __restrict__ lse, float* __restrict__ lse2,
-                                         float* __restrict__ delta, int B, int H, int Tq,
-                                         int Tpad, long long do_sb, long long do_st, long long do_sh, long long o_sb,
-                                         long long o_st, long long o_sh) {
-  const long long w = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
-  const long long total = static_cast<long long>(B) * H * Tpad;
-  if (w >= total) return;
-  const int row = static_cast<int>(w % Tpad);
-  const int h = static_cast<int>((w / Tpad) % H);
-  const int b = static_cast<int>(w / (static_cast<long long>(Tpad) * H));
-  float acc = 0.f, l2 = INFINITY;
-  if (row < Tq) {
-    const uint2 a = *reinterpret_cast<const uint2*>(dO + b * do_sb + static_cast<long long>(row) * do_st + h * do_sh + lane * 4);
-    const uint2 c = *reinterpret_cast<const uint2*>(O + b * o_sb + static_cast<long long>(row) * o_st + h * o_sh + lane * 4);
-    const float2 a0 = unpack_bf16x2(a.x), a1 = unpack_bf16x2(a.y), c0 = unpack_bf16x2(c.x), c1 = unpack_bf16x2(c.y);
-    acc = warp_sum(a0.x * c0.x + a0.y * c0.y + a1.x * c1.x + a1.y * c1.y);
-    const float l = lse[(static_cast<long long>(b) * H + h) * Tq + row];
-    l2 = (l == -INFINITY) ? INFINITY : l * 1.4426950408889634f;
-  }
-  if (lane == 0) {
-    delta[w] = acc;
-    lse2[w] = l2;
+// Sixteen threads per (batch, head, padded row), 16 bytes each: delta = sum_d dO*O and lse in base 2 (+inf where the row is
+// padding or saw no key).  32-bit index arithmetic (the row count is checked on the host).
+__global__ void __launch_bounds__(256)
+flash_bwd_prepare_kernel(const __nv_bfloat16* __restrict__ dO, const __nv_bfloat16* __restrict__ O,
+                         const float* __restrict__ lse, float* __restrict__ lse2, float* __restrict__ delta, int B, int H,
+                         int Tq, int Tpad, long long do_sb, long long do_st, long long do_sh, long long o_sb, long long o_st,
+                         long long o_sh) {
+  const int total = B * H * Tpad;
+  const int sub = threadIdx.x & 15;
+  for (int w = blockIdx.x * 16 + (threadIdx.x >> 4); w < total; w += gridDim.x * 16) {
+    const int row = w % Tpad;
+    const int bh = w / Tpad;
+    const int h = bh % H, b = bh / H;
+    float acc = 0.f, l2 = INFINITY;
+    if (row < Tq) {
+      const uint4 a = *reinterpret_cast<const uint4*>(dO + b * do_sb + static_cast<long long>(row) * do_st + h * do_sh + sub * 8);
+      const uint4 c = *reinterpret_cast<const uint4*>(O + b * o_sb + static_cast<long long>(row) * o_st + h * o_sh + sub * 8);
+      const float2 a0 = unpack_bf16x2(a.x), a1 = unpack_bf16x2(a.y), a2 = unpack_bf16x2(a.z), a3 = unpack_bf16x2(a.w);
+      const float2 c0 = unpack_bf16x2(c.x), c1 = unpack_bf16x2(c.y), c2 = unpack_bf16x2(c.z), c3 = unpack_bf16x2(c.w);
+      acc = (a0.x * c0.x + a0.y * c0.y) + (a1.x * c1.x + a1.y * c1.y) + (a2.x * c2.x + a2.y * c2.y) + (a3.x * c3.x + a3.y * c3.y);
+      if (sub == 0) {
+        const float l = lse[static_cast<long long>(bh) * Tq + row];
+        l2 = (l == -INFINITY) ? INFINITY : l * 1.4426950408889634f;
+      }
+    }
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (sub == 0) {
+      delta[w] = acc;
+      lse2[w] = l2;
+    }
   }
 }
 
@@ -784,9 +789,11 @@ extern "C" TYR_EXPORT int tyr_flash_bwd(const void* dout, const void* q, const v
     configured = true;
   }
   cudaStream_t cs = (cudaStream_t)stream;
+  if (rows >= (1LL << 31) - 4096) return -5;
   {
-    const long long threads = rows * 32;
-    flash_bwd_prepare_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, cs>>>(
+    long long blocks = (rows + 15) / 16;
+    if (blocks > 148LL * 64) blocks = 148LL * 64;
+    flash_bwd_prepare_kernel<<<(unsigned)blocks, 256, 0, cs>>>(
         (const __nv_bfloat16*)dout, (const __nv_bfloat16*)o, lse, lse2, delta, B, Hq, Tq, tpad, sdo[0], sdo[1],
         sdo[2], so[0], so[1], so[2]);
   }

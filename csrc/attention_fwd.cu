@@ -3,16 +3,22 @@
 // One CTA owns TWO 128-row query tiles of one (batch, head) and walks the key/value sequence
 // in 128-row blocks:
 //
-//   warp 9      TMA producer: Q tiles once, then K_j / V_j into a 2-stage shared-memory ring
-//   warp 8      MMA issuer:   S_t = Q_t K_j^T  (SS, fp32 in TMEM)  and  O_t += P_t V_j  (TS: the
+//   warp 17      TMA producer: Q tiles once, then K_j / V_j into a 2-stage shared-memory ring
+//   warp 16      MMA issuer:   S_t = Q_t K_j^T  (SS, fp32 in TMEM)  and  O_t += P_t V_j  (TS: the
 //                              bf16 probabilities are read straight from TMEM, they never touch
 //                              shared memory)
-//   warps 0-3   softmax for query tile 0 (one thread per query row / TMEM lane)
-//   warps 4-7   softmax for query tile 1
+//   warps 0-7    softmax for query tile 0, warps 8-15 for query tile 1.  TWO threads share a score row
+//                (TMEM lane): warps 0-3 / 8-11 take key columns 0..63 of the block, warps 4-7 / 12-15
+//                columns 64..127.  The halves exchange their row maxima (and, once, their row sums)
+//                through a pair of shared-memory slots with a bounded pairwise handshake.  Four softmax
+//                warps per scheduler partition instead of two: with one thread per row each warp ran a
+//                dependent chain of about 900 instructions per key block and the partition issued on a
+//                third of its cycles.
 //
 // The two tiles ping-pong: while the softmax warps of one tile run exp2 on the SFUs, the tensor
 // core works on the other tile.  TMEM map (512 columns): S0 | S1 | O0 | O1, 128 columns each;
-// P_t overwrites the first 64 columns of S_t as packed bf16.
+// P_t overwrites the first 64 columns of S_t as packed bf16 (each half writes 32 of them, after both
+// halves have their scores in registers).
 // Online softmax uses a lazily updated running maximum: O is only rescaled (read-modify-write
 // of its TMEM tile) when some row's maximum grew by more than 2^8, which keeps the result exact
 // because the same stale maximum is used for the row sum.
@@ -51,12 +57,44 @@ struct __align__(1024) AttnSmem {
   uint64_t q_full;
   uint64_t k_full[ATT_STAGES];
   uint64_t v_full[ATT_STAGES];
-  uint64_t kv_empty[ATT_STAGES];
+  uint64_t k_empty[ATT_STAGES];   // K_j is free once both S products of block j retired (long before V_j is)
+  uint64_t v_empty[ATT_STAGES];
   uint64_t s_ready[2];     // MMA -> softmax: S_t written
   uint64_t p_ready[2];     // softmax -> MMA: P_t written (one arrival per softmax warp)
   uint64_t o_done[2];      // MMA -> softmax: all PV of tile t retired
+  uint2 xch[2][2][2][ATT_BM];   // [tile][parity][column half][row]: {value bits, sequence} of the row-maximum exchange
+  uint2 xsum[2][2][ATT_BM];     // [tile][column half][row]: the row-sum exchange of the epilogue
   uint32_t tmem_base;
 };
+
+// Pairwise exchange between the two threads of a row: publish {value, seq} in my slot, poll the partner's slot until it
+// carries the same sequence number.  Bounded: gives up after about a second and records an error.
+__device__ __forceinline__ bool pair_exchange(uint2* mine, const uint2* theirs, float v, uint32_t seq, float& other,
+                                              int* err, int tag) {
+  asm volatile("st.volatile.shared.v2.u32 [%0], {%1, %2};" ::"r"(smem_u32(mine)), "r"(__float_as_uint(v)), "r"(seq) : "memory");
+  const uint32_t addr = smem_u32(theirs);
+  uint32_t a, b;
+  long long start = 0;
+  for (uint32_t spins = 0;; ++spins) {
+    asm volatile("ld.volatile.shared.v2.u32 {%0, %1}, [%2];" : "=r"(a), "=r"(b) : "r"(addr) : "memory");
+    if (b == seq) break;
+    if ((spins & 0xfff) == 0xfff) {
+      const long long now = clock64();
+      if (start == 0) start = now;
+      if (now - start > kWaitBudgetCycles) {
+        report_error(err, ERR_MBAR_TIMEOUT, tag);
+        return false;
+      }
+    }
+  }
+  other = __uint_as_float(a);
+  return true;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
 
 __device__ __forceinline__ void tmem_ld_32x32_nowait(uint32_t taddr, uint32_t* r) {
   asm volatile(
@@ -96,7 +134,7 @@ __device__ __forceinline__ void kv_range(const AttnParams& p, int r0, int& lo, i
   if (hi < lo) hi = lo;
 }
 
-__global__ void __launch_bounds__(384, 1)
+__global__ void __launch_bounds__(640, 1)
 flash_fwd_d128_kernel(const __grid_constant__ CUtensorMap tmQ,
                       const __grid_constant__ CUtensorMap tmK,
                       const __grid_constant__ CUtensorMap tmV, AttnParams p) {
@@ -126,16 +164,19 @@ flash_fwd_d128_kernel(const __grid_constant__ CUtensorMap tmQ,
     for (int i = 0; i < ATT_STAGES; ++i) {
       mbar_init(&s.k_full[i], 1);
       mbar_init(&s.v_full[i], 1);
-      mbar_init(&s.kv_empty[i], 1);
+      mbar_init(&s.k_empty[i], 1);
+      mbar_init(&s.v_empty[i], 1);
     }
     for (int t = 0; t < 2; ++t) {
       mbar_init(&s.s_ready[t], 1);
-      mbar_init(&s.p_ready[t], ATT_BM / 32);   // one arrival per softmax warp
+      mbar_init(&s.p_ready[t], 8);             // one arrival per softmax warp of the tile
       mbar_init(&s.o_done[t], 1);
     }
     mbar_fence_init();
   }
-  if (warp == 8) {
+  for (int i = threadIdx.x; i < 2 * 2 * 2 * ATT_BM; i += blockDim.x) (&s.xch[0][0][0][0])[i] = make_uint2(0u, 0u);
+  for (int i = threadIdx.x; i < 2 * 2 * ATT_BM; i += blockDim.x) (&s.xsum[0][0][0])[i] = make_uint2(0u, 0u);
+  if (warp == 16) {
     tmem_alloc(&s.tmem_base, 512);
     tmem_relinquish();
   }
@@ -145,15 +186,13 @@ flash_fwd_d128_kernel(const __grid_constant__ CUtensorMap tmQ,
   const uint32_t tmem_base = s.tmem_base;
   constexpr uint32_t kChunk = ATT_BM * 64 * 2;   // one [128 x 64] bf16 swizzled chunk = 16 KB
 
-  // Register re-allocation between warpgroups: the two softmax warpgroups keep a whole 128-value
-  // score row in registers, the producer/MMA warpgroup needs almost none.
-  // Register re-allocation between warpgroups: the two softmax warpgroups keep a whole 128-value
-  // score row in registers, the producer/MMA warpgroup needs few.  The per-thread budgets must sum
-  // to at most the launch allocation (3 warpgroups x 168 = 504): 72 + 216 + 216.  A larger sum makes
-  // setmaxnreg.inc wait forever for registers nobody releases.
-  if (warp >= 8) {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
-  if (warp == 9) {
+  // Register re-allocation between warpgroups: the four softmax warpgroups keep 64 scores per thread in registers, the
+  // producer / MMA warpgroup (warps 16-19, two of them idle) needs few.  The launch allocates 96 registers per thread
+  // (640 threads); 40 x 128 + 104 x 512 stays below that total, so setmaxnreg.inc never waits for registers nobody
+  // releases.
+  if (warp >= 16) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+  if (warp == 17) {
     // ------------------------------------------------------------------ TMA producer
     if (elect_one()) {
       tma_prefetch_desc(&tmQ);
@@ -169,22 +208,23 @@ flash_fwd_d128_kernel(const __grid_constant__ CUtensorMap tmQ,
       for (int j = jlo; j < jhi && ok; ++j, ++it) {
         const int st = it % ATT_STAGES;
         const uint32_t ph = (it / ATT_STAGES) & 1;
-        if (!mbar_wait(&s.kv_empty[st], ph ^ 1, p.err, 500 + st)) { ok = false; break; }
+        // K and V have separate rings: a K stage is released a whole iteration before the V stage of the same block, so
+        // its next load has that much longer to arrive
+        if (!mbar_wait(&s.k_empty[st], ph ^ 1, p.err, 500 + st)) { ok = false; break; }
         mbar_expect_tx(&s.k_full[st], 2 * kChunk);
         for (int c = 0; c < 2; ++c)
           tma_load_4d(s.k[st] + c * kChunk, &tmK, &s.k_full[st], c * 64, kv_head, j * ATT_BN, batch);
+        if (!mbar_wait(&s.v_empty[st], ph ^ 1, p.err, 510 + st)) { ok = false; ++it; break; }
         mbar_expect_tx(&s.v_full[st], 2 * kChunk);
         for (int c = 0; c < 2; ++c)
           tma_load_4d(s.v[st] + c * kChunk, &tmV, &s.v_full[st], c * 64, kv_head, j * ATT_BN, batch);
       }
-      if (!ok) {
-        for (uint32_t q = (it > ATT_STAGES ? it - ATT_STAGES : 0); q < it; ++q) {
+      if (!ok) {   // let the K copies in flight land before the CTA unwinds (a V copy is only issued after its wait succeeded)
+        for (uint32_t q = (it > ATT_STAGES ? it - ATT_STAGES : 0); q < it; ++q)
           mbar_wait(&s.k_full[q % ATT_STAGES], (q / ATT_STAGES) & 1, nullptr, 0);
-          mbar_wait(&s.v_full[q % ATT_STAGES], (q / ATT_STAGES) & 1, nullptr, 0);
-        }
       }
     }
-  } else if (warp == 8) {
+  } else if (warp == 16) {
     // ------------------------------------------------------------------ MMA issuer
     if (elect_one()) {
       constexpr uint32_t idesc_s = make_idesc_f16(1, ATT_BM, ATT_BN, 0, 0);   // Q K^T
@@ -220,6 +260,7 @@ flash_fwd_d128_kernel(const __grid_constant__ CUtensorMap tmQ,
         tc_fence_after();
         for (int t = 0; t < 2 && ok; ++t)
           if (jlo >= lo[t] && jlo < hi[t]) issue_s(t, 0);
+        umma_commit(&s.k_empty[0]);                              // K of the first block: its S products are queued
       }
       for (int j = jlo; j < jhi && ok; ++j, ++it) {
         const int st = it % ATT_STAGES;
@@ -248,84 +289,95 @@ flash_fwd_d128_kernel(const __grid_constant__ CUtensorMap tmQ,
             issue_s(t, st_n);
           }
         }
-        if (ok) umma_commit(&s.kv_empty[st]);   // K_j and V_j no longer needed
+        if (ok) {
+          umma_commit(&s.v_empty[st]);                           // V_j: both PV products are queued
+          if (j + 1 < jhi) umma_commit(&s.k_empty[st_n]);        // K_{j+1}: both S products are queued
+        }
       }
     }
   }
   } else {
-    // ------------------------------------------------------------------ softmax warps
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
-    const int t = warp >> 2;                // query tile of this warpgroup
+    // ------------------------------------------------------------------ softmax warps (two threads per row)
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 104;");
+    const int t = warp >> 3;                // query tile of this warp
+    const int h = (warp >> 2) & 1;          // column half of the key block
     const int lrow = (warp & 3) * 32 + lane;
     const int row = row0 + t * ATT_BM + lrow;
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const uint32_t s_addr = tmem_base + t * 128 + lane_addr;
-    const uint32_t o_addr = tmem_base + 256 + t * 128 + lane_addr;
+    const uint32_t s_addr = tmem_base + t * 128 + h * 64 + lane_addr;     // my 64 score columns
+    const uint32_t p_addr = tmem_base + t * 128 + h * 32 + lane_addr;     // my 32 packed-probability columns
+    const uint32_t o_addr = tmem_base + 256 + t * 128 + h * 64 + lane_addr;
     const bool tile_live = (t == 0) || tile1_live;
     float m_used = -INFINITY;   // running maximum the exponentials are taken against
-    float l_sum = 0.f;
+    float l_sum = 0.f;          // this half's part of the row sum
     bool ok = true;
     uint32_t cnt = 0;
     if (tile_live) {
       for (int j = lo[t]; j < hi[t] && ok; ++j, ++cnt) {
         if (!mbar_wait(&s.s_ready[t], cnt & 1, p.err, 700 + t)) { ok = false; break; }
         tc_fence_after();
-        uint32_t r[128];
+        uint32_t r[64];
         tmem_ld_32x32_nowait(s_addr, r);
         tmem_ld_32x32_nowait(s_addr + 32, r + 32);
-        tmem_ld_32x32_nowait(s_addr + 64, r + 64);
-        tmem_ld_32x32_nowait(s_addr + 96, r + 96);
         tmem_wait_ld();
-        const int col0 = j * ATT_BN;
+        const int col0 = j * ATT_BN + h * 64;
         // mask needed on boundary blocks only
         const int qi = row + p.q_offset;
-        const bool need_mask = (col0 + ATT_BN > p.Tk) || (p.causal && col0 + ATT_BN - 1 > row0 + t * ATT_BM + p.q_offset) ||
-                               (p.window > 0 && col0 < row0 + t * ATT_BM + ATT_BM - 1 + p.q_offset - p.window + 1);
-        // Row maximum on the raw scores (the softmax scale is positive, so it commutes with max); four
-        // independent chains keep the dependent-issue latency off the critical path.
-        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        const bool need_mask = (j * ATT_BN + ATT_BN > p.Tk) || (p.causal && j * ATT_BN + ATT_BN - 1 > row0 + t * ATT_BM + p.q_offset) ||
+                               (p.window > 0 && j * ATT_BN < row0 + t * ATT_BM + ATT_BM - 1 + p.q_offset - p.window + 1);
         if (need_mask) {
 #pragma unroll
-          for (int c = 0; c < 128; ++c) {
+          for (int c = 0; c < 64; ++c) {
             const int col = col0 + c;
             bool keep = col < p.Tk;
             if (p.causal) keep = keep && (col <= qi);
             if (p.window > 0) keep = keep && (col > qi - p.window);
-            const float v = keep ? __uint_as_float(r[c]) : -INFINITY;
-            r[c] = __float_as_uint(v);
-            mx4[c & 3] = fmaxf(mx4[c & 3], v);
+            if (!keep) r[c] = __float_as_uint(-INFINITY);
           }
-        } else {
-#pragma unroll
-          for (int c = 0; c < 128; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(r[c]));
         }
-        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
-        // lazy rescale: move the reference maximum only when it grew by more than 8 (log2 units)
+        // row maximum of my half on the raw scores (the softmax scale is positive, so it commutes with max):
+        // three-input max, four independent chains
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+        for (int c = 0; c < 64; c += 8) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            mx4[u] = max3(mx4[u], __uint_as_float(r[c + 2 * u]), __uint_as_float(r[c + 2 * u + 1]));
+        }
+        float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+        float other;
+        if (!pair_exchange(&s.xch[t][cnt & 1][h][lrow], &s.xch[t][cnt & 1][h ^ 1][lrow], mx, cnt + 1, other, p.err, 720 + t)) {
+          ok = false;
+          break;
+        }
+        // both halves hold their scores in registers from here on: the packed probabilities may overwrite them
+        mx = fmaxf(mx, other) * p.scale_log2;
+        // lazy rescale: move the reference maximum only when it grew by more than 8 (log2 units); both halves of a row
+        // take the same decision because they see the same maximum
         const bool first = (j == lo[t]);
         float m_new = fmaxf(m_used, mx);
         const bool want = first || (m_new > m_used + 8.f);
         if (__any_sync(0xffffffffu, want && !first)) {
           // O is idle here: S_j was queued behind PV_{j-1}, so its completion implies PV_{j-1}'s.
           const float f = want ? exp2f(m_used - m_new) : 1.f;
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            uint32_t o[32];
-            tmem_ld_32x32_nowait(o_addr + c * 32, o);
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {          // 16 columns at a time: the 64 scores stay in registers meanwhile
+            uint32_t o[16];
+            tmem_ld_32x16(o_addr + c * 16, o);
             tmem_wait_ld();
 #pragma unroll
-            for (int q = 0; q < 32; ++q) o[q] = __float_as_uint(__uint_as_float(o[q]) * f);
-            tmem_st_32x32(o_addr + c * 32, o);
+            for (int q = 0; q < 16; ++q) o[q] = __float_as_uint(__uint_as_float(o[q]) * f);
+            tmem_st_32x16(o_addr + c * 16, o);
           }
           tmem_wait_st();
           if (want) l_sum *= f;
         }
         if (want) m_used = (m_new == -INFINITY) ? 0.f : m_new;
-        // probabilities exp2(s * scale - m) -> bf16 -> TMEM (over the first 64 columns of S); the row sum is
-        // taken in fp32 over four chains
+        // probabilities exp2(s * scale - m) -> bf16 -> TMEM; the row sum is taken in fp32 over four chains
         float ls4[4] = {0.f, 0.f, 0.f, 0.f};
         const float neg_m = -m_used;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 2; ++c) {
           uint32_t pk[16];
 #pragma unroll
           for (int q = 0; q < 16; ++q) {
@@ -334,25 +386,29 @@ flash_fwd_d128_kernel(const __grid_constant__ CUtensorMap tmQ,
             pk[q] = pack_bf16x2(p0, p1);
             ls4[q & 3] += p0 + p1;
           }
-          tmem_st_32x16(s_addr + c * 16, pk);
+          tmem_st_32x16(p_addr + c * 16, pk);
         }
-        const float ls = (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
-        l_sum += ls;
+        l_sum += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
         tmem_wait_st();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&s.p_ready[t]);   // one arrival per warp: 128 arrivals on one barrier serialise
+        if (lane == 0) mbar_arrive(&s.p_ready[t]);   // one arrival per warp
       }
       // ---------------------------------------------------------------- epilogue
       if (ok && hi[t] > lo[t]) ok = mbar_wait(&s.o_done[t], 0, p.err, 710 + t);
       tc_fence_after();
       if (ok && hi[t] > lo[t]) {
+        float other;
+        ok = pair_exchange(&s.xsum[t][h][lrow], &s.xsum[t][h ^ 1][lrow], l_sum, 1u, other, p.err, 730 + t);
+        l_sum += other;
+      }
+      if (ok && hi[t] > lo[t]) {
         const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
         const bool row_ok = row < p.Tq;
         __nv_bfloat16* out = p.O + batch * p.o_batch_stride + static_cast<long long>(row) * p.o_row_stride +
-                             head * p.o_head_stride;
+                             head * p.o_head_stride + h * 64;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 2; ++c) {
           uint32_t o[32];
           tmem_ld_32x32_nowait(o_addr + c * 32, o);   // warp-collective: every lane takes part
           tmem_wait_ld();
@@ -368,7 +424,7 @@ flash_fwd_d128_kernel(const __grid_constant__ CUtensorMap tmQ,
             }
           }
         }
-        if (p.lse && row_ok)
+        if (p.lse && row_ok && h == 0)
           p.lse[(static_cast<long long>(batch) * p.Hq + head) * p.Tq + row] =
               l_sum > 0.f ? (m_used + log2f(l_sum)) * 0.6931471805599453f : -INFINITY;
       }
@@ -377,7 +433,7 @@ flash_fwd_d128_kernel(const __grid_constant__ CUtensorMap tmQ,
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 8) {
+  if (warp == 16) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
@@ -454,7 +510,7 @@ extern "C" TYR_EXPORT int tyr_flash_fwd(const void* q, const void* k, const void
   p.O = (__nv_bfloat16*)o; p.o_row_stride = o_st; p.o_batch_stride = o_sb; p.o_head_stride = o_sh;
   p.lse = lse; p.err = err;
   dim3 grid((Tq + 2 * ATT_BM - 1) / (2 * ATT_BM), Hq, B);
-  flash_fwd_d128_kernel<<<grid, 384, smem, (cudaStream_t)stream>>>(tq, tk, tv, p);
+  flash_fwd_d128_kernel<<<grid, 640, smem, (cudaStream_t)stream>>>(tq, tk, tv, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 2000 + (int)e;
 }

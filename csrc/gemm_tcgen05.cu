@@ -136,8 +136,8 @@ __device__ __forceinline__ void epi_chunk(const uint32_t (&r)[32], const float (
 // loads whose completion is counted on the leader's `full` barrier; the leader (cluster rank 0) issues every MMA and
 // commits to the `empty` / `acc_full` barriers of both CTAs; each CTA's epilogue drains its own 128 accumulator rows
 // and arrives on the leader's `acc_empty`.  A stage costs 32 KB instead of 48 KB and every operand byte in shared
-// memory feeds twice the tensor-core work, which is what the single-CTA form runs short of.  Plain mode only (no
-// grouped rows, no K split, no tensor-parallel fusion, K-major A).
+// memory feeds twice the tensor-core work, which is what the single-CTA form runs short of.  Plain and K-split products
+// in all four operand layouts; grouped rows and the tensor-parallel fusions stay on the single-CTA form.
 //
 // The pair form runs 320 threads: warps 2-5 drain the left half of the accumulator columns and warps 6-9 the right half
 // (two epilogue warps per scheduler partition hide each other's latencies; with one, a 128 x 256 tile took about
@@ -353,7 +353,13 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
             // both CTAs' bytes are counted on the leader's barrier; only the leader arms it
             const uint32_t bar = mapa_shared(smem_u32(&s.full[st]), 0);
             if (cta_rank == 0) mbar_expect_tx(&s.full[st], 2 * kStageBytes);
-            tma_load_3d_pair(s.a[st], &tmA, bar, k0, m0, bi);
+            if (!A_MN) {
+              tma_load_3d_pair(s.a[st], &tmA, bar, k0, m0, bi);
+            } else {
+#pragma unroll
+              for (int c = 0; c < BM / 64; ++c)
+                tma_load_3d_pair(s.a[st] + c * (64 * BK * 2), &tmA, bar, m0 + c * 64, k0, bi);
+            }
             const int nb = n0 + static_cast<int>(cta_rank) * BNL;
             if (!B_MN) {
               tma_load_3d_pair(s.b[st], &tmB, bar, k0, nb, bi);
@@ -854,7 +860,13 @@ static int launch_gemm(const TyrGemmArgs& a, const CUtensorMap& tmA, const CUten
   long long tiles = static_cast<long long>((a.M + TILE_M - 1) / TILE_M) * ((a.N + BN - 1) / BN) * a.batch;
   if (a.group_offsets != nullptr)   // host-side bound: every group may add one partial m-tile
     tiles = ((a.sA + BM - 1) / BM + (a.batch < a.sA ? a.batch : a.sA)) * ((a.N + BN - 1) / BN);
+  // `grid` counts scheduler units: CTAs, or CTA pairs
   int grid = a.sm_count > 0 ? a.sm_count : g_sm_count;
+  if (PAIR) {
+    grid /= 2;
+    if (g_pair_clusters_dev[dev] < grid) grid = g_pair_clusters_dev[dev];
+    if (grid < 1) grid = 1;
+  }
   if (a.out_mode != 2 && tiles < grid) grid = static_cast<int>(tiles);
   p.raster_m = (a.group_offsets == nullptr && tp.tp_mode == 0 && a.M < a.N && g_raster_m) ? 1 : 0;
   p.l2_prefetch = (a.group_offsets == nullptr && tp.tp_mode == 0) ? g_l2_prefetch : 0;
@@ -880,12 +892,8 @@ static int launch_gemm(const TyrGemmArgs& a, const CUtensorMap& tmA, const CUten
   }
   if (grid < 1) grid = 1;
   if (PAIR) {
-    int pairs = g_pair_clusters_dev[dev];
-    if (a.sm_count > 0 && a.sm_count / 2 < pairs) pairs = a.sm_count / 2;
-    if (pairs < 1) pairs = 1;
-    if (tiles < pairs) pairs = static_cast<int>(tiles);
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));
+    cfg.gridDim = dim3(static_cast<unsigned>(2 * grid));
     cfg.blockDim = dim3(kThreads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = reinterpret_cast<cudaStream_t>(a.stream);
@@ -985,8 +993,8 @@ static int gemm_impl(const TyrGemmArgs& a, const TyrTpArgs* tpa) {
     r = make_tmap_bf16_3d(&tmA, a.A, a.M, a.K, a.batch, a.lda, a.sA, BK);
   if (r) return 3000 + r;
   // CTA pairs: plain products with a K-major A whose tiles are 256 columns wide
-  const bool pair = g_pair_enabled && tpa == nullptr && a.group_offsets == nullptr && a.out_mode != 2 && !a.a_mn &&
-                    bn == 256 && a.act != 4 && a.act != 5;
+  const bool pair = g_pair_enabled && tpa == nullptr && a.group_offsets == nullptr && bn == 256 && a.act != 4 &&
+                    a.act != 5 && (a.out_mode != 2 || g_aligned_split);
   if (!a.b_mn)
     r = make_tmap_bf16_3d(&tmB, a.B, a.K, a.N, a.batch, a.ldb, a.sB, pair ? bn / 2 : bn);
   else
@@ -1014,8 +1022,10 @@ static int gemm_impl(const TyrGemmArgs& a, const TyrTpArgs* tpa) {
     return launch_gemm<BNv, ST, true, false>(a, tmA, tmB, tmC, tmP, tp);                      \
   } while (0)
   if (pair) {
-    if (!a.b_mn) return launch_gemm<256, 6, false, false, true>(a, tmA, tmB, tmC, tmP, tp);
-    return launch_gemm<256, 6, false, true, true>(a, tmA, tmB, tmC, tmP, tp);
+    if (!a.a_mn && !a.b_mn) return launch_gemm<256, 6, false, false, true>(a, tmA, tmB, tmC, tmP, tp);
+    if (!a.a_mn && a.b_mn) return launch_gemm<256, 6, false, true, true>(a, tmA, tmB, tmC, tmP, tp);
+    if (a.a_mn && a.b_mn) return launch_gemm<256, 6, true, true, true>(a, tmA, tmB, tmC, tmP, tp);
+    return launch_gemm<256, 6, true, false, true>(a, tmA, tmB, tmC, tmP, tp);
   }
   if (bn == 256) TYR_DISPATCH(256, 4);
   if (bn == 128) TYR_DISPATCH(128, 6);

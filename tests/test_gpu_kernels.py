@@ -286,6 +286,32 @@ def test_rmsnorm_weighted_and_rope_norm():
     assert _rel_err(yy.cpu(), yy_ref) < 1e-2
 
 
+def test_nanochat_step_graph_matches_eager_steps():
+    """Forward + backward replayed from a CUDA graph (after two eager steps) trains like the eager step: same losses and
+    parameters over six steps on changing batches, up to the fp32 summation order of the split-K weight gradients."""
+    from tyr_b200.models import nanochat as nc
+    from tyr_b200.train import nanochat_engine as eng
+    cfg = nc.Config(vocab_size=2048, n_layer=7, n_head=2, half_head_dim=64, max_seq_len=128)
+    hp = eng.Hyperparameters(device_batch_size=4, max_seq_len=128, total_batch_size_tokens=512)
+    gen = torch.Generator().manual_seed(5)
+    toks = [torch.randint(0, cfg.vocab_size, (4, 129), generator=gen).to(_dev()) for _ in range(6)]
+    runs = []
+    for graphed in (False, True):
+        tr = eng.NanoChatTrainer(cfg, hp, device=_dev(), compute_dtype=torch.bfloat16, seed=3, ce_chunk_rows=256)
+        tr._graph_enabled = graphed
+        losses = [float(tr.step([(t[:, :-1], t[:, 1:])]).loss.item()) for t in toks]
+        torch.cuda.synchronize()
+        if graphed:
+            assert tr._graph is not None and tr._graph_launches > 50, "the step graph was not captured"
+        runs.append((losses, {k: v.detach().clone() for k, v in tr.params.master.items()}))
+    (l0, p0), (l1, p1) = runs
+    for a, b in zip(l0, l1):
+        assert abs(a - b) < 2e-2 * max(1.0, abs(a)), (l0, l1)
+    assert l0[-1] < l0[0]
+    for k in p0:
+        assert _rel_err(p1[k], p0[k]) < 2e-2, k
+
+
 def test_nanochat_fused_vs_reference_gpu():
     from tyr_b200.models import nanochat as nc
     cfg = nc.Config(vocab_size=2048, n_layer=7, n_head=2, half_head_dim=64, max_seq_len=128)

@@ -225,6 +225,13 @@ class NanoChatTrainer:
             })
         if sharded:
             dp.attach(self)
+        # Forward + backward of a fixed-shape single micro-batch is replayed as ONE CUDA graph after two eager steps
+        # (about a thousand launches per step otherwise, and the host cannot keep the GPU fed through the short ones).
+        # The optimizer step stays outside the graph: its learning rates, momentum and bias corrections change per step.
+        self._graph_enabled = self.device.type == "cuda" and os.environ.get("TYR_STEP_GRAPH", "1") != "0"
+        self._graph = None
+        self._graph_key = None
+        self._graph_eager_steps = 0
 
     # ------------------------------------------------------------------------------------------
     def learning_rates(self, step: int):
@@ -234,7 +241,7 @@ class NanoChatTrainer:
                 get_learning_rate(step, hp, hp.unembedding_lr * bs * ds),
                 get_learning_rate(step, hp, hp.matrix_lr * bs))
 
-    def forward_backward(self, micro_batches: Sequence[Tuple[torch.Tensor, torch.Tensor]]) -> torch.Tensor:
+    def _forward_backward_eager(self, micro_batches) -> torch.Tensor:
         self.params.zero_grads()
         n = len(micro_batches)
         total = None
@@ -243,6 +250,55 @@ class NanoChatTrainer:
             loss.backward()
             total = loss.detach() if total is None else total + loss.detach()
         return total
+
+    def _capture_step_graph(self, inp: torch.Tensor, tgt: torch.Tensor) -> bool:
+        """Record zero-grads + forward + backward for this input shape.  Returns False (and stays eager for good) when the
+        capture fails, e.g. because an operator on the path needs the host."""
+        self._static_inp, self._static_tgt = inp.clone(), tgt.clone()
+        graph = torch.cuda.CUDAGraph()
+        try:
+            torch.cuda.synchronize(self.device)
+            with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+                self.params.zero_grads()
+                loss = nc.loss_fused(self.params, self._static_inp, self._static_tgt, loss_scale=1.0,
+                                     ce_chunk_rows=self.ce_chunk_rows)
+                loss.backward()
+                self._static_loss = loss.detach()
+        except Exception as e:       # leave no half-recorded state behind
+            self._graph_enabled = False
+            self._graph = None
+            torch.cuda.synchronize(self.device)
+            import warnings
+            warnings.warn(f"NanoChat step graph capture failed, staying eager: {type(e).__name__}: {e}")
+            return False
+        self._graph = graph
+        return True
+
+    def forward_backward(self, micro_batches: Sequence[Tuple[torch.Tensor, torch.Tensor]]) -> torch.Tensor:
+        if not (self._graph_enabled and len(micro_batches) == 1 and micro_batches[0][0].is_cuda):
+            return self._forward_backward_eager(micro_batches)
+        inp, tgt = micro_batches[0]
+        key = (tuple(inp.shape), inp.dtype, tuple(tgt.shape), tgt.dtype)
+        if self._graph is not None and key == self._graph_key:
+            self._static_inp.copy_(inp)
+            self._static_tgt.copy_(tgt)
+            self._graph.replay()
+            from ..ops import _common as opc
+            opc.LAUNCH_COUNT[0] += self._graph_launches
+            return self._static_loss
+        if key != self._graph_key:
+            self._graph_key, self._graph_eager_steps, self._graph = key, 0, None
+        if self._graph_eager_steps < 2:          # warm-up: lazily built buffers, module loading, autograd threads
+            self._graph_eager_steps += 1
+            return self._forward_backward_eager(micro_batches)
+        from ..ops import _common as opc
+        before = opc.LAUNCH_COUNT[0]
+        if not self._capture_step_graph(inp, tgt):
+            return self._forward_backward_eager(micro_batches)
+        self._graph_launches = opc.LAUNCH_COUNT[0] - before
+        self._graph.replay()
+        opc.LAUNCH_COUNT[0] += self._graph_launches
+        return self._static_loss
 
     def _smear_gate_step(self, lr: float, momentum: float):
         """Muon on the [1, 12] smear gate (tiny: plain torch ops; same math as the batched path)."""
