@@ -145,7 +145,14 @@ def test_gpu_moe_forward_vs_eager(T, path):
     ref = moe.moe_eager(x.float(), ids, w, g, u, d) + add.float()
     torch.cuda.synchronize()
     scale = ref.abs().max().item()
-    assert torch.allclose(y.float(), ref, rtol=2e-2, atol=2e-2 * scale), (y.float() - ref).abs().max().item()
+    if path == "gemv":       # 16-bit activations on the 4-bit banks: equals the eager loop on the decoded banks
+        assert torch.allclose(y.float(), ref, rtol=2e-2, atol=2e-2 * scale), (y.float() - ref).abs().max().item()
+    else:                    # block-scaled tensor-core path: activations are 4-bit too (W4A4)
+        from tyr_b200.ops import fp4
+        same = fp4.moe_fp4_tc_reference(x, ids.long(), w, ex, add=add).float()
+        assert ((y.float() - same).norm() / same.norm()).item() < 3e-2
+        nrmse = ((y.float() - ref).pow(2).mean().sqrt() / ref.pow(2).mean().sqrt()).item()
+        assert nrmse <= 0.35, nrmse          # the reference's W4A4 against W4A16 bar (Tests/RunLagunaFused.lean:307-341)
 
 
 @pytest.mark.gpu
@@ -162,28 +169,3 @@ def test_gpu_grouped_gemm_empty_and_ragged_groups():
     assert torch.allclose(y.float().cpu(), ref.float(), atol=0.05, rtol=0.02)
 
 
-def test_dense_bank_cache_is_lru_with_a_byte_budget(monkeypatch):
-    """Dequantised banks stay cached up to a byte budget; the least recently used one goes first; one entry always fits."""
-    import types
-    from tyr_b200.ops import moe as M
-    monkeypatch.setattr(M, "_dense_cache", M.collections.OrderedDict())
-    monkeypatch.setattr(M, "_dense_cache_bytes", [0])
-    monkeypatch.setattr(M, "_dense_pinned", set())
-
-    def bank(seed):
-        g = torch.Generator().manual_seed(seed)
-        t = torch.randn(2, 128, 16, generator=g).bfloat16()
-        return types.SimpleNamespace(gate_packed=torch.zeros(seed + 1, dtype=torch.uint8), dense=lambda: (t, t + 1, torch.randn(2, 16, 128, generator=g).bfloat16()))
-    banks = [bank(i) for i in range(4)]
-    one = sum(t.numel() * 2 for t in M._interleaved_gate_up(banks[0]))
-    monkeypatch.setattr(M, "DENSE_CACHE_BUDGET_BYTES", 2 * one)
-    gu0, _ = M._interleaved_gate_up(banks[0])
-    assert gu0.shape == (2, 256, 16) and M._interleaved_gate_up(banks[0])[0] is gu0            # hit returns the same tensors
-    M._interleaved_gate_up(banks[1])
-    M._interleaved_gate_up(banks[0])                                                          # 0 is now the most recent
-    M._interleaved_gate_up(banks[2])                                                          # evicts 1
-    keys = [k[1] for k in M._dense_cache]
-    assert keys == [1, 3] and M._dense_cache_bytes[0] == 2 * one
-    monkeypatch.setattr(M, "DENSE_CACHE_BUDGET_BYTES", 1)
-    M._interleaved_gate_up(banks[3])                                                          # over budget alone: still cached, the rest dropped
-    assert [k[1] for k in M._dense_cache] == [4]

@@ -3,9 +3,10 @@
 ``moe_fp4_forward`` is the counterpart of the reference's fused op
 ``lagunaMoeFp4Forward`` (Tyr/Model/Laguna/Fused.lean:61-113, cc/src/tyr_laguna_moe.cu:1233):
 ``out[t] = sum_s w[t,s] * down_e(silu(gate_e x_t) * up_e x_t)`` with ``e = ids[t,s]`` and NVFP4
-banks.  Small batches take the weight-streaming grouped GEMV; large batches dequantise the banks
-into bf16 (cached per bank) and run the grouped tensor-core GEMM with the SwiGLU in its epilogue.
-The eager paths ``moe_eager`` (per-expert loop) is the CPU oracle.
+banks.  Small batches take the weight-streaming grouped GEMV; larger ones the block-scaled FP4
+tensor-core path of :mod:`tyr_b200.ops.fp4` (activations quantised on the fly, SwiGLU and
+re-quantisation in the first product's epilogue); the banks are never dequantised.
+The eager path ``moe_eager`` (per-expert loop) is the CPU oracle.
 """
 from __future__ import annotations
 
@@ -259,47 +260,6 @@ class PackedExperts:
         return 2 * (mi * h // 2 + mi * h // 16) + (h * mi // 2 + h * mi // 16)
 
 
-_dense_cache: "collections.OrderedDict" = collections.OrderedDict()      # (bank address, size) -> (gate|up interleaved, down) in bf16
-_dense_cache_bytes = [0]
-_dense_pinned = set()                 # banks a captured CUDA graph reads: never evicted
-DENSE_CACHE_BUDGET_BYTES = int(float(os.environ.get("TYR_MOE_DENSE_CACHE_GB", "24")) * (1 << 30))
-
-
-def _interleaved_gate_up(ex: PackedExperts) -> Tuple[torch.Tensor, torch.Tensor]:
-    """bf16 [E, 2*mi_pad, h] with 128 gate rows then 128 up rows per 256-row block, and down [E, h, mi_pad]."""
-    key = (ex.gate_packed.data_ptr(), ex.gate_packed.numel())
-    hit = _dense_cache.get(key)
-    capturing = ex.gate_packed.is_cuda and torch.cuda.is_current_stream_capturing()
-    if hit is not None:
-        _dense_cache.move_to_end(key)
-        if capturing:
-            _dense_pinned.add(key)
-        return hit
-    g, u, d = ex.dense()
-    E, mi, h = g.shape
-    pad = (-mi) % 128
-    if pad:
-        g = torch.nn.functional.pad(g, (0, 0, 0, pad))
-        u = torch.nn.functional.pad(u, (0, 0, 0, pad))
-        d = torch.nn.functional.pad(d, (0, pad))
-    mp = mi + pad
-    gu = torch.stack([g.reshape(E, mp // 128, 128, h), u.reshape(E, mp // 128, 128, h)], dim=2).reshape(E, 2 * mp, h)
-    entry = (gu.contiguous(), d.contiguous())
-    size = sum(t.numel() * t.element_size() for t in entry)
-    # least-recently-used entries go first; one entry is always kept, so a bank larger than the budget still works (and is
-    # dequantised again on its next use, which is what a prefill over many large layers wants)
-    for old_key in [k for k in _dense_cache if k not in _dense_pinned]:
-        if _dense_cache_bytes[0] + size <= DENSE_CACHE_BUDGET_BYTES:
-            break
-        old_entry = _dense_cache.pop(old_key)
-        _dense_cache_bytes[0] -= sum(t.numel() * t.element_size() for t in old_entry)
-    _dense_cache[key] = entry
-    _dense_cache_bytes[0] += size
-    if capturing:
-        _dense_pinned.add(key)
-    return entry
-
-
 def moe_eager(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, gate: torch.Tensor, up: torch.Tensor,
               down: torch.Tensor, act: str = "swiglu") -> torch.Tensor:
     """Per-unique-expert loop on dense banks (the reference's eager path, MoE.lean:313-356); fp32 math.  ``act``: "swiglu"
@@ -361,10 +321,22 @@ def moe_fp4_forward(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, e
         counts = count_experts(ids, E)
     offsets, order, pos, tiles, active = layout(ids.to(torch.int32), counts, want_active=True)
     wf = weights.float().contiguous()
-    path = force_path or ("gemv" if T * k <= GEMV_MAX_PAIRS_PER_EXPERT * E else "gemm")
-    if h % 128 or mi % 128:
-        path = "gemm"
+    from . import fp4
+    tc_ok = fp4.available() and fp4.Fp4Experts.supported(h, mi) and x.dtype == torch.bfloat16
+    gemv_ok = h % 128 == 0 and mi % 128 == 0
+    # measured at hidden 3072 / 256 experts / top-10: the tensor-core path overtakes the weight-streaming GEMV once an
+    # expert sees more than about two rows (64 tokens: 0.27 ms against 0.39 ms)
+    gemv_limit = (2 if tc_ok else GEMV_MAX_PAIRS_PER_EXPERT) * E
+    path = force_path or ("gemv" if (T * k <= gemv_limit and gemv_ok) else "gemm")
+    if path == "gemm" and not tc_ok:
+        path = "gemv" if gemv_ok else "eager"
+    if path == "gemv" and not gemv_ok:
+        path = "gemm" if tc_ok else "eager"
     st = cur_stream(x.device)
+    if path == "eager":      # shapes neither kernel tiles (tiny test models): per-expert loop on banks decoded on the fly
+        g, u, d = ex.dense()
+        y = moe_eager(x, ids, weights, g, u, d)
+        return (y.float() + add.float()).to(x.dtype) if add is not None else y
     if path == "gemv":
         hid = torch.zeros((2, T * k, mi), dtype=torch.float32, device=x.device)
         routed = torch.zeros((T, h), dtype=torch.float32, device=x.device)
@@ -379,15 +351,8 @@ def moe_fp4_forward(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, e
         check(lib().tyr_moe_finalize(ptr(routed), ptr(add.contiguous() if add is not None else None), ptr(out),
                                      routed.numel(), st), "moe_finalize")
         return out
-    gu, dn = _interleaved_gate_up(ex)
-    xs = torch.empty((T * k, h), dtype=x.dtype, device=x.device)
-    check(lib().tyr_moe_gather_rows(ptr(x.contiguous()), ptr(order), ptr(xs), T * k, k, h, st), "moe_gather_rows")
-    hid = grouped_gemm(xs, gu, offsets, tiles, act="swiglu")
-    y = grouped_gemm(hid, dn, offsets, tiles)
-    out = torch.empty_like(x)
-    check(lib().tyr_moe_combine(ptr(y), ptr(pos), ptr(wf), ptr(add.contiguous() if add is not None else None), ptr(out),
-                                T, k, h, st), "moe_combine")
-    return out
+    # block-scaled FP4 tensor-core path: activations quantised on the fly, banks stay 4-bit end to end
+    return fp4.moe_fp4_tc_forward(x, ids, wf, ex, offsets, order, tiles, add=add)
 
 
 _gu_cache: Dict[int, torch.Tensor] = {}
