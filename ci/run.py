@@ -37,7 +37,9 @@ OUT = ROOT / "build" / "ci"
 # CUDA entry points that are closed on the B200 pool, and the load form that must never reach another GPU's memory.
 FORBIDDEN = [
     ("batched memcpy", re.compile(r"cu(?:da)?Memcpy(?:3D)?Batch" + r"Async")),
-    ("cluster-multicast bulk load", re.compile(r"cp\.async\.bulk[\w.:]*\.multicast" + r"::cluster")),
+    # the qualifier that lets one bulk / TMA load feed several CTAs of a cluster (assembled from pieces so that this
+    # checker is not itself reported by scanners that look for the same text)
+    ("bulk load shared by several CTAs", re.compile(r"cp\.async\.bulk[\w.:]*\." + "multi" + "cast" + "::" + "cluster")),
     ("GPU clock / power setting", re.compile(r"nvidia-smi\s+(?:-lgc|-ac|-pl|-pm|--lock-gpu-clocks|-rgc|--gpu-reset)")),
     ("device-side trap", re.compile(r"\b__trap\s*\(")),
 ]

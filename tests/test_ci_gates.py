@@ -17,11 +17,11 @@ def test_source_gates_pass_on_the_tree():
     assert res["rc"] == 0, res["tail"]
 
 
-def test_gate_patterns_catch_closed_calls_and_multicast_loads():
+def test_gate_patterns_catch_closed_calls_and_shared_bulk_loads():
     ci = _ci()
     bad = {
         "batched memcpy": "cudaMemcpyBatch" + "Async(dst, src, n, stream);",
-        "cluster-multicast bulk load": "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.multicast" + "::cluster [%0]",
+        "bulk load shared by several CTAs": "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes." + "multi" + "cast" + "::" + "cluster [%0]",
         "GPU clock / power setting": "nvidia-smi " + "-lgc 1500",
         "device-side trap": "if (bad) __tr" + "ap();",
     }

@@ -32,6 +32,7 @@ def main():
 
     dp = FusedDataParallel(rank, world, dev)
     tr = eng.NanoChatTrainer(cfg, hp, device=dev, seed=7, world_size=world, rank=rank, dp=dp, ce_chunk_rows=256)
+    init = {k: v.detach().float().clone() for k, v in tr.params.named_parameters("work").items()}
     losses = []
     for s in range(steps):
         t = toks[s, rank].to(dev)
@@ -61,12 +62,36 @@ def main():
             single.step(mbs)
         torch.cuda.synchronize()
         ref = single.params.named_parameters("work")
+        worst = ("", 0.0)
         for k, v in work.items():
-            a, b = v, ref[k].float()
-            err = ((a - b).norm() / (b.norm() + 1e-9)).item()
-            if not err < 2e-2:
+            # the UPDATE (parameter - initial value) is compared, not the parameter: three small steps move a weight by
+            # about a percent, so a skipped or doubled update would hide inside a tolerance on the parameter itself
+            da, db = v - init[k], ref[k].float() - init[k]
+            if db.norm().item() == 0.0:
+                if da.norm().item() != 0.0:
+                    ok = False
+                    msg += f"{k}: moved in the data-parallel run but not in the single-process run\n"
+                continue
+            err = ((da - db).norm() / db.norm()).item()
+            if err > worst[1]:
+                worst = (k, err)
+            # Bound: measured 0.10 - 0.18 between runs of this tiny model (Newton-Schulz amplifies the summation-order
+            # noise of near-rank-deficient gradients in the first steps); one skipped or doubled step out of three is an
+            # error of 0.33 or more
+            if not err < float(os.environ.get("TYR_DP_DELTA_TOL", "0.3")):
                 ok = False
-                msg += f"{k}: rel err {err:.4f} vs single-process accumulation\n"
+                msg += f"{k}: update differs by {err:.4f} (relative) from single-process accumulation\n"
+        print(f"DP_WORKER worst update error {worst[1]:.4f} at {worst[0]}", flush=True)
+        # optimizer moments of the tensors this rank owns agree with the single-process state
+        mine = tr.optimizer_state_dict()
+        theirs = single.optimizer_state_dict()
+        for k in ("adam.scalars.exp_avg", "adam.scalars.exp_avg_sq", "muon.smear_gate.momentum"):
+            if k in mine and k in theirs:
+                a, b = mine[k].float(), theirs[k].float()
+                e = ((a - b).norm() / (b.norm() + 1e-12)).item()
+                if not e < 0.25:       # measured 0.05 - 0.11 run to run (sums with heavy cancellation over bf16 activations)
+                    ok = False
+                    msg += f"{k}: moment differs by {e:.4f}\n"
     flag = torch.tensor([0 if ok else 1], device=dev)
     dist.all_reduce(flag)
     if rank == 0:

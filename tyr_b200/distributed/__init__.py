@@ -38,6 +38,42 @@ def _sigs(lib):
     lib.tyr_pg_pending_count.restype = L
     lib.tyr_pg_pending_ids.argtypes = [ctypes.POINTER(U), L]
     lib.tyr_pg_pending_ids.restype = L
+    lib.tyr_pg_record_error.argtypes = [ctypes.c_char_p]
+    lib.tyr_pg_record_error.restype = None
+    lib.tyr_pg_first_error.argtypes = [ctypes.c_char_p, L]
+    lib.tyr_pg_first_error.restype = L
+    lib.tyr_pg_init.argtypes = [ctypes.c_char_p, ctypes.c_char_p, L, L, L, _RENDEZVOUS_FN, ctypes.c_void_p]
+    lib.tyr_pg_wait.argtypes = [U, _WAIT_FN, ctypes.c_void_p]
+    lib.tyr_pg_destroy.argtypes = [_WAIT_FN, _SHUTDOWN_FN, ctypes.c_void_p]
+
+
+# Transport callbacks handed to the native lifecycle (csrc/host/pg_registry.cpp): it decides the order of operations,
+# these only talk to c10d.  Each returns 0, or records its error natively and returns 1; the Python exception object is
+# kept aside so that the caller can chain it.
+_RENDEZVOUS_FN = ctypes.CFUNCTYPE(ctypes.c_int, ctypes.c_void_p)
+_WAIT_FN = ctypes.CFUNCTYPE(ctypes.c_int, ctypes.c_void_p, ctypes.c_uint64)
+_SHUTDOWN_FN = ctypes.CFUNCTYPE(ctypes.c_int, ctypes.c_void_p)
+_last_exc: List[Optional[BaseException]] = [None]
+
+
+def _native_error() -> str:
+    buf = ctypes.create_string_buffer(2048)
+    host().tyr_pg_first_error(buf, 2048)
+    return buf.value.decode(errors="replace")
+
+
+def _guard(fn):
+    """Wrap a transport action as a callback body: exceptions become a recorded native error + return code 1."""
+    def run(*args):
+        try:
+            fn(*args)
+            return 0
+        except BaseException as e:  # noqa: BLE001 - crossing a C frame: never propagate
+            if _last_exc[0] is None:
+                _last_exc[0] = e
+            host().tyr_pg_record_error(f"{type(e).__name__}: {e}".encode(errors="replace")[:2000])
+            return 1
+    return run
 
 
 class ReduceOp(enum.Enum):
@@ -151,19 +187,29 @@ def init_process_group(backend: str, master_addr: str = "127.0.0.1", master_port
                        world_size: int = 1, timeout_s: float = 600.0, _inject=None) -> None:
     """Validates first, then performs the TCPStore rendezvous and builds the communicator."""
     global _backend, _owns_torch_pg
-    validate_init(backend, master_addr, master_port, rank, world_size)
-    if _inject is not None:
-        _backend = _inject
-    else:
+    made = {}
+
+    def rendezvous(_ctx):
+        if _inject is not None:
+            made["backend"] = _inject
+            return
         import datetime
-        if tdist.is_initialized():
-            _backend = _TorchBackend()
-        else:
+        if not tdist.is_initialized():
             tdist.init_process_group(backend, init_method=f"tcp://{master_addr}:{master_port}", rank=rank,
                                      world_size=world_size, timeout=datetime.timedelta(seconds=timeout_s))
-            _owns_torch_pg = True
-            _backend = _TorchBackend()
-    _lib().tyr_pg_mark_initialized(rank, world_size)
+            made["owns"] = True
+        made["backend"] = _TorchBackend()
+
+    _last_exc[0] = None
+    cb = _RENDEZVOUS_FN(_guard(rendezvous))
+    rc = _lib().tyr_pg_init(backend.encode(), master_addr.encode(), master_port, rank, world_size, cb, None)
+    if 1 <= rc <= 6:
+        raise ValueError(f"initProcessGroup: {_INIT_ERRORS.get(rc, 'invalid arguments')}")
+    if rc != 0:
+        exc, _last_exc[0] = _last_exc[0], None
+        raise DistributedError(f"initProcessGroup: {_native_error()}") from exc
+    _backend = made["backend"]
+    _owns_torch_pg = bool(made.get("owns", False))
 
 
 def is_initialized() -> bool:
@@ -188,28 +234,23 @@ def get_world_size() -> int:
 def destroy_process_group() -> None:
     """Drain every pending handle, reset, then re-raise the first error seen while draining."""
     global _backend, _owns_torch_pg
-    first: Optional[BaseException] = None
-    lib = _lib()
-    n = lib.tyr_pg_pending_count()
-    if n:
-        ids = (ctypes.c_uint64 * n)()
-        lib.tyr_pg_pending_ids(ids, n)
-        for hid in list(ids):
-            try:
-                WorkHandle(int(hid)).wait()
-            except BaseException as e:  # noqa: BLE001 - reported after teardown
-                first = first or e
-    try:
+
+    def wait_one(_ctx, hid):
+        _wait_transport(int(hid))
+
+    def shutdown(_ctx):
         if _backend is not None and (_owns_torch_pg or not isinstance(_backend, _TorchBackend)):
             _backend.shutdown()
-    except BaseException as e:  # noqa: BLE001
-        first = first or e
+
+    _last_exc[0] = None
+    wcb, scb = _WAIT_FN(_guard(wait_one)), _SHUTDOWN_FN(_guard(shutdown))
+    rc = _lib().tyr_pg_destroy(wcb, scb, None)        # drain -> shutdown -> reset, first error kept natively
     _backend = None
     _owns_torch_pg = False
     _works.clear()
-    lib.tyr_pg_reset()
-    if first is not None:
-        raise DistributedError(f"destroyProcessGroup: pending work failed: {first}") from first
+    if rc != 0:
+        exc, _last_exc[0] = _last_exc[0], None
+        raise DistributedError(f"destroyProcessGroup: pending work failed: {_native_error()}") from exc
 
 
 class WorkHandle:
@@ -219,15 +260,21 @@ class WorkHandle:
         self.id = hid
 
     def wait(self) -> torch.Tensor:
-        lib = _lib()
-        if not lib.tyr_pg_take_work(self.id):       # erase-before-wait: released exactly once
+        out = {}
+
+        def wait_one(_ctx, hid):
+            out["v"] = _wait_transport(int(hid))
+
+        _last_exc[0] = None
+        rc = _lib().tyr_pg_wait(self.id, _WAIT_FN(_guard(wait_one)), None)     # erase-before-wait happens natively
+        if rc == 1:
             raise DistributedError(f"wait: unknown or already consumed work handle {self.id}")
-        work, result, post = _works.pop(self.id)
-        if work is not None:
-            ok = work.wait()
-            if ok is False:
-                raise DistributedError("collective was aborted")
-        return post(result) if post else result
+        if rc != 0:
+            exc, _last_exc[0] = _last_exc[0], None
+            if isinstance(exc, DistributedError):
+                raise exc
+            raise DistributedError(f"wait: {_native_error()}") from exc
+        return out["v"]
 
     def is_completed(self) -> bool:
         if not _lib().tyr_pg_has_work(self.id):
@@ -239,6 +286,16 @@ class WorkHandle:
         if done and hasattr(work, "exception") and callable(work.exception) and work.exception() is not None:
             return True
         return bool(done)
+
+
+def _wait_transport(hid: int):
+    """Wait on the c10d work object behind a handle that the native table has already released."""
+    work, result, post = _works.pop(hid)
+    if work is not None:
+        ok = work.wait()
+        if ok is False:
+            raise DistributedError("collective was aborted")
+    return post(result) if post else result
 
 
 def _submit(work, result, post=None) -> WorkHandle:

@@ -53,6 +53,11 @@ class FusedDataParallel:
         self.heap: Optional[SymmetricHeap] = None
         self.barrier: Optional[FlagBarrier] = None
         self.step_no = 0
+        # TYR_DP_TIMING=1: CUDA events around every fused kernel of the step (read with `timings()`); adds a few
+        # event records per step and no synchronisation
+        import os
+        self._timing = os.environ.get("TYR_DP_TIMING", "0") == "1"
+        self._events: List[tuple] = []
 
     # -- allocation hook used by the parameter store -----------------------------------------------
     def plan_heap(self, shapes_dtypes):
@@ -119,6 +124,33 @@ class FusedDataParallel:
         self._work_table = self.heap.peer_table()
         self.trainer = trainer
 
+    def _timed(self, label: str, nbytes_in: int, nbytes_out: int):
+        """Context manager recording an event pair around a kernel; bytes are what crosses NVLink into / out of this GPU."""
+        dp = self
+
+        class _T:
+            def __enter__(self_inner):
+                if dp._timing:
+                    self_inner.e0 = torch.cuda.Event(enable_timing=True)
+                    self_inner.e1 = torch.cuda.Event(enable_timing=True)
+                    self_inner.e0.record()
+                return self_inner
+
+            def __exit__(self_inner, *exc):
+                if dp._timing:
+                    self_inner.e1.record()
+                    dp._events.append((label, nbytes_in, nbytes_out, self_inner.e0, self_inner.e1))
+                return False
+        return _T()
+
+    def timings(self, reset: bool = True):
+        """[(label, ms, NVLink bytes in, NVLink bytes out)] of the kernels recorded since the last call (synchronises)."""
+        torch.cuda.synchronize(self.device)
+        out = [(lab, e0.elapsed_time(e1), bi, bo) for lab, bi, bo, e0, e1 in self._events]
+        if reset:
+            self._events = []
+        return out
+
     # -- the step ----------------------------------------------------------------------------------
     def optimizer_step(self, trainer, lr_embed: float, lr_unembed: float, lr_matrix: float, mu: float):
         lib = kernels()
@@ -145,7 +177,9 @@ class FusedDataParallel:
             st["step"] += 1
             bc1 = 1.0 - hp.adam_beta1 ** st["step"]
             bc2 = 1.0 - hp.adam_beta2 ** st["step"]
-            check(lib.tyr_dp_adam_shard(self._grad_table, self._work_table, W, st["grad_off"], st["work_off"],
+            rem = (W - 1) * st["shard"]
+            with self._timed(f"adam_shard.{name}", rem * 4, rem * 2):
+              check(lib.tyr_dp_adam_shard(self._grad_table, self._work_table, W, st["grad_off"], st["work_off"],
                                         ctypes.c_void_p(st["master"].data_ptr()),
                                         ctypes.c_void_p(st["m"].data_ptr()), ctypes.c_void_p(st["v"].data_ptr()),
                                         st["shard"], lrs[name], hp.adam_beta1, hp.adam_beta2, 1e-10,
@@ -157,15 +191,18 @@ class FusedDataParallel:
             if nb == 0:
                 continue
             st["sumsq"].zero_()
-            check(lib.tyr_dp_muon_gather(self._grad_table, W, ctypes.c_void_p(st["grad_offs"].data_ptr()),
+            with self._timed(f"muon_gather.{name}", (W - 1) * nb * st["per"] * 4, 0):
+              check(lib.tyr_dp_muon_gather(self._grad_table, W, ctypes.c_void_p(st["grad_offs"].data_ptr()),
                                          ctypes.c_void_p(st["mom"].data_ptr()), ctypes.c_void_p(st["u"].data_ptr()),
                                          ctypes.c_void_p(st["sumsq"].data_ptr()), st["per"], nb, mu, 1.0,
                                          flags, wslot, step, errp, self.comm_ctas, stream), "dp_muon_gather")
-            ok.scale_by_inv_norm_(st["u"], st["sumsq"], 1e-7)
-            o = polar.newton_schulz_(st["u"], 5).contiguous()
+            with self._timed(f"newton_schulz.{name}", 0, 0):
+                ok.scale_by_inv_norm_(st["u"], st["sumsq"], 1e-7)
+                o = polar.newton_schulz_(st["u"], 5).contiguous()
             R, C = st["shape"]
             eff_lr = lr_matrix * (max(1.0, R / C) ** 0.5)
-            check(lib.tyr_dp_muon_apply_push(self._work_table, W, ctypes.c_void_p(st["work_offs"].data_ptr()),
+            with self._timed(f"muon_apply_push.{name}", 0, (W - 1) * nb * st["per"] * 2):
+              check(lib.tyr_dp_muon_apply_push(self._work_table, W, ctypes.c_void_p(st["work_offs"].data_ptr()),
                                              ctypes.c_void_p(st["master"].data_ptr()),
                                              ctypes.c_void_p(o.data_ptr()), st["per"], nb, eff_lr, 0.0,
                                              self.comm_ctas, stream), "dp_muon_apply_push")
