@@ -780,7 +780,10 @@ extern "C" TYR_EXPORT int tyr_flash_bwd(const void* dout, const void* q, const v
   if ((r = make_map(&tv, v, B, Tk, Hkv, sv[0], sv[1], sv[2]))) return 5000 + r;
   if ((r = make_map(&tdo, dout, B, Tq, Hq, sdo[0], sdo[1], sdo[2]))) return 6000 + r;
   constexpr size_t smem = sizeof(BwdSmem), smem_dq = sizeof(DqSmem);
-  static bool configured = false;
+  static bool configured_dev[64] = {false};     // the attribute is per device
+  int cfg_dev = 0;
+  if (cudaGetDevice(&cfg_dev) != cudaSuccess || cfg_dev < 0 || cfg_dev >= 64) cfg_dev = 0;
+  bool& configured = configured_dev[cfg_dev];
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(flash_bwd_d128_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e == cudaSuccess)

@@ -496,7 +496,10 @@ extern "C" TYR_EXPORT int tyr_flash_fwd(const void* q, const void* k, const void
   if ((r = make_tmap_bthd(&tk, k, B, Tk, Hkv, D, k_sb, k_st, k_sh, ATT_BN))) return 4000 + r;
   if ((r = make_tmap_bthd(&tv, v, B, Tk, Hkv, D, v_sb, v_st, v_sh, ATT_BN))) return 5000 + r;
   constexpr size_t smem = sizeof(AttnSmem) + 1024;
-  static bool configured = false;
+  static bool configured_dev[64] = {false};     // the attribute is per device
+  int cfg_dev = 0;
+  if (cudaGetDevice(&cfg_dev) != cudaSuccess || cfg_dev < 0 || cfg_dev >= 64) cfg_dev = 0;
+  bool& configured = configured_dev[cfg_dev];
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(flash_fwd_d128_kernel,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

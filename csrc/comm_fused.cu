@@ -19,8 +19,8 @@
 //  * signal / wait_all: a flag barrier in symmetric memory (st.release.sys / ld.acquire.sys).
 //    Waits are bounded: on timeout the kernel records ERR_PEER_FLAG_TIMEOUT and returns.
 //
-// Tensor-parallel and expert-parallel fused kernels (GEMM -> reduce-scatter epilogue, all-gather
-// prologue, MoE dispatch/combine) live in tp_fused.cu / moe_ep.cu and reuse the helpers here.
+// The tensor-parallel fusions (GEMM -> reduce-scatter epilogue, all-gather prologue) are modes of the GEMM kernel in
+// gemm_tcgen05.cu; the expert-parallel dispatch / combine kernels live in ep_fused.cu.
 #include "common.cuh"
 
 namespace tyr {
@@ -39,9 +39,11 @@ __device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long
   asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(addr) : "memory");
   return v;
 }
+// Peer data is written by the other ranks while this kernel may already be resident (it waits for their flags itself), so
+// the load must go through the coherent path: no `.nc`.  It bypasses L1 allocation because every value is read once.
 __device__ __forceinline__ float4 ld_peer_f4(const float* p) {
   float4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.f32 {%0, %1, %2, %3}, [%4];"
+  asm volatile("ld.global.L1::no_allocate.v4.f32 {%0, %1, %2, %3}, [%4];"
                : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
                : "l"(p));
   return v;
@@ -120,37 +122,55 @@ __global__ void __launch_bounds__(256) dp_adam_shard_kernel(DpAdamArgs a) {
   }
   const long long n4 = a.n >> 2;
   const float inv_w = a.grad_scale / a.world;
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n4;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    float4 g = make_float4(0.f, 0.f, 0.f, 0.f);
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  // Four independent 16-byte elements per thread and iteration: all of their peer loads are issued before the first
+  // result is used, so several NVLink round trips are in flight per thread (one element at a time reached about half of
+  // the link bandwidth).
+  constexpr int U = 4;
+  for (long long i0 = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i0 < n4; i0 += stride * U) {
+    float4 g[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) g[u] = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
     for (int r = 0; r < kMaxRanks; ++r) {
       if (r < a.world) {
-        float4 t = ld_peer_f4(reinterpret_cast<const float*>(a.grads.p[r]) + a.grad_off + i * 4);
-        g.x += t.x; g.y += t.y; g.z += t.z; g.w += t.w;
+        const float* src = reinterpret_cast<const float*>(a.grads.p[r]) + a.grad_off;
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const long long i = i0 + u * stride;
+          if (i < n4) {
+            const float4 t = ld_peer_f4(src + i * 4);
+            g[u].x += t.x; g[u].y += t.y; g[u].z += t.z; g[u].w += t.w;
+          }
+        }
       }
     }
-    float4 p = reinterpret_cast<float4*>(a.master)[i];
-    float4 m = reinterpret_cast<float4*>(a.m)[i];
-    float4 v = reinterpret_cast<float4*>(a.v)[i];
-    float gg[4] = {g.x * inv_w, g.y * inv_w, g.z * inv_w, g.w * inv_w};
-    float pp[4] = {p.x, p.y, p.z, p.w}, mm[4] = {m.x, m.y, m.z, m.w}, vv[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      mm[j] = a.beta1 * mm[j] + (1.f - a.beta1) * gg[j];
-      vv[j] = a.beta2 * vv[j] + (1.f - a.beta2) * gg[j] * gg[j];
-      pp[j] = pp[j] * (1.f - a.lr * a.wd) - a.lr * (mm[j] / a.bc1) / (sqrtf(vv[j] / a.bc2) + a.eps);
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride;
+      if (i >= n4) break;
+      float4 p = reinterpret_cast<float4*>(a.master)[i];
+      float4 m = reinterpret_cast<float4*>(a.m)[i];
+      float4 v = reinterpret_cast<float4*>(a.v)[i];
+      float gg[4] = {g[u].x * inv_w, g[u].y * inv_w, g[u].z * inv_w, g[u].w * inv_w};
+      float pp[4] = {p.x, p.y, p.z, p.w}, mm[4] = {m.x, m.y, m.z, m.w}, vv[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        mm[j] = a.beta1 * mm[j] + (1.f - a.beta1) * gg[j];
+        vv[j] = a.beta2 * vv[j] + (1.f - a.beta2) * gg[j] * gg[j];
+        pp[j] = pp[j] * (1.f - a.lr * a.wd) - a.lr * (mm[j] / a.bc1) / (sqrtf(vv[j] / a.bc2) + a.eps);
+      }
+      reinterpret_cast<float4*>(a.master)[i] = make_float4(pp[0], pp[1], pp[2], pp[3]);
+      reinterpret_cast<float4*>(a.m)[i] = make_float4(mm[0], mm[1], mm[2], mm[3]);
+      reinterpret_cast<float4*>(a.v)[i] = make_float4(vv[0], vv[1], vv[2], vv[3]);
+      uint2 w;
+      w.x = pack_bf16x2(pp[0], pp[1]);
+      w.y = pack_bf16x2(pp[2], pp[3]);
+#pragma unroll
+      for (int r = 0; r < kMaxRanks; ++r)
+        if (r < a.world)
+          reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(a.work.p[r]) + a.work_off)[i] = w;
     }
-    reinterpret_cast<float4*>(a.master)[i] = make_float4(pp[0], pp[1], pp[2], pp[3]);
-    reinterpret_cast<float4*>(a.m)[i] = make_float4(mm[0], mm[1], mm[2], mm[3]);
-    reinterpret_cast<float4*>(a.v)[i] = make_float4(vv[0], vv[1], vv[2], vv[3]);
-    uint2 w;
-    w.x = pack_bf16x2(pp[0], pp[1]);
-    w.y = pack_bf16x2(pp[2], pp[3]);
-#pragma unroll
-    for (int r = 0; r < kMaxRanks; ++r)
-      if (r < a.world)
-        reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(a.work.p[r]) + a.work_off)[i] = w;
   }
 }
 
@@ -184,27 +204,43 @@ __global__ void __launch_bounds__(256) dp_muon_gather_kernel(DpMuonGatherArgs a)
   const float inv_w = a.grad_scale / a.world;
   const float om = 1.f - a.mu;
   float ss = 0.f;
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n4;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    float4 g = make_float4(0.f, 0.f, 0.f, 0.f);
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  constexpr int U = 4;          // see dp_adam_shard_kernel
+  for (long long i0 = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i0 < n4; i0 += stride * U) {
+    float4 gs[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) gs[u] = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
     for (int r = 0; r < kMaxRanks; ++r) {
       if (r < a.world) {
-        float4 t = ld_peer_f4(reinterpret_cast<const float*>(a.grads.p[r]) + goff + i * 4);
-        g.x += t.x; g.y += t.y; g.z += t.z; g.w += t.w;
+        const float* src = reinterpret_cast<const float*>(a.grads.p[r]) + goff;
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const long long i = i0 + u * stride;
+          if (i < n4) {
+            const float4 t = ld_peer_f4(src + i * 4);
+            gs[u].x += t.x; gs[u].y += t.y; gs[u].z += t.z; gs[u].w += t.w;
+          }
+        }
       }
     }
-    g.x *= inv_w; g.y *= inv_w; g.z *= inv_w; g.w *= inv_w;
-    float4 m = *reinterpret_cast<float4*>(a.mom + base + i * 4);
-    m.x = a.mu * m.x + om * g.x; m.y = a.mu * m.y + om * g.y;
-    m.z = a.mu * m.z + om * g.z; m.w = a.mu * m.w + om * g.w;
-    *reinterpret_cast<float4*>(a.mom + base + i * 4) = m;
-    uint2 w;
-    w.x = pack_bf16x2(om * g.x + a.mu * m.x, om * g.y + a.mu * m.y);
-    w.y = pack_bf16x2(om * g.z + a.mu * m.z, om * g.w + a.mu * m.w);
-    *reinterpret_cast<uint2*>(a.u + base + i * 4) = w;
-    float2 r0 = unpack_bf16x2(w.x), r1 = unpack_bf16x2(w.y);
-    ss += r0.x * r0.x + r0.y * r0.y + r1.x * r1.x + r1.y * r1.y;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride;
+      if (i >= n4) break;
+      float4 g = gs[u];
+      g.x *= inv_w; g.y *= inv_w; g.z *= inv_w; g.w *= inv_w;
+      float4 m = *reinterpret_cast<float4*>(a.mom + base + i * 4);
+      m.x = a.mu * m.x + om * g.x; m.y = a.mu * m.y + om * g.y;
+      m.z = a.mu * m.z + om * g.z; m.w = a.mu * m.w + om * g.w;
+      *reinterpret_cast<float4*>(a.mom + base + i * 4) = m;
+      uint2 w;
+      w.x = pack_bf16x2(om * g.x + a.mu * m.x, om * g.y + a.mu * m.y);
+      w.y = pack_bf16x2(om * g.z + a.mu * m.z, om * g.w + a.mu * m.w);
+      *reinterpret_cast<uint2*>(a.u + base + i * 4) = w;
+      float2 r0 = unpack_bf16x2(w.x), r1 = unpack_bf16x2(w.y);
+      ss += r0.x * r0.x + r0.y * r0.y + r1.x * r1.x + r1.y * r1.y;
+    }
   }
   __shared__ float red[8];
   ss = warp_sum(ss);

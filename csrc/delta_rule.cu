@@ -622,7 +622,10 @@ extern "C" TYR_EXPORT int tyr_gdr_chunk_prepare(const void* q, const void* k, co
   a.v_sb = strides[6]; a.v_ss = strides[7]; a.v_sh = strides[8];
   a.S = S; a.n = (S + GC_C - 1) / GC_C; a.Hk = Hk; a.Hv = Hv; a.dv = dv;
   constexpr size_t smem = sizeof(GdrPrepSmem);
-  static bool configured = false;
+  static bool configured_dev[64] = {false};     // the attribute is per device
+  int cfg_dev = 0;
+  if (cudaGetDevice(&cfg_dev) != cudaSuccess || cfg_dev < 0 || cfg_dev >= 64) cfg_dev = 0;
+  bool& configured = configured_dev[cfg_dev];
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gdr_chunk_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return 1000 + (int)e;
@@ -647,7 +650,10 @@ extern "C" TYR_EXPORT int tyr_gdr_chunk_scan(const float* u, const float* w, con
        reinterpret_cast<uintptr_t>(state_out) | reinterpret_cast<uintptr_t>(state_in)) & 15)
     return -2;
   constexpr size_t smem = sizeof(GdrChunkSmem);
-  static bool configured = false;
+  static bool configured_dev[64] = {false};     // the attribute is per device
+  int cfg_dev = 0;
+  if (cudaGetDevice(&cfg_dev) != cudaSuccess || cfg_dev < 0 || cfg_dev >= 64) cfg_dev = 0;
+  bool& configured = configured_dev[cfg_dev];
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gdr_chunk_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return 1000 + (int)e;

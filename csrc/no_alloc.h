@@ -28,10 +28,13 @@ extern "C" {
 //            TYR_NS_STATIC_SCRATCH_BYTES, 9000+e if resolving the array's device address failed
 //            with CUDA error e, other positive values as tyr_gemm_bf16.
 //
-// * The array occupies TYR_NS_STATIC_SCRATCH_BYTES on every GPU that loads the library, from load
-//   until the process exits.
+// * The array occupies TYR_NS_STATIC_SCRATCH_BYTES on every GPU that uses the library's code, until the
+//   process exits.  With CUDA's lazy module loading the driver reserves it when the module is first
+//   used on a device, which is at the latest this entry's first call there: a process whose pool wants
+//   the whole device should make one warm-up call at start-up, before the pool takes the rest.
 // * The first call on each device looks up the array's address on that device (the calling
-//   thread's current device) and remembers it.  Make that first call outside any stream capture.
+//   thread's current device), raises the kernels' shared-memory limit there, and remembers both.
+//   Make that first call outside any stream capture.
 // * No cudaMalloc, cudaFree or allocating library routine is called, on any call.
 // * Every call uses the same array.  Nothing in it has to start at zero (each launch overwrites what
 //   it later reads), and it keeps whatever the previous call left.  Two calls that overlap on the

@@ -52,13 +52,20 @@ def test_static_scratch_entry_matches_ordinary_entry(batch, R, C):
         rc = lib.tyr_newton_schulz_bf16(ctypes.c_void_p(ref.data_ptr()), ctypes.c_void_p(scratch.data_ptr()),
                                         need, batch, R, C, 5, a, b, c, ctypes.c_void_p(err.data_ptr()), stream)
         assert rc == 0
+        torch.cuda.synchronize()
+        free_before, _ = torch.cuda.mem_get_info(dev)
+        reserved_before = torch.cuda.memory_reserved(dev)
         rc = lib.tyr_newton_schulz_bf16_static(ctypes.c_void_p(got.data_ptr()), batch, R, C, 5, a, b, c,
                                                ctypes.c_void_p(err.data_ptr()), stream)
         assert rc == 0
         torch.cuda.synchronize()
         raise_on_device_error(dev)
-        rel = ((got.float() - ref.float()).norm() / ref.float().norm()).item()
-        assert rel < 1e-2, (call, rel)
+        if call == 1:      # the first call on a device may load the module and resolve the array's address
+            free_after, _ = torch.cuda.mem_get_info(dev)
+            assert free_after == free_before and torch.cuda.memory_reserved(dev) == reserved_before, \
+                "the entry that must not allocate changed the device's free memory"
+        # both entries run the same launches on the same data: the results are identical bit for bit
+        assert torch.equal(got, ref), (call, ((got.float() - ref.float()).abs().max().item()))
         # and both are a real orthogonalisation of the input
         sv = torch.linalg.svdvals(got[0].float())
         assert sv.max() < 1.35 and sv.min() > 0.3

@@ -134,8 +134,9 @@ class FlagBarrier:
     def __init__(self, heap: SymmetricHeap, n_slots: int = 16):
         self.heap = heap
         self.n_slots = n_slots
+        # the heap was zero-filled before its handles were exchanged; zeroing again here would be an asynchronous fill that
+        # can run after a fast peer's first signal has already landed and erase it
         self.flags = heap.alloc((n_slots * heap.world_size,), torch.int64)
-        self.flags.zero_()
         self._off = heap.offset_bytes(self.flags)
         self._table = heap.peer_table_at(self._off)
 
