@@ -1,4 +1,6 @@
-"""Kernel micro-benchmarks: `python -m benchmarks.kernel_bench [gemm|attention|moe|moe-decode|decode-attn|skinny|qwen3-decode|all]`.
+"""Kernel micro-benchmarks: `python -m benchmarks.kernel_bench [gemm|attention|attention-bwd|moe|moe-decode|decode-attn|skinny|elementwise|ns|gdr|qwen3-decode|all]`
+(plus `*-small` cases sized for a profiler: gemm-fwd-small, attention-fwd-small, attention-bwd-small, elementwise-small,
+ns-small, fp4-small, gdr-small, decode-attn-small).
 
 Times the hand-written kernels with CUDA events (5 warm-up + 20 timed iterations, a 256 MB
 buffer written between iterations to flush the 126 MB L2) on the NanoChat d20 shapes and prints
@@ -300,6 +302,92 @@ def bench_qwen3_decode(results):
             os.environ["TYR_DECODE_GRAPH"] = saved
 
 
+def bench_elementwise(results, small=False):
+    """Bandwidth-bound kernels of the NanoChat and Flux steps at their production shapes (``small``: an eighth of the
+    rows, still larger than L2, few launches: the case to put under a profiler).  Achieved GB/s counts the algorithmic
+    bytes (every operand read once, every result written once) against the measured copy bandwidth of 6538 GB/s."""
+    from tyr_b200 import ops
+    from tyr_b200.ops import ce as CE
+    from tyr_b200.ops import modulate as MOD
+    dev = torch.device("cuda")
+    flush = None if small else torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    it = dict(iters=3, warmup=2) if small else dict()
+    N, d, H, D, T = (8192 if small else 65536), 1280, 10, 128, 2048
+    g = torch.Generator(device="cuda").manual_seed(0)
+    rnd = lambda *sh: torch.randn(*sh, device=dev, generator=g).bfloat16()
+
+    def row(name, ms, nbytes):
+        results.append({"kernel": name, "ms": ms, "gbs": nbytes / ms / 1e6, "fraction_of_copy_bw": nbytes / ms / 1e6 / 6538.0})
+        print(f"{name:34s} {ms:8.3f} ms  {nbytes / ms / 1e6:8.1f} GB/s  {nbytes / ms / 1e6 / 6538.0:5.2f} of measured copy bandwidth", flush=True)
+
+    # lincomb + RMSNorm, three inputs, forward and backward
+    xs = [rnd(N, d).requires_grad_(True) for _ in range(3)]
+    sc = torch.tensor([0.7, 0.3, 0.5], device=dev, requires_grad=True)
+    t = N * d * 2
+    row("lincomb_rmsnorm_fwd<3>", _time(lambda: ops.lincomb_rmsnorm(xs, sc), flush=flush, **it), 5 * t)
+    out, normed = ops.lincomb_rmsnorm(xs, sc)
+    go, gn = rnd(N, d), rnd(N, d)
+    row("lincomb_rmsnorm_bwd<3>", _time(lambda: torch.autograd.grad([out, normed], xs + [sc], [go, gn], retain_graph=True),
+                                        flush=flush, **it), 8 * t)
+    # RoPE + QK norm + value-embedding blend on the packed projection, forward and backward
+    qkv = rnd(N, 3 * H * D).requires_grad_(True)
+    ve = rnd(N, H * D).requires_grad_(True)
+    mix = torch.tensor(0.4, device=dev, requires_grad=True)
+    cos, sin = ops.rotary_freqs(T, D, 500000.0, device=dev)
+    q3 = N * 3 * H * D * 2
+    row("qkv_post_fwd", _time(lambda: ops.qkv_post(qkv, ve, mix, cos, sin, T, H, D), flush=flush, **it), 2 * q3 + q3 // 3)
+    y = ops.qkv_post(qkv, ve, mix, cos, sin, T, H, D)
+    gy = rnd(N, 3 * H * D)
+    row("qkv_post_bwd", _time(lambda: torch.autograd.grad(y, [qkv, ve, mix], gy, retain_graph=True), flush=flush, **it),
+        3 * q3 + 2 * (q3 // 3))
+    # soft-capped cross-entropy with the gradient written in place
+    rows_ce, V = (1024 if small else 8192), 65536
+    logits = rnd(rows_ce, V)
+    tg = torch.randint(0, V, (rows_ce,), device=dev, generator=g)
+    row("softcap_ce (fwd + grad in place)", _time(lambda: CE.softcap_ce_(logits, tg, 15.0), flush=flush, **it), 2 * rows_ce * V * 2)
+    # Flux modulation kernels
+    B, S, Df = (1 if small else 4), 4608, 3072
+    x = rnd(B, S, Df)
+    mod = rnd(B, 3 * Df)
+    xb = B * S * Df * 2
+    row("layernorm_modulate", _time(lambda: MOD.layernorm_modulate(x, mod[:, :Df], mod[:, Df:2 * Df]), flush=flush, **it), 2 * xb)
+    yv = rnd(B, S, Df)
+    row("gate_residual", _time(lambda: MOD.gate_residual(x, yv, mod[:, 2 * Df:]), flush=flush, **it), 3 * xb)
+
+
+def bench_ns(results, small=False):
+    """Newton-Schulz chain (5 iterations, 15 batched tcgen05 GEMMs with the scale / add terms in their epilogues) on the two
+    Muon shape classes of NanoChat d20; ``small``: 8 matrices, few launches, for a profiler."""
+    from tyr_b200.ops import polar
+    dev = torch.device("cuda")
+    flush = None if small else torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    it = dict(iters=3, warmup=2) if small else dict()
+    for name, (Bm, R, C) in (("attention matrices", (8 if small else 76, 1280, 1280)), ("MLP matrices", (4 if small else 40, 5120, 1280))):
+        x = torch.randn(Bm, R, C, device=dev)
+        x = (x / x.pow(2).sum((1, 2), keepdim=True).sqrt()).bfloat16().contiguous()
+        ms = _time(lambda: polar.newton_schulz_(x.clone(), 5), flush=flush, **it)
+        S = min(R, C)
+        flops = 5 * Bm * (2.0 * S * S * max(R, C) + 2.0 * S * S * S + 2.0 * S * S * max(R, C))
+        results.append({"kernel": "newton_schulz", "shape": f"{Bm}x[{R}x{C}]", "ms": ms, "tflops": flops / ms / 1e9})
+        print(f"newton_schulz {name:20s} {Bm}x[{R}x{C}]: {ms:8.3f} ms  {flops / ms / 1e9:7.1f} TF/s", flush=True)
+
+
+def bench_fp4_small(results):
+    """The block-scaled FP4 expert path on a case sized for a profiler: 2048 tokens, 64 experts top-8, hidden 2048, FFN 768."""
+    from tyr_b200.models import laguna as L
+    from tyr_b200.ops import moe
+    dev = torch.device("cuda")
+    cfg = L.LagunaConfig(hidden_size=2048, num_experts=64, num_experts_per_tok=8, moe_intermediate_size=768)
+    ex = L.random_packed_experts(cfg, dev, torch.Generator().manual_seed(0))
+    T = 2048
+    x = torch.randn(T, 2048, device=dev).bfloat16()
+    ids, w, cnt = moe.route(torch.randn(T, 64, device=dev), 8)
+    ms = _time(lambda: moe.moe_fp4_forward(x, ids, w, ex, counts=cnt, force_path="gemm"), iters=3, warmup=2)
+    flops = 6.0 * T * 8 * 2048 * 768
+    results.append({"kernel": "moe_fp4_tensor_core", "tokens": T, "ms": ms, "tflops": flops / ms / 1e9})
+    print(f"moe fp4 tensor-core path T={T}: {ms:.3f} ms {flops / ms / 1e9:.1f} TF/s", flush=True)
+
+
 def main(argv):
     what = argv[1] if len(argv) > 1 else "all"
     results = []
@@ -329,6 +417,16 @@ def main(argv):
         bench_decode_attention_small(results)
     if what in ("skinny", "all"):
         bench_skinny(results)
+    if what in ("elementwise", "all"):
+        bench_elementwise(results)
+    if what == "elementwise-small":
+        bench_elementwise(results, small=True)
+    if what in ("ns", "all"):
+        bench_ns(results)
+    if what == "ns-small":
+        bench_ns(results, small=True)
+    if what == "fp4-small":
+        bench_fp4_small(results)
     if what == "moe-decode":
         bench_moe(results, ((1, "gemv"), (64, "gemv")))
     print(json.dumps(results))

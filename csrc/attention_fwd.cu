@@ -17,8 +17,8 @@
 //
 // The two tiles ping-pong: while the softmax warps of one tile run exp2 on the SFUs, the tensor
 // core works on the other tile.  TMEM map (512 columns): S0 | S1 | O0 | O1, 128 columns each;
-// P_t overwrites the first 64 columns of S_t as packed bf16 (each half writes 32 of them, after both
-// halves have their scores in registers).
+// P_t overwrites S_t as packed bf16: each half of a row writes its 32 packed columns over the start of its own 64
+// score columns (columns 0..31 and 64..95 of the tile), which only it reads.
 // Online softmax uses a lazily updated running maximum: O is only rescaled (read-modify-write
 // of its TMEM tile) when some row's maximum grew by more than 2^8, which keeps the result exact
 // because the same stale maximum is used for the row sum.
@@ -247,7 +247,7 @@ flash_fwd_d128_kernel(const __grid_constant__ CUtensorMap tmQ,
 #pragma unroll
         for (int k = 0; k < ATT_BN / 16; ++k) {
           // A: 16 bf16 of P per lane = 8 TMEM columns; B: 16 key rows of V = 2 KB, d-chunks 16 KB apart
-          umma_f16_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + k * 8,
+          umma_f16_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + (k >> 2) * 64 + (k & 3) * 8,
                       make_smem_desc_sw128(va + k * 2048, kChunk, 1024), idesc_o,
                       (first && k == 0) ? 0u : 1u);
         }
@@ -305,7 +305,7 @@ flash_fwd_d128_kernel(const __grid_constant__ CUtensorMap tmQ,
     const int row = row0 + t * ATT_BM + lrow;
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t s_addr = tmem_base + t * 128 + h * 64 + lane_addr;     // my 64 score columns
-    const uint32_t p_addr = tmem_base + t * 128 + h * 32 + lane_addr;     // my 32 packed-probability columns
+    const uint32_t p_addr = tmem_base + t * 128 + h * 64 + lane_addr;     // my 32 packed-probability columns: the start of my own score columns
     const uint32_t o_addr = tmem_base + 256 + t * 128 + h * 64 + lane_addr;
     const bool tile_live = (t == 0) || tile1_live;
     float m_used = -INFINITY;   // running maximum the exponentials are taken against
@@ -316,41 +316,51 @@ flash_fwd_d128_kernel(const __grid_constant__ CUtensorMap tmQ,
       for (int j = lo[t]; j < hi[t] && ok; ++j, ++cnt) {
         if (!mbar_wait(&s.s_ready[t], cnt & 1, p.err, 700 + t)) { ok = false; break; }
         tc_fence_after();
-        uint32_t r[64];
-        tmem_ld_32x32_nowait(s_addr, r);
-        tmem_ld_32x32_nowait(s_addr + 32, r + 32);
-        tmem_wait_ld();
         const int col0 = j * ATT_BN + h * 64;
         // mask needed on boundary blocks only
         const int qi = row + p.q_offset;
         const bool need_mask = (j * ATT_BN + ATT_BN > p.Tk) || (p.causal && j * ATT_BN + ATT_BN - 1 > row0 + t * ATT_BM + p.q_offset) ||
                                (p.window > 0 && j * ATT_BN < row0 + t * ATT_BM + ATT_BM - 1 + p.q_offset - p.window + 1);
-        if (need_mask) {
+        auto masked = [&](uint32_t (&v)[32], int base) {
 #pragma unroll
-          for (int c = 0; c < 64; ++c) {
-            const int col = col0 + c;
+          for (int c = 0; c < 32; ++c) {
+            const int col = base + c;
             bool keep = col < p.Tk;
             if (p.causal) keep = keep && (col <= qi);
             if (p.window > 0) keep = keep && (col > qi - p.window);
-            if (!keep) r[c] = __float_as_uint(-INFINITY);
+            if (!keep) v[c] = __float_as_uint(-INFINITY);
           }
-        }
-        // row maximum of my half on the raw scores (the softmax scale is positive, so it commutes with max):
-        // three-input max, four independent chains
-        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        };
+        // Pass 1: row maximum of my 64 columns on the raw scores (the softmax scale is positive, so it commutes with
+        // max).  The scores are NOT kept: pass 2 reads them from TMEM again, 32 at a time, which costs one more TMEM load
+        // (about 100 cycles) and keeps the live registers far below the 96 the 640-thread launch allows (holding all 64
+        // scores spilled, and the maximum alone took 500 cycles per block).
+        float mx;
+        {
+          uint32_t r0[32], r1[32];
+          tmem_ld_32x32_nowait(s_addr, r0);
+          tmem_ld_32x32_nowait(s_addr + 32, r1);
+          tmem_wait_ld();
+          if (need_mask) {
+            masked(r0, col0);
+            masked(r1, col0 + 32);
+          }
+          float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-        for (int c = 0; c < 64; c += 8) {
+          for (int c = 0; c < 32; c += 8) {
 #pragma unroll
-          for (int u = 0; u < 4; ++u)
-            mx4[u] = max3(mx4[u], __uint_as_float(r[c + 2 * u]), __uint_as_float(r[c + 2 * u + 1]));
+            for (int u = 0; u < 4; ++u) {
+              mx4[u] = max3(mx4[u], __uint_as_float(r0[c + 2 * u]), __uint_as_float(r0[c + 2 * u + 1]));
+              mx4[u] = max3(mx4[u], __uint_as_float(r1[c + 2 * u]), __uint_as_float(r1[c + 2 * u + 1]));
+            }
+          }
+          mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
         }
-        float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
         float other;
         if (!pair_exchange(&s.xch[t][cnt & 1][h][lrow], &s.xch[t][cnt & 1][h ^ 1][lrow], mx, cnt + 1, other, p.err, 720 + t)) {
           ok = false;
           break;
         }
-        // both halves hold their scores in registers from here on: the packed probabilities may overwrite them
         mx = fmaxf(mx, other) * p.scale_log2;
         // lazy rescale: move the reference maximum only when it grew by more than 8 (log2 units); both halves of a row
         // take the same decision because they see the same maximum
@@ -361,7 +371,7 @@ flash_fwd_d128_kernel(const __grid_constant__ CUtensorMap tmQ,
           // O is idle here: S_j was queued behind PV_{j-1}, so its completion implies PV_{j-1}'s.
           const float f = want ? exp2f(m_used - m_new) : 1.f;
 #pragma unroll 1
-          for (int c = 0; c < 4; ++c) {          // 16 columns at a time: the 64 scores stay in registers meanwhile
+          for (int c = 0; c < 4; ++c) {
             uint32_t o[16];
             tmem_ld_32x16(o_addr + c * 16, o);
             tmem_wait_ld();
@@ -373,16 +383,22 @@ flash_fwd_d128_kernel(const __grid_constant__ CUtensorMap tmQ,
           if (want) l_sum *= f;
         }
         if (want) m_used = (m_new == -INFINITY) ? 0.f : m_new;
-        // probabilities exp2(s * scale - m) -> bf16 -> TMEM; the row sum is taken in fp32 over four chains
+        // Pass 2: probabilities exp2(s * scale - m) -> bf16 -> TMEM, 32 scores at a time.  My packed probabilities go to
+        // the first 32 columns of MY OWN 64 score columns (chunk c lands on columns 16 c .. 16 c + 15, which chunk c
+        // itself or an earlier chunk was read from), so neither half ever writes where the other half still reads.
         float ls4[4] = {0.f, 0.f, 0.f, 0.f};
         const float neg_m = -m_used;
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(s_addr + c * 32, r);
+          tmem_wait_ld();
+          if (need_mask) masked(r, col0 + c * 32);
           uint32_t pk[16];
 #pragma unroll
           for (int q = 0; q < 16; ++q) {
-            const float p0 = exp2f(fmaf(__uint_as_float(r[c * 32 + 2 * q]), p.scale_log2, neg_m));
-            const float p1 = exp2f(fmaf(__uint_as_float(r[c * 32 + 2 * q + 1]), p.scale_log2, neg_m));
+            const float p0 = exp2f(fmaf(__uint_as_float(r[2 * q]), p.scale_log2, neg_m));
+            const float p1 = exp2f(fmaf(__uint_as_float(r[2 * q + 1]), p.scale_log2, neg_m));
             pk[q] = pack_bf16x2(p0, p1);
             ls4[q & 3] += p0 + p1;
           }

@@ -286,6 +286,26 @@ def test_rmsnorm_weighted_and_rope_norm():
     assert _rel_err(yy.cpu(), yy_ref) < 1e-2
 
 
+def test_embedding_grad_sorted_matches_index_add():
+    """Zipf-like tokens (a few ids own most rows), row strides of a packed buffer, ids at both ends of the table."""
+    from tyr_b200.ops import embed
+    g = torch.Generator(device="cuda").manual_seed(4)
+    N, d, V = 5000, 256, 1000
+    idx = (torch.rand(N, device=_dev(), generator=g) ** 6 * V).long().clamp(0, V - 1)
+    idx[:3] = torch.tensor([0, V - 1, V - 1], device=_dev())
+    big = torch.randn(N, 3 * d, device=_dev(), generator=g).bfloat16()
+    dy = big[:, d:2 * d]                                   # strided rows
+    table = torch.randn(V, d, device=_dev(), generator=g)
+    want = table.clone().index_add_(0, idx, dy.float())
+    got = table.clone()
+    embed.embedding_grad_(got, dy, idx)
+    torch.cuda.synchronize()
+    assert (got - want).abs().max().item() < 1e-3 * max(1.0, want.abs().max().item())
+    untouched = torch.ones(V, dtype=torch.bool, device=_dev())
+    untouched[idx] = False
+    assert torch.equal(got[untouched], table[untouched])
+
+
 def test_nanochat_step_graph_matches_eager_steps():
     """Forward + backward replayed from a CUDA graph (after two eager steps) trains like the eager step: same losses and
     parameters over six steps on changing batches, up to the fp32 summation order of the split-K weight gradients."""

@@ -39,6 +39,7 @@ def parse(argv):
     p.add_argument("--random-init", action="store_true")
     p.add_argument("--bench", action="store_true")
     p.add_argument("--batch", type=int, default=1)
+    p.add_argument("--kernel-shares", action="store_true", help="with --bench: kernel time shares of one denoising step")
     p.add_argument("--txt-len", type=int, default=MAX_SEQ)
     return p.parse_args(argv)
 
@@ -82,16 +83,33 @@ def main(argv=None) -> int:
     noise = torch.randn((a.batch, 128, a.latent_h, a.latent_w), generator=gen).permute(0, 2, 3, 1).reshape(a.batch, -1, 128)
     noise = noise.to(device=dev, dtype=dtype)
     if a.bench:
-        FX.denoise(model, noise, txt, img_ids, txt_ids, 1)
-        if dev.type == "cuda":
-            torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        FX.denoise(model, noise, txt, img_ids, txt_ids, a.steps)
-        if dev.type == "cuda":
-            torch.cuda.synchronize()
-        dt = time.perf_counter() - t0
+        for _ in range(3):                                   # warm-up: module loading, workspaces, clocks
+            FX.denoise(model, noise, txt, img_ids, txt_ids, 1)
         toks = a.batch * (noise.shape[1] + a.txt_len)
-        print(f"BENCH steps={a.steps} ms_per_step={dt / a.steps * 1e3:.2f} it_s={a.steps / dt:.3f} tokens_per_step={toks}")
+        if dev.type == "cuda":
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            FX.denoise(model, noise, txt, img_ids, txt_ids, a.steps)
+            e1.record()
+            torch.cuda.synchronize()
+            dt = e0.elapsed_time(e1) / 1e3                   # device time of the whole sampling run
+        else:
+            t0 = time.perf_counter()
+            FX.denoise(model, noise, txt, img_ids, txt_ids, a.steps)
+            dt = time.perf_counter() - t0
+        print(f"BENCH steps={a.steps} batch={a.batch} ms_per_step={dt / a.steps * 1e3:.2f} it_s={a.steps / dt:.3f} "
+              f"tokens_per_step={toks} images_per_s={a.batch / dt:.3f}")
+        if a.kernel_shares and dev.type == "cuda":
+            from torch.profiler import ProfilerActivity, profile
+            with profile(activities=[ProfilerActivity.CUDA]) as prof:
+                FX.denoise(model, noise, txt, img_ids, txt_ids, 1)
+                torch.cuda.synchronize()
+            rows = sorted(((e.device_time_total, e.count, e.key) for e in prof.key_averages() if e.device_time_total > 0), reverse=True)
+            total = sum(r[0] for r in rows)
+            print(f"kernel time of one denoising step: {total / 1e3:.2f} ms in {sum(r[1] for r in rows)} launches")
+            for t_us, n, k in rows[:14]:
+                print(f"  {t_us / 1e3:8.3f} ms  {100 * t_us / total:5.1f} %  x{n:<4d} {k[:100]}")
         return 0
     print("  [3/4] Running Flux denoising...", flush=True)
     latents = FX.denoise(model, noise, txt, img_ids, txt_ids, a.steps)

@@ -295,28 +295,32 @@ class ModdedGPTParams:
 # --------------------------------------------------------------------------------------------
 class _EmbeddingFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, table, idx):
-        ctx.save_for_backward(idx)
+    def forward(ctx, table, idx, sorted_ids, order):
+        ctx.save_for_backward(idx, sorted_ids, order)
         ctx.table = table
         return F.embedding(idx, table)
 
     @staticmethod
     def backward(ctx, dy):
-        (idx,) = ctx.saved_tensors
+        idx, sorted_ids, order = ctx.saved_tensors
         table = ctx.table
         mg = getattr(table, "main_grad", None)
         flat = dy.reshape(-1, dy.shape[-1])
         if mg is not None:
-            mg.index_add_(0, idx.reshape(-1), flat.to(mg.dtype))
+            # rows sorted by token id, one table update per id and run of rows instead of one atomic per occurrence
+            ops.embed.embedding_grad_(mg, flat, idx, sorted_ids, order)
             table.grad_ready = True
-            return None, None
+            return None, None, None, None
         g = torch.zeros(table.shape, dtype=torch.float32, device=table.device)
         g.index_add_(0, idx.reshape(-1), flat.float())
-        return g.to(table.dtype), None
+        return g.to(table.dtype), None, None, None
 
 
-def embedding(table: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
-    return _EmbeddingFn.apply(table, idx)
+def embedding(table: torch.Tensor, idx: torch.Tensor, sorted_ids=None, order=None) -> torch.Tensor:
+    """``sorted_ids`` / ``order``: the result of ``ops.embed.sort_tokens(idx)`` when several tables share the tokens."""
+    if sorted_ids is None and idx.is_cuda:
+        sorted_ids, order = ops.embed.sort_tokens(idx)
+    return _EmbeddingFn.apply(table, idx, sorted_ids, order)
 
 
 # --------------------------------------------------------------------------------------------
@@ -386,12 +390,13 @@ def loss_fused(params: ModdedGPTParams, input_seq: torch.Tensor, targets: torch.
     one = torch.ones((), dtype=torch.float32, device=dev)
 
     # token embedding + smear gate + norm
-    tok = embedding(params.leaf("embed"), idx)                              # [N, d]
+    sorted_ids, order = ops.embed.sort_tokens(idx) if idx.is_cuda else (None, None)   # shared by the four tables' gradients
+    tok = embedding(params.leaf("embed"), idx, sorted_ids, order)           # [N, d]
     gate = torch.sigmoid(F.linear(tok[:, :12].float(), params.leaf("smearGate.weight").float()))
     x0_pre = (tok.float() * (1.0 + gate)).to(dt)
     _, x0 = ops.lincomb_rmsnorm([x0_pre], None)
 
-    ve = [embedding(params.leaf(f"valueEmbeds.{i}"), idx) for i in range(cfg.num_value_embeds)]
+    ve = [embedding(params.leaf(f"valueEmbeds.{i}"), idx, sorted_ids, order) for i in range(cfg.num_value_embeds)]
     value_mix = sig[L * 4]
     skip_mix = sig[L * 4 + 1]
     final_scale = sig[L * 4 + 2]
