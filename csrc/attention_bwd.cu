@@ -9,12 +9,18 @@
 //   S^T  = K Q_i^T                 (SS)      TMEM columns   0..127
 //   dP^T = V dO_i^T                (SS)      TMEM columns 256..383
 //   P^T  = exp2(S^T * c - lse_i)             bf16, packed over the S^T columns it came from
-//   dS^T = P^T o (dP^T - delta_i)            bf16 -> shared memory, [keys][query rows], 128B swizzle, K-major A of dK
+//   dS^T = P^T o (dP^T - delta_i)            bf16, packed over the dP^T columns it came from
 //   dV  += P^T dO_i                (TS)      TMEM columns 128..255
-//   dK  += dS^T Q_i                (SS)      TMEM columns 384..511
+//   dK  += dS^T Q_i                (TS)      TMEM columns 384..511
+//
+// Both A operands that the score warps produce stay in TMEM, so shared memory holds only what TMA brings: K_j, V_j, a
+// 3-stage ring of Q_i (with the rows' lse and delta) and a 2-stage ring of dO_i.  Q_i lives from S^T to dK (almost two
+// iterations) and dO_i from dP^T to dV (one); with one stage more than each tile's lifetime the next tile's load is issued
+// a whole iteration before its first product, which hides the TMA latency (with two 64 KB stages it was exposed every
+// iteration: the tensor pipe idled about 1500 cycles of 3800).
 //
 // dQ comes from a second kernel with the loops the other way round (one CTA per 128-row query block, walking the key
-// blocks): S = Q_i K_j^T and dP = dO_i V_j^T are recomputed, dS goes to shared memory and dQ_i += dS K_j accumulates in
+// blocks): S = Q_i K_j^T and dP = dO_i V_j^T are recomputed, dS is packed over dP in TMEM and dQ_i += dS K_j accumulates in
 // TMEM, so no partial dQ tile ever leaves the SM.  Seven products per (query block, key block) pair instead of five, but
 // the first version, which reduced the dQ tiles of all key blocks into an fp32 accumulator with vector atomics, was bound by
 // the L2 atomic rate (about 1.5 TB/s) at less than a quarter of the tensor throughput.  A small kernel before the two computes
@@ -53,19 +59,24 @@ struct BwdParams {
   int* err;
 };
 
+constexpr int BW_QST = 3;    // stages of the Q ring (dK/dV kernel) and of the K ring (dQ kernel)
+
 struct __align__(1024) BwdSmem {
   uint8_t k[BW_TILE];
   uint8_t v[BW_TILE];
-  uint8_t q[2][BW_TILE];
+  uint8_t q[BW_QST][BW_TILE];
   uint8_t dout[2][BW_TILE];
-  uint8_t ds[BW_TILE];
-  float lse[2][BW_T];
-  float delta[2][BW_T];
+  float lse[BW_QST][BW_T];       // travels with Q_i: the stage is released after dK, long after the exponentials read it
+  float delta[2][BW_T];          // a ring of its own, released by the score warps (dO_i's stage is free again before they
+                                 // read delta_i, and a third stage next to Q_i's would not fit in 227 KB)
   uint64_t kv_full;
-  uint64_t q_full[2];      // Q_i + lse_i
-  uint64_t do_full[2];     // dO_i + delta_i
-  uint64_t qdo_empty[2];
-  uint64_t s_ready, dp_ready, p_ready, ds_ready, ds_free, acc_done;
+  uint64_t q_full[BW_QST];       // Q_i + lse_i
+  uint64_t q_empty[BW_QST];
+  uint64_t do_full[2];
+  uint64_t do_empty[2];
+  uint64_t delta_full[2];
+  uint64_t delta_empty[2];       // one arrival per score warp
+  uint64_t s_ready, dp_ready, p_ready, ds_ready, acc_done;
   uint32_t tmem_base;
 };
 
@@ -114,16 +125,20 @@ flash_bwd_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 
   if (threadIdx.x == 0) {
     mbar_init(&s.kv_full, 1);
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < BW_QST; ++i) {
       mbar_init(&s.q_full[i], 1);
+      mbar_init(&s.q_empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
       mbar_init(&s.do_full[i], 1);
-      mbar_init(&s.qdo_empty[i], 1);
+      mbar_init(&s.do_empty[i], 1);
+      mbar_init(&s.delta_full[i], 1);
+      mbar_init(&s.delta_empty[i], 16);
     }
     mbar_init(&s.s_ready, 1);
     mbar_init(&s.dp_ready, 1);
     mbar_init(&s.p_ready, 16);      // one arrival per score warp (512 single-thread arrivals on one barrier serialise)
     mbar_init(&s.ds_ready, 16);
-    mbar_init(&s.ds_free, 1);
     mbar_init(&s.acc_done, 1);
     mbar_fence_init();
   }
@@ -152,29 +167,35 @@ flash_bwd_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           tma_load_4d(s.v + c * BW_CHUNK, &tmV, &s.kv_full, c * 64, kvh, j * BW_T, batch);
         }
         bool ok = true;
-        int it = 0;
+        int it = 0, qs = 0, n_do = 0, n_dl = 0;
+        uint32_t qph = 0;
         for (; it < n_it; ++it) {
-          const int st = it & 1;
-          const uint32_t ph = (it >> 1) & 1;
+          const int ds_ = it & 1;
+          const uint32_t dph = (it >> 1) & 1;
           const int head = kvh * G + it / ni;
           const int i = ilo + it % ni;
-          if (!mbar_wait(&s.qdo_empty[st], ph ^ 1, p.err, 810 + st)) { ok = false; break; }
+          if (!mbar_wait(&s.q_empty[qs], qph ^ 1, p.err, 810 + qs)) { ok = false; break; }
           const long long stat = (static_cast<long long>(batch) * p.Hq + head) * p.Tpad + i * BW_T;
-          mbar_expect_tx(&s.q_full[st], BW_TILE + BW_T * 4);
+          mbar_expect_tx(&s.q_full[qs], BW_TILE + BW_T * 4);
           for (int c = 0; c < 2; ++c)
-            tma_load_4d(s.q[st] + c * BW_CHUNK, &tmQ, &s.q_full[st], c * 64, head, i * BW_T, batch);
-          bulk_load_1d(s.lse[st], p.lse2 + stat, BW_T * 4, &s.q_full[st]);
-          mbar_expect_tx(&s.do_full[st], BW_TILE + BW_T * 4);
+            tma_load_4d(s.q[qs] + c * BW_CHUNK, &tmQ, &s.q_full[qs], c * 64, head, i * BW_T, batch);
+          bulk_load_1d(s.lse[qs], p.lse2 + stat, BW_T * 4, &s.q_full[qs]);
+          if (!mbar_wait(&s.do_empty[ds_], dph ^ 1, p.err, 814 + ds_)) { ++it; ok = false; break; }
+          mbar_expect_tx(&s.do_full[ds_], BW_TILE);
           for (int c = 0; c < 2; ++c)
-            tma_load_4d(s.dout[st] + c * BW_CHUNK, &tmDO, &s.do_full[st], c * 64, head, i * BW_T, batch);
-          bulk_load_1d(s.delta[st], p.delta + stat, BW_T * 4, &s.do_full[st]);
+            tma_load_4d(s.dout[ds_] + c * BW_CHUNK, &tmDO, &s.do_full[ds_], c * 64, head, i * BW_T, batch);
+          ++n_do;
+          if (!mbar_wait(&s.delta_empty[ds_], dph ^ 1, p.err, 816 + ds_)) { ++it; ok = false; break; }
+          mbar_expect_tx(&s.delta_full[ds_], BW_T * 4);
+          bulk_load_1d(s.delta[ds_], p.delta + stat, BW_T * 4, &s.delta_full[ds_]);
+          ++n_dl;
+          if (++qs == BW_QST) { qs = 0; qph ^= 1; }
         }
-        if (!ok) {   // let the copies in flight land before the CTA unwinds
+        if (!ok) {   // let the copies in flight land before the CTA unwinds (a Q tile whose dO was not issued included)
           mbar_wait(&s.kv_full, 0, nullptr, 0);
-          for (int q = max(0, it - 2); q < it; ++q) {
-            mbar_wait(&s.q_full[q & 1], (q >> 1) & 1, nullptr, 0);
-            mbar_wait(&s.do_full[q & 1], (q >> 1) & 1, nullptr, 0);
-          }
+          for (int q = max(0, it - BW_QST); q < it; ++q) mbar_wait(&s.q_full[q % BW_QST], (q / BW_QST) & 1, nullptr, 0);
+          for (int q = max(0, n_do - 2); q < n_do; ++q) mbar_wait(&s.do_full[q & 1], (q >> 1) & 1, nullptr, 0);
+          for (int q = max(0, n_dl - 2); q < n_dl; ++q) mbar_wait(&s.delta_full[q & 1], (q >> 1) & 1, nullptr, 0);
         }
       }
     } else if (warp == 16) {
@@ -182,7 +203,7 @@ flash_bwd_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       if (elect_one() && n_it > 0) {
         constexpr uint32_t idesc_kk = make_idesc_f16(1, BW_T, BW_T, 0, 0);   // both operands K-major
         constexpr uint32_t idesc_kn = make_idesc_f16(1, BW_T, BW_T, 0, 1);   // B MN-major
-        const uint32_t ka = smem_u32(s.k), va = smem_u32(s.v), dsa = smem_u32(s.ds);
+        const uint32_t ka = smem_u32(s.k), va = smem_u32(s.v);
         // D = A[128 x 128, K-major] * B[128 x 128, K-major]^T
         auto mma_kk = [&](uint32_t d_col, uint32_t a, uint32_t b) {
 #pragma unroll
@@ -191,6 +212,14 @@ flash_bwd_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             umma_f16_ss(tmem_base + d_col, make_smem_desc_sw128(a + off, 16, 1024),
                         make_smem_desc_sw128(b + off, 16, 1024), idesc_kk, k > 0 ? 1u : 0u);
           }
+        };
+        // D += A^T-in-TMEM [128 keys x 128 rows] * B[rows][d] (MN-major).  A: 16 bf16 per K step = 8 columns; the four score
+        // warpgroups packed their quarters over the first 16 of their own 32 columns (0, 32, 64, 96).
+        auto mma_ts = [&](uint32_t d_col, uint32_t a_col, uint32_t b, bool first) {
+#pragma unroll
+          for (int k = 0; k < BW_T / 16; ++k)
+            umma_f16_ts(tmem_base + d_col, tmem_base + a_col + (k >> 1) * 32 + (k & 1) * 8,
+                        make_smem_desc_sw128(b + k * 2048, BW_CHUNK, 1024), idesc_kn, (first && k == 0) ? 0u : 1u);
         };
         bool ok = mbar_wait(&s.kv_full, 0, p.err, 820);
         ok = ok && mbar_wait(&s.q_full[0], 0, p.err, 821);
@@ -205,43 +234,40 @@ flash_bwd_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           mma_kk(COL_DP, va, smem_u32(s.dout[0]));
           umma_commit(&s.dp_ready);
         }
+        int qs = 0;            // ring stage of Q_it
+        uint32_t qph = 0;
         for (int it = 0; it < n_it && ok; ++it) {
-          const int st = it & 1;
+          const int dst = it & 1;
           const uint32_t par = it & 1;
-          const uint32_t qa = smem_u32(s.q[st]), doa = smem_u32(s.dout[st]);
-          // dV += P^T dO_i : A from TMEM (16 bf16 per K step = 8 columns; the four score warpgroups
-          // packed their quarters at columns 0, 32, 64 and 96), B = dO_i [rows][d] MN-major
+          int qn = qs + 1;     // ring stage and parity of Q_{it+1}
+          uint32_t qnph = qph;
+          if (qn == BW_QST) { qn = 0; qnph ^= 1; }
+          // dV += P^T dO_i
           if (!mbar_wait(&s.p_ready, par, p.err, 830)) { ok = false; break; }
           tc_fence_after();
-#pragma unroll
-          for (int k = 0; k < BW_T / 16; ++k)
-            umma_f16_ts(tmem_base + COL_DV, tmem_base + COL_S + (k >> 1) * 32 + (k & 1) * 8,
-                        make_smem_desc_sw128(doa + k * 2048, BW_CHUNK, 1024), idesc_kn,
-                        (it == 0 && k == 0) ? 0u : 1u);
+          mma_ts(COL_DV, COL_S, smem_u32(s.dout[dst]), it == 0);
+          umma_commit(&s.do_empty[dst]);
+          // S^T of the next block over the P^T that dV has just consumed
           if (it + 1 < n_it) {
-            const int sn = (it + 1) & 1;
-            if (!mbar_wait(&s.q_full[sn], ((it + 1) >> 1) & 1, p.err, 831)) { ok = false; break; }
+            if (!mbar_wait(&s.q_full[qn], qnph, p.err, 831)) { ok = false; break; }
             tc_fence_after();
-            mma_kk(COL_S, ka, smem_u32(s.q[sn]));
+            mma_kk(COL_S, ka, smem_u32(s.q[qn]));
             umma_commit(&s.s_ready);
           }
+          // dK += dS^T Q_i, then dP^T of the next block over the dS^T that dK has just consumed
           if (!mbar_wait(&s.ds_ready, par, p.err, 832)) { ok = false; break; }
           tc_fence_after();
-          // dP^T of the next block first (the score warps are done with this one), then
-          // dK += dS^T Q_i : A = dS^T [keys][rows] K-major, B = Q_i [rows][d] MN-major
+          mma_ts(COL_DK, COL_DP, smem_u32(s.q[qs]), it == 0);
+          umma_commit(&s.q_empty[qs]);
           if (it + 1 < n_it) {
-            const int sn = (it + 1) & 1;
-            if (!mbar_wait(&s.do_full[sn], ((it + 1) >> 1) & 1, p.err, 833)) { ok = false; break; }
+            const int dn = (it + 1) & 1;
+            if (!mbar_wait(&s.do_full[dn], ((it + 1) >> 1) & 1, p.err, 833)) { ok = false; break; }
             tc_fence_after();
-            mma_kk(COL_DP, va, smem_u32(s.dout[sn]));
+            mma_kk(COL_DP, va, smem_u32(s.dout[dn]));
             umma_commit(&s.dp_ready);
           }
-#pragma unroll
-          for (int k = 0; k < BW_T / 16; ++k)
-            umma_f16_ss(tmem_base + COL_DK, make_smem_desc_sw128(dsa + (k >> 2) * BW_CHUNK + (k & 3) * 32, 16, 1024),
-                        make_smem_desc_sw128(qa + k * 2048, BW_CHUNK, 1024), idesc_kn, (it == 0 && k == 0) ? 0u : 1u);
-          umma_commit(&s.ds_free);
-          umma_commit(&s.qdo_empty[st]);
+          qs = qn;
+          qph = qnph;
         }
         if (ok) umma_commit(&s.acc_done);
       }
@@ -258,11 +284,10 @@ flash_bwd_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     const int rmin = p.causal ? key - p.q_offset : INT_MIN;                 // rows that see this key: [rmin, rmax)
     const int rmax = p.window > 0 ? key - p.q_offset + p.window : INT_MAX;
     const bool key_ok = key < p.Tk;
-    uint8_t* ds_row = s.ds + (wg >> 1) * BW_CHUNK + r * 128;
     bool ok = true;
+    int st = 0;              // ring stage of Q_it (and of its lse row)
+    uint32_t ph = 0;
     for (int it = 0; it < n_it && ok; ++it) {
-      const int st = it & 1;
-      const uint32_t ph = (it >> 1) & 1;
       const int i = ilo + it % ni;
       const int row0 = i * BW_T + wg * 32;               // first query row of this thread's columns
       if (!mbar_wait(&s.q_full[st], ph, p.err, 850)) { ok = false; break; }
@@ -311,32 +336,35 @@ flash_bwd_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s.p_ready);
-      if (!mbar_wait(&s.do_full[st], ph, p.err, 852)) { ok = false; break; }
+      // dP^T_it was queued behind dK of the previous block, so its completion also says that the dS^T columns are free
+      if (!mbar_wait(&s.delta_full[it & 1], (it >> 1) & 1, p.err, 852)) { ok = false; break; }
       if (!mbar_wait(&s.dp_ready, it & 1, p.err, 853)) { ok = false; break; }
-      if (it > 0 && !mbar_wait(&s.ds_free, (it - 1) & 1, p.err, 854)) { ok = false; break; }   // dK of the previous block has read dS
       tc_fence_after();
-      const float4* d4 = reinterpret_cast<const float4*>(&s.delta[st][wg * 32]);
+      const float4* d4 = reinterpret_cast<const float4*>(&s.delta[it & 1][wg * 32]);
       {
         uint32_t t[32];
         tmem_ld_32x32(dp_addr, t);
         tmem_wait_ld();
+        uint32_t pk[16];
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
           const float4 da = d4[u * 2], db = d4[u * 2 + 1];
           const float* pp = pr + u * 8;
-          uint4 w;
-          w.x = pack_bf16x2(pp[0] * (__uint_as_float(t[u * 8 + 0]) - da.x), pp[1] * (__uint_as_float(t[u * 8 + 1]) - da.y));
-          w.y = pack_bf16x2(pp[2] * (__uint_as_float(t[u * 8 + 2]) - da.z), pp[3] * (__uint_as_float(t[u * 8 + 3]) - da.w));
-          w.z = pack_bf16x2(pp[4] * (__uint_as_float(t[u * 8 + 4]) - db.x), pp[5] * (__uint_as_float(t[u * 8 + 5]) - db.y));
-          w.w = pack_bf16x2(pp[6] * (__uint_as_float(t[u * 8 + 6]) - db.z), pp[7] * (__uint_as_float(t[u * 8 + 7]) - db.w));
-          const int unit = (wg & 1) * 4 + u;
-          *reinterpret_cast<uint4*>(ds_row + ((unit ^ (r & 7)) << 4)) = w;
+          pk[u * 4 + 0] = pack_bf16x2(pp[0] * (__uint_as_float(t[u * 8 + 0]) - da.x), pp[1] * (__uint_as_float(t[u * 8 + 1]) - da.y));
+          pk[u * 4 + 1] = pack_bf16x2(pp[2] * (__uint_as_float(t[u * 8 + 2]) - da.z), pp[3] * (__uint_as_float(t[u * 8 + 3]) - da.w));
+          pk[u * 4 + 2] = pack_bf16x2(pp[4] * (__uint_as_float(t[u * 8 + 4]) - db.x), pp[5] * (__uint_as_float(t[u * 8 + 5]) - db.y));
+          pk[u * 4 + 3] = pack_bf16x2(pp[6] * (__uint_as_float(t[u * 8 + 6]) - db.z), pp[7] * (__uint_as_float(t[u * 8 + 7]) - db.w));
         }
+        tmem_st_32x16(dp_addr, pk);     // dS^T over the first 16 of this warpgroup's own 32 dP^T columns
       }
-      fence_proxy_async();
+      tmem_wait_st();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&s.ds_ready);
+      if (++st == BW_QST) { st = 0; ph ^= 1; }
+      if (lane == 0) {
+        mbar_arrive(&s.ds_ready);
+        mbar_arrive(&s.delta_empty[it & 1]);
+      }
     }
     // ---------------------------------------------------------------- dK / dV epilogue
     if (ok && n_it > 0) ok = mbar_wait(&s.acc_done, 0, p.err, 860);
@@ -416,21 +444,22 @@ flash_bwd_prepare_kernel(const __nv_bfloat16* __restrict__ dO, const __nv_bfloat
 }
 
 // ------------------------------------------------------------------------------------------------------------------
-// dQ: one CTA per 128-row query block of one (batch, head).  Q_i and dO_i stay in shared memory, K_j / V_j stream through a
-// 2-stage ring; per key block:  S = Q_i K_j^T (TMEM columns 0..127), dP = dO_i V_j^T (128..255), the score warps turn them
-// into dS = P o (dP - delta) in shared memory ([rows][keys], K-major A), and dQ_i += dS K_j accumulates at columns 256..383.
+// dQ: one CTA per 128-row query block of one (batch, head).  Q_i and dO_i stay in shared memory, K_j streams through a
+// 3-stage ring (it lives from S, computed two blocks ahead, to dQ) and V_j through a 2-stage ring (dP only); per key block:
+// S = Q_i K_j^T (TMEM columns 0..127 or 384..511), dP = dO_i V_j^T (128..255), the score warps turn them into
+// dS = P o (dP - delta) packed as bf16 over the dP columns (the A operand of the next product, read from TMEM), and
+// dQ_i += dS K_j accumulates at columns 256..383.
 //   warps 0-15  scores: four warpgroups of 32 key columns each (one thread per query row / TMEM lane)
 //   warp 16     MMA issuer, warp 17 TMA producer
 // ------------------------------------------------------------------------------------------------------------------
 struct __align__(1024) DqSmem {
   uint8_t q[BW_TILE];
   uint8_t dout[BW_TILE];
-  uint8_t k[2][BW_TILE];
+  uint8_t k[BW_QST][BW_TILE];
   uint8_t v[2][BW_TILE];
-  uint8_t ds[BW_TILE];
   uint64_t qdo_full;
-  uint64_t k_full[2], v_full[2], kv_empty[2];
-  uint64_t s_ready[2], s_free[2], dp_ready, ds_ready, ds_free, acc_done;
+  uint64_t k_full[BW_QST], k_empty[BW_QST], v_full[2], v_empty[2];
+  uint64_t s_ready[2], s_free[2], dp_ready, ds_ready, acc_done;
   uint32_t tmem_base;
 };
 static_assert(sizeof(DqSmem) <= 227 * 1024, "dQ tiles exceed the shared memory of one CTA");
@@ -467,10 +496,13 @@ flash_bwd_dq_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
 
   if (threadIdx.x == 0) {
     mbar_init(&s.qdo_full, 1);
-    for (int q = 0; q < 2; ++q) {
+    for (int q = 0; q < BW_QST; ++q) {
       mbar_init(&s.k_full[q], 1);
+      mbar_init(&s.k_empty[q], 1);
+    }
+    for (int q = 0; q < 2; ++q) {
       mbar_init(&s.v_full[q], 1);
-      mbar_init(&s.kv_empty[q], 1);
+      mbar_init(&s.v_empty[q], 1);
     }
     mbar_init(&s.s_ready[0], 1);
     mbar_init(&s.s_ready[1], 1);
@@ -478,7 +510,6 @@ flash_bwd_dq_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
     mbar_init(&s.s_free[1], 16);
     mbar_init(&s.dp_ready, 1);
     mbar_init(&s.ds_ready, 16);
-    mbar_init(&s.ds_free, 1);
     mbar_init(&s.acc_done, 1);
     mbar_fence_init();
   }
@@ -507,24 +538,26 @@ flash_bwd_dq_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
         tma_load_4d(s.dout + c * BW_CHUNK, &tmDO, &s.qdo_full, c * 64, head, i * BW_T, batch);
       }
       bool ok = true;
-      int it = 0;
+      int it = 0, ks = 0, n_v = 0;
+      uint32_t kph = 0;
       for (; it < n_it; ++it) {
-        const int st = it & 1;
-        const uint32_t ph = (it >> 1) & 1;
-        if (!mbar_wait(&s.kv_empty[st], ph ^ 1, p.err, 910 + st)) { ok = false; break; }
-        mbar_expect_tx(&s.k_full[st], BW_TILE);
+        const int vs = it & 1;
+        const uint32_t vph = (it >> 1) & 1;
+        if (!mbar_wait(&s.k_empty[ks], kph ^ 1, p.err, 910 + ks)) { ok = false; break; }
+        mbar_expect_tx(&s.k_full[ks], BW_TILE);
         for (int c = 0; c < 2; ++c)
-          tma_load_4d(s.k[st] + c * BW_CHUNK, &tmK, &s.k_full[st], c * 64, kvh, (jlo + it) * BW_T, batch);
-        mbar_expect_tx(&s.v_full[st], BW_TILE);
+          tma_load_4d(s.k[ks] + c * BW_CHUNK, &tmK, &s.k_full[ks], c * 64, kvh, (jlo + it) * BW_T, batch);
+        if (++ks == BW_QST) { ks = 0; kph ^= 1; }
+        if (!mbar_wait(&s.v_empty[vs], vph ^ 1, p.err, 914 + vs)) { ++it; ok = false; break; }
+        mbar_expect_tx(&s.v_full[vs], BW_TILE);
         for (int c = 0; c < 2; ++c)
-          tma_load_4d(s.v[st] + c * BW_CHUNK, &tmV, &s.v_full[st], c * 64, kvh, (jlo + it) * BW_T, batch);
+          tma_load_4d(s.v[vs] + c * BW_CHUNK, &tmV, &s.v_full[vs], c * 64, kvh, (jlo + it) * BW_T, batch);
+        ++n_v;
       }
       if (!ok) {   // let the copies in flight land before the CTA unwinds
         mbar_wait(&s.qdo_full, 0, nullptr, 0);
-        for (int q = max(0, it - 2); q < it; ++q) {
-          mbar_wait(&s.k_full[q & 1], (q >> 1) & 1, nullptr, 0);
-          mbar_wait(&s.v_full[q & 1], (q >> 1) & 1, nullptr, 0);
-        }
+        for (int q = max(0, it - BW_QST); q < it; ++q) mbar_wait(&s.k_full[q % BW_QST], (q / BW_QST) & 1, nullptr, 0);
+        for (int q = max(0, n_v - 2); q < n_v; ++q) mbar_wait(&s.v_full[q & 1], (q >> 1) & 1, nullptr, 0);
       }
     }
   } else if (warp == 16) {
@@ -532,7 +565,7 @@ flash_bwd_dq_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
     if (elect_one() && n_it > 0) {
       constexpr uint32_t idesc_kk = make_idesc_f16(1, BW_T, BW_T, 0, 0);
       constexpr uint32_t idesc_kn = make_idesc_f16(1, BW_T, BW_T, 0, 1);
-      const uint32_t qa = smem_u32(s.q), doa = smem_u32(s.dout), dsa = smem_u32(s.ds);
+      const uint32_t qa = smem_u32(s.q), doa = smem_u32(s.dout);
       auto mma_kk = [&](uint32_t d_col, uint32_t a, uint32_t b) {
 #pragma unroll
         for (int k = 0; k < BW_T / 16; ++k) {
@@ -553,8 +586,9 @@ flash_bwd_dq_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
         tc_fence_after();
         mma_kk(COL_DP, doa, smem_u32(s.v[0]));
         umma_commit(&s.dp_ready);
+        umma_commit(&s.v_empty[0]);
       }
-      // S of the second block right away: its TMEM buffer is free and K_1 sits in the other ring stage
+      // S of the second block right away: its TMEM buffer is free and K_1 sits in the next ring stage
       if (ok && n_it > 1) {
         ok = mbar_wait(&s.k_full[1], 0, p.err, 923);
         if (ok) {
@@ -563,11 +597,23 @@ flash_bwd_dq_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
           umma_commit(&s.s_ready[1]);
         }
       }
+      int ks = 0;                        // ring stage of K_it; K_{it+2} sits in stage (ks + 2) % 3
       for (int it = 0; it < n_it && ok; ++it) {
         const int st = it & 1;
-        // the score warps have read S_j and dP_j and written dS_j
+        int k2 = ks + 2;
+        if (k2 >= BW_QST) k2 -= BW_QST;
+        // the score warps have read S_j and dP_j and written dS_j over dP_j
         if (!mbar_wait(&s.ds_ready, it & 1, p.err, 930)) { ok = false; break; }
         tc_fence_after();
+        // dQ_i += dS K_j : A = dS [rows][keys] from TMEM (16 bf16 per K step = 8 columns; the four score warpgroups packed
+        // their quarters over the first 16 of their own 32 columns), B = K_j [keys][d] MN-major
+        const uint32_t ka = smem_u32(s.k[ks]);
+#pragma unroll
+        for (int k = 0; k < BW_T / 16; ++k)
+          umma_f16_ts(tmem_base + COL_DQ, tmem_base + COL_DP + (k >> 1) * 32 + (k & 1) * 8,
+                      make_smem_desc_sw128(ka + k * 2048, BW_CHUNK, 1024), idesc_kn, (it == 0 && k == 0) ? 0u : 1u);
+        umma_commit(&s.k_empty[ks]);
+        // dP of the next block over the dS that dQ has just consumed
         if (it + 1 < n_it) {
           const int sn = (it + 1) & 1;
           const uint32_t phn = ((it + 1) >> 1) & 1;
@@ -575,25 +621,17 @@ flash_bwd_dq_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
           tc_fence_after();
           mma_kk(COL_DP, doa, smem_u32(s.v[sn]));
           umma_commit(&s.dp_ready);
+          umma_commit(&s.v_empty[sn]);
         }
-        // dQ_i += dS K_j : A = dS [rows][keys] K-major, B = K_j [keys][d] MN-major
-        const uint32_t ka = smem_u32(s.k[st]);
-#pragma unroll
-        for (int k = 0; k < BW_T / 16; ++k)
-          umma_f16_ss(tmem_base + COL_DQ, make_smem_desc_sw128(dsa + (k >> 2) * BW_CHUNK + (k & 3) * 32, 16, 1024),
-                      make_smem_desc_sw128(ka + k * 2048, BW_CHUNK, 1024), idesc_kn, (it == 0 && k == 0) ? 0u : 1u);
-        umma_commit(&s.ds_free);
-        umma_commit(&s.kv_empty[st]);
-        // S of block it + 2 into the buffer block it used: the score warps released it after their exponentials, and its
-        // K tile lands in the ring stage that the commit above frees
+        // S of block it + 2 into the buffer block it used: the score warps released it after their exponentials
         if (it + 2 < n_it) {
-          const uint32_t ph2 = ((it + 2) >> 1) & 1;
           if (!mbar_wait(&s.s_free[st], (it >> 1) & 1, p.err, 933)) { ok = false; break; }
-          if (!mbar_wait(&s.k_full[st], ph2, p.err, 931)) { ok = false; break; }
+          if (!mbar_wait(&s.k_full[k2], static_cast<uint32_t>(((it + 2) / BW_QST) & 1), p.err, 931)) { ok = false; break; }
           tc_fence_after();
-          mma_kk(st ? COL_S1 : COL_S0, qa, smem_u32(s.k[st]));
+          mma_kk(st ? COL_S1 : COL_S0, qa, smem_u32(s.k[k2]));
           umma_commit(&s.s_ready[st]);
         }
+        if (++ks == BW_QST) ks = 0;
       }
       if (ok) umma_commit(&s.acc_done);
     }
@@ -611,7 +649,6 @@ flash_bwd_dq_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
     const float delta = p.delta[stat];
     const int kmin = p.window > 0 ? row + p.q_offset - p.window + 1 : INT_MIN;      // keys this row sees: [kmin, kmax]
     const int kmax = min(p.Tk - 1, p.causal ? row + p.q_offset : INT_MAX);
-    uint8_t* ds_row = s.ds + (wg >> 1) * BW_CHUNK + r * 128;
     bool ok = true;
     for (int it = 0; it < n_it && ok; ++it) {
       const int j = jlo + it;
@@ -631,10 +668,7 @@ flash_bwd_dq_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
                           (p.window <= 0 || j * BW_T > i * BW_T + BW_T - 1 + p.q_offset - p.window);
         if (full) {
 #pragma unroll
-          for (int c = 0; c < 32; c += 2) {           
-            pr[c] = exp2f(fmaf(__uint_as_float(t[c]), p.scale_log2, -lse2));
-            pr[c + 1] = exp2f(fmaf(__uint_as_float(t[c + 1]), p.scale_log2, -lse2));
-          }
+          for (int c = 0; c < 32; ++c) pr[c] = exp2f(fmaf(__uint_as_float(t[c]), p.scale_log2, -lse2));
         } else {
 #pragma unroll
           for (int c = 0; c < 32; ++c) {
@@ -643,26 +677,20 @@ flash_bwd_dq_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
           }
         }
       }
+      // dP_it was queued behind dQ of the previous block, so its completion also says that the dS columns are free
       if (!mbar_wait(&s.dp_ready, it & 1, p.err, 951)) { ok = false; break; }
-      if (it > 0 && !mbar_wait(&s.ds_free, (it - 1) & 1, p.err, 952)) { ok = false; break; }   // dQ of the previous block has read dS
       tc_fence_after();
       {
         uint32_t t[32];
         tmem_ld_32x32(dp_addr, t);
         tmem_wait_ld();
+        uint32_t pk[16];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const float* pp = pr + u * 8;
-          uint4 w;
-          w.x = pack_bf16x2(pp[0] * (__uint_as_float(t[u * 8 + 0]) - delta), pp[1] * (__uint_as_float(t[u * 8 + 1]) - delta));
-          w.y = pack_bf16x2(pp[2] * (__uint_as_float(t[u * 8 + 2]) - delta), pp[3] * (__uint_as_float(t[u * 8 + 3]) - delta));
-          w.z = pack_bf16x2(pp[4] * (__uint_as_float(t[u * 8 + 4]) - delta), pp[5] * (__uint_as_float(t[u * 8 + 5]) - delta));
-          w.w = pack_bf16x2(pp[6] * (__uint_as_float(t[u * 8 + 6]) - delta), pp[7] * (__uint_as_float(t[u * 8 + 7]) - delta));
-          const int unit = (wg & 1) * 4 + u;
-          *reinterpret_cast<uint4*>(ds_row + ((unit ^ (r & 7)) << 4)) = w;
-        }
+        for (int q = 0; q < 16; ++q)
+          pk[q] = pack_bf16x2(pr[2 * q] * (__uint_as_float(t[2 * q]) - delta), pr[2 * q + 1] * (__uint_as_float(t[2 * q + 1]) - delta));
+        tmem_st_32x16(dp_addr, pk);     // dS over the first 16 of this warpgroup's own 32 dP columns
       }
-      fence_proxy_async();
+      tmem_wait_st();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s.ds_ready);
