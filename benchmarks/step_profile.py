@@ -33,6 +33,7 @@ def main(argv=None):
     ap.add_argument("--seq", type=int, default=2048)
     ap.add_argument("--rows", type=int, default=70)
     ap.add_argument("--out", default=None)
+    ap.add_argument("--gaps", type=int, default=0, help="also list the N largest idle gaps of the device inside the step")
     args = ap.parse_args(argv)
     from torch.profiler import ProfilerActivity, profile
 
@@ -63,6 +64,23 @@ def main(argv=None):
     lines.append(f"total kernel time {all_t / 1000:.2f} ms in {all_n} launches; repository kernels "
                  f"{own_t / 1000:.2f} ms ({100 * own_t / max(all_t, 1):.1f} %) in {own_n} launches "
                  f"({100 * own_n / max(all_n, 1):.1f} %)")
+    if args.gaps:
+        # Idle time of the device inside the step: kernels sorted by start time, a gap is the time between the latest end
+        # seen so far and the next start.
+        evs = sorted(((e.time_range.start, e.time_range.end, e.name) for e in prof.events()
+                      if str(e.device_type).endswith("CUDA") and e.time_range.end > e.time_range.start), key=lambda t: t[0])
+        gaps, busy_end, prev = [], None, ""
+        for st, en, name in evs:
+            if busy_end is not None and st > busy_end:
+                gaps.append((st - busy_end, prev, name, st - evs[0][0]))
+            if busy_end is None or en > busy_end:
+                busy_end, prev = en, name
+        span = evs[-1][1] - evs[0][0] if evs else 0.0
+        idle = sum(g[0] for g in gaps)
+        lines.append(f"device span {span / 1000:.2f} ms, idle {idle / 1000:.2f} ms in {len(gaps)} gaps; "
+                     f"gaps > 20 us: {sum(g[0] for g in gaps if g[0] > 20) / 1000:.2f} ms")
+        for d, a_, b_, at in sorted(gaps, reverse=True)[:args.gaps]:
+            lines.append(f"  gap {d:8.1f} us at +{at / 1000:7.2f} ms  after {a_[:60]}  before {b_[:60]}")
     text = "\n".join(lines)
     print(text)
     if args.out:

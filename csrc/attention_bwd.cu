@@ -206,20 +206,22 @@ flash_bwd_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         const uint32_t ka = smem_u32(s.k), va = smem_u32(s.v);
         // D = A[128 x 128, K-major] * B[128 x 128, K-major]^T
         auto mma_kk = [&](uint32_t d_col, uint32_t a, uint32_t b) {
+          const uint64_t da = make_smem_desc_sw128(a, 16, 1024), db = make_smem_desc_sw128(b, 16, 1024);
 #pragma unroll
           for (int k = 0; k < BW_T / 16; ++k) {
             const uint32_t off = (k >> 2) * BW_CHUNK + (k & 3) * 32;
-            umma_f16_ss(tmem_base + d_col, make_smem_desc_sw128(a + off, 16, 1024),
-                        make_smem_desc_sw128(b + off, 16, 1024), idesc_kk, k > 0 ? 1u : 0u);
+            umma_f16_ss(tmem_base + d_col, smem_desc_advance(da, off), smem_desc_advance(db, off), idesc_kk, k > 0 ? 1u : 0u);
           }
         };
         // D += A^T-in-TMEM [128 keys x 128 rows] * B[rows][d] (MN-major).  A: 16 bf16 per K step = 8 columns; the four score
         // warpgroups packed their quarters over the first 16 of their own 32 columns (0, 32, 64, 96).
         auto mma_ts = [&](uint32_t d_col, uint32_t a_col, uint32_t b, bool first) {
+          const uint64_t db = make_smem_desc_sw128(b, BW_CHUNK, 1024);
+          const uint32_t d = tmem_base + d_col, a0 = tmem_base + a_col;
+          umma_f16_ts(d, a0, db, idesc_kn, first ? 0u : 1u);
 #pragma unroll
-          for (int k = 0; k < BW_T / 16; ++k)
-            umma_f16_ts(tmem_base + d_col, tmem_base + a_col + (k >> 1) * 32 + (k & 1) * 8,
-                        make_smem_desc_sw128(b + k * 2048, BW_CHUNK, 1024), idesc_kn, (first && k == 0) ? 0u : 1u);
+          for (int k = 1; k < BW_T / 16; ++k)
+            umma_f16_ts(d, a0 + (k >> 1) * 32 + (k & 1) * 8, smem_desc_advance(db, k * 2048), idesc_kn, 1u);
         };
         bool ok = mbar_wait(&s.kv_full, 0, p.err, 820);
         ok = ok && mbar_wait(&s.q_full[0], 0, p.err, 821);
@@ -567,11 +569,11 @@ flash_bwd_dq_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
       constexpr uint32_t idesc_kn = make_idesc_f16(1, BW_T, BW_T, 0, 1);
       const uint32_t qa = smem_u32(s.q), doa = smem_u32(s.dout);
       auto mma_kk = [&](uint32_t d_col, uint32_t a, uint32_t b) {
+        const uint64_t da = make_smem_desc_sw128(a, 16, 1024), db = make_smem_desc_sw128(b, 16, 1024);
 #pragma unroll
         for (int k = 0; k < BW_T / 16; ++k) {
           const uint32_t off = (k >> 2) * BW_CHUNK + (k & 3) * 32;
-          umma_f16_ss(tmem_base + d_col, make_smem_desc_sw128(a + off, 16, 1024), make_smem_desc_sw128(b + off, 16, 1024),
-                      idesc_kk, k > 0 ? 1u : 0u);
+          umma_f16_ss(tmem_base + d_col, smem_desc_advance(da, off), smem_desc_advance(db, off), idesc_kk, k > 0 ? 1u : 0u);
         }
       };
       bool ok = mbar_wait(&s.qdo_full, 0, p.err, 920);
@@ -608,10 +610,12 @@ flash_bwd_dq_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
         // dQ_i += dS K_j : A = dS [rows][keys] from TMEM (16 bf16 per K step = 8 columns; the four score warpgroups packed
         // their quarters over the first 16 of their own 32 columns), B = K_j [keys][d] MN-major
         const uint32_t ka = smem_u32(s.k[ks]);
+        const uint64_t dk = make_smem_desc_sw128(ka, BW_CHUNK, 1024);
+        umma_f16_ts(tmem_base + COL_DQ, tmem_base + COL_DP, dk, idesc_kn, it == 0 ? 0u : 1u);
 #pragma unroll
-        for (int k = 0; k < BW_T / 16; ++k)
-          umma_f16_ts(tmem_base + COL_DQ, tmem_base + COL_DP + (k >> 1) * 32 + (k & 1) * 8,
-                      make_smem_desc_sw128(ka + k * 2048, BW_CHUNK, 1024), idesc_kn, (it == 0 && k == 0) ? 0u : 1u);
+        for (int k = 1; k < BW_T / 16; ++k)
+          umma_f16_ts(tmem_base + COL_DQ, tmem_base + COL_DP + (k >> 1) * 32 + (k & 1) * 8, smem_desc_advance(dk, k * 2048),
+                      idesc_kn, 1u);
         umma_commit(&s.k_empty[ks]);
         // dP of the next block over the dS that dQ has just consumed
         if (it + 1 < n_it) {
