@@ -538,13 +538,16 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       if (p.act == 4 || p.act == 5) {
         // gated MLP over column halves of the tile: out[:, n0/2 + j] = act(acc[:, j]) * acc[:, BN/2 + j], act = SiLU (4) or
         // tanh-GELU (5)
+        // with eight epilogue warps (CTA pairs) each set of four takes half of the output columns
+        const int gc0 = (EPI_WARPS == 8) ? (epi >> 2) * (BN / 128) : 0;
+        const int gc1 = (EPI_WARPS == 8) ? gc0 + BN / 128 : BN / 64;
 #pragma unroll 1
-        for (int c = 0; c < BN / 64; ++c) {
+        for (int c = gc0; c < gc1; ++c) {
           uint32_t rg[32], ru[32];
           tmem_ld_32x32(t_row + c * 32, rg);
           tmem_ld_32x32(t_row + BN / 2 + c * 32, ru);
           tmem_wait_ld();
-          if (c == BN / 64 - 1) {
+          if (c == gc1 - 1) {
             tc_fence_before();
             __syncwarp();
             if (lane == 0) {
@@ -993,8 +996,8 @@ static int gemm_impl(const TyrGemmArgs& a, const TyrTpArgs* tpa) {
     r = make_tmap_bf16_3d(&tmA, a.A, a.M, a.K, a.batch, a.lda, a.sA, BK);
   if (r) return 3000 + r;
   // CTA pairs: plain products with a K-major A whose tiles are 256 columns wide
-  const bool pair = g_pair_enabled && tpa == nullptr && a.group_offsets == nullptr && bn == 256 && a.act != 4 &&
-                    a.act != 5 && (a.out_mode != 2 || g_aligned_split);
+  const bool pair = g_pair_enabled && tpa == nullptr && a.group_offsets == nullptr && bn == 256 &&
+                    (a.out_mode != 2 || g_aligned_split);
   if (!a.b_mn)
     r = make_tmap_bf16_3d(&tmB, a.B, a.K, a.N, a.batch, a.ldb, a.sB, pair ? bn / 2 : bn);
   else

@@ -2,6 +2,9 @@
 // once and written once:
 //  * layernorm_modulate:  y = (1 + scale[b]) * LayerNorm(x) + shift[b]   (no affine weights)
 //  * gate_residual:       out = x + gate[b] * y
+//  * flux_qk_post:        q, k <- RoPE(RMSNorm(q, k) * weight) per head, straight from the fused projection's output into the
+//                         packed [B, S_total, 3, H, 128] buffer the attention kernel reads (in place when source and destination
+//                         coincide; text and image streams land at their row offsets of one joint buffer, so no concatenation)
 // Rows are [batch, seq, D] bf16; scale / shift / gate are per-batch vectors addressed with an
 // element stride so that the chunks of one [batch, n_mods, D] modulation tensor are used in place
 // (Tyr/Model/Flux/Modulation.lean:84-109, DoubleStreamBlock.lean:143-215 of the reference).
@@ -81,7 +84,87 @@ gate_residual_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
   }
 }
 
+struct FluxQkPostArgs {
+  const __nv_bfloat16* src;      // [B, S, >= 3 * H * 128]: q at column 0, k at H * 128, v at 2 * H * 128
+  long long src_sb, src_st;      // element strides of batch and row
+  __nv_bfloat16* dst;            // same column layout; row s of the source goes to row dst_row0 + s
+  long long dst_sb, dst_st;
+  const __nv_bfloat16* wq;       // [128] RMSNorm weights
+  const __nv_bfloat16* wk;
+  const float* cosv;             // [B or 1, S, 64]
+  const float* sinv;
+  long long cs_sb;               // batch stride of cos / sin (0: shared by the batch)
+  int B, S, H, dst_row0, copy_v;
+  float eps;
+};
+
+// One warp per (batch, row, head): lane l owns elements 4l .. 4l+3 of the 128-wide head, i.e. the rotation pairs 2l and 2l+1.
+// fp32 throughout; one rounding to bf16 at the end (the unfused sequence rounds after the norm as well).
+__global__ void __launch_bounds__(256) flux_qk_post_kernel(FluxQkPostArgs a) {
+  const int lane = threadIdx.x & 31;
+  const long long total = static_cast<long long>(a.B) * a.S * a.H;
+  const float2 wq0 = unpack_bf16x2(reinterpret_cast<const uint32_t*>(a.wq)[2 * lane]);
+  const float2 wq1 = unpack_bf16x2(reinterpret_cast<const uint32_t*>(a.wq)[2 * lane + 1]);
+  const float2 wk0 = unpack_bf16x2(reinterpret_cast<const uint32_t*>(a.wk)[2 * lane]);
+  const float2 wk1 = unpack_bf16x2(reinterpret_cast<const uint32_t*>(a.wk)[2 * lane + 1]);
+  for (long long w = blockIdx.x * 8LL + (threadIdx.x >> 5); w < total; w += gridDim.x * 8LL) {
+    const int h = static_cast<int>(w % a.H);
+    const long long bs = w / a.H;
+    const int srow = static_cast<int>(bs % a.S);
+    const int b = static_cast<int>(bs / a.S);
+    const __nv_bfloat16* src = a.src + b * a.src_sb + static_cast<long long>(srow) * a.src_st + h * 128 + lane * 4;
+    __nv_bfloat16* dst = a.dst + b * a.dst_sb + static_cast<long long>(a.dst_row0 + srow) * a.dst_st + h * 128 + lane * 4;
+    const int hd = a.H * 128;
+    const uint2 uq = *reinterpret_cast<const uint2*>(src);
+    const uint2 uk = *reinterpret_cast<const uint2*>(src + hd);
+    const float2 cs = *reinterpret_cast<const float2*>(a.cosv + b * a.cs_sb + static_cast<long long>(srow) * 64 + lane * 2);
+    const float2 sn = *reinterpret_cast<const float2*>(a.sinv + b * a.cs_sb + static_cast<long long>(srow) * 64 + lane * 2);
+    float2 q0 = unpack_bf16x2(uq.x), q1 = unpack_bf16x2(uq.y), k0 = unpack_bf16x2(uk.x), k1 = unpack_bf16x2(uk.y);
+    float sq = q0.x * q0.x + q0.y * q0.y + q1.x * q1.x + q1.y * q1.y;
+    float sk = k0.x * k0.x + k0.y * k0.y + k1.x * k1.x + k1.y * k1.y;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      sq += __shfl_xor_sync(0xffffffffu, sq, o);
+      sk += __shfl_xor_sync(0xffffffffu, sk, o);
+    }
+    const float rq = rsqrtf(sq * (1.f / 128.f) + a.eps), rk = rsqrtf(sk * (1.f / 128.f) + a.eps);
+    q0.x *= rq * wq0.x; q0.y *= rq * wq0.y; q1.x *= rq * wq1.x; q1.y *= rq * wq1.y;
+    k0.x *= rk * wk0.x; k0.y *= rk * wk0.y; k1.x *= rk * wk1.x; k1.y *= rk * wk1.y;
+    uint2 oq, ok;
+    oq.x = pack_bf16x2(cs.x * q0.x - sn.x * q0.y, sn.x * q0.x + cs.x * q0.y);
+    oq.y = pack_bf16x2(cs.y * q1.x - sn.y * q1.y, sn.y * q1.x + cs.y * q1.y);
+    ok.x = pack_bf16x2(cs.x * k0.x - sn.x * k0.y, sn.x * k0.x + cs.x * k0.y);
+    ok.y = pack_bf16x2(cs.y * k1.x - sn.y * k1.y, sn.y * k1.x + cs.y * k1.y);
+    *reinterpret_cast<uint2*>(dst) = oq;
+    *reinterpret_cast<uint2*>(dst + hd) = ok;
+    if (a.copy_v) *reinterpret_cast<uint2*>(dst + 2 * hd) = *reinterpret_cast<const uint2*>(src + 2 * hd);
+  }
+}
+
 }  // namespace tyr
+
+// Returns 0 on success, -1 on a bad shape, stride or alignment.
+extern "C" TYR_EXPORT int tyr_flux_qk_post(const void* src, long long src_sb, long long src_st, void* dst, long long dst_sb,
+                                           long long dst_st, const void* wq, const void* wk, const float* cosv, const float* sinv,
+                                           long long cs_sb, int B, int S, int H, int D, int dst_row0, int copy_v, float eps,
+                                           void* stream) {
+  using namespace tyr;
+  if (D != 128 || B <= 0 || S <= 0 || H <= 0 || dst_row0 < 0) return -1;
+  if ((src_sb & 3) || (src_st & 3) || (dst_sb & 3) || (dst_st & 3) || (cs_sb & 1)) return -1;
+  if ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(wq) |
+       reinterpret_cast<uintptr_t>(wk) | reinterpret_cast<uintptr_t>(cosv) | reinterpret_cast<uintptr_t>(sinv)) & 7)
+    return -1;
+  FluxQkPostArgs a;
+  a.src = (const __nv_bfloat16*)src; a.src_sb = src_sb; a.src_st = src_st;
+  a.dst = (__nv_bfloat16*)dst; a.dst_sb = dst_sb; a.dst_st = dst_st;
+  a.wq = (const __nv_bfloat16*)wq; a.wk = (const __nv_bfloat16*)wk;
+  a.cosv = cosv; a.sinv = sinv; a.cs_sb = cs_sb;
+  a.B = B; a.S = S; a.H = H; a.dst_row0 = dst_row0; a.copy_v = copy_v; a.eps = eps;
+  long long blocks = (static_cast<long long>(B) * S * H + 7) / 8;
+  if (blocks > 148LL * 32) blocks = 148LL * 32;
+  flux_qk_post_kernel<<<static_cast<int>(blocks), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(a);
+  return static_cast<int>(cudaGetLastError());
+}
 
 extern "C" TYR_EXPORT int tyr_layernorm_modulate(const void* x, const void* scale, const void* shift, void* y,
                                                  long long rows, int seq, int D, long long mod_bstride, float eps,

@@ -122,6 +122,52 @@ def test_gpu_modulate_kernels_match_reference():
 
 
 @pytest.mark.gpu
+def test_gpu_flux_qk_post_matches_unfused_ops():
+    """QK-norm + RoPE kernel against the fp32 formula, into a joint buffer at a row offset (with the v copy) and in place."""
+    from tyr_b200.ops.modulate import flux_qk_post
+    B, S, H, D, extra = 2, 200, 3, 128, 256
+    g = torch.Generator(device="cuda").manual_seed(3)
+    src = torch.randn(B, S, 3 * H * D + extra, device="cuda", generator=g).bfloat16()
+    wq = (1 + 0.1 * torch.randn(D, device="cuda", generator=g)).bfloat16()
+    wk = (1 + 0.1 * torch.randn(D, device="cuda", generator=g)).bfloat16()
+    ids = torch.randint(0, 50, (B, S, 4), device="cuda", generator=g)
+    cos, sin = FX.rope_embed(ids, (16, 16, 16, 16), 2000)
+
+    def ref(x, w):
+        xf = x.float().reshape(B, S, H, D)
+        n = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-6) * w.float()
+        return FX.apply_rope(n, (cos, sin)).reshape(B, S, H * D)
+    rq, rk = ref(src[..., :H * D], wq), ref(src[..., H * D:2 * H * D], wk)
+    dst = torch.zeros(B, S + 40, 3 * H * D, device="cuda", dtype=torch.bfloat16)
+    flux_qk_post(src, dst, wq, wk, cos, sin, H, dst_row0=40, copy_v=True)
+    assert torch.equal(dst[:, :40], torch.zeros_like(dst[:, :40]))
+    assert (dst[:, 40:, :H * D].float() - rq).abs().max().item() < 2e-2 * rq.abs().max().item()
+    assert (dst[:, 40:, H * D:2 * H * D].float() - rk).abs().max().item() < 2e-2 * rk.abs().max().item()
+    assert torch.equal(dst[:, 40:, 2 * H * D:], src[..., 2 * H * D:3 * H * D])
+    inplace = src.clone()
+    flux_qk_post(inplace, inplace, wq, wk, cos, sin, H)
+    assert torch.equal(inplace[..., :2 * H * D], dst[:, 40:, :2 * H * D]) and torch.equal(inplace[..., 2 * H * D:], src[..., 2 * H * D:])
+
+
+@pytest.mark.gpu
+def test_gpu_gated_gemm_matches_reference():
+    """SwiGLU in the epilogue of a dense product, written into a column window of a wider buffer."""
+    from tyr_b200.ops.gemm import gemm, interleave_gate_up
+    g = torch.Generator(device="cuda").manual_seed(5)
+    M, K, Mh = 1000, 512, 384
+    x = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    w1 = (torch.randn(2 * Mh, K, device="cuda", generator=g) * K ** -0.5).bfloat16()
+    gu = x.float() @ w1.float().T
+    ref = torch.nn.functional.silu(gu[:, :Mh]) * gu[:, Mh:]
+    buf = torch.zeros(M, 128 + Mh, device="cuda", dtype=torch.bfloat16)
+    gemm(x, interleave_gate_up(w1), act="swiglu", out=buf[:, 128:])
+    assert torch.equal(buf[:, :128], torch.zeros_like(buf[:, :128]))
+    assert (buf[:, 128:].float() - ref).abs().max().item() < 2e-2 * ref.abs().max().item()
+    cpu = gemm(x.cpu().float(), interleave_gate_up(w1).cpu().float(), act="swiglu")
+    assert torch.allclose(cpu, ref.cpu(), atol=1e-3, rtol=1e-3)
+
+
+@pytest.mark.gpu
 def test_gpu_flux_bf16_matches_fp32_cpu():
     cfg = FX.FluxConfig(hidden_size=256, num_heads=2, half_head_dim=64, num_double_layers=1, num_single_layers=1, context_in_dim=64,
                         in_channels=32, time_dim=64, mlp_hidden_dim=512)

@@ -24,7 +24,7 @@ import torch
 from .._native import GemmArgs
 from ._common import check, cur_stream, err_word, lib
 
-_ACT = {None: 0, "none": 0, "relu2": 1, "relu": 2, "relu2_grad": 3}
+_ACT = {None: 0, "none": 0, "relu2": 1, "relu": 2, "relu2_grad": 3, "swiglu": 4, "geglu": 5}
 
 
 def _dims(t, layout, is_a):
@@ -50,6 +50,13 @@ def _reference(a, b, a_layout, b_layout, aux, alpha, beta, act, out_dtype):
     A = a.float() if a_layout == "K" else a.float().transpose(-1, -2)
     B = b.float().transpose(-1, -2) if b_layout == "K" else b.float()
     acc = A @ B
+    if act in ("swiglu", "geglu"):
+        # column blocks of 256: 128 gate columns followed by the matching 128 up columns
+        N = acc.shape[-1]
+        blk = acc.reshape(*acc.shape[:-1], N // 256, 2, 128)
+        gate, up = alpha * blk[..., 0, :], beta * blk[..., 1, :]
+        fn = torch.nn.functional.silu if act == "swiglu" else (lambda t: torch.nn.functional.gelu(t, approximate="tanh"))
+        return (fn(gate) * up).reshape(*acc.shape[:-1], N // 2).to(out_dtype)
     if act == "relu2":
         acc = torch.relu(acc) ** 2
     elif act == "relu":
@@ -75,7 +82,17 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_layout: str = "K", b_layout: str
     batch = max(batch_a, batch_b)
     if batch_a not in (1, batch) or batch_b not in (1, batch):
         raise ValueError("gemm batch mismatch")
-    shape = (M, N) if (a.dim() == 2 and b.dim() == 2) else (batch, M, N)
+    gated = act in ("swiglu", "geglu")
+    if gated:
+        # b holds, per block of 256 rows, 128 gate rows then the matching 128 up rows (`interleave_gate_up`); the result
+        # is silu(alpha * gate) * (beta * up) (tanh-GELU for "geglu"), N / 2 columns wide
+        if N % 256 != 0 or b_layout != "K" or aux is not None or accumulate or batch != 1:
+            raise ValueError("gated gemm needs K-major b with N % 256 == 0, no aux, no accumulation, no batch")
+        if beta == 0.0:
+            beta = 1.0
+        bn = 256
+    n_out = N // 2 if gated else N
+    shape = (M, n_out) if (a.dim() == 2 and b.dim() == 2) else (batch, M, n_out)
     if out_dtype is None:
         out_dtype = torch.bfloat16 if a.is_cuda else a.dtype
     if accumulate:
@@ -166,6 +183,16 @@ class _LinearFn(torch.autograd.Function):
                 gemm(dy2, x2, a_layout="MN", b_layout="MN", out=dw32, accumulate=True)
                 dw = dw32.to(w.dtype)
         return dx, dw, None
+
+
+def interleave_gate_up(w: torch.Tensor) -> torch.Tensor:
+    """[2*M, K] weights with the M gate rows first and the M up rows second -> the row order the gated epilogue reads:
+    per block of 256 rows, 128 gate rows followed by the matching 128 up rows (M % 128 == 0)."""
+    M2, K = w.shape
+    M = M2 // 2
+    if M % 128:
+        raise ValueError("interleave_gate_up needs a multiple of 128 rows per half")
+    return torch.stack([w[:M].reshape(M // 128, 128, K), w[M:].reshape(M // 128, 128, K)], dim=1).reshape(M2, K).contiguous()
 
 
 def relu2_bwd(dy, y):
