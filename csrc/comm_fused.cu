@@ -301,6 +301,56 @@ peer_sum_kernel(PeerPtrs src, long long off, float* out, long long n, int world,
   }
 }
 
+// The same sum with 16-byte peer loads, four per thread in flight (off and n multiples of 4 elements, 16-byte aligned bases).
+__global__ void __launch_bounds__(256)
+peer_sum_v4_kernel(PeerPtrs src, long long off, float* out, long long n4, int world, float scale) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i0 = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i0 < n4; i0 += 4 * stride) {
+    float4 acc[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int r = 0; r < world; ++r) {
+      const float* base = reinterpret_cast<const float*>(src.p[r]) + off;
+      float4 t[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (i0 + u * stride < n4) t[u] = ld_peer_f4(base + (i0 + u * stride) * 4);
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (i0 + u * stride < n4) { acc[u].x += t[u].x; acc[u].y += t[u].y; acc[u].z += t[u].z; acc[u].w += t[u].w; }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (i0 + u * stride < n4)
+        reinterpret_cast<float4*>(out)[i0 + u * stride] =
+            make_float4(acc[u].x * scale, acc[u].y * scale, acc[u].z * scale, acc[u].w * scale);
+  }
+}
+
+// All-gather flavour: out[r * m + i] = src_r[off + i] for every rank r (m a multiple of 4 elements): every rank pulls the
+// other ranks' pieces with plain peer loads.
+__global__ void __launch_bounds__(256)
+peer_gather_kernel(PeerPtrs src, long long off, float* out, long long m4, int world) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  const long long total = m4 * world;
+  for (long long i0 = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i0 < total; i0 += 4 * stride) {
+    float4 t[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const long long i = i0 + u * stride;
+      if (i < total) {
+        const int r = static_cast<int>(i / m4);
+        t[u] = ld_peer_f4(reinterpret_cast<const float*>(src.p[r]) + off + (i - r * m4) * 4);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const long long i = i0 + u * stride;
+      if (i < total) reinterpret_cast<float4*>(out)[i] = t[u];
+    }
+  }
+}
+
 }  // namespace tyr
 
 using namespace tyr;
@@ -456,10 +506,33 @@ extern "C" TYR_EXPORT int tyr_dp_muon_apply_push(void* const* work_ptrs, int wor
 extern "C" TYR_EXPORT int tyr_peer_sum(void* const* src_ptrs, int world, long long off, float* out,
                                        long long n, float scale, void* stream) {
   if (world < 1 || world > kMaxRanks || n <= 0) return -1;
+  bool vec = (off & 3) == 0 && (n & 3) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+  for (int r = 0; r < world && vec; ++r) vec = (reinterpret_cast<uintptr_t>(src_ptrs[r]) & 15) == 0;
+  if (vec) {
+    long long blocks = (n / 4 + 1023) / 1024;
+    if (blocks > 148 * 4) blocks = 148 * 4;
+    if (blocks < 1) blocks = 1;
+    peer_sum_v4_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>(make_peers(src_ptrs, world), off, out, n / 4, world,
+                                                                       scale);
+    return (int)cudaGetLastError();
+  }
   long long blocks = (n + 255) / 256;
   if (blocks > 148 * 4) blocks = 148 * 4;
   peer_sum_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>(make_peers(src_ptrs, world), off, out, n,
                                                                  world, scale);
+  return (int)cudaGetLastError();
+}
+
+// out[r * m + i] = src_r[off + i], i < m, for every rank r.  off, m multiples of 4 elements; bases 16-byte aligned.
+extern "C" TYR_EXPORT int tyr_peer_gather(void* const* src_ptrs, int world, long long off, float* out, long long m,
+                                          void* stream) {
+  if (world < 1 || world > kMaxRanks || m <= 0 || (m & 3) || (off & 3) || (reinterpret_cast<uintptr_t>(out) & 15)) return -1;
+  for (int r = 0; r < world; ++r)
+    if (reinterpret_cast<uintptr_t>(src_ptrs[r]) & 15) return -1;
+  long long blocks = (m / 4 * world + 1023) / 1024;
+  if (blocks > 148 * 4) blocks = 148 * 4;
+  if (blocks < 1) blocks = 1;
+  peer_gather_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>(make_peers(src_ptrs, world), off, out, m / 4, world);
   return (int)cudaGetLastError();
 }
 

@@ -41,3 +41,13 @@ def test_expert_parallel_pull_dispatch_and_combine(nproc):
         pytest.skip(f"needs {nproc} GPUs")
     r = _run_torchrun(os.path.join(ROOT, "tests", "workers", "ep_worker.py"), nproc, port=29651 + nproc)
     assert "EP_WORKER_RESULT PASS" in r.stdout, (r.stdout[-3000:], r.stderr[-3000:])
+
+
+@pytest.mark.parametrize("nproc", [2, 4, 8])
+def test_peer_memory_collectives_match_transport(nproc):
+    """all_reduce / reduce_scatter(_list) / all_gather(_list) and the public DistAdam / NorMuon steps over the symmetric-heap
+    kernels against the same calls over NCCL."""
+    if torch.cuda.device_count() < nproc:
+        pytest.skip(f"needs {nproc} GPUs")
+    r = _run_torchrun(os.path.join(ROOT, "tests", "workers", "peer_coll_worker.py"), nproc, port=29671 + nproc)
+    assert "PEER_COLLECTIVES_OK" in r.stdout, (r.stdout[-3000:], r.stderr[-3000:])

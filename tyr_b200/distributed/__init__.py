@@ -233,7 +233,14 @@ def get_world_size() -> int:
 
 def destroy_process_group() -> None:
     """Drain every pending handle, reset, then re-raise the first error seen while draining."""
-    global _backend, _owns_torch_pg
+    global _backend, _owns_torch_pg, _peer
+    if _peer is not None:
+        # every peer collective ends with a barrier after the last peer read, so the staging heap is idle here
+        try:
+            torch.cuda.synchronize(_peer.device)
+            _peer.close()
+        finally:
+            _peer = None
 
     def wait_one(_ctx, hid):
         _wait_transport(int(hid))
@@ -321,8 +328,50 @@ def _avg_post(op: ReduceOp, world: int):
     return post
 
 
+# ---- peer-memory collectives (distributed/peer.py) --------------------------------------------------------------
+_peer = None
+
+
+def enable_peer_collectives(capacity_bytes: int = 256 << 20, device=None):
+    """Routes ``all_reduce`` / ``reduce_scatter(_list)`` / ``all_gather(_list)`` of floating-point CUDA tensors (sum and
+    avg) through the hand-written peer-memory kernels instead of NCCL.  Collective: every rank calls it, once, after
+    ``init_process_group``; needs one process per GPU on one node.  Returns the ``PeerCollectives`` object."""
+    global _peer
+    b = _require()
+    if _peer is None:
+        from .peer import PeerCollectives
+        dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        _peer = PeerCollectives(b.rank(), b.size(), dev, capacity_bytes, getattr(b, "group", None))
+    return _peer
+
+
+def disable_peer_collectives() -> None:
+    global _peer
+    if _peer is not None:
+        torch.cuda.synchronize(_peer.device)
+        barrier()
+        _peer.close()
+        _peer = None
+
+
+def _use_peer(t: torch.Tensor, op: ReduceOp, copies: int = 1) -> bool:
+    return _peer is not None and op in (ReduceOp.sum, ReduceOp.avg) and _peer.supports(t, copies)
+
+
+class _Done:
+    """Stands in for a transport work object when the result was produced by stream-ordered kernels."""
+
+    def wait(self):
+        return True
+
+    def is_completed(self):
+        return True
+
+
 def all_reduce_async(t: torch.Tensor, op: ReduceOp = ReduceOp.sum) -> WorkHandle:
     b = _require()
+    if _use_peer(t, op):
+        return _submit(_Done(), _peer.all_reduce(t, op is ReduceOp.avg))
     out = t.detach().clone()
     work = b.all_reduce(out, op, True)
     return _submit(work, out, _avg_post(op, b.size()))
@@ -348,6 +397,8 @@ def reduce_scatter(t: torch.Tensor, op: ReduceOp = ReduceOp.sum) -> torch.Tensor
     W = b.size()
     if t.dim() == 0 or t.shape[0] % W != 0:
         raise ValueError(f"reduceScatter: dim 0 of {list(t.shape)} does not divide by world size {W}")
+    if _use_peer(t, op):
+        return _peer.reduce_scatter(t, op is ReduceOp.avg)
     inp = t.detach().clone().contiguous()
     out = torch.empty((t.shape[0] // W,) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
     b.reduce_scatter_tensor(out, inp, op, False)
@@ -362,6 +413,8 @@ def reduce_scatter_list(ts: Sequence[torch.Tensor], op: ReduceOp = ReduceOp.sum)
         raise ValueError(f"reduceScatterList: expected {W} tensors, got {len(ts)}")
     if any(x.shape != ts[0].shape or x.dtype != ts[0].dtype for x in ts):
         raise ValueError("reduceScatterList: tensors must share shape and dtype")
+    if _use_peer(ts[0], op, W):
+        return _peer.reduce_scatter_list(ts, op is ReduceOp.avg)
     ins = [x.detach().clone().contiguous() for x in ts]
     out = torch.empty_like(ins[0])
     b.reduce_scatter_list(out, ins, op, False)
@@ -372,6 +425,8 @@ def reduce_scatter_list(ts: Sequence[torch.Tensor], op: ReduceOp = ReduceOp.sum)
 def all_gather(t: torch.Tensor) -> torch.Tensor:
     """Concatenation of every rank's tensor along dim 0."""
     b = _require()
+    if _use_peer(t, ReduceOp.sum):
+        return _peer.all_gather(t)
     inp = t.detach().clone().contiguous()
     if inp.dim() == 0:
         inp = inp.reshape(1)
@@ -382,6 +437,8 @@ def all_gather(t: torch.Tensor) -> torch.Tensor:
 
 def all_gather_list(t: torch.Tensor) -> List[torch.Tensor]:
     b = _require()
+    if _use_peer(t, ReduceOp.sum):
+        return _peer.all_gather_list(t)
     inp = t.detach().clone().contiguous()
     outs = [torch.empty_like(inp) for _ in range(b.size())]
     b.all_gather_list(outs, inp, False)

@@ -59,6 +59,9 @@ def _dist():
 
 
 def step_distributed(param, grad, state: ParamState, cfg: Config, lr_mul: float = 1.0, wd_mul: float = 1.0):
+    """Reduce-scatter the gradient, AdamW on the owned rows, all-gather parameter and moments
+    (Tyr/Optim/DistAdam.lean:185-267).  The collectives are those of ``tyr_b200.distributed``: after
+    ``distributed.enable_peer_collectives()`` they run on the peer-memory kernels instead of NCCL."""
     dist = _dist()
     if not cfg.distributed or not dist.is_initialized() or dist.get_world_size() <= 1:
         return step_single(param, grad, state, cfg, lr_mul, wd_mul)

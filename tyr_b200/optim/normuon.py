@@ -128,7 +128,9 @@ def step_distributed_group(params: List[torch.Tensor], grads: List[torch.Tensor]
                            cfg: Config, lr_mul: float = 1.0, wd_mul: float = 1.0):
     """Parameters are processed in blocks of ``world``; rank r owns parameter ``base + r``.
     Gradients are averaged with reduce_scatter over per-rank lists (zero-padded tail blocks), the
-    owner steps, parameters AND momentum are replicated with all_gather."""
+    owner steps, parameters AND momentum are replicated with all_gather (Tyr/Optim/NorMuon.lean:346-425).  The collectives
+    are those of ``tyr_b200.distributed``: after ``distributed.enable_peer_collectives()`` they run on the peer-memory
+    kernels instead of NCCL."""
     dist = _dist()
     if not params:
         return params, states
