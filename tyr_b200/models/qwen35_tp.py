@@ -198,6 +198,30 @@ class TPCache:
         I = gu.shape[-1] // 2
         return (F.silu(gu[..., :I].float()) * gu[..., I:].float()).to(gu.dtype)
 
+    def sequence_parallel(self, B: int, S: int) -> bool:
+        """Whether ``run`` scatters the rows of a [B, S] chunk over the ranks (prefill) or keeps them replicated (decode)."""
+        W, rows = self.m.world, B * S
+        return W > 1 and S > 1 and rows % W == 0 and (rows // W) % (128 if self.m.tp.fused else 1) == 0
+
+    @torch.no_grad()
+    def layer_forward(self, i: int, x: torch.Tensor, B: int, S: int, cos, sin, seq_par: bool) -> torch.Tensor:
+        """One decoder layer on the residual stream ``x``: this rank's ``[B*S / world, hidden]`` rows when ``seq_par``, else
+        all ``[B*S, hidden]`` rows (replicated).  Advances layer i's cache.  ``run`` is a loop over this; tests drive it
+        layer by layer with the single-device model's activations as input."""
+        m, tp = self.m, self.m.tp
+        l, eps, rows = m.layers[i], m.cfg.rms_norm_eps, B * S
+        w_out = l.mixer.o_proj if isinstance(l.mixer, TPAttention) else l.mixer.out_proj
+        if seq_par:
+            proj = tp.allgather_gemm(Q.rms(x, l.input_layernorm, eps), l.mixer.in_proj)
+            core = self._mixer(i, l, proj, B, S, cos, sin).reshape(rows, -1)
+            x = tp.gemm_reduce_scatter(core, w_out, add=x)
+            gu = tp.allgather_gemm(Q.rms(x, l.post_attention_layernorm, eps), l.ffn.gate_up)
+            return tp.gemm_reduce_scatter(self._swiglu(gu), l.ffn.down, add=x)
+        proj = lin(Q.rms(x, l.input_layernorm, eps), l.mixer.in_proj)
+        core = self._mixer(i, l, proj, B, S, cos, sin).reshape(rows, -1)
+        x = tp.linear_all_reduce(core, w_out, add=x)
+        return tp.linear_all_reduce(self._mlp_hidden(Q.rms(x, l.post_attention_layernorm, eps), l.ffn.gate_up), l.ffn.down, add=x)
+
     @torch.no_grad()
     def run(self, ids: torch.Tensor) -> torch.Tensor:
         """ids: [B, S] (identical on every rank) -> full-vocabulary logits of the last position, [B, V], on every rank."""
@@ -207,16 +231,12 @@ class TPCache:
             raise ValueError("Qwen3.5 cache overflow")
         cos, sin = self.cos[self.pos:self.pos + S], self.sin[self.pos:self.pos + S]
         rows, W, eps = B * S, m.world, cfg.rms_norm_eps
-        seq_par = W > 1 and S > 1 and rows % W == 0 and (rows // W) % (128 if tp.fused else 1) == 0
+        seq_par = self.sequence_parallel(B, S)
         if seq_par:
             rpr = rows // W
             x = F.embedding(ids.reshape(-1)[m.rank * rpr:(m.rank + 1) * rpr], m.embed_tokens)               # this rank's rows
-            for i, l in enumerate(m.layers):
-                proj = tp.allgather_gemm(Q.rms(x, l.input_layernorm, eps), l.mixer.in_proj)
-                core = self._mixer(i, l, proj, B, S, cos, sin).reshape(rows, -1)
-                x = tp.gemm_reduce_scatter(core, l.mixer.o_proj if isinstance(l.mixer, TPAttention) else l.mixer.out_proj, add=x)
-                gu = tp.allgather_gemm(Q.rms(x, l.post_attention_layernorm, eps), l.ffn.gate_up)
-                x = tp.gemm_reduce_scatter(self._swiglu(gu), l.ffn.down, add=x)
+            for i in range(len(m.layers)):
+                x = self.layer_forward(i, x, B, S, cos, sin, True)
             last = torch.zeros((B, cfg.hidden_size), dtype=torch.float32, device=x.device)
             want = torch.arange(B, device=x.device) * S + (S - 1)
             mine = (want >= m.rank * rpr) & (want < (m.rank + 1) * rpr)
@@ -226,11 +246,8 @@ class TPCache:
             x_last = last.to(x.dtype)
         else:
             x = F.embedding(ids.reshape(-1), m.embed_tokens)                                                # replicated rows
-            for i, l in enumerate(m.layers):
-                proj = lin(Q.rms(x, l.input_layernorm, eps), l.mixer.in_proj)
-                core = self._mixer(i, l, proj, B, S, cos, sin).reshape(rows, -1)
-                x = tp.linear_all_reduce(core, l.mixer.o_proj if isinstance(l.mixer, TPAttention) else l.mixer.out_proj, add=x)
-                x = tp.linear_all_reduce(self._mlp_hidden(Q.rms(x, l.post_attention_layernorm, eps), l.ffn.gate_up), l.ffn.down, add=x)
+            for i in range(len(m.layers)):
+                x = self.layer_forward(i, x, B, S, cos, sin, False)
             x_last = x.reshape(B, S, -1)[:, -1]
         self.pos += S
         return tp.all_gather_cols(lin(Q.rms(x_last, m.norm, eps), m.lm_head))
