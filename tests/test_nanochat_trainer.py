@@ -1,7 +1,9 @@
 """Training engine: schedules and a few optimisation steps on CPU
 (Tests/TestModdedGPT.lean, Tests/TestNorMuon*.lean style checks)."""
 import math
+import os
 
+import pytest
 import torch
 
 from tyr_b200.models import nanochat as nc
@@ -55,3 +57,18 @@ def test_training_reduces_loss_cpu():
     # the zero-initialised projections must have moved (Muon update applied)
     assert tr.params.master["attn_w"][:, 3].abs().sum() > 0
     assert tr.params.master["mlp_w"][:, 1].abs().sum() > 0
+
+
+def test_restated_reference_arm_steps_on_cpu():
+    """The comparison arm (library ops only, fp32 as the reference trains) takes steps and lowers the loss on a repeated batch."""
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    from baseline.restated_reference import RestatedTrainer
+    cfg = nc.Config(vocab_size=256, n_layer=4, n_head=2, half_head_dim=8, max_seq_len=32)
+    hp = eng.Hyperparameters(device_batch_size=2, max_seq_len=32, total_batch_size_tokens=64)
+    tr = RestatedTrainer(cfg, hp, device="cpu", precision="fp32")
+    tok = torch.randint(0, 256, (2, 33), generator=torch.Generator().manual_seed(0))
+    losses = [float(tr.step([(tok[:, :-1], tok[:, 1:])]).loss) for _ in range(4)]
+    assert all(l == l for l in losses) and losses[-1] < losses[0]
+    with pytest.raises(ValueError):
+        RestatedTrainer(cfg, hp, device="cpu", precision="fp16")
