@@ -50,6 +50,7 @@ def parse_args():
     ap.add_argument("--no-laguna", action="store_true", help="skip the Laguna MoE decode half of the metric")
     ap.add_argument("--laguna-steps", type=int, default=48)
     ap.add_argument("--laguna-layers", type=int, default=24)
+    ap.add_argument("--restated-micro-batch", type=int, default=4, help="--impl restated in fp32: rows per micro-batch")
     ap.add_argument("--restated-precision", default="fp32", choices=["fp32", "bf16"],
                     help="--impl restated: fp32 as the reference trains, or bf16 autocast (the generous reading)")
     return ap.parse_args()
@@ -280,10 +281,16 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    # the restated arm in fp32 accumulates the same 32 x 2048 tokens over micro-batches (its fp32 logits and activations
+    # for all rows at once do not fit in 180 GB)
+    micro = B
+    if args.impl == "restated" and args.restated_precision == "fp32":
+        micro = min(B, args.restated_micro_batch)
+
     def run_device_step(i):
         tok = dev_tok[i % n_pool]
         flush.zero_()  # L2 flush (256 MB > 126 MB L2) between iterations
-        return trainer.step([(tok[:, :-1], tok[:, 1:])])
+        return trainer.step([(tok[r:r + micro, :-1], tok[r:r + micro, 1:]) for r in range(0, B, micro)])
 
     for i in range(args.warmup):
         run_device_step(i)

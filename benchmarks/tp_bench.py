@@ -16,7 +16,7 @@ import sys
 import torch
 import torch.distributed as dist
 
-from .tp import TensorParallel
+from tyr_b200.parallel.tp import TensorParallel
 
 
 def _time(fn, iters=10, warmup=3):

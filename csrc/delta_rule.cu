@@ -18,7 +18,12 @@ __global__ void __launch_bounds__(512)
 gdr_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
                   const __nv_bfloat16* __restrict__ v, const float* __restrict__ g,
                   const float* __restrict__ beta, float* __restrict__ state, __nv_bfloat16* __restrict__ out,
-                  int Hk, int Hv, int dv, long long q_bstride, long long v_bstride) {
+                  int Hk, int Hv, int dv, long long q_bstride, long long v_bstride,
+                  const __nv_bfloat16* __restrict__ z, long long z_bstride, const __nv_bfloat16* __restrict__ norm_w,
+                  float norm_eps) {
+  // z != nullptr (dv == 128, one column pass): the layer's gated RMSNorm runs in the epilogue,
+  //   out = rmsnorm_over_dv(o) * norm_w * silu(z),
+  // with o rounded to bf16 first, as the separate kernels see it.
   // 128 state columns x 4 row groups per CTA: a thread keeps DK / 4 values of one column in registers; the two column
   // reductions (S^T k and S^T q) are finished across the row groups through shared memory.
   constexpr int RPT = DK / 4;
@@ -75,9 +80,65 @@ gdr_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __re
     }
     part[rg][cl] = o;
     __syncthreads();
-    if (rg == 0 && live)
-      out[(static_cast<long long>(bh)) * dv + col] = __float2bfloat16((part[0][cl] + part[1][cl] + part[2][cl] + part[3][cl]) * qn);
+    if (z == nullptr) {
+      if (rg == 0 && live)
+        out[(static_cast<long long>(bh)) * dv + col] = __float2bfloat16((part[0][cl] + part[1][cl] + part[2][cl] + part[3][cl]) * qn);
+    } else {
+      float ov = 0.f;
+      if (rg == 0 && live) ov = __bfloat162float(__float2bfloat16((part[0][cl] + part[1][cl] + part[2][cl] + part[3][cl]) * qn));
+      float sq2 = warp_sum(ov * ov);                      // row groups 1..3 contribute zeros
+      if ((tid & 31) == 0) red[0][tid >> 5] = sq2;
+      __syncthreads();
+      if (rg == 0 && live) {
+        float tot = 0.f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) tot += red[0][i];
+        const float rstd = rsqrtf(tot / static_cast<float>(dv) + norm_eps);
+        const float zz = __bfloat162float(z[b * z_bstride + static_cast<long long>(hv) * dv + col]);
+        const float y = ov * rstd * __bfloat162float(norm_w[col]);
+        out[(static_cast<long long>(bh)) * dv + col] = __float2bfloat16(y * (zz / (1.f + __expf(-zz))));
+      }
+    }
     __syncthreads();
+  }
+}
+
+// Everything in front of the recurrent step for one new token per row: the causal depthwise conv (window of K taps kept as
+// the layer's conv state, shifted in place: a channel belongs to exactly one thread) with bias and SiLU, and the per-head
+// gates beta = sigmoid(b), g = -softplus(a + dt_bias) * exp(a_log).  `mixed` / `b_in` / `a_in` are rows of projection outputs
+// (column windows of one fused projection or separate tensors: row strides ld_m / ld_b / ld_a); outputs: conv_out bf16 [B, cd], g / beta fp32 [B, Hv].
+// The reference runs this as about twenty library launches (cc/src/tyr_qwen35.cpp:121-170).
+__global__ void __launch_bounds__(256)
+gdn_conv_gates_kernel(const __nv_bfloat16* __restrict__ mixed, const __nv_bfloat16* __restrict__ b_in,
+                      const __nv_bfloat16* __restrict__ a_in, long long ld_m, long long ld_b, long long ld_a,
+                      __nv_bfloat16* __restrict__ conv_state,
+                      const __nv_bfloat16* __restrict__ conv_w, const __nv_bfloat16* __restrict__ conv_b,
+                      const float* __restrict__ dt_bias, const float* __restrict__ a_log, __nv_bfloat16* __restrict__ conv_out,
+                      float* __restrict__ g, float* __restrict__ beta, int B, int cd, int K, int Hv) {
+  const long long idx = blockIdx.x * 256LL + threadIdx.x;
+  const long long n_conv = static_cast<long long>(B) * cd;
+  if (idx < n_conv) {
+    const int b = static_cast<int>(idx / cd), c = static_cast<int>(idx - static_cast<long long>(b) * cd);
+    __nv_bfloat16* st = conv_state + idx * K;
+    const __nv_bfloat16* w = conv_w + static_cast<long long>(c) * K;
+    const __nv_bfloat16 x_new = mixed[b * ld_m + c];
+    float acc = conv_b ? __bfloat162float(conv_b[c]) : 0.f;
+    for (int j = 0; j + 1 < K; ++j) {
+      const __nv_bfloat16 t = st[j + 1];
+      st[j] = t;
+      acc += __bfloat162float(t) * __bfloat162float(w[j]);
+    }
+    st[K - 1] = x_new;
+    acc += __bfloat162float(x_new) * __bfloat162float(w[K - 1]);
+    conv_out[idx] = __float2bfloat16(acc / (1.f + __expf(-acc)));
+  } else if (idx < n_conv + static_cast<long long>(B) * Hv) {
+    const long long j = idx - n_conv;
+    const int b = static_cast<int>(j / Hv), h = static_cast<int>(j - static_cast<long long>(b) * Hv);
+    const float bv = __bfloat162float(b_in[b * ld_b + h]);
+    const float av = __bfloat162float(a_in[b * ld_a + h]) + dt_bias[h];
+    const float sp = av > 20.f ? av : log1pf(__expf(av));
+    beta[j] = 1.f / (1.f + __expf(-bv));
+    g[j] = -sp * __expf(a_log[h]);
   }
 }
 
@@ -664,13 +725,45 @@ extern "C" TYR_EXPORT int tyr_gdr_chunk_scan(const float* u, const float* w, con
   return static_cast<int>(cudaGetLastError());
 }
 
+extern "C" TYR_EXPORT int tyr_gdr_decode_norm(const void* q, const void* k, const void* v, const float* g, const float* beta,
+                                              float* state, void* out, int B, int Hk, int Hv, int dk, int dv,
+                                              long long q_bstride, long long v_bstride, const void* z, long long z_bstride,
+                                              const void* norm_w, float norm_eps, void* stream);
+
+// Conv + SiLU (state shifted in place) and the per-head gates of one decode token; see gdn_conv_gates_kernel.
+extern "C" TYR_EXPORT int tyr_gdn_conv_gates(const void* mixed, const void* b_in, const void* a_in, long long ld_m, long long ld_b,
+                                             long long ld_a, void* conv_state,
+                                             const void* conv_w, const void* conv_b, const float* dt_bias, const float* a_log,
+                                             void* conv_out, float* g, float* beta, int B, int cd, int K, int Hv, void* stream) {
+  using namespace tyr;
+  if (B <= 0 || cd <= 0 || K < 1 || K > 8 || Hv <= 0) return -1;
+  const long long n = static_cast<long long>(B) * cd + static_cast<long long>(B) * Hv;
+  gdn_conv_gates_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      (const __nv_bfloat16*)mixed, (const __nv_bfloat16*)b_in, (const __nv_bfloat16*)a_in, ld_m, ld_b, ld_a, (__nv_bfloat16*)conv_state,
+      (const __nv_bfloat16*)conv_w, (const __nv_bfloat16*)conv_b, dt_bias, a_log, (__nv_bfloat16*)conv_out, g, beta, B, cd, K, Hv);
+  return static_cast<int>(cudaGetLastError());
+}
+
 // q, k: bf16 [B, Hk, dk] (rows may be strided by q_bstride elements between batches); v: bf16 [B, Hv, dv]
 // (v_bstride); g, beta: fp32 [B, Hv]; state: fp32 [B, Hv, dk, dv] updated in place; out: bf16 [B, Hv, dv].
 extern "C" TYR_EXPORT int tyr_gdr_decode(const void* q, const void* k, const void* v, const float* g, const float* beta,
                                          float* state, void* out, int B, int Hk, int Hv, int dk, int dv,
                                          long long q_bstride, long long v_bstride, void* stream) {
+  return tyr_gdr_decode_norm(q, k, v, g, beta, state, out, B, Hk, Hv, dk, dv, q_bstride, v_bstride, nullptr, 0, nullptr, 0.f,
+                             stream);
+}
+
+// The same step with the layer's gated RMSNorm in the epilogue when `z` (bf16 [B, Hv, dv], batch stride z_bstride) and
+// `norm_w` (bf16 [dv]) are given; that form needs dv == 128.
+extern "C" TYR_EXPORT int tyr_gdr_decode_norm(const void* q, const void* k, const void* v, const float* g, const float* beta,
+                                              float* state, void* out, int B, int Hk, int Hv, int dk, int dv,
+                                              long long q_bstride, long long v_bstride, const void* z, long long z_bstride,
+                                              const void* norm_w, float norm_eps, void* stream) {
   using namespace tyr;
   if (B <= 0 || Hk <= 0 || Hv <= 0 || Hv % Hk != 0 || dv <= 0) return -1;
+  if (z != nullptr && (dv != 128 || norm_w == nullptr)) return -3;
+  auto* zz = reinterpret_cast<const __nv_bfloat16*>(z);
+  auto* nw = reinterpret_cast<const __nv_bfloat16*>(norm_w);
   dim3 grid(B * Hv, (dv + 127) / 128);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   auto* qq = reinterpret_cast<const __nv_bfloat16*>(q);
@@ -678,9 +771,11 @@ extern "C" TYR_EXPORT int tyr_gdr_decode(const void* q, const void* k, const voi
   auto* vv = reinterpret_cast<const __nv_bfloat16*>(v);
   auto* oo = reinterpret_cast<__nv_bfloat16*>(out);
   if (dk == 128)
-    gdr_decode_kernel<128><<<grid, 512, 0, st>>>(qq, kk, vv, g, beta, state, oo, Hk, Hv, dv, q_bstride, v_bstride);
+    gdr_decode_kernel<128><<<grid, 512, 0, st>>>(qq, kk, vv, g, beta, state, oo, Hk, Hv, dv, q_bstride, v_bstride, zz, z_bstride,
+                                                 nw, norm_eps);
   else if (dk == 64)
-    gdr_decode_kernel<64><<<grid, 512, 0, st>>>(qq, kk, vv, g, beta, state, oo, Hk, Hv, dv, q_bstride, v_bstride);
+    gdr_decode_kernel<64><<<grid, 512, 0, st>>>(qq, kk, vv, g, beta, state, oo, Hk, Hv, dv, q_bstride, v_bstride, zz, z_bstride,
+                                                nw, norm_eps);
   else
     return -2;
   return static_cast<int>(cudaGetLastError());

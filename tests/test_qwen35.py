@@ -104,6 +104,40 @@ def test_gpu_gdr_decode_kernel_matches_recurrence():
 
 
 @pytest.mark.gpu
+def test_gpu_gdn_decode_fused_matches_library_op_sequence():
+    """Conv + gates kernel and the recurrent kernel with the gated-norm epilogue against the op-by-op decode branch, on column
+    windows of one projection output, over several tokens (conv window and recurrent state carried in place)."""
+    cfg = tiny(0, hidden_size=256, intermediate_size=512, head_dim=128, half_rotary_dim=32, linear_key_head_dim=128, linear_value_head_dim=128,
+               num_attention_heads=4, num_key_value_heads=1)
+    m = Q.init(cfg, device="cuda", dtype=torch.bfloat16)
+    layer = next(l for i, l in enumerate(m.layers) if not cfg.is_full(i))
+    mix = layer.mixer
+    mix.conv1d_bias = (torch.randn(cfg.linear_conv_dim, device="cuda") * 0.1).bfloat16()
+    B, cd, vd, Hv, K = 5, cfg.linear_conv_dim, cfg.linear_value_dim, cfg.linear_num_value_heads, cfg.linear_conv_kernel_dim
+    g = torch.Generator(device="cuda").manual_seed(2)
+
+    def fresh():
+        gs = torch.Generator(device="cuda").manual_seed(9)
+        return Q.LinearState(torch.randn(B, cd, K, device="cuda", generator=gs).bfloat16(),
+                             torch.randn(B, Hv, cfg.linear_key_head_dim, cfg.linear_value_head_dim, device="cuda", generator=gs) * 0.1)
+    s_ref, s_fused = fresh(), fresh()
+    for t in range(4):
+        proj = torch.randn(B, 1, cd + vd + 2 * Hv + 6, device="cuda", generator=g).bfloat16()
+        views = (proj[..., :cd], proj[..., cd:cd + vd], proj[..., cd + vd:cd + vd + Hv], proj[..., cd + vd + Hv:cd + vd + 2 * Hv])
+        D._GDN_FUSED = False
+        try:
+            ref = Q.gated_delta_net_core(cfg, mix, *views, s_ref)
+        finally:
+            D._GDN_FUSED = True
+        assert D.gdn_decode_fused_supported(views[0], s_fused.conv, s_fused.rec, 128, 128)
+        got = Q.gated_delta_net_core(cfg, mix, *views, s_fused)
+        assert got.shape == ref.shape
+        assert (got.float() - ref.float()).abs().max().item() < 2e-2 * max(1.0, ref.float().abs().max().item()), t
+        assert torch.equal(s_fused.conv, s_ref.conv)
+        assert torch.allclose(s_fused.rec, s_ref.rec, atol=2e-3, rtol=2e-3)
+
+
+@pytest.mark.gpu
 def test_gpu_qwen35_moe_bf16_cached_matches_full_forward():
     cfg = tiny(8, hidden_size=256, head_dim=128, half_rotary_dim=32, linear_key_head_dim=128, linear_value_head_dim=128,
                moe_intermediate_size=128, shared_expert_intermediate_size=128, num_attention_heads=2, num_key_value_heads=1)

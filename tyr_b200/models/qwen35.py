@@ -307,6 +307,9 @@ def gated_delta_net_core(cfg: Qwen35Config, m, mixed, z, b, a, state: Optional[L
     Hk, Hv, dk, dv = cfg.linear_num_key_heads, cfg.linear_num_value_heads, cfg.linear_key_head_dim, cfg.linear_value_head_dim
     z = z.reshape(B, S, Hv, dv)
     step = state is not None and state.conv is not None and S == 1
+    if step and state.rec is not None and dr.gdn_decode_fused_supported(mixed, state.conv, state.rec, dk, dv):
+        return dr.gdn_decode_fused(mixed, z, b, a, state.conv, m.conv1d_weight, m.conv1d_bias, m.dt_bias, m.a_log, m.norm_weight,
+                                   cfg.rms_norm_eps, state.rec, Hk, Hv, dk, dv)
     w = m.conv1d_weight.reshape(cd, K).to(mixed.dtype)
     if step:
         window = torch.cat([state.conv[:, :, 1:], mixed.transpose(1, 2)], dim=2)       # [B, cd, K]

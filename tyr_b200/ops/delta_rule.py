@@ -22,6 +22,14 @@ def _sigs(lib_):
     if fn is not None:
         fn.argtypes = [P, P, P, P, P, P, P, I, I, I, I, I, L, L, P]
         fn.restype = ctypes.c_int
+    fn = getattr(lib_, "tyr_gdr_decode_norm", None)
+    if fn is not None:
+        fn.argtypes = [P, P, P, P, P, P, P, I, I, I, I, I, L, L, P, L, P, ctypes.c_float, P]
+        fn.restype = ctypes.c_int
+    fn = getattr(lib_, "tyr_gdn_conv_gates", None)
+    if fn is not None:
+        fn.argtypes = [P] * 3 + [L, L, L] + [P] * 8 + [I, I, I, I, P]
+        fn.restype = ctypes.c_int
     fn = getattr(lib_, "tyr_gdr_chunk_scan", None)
     if fn is not None:
         fn.argtypes = [P] * 9 + [I, I, I, I, I, I, I, P]
@@ -167,4 +175,46 @@ def gdr_decode_step(q, k, v, g, beta, state: torch.Tensor) -> torch.Tensor:
     qr, kr = q.repeat_interleave(rep, dim=2), k.repeat_interleave(rep, dim=2)
     out, st = recurrent_gated_delta_rule(qr, kr, v, g, beta, state)
     state.copy_(st)
+    return out
+
+
+_GDN_FUSED = os.environ.get("TYR_GDN_DECODE_FUSED", "1") != "0"
+
+
+def gdn_decode_fused_supported(mixed, conv_state, rec_state, dk: int, dv: int) -> bool:
+    return (_GDN_FUSED and mixed.is_cuda and mixed.dtype == torch.bfloat16 and mixed.shape[1] == 1 and mixed.stride(-1) == 1
+            and conv_state is not None and conv_state.dtype == torch.bfloat16 and conv_state.is_contiguous()
+            and rec_state is not None and rec_state.dtype == torch.float32 and rec_state.is_contiguous()
+            and dk in (64, 128) and dv == 128 and hasattr(lib(), "tyr_gdn_conv_gates") and hasattr(lib(), "tyr_gdr_decode_norm"))
+
+
+def gdn_decode_fused(mixed, z, b, a, conv_state, conv_w, conv_b, dt_bias, a_log, norm_w, eps: float, rec_state,
+                     Hk: int, Hv: int, dk: int, dv: int) -> torch.Tensor:
+    """One GatedDeltaNet decode token between the input and output projections in two launches.
+
+    ``mixed`` [B, 1, cd] (q | k | v channels), ``z`` [B, 1, Hv*dv], ``b`` / ``a`` [B, 1, Hv]: column windows of one projection
+    output or separate tensors (rows may be strided).  Kernel 1: causal conv + bias + SiLU with ``conv_state`` ([B, cd, K] bf16) shifted in place,
+    beta = sigmoid(b), g = -softplus(a + dt_bias) * exp(a_log).  Kernel 2: the recurrent step on ``rec_state`` (fp32
+    [B, Hv, dk, dv], in place; L2-normalised q / k inside) with the gated RMSNorm ``norm(o) * norm_w * silu(z)`` in its
+    epilogue.  Returns [B, 1, Hv*dv].  Model.lean:642-779 of the reference, which issues library ops."""
+    B, _, cd = mixed.shape
+    K = conv_state.shape[-1]
+    assert b.stride(-1) == 1 and a.stride(-1) == 1 and z.stride(-1) == 1 and b.dtype == a.dtype == z.dtype == torch.bfloat16
+    dev = mixed.device
+    conv_out = torch.empty((B, cd), dtype=torch.bfloat16, device=dev)
+    g = torch.empty((B, Hv), dtype=torch.float32, device=dev)
+    beta = torch.empty((B, Hv), dtype=torch.float32, device=dev)
+    w = conv_w.reshape(cd, K)
+    if w.dtype != torch.bfloat16 or not w.is_contiguous():
+        w = w.to(torch.bfloat16).contiguous()
+    cb = None if conv_b is None else conv_b.to(torch.bfloat16).contiguous()
+    check(lib().tyr_gdn_conv_gates(ptr(mixed), ptr(b), ptr(a), mixed.stride(0), b.stride(0), a.stride(0), ptr(conv_state), ptr(w), ptr(cb), ptr(dt_bias.float().contiguous()),
+                                   ptr(a_log.float().contiguous()), ptr(conv_out), ptr(g), ptr(beta), B, cd, K, Hv, cur_stream(dev)),
+          "gdn_conv_gates")
+    kd = Hk * dk
+    q, k, v = conv_out[:, :kd], conv_out[:, kd:2 * kd], conv_out[:, 2 * kd:]
+    out = torch.empty((B, 1, Hv * dv), dtype=torch.bfloat16, device=dev)
+    nw = norm_w if (norm_w.dtype == torch.bfloat16 and norm_w.is_contiguous()) else norm_w.to(torch.bfloat16).contiguous()
+    check(lib().tyr_gdr_decode_norm(ptr(q), ptr(k), ptr(v), ptr(g), ptr(beta), ptr(rec_state), ptr(out), B, Hk, Hv, dk, dv, cd, cd,
+                                    ptr(z), z.stride(0), ptr(nw), eps, cur_stream(dev)), "gdr_decode_norm")
     return out
