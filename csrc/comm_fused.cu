@@ -612,6 +612,158 @@ peer_sum_bf16_kernel(PeerPtrs src, int world, long long n, const __nv_bfloat16* 
 }
 }  // namespace tyr
 
+// ---------------------------------------------------------------------------------------------
+// Decode-sized all-reduce of a tensor-parallel sub-layer, with everything that follows it, in one launch:
+//   flag barrier (this rank's partial is published, every peer's partial is waited for, bounded)
+//   -> x = sum over ranks of the bf16 partials [M, N] (peer loads) + residual
+//   -> out_resid = bf16(x);  out_norm = RMSNorm(out_resid) * (w or 1 + w)   (the next sub-layer's input)
+// One CTA per row; the row stays in registers between the sum and the norm.  The barrier's sequence number lives in device
+// memory (the same counter as tyr_barrier_dev uses for the slot), advanced by the last CTA to finish, so the launch can be
+// replayed from a CUDA graph.  Replaces a barrier launch, a peer-sum launch and a norm launch.
+// ---------------------------------------------------------------------------------------------
+namespace tyr {
+struct TpArNormArgs {
+  PeerPtrs part;
+  PeerPtrs flags;
+  const unsigned long long* local_flags;
+  unsigned long long* seq;
+  int* done;
+  const __nv_bfloat16* resid;
+  const __nv_bfloat16* norm_w;
+  __nv_bfloat16* out_resid;
+  __nv_bfloat16* out_norm;
+  int world, my_rank, slot_base, M, N, one_plus_w;
+  float eps;
+  int* err;
+};
+
+constexpr int kArVecs = 4;      // 16-byte vectors per thread: N <= 256 * 4 * 8 = 8192
+
+__global__ void __launch_bounds__(256) tp_allreduce_norm_kernel(TpArNormArgs a) {
+  __shared__ float red[8];
+  const int tid = threadIdx.x;
+  const unsigned long long value = *a.seq + 1;
+  if (blockIdx.x == 0 && tid < a.world) {
+    __threadfence_system();
+    st_release_sys(reinterpret_cast<unsigned long long*>(a.flags.p[tid]) + a.slot_base + a.my_rank, value);
+  }
+  if (tid < a.world) {
+    const unsigned long long* f = a.local_flags + a.slot_base + tid;
+    const long long start = clock64();
+    while (ld_acquire_sys(f) < value) {
+      if (clock64() - start > kWaitBudgetCycles * 4) {
+        report_error(a.err, ERR_PEER_FLAG_TIMEOUT, a.slot_base + tid);
+        break;
+      }
+      __nanosleep(40);
+    }
+  }
+  __syncthreads();
+  const int row = blockIdx.x;
+  const int nvec = a.N >> 3;
+  float x[kArVecs][8];
+  float sq = 0.f;
+#pragma unroll
+  for (int j = 0; j < kArVecs; ++j) {
+    const int v = tid + j * 256;
+    if (v < nvec) {
+      const long long off = static_cast<long long>(row) * a.N + v * 8;
+      uint4 u[kMaxRanks];
+#pragma unroll
+      for (int r = 0; r < kMaxRanks; ++r)
+        if (r < a.world) {
+          const __nv_bfloat16* p = reinterpret_cast<const __nv_bfloat16*>(a.part.p[r]) + off;
+          asm volatile("ld.global.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(u[r].x), "=r"(u[r].y), "=r"(u[r].z), "=r"(u[r].w)
+                       : "l"(p));
+        }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) x[j][e] = 0.f;
+#pragma unroll
+      for (int r = 0; r < kMaxRanks; ++r)
+        if (r < a.world) {
+          const float2 p0 = unpack_bf16x2(u[r].x), p1 = unpack_bf16x2(u[r].y), p2 = unpack_bf16x2(u[r].z), p3 = unpack_bf16x2(u[r].w);
+          x[j][0] += p0.x; x[j][1] += p0.y; x[j][2] += p1.x; x[j][3] += p1.y;
+          x[j][4] += p2.x; x[j][5] += p2.y; x[j][6] += p3.x; x[j][7] += p3.y;
+        }
+      if (a.resid) {
+        const uint4 rv = *reinterpret_cast<const uint4*>(a.resid + off);
+        const float2 p0 = unpack_bf16x2(rv.x), p1 = unpack_bf16x2(rv.y), p2 = unpack_bf16x2(rv.z), p3 = unpack_bf16x2(rv.w);
+        x[j][0] += p0.x; x[j][1] += p0.y; x[j][2] += p1.x; x[j][3] += p1.y;
+        x[j][4] += p2.x; x[j][5] += p2.y; x[j][6] += p3.x; x[j][7] += p3.y;
+      }
+      uint4 o;
+      o.x = pack_bf16x2(x[j][0], x[j][1]); o.y = pack_bf16x2(x[j][2], x[j][3]);
+      o.z = pack_bf16x2(x[j][4], x[j][5]); o.w = pack_bf16x2(x[j][6], x[j][7]);
+      *reinterpret_cast<uint4*>(a.out_resid + off) = o;
+      // the norm sees the rounded residual stream, like a separate norm kernel would
+      const float2 q0 = unpack_bf16x2(o.x), q1 = unpack_bf16x2(o.y), q2 = unpack_bf16x2(o.z), q3 = unpack_bf16x2(o.w);
+      x[j][0] = q0.x; x[j][1] = q0.y; x[j][2] = q1.x; x[j][3] = q1.y; x[j][4] = q2.x; x[j][5] = q2.y; x[j][6] = q3.x; x[j][7] = q3.y;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) sq += x[j][e] * x[j][e];
+    }
+  }
+  if (a.out_norm != nullptr) {
+    sq = warp_sum(sq);
+    if ((tid & 31) == 0) red[tid >> 5] = sq;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) tot += red[i];
+    const float rstd = rsqrtf(tot / static_cast<float>(a.N) + a.eps);
+#pragma unroll
+    for (int j = 0; j < kArVecs; ++j) {
+      const int v = tid + j * 256;
+      if (v < nvec) {
+        const uint4 wv = *reinterpret_cast<const uint4*>(a.norm_w + v * 8);
+        const float2 w0 = unpack_bf16x2(wv.x), w1 = unpack_bf16x2(wv.y), w2 = unpack_bf16x2(wv.z), w3 = unpack_bf16x2(wv.w);
+        const float wf[8] = {w0.x, w0.y, w1.x, w1.y, w2.x, w2.y, w3.x, w3.y};
+        float y[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) y[e] = x[j][e] * rstd * (a.one_plus_w ? 1.f + wf[e] : wf[e]);
+        uint4 o;
+        o.x = pack_bf16x2(y[0], y[1]); o.y = pack_bf16x2(y[2], y[3]); o.z = pack_bf16x2(y[4], y[5]); o.w = pack_bf16x2(y[6], y[7]);
+        *reinterpret_cast<uint4*>(a.out_norm + static_cast<long long>(row) * a.N + v * 8) = o;
+      }
+    }
+  }
+  // the last CTA to get here advances the barrier's sequence number (every CTA has read it by then)
+  __syncthreads();
+  if (tid == 0) {
+    if (atomicAdd(a.done, 1) == static_cast<int>(gridDim.x) - 1) {
+      *a.done = 0;
+      __threadfence();
+      *a.seq = value;
+    }
+  }
+}
+}  // namespace tyr
+
+// part_ptrs / flag_ptrs: per-rank base pointers of the bf16 partial [M, N] and of the flag array; `seq` is the slot's device
+// counter, `done` a zeroed int.  resid, norm_w, out_norm may be null.  N % 8 == 0, N <= 8192, 16-byte aligned pointers.
+extern "C" TYR_EXPORT int tyr_tp_allreduce_norm(void* const* part_ptrs, void* const* flag_ptrs, const void* local_flags, int world,
+                                                int my_rank, int slot_base, void* seq, int* done, const void* resid,
+                                                const void* norm_w, void* out_resid, void* out_norm, int M, int N, int one_plus_w,
+                                                float eps, int* err, void* stream) {
+  using namespace tyr;
+  if (world < 1 || world > kMaxRanks || M <= 0 || N <= 0 || (N & 7) || N > 256 * kArVecs * 8) return -1;
+  if (out_resid == nullptr || seq == nullptr || done == nullptr || (out_norm != nullptr && norm_w == nullptr)) return -1;
+  uintptr_t al = reinterpret_cast<uintptr_t>(resid) | reinterpret_cast<uintptr_t>(norm_w) | reinterpret_cast<uintptr_t>(out_resid) |
+                 reinterpret_cast<uintptr_t>(out_norm);
+  for (int r = 0; r < world; ++r) al |= reinterpret_cast<uintptr_t>(part_ptrs[r]);
+  if (al & 15) return -2;
+  TpArNormArgs a;
+  a.part = make_peers(part_ptrs, world);
+  a.flags = make_peers(flag_ptrs, world);
+  a.local_flags = (const unsigned long long*)local_flags;
+  a.seq = (unsigned long long*)seq; a.done = done;
+  a.resid = (const __nv_bfloat16*)resid; a.norm_w = (const __nv_bfloat16*)norm_w;
+  a.out_resid = (__nv_bfloat16*)out_resid; a.out_norm = (__nv_bfloat16*)out_norm;
+  a.world = world; a.my_rank = my_rank; a.slot_base = slot_base; a.M = M; a.N = N; a.one_plus_w = one_plus_w; a.eps = eps; a.err = err;
+  tp_allreduce_norm_kernel<<<M, 256, 0, (cudaStream_t)stream>>>(a);
+  return (int)cudaGetLastError();
+}
+
 extern "C" TYR_EXPORT int tyr_peer_sum_bf16(void* const* src_ptrs, int world, long long n, const void* add, void* out,
                                             void* stream) {
   if (world < 1 || world > tyr::kMaxRanks || n <= 0 || (n & 7)) return -1;

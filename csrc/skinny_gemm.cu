@@ -1,4 +1,4 @@
-// y[M, N] = x[M, K] @ W[N, K]^T (+ bias) for decode-sized M (1..16 rows): a weight-streaming kernel.  The product is bound
+// y[M, N] = x[M, K] @ W[N, K]^T (+ bias) for decode-sized M (1..32 rows): a weight-streaming kernel.  The product is bound
 // by reading W once from HBM, so a CTA owns 16 weight rows and its 8 warps split K; every lane streams 16 bytes of two
 // weight rows per step straight into mma.sync m16n8k16 A fragments (W rows are the M dimension of the tile, the tokens the
 // N dimension; the reduction over K is order-free, so a lane's 8 consecutive channels serve as the fragment's k-slots and
@@ -147,14 +147,15 @@ extern "C" TYR_EXPORT int tyr_skinny_gemm_splits(int N, int K) {
 extern "C" TYR_EXPORT int tyr_skinny_gemm_bf16(const void* x, const void* w, const void* bias, void* y, void* ws, long long ldx,
                                                long long ldw, long long ldy, int M, int N, int K, void* stream) {
   using namespace tyr;
-  if (M < 1 || M > 16 || N < 1 || K < 32 || (K & 31)) return -1;
+  if (M < 1 || M > 32 || N < 1 || K < 32 || (K & 31)) return -1;
   if ((ldx | ldw) & 7) return -2;                                    // 16-byte loads
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) return -3;
   SkinnyArgs a{(const __nv_bfloat16*)x, (const __nv_bfloat16*)w, nullptr, (const __nv_bfloat16*)bias, (__nv_bfloat16*)y, (float*)ws, ldx, ldw, ldy, M, N, K};
   const int splits = ws != nullptr ? tyr_skinny_gemm_splits(N, K) : 1;
   const dim3 grid((N + 15) / 16, splits);
   if (M <= 8) skinny_gemm_kernel<1, false><<<grid, kSkWarps * 32, 0, (cudaStream_t)stream>>>(a);
-  else skinny_gemm_kernel<2, false><<<grid, kSkWarps * 32, 0, (cudaStream_t)stream>>>(a);
+  else if (M <= 16) skinny_gemm_kernel<2, false><<<grid, kSkWarps * 32, 0, (cudaStream_t)stream>>>(a);
+  else skinny_gemm_kernel<4, false><<<grid, kSkWarps * 32, 0, (cudaStream_t)stream>>>(a);
   if (splits > 1) {
     long long blocks = (static_cast<long long>(M) * N + 255) / 256;
     if (blocks > 592) blocks = 592;
@@ -168,12 +169,13 @@ extern "C" TYR_EXPORT int tyr_skinny_gemm_bf16(const void* x, const void* w, con
 extern "C" TYR_EXPORT int tyr_skinny_swiglu_bf16(const void* x, const void* wg, const void* wu, void* y, long long ldx,
                                                  long long ldw, long long ldy, int M, int N, int K, void* stream) {
   using namespace tyr;
-  if (M < 1 || M > 16 || N < 1 || K < 32 || (K & 31)) return -1;
+  if (M < 1 || M > 32 || N < 1 || K < 32 || (K & 31)) return -1;
   if ((ldx | ldw) & 7) return -2;
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(wg) | reinterpret_cast<uintptr_t>(wu)) & 15) return -3;
   SkinnyArgs a{(const __nv_bfloat16*)x, (const __nv_bfloat16*)wg, (const __nv_bfloat16*)wu, nullptr, (__nv_bfloat16*)y, nullptr, ldx, ldw, ldy, M, N, K};
   const dim3 grid((N + 15) / 16, 1);
   if (M <= 8) skinny_gemm_kernel<1, true><<<grid, kSkWarps * 32, 0, (cudaStream_t)stream>>>(a);
-  else skinny_gemm_kernel<2, true><<<grid, kSkWarps * 32, 0, (cudaStream_t)stream>>>(a);
+  else if (M <= 16) skinny_gemm_kernel<2, true><<<grid, kSkWarps * 32, 0, (cudaStream_t)stream>>>(a);
+  else skinny_gemm_kernel<4, true><<<grid, kSkWarps * 32, 0, (cudaStream_t)stream>>>(a);
   return (int)cudaGetLastError();
 }

@@ -78,6 +78,47 @@ def qwen35_tp_layers_match_single_gpu(rank, world, dev, dtype, full, m, ids, S):
     return ok
 
 
+def qwen35_tp_graph_decode_matches_eager(rank, world, dev, group):
+    """The CUDA-graph decode step (weight-streaming partial products into the symmetric buffer, one barrier + sum + residual +
+    norm kernel per sub-layer, two-launch GatedDeltaNet token) against the same tokens through ``run`` (library product,
+    separate barrier / sum / norm launches, op-by-op GatedDeltaNet)."""
+    from tyr_b200.models import qwen35 as Q, qwen35_tp as QT
+    from tyr_b200.ops import delta_rule as D
+    cfg = Q.Qwen35Config(vocab_size=512, hidden_size=512, intermediate_size=1024, num_hidden_layers=4, num_attention_heads=8, num_key_value_heads=8,
+                         head_dim=128, half_rotary_dim=32, linear_key_head_dim=128, linear_value_head_dim=128, linear_num_key_heads=8,
+                         linear_num_value_heads=16)
+    B, S, steps = 8, 16, 6
+    tp = TensorParallel(rank, world, dev, group=group, max_rows=max(B * S, 128 * world), max_cols=512, max_k=512)
+    m = QT.init_sharded(cfg, rank, world, tp, device=dev, seed=5)
+    ids = torch.randint(0, 512, (B, S), generator=torch.Generator().manual_seed(21)).to(dev)
+    a, b = QT.TPCache(m, B, S + steps + 2), QT.TPCache(m, B, S + steps + 2)
+    if not b.device_step_supported():
+        print(f"rank {rank}: device step unsupported for the test geometry", flush=True)
+        tp.close()
+        return False
+    ta = a.prefill(ids).argmax(-1)
+    tb = b.prefill(ids).argmax(-1)
+    ok = bool(torch.equal(ta, tb))
+    tok = ta
+    for t in range(steps):
+        D._GDN_FUSED = False
+        try:
+            want = a.run(tok.reshape(-1, 1)).float()
+        finally:
+            D._GDN_FUSED = True
+        got = b.step(tok).float()
+        err = (want - got).abs().max().item() / max(1e-6, want.abs().max().item())
+        if not err < 3e-2:
+            print(f"rank {rank} graph decode step {t}: relative error {err:.4f} FAIL", flush=True)
+            ok = False
+        tok = want.argmax(-1)
+    ok = ok and b._graph.replays >= steps - 1
+    if rank == 0:
+        print(f"rank 0 qwen35 tp graph decode: {b._graph.replays} replays, last step error {err:.5f}", flush=True)
+    tp.close()
+    return ok
+
+
 def main():
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     backend = os.environ.get("TYR_TEST_BACKEND", "nccl")
@@ -116,6 +157,8 @@ def main():
             print(f"rank {rank} it {it}: rs err {err} ag err {err2}", flush=True)
             break
     ok &= qwen35_tp_matches_single_gpu(rank, world, dev, dtype, tp.group)
+    if dev.type == "cuda":
+        ok &= qwen35_tp_graph_decode_matches_eager(rank, world, dev, tp.group)
     if dev.type == "cuda":
         torch.cuda.synchronize()
         from tyr_b200.ops._common import raise_on_device_error

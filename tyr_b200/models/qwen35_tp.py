@@ -266,8 +266,11 @@ class TPCache:
         m, cfg, loc, tp = self.m, self.m.cfg, self.m.local, self.m.tp
         eps, B = cfg.rms_norm_eps, tok.numel()
         x = F.embedding(tok.reshape(-1), m.embed_tokens)
+        # every all-reduce hands back the residual stream and the next sub-layer's normed input from one kernel
+        h = Q.rms(x, m.layers[0].input_layernorm, eps)
+        n_layers = len(m.layers)
         for i, l in enumerate(m.layers):
-            proj = lin(Q.rms(x, l.input_layernorm, eps), l.mixer.in_proj).reshape(B, 1, -1)
+            proj = lin(h, l.mixer.in_proj).reshape(B, 1, -1)
             if isinstance(l.mixer, TPAttention):
                 nq, nkv = loc.num_attention_heads * 2 * loc.head_dim, loc.num_key_value_heads * loc.head_dim
                 core = Q.attention_core_decode(loc, l.mixer.q_norm, l.mixer.k_norm, proj[..., :nq], proj[..., nq:nq + nkv], proj[..., nq + nkv:],
@@ -277,10 +280,11 @@ class TPCache:
                 cd, vd, Hv = loc.linear_conv_dim, loc.linear_value_dim, loc.linear_num_value_heads
                 core = Q.gated_delta_net_core(loc, l.mixer, proj[..., :cd], proj[..., cd:cd + vd], proj[..., cd + vd:cd + vd + Hv], proj[..., cd + vd + Hv:cd + vd + 2 * Hv], self.lin[i])
                 w_out = l.mixer.out_proj
-            x = tp.linear_all_reduce(core.reshape(B, -1), w_out, add=x)
-            x = tp.linear_all_reduce(self._mlp_hidden(Q.rms(x, l.post_attention_layernorm, eps), l.ffn.gate_up), l.ffn.down, add=x)
+            x, h = tp.linear_all_reduce_norm(core.reshape(B, -1), w_out, x, l.post_attention_layernorm, eps)
+            next_w = m.layers[i + 1].input_layernorm if i + 1 < n_layers else m.norm
+            x, h = tp.linear_all_reduce_norm(self._mlp_hidden(h, l.ffn.gate_up), l.ffn.down, x, next_w, eps)
         self.pos_t += 1
-        return Q.rms(x, m.norm, eps)
+        return h
 
     def step(self, tok):
         if self.pos == 0 or not self.device_step_supported():

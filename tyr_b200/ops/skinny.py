@@ -1,4 +1,4 @@
-"""Decode-sized linear layers (1..16 rows) on the weight-streaming kernel (csrc/skinny_gemm.cu)."""
+"""Decode-sized linear layers (1..32 rows) on the weight-streaming kernel (csrc/skinny_gemm.cu)."""
 from __future__ import annotations
 
 import ctypes
@@ -10,7 +10,7 @@ import torch
 from .._native import register_signatures
 from ._common import check, cur_stream, lib, ptr
 
-MAX_ROWS = 16
+MAX_ROWS = 32
 _workspaces = {}
 
 
@@ -38,25 +38,34 @@ def _sigs(lib_):
         fn.restype = I
 
 
-def supported(x2: torch.Tensor, w: torch.Tensor) -> bool:
+LINEAR_MAX_ROWS = 16     # plain products above this many rows go to the library GEMM (measured 2.5x faster at 32 rows)
+
+
+def supported(x2: torch.Tensor, w: torch.Tensor, max_rows: int = LINEAR_MAX_ROWS) -> bool:
     M, K = x2.shape
     # 9..16 rows with a long contraction leave too few loads in flight per warp; the library GEMM is faster there
-    return (x2.is_cuda and x2.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and 1 <= M <= MAX_ROWS and (M <= 8 or K <= 8192) and K >= 32 and K % 32 == 0
+    return (x2.is_cuda and x2.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and 1 <= M <= min(max_rows, MAX_ROWS) and (M <= 8 or K <= 8192) and K >= 32 and K % 32 == 0
             and x2.stride(1) == 1 and w.stride(1) == 1 and x2.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
             and x2.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-def skinny_linear(x2: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """x2: [M <= 16, K] bf16, w: [N, K] bf16 (rows may be strided) -> [M, N] bf16 with fp32 accumulation."""
+def skinny_linear(x2: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x2: [M <= 32, K] bf16, w: [N, K] bf16 (rows may be strided) -> [M, N] bf16 with fp32 accumulation; ``out`` (rows may be
+    strided, e.g. a window of a symmetric-heap buffer) receives the result when given."""
     M, K = x2.shape
     N = w.shape[0]
     if not x2.is_cuda:
         y = x2.float() @ w.float().T
-        return (y if bias is None else y + bias.float()).to(x2.dtype)
-    y = torch.empty((M, N), dtype=torch.bfloat16, device=x2.device)
+        y = (y if bias is None else y + bias.float()).to(x2.dtype)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+    y = torch.empty((M, N), dtype=torch.bfloat16, device=x2.device) if out is None else out
+    assert y.shape == (M, N) and y.dtype == torch.bfloat16 and y.stride(1) == 1
     b = None if bias is None else bias.to(torch.bfloat16).contiguous()
     ws = _workspace(x2.device, M, N) if lib().tyr_skinny_gemm_splits(N, K) > 1 else None
-    check(lib().tyr_skinny_gemm_bf16(ptr(x2), ptr(w), ptr(b), ptr(y), ptr(ws), x2.stride(0), w.stride(0), N, M, N, K, cur_stream(x2.device)), "skinny_gemm_bf16")
+    check(lib().tyr_skinny_gemm_bf16(ptr(x2), ptr(w), ptr(b), ptr(y), ptr(ws), x2.stride(0), w.stride(0), y.stride(0), M, N, K, cur_stream(x2.device)), "skinny_gemm_bf16")
     return y
 
 
@@ -64,12 +73,13 @@ _SWIGLU = os.environ.get("TYR_SKINNY_SWIGLU", "1") != "0"
 
 
 def swiglu_supported(x2: torch.Tensor, gate_w: torch.Tensor, up_w: torch.Tensor) -> bool:
-    return (_SWIGLU and supported(x2, gate_w) and supported(x2, up_w) and gate_w.shape == up_w.shape and gate_w.stride(0) == up_w.stride(0)
+    # the gated form replaces a library product plus two element-wise launches and stays ahead of them up to 32 rows
+    return (_SWIGLU and supported(x2, gate_w, MAX_ROWS) and supported(x2, up_w, MAX_ROWS) and gate_w.shape == up_w.shape and gate_w.stride(0) == up_w.stride(0)
             and hasattr(lib(), "tyr_skinny_swiglu_bf16"))
 
 
 def skinny_swiglu(x2: torch.Tensor, gate_w: torch.Tensor, up_w: torch.Tensor) -> torch.Tensor:
-    """x2: [M <= 16, K] bf16 -> silu(x2 gate_w^T) * (x2 up_w^T) as [M, N] bf16: both matrices streamed once, one launch."""
+    """x2: [M <= 32, K] bf16 -> silu(x2 gate_w^T) * (x2 up_w^T) as [M, N] bf16: both matrices streamed once, one launch."""
     M, K = x2.shape
     N = gate_w.shape[0]
     if not x2.is_cuda:

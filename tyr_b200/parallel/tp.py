@@ -42,6 +42,11 @@ def _declare(lib):
     lib.tyr_slot_sum_bf16.restype = ctypes.c_int
     lib.tyr_peer_sum_bf16.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
     lib.tyr_peer_sum_bf16.restype = ctypes.c_int
+    fn = getattr(lib, "tyr_tp_allreduce_norm", None)
+    if fn is not None:
+        P, I = ctypes.c_void_p, ctypes.c_int
+        fn.argtypes = [P, P, P, I, I, I, P, P, P, P, P, P, I, I, I, ctypes.c_float, P, P]
+        fn.restype = I
     lib._tp_declared = True
 
 
@@ -144,6 +149,44 @@ class TensorParallel:
         check(kernels().tyr_peer_sum_bf16(self._peers(part), self.world, M * N, ptr(add.contiguous() if add is not None else None),
                                           ptr(out), cur_stream(x.device)), "peer_sum_bf16")
         return out
+
+    def linear_all_reduce_norm(self, x: torch.Tensor, w: torch.Tensor, add: torch.Tensor, norm_w: Optional[torch.Tensor],
+                               eps: float, one_plus_w: bool = True):
+        """``linear_all_reduce`` followed by the next sub-layer's RMSNorm: returns ``(r, n)`` with ``r = sum_ranks x @ w^T + add``
+        (the new residual stream) and ``n = rmsnorm(r) * (1 + norm_w)`` (``* norm_w`` without ``one_plus_w``; ``None`` when
+        ``norm_w`` is ``None``).  On the fused path the partial product comes from the weight-streaming kernel straight into
+        this rank's symmetric buffer and ONE kernel does the flag barrier, the sum over the peers' partials, the residual add
+        and the norm (``tyr_tp_allreduce_norm``); otherwise it falls back to ``linear_all_reduce`` and the norm op."""
+        from ..ops import skinny
+        from ..ops.norm import rms_norm_weighted
+        M, N = x.shape[0], w.shape[0]
+        fused = (self.fused and x.dtype == torch.bfloat16 and N % 8 == 0 and N <= 8192 and M * N <= self._slots[0].numel()
+                 and add is not None and add.is_contiguous() and hasattr(kernels(), "tyr_tp_allreduce_norm"))
+        if not fused:
+            r = self.linear_all_reduce(x, w, add=add)
+            return r, (None if norm_w is None else rms_norm_weighted(r, norm_w, eps, one_plus_w=one_plus_w))
+        part = self._slots[self._parity]
+        self._parity ^= 1
+        pv = part[:M * N].view(M, N)
+        if skinny.supported(x, w):
+            skinny.skinny_linear(x, w, out=pv)
+        else:
+            torch.matmul(x, w.T, out=pv)
+        bar = self.barrier
+        if getattr(bar, "_seq_dev", None) is None:
+            bar._seq_dev = torch.zeros(bar.n_slots, dtype=torch.int64, device=self.device)
+        if getattr(self, "_ar_done", None) is None:
+            self._ar_done = torch.zeros(1, dtype=torch.int32, device=self.device)
+        nw = None
+        if norm_w is not None:
+            nw = norm_w if (norm_w.dtype == torch.bfloat16 and norm_w.is_contiguous()) else norm_w.to(torch.bfloat16).contiguous()
+        r = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+        n = torch.empty((M, N), dtype=torch.bfloat16, device=x.device) if nw is not None else None
+        check(kernels().tyr_tp_allreduce_norm(self._peers(part), bar._table, ctypes.c_void_p(bar.flags.data_ptr()), self.world, self.rank,
+                                              0, ctypes.c_void_p(bar._seq_dev.data_ptr()), ptr(self._ar_done), ptr(add), ptr(nw), ptr(r), ptr(n),
+                                              M, N, 1 if one_plus_w else 0, eps, ptr(err_word(self.device)), cur_stream(x.device)),
+              "tp_allreduce_norm")
+        return r, n
 
     def all_gather_cols(self, y_local: torch.Tensor) -> torch.Tensor:
         """[M, N_local] per rank -> [M, N_local * world] (rank-major columns); used for vocabulary-parallel logits."""
