@@ -36,7 +36,25 @@ struct DecodeAttnArgs {
   int B, Hq, Hkv, cap, ring, window, splits, append;
   float scale_log2;
   int* err;
+  // optional output gate, applied when the result is written: mode 1 = one value per (batch, head), out *= softplus(g)
+  // (Laguna); mode 2 = one value per element, out *= sigmoid(g) (Qwen3.5).  Element (b, h, d) is at gate + b * gate_bs +
+  // h * gate_hs (+ d in mode 2).
+  const __nv_bfloat16* gate;
+  long long gate_bs, gate_hs;
+  int gate_mode;
 };
+
+__device__ __forceinline__ float decode_gate(const DecodeAttnArgs& a, int b, int h, int d) {
+  if (a.gate_mode == 1) {
+    const float g = __bfloat162float(a.gate[b * a.gate_bs + h * a.gate_hs]);
+    return g > 20.f ? g : log1pf(__expf(g));
+  }
+  if (a.gate_mode == 2) {
+    const float g = __bfloat162float(a.gate[b * a.gate_bs + h * a.gate_hs + d]);
+    return 1.f / (1.f + __expf(-g));
+  }
+  return 1.f;
+}
 
 // One m16n8k16 step.  `lo` accumulates the tile's rows 0..7 (query head g of the lane), `hi` rows 8..15 (head g + 8).
 // With at most 8 query heads per K/V head the upper rows are padding: their A registers are zero and their accumulators
@@ -253,7 +271,7 @@ __global__ void __launch_bounds__(kDecWarps * 32) decode_attention_kernel(Decode
     }
     const long long row = static_cast<long long>(b) * a.Hq + hq0 + g;
     if (a.splits == 1) {
-      a.out[row * D + d] = __float2bfloat16(L > 0.f ? A / L : 0.f);
+      a.out[row * D + d] = __float2bfloat16((L > 0.f ? A / L : 0.f) * decode_gate(a, b, hq0 + g, d));
     } else {
       a.part_acc[(row * a.splits + split) * D + d] = A;
       if (d == 0) {
@@ -284,7 +302,7 @@ __global__ void __launch_bounds__(kDecWarps * 32) decode_attention_kernel(Decode
         A += __ldcg(&a.part_acc[(row * a.splits + sp) * D + d]) * f;
       }
     }
-    a.out[row * D + d] = __float2bfloat16(L > 0.f ? A / L : 0.f);
+    a.out[row * D + d] = __float2bfloat16((L > 0.f ? A / L : 0.f) * decode_gate(a, b, hq0 + g, d));
   }
   if (tid == 0) a.counters[b * a.Hkv + hkv] = 0;
 }
@@ -296,12 +314,29 @@ extern "C" TYR_EXPORT long long tyr_decode_attention_workspace_bytes(int B, int 
   return static_cast<long long>(B) * Hq * splits * (D + 2) * 4 + static_cast<long long>(B) * Hkv * 4;
 }
 
+extern "C" TYR_EXPORT int tyr_decode_attention_gated(const void* q, const void* k_new, const void* v_new, void* k_cache,
+                                                     void* v_cache, const void* pos, void* out, void* workspace, long long q_bs,
+                                                     long long kn_bs, long long vn_bs, int B, int Hq, int Hkv, int D, int cap,
+                                                     int ring, int window, int splits, int append, float scale, const void* gate,
+                                                     long long gate_bs, long long gate_hs, int gate_mode, void* err, void* stream);
+
 // `workspace` must be zero-filled once after allocation (the kernel leaves the counters at zero).
 extern "C" TYR_EXPORT int tyr_decode_attention(const void* q, const void* k_new, const void* v_new, void* k_cache, void* v_cache,
                                                const void* pos, void* out, void* workspace, long long q_bs, long long kn_bs,
                                                long long vn_bs, int B, int Hq, int Hkv, int D, int cap, int ring, int window,
                                                int splits, int append, float scale, void* err, void* stream) {
+  return tyr_decode_attention_gated(q, k_new, v_new, k_cache, v_cache, pos, out, workspace, q_bs, kn_bs, vn_bs, B, Hq, Hkv, D, cap,
+                                    ring, window, splits, append, scale, nullptr, 0, 0, 0, err, stream);
+}
+
+// The same with an output gate folded into the final write (see DecodeAttnArgs::gate).
+extern "C" TYR_EXPORT int tyr_decode_attention_gated(const void* q, const void* k_new, const void* v_new, void* k_cache,
+                                                     void* v_cache, const void* pos, void* out, void* workspace, long long q_bs,
+                                                     long long kn_bs, long long vn_bs, int B, int Hq, int Hkv, int D, int cap,
+                                                     int ring, int window, int splits, int append, float scale, const void* gate,
+                                                     long long gate_bs, long long gate_hs, int gate_mode, void* err, void* stream) {
   using namespace tyr;
+  if (gate_mode < 0 || gate_mode > 2 || (gate_mode != 0 && gate == nullptr)) return -5;
   if (B <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv != 0 || Hq / Hkv > 16 || cap <= 0 || splits < 1 || splits > 64) return -1;
   if (D != 64 && D != 128 && D != 256) return -2;
   const bool wide = Hq / Hkv > 8;
@@ -318,6 +353,7 @@ extern "C" TYR_EXPORT int tyr_decode_attention(const void* q, const void* k_new,
   a.B = B; a.Hq = Hq; a.Hkv = Hkv; a.cap = cap; a.ring = ring; a.window = window; a.splits = splits; a.append = append;
   a.scale_log2 = scale * 1.4426950408889634f;
   a.err = (int*)err;
+  a.gate = (const __nv_bfloat16*)gate; a.gate_bs = gate_bs; a.gate_hs = gate_hs; a.gate_mode = gate == nullptr ? 0 : gate_mode;
   const dim3 grid(splits, Hkv, B);
   const cudaStream_t st = (cudaStream_t)stream;
   if (D == 64 && !wide) decode_attention_kernel<64, false><<<grid, kDecWarps * 32, 0, st>>>(a);

@@ -118,11 +118,14 @@ struct RouteArgs {
 
 // One warp routes one token from its row of logits.  The row may have been written by other CTAs of the same launch, so it is
 // read with L2-coherent loads.
-__device__ __forceinline__ void route_token(const RouteArgs& a, const float* row, int tok, int lane) {
-  constexpr int kMaxPer = 16;   // E <= 512
+// kMaxPer experts per lane (E <= 32 * kMaxPer): the loops below are unrolled over it, so a 64-expert router instantiated
+// with 2 does an eighth of the work of the 512-expert form (the routing of a decode step ran 23 us per layer with 16).
+template <int kMaxPer>
+__device__ __forceinline__ void route_token_n(const RouteArgs& a, const float* row, int tok, int lane) {
   float score[kMaxPer], sel[kMaxPer];
   const int per = (a.E + 31) / 32;
   float mx = -INFINITY;
+#pragma unroll
   for (int j = 0; j < kMaxPer; ++j) {
     const int e = lane + 32 * j;
     float l = (j < per && e < a.E) ? __ldcg(row + e) : -INFINITY;
@@ -182,6 +185,14 @@ __device__ __forceinline__ void route_token(const RouteArgs& a, const float* row
   }
 }
 
+__device__ __forceinline__ void route_token(const RouteArgs& a, const float* row, int tok, int lane) {
+  if (a.E <= 32) route_token_n<1>(a, row, tok, lane);
+  else if (a.E <= 64) route_token_n<2>(a, row, tok, lane);
+  else if (a.E <= 128) route_token_n<4>(a, row, tok, lane);
+  else if (a.E <= 256) route_token_n<8>(a, row, tok, lane);
+  else route_token_n<16>(a, row, tok, lane);       // E <= 512
+}
+
 __global__ void __launch_bounds__(256) moe_route_kernel(RouteArgs a) {
   const int lane = threadIdx.x & 31;
   const int tok = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -189,12 +200,14 @@ __global__ void __launch_bounds__(256) moe_route_kernel(RouteArgs a) {
   route_token(a, a.logits + static_cast<long long>(tok) * a.E, tok, lane);
 }
 
-// Decode-sized batches: router logits and routing in one launch.  CTA (token group, expert group) takes kRouteTok
-// tokens and 8 experts (one per warp): each warp streams its expert's fp32 weight row once and dots it with the
-// group's bf16 activation rows staged in shared memory (fp32 accumulation), so the router matrix is read once per
-// token group.  Logits go to a small global scratch; the last CTA of a token group to finish (atomic ticket) routes the
-// group's tokens, one warp per token.  `tickets` holds one zeroed counter per token group.
-constexpr int kRouteTok = 8;
+// Decode-sized batches: router logits and routing in one launch.  CTA (token group, expert group) takes kRouteTok tokens and
+// kRouteExp experts; two warps share an expert, each streaming half of its fp32 weight row and dotting it with the group's
+// bf16 activation rows staged in shared memory (fp32 accumulation).  Logits go to a small global scratch; the last CTA of
+// a token group to finish (atomic ticket) routes the group's tokens, one warp per token.  `tickets` holds one zeroed counter
+// per token group.  Small groups on purpose: the kernel is a chain of dependent loads and FMAs per warp, so its duration is
+// the instruction count of ONE warp; with 8 tokens x one whole row per warp it ran 20 - 24 us whatever the shape.
+constexpr int kRouteTok = 4;
+constexpr int kRouteExp = 4;
 
 __global__ void __launch_bounds__(256) moe_route_fused_kernel(RouteArgs a, const __nv_bfloat16* __restrict__ x,
                                                               const float* __restrict__ wr, float* __restrict__ logits,
@@ -202,6 +215,7 @@ __global__ void __launch_bounds__(256) moe_route_fused_kernel(RouteArgs a, const
   extern __shared__ __align__(16) uint8_t route_smem[];
   __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(route_smem);     // [kRouteTok][h]
   __shared__ int s_last;
+  __shared__ float s_part[kRouteExp][kRouteTok];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tok0 = blockIdx.x * kRouteTok;
   const int nt = min(kRouteTok, a.T - tok0);
@@ -209,14 +223,17 @@ __global__ void __launch_bounds__(256) moe_route_fused_kernel(RouteArgs a, const
   for (int i = threadIdx.x * 8; i < nt * h; i += blockDim.x * 8)
     *reinterpret_cast<uint4*>(xs + i) = *reinterpret_cast<const uint4*>(x + static_cast<long long>(tok0) * h + i);
   __syncthreads();
-  const int e = blockIdx.y * 8 + warp;
-  if (e < a.E) {
-    float acc[kRouteTok];
+  const int el = warp >> 1, half = warp & 1;          // expert of this warp inside the CTA's group, half of the row
+  const int e = blockIdx.y * kRouteExp + el;
+  float acc[kRouteTok];
 #pragma unroll
-    for (int t = 0; t < kRouteTok; ++t) acc[t] = 0.f;
+  for (int t = 0; t < kRouteTok; ++t) acc[t] = 0.f;
+  if (e < a.E) {
     const float4* w4 = reinterpret_cast<const float4*>(wr + static_cast<long long>(e) * h);
+    const int q4 = h >> 2;                            // float4 groups per row; this warp takes [half * q4 / 2, ...)
+    const int lo = half * (q4 >> 1), hi = half ? q4 : (q4 >> 1);
 #pragma unroll 4
-    for (int i = lane; i < (h >> 2); i += 32) {          // four weight loads in flight per lane
+    for (int i = lo + lane; i < hi; i += 32) {        // four weight loads in flight per lane
       const float4 w = __ldg(w4 + i);
 #pragma unroll
       for (int t = 0; t < kRouteTok; ++t) {
@@ -227,11 +244,18 @@ __global__ void __launch_bounds__(256) moe_route_fused_kernel(RouteArgs a, const
         }
       }
     }
+  }
 #pragma unroll
-    for (int t = 0; t < kRouteTok; ++t) {
-      const float v = warp_sum(acc[t]);
-      if (lane == 0 && t < nt) logits[static_cast<long long>(tok0 + t) * a.E + e] = v;
-    }
+  for (int t = 0; t < kRouteTok; ++t) acc[t] = warp_sum(acc[t]);
+  if (half == 1 && lane == 0) {
+#pragma unroll
+    for (int t = 0; t < kRouteTok; ++t) s_part[el][t] = acc[t];
+  }
+  __syncthreads();
+  if (half == 0 && lane == 0 && e < a.E) {
+#pragma unroll
+    for (int t = 0; t < kRouteTok; ++t)
+      if (t < nt) logits[static_cast<long long>(tok0 + t) * a.E + e] = acc[t] + s_part[el][t];
   }
   __threadfence();
   __syncthreads();
@@ -619,7 +643,7 @@ extern "C" TYR_EXPORT int tyr_moe_route(const float* logits, const float* bias, 
 }
 
 // Router GEMV + routing in one launch: x bf16 [T, h] (h a multiple of 8), router weight fp32 [E, h], `logits` a scratch of
-// T * E floats, `tickets` ceil(T / 8) zeroed ints.
+// T * E floats, `tickets` ceil(T / 4) zeroed ints.
 extern "C" TYR_EXPORT int tyr_moe_route_fused(const void* x, const float* router_w, const float* bias, float* logits,
                                               int* tickets, int* ids, float* weights, int* counts, int T, int E, int k,
                                               int h, int softmax, int renorm, float softcap, float scale, void* stream) {
@@ -633,7 +657,7 @@ extern "C" TYR_EXPORT int tyr_moe_route_fused(const void* x, const float* router
     configured = smem;
   }
   RouteArgs a{nullptr, bias, ids, weights, counts, T, E, k, softmax, renorm, softcap, scale};
-  dim3 grid((T + kRouteTok - 1) / kRouteTok, (E + 7) / 8);
+  dim3 grid((T + kRouteTok - 1) / kRouteTok, (E + kRouteExp - 1) / kRouteExp);
   moe_route_fused_kernel<<<grid, 256, smem, (cudaStream_t)stream>>>(a, (const __nv_bfloat16*)x, router_w, logits,
                                                                     tickets, h);
   return (int)cudaGetLastError();

@@ -263,6 +263,73 @@ __global__ void __launch_bounds__(256) rmsnorm_weighted_kernel(RmsWArgs a) {
   }
 }
 
+// Decode-sized inputs (a few dozen rows of a few thousand channels): one CTA per row, the row stays in registers between
+// the sum of squares and the scaled write, so every operand is read once and the kernel is one load latency deep instead
+// of two loops of eight dependent iterations per warp (8 - 9 us per launch with one warp per row, measured in a decode step).
+constexpr int kRowVecs = 4;     // 16-byte vectors per thread: D <= 256 * 4 * 8
+
+__global__ void __launch_bounds__(256) rmsnorm_weighted_row_kernel(RmsWArgs a) {
+  __shared__ float red[8];
+  const int tid = threadIdx.x;
+  const int nvec = a.D >> 3;
+  const long long base = static_cast<long long>(blockIdx.x) * a.D;
+  float f[kRowVecs][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < kRowVecs; ++j) {
+    const int v = tid + j * 256;
+    if (v < nvec) {
+      load8(a.x + base + v * 8, f[j]);
+      if (a.resid) {
+        float r[8];
+        load8(a.resid + base + v * 8, r);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[j][e] += r[e];
+        if (a.resid_out) {
+          store8(a.resid_out + base + v * 8, f[j]);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) f[j][e] = __bfloat162float(__float2bfloat16(f[j][e]));
+        }
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ss += f[j][e] * f[j][e];
+    }
+  }
+  ss = warp_sum(ss);
+  if ((tid & 31) == 0) red[tid >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) tot += (i < (blockDim.x >> 5)) ? red[i] : 0.f;
+  const float rstd = rsqrtf(tot / a.D + a.eps);
+#pragma unroll
+  for (int j = 0; j < kRowVecs; ++j) {
+    const int v = tid + j * 256;
+    if (v < nvec) {
+      float w[8];
+      if (a.w) {
+        load8(a.w + v * 8, w);
+        if (a.one_plus_w) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) w[e] += 1.f;
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) w[e] = 1.f;
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) f[j][e] = f[j][e] * rstd * w[e];
+      if (a.gate) {
+        float g[8];
+        load8(a.gate + base + v * 8, g);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[j][e] *= g[e] / (1.f + __expf(-g[e]));
+      }
+      store8(a.y + base + v * 8, f[j]);
+    }
+  }
+}
+
 static int grid_for_rows(long long rows, int warps_per_block) {
   long long blocks = (rows + warps_per_block - 1) / warps_per_block;
   const long long cap = 148LL * 16;
@@ -332,6 +399,9 @@ extern "C" TYR_EXPORT int tyr_rmsnorm_weighted(const void* x, const void* w, con
   a.gate = (const __nv_bfloat16*)gate; a.resid = (const __nv_bfloat16*)resid;
   a.resid_out = (__nv_bfloat16*)resid_out; a.y = (__nv_bfloat16*)y;
   a.rows = rows; a.D = D; a.eps = eps; a.one_plus_w = one_plus_w;
-  rmsnorm_weighted_kernel<<<grid_for_rows(rows, 8), 256, 0, (cudaStream_t)stream>>>(a);
+  if (rows <= 2048 && D >= 1024 && D <= 256 * kRowVecs * 8)
+    rmsnorm_weighted_row_kernel<<<rows, 256, 0, (cudaStream_t)stream>>>(a);
+  else
+    rmsnorm_weighted_kernel<<<grid_for_rows(rows, 8), 256, 0, (cudaStream_t)stream>>>(a);
   return (int)cudaGetLastError();
 }

@@ -286,6 +286,24 @@ def test_rmsnorm_weighted_and_rope_norm():
     assert _rel_err(yy.cpu(), yy_ref) < 1e-2
 
 
+@pytest.mark.parametrize("rows,D", [(64, 5120), (7, 8192), (33, 1024), (3000, 2048), (64, 512)])
+def test_rmsnorm_weighted_row_and_warp_kernels(rows, D):
+    """Decode-sized inputs take the one-CTA-per-row kernel, the rest one warp per row; both against the fp32 formula."""
+    from tyr_b200.ops.norm import rms_norm_weighted
+    g = torch.Generator(device="cuda").manual_seed(rows + D)
+    x = torch.randn(rows, D, device=_dev(), generator=g).bfloat16()
+    w = (0.1 * torch.randn(D, device=_dev(), generator=g)).bfloat16()
+    r = torch.randn(rows, D, device=_dev(), generator=g).bfloat16()
+    y, ro = rms_norm_weighted(x, w, 1e-6, one_plus_w=True, residual=r, return_residual=True)
+    s_ref = (x.float() + r.float()).bfloat16()
+    y_ref = s_ref.float() * torch.rsqrt(s_ref.float().pow(2).mean(-1, keepdim=True) + 1e-6) * (1 + w.float())
+    assert torch.equal(ro, s_ref)
+    assert (y.float() - y_ref).abs().max().item() < 2e-2 * max(1.0, y_ref.abs().max().item())
+    y2 = rms_norm_weighted(x, w, 1e-6)
+    y2_ref = x.float() * torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + 1e-6) * w.float()
+    assert (y2.float() - y2_ref).abs().max().item() < 2e-2 * max(1.0, y2_ref.abs().max().item())
+
+
 def test_embedding_grad_sorted_matches_index_add():
     """Zipf-like tokens (a few ids own most rows), row strides of a packed buffer, ids at both ends of the table."""
     from tyr_b200.ops import embed
@@ -463,6 +481,32 @@ def test_decode_attention_matches_reference(B, Hq, Hkv, D, cap, pos, ring, windo
     torch.cuda.synchronize()
     assert torch.equal(kd.cpu(), kc_ref) and torch.equal(vd.cpu(), vc_ref)
     assert (out.float().cpu() - ref.float()).abs().max() < 2e-2
+    # output gates folded into the final write: per head softplus, per element sigmoid (strided views of wider rows)
+    hg = torch.randn(B, Hq + 3, generator=g).to(torch.bfloat16).cuda()[:, 1:Hq + 1]
+    eg = torch.randn(B, Hq, 2 * D, generator=g).to(torch.bfloat16).cuda()[..., D:]
+    for kw, factor in (({"head_gate": hg}, torch.nn.functional.softplus(hg.float()).unsqueeze(-1)), ({"elem_gate": eg}, torch.sigmoid(eg.float()))):
+        got = decode_attention(qv, kv, vv, kd, vd, pt.cuda(), ring=ring, window=window, splits=splits, append=False, **kw)
+        want = out.float() * factor
+        assert (got.float() - want).abs().max().item() < 2e-2 * max(1.0, want.abs().max().item()), list(kw)
+
+
+@pytest.mark.parametrize("M,N,K", [(17, 512, 1024), (32, 2176, 5120), (25, 100, 96)])
+def test_skinny_swiglu_up_to_32_rows_and_strided_out(M, N, K):
+    from tyr_b200.ops import skinny
+    g = torch.Generator().manual_seed(M + N)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
+    wg = (torch.randn(N, K, generator=g) * K ** -0.5).to(torch.bfloat16).cuda()
+    wu = (torch.randn(N, K, generator=g) * K ** -0.5).to(torch.bfloat16).cuda()
+    assert skinny.swiglu_supported(x, wg, wu) and not skinny.supported(x, wg)       # plain products stop at 16 rows
+    ref = torch.nn.functional.silu(x.float() @ wg.float().T) * (x.float() @ wu.float().T)
+    got = skinny.skinny_swiglu(x, wg, wu)
+    assert (got.float() - ref).abs().max().item() < 2e-2 * max(1.0, ref.abs().max().item())
+    # the plain kernel itself handles 32 rows (used through out= by callers that choose it) and strided outputs
+    buf = torch.zeros(M, N + 16, dtype=torch.bfloat16, device="cuda")
+    skinny.skinny_linear(x, wg, out=buf[:, 8:8 + N])
+    ref2 = x.float() @ wg.float().T
+    assert (buf[:, 8:8 + N].float() - ref2).abs().max().item() < 2e-2 * max(1.0, ref2.abs().max().item())
+    assert torch.equal(buf[:, :8], torch.zeros_like(buf[:, :8])) and torch.equal(buf[:, 8 + N:], torch.zeros_like(buf[:, 8 + N:]))
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 3072, 9216), (3, 100, 64), (8, 4096, 1024), (9, 1000, 2048), (16, 272, 3072)])

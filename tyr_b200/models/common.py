@@ -57,8 +57,10 @@ def swiglu_mlp(x, gate_w, up_w, down_w):
     return lin(F.silu(lin(x, gate_w)) * lin(x, up_w), down_w)
 
 
-def norm_w(x, w, eps, one_plus_w: bool = False):
-    return rms_norm_weighted(x, w, eps, one_plus_w=one_plus_w)
+def norm_w(x, w, eps, one_plus_w: bool = False, residual=None, return_residual: bool = False):
+    """Weighted RMSNorm; with ``residual`` the norm is taken of ``x + residual`` in the same kernel and, with
+    ``return_residual``, the sum comes back as the second result (the new residual stream)."""
+    return rms_norm_weighted(x, w, eps, one_plus_w=one_plus_w, residual=residual, return_residual=return_residual)
 
 
 # ---- rotary ---------------------------------------------------------------------------------------

@@ -407,22 +407,27 @@ def attention_decode(cfg: LagunaConfig, i: int, a: Attention, x: torch.Tensor, t
     rot = 2 * cos.shape[1]
     q = rope_norm(q, cos, sin, weight=a.q_norm, positions=positions, rot=rot, eps=cfg.rms_norm_eps)
     k = rope_norm(k, cos, sin, weight=a.k_norm, positions=positions, rot=rot, eps=cfg.rms_norm_eps)
-    o = decode_attention(q, k, v, cache.k, cache.v, pos_t, ring=cache.ring, window=None if cfg.is_full(i) else cfg.sliding_window)
-    gated = (o * F.softplus(g.float()).to(x.dtype).unsqueeze(-1)).reshape(B, 1, H * D)
-    return lin(gated, a.o_proj)
+    # the per-head softplus gate is applied inside the attention kernel's final write
+    o = decode_attention(q, k, v, cache.k, cache.v, pos_t, ring=cache.ring, window=None if cfg.is_full(i) else cfg.sliding_window,
+                         head_gate=g)
+    return lin(o.reshape(B, 1, H * D), a.o_proj)
 
 
-def layer_decode(cfg: LagunaConfig, i: int, layer: Layer, x: torch.Tensor, tables: RotaryTables, pos_t: torch.Tensor,
-                 cache: KVCache, use_fused: bool = True, ep=None) -> torch.Tensor:
+def layer_decode(cfg: LagunaConfig, i: int, layer: Layer, x: torch.Tensor, h1: torch.Tensor, next_norm: torch.Tensor,
+                 tables: RotaryTables, pos_t: torch.Tensor, cache: KVCache, use_fused: bool = True, ep=None):
+    """One decode layer on the residual stream ``x`` whose input norm ``h1`` is already taken.  Returns the new residual
+    stream and its norm under ``next_norm`` (the next layer's input norm or the final norm): each residual add runs inside
+    the norm kernel that follows it."""
     B, S, h = x.shape
-    h1 = norm_w(x, layer.input_layernorm, cfg.rms_norm_eps)
-    h2 = x + attention_decode(cfg, i, layer.attn, h1, tables, pos_t, cache)
-    h3 = norm_w(h2, layer.post_attention_layernorm, cfg.rms_norm_eps)
+    eps = cfg.rms_norm_eps
+    h3, h2 = norm_w(attention_decode(cfg, i, layer.attn, h1, tables, pos_t, cache), layer.post_attention_layernorm, eps,
+                    residual=x, return_residual=True)
     if isinstance(layer.ffn, DenseMLP):
         f = swiglu_mlp(h3, layer.ffn.gate_proj, layer.ffn.up_proj, layer.ffn.down_proj)
     else:
         f = moe_forward(cfg, layer.ffn, h3.reshape(B * S, h), use_fused, ep).reshape(B, S, h)
-    return h2 + f
+    h_next, x_new = norm_w(f, next_norm, eps, residual=h2, return_residual=True)
+    return x_new, h_next
 
 
 def layer_forward(cfg: LagunaConfig, i: int, layer: Layer, x: torch.Tensor, tables: RotaryTables, position: int,
@@ -516,9 +521,12 @@ class CacheSession:
         x = F.embedding(tokens.reshape(self.batch, 1), self.m.embed_tokens)
         if self.m.ep is not None and len(self.m.layers) % 2:
             self.m.ep._sync(0)    # odd depth: the first layer of a replay reuses the exchange buffers of the last layer before it
-        for i, layer in enumerate(self.m.layers):
-            x = layer_decode(cfg, i, layer, x, self.tables, self.pos_t, self.caches[i], use_fused, self.m.ep)
-        logits = lin(norm_w(x, self.m.norm, cfg.rms_norm_eps)[:, -1], self.m.lm_head)
+        layers = self.m.layers
+        h1 = norm_w(x, layers[0].input_layernorm, cfg.rms_norm_eps)
+        for i, layer in enumerate(layers):
+            next_norm = layers[i + 1].input_layernorm if i + 1 < len(layers) else self.m.norm
+            x, h1 = layer_decode(cfg, i, layer, x, h1, next_norm, self.tables, self.pos_t, self.caches[i], use_fused, self.m.ep)
+        logits = lin(h1[:, -1], self.m.lm_head)
         self.pos_t += 1
         return logits
 

@@ -276,8 +276,9 @@ def attention_core_decode(cfg: Qwen35Config, q_norm, k_norm, qg, k, v, cos_table
     rot = 2 * cos_table.shape[1]
     q = rope_norm(qg[..., :D], cos_table, sin_table, weight=q_norm, positions=positions, rot=rot, eps=cfg.rms_norm_eps, one_plus_w=True)
     kn = rope_norm(k.reshape(B, Hkv, D), cos_table, sin_table, weight=k_norm, positions=positions, rot=rot, eps=cfg.rms_norm_eps, one_plus_w=True)
-    o = decode_attention(q, kn, v.reshape(B, Hkv, D), cache.k, cache.v, pos_t)
-    return (o.reshape(B, 1, H * D) * torch.sigmoid(qg[..., D:].reshape(B, 1, H * D)))
+    # the element-wise sigmoid gate is applied inside the attention kernel's final write
+    o = decode_attention(q, kn, v.reshape(B, Hkv, D), cache.k, cache.v, pos_t, elem_gate=qg[..., D:])
+    return o.reshape(B, 1, H * D)
 
 
 def attention_forward(cfg: Qwen35Config, a: Attention, x, cos, sin, cache: Optional[KVCache], attn_mask=None):
@@ -430,8 +431,9 @@ class HybridCache:
         m, cfg = self.m, self.m.cfg
         eps = cfg.rms_norm_eps
         x = F.embedding(tok.reshape(-1, 1), m.embed_tokens)
+        n_layers = len(m.layers)
+        h1 = rms(x, m.layers[0].input_layernorm, eps)
         for i, l in enumerate(m.layers):
-            h1 = rms(x, l.input_layernorm, eps)
             if cfg.is_full(i):
                 a = l.mixer
                 o = attention_core_decode(cfg, a.q_norm, a.k_norm, lin(h1, a.q_proj), lin(h1, a.k_proj), lin(h1, a.v_proj), self.cos, self.sin,
@@ -439,13 +441,14 @@ class HybridCache:
                 mixed = lin(o, a.o_proj)
             else:
                 mixed = gated_delta_net_forward(cfg, l.mixer, h1, self.lin[i])
-            h2 = x + mixed
-            h3 = rms(h2, l.post_attention_layernorm, eps)
+            # residual add and the next norm in one kernel: (normed, new residual stream)
+            h3, h2 = norm_w(mixed, l.post_attention_layernorm, eps, one_plus_w=True, residual=x, return_residual=True)
             f = swiglu_mlp(h3, l.ffn.gate_proj, l.ffn.up_proj, l.ffn.down_proj) if isinstance(l.ffn, MLP) else \
                 moe_forward(cfg, l.ffn, h3.reshape(-1, cfg.hidden_size)).reshape(h3.shape)
-            x = h2 + f
+            next_w = m.layers[i + 1].input_layernorm if i + 1 < n_layers else m.norm
+            h1, x = norm_w(f, next_w, eps, one_plus_w=True, residual=h2, return_residual=True)
         self.pos_t += 1
-        return lin(rms(x[:, -1], m.norm, eps), m.lm_head)
+        return lin(h1[:, -1], m.lm_head)
 
     def _advance_host(self):
         self.pos += 1

@@ -23,6 +23,10 @@ def _sigs(lib_):
     if fn is not None:
         fn.argtypes = [P, P, P, P, P, P, P, P, L, L, L, I, I, I, I, I, I, I, I, I, F, P, P]
         fn.restype = I
+        g = getattr(lib_, "tyr_decode_attention_gated", None)
+        if g is not None:
+            g.argtypes = [P, P, P, P, P, P, P, P, L, L, L, I, I, I, I, I, I, I, I, I, F, P, L, L, I, P, P]
+            g.restype = I
         lib_.tyr_decode_attention_workspace_bytes.argtypes = [I, I, I, I, I]
         lib_.tyr_decode_attention_workspace_bytes.restype = L
 
@@ -49,11 +53,14 @@ def _rows_ok(t: torch.Tensor, D: int) -> bool:
 
 def decode_attention(q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                      pos: torch.Tensor, *, ring: bool = False, window: Optional[int] = None, scale: Optional[float] = None,
-                     append: bool = True, splits: Optional[int] = None) -> torch.Tensor:
+                     append: bool = True, splits: Optional[int] = None, head_gate: Optional[torch.Tensor] = None,
+                     elem_gate: Optional[torch.Tensor] = None) -> torch.Tensor:
     """q: [B, Hq, D]; k_new, v_new: [B, Hkv, D] (the new position, RoPE applied); stores ``[B, Hkv, cap, D]``;
     ``pos``: int32 tensor holding the absolute position of the new token.  Writes the new K/V at slot ``pos`` (``pos % cap``
     for a ring store) when ``append`` and returns the attention of the new query over the retained keys (all of a ring
-    store; the last ``window`` positions of a plain one), ``[B, Hq, D]``."""
+    store; the last ``window`` positions of a plain one), ``[B, Hq, D]``.  ``head_gate`` ([B, Hq]) multiplies each head's
+    output by ``softplus(gate)``, ``elem_gate`` ([B, Hq, D]) each element by ``sigmoid(gate)``; on the GPU the gate is
+    applied inside the kernel's final write."""
     B, Hq, D = q.shape
     Hkv, cap = k_cache.shape[1], k_cache.shape[2]
     sc = scale if scale is not None else 1.0 / math.sqrt(D)
@@ -73,7 +80,12 @@ def decode_attention(q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor, 
         k[:, :, slot - lo], v[:, :, slot - lo] = k_new.float(), v_new.float()
         G = Hq // Hkv
         s = torch.einsum("bhgd,bhkd->bhgk", q.float().reshape(B, Hkv, G, D), k) * sc
-        return torch.einsum("bhgk,bhkd->bhgd", torch.softmax(s, -1), v).reshape(B, Hq, D).to(q.dtype)
+        o = torch.einsum("bhgk,bhkd->bhgd", torch.softmax(s, -1), v).reshape(B, Hq, D)
+        if head_gate is not None:
+            o = o * torch.nn.functional.softplus(head_gate.float()).unsqueeze(-1)
+        if elem_gate is not None:
+            o = o * torch.sigmoid(elem_gate.float())
+        return o.to(q.dtype)
     if not supported(q, Hkv):
         raise ValueError(f"decode_attention: unsupported geometry Hq={Hq} Hkv={Hkv} D={D} dtype={q.dtype}")
     if not k_cache.is_contiguous() or not v_cache.is_contiguous():
@@ -87,7 +99,22 @@ def decode_attention(q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor, 
     if ws is None:
         ws = _workspaces[key] = torch.zeros(lib().tyr_decode_attention_workspace_bytes(B, Hq, Hkv, D, splits) // 4, dtype=torch.int32, device=q.device)
     out = torch.empty((B, Hq, D), dtype=q.dtype, device=q.device)
-    check(lib().tyr_decode_attention(ptr(q), ptr(k_new), ptr(v_new), ptr(k_cache), ptr(v_cache), ptr(pos), ptr(out), ptr(ws),
-                                     q.stride(0), k_new.stride(0), v_new.stride(0), B, Hq, Hkv, D, cap, 1 if ring else 0, int(window or 0),
-                                     splits, 1 if append else 0, sc, ptr(err_word(q.device)), cur_stream(q.device)), "decode_attention")
+    gate, mode = None, 0
+    if head_gate is not None:
+        gate, mode = head_gate, 1
+        assert gate.shape == (B, Hq) and gate.dtype == torch.bfloat16 and elem_gate is None
+        gs = (gate.stride(0), gate.stride(1))
+    elif elem_gate is not None:
+        gate, mode = elem_gate, 2
+        assert gate.shape == (B, Hq, D) and gate.dtype == torch.bfloat16 and gate.stride(2) == 1
+        gs = (gate.stride(0), gate.stride(1))
+    if gate is None:
+        check(lib().tyr_decode_attention(ptr(q), ptr(k_new), ptr(v_new), ptr(k_cache), ptr(v_cache), ptr(pos), ptr(out), ptr(ws),
+                                         q.stride(0), k_new.stride(0), v_new.stride(0), B, Hq, Hkv, D, cap, 1 if ring else 0, int(window or 0),
+                                         splits, 1 if append else 0, sc, ptr(err_word(q.device)), cur_stream(q.device)), "decode_attention")
+    else:
+        check(lib().tyr_decode_attention_gated(ptr(q), ptr(k_new), ptr(v_new), ptr(k_cache), ptr(v_cache), ptr(pos), ptr(out), ptr(ws),
+                                               q.stride(0), k_new.stride(0), v_new.stride(0), B, Hq, Hkv, D, cap, 1 if ring else 0,
+                                               int(window or 0), splits, 1 if append else 0, sc, ptr(gate), gs[0], gs[1], mode,
+                                               ptr(err_word(q.device)), cur_stream(q.device)), "decode_attention_gated")
     return out

@@ -169,7 +169,7 @@ def route_fused(x: torch.Tensor, router_w: torch.Tensor, k: int, *, softmax: boo
     T, E = x.shape[0], router_w.shape[0]
     ids = torch.empty((T, k), dtype=torch.int32, device=x.device)
     w = torch.empty((T, k), dtype=torch.float32, device=x.device)
-    zeros = torch.zeros(E + (T + 7) // 8, dtype=torch.int32, device=x.device)       # expert counts, then one ticket per token group
+    zeros = torch.zeros(E + (T + 3) // 4, dtype=torch.int32, device=x.device)       # expert counts, then one ticket per group of 4 tokens
     counts, tickets = zeros[:E], zeros[E:]
     logits = torch.empty((T, E), dtype=torch.float32, device=x.device)
     b = bias.float().contiguous() if bias is not None else None
