@@ -39,7 +39,8 @@ def main(argv=None):
     import dataclasses
     cfg = dataclasses.replace(PRESETS[a.preset](), num_hidden_layers=a.layers, layer_types=None)
     B, S = a.batch, a.prompt
-    tp = TensorParallel(rank, world, dev, max_rows=max(B * S, 1024), max_cols=cfg.hidden_size, max_k=cfg.hidden_size)
+    tp = TensorParallel(rank, world, dev, max_rows=max(B * S, 1024), max_cols=cfg.hidden_size, max_k=cfg.hidden_size,
+                        gather_elems=B * -(-cfg.vocab_size // world))
     m = QT.init_sharded(cfg, rank, world, tp, device=dev)
     cache = QT.TPCache(m, B, S + a.steps + 16)
     ids = torch.randint(0, cfg.vocab_size, (B, S), device=dev, generator=torch.Generator(device=dev).manual_seed(1))

@@ -764,6 +764,55 @@ extern "C" TYR_EXPORT int tyr_tp_allreduce_norm(void* const* part_ptrs, void* co
   return (int)cudaGetLastError();
 }
 
+// Column gather of a vocabulary-parallel product: every rank holds y_r [M, Nl] bf16 at the same offset of its heap;
+// out[m, r * Nl + c] = y_r[m, c] on every rank, read with 16-byte peer loads (Nl % 8 == 0).  The caller orders it after a flag
+// barrier.  Replaces an NCCL all-gather plus a concatenation.
+namespace tyr {
+__global__ void __launch_bounds__(256)
+peer_gather_cols_bf16_kernel(PeerPtrs src, int world, int M, int Nl, __nv_bfloat16* __restrict__ out) {
+  const int vpr = Nl >> 3;                                    // vectors per source row
+  const long long total = static_cast<long long>(world) * M * vpr;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i0 = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i0 < total; i0 += 4 * stride) {
+    uint4 t[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const long long i = i0 + u * stride;
+      if (i < total) {
+        const int r = static_cast<int>(i / (static_cast<long long>(M) * vpr));
+        const long long j = i - static_cast<long long>(r) * M * vpr;
+        const __nv_bfloat16* p = reinterpret_cast<const __nv_bfloat16*>(src.p[r]) + j * 8;
+        asm volatile("ld.global.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(t[u].x), "=r"(t[u].y), "=r"(t[u].z), "=r"(t[u].w)
+                     : "l"(p));
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const long long i = i0 + u * stride;
+      if (i < total) {
+        const int r = static_cast<int>(i / (static_cast<long long>(M) * vpr));
+        const long long j = i - static_cast<long long>(r) * M * vpr;
+        const int m = static_cast<int>(j / vpr), c = static_cast<int>(j - static_cast<long long>(m) * vpr);
+        *reinterpret_cast<uint4*>(out + (static_cast<long long>(m) * world + r) * Nl + c * 8) = t[u];
+      }
+    }
+  }
+}
+}  // namespace tyr
+
+extern "C" TYR_EXPORT int tyr_peer_gather_cols_bf16(void* const* src_ptrs, int world, int M, int Nl, void* out, void* stream) {
+  if (world < 1 || world > tyr::kMaxRanks || M <= 0 || Nl <= 0 || (Nl & 7) || (reinterpret_cast<uintptr_t>(out) & 15)) return -1;
+  for (int r = 0; r < world; ++r)
+    if (reinterpret_cast<uintptr_t>(src_ptrs[r]) & 15) return -1;
+  long long blocks = (static_cast<long long>(world) * M * (Nl >> 3) + 1023) / 1024;
+  if (blocks > 148 * 4) blocks = 148 * 4;
+  if (blocks < 1) blocks = 1;
+  tyr::peer_gather_cols_bf16_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>(make_peers(src_ptrs, world), world, M, Nl,
+                                                                                   (__nv_bfloat16*)out);
+  return (int)cudaGetLastError();
+}
+
 extern "C" TYR_EXPORT int tyr_peer_sum_bf16(void* const* src_ptrs, int world, long long n, const void* add, void* out,
                                             void* stream) {
   if (world < 1 || world > tyr::kMaxRanks || n <= 0 || (n & 7)) return -1;

@@ -88,8 +88,18 @@ def qwen35_tp_graph_decode_matches_eager(rank, world, dev, group):
                          head_dim=128, half_rotary_dim=32, linear_key_head_dim=128, linear_value_head_dim=128, linear_num_key_heads=8,
                          linear_num_value_heads=16)
     B, S, steps = 8, 16, 6
-    tp = TensorParallel(rank, world, dev, group=group, max_rows=max(B * S, 128 * world), max_cols=512, max_k=512)
+    tp = TensorParallel(rank, world, dev, group=group, max_rows=max(B * S, 128 * world), max_cols=512, max_k=512, gather_elems=B * 512)
     m = QT.init_sharded(cfg, rank, world, tp, device=dev, seed=5)
+    # the vocabulary-parallel column gather through peer loads against the transport's all-gather
+    for rep_ in range(3):
+        y_local = torch.randn(B, 512 // world, device=dev, generator=torch.Generator(device=dev).manual_seed(rank * 10 + rep_)).bfloat16()
+        got = tp.all_gather_cols(y_local)
+        parts = [torch.empty_like(y_local) for _ in range(world)]
+        dist.all_gather(parts, y_local, group=group)
+        if not torch.equal(got, torch.cat(parts, dim=-1)):
+            print(f"rank {rank}: peer column gather differs from all_gather (call {rep_})", flush=True)
+            tp.close()
+            return False
     ids = torch.randint(0, 512, (B, S), generator=torch.Generator().manual_seed(21)).to(dev)
     a, b = QT.TPCache(m, B, S + steps + 2), QT.TPCache(m, B, S + steps + 2)
     if not b.device_step_supported():

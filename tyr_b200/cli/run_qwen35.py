@@ -122,7 +122,8 @@ def main(argv=None):
         from ..models import qwen35_tp as QT
         from ..parallel.tp import TensorParallel
         rows = a.batch_size * ids.shape[1]
-        tp = TensorParallel(rank, world, dev, max_rows=max(rows, 128 * world), max_cols=cfg.hidden_size, max_k=cfg.hidden_size)
+        tp = TensorParallel(rank, world, dev, max_rows=max(rows, 128 * world), max_cols=cfg.hidden_size, max_k=cfg.hidden_size,
+                            gather_elems=a.batch_size * -(-cfg.vocab_size // world))
         if a.random_init:
             model = QT.init_sharded(cfg, rank, world, tp, dev, dtype)
         else:

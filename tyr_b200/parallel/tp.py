@@ -42,6 +42,10 @@ def _declare(lib):
     lib.tyr_slot_sum_bf16.restype = ctypes.c_int
     lib.tyr_peer_sum_bf16.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
     lib.tyr_peer_sum_bf16.restype = ctypes.c_int
+    fn = getattr(lib, "tyr_peer_gather_cols_bf16", None)
+    if fn is not None:
+        fn.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p]
+        fn.restype = ctypes.c_int
     fn = getattr(lib, "tyr_tp_allreduce_norm", None)
     if fn is not None:
         P, I = ctypes.c_void_p, ctypes.c_int
@@ -52,9 +56,12 @@ def _declare(lib):
 
 class TensorParallel:
     """Buffers are sized once: ``max_rows`` total activation rows (all ranks), ``max_cols`` widest
-    reduce-scatter output, ``max_k`` widest gathered input."""
+    reduce-scatter output, ``max_k`` widest gathered input, ``gather_elems`` the largest per-rank block that
+    ``all_gather_cols`` gathers through peer loads (rows x local columns, e.g. decode batch x vocabulary / world; 0: that
+    call uses the transport)."""
 
-    def __init__(self, rank: int, world: int, device, group=None, max_rows: int = 8192, max_cols: int = 8192, max_k: int = 8192):
+    def __init__(self, rank: int, world: int, device, group=None, max_rows: int = 8192, max_cols: int = 8192, max_k: int = 8192,
+                 gather_elems: int = 0):
         self.rank, self.world, self.group = rank, world, group
         self.device = torch.device(device)
         self.fused = self.device.type == "cuda" and world > 1
@@ -69,9 +76,11 @@ class TensorParallel:
         rpr = (max_rows + world - 1) // world
         slot_bytes = world * rpr * max_cols * 2
         stage_bytes = rpr * max_k * 2
-        self.heap = SymmetricHeap(2 * slot_bytes + 2 * stage_bytes + 65536, rank, world, self.device, group)
+        self.heap = SymmetricHeap(2 * slot_bytes + 2 * stage_bytes + 4 * gather_elems + 65536, rank, world, self.device, group)
         self._slots = [self.heap.alloc((world * rpr * max_cols,), torch.bfloat16) for _ in range(2)]
         self._stage = [self.heap.alloc((rpr * max_k,), torch.bfloat16) for _ in range(2)]
+        self._gcols = [self.heap.alloc((gather_elems,), torch.bfloat16) for _ in range(2)] if gather_elems > 0 else None
+        self._gparity = 0
         self.barrier = FlagBarrier(self.heap, n_slots=2)
         # landing buffer of the all-gather GEMM (peers' rows cross NVLink once) and its per-row-tile counters
         self._gather = torch.empty((world * rpr * max_k,), dtype=torch.bfloat16, device=self.device)
@@ -192,6 +201,19 @@ class TensorParallel:
         """[M, N_local] per rank -> [M, N_local * world] (rank-major columns); used for vocabulary-parallel logits."""
         if self.world == 1:
             return y_local
+        M, Nl = y_local.shape
+        if (self.fused and self._gcols is not None and y_local.dtype == torch.bfloat16 and Nl % 8 == 0
+                and M * Nl <= self._gcols[0].numel() and hasattr(kernels(), "tyr_peer_gather_cols_bf16")):
+            # peer loads: the block goes into this rank's symmetric buffer (two alternate, so a rank that is already a call
+            # ahead cannot overwrite what a slower peer still reads), one flag barrier, every rank pulls all blocks
+            buf = self._gcols[self._gparity]
+            self._gparity ^= 1
+            buf[:M * Nl].view(M, Nl).copy_(y_local)
+            self._sync(1)
+            out = torch.empty((M, Nl * self.world), dtype=torch.bfloat16, device=y_local.device)
+            check(kernels().tyr_peer_gather_cols_bf16(self._peers(buf), self.world, M, Nl, ptr(out), cur_stream(y_local.device)),
+                  "peer_gather_cols_bf16")
+            return out
         parts = [torch.empty_like(y_local) for _ in range(self.world)]
         dist.all_gather(parts, y_local.contiguous(), group=self.group)
         return torch.cat(parts, dim=-1)
