@@ -43,6 +43,7 @@ constexpr int F4_STAGES = 5;
 constexpr int F4_SF_STAGE = 2048;      // scale bytes per 128 rows and stage
 constexpr uint32_t F4_COL_SFA = 256;   // TMEM columns: accumulators 0..255, then 16 columns per stage for each operand's scales
 constexpr uint32_t F4_COL_SFB = 256 + 16 * F4_STAGES;
+constexpr int F4_MAX_GROUPS = 1024;    // experts per call (their prefix tables are staged in shared memory)
 
 struct Fp4Params {
   int N, K;                    // weight rows per expert, reduction length in elements (multiple of 256)
@@ -51,6 +52,7 @@ struct Fp4Params {
   const int* group_rows;       // [groups + 1] exclusive prefix of true rows (device memory)
   const uint8_t* sfa;          // activation scales, tensor-core order over the padded rows
   const uint8_t* sfb;          // weight scales, tensor-core order, [groups][N / 128][K / 64][512]
+  const uint8_t* w_tiled;      // weights as shared-memory images: [groups][N / 128][K / 256][128 rows x 128 bytes, 128B swizzle]
   const float* a_row_scale;    // [padded rows] or nullptr (= 1)
   const float* w_global;       // [groups]: result is divided by it
   const float* w_global2;      // mode 1: the global of the `up` bank (w_global is the gate bank's)
@@ -70,6 +72,11 @@ struct __align__(1024) Fp4Smem {
   uint64_t acc_full[2];
   uint64_t acc_empty[2];
   uint32_t tmem_base;
+  // copies of the two per-expert prefix tables: every role finds a tile's expert by binary search, and with the tables in
+  // global memory that was six dependent L2 round trips per tile in the producer (2 - 3 us during which the five-stage ring
+  // ran dry: a decode-sized product has only three to eight stages per tile)
+  int gt[F4_MAX_GROUPS + 1];
+  int gr[F4_MAX_GROUPS + 1];
 };
 
 // kind::mxf4nvf4 instruction descriptor: e2m1 x e2m1 (format code 1), UE4M3 scales, K-major operands, dense K = 64.
@@ -195,7 +202,7 @@ fp4_gather_quantize_kernel(const __nv_bfloat16* __restrict__ x, const int* __res
 // The GEMM
 // ---------------------------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(320, 1)
-fp4_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, Fp4Params p) {
+fp4_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, Fp4Params p) {
   extern __shared__ uint8_t smem_raw[];
   Fp4Smem& s = *reinterpret_cast<Fp4Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   const int warp = threadIdx.x >> 5;
@@ -203,7 +210,19 @@ fp4_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
   const int tiles_n = p.N / F4_BN;
   const int num_ks = p.K / 256;                 // stages per tile
   const int ktiles = p.K >> 6;                  // 64-element scale chunks along K
-  const long long tiles = static_cast<long long>(p.group_tiles[p.groups]) * tiles_n;
+  for (int i = threadIdx.x; i <= p.groups; i += blockDim.x) {
+    s.gt[i] = p.group_tiles[i];
+    s.gr[i] = p.group_rows[i];
+  }
+  __syncthreads();
+  const long long tiles = static_cast<long long>(s.gt[p.groups]) * tiles_n;
+  // The number of tiles is only known on the device.  All CTAs take the same number of rounds; the stride is the smallest
+  // number of CTAs that finishes in that many rounds, so no round runs on a fraction of the SMs while the rest idle
+  // (768 tiles on 148 SMs: 128 CTAs do six rounds each instead of 28 CTAs doing a sixth round alone).  The CTAs beyond the
+  // stride find no tile.
+  const long long rounds = (tiles + gridDim.x - 1) / gridDim.x;
+  const long long stride = rounds > 0 ? (tiles + rounds - 1) / rounds : 1;
+  const long long tile0 = blockIdx.x < stride ? blockIdx.x : tiles;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < F4_STAGES; ++i) {
@@ -232,7 +251,7 @@ fp4_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     int lo = 0, hi = p.groups;                   // group_tiles[lo] <= mt < group_tiles[hi]
     while (hi - lo > 1) {
       const int mid = (lo + hi) >> 1;
-      if (p.group_tiles[mid] <= mt) lo = mid; else hi = mid;
+      if (s.gt[mid] <= mt) lo = mid; else hi = mid;
     }
     e = lo;
   };
@@ -241,21 +260,23 @@ fp4_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     // ------------------------------------------------------------------ producer
     if (elect_one()) {
       tma_prefetch_desc(&tmA);
-      tma_prefetch_desc(&tmB);
       uint32_t it = 0;
       bool ok = true;
-      for (long long tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+      for (long long tile = tile0; tile < tiles && ok; tile += stride) {
         int e, mt, nt;
         decode(tile, e, mt, nt);
         const uint8_t* sfa = p.sfa + static_cast<long long>(mt) * ktiles * 512;
         const uint8_t* sfb = p.sfb + (static_cast<long long>(e) * tiles_n + nt) * ktiles * 512;
+        // the weight tile of a stage is one contiguous 16 KB image (rows already swizzled): a plain bulk copy, and DRAM sees
+        // 16 KB bursts instead of 128 separate 128-byte row segments
+        const uint8_t* wt = p.w_tiled + (static_cast<long long>(e) * tiles_n + nt) * num_ks * (F4_BN * F4_BKB);
         for (int ks = 0; ks < num_ks; ++ks, ++it) {
           const int st = it % F4_STAGES;
           const uint32_t ph = (it / F4_STAGES) & 1;
           if (!mbar_wait(&s.empty[st], ph ^ 1, p.err, 1100 + st)) { ok = false; break; }
           mbar_expect_tx(&s.full[st], kStageBytes);
           tma_load_2d(s.a[st], &tmA, &s.full[st], ks * F4_BKB, mt * F4_BM);
-          tma_load_2d(s.b[st], &tmB, &s.full[st], ks * F4_BKB, e * p.N + nt * F4_BN);
+          bulk_load(s.b[st], wt + static_cast<long long>(ks) * (F4_BN * F4_BKB), F4_BN * F4_BKB, &s.full[st]);
           bulk_load(s.sfa[st], sfa + static_cast<long long>(ks) * F4_SF_STAGE, F4_SF_STAGE, &s.full[st]);
           bulk_load(s.sfb[st], sfb + static_cast<long long>(ks) * F4_SF_STAGE, F4_SF_STAGE, &s.full[st]);
         }
@@ -270,7 +291,7 @@ fp4_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
       constexpr uint32_t idesc = make_idesc_nvf4(F4_BM, F4_BN);
       uint32_t it = 0, seg = 0;
       bool ok = true;
-      for (long long tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++seg) {
+      for (long long tile = tile0; tile < tiles && ok; tile += stride, ++seg) {
         const uint32_t buf = seg & 1;
         if (!mbar_wait(&s.acc_empty[buf], ((seg >> 1) & 1) ^ 1, p.err, 1200 + buf)) { ok = false; break; }
         tc_fence_after();
@@ -301,15 +322,15 @@ fp4_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     const int half = (warp - 2) >> 2;          // mode 0: columns [64 half, 64 half + 64); mode 1: 32 of the 64 results
     uint32_t seg = 0;
     bool ok = true;
-    for (long long tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++seg) {
+    for (long long tile = tile0; tile < tiles && ok; tile += stride, ++seg) {
       int e, mt, nt;
       decode(tile, e, mt, nt);
       const uint32_t buf = seg & 1;
       if (!mbar_wait(&s.acc_full[buf], (seg >> 1) & 1, p.err, 1400 + buf)) { ok = false; break; }
       tc_fence_after();
       const int prow = mt * F4_BM + quarter * 32 + lane;                       // padded row
-      const int local = (mt - p.group_tiles[e]) * F4_BM + quarter * 32 + lane; // row inside the expert
-      const bool row_ok = local < p.group_rows[e + 1] - p.group_rows[e];
+      const int local = (mt - s.gt[e]) * F4_BM + quarter * 32 + lane; // row inside the expert
+      const bool row_ok = local < s.gr[e + 1] - s.gr[e];
       const uint32_t t_row = tmem_base + buf * F4_BN + (static_cast<uint32_t>(quarter * 32) << 16);
       const float sa = p.a_row_scale ? p.a_row_scale[prow] : 1.f;
       if (p.mode == 0) {
@@ -443,7 +464,7 @@ struct TyrFp4GemmArgs {
   const void* a_packed;      // [padded_rows, K / 2]
   const void* a_sf;
   const float* a_row_scale;  // nullable
-  const void* w_packed;      // [groups * N, K / 2]
+  const void* w_packed;      // weight tiles as shared-memory images (ops/fp4.py tile_weights): [groups][N / 128][K / 256][16 KB]
   const void* w_sf;
   const float* w_global;     // [groups]
   const float* w_global2;    // mode 1
@@ -459,18 +480,17 @@ struct TyrFp4GemmArgs {
 
 // Returns 0 on success; negative = invalid argument; positive = CUDA / driver error.
 TYR_EXPORT int tyr_fp4_grouped_gemm(const TyrFp4GemmArgs* a) {
-  if (a->padded_rows <= 0 || (a->padded_rows & 127) || a->N <= 0 || (a->N & 127) || a->K <= 0 || (a->K & 255) || a->groups <= 0)
+  if (a->padded_rows <= 0 || (a->padded_rows & 127) || a->N <= 0 || (a->N & 127) || a->K <= 0 || (a->K & 255) || a->groups <= 0 ||
+      a->groups > F4_MAX_GROUPS)
     return -1;
   if (a->mode != 0 && a->mode != 1) return -2;
   if (a->mode == 1 && (a->out_sf == nullptr || a->w_global2 == nullptr || ((a->N >> 1) & 63))) return -3;
   if ((reinterpret_cast<uintptr_t>(a->a_packed) | reinterpret_cast<uintptr_t>(a->w_packed) | reinterpret_cast<uintptr_t>(a->a_sf) |
        reinterpret_cast<uintptr_t>(a->w_sf) | reinterpret_cast<uintptr_t>(a->out)) & 15)
     return -4;
-  CUtensorMap tmA, tmB;
+  CUtensorMap tmA;
   int r = make_tmap_u8(&tmA, a->a_packed, static_cast<uint64_t>(a->K) / 2, static_cast<uint64_t>(a->padded_rows));
   if (r) return 3000 + r;
-  r = make_tmap_u8(&tmB, a->w_packed, static_cast<uint64_t>(a->K) / 2, static_cast<uint64_t>(a->groups) * a->N);
-  if (r) return 4000 + r;
   constexpr size_t smem = sizeof(Fp4Smem) + 1024;
   static bool configured[64] = {false};
   static int sms[64] = {0};
@@ -486,13 +506,14 @@ TYR_EXPORT int tyr_fp4_grouped_gemm(const TyrFp4GemmArgs* a) {
   p.N = a->N; p.K = a->K; p.groups = a->groups;
   p.group_tiles = a->group_tiles; p.group_rows = a->group_rows;
   p.sfa = reinterpret_cast<const uint8_t*>(a->a_sf); p.sfb = reinterpret_cast<const uint8_t*>(a->w_sf);
+  p.w_tiled = reinterpret_cast<const uint8_t*>(a->w_packed);
   p.a_row_scale = a->a_row_scale; p.w_global = a->w_global; p.w_global2 = a->w_global2;
   p.mode = a->mode; p.out = a->out; p.out_sf = reinterpret_cast<uint8_t*>(a->out_sf); p.err = a->err;
   int grid = a->sm_count > 0 ? a->sm_count : sms[dev];
   const long long max_tiles = static_cast<long long>(a->padded_rows / 128) * (a->N / 128);
   if (max_tiles < grid) grid = static_cast<int>(max_tiles);
   if (grid < 1) grid = 1;
-  fp4_grouped_gemm_kernel<<<grid, 320, smem, reinterpret_cast<cudaStream_t>(a->stream)>>>(tmA, tmB, p);
+  fp4_grouped_gemm_kernel<<<grid, 320, smem, reinterpret_cast<cudaStream_t>(a->stream)>>>(tmA, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 2000 + static_cast<int>(e);
 }

@@ -59,7 +59,7 @@ def test_fp4_gemm_dense_matches_decoded_operands(M_, N, K):
     wp, ws, wg = M.nvfp4_quantize(w)
     tiles = torch.tensor([0, M_ // 128], dtype=torch.int32, device=dev)
     rows = torch.tensor([0, M_], dtype=torch.int32, device=dev)
-    out = fp4.grouped_gemm_fp4(xq, xsf, xrs, wp.reshape(N, K // 2), fp4.swizzle_scales(ws.view(torch.uint8))[0].contiguous(), wg,
+    out = fp4.grouped_gemm_fp4(xq, xsf, xrs, fp4.tile_weights(wp.reshape(1, N, K // 2)), fp4.swizzle_scales(ws.view(torch.uint8))[0].contiguous(), wg,
                                tiles, rows, N, K, mode=0)
     torch.cuda.synchronize()
     a_hat = fp4.dequant_rows_ref(codes, sb, rs)
@@ -108,9 +108,9 @@ def test_fp4_moe_tensor_core_path(T, E, k, h, mi, skew):
     w4 = fp4.prepared(ex)
     padded = ((T * k + 127 * min(E, T * k) + 127) // 128) * 128
     xq, xsf, xrs, ppos = fp4.gather_quantize(x, order, ids.reshape(-1).contiguous(), offsets, tiles, k, padded, T * k)
-    hq, hsf = fp4.grouped_gemm_fp4(xq, xsf, xrs, w4.gu_packed.reshape(-1, h // 2), w4.gu_sf, w4.gate_global, tiles, offsets,
+    hq, hsf = fp4.grouped_gemm_fp4(xq, xsf, xrs, w4.gu_packed, w4.gu_sf, w4.gate_global, tiles, offsets,
                                    2 * mi, h, mode=1, w_global2=w4.up_global)
-    y = fp4.grouped_gemm_fp4(hq, hsf, None, w4.dn_packed.reshape(-1, mi // 2), w4.dn_sf, w4.dn_global, tiles, offsets, h, mi, mode=0)
+    y = fp4.grouped_gemm_fp4(hq, hsf, None, w4.dn_packed, w4.dn_sf, w4.dn_global, tiles, offsets, h, mi, mode=0)
     torch.cuda.synchronize()
     lut = fp4.E2M1_VALUES.to(dev)
 

@@ -104,11 +104,30 @@ def dequant_rows_ref(codes: torch.Tensor, sb: torch.Tensor, g: torch.Tensor) -> 
     return vals * (sb * g[:, None]).repeat_interleave(16, dim=1)
 
 
+def tile_weights(w: torch.Tensor) -> torch.Tensor:
+    """[E, N, K/2] packed bytes (N % 128 == 0, K % 256 == 0) -> [E, N/128, K/256, 16384]: for every (128-row tile, 256-element
+    stage) the 16 KB image the kernel's shared memory holds for it, i.e. rows of 128 bytes whose 16-byte chunks are XOR-ed with
+    (row & 7) (the 128-byte swizzle the tensor-core descriptors expect).  The kernel then fetches a stage's weights with ONE
+    contiguous bulk copy instead of a 128-row tiled copy, and DRAM sees 16 KB bursts."""
+    E, N, Kb = w.shape
+    if N % 128 or Kb % 128:
+        raise ValueError("tile_weights: rows must be a multiple of 128 and the reduction a multiple of 256 elements")
+    r = torch.arange(128, device=w.device)
+    src_chunk = (torch.arange(8, device=w.device)[None, :] ^ (r[:, None] & 7))               # [128, 8]: chunk stored at (r, c')
+    idx = src_chunk[None, None, None, :, :, None].expand(1, N // 128, Kb // 128, 128, 8, 16)
+    out = torch.empty((E, N // 128, Kb // 128, 128 * 128), dtype=torch.uint8, device=w.device)
+    for e in range(E):                                                                    # one expert at a time: bounded scratch
+        t = w[e].reshape(N // 128, 128, Kb // 128, 8, 16).permute(0, 2, 1, 3, 4).unsqueeze(0)   # [1, nt, ks, r, c, 16]
+        out[e] = torch.gather(t, 4, idx).reshape(N // 128, Kb // 128, 128 * 128)
+    return out
+
+
 # ---- prepared weights ----------------------------------------------------------------------------------------
 @dataclass
 class Fp4Experts:
     """NVFP4 banks in the layout of the tensor-core kernels.  ``gu_*``: gate and up rows interleaved in groups of 64
-    ([E, 2 * mi, h / 2] bytes); ``dn_*``: the down bank ([E, h, mi / 2]).  Scales are flat per expert, tensor-core order."""
+    ([E, 2 * mi, h / 2] bytes) and then cut into per-stage shared-memory images (``tile_weights``); ``dn_*``: the down bank
+    ([E, h, mi / 2]) likewise.  Scales are flat per expert, tensor-core order."""
     gu_packed: torch.Tensor
     gu_sf: torch.Tensor
     gate_global: torch.Tensor
@@ -135,10 +154,10 @@ class Fp4Experts:
             return torch.stack([g.reshape(E, mi // 64, 64, c), u.reshape(E, mi // 64, 64, c)], dim=2).reshape(E, 2 * mi, c)
 
         u8 = lambda t: t.view(torch.uint8) if t.dtype != torch.uint8 else t
-        gu_packed = inter(ex.gate_packed, ex.up_packed).contiguous()
+        gu_packed = tile_weights(inter(ex.gate_packed, ex.up_packed).contiguous())
         gu_sf = swizzle_scales(inter(u8(ex.gate_scale), u8(ex.up_scale)))
         return Fp4Experts(gu_packed, gu_sf.contiguous(), ex.gate_global.float().contiguous(), ex.up_global.float().contiguous(),
-                          ex.down_packed.contiguous(), swizzle_scales(u8(ex.down_scale)).contiguous(),
+                          tile_weights(ex.down_packed.contiguous()), swizzle_scales(u8(ex.down_scale)).contiguous(),
                           ex.down_global.float().contiguous(), h, mi)
 
 
@@ -176,7 +195,8 @@ def gather_quantize(x: torch.Tensor, order: Optional[torch.Tensor], ids: Optiona
 
 def grouped_gemm_fp4(a_packed, a_sf, a_row_scale, w_packed, w_sf, w_global, tiles, rows, N: int, K: int, *, mode: int = 0,
                      w_global2=None, sm_count: int = 0):
-    """mode 0 -> bf16 [padded_rows, N]; mode 1 -> (packed [padded_rows, N/4] u8, scales flat u8) of silu(gate) * up."""
+    """``w_packed``: the weights as ``tile_weights`` images.  mode 0 -> bf16 [padded_rows, N]; mode 1 -> (packed
+    [padded_rows, N/4] u8, scales flat u8) of silu(gate) * up."""
     padded = a_packed.shape[0]
     dev = a_packed.device
     groups = tiles.numel() - 1
@@ -213,9 +233,9 @@ def moe_fp4_tc_forward(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor
     st = cur_stream(x.device)
     ids32 = ids.to(torch.int32).contiguous()
     xq, xsf, xrs, ppos = gather_quantize(x, order, ids32.reshape(-1), offsets, tiles, k, padded, pairs)
-    hq, hsf = grouped_gemm_fp4(xq, xsf, xrs, w4.gu_packed.reshape(-1, h // 2), w4.gu_sf, w4.gate_global, tiles, offsets,
+    hq, hsf = grouped_gemm_fp4(xq, xsf, xrs, w4.gu_packed, w4.gu_sf, w4.gate_global, tiles, offsets,
                                2 * mi, h, mode=1, w_global2=w4.up_global)
-    y = grouped_gemm_fp4(hq, hsf, None, w4.dn_packed.reshape(-1, mi // 2), w4.dn_sf, w4.dn_global, tiles, offsets, h, mi, mode=0)
+    y = grouped_gemm_fp4(hq, hsf, None, w4.dn_packed, w4.dn_sf, w4.dn_global, tiles, offsets, h, mi, mode=0)
     out = torch.empty_like(x)
     check(lib().tyr_moe_combine(ptr(y), ptr(ppos), ptr(weights.float().contiguous()), ptr(add.contiguous() if add is not None else None),
                                 ptr(out), T, k, h, st), "moe_combine")
