@@ -295,7 +295,12 @@ class TPCache:
             from ..utils.graph import GraphedStep
             self.pos_t = torch.full((1,), self.pos, dtype=torch.int32, device=self.m.device)
             state = [self.pos_t] + [t for s in self.lin if s is not None for t in (s.conv, s.rec)]
+            parity0 = self.m.tp._parity
             self._graph = GraphedStep(self._device_step, (tok.reshape(-1).clone(),), advancing_state=state)
+            # the symmetric partial-product buffers alternate per call and the choice is baked into the captured graph: a
+            # replay is only safe when one step makes an even number of such calls (two per layer here)
+            if self.m.tp._parity != parity0:
+                raise RuntimeError("tensor-parallel decode step made an odd number of double-buffered calls; it cannot be replayed from a graph")
         h = self._graph(tok.reshape(-1))
         self.pos += 1
         for c in self.kv:
