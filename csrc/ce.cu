@@ -12,9 +12,6 @@
 // (no host synchronisation).  target == ignore_index is skipped silently.
 #include "common.cuh"
 
-#include <cstdlib>
-#include <cuda_fp16.h>
-
 namespace tyr {
 
 struct CeArgs {
@@ -36,7 +33,7 @@ __device__ __forceinline__ float softcap(float l, float cap, float inv_cap) {
 
 __global__ void __launch_bounds__(512) softcap_ce_kernel(CeArgs a) {
   __shared__ float red_m[16], red_s[16];
-  __shared__ float sh_lse;
+  __shared__ float sh_m, sh_lse;
   const int tid = threadIdx.x;
   const int lane = tid & 31, wid = tid >> 5, nw = blockDim.x >> 5;
   const float inv_cap = a.cap > 0.f ? 1.f / a.cap : 0.f;
@@ -87,7 +84,10 @@ __global__ void __launch_bounds__(512) softcap_ce_kernel(CeArgs a) {
         sv = (mm == -INFINITY ? 0.f : sv * __expf(mm - mx)) + (m2 == -INFINITY ? 0.f : s2 * __expf(m2 - mx));
         mm = mx;
       }
-      if (lane == 0) sh_lse = mm + __logf(sv);
+      if (lane == 0) {
+        sh_m = mm;
+        sh_lse = mm + __logf(sv);
+      }
     }
     __syncthreads();
     const float lse = sh_lse;
@@ -132,83 +132,6 @@ __global__ void __launch_bounds__(512) softcap_ce_kernel(CeArgs a) {
   }
 }
 
-// The soft-capped form with the row's tanh values kept in shared memory between the two passes.
-//
-// The kernel above spends its time in the special-function unit (ncu: SM throughput 76 %, DRAM 32 %): per logit a tanh and
-// an exp in each pass plus the rescaling exps of the running maximum.  With a soft cap z lies in [-cap, cap], so the first
-// pass needs no running maximum (it sums exp(z - cap), at least e^(-2 cap) per term, directly), and the second pass
-// reads tanh back from shared memory (fp16, 2 bytes per logit: 128 KB for 65536 logits) instead of recomputing it from the
-// logits: three special-function operations per logit instead of a little over four, and the logits are read from memory
-// once.  fp16 holds tanh to 2^-12, i.e. z to 0.4 % of a unit at cap 15, the size of the bf16 rounding of the gradient
-// itself.  One CTA per SM (the row buffer fills its shared memory); rows are dealt round-robin.
-__global__ void __launch_bounds__(1024, 1) softcap_ce_cached_kernel(CeArgs a) {
-  extern __shared__ __align__(16) __half th_row[];
-  __shared__ float red_s[32];
-  __shared__ float sh_lse;
-  const int tid = threadIdx.x;
-  const int lane = tid & 31, wid = tid >> 5, nw = blockDim.x >> 5;
-  const float inv_cap = 1.f / a.cap;
-  for (int row = blockIdx.x; row < a.rows; row += gridDim.x) {
-    __nv_bfloat16* l = a.logits + static_cast<long long>(row) * a.ld;
-    float s = 0.f;
-    for (int v = tid * 8; v < a.V; v += blockDim.x * 8) {
-      const uint4 u = *reinterpret_cast<const uint4*>(l + v);
-      const float2 p[4] = {unpack_bf16x2(u.x), unpack_bf16x2(u.y), unpack_bf16x2(u.z), unpack_bf16x2(u.w)};
-      __half2 h[4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float t0 = tanhf(p[j].x * inv_cap), t1 = tanhf(p[j].y * inv_cap);
-        h[j] = __floats2half2_rn(t0, t1);
-        // the sum uses the values the second pass will see, so that the probabilities it forms sum to one
-        const float2 tr = __half22float2(h[j]);
-        s += __expf(a.cap * tr.x - a.cap) + __expf(a.cap * tr.y - a.cap);
-      }
-      *reinterpret_cast<uint4*>(th_row + v) = *reinterpret_cast<const uint4*>(h);
-    }
-    s = warp_sum(s);
-    if (lane == 0) red_s[wid] = s;
-    __syncthreads();
-    if (wid == 0) {
-      float sv = lane < nw ? red_s[lane] : 0.f;
-      sv = warp_sum(sv);
-      if (lane == 0) sh_lse = a.cap + __logf(sv);
-    }
-    __syncthreads();
-    const float lse = sh_lse;
-    const long long t = a.targets[row];
-    const bool ignored = (t == a.ignore_index);
-    const bool valid = !ignored && t >= 0 && t < a.V;
-    if (tid == 0) {
-      float loss = 0.f;
-      if (valid) loss = lse - a.cap * __half2float(th_row[t]);
-      else if (!ignored && a.bad_count) atomicAdd(a.bad_count, 1);
-      a.loss_rows[row] = loss;
-    }
-    if (a.write_grad) {
-      const float g = valid ? a.gscale * (a.gscale_dev ? *a.gscale_dev : 1.f) : 0.f;
-      for (int v = tid * 8; v < a.V; v += blockDim.x * 8) {
-        __half2 h[4];
-        *reinterpret_cast<uint4*>(h) = *reinterpret_cast<const uint4*>(th_row + v);
-        float o[8];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float2 tr = __half22float2(h[j]);
-          float p0 = __expf(a.cap * tr.x - lse), p1 = __expf(a.cap * tr.y - lse);
-          if (v + 2 * j == t) p0 -= 1.f;
-          if (v + 2 * j + 1 == t) p1 -= 1.f;
-          o[2 * j] = g * p0 * (1.f - tr.x * tr.x);
-          o[2 * j + 1] = g * p1 * (1.f - tr.y * tr.y);
-        }
-        uint4 w;
-        w.x = pack_bf16x2(o[0], o[1]); w.y = pack_bf16x2(o[2], o[3]);
-        w.z = pack_bf16x2(o[4], o[5]); w.w = pack_bf16x2(o[6], o[7]);
-        *reinterpret_cast<uint4*>(l + v) = w;
-      }
-    }
-    __syncthreads();      // the row buffer and sh_lse are reused by the next row
-  }
-}
-
 }  // namespace tyr
 
 using namespace tyr;
@@ -220,23 +143,6 @@ extern "C" TYR_EXPORT int tyr_softcap_ce(void* logits, const long long* targets,
   if ((V & 7) || (ld & 7) || rows <= 0) return -1;
   CeArgs a{(__nv_bfloat16*)logits, targets, loss_rows, bad_count, rows, V, ld, cap, gscale,
            gscale_dev, ignore_index, write_grad};
-  // soft-capped rows that fit in shared memory as fp16 tanh values take the cached form (TYR_CE_CACHED=0 keeps the plain one)
-  static const bool cached_ok = [] { const char* e = getenv("TYR_CE_CACHED"); return !(e && e[0] == '0'); }();
-  const size_t row_bytes = static_cast<size_t>(V) * sizeof(__half);
-  if (cached_ok && cap > 0.f && row_bytes <= 200 * 1024 && rows >= 148) {
-    static bool configured[64] = {false};
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
-    if (!configured[dev]) {
-      if (cudaFuncSetAttribute(softcap_ce_cached_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
-        return -2;
-      configured[dev] = true;
-    }
-    int sms = 148;
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    softcap_ce_cached_kernel<<<rows < sms ? rows : sms, 1024, row_bytes, (cudaStream_t)stream>>>(a);
-    return (int)cudaGetLastError();
-  }
   const int grid = rows < 148 * 8 ? rows : 148 * 8;
   softcap_ce_kernel<<<grid, 512, 0, (cudaStream_t)stream>>>(a);
   return (int)cudaGetLastError();

@@ -214,27 +214,6 @@ def test_softcap_ce_kernel_and_lm_head():
     assert _rel_err(w.grad, wr.grad) < 3e-2
 
 
-@pytest.mark.parametrize("rows,V,scale", [(200, 65536, 6.0), (150, 8192, 30.0), (333, 50304, 2.0)])
-def test_softcap_ce_cached_tanh_kernel(rows, V, scale):
-    """At least 148 soft-capped rows whose fp16 tanh values fit in shared memory take the kernel that keeps them there between
-    the passes: loss and gradient against the fp32 formula (large logits saturate the cap), ignored and out-of-range targets."""
-    from tyr_b200.ops.ce import softcap_ce_, softcap_ce_ref
-    g = torch.Generator(device="cuda").manual_seed(rows + V)
-    logits = (torch.randn(rows, V, device=_dev(), generator=g) * scale).bfloat16()
-    t = torch.randint(0, V, (rows,), device=_dev(), generator=g)
-    t[5] = -100
-    t[7] = V - 1
-    lr = logits.detach().float().requires_grad_(True)
-    ref = softcap_ce_ref(lr, t, 15.0)
-    ref.sum().backward()
-    work = logits.clone()
-    loss = softcap_ce_(work, t, 15.0, 1.0)
-    assert torch.allclose(loss, ref, rtol=5e-3, atol=5e-3), (loss - ref).abs().max().item()
-    assert loss[5].item() == 0.0 and work[5].float().abs().max().item() == 0.0
-    assert _rel_err(work, lr.grad) < 2e-2
-    assert (work.float() - lr.grad).abs().max().item() < 2e-2 * lr.grad.abs().max().item() + 1e-6
-
-
 def test_adamw_and_muon_kernels():
     from tyr_b200.ops import optim_kernels as ok
     from tyr_b200.ops import polar
