@@ -1,6 +1,7 @@
 """Laguna: config validation, rotary tables, cached vs uncached parity, ring caches, weight
 round trip, generation (mirrors Tests/RunLaguna{Rope,Moe,Model,Parity}.lean)."""
 import math
+import os
 
 import pytest
 import torch
@@ -174,3 +175,32 @@ def test_gpu_laguna_bf16_fused_decode_matches_eager():
             # a near-tie in a router can pick a different expert once the arithmetic differs in the last bf16
             # bit, which changes that row discretely; everything else must agree
             assert ok >= 0.85, (fused, ok)
+
+
+def test_tiny_fixture_generator_is_deterministic_and_self_consistent(tmp_path):
+    """tests/fixtures/make_tiny_laguna.py: two runs write identical files, the checkpoint loads back through the public loader
+    and reproduces the stored references (fp32 CPU) and the greedy ids; the NVFP4 form goes through the packed-expert loader."""
+    import importlib.util
+    import json
+    spec = importlib.util.spec_from_file_location("make_tiny_laguna", os.path.join(os.path.dirname(__file__), "fixtures", "make_tiny_laguna.py"))
+    gen = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(gen)
+    for nvfp4 in (False, True):
+        a, b = str(tmp_path / f"a{int(nvfp4)}"), str(tmp_path / f"b{int(nvfp4)}")
+        gen.generate(a, seed=77, nvfp4=nvfp4)
+        gen.generate(b, seed=77, nvfp4=nvfp4)
+        for name in ("config.json", "model.safetensors", "reference.safetensors", "reference.json"):
+            assert open(os.path.join(a, name), "rb").read() == open(os.path.join(b, name), "rb").read(), name
+        cfg = L.LagunaConfig.load_from_pretrained_dir(a)
+        assert cfg == gen.tiny_config()
+        m = L.load_pretrained(a, device="cpu", dtype=torch.float32)
+        hdl = st.open_handle(os.path.join(a, "reference.safetensors"))
+        ref = {k: st.read_tensor(hdl, k) for k in ("logits_a", "gen_logits_last")}
+        meta = json.load(open(os.path.join(a, "reference.json")))
+        ids = torch.tensor([meta["input_ids_a"]])
+        with torch.no_grad():
+            assert torch.allclose(L.forward(m, ids, use_fused=False)[0], ref["logits_a"], atol=1e-5)
+            out = L.generate_greedy(m, ids, max_new_tokens=16, eos_token_ids=[])
+        assert out[0, len(meta["input_ids_a"]):].tolist() == meta["gen_ids"]
+        moe = next(l.ffn for i, l in enumerate(m.layers) if cfg.is_moe_layer(i))
+        assert (moe.dense_experts is None) == nvfp4

@@ -176,6 +176,26 @@ class LagunaConfig:
             mlp_only_layers=tuple(j.get("mlp_only_layers", [i for i in d.mlp_only_layers if i < n])),
             eos_token_ids=eos, **simple)
 
+    def to_json(self) -> dict:
+        """The HF ``config.json`` form that ``from_json`` reads back to an equal config (fixture generators, export)."""
+        rope = {
+            FULL: {"rope_theta": self.rope_theta_full, "partial_rotary_factor": 2 * self.half_rotary_dim_full / self.head_dim,
+                   "factor": self.yarn_factor, "original_max_position_embeddings": self.yarn_original_max_position_embeddings,
+                   "beta_fast": self.yarn_beta_fast, "beta_slow": self.yarn_beta_slow, "attention_factor": self.yarn_attention_factor},
+            SLIDING: {"rope_theta": self.rope_theta_sliding, "partial_rotary_factor": 2 * self.half_rotary_dim_sliding / self.head_dim},
+        }
+        return {"model_type": "laguna", "hidden_act": "silu", "attention_bias": False, "vocab_size": self.vocab_size,
+                "hidden_size": self.hidden_size, "intermediate_size": self.intermediate_size,
+                "num_hidden_layers": self.num_hidden_layers, "layer_types": list(self.layer_types),
+                "num_attention_heads": self.num_attention_heads, "num_attention_heads_sliding": self.num_attention_heads_sliding,
+                "num_key_value_heads": self.num_key_value_heads, "head_dim": self.head_dim, "rms_norm_eps": self.rms_norm_eps,
+                "sliding_window": self.sliding_window, "num_experts": self.num_experts,
+                "num_experts_per_tok": self.num_experts_per_tok, "moe_intermediate_size": self.moe_intermediate_size,
+                "shared_expert_intermediate_size": self.shared_expert_intermediate_size, "norm_topk_prob": self.norm_topk_prob,
+                "moe_routed_scaling_factor": self.moe_routed_scaling_factor,
+                "moe_router_logit_softcapping": self.moe_router_logit_softcapping, "mlp_only_layers": list(self.mlp_only_layers),
+                "eos_token_id": list(self.eos_token_ids), "rope_parameters": rope}
+
     @staticmethod
     def load_from_pretrained_dir(model_dir: str) -> "LagunaConfig":
         with open(os.path.join(model_dir, "config.json")) as f:
