@@ -183,7 +183,7 @@ def bench_moe(results, cases=None):
     gen = torch.Generator().manual_seed(0)
     ex = L.random_packed_experts(cfg, dev, gen)
     E, k, h, mi = cfg.num_experts, cfg.num_experts_per_tok, cfg.hidden_size, cfg.moe_intermediate_size
-    for T, path in cases or ((1, "gemv"), (4, "gemv"), (16, "gemv"), (64, "gemv"), (64, "gemm"), (512, "gemm"), (4096, "gemm")):
+    for T, path in cases or ((1, "gemv"), (4, "gemv"), (16, "gemv"), (64, "gemv"), (32, "gemm_sorted"), (32, "gemm"), (64, "gemm_sorted"), (64, "gemm"), (128, "gemm_sorted"), (128, "gemm"), (512, "gemm"), (4096, "gemm")):
         x = torch.randn(T, h, device=dev).bfloat16()
         ids, w, cnt = moe.route(torch.randn(T, E, device=dev), k)
         fn = lambda: moe.moe_fp4_forward(x, ids, w, ex, counts=cnt, force_path=path)

@@ -199,8 +199,84 @@ fp4_gather_quantize_kernel(const __nv_bfloat16* __restrict__ x, const int* __res
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
-// The GEMM
+// Decode-sized batches (T <= 128): quantise + scatter without a sorted layout.  Every expert owns the fixed row tile
+// [128 e, 128 e + 128): a token can reach an expert once, so 128 slots always suffice, and a slot is taken with one atomic on
+// the expert's cursor (zero on entry, the expert's row count on exit: the grouped GEMM reads it in place of its row table).
+// One warp per token: the row is quantised once into shared memory and written to each of its k experts' slots.  Replaces the
+// offsets / scatter / zero-fill / gather launches of the sorted layout.
+constexpr int F4_SCATTER_WARPS = 4;
+
+__global__ void __launch_bounds__(F4_SCATTER_WARPS * 32)
+fp4_scatter_quantize_fixed_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ ids, int* __restrict__ cursors,
+                                  uint8_t* __restrict__ packed, uint8_t* __restrict__ sf, float* __restrict__ row_scale,
+                                  int* __restrict__ pair_ppos, int T, int k, int h, int E, int* err) {
+  extern __shared__ __align__(16) uint8_t sq_smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row_bytes = (h >> 1) + (h >> 4);                 // packed values then scale bytes
+  uint8_t* q = sq_smem + warp * ((row_bytes + 15) & ~15);
+  uint8_t* qs = q + (h >> 1);
+  const int ktiles = h >> 6;
+  const int tok = blockIdx.x * F4_SCATTER_WARPS + warp;
+  if (tok >= T) return;
+  const __nv_bfloat16* src = x + static_cast<long long>(tok) * h;
+  float amax = 0.f;
+  for (int c = lane * 8; c < h; c += 256) {
+    const uint4 u = *reinterpret_cast<const uint4*>(src + c);
+    const float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y), f2 = unpack_bf16x2(u.z), f3 = unpack_bf16x2(u.w);
+    amax = fmaxf(amax, fmaxf(fmaxf(fabsf(f0.x), fabsf(f0.y)), fmaxf(fabsf(f1.x), fabsf(f1.y))));
+    amax = fmaxf(amax, fmaxf(fmaxf(fabsf(f2.x), fabsf(f2.y)), fmaxf(fabsf(f3.x), fabsf(f3.y))));
+  }
+  amax = warp_max(amax);
+  const float g = amax > 0.f ? amax * (1.f / (6.f * 448.f)) : 1.f;
+  const float inv_g = 1.f / g;
+  for (int c = lane * 8; c < h; c += 256) {
+    const uint4 u = *reinterpret_cast<const uint4*>(src + c);
+    float v[8];
+    { const float2 f = unpack_bf16x2(u.x); v[0] = f.x; v[1] = f.y; }
+    { const float2 f = unpack_bf16x2(u.y); v[2] = f.x; v[3] = f.y; }
+    { const float2 f = unpack_bf16x2(u.z); v[4] = f.x; v[5] = f.y; }
+    { const float2 f = unpack_bf16x2(u.w); v[6] = f.x; v[7] = f.y; }
+    float bm = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) bm = fmaxf(bm, fabsf(v[j]));
+    bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 1));
+    const uint8_t sb = ue4m3_encode(bm * inv_g * (1.f / 6.f));
+    const float sdec = ue4m3_decode(sb) * g;
+    const float inv_s = sdec > 0.f ? 1.f / sdec : 0.f;
+    uint32_t w = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) w |= e2m1_code(v[j] * inv_s) << (4 * j);
+    *reinterpret_cast<uint32_t*>(q + (c >> 1)) = w;
+    if ((lane & 1) == 0) qs[c >> 4] = sb;
+  }
+  __syncwarp();
+  for (int j = 0; j < k; ++j) {
+    const int pair = tok * k + j;
+    const int e = ids[pair];
+    if (e < 0 || e >= E) {                        // not routed (padding id): takes no slot
+      if (lane == 0) pair_ppos[pair] = -1;
+      continue;
+    }
+    int slot = 0;
+    if (lane == 0) slot = atomicAdd(cursors + e, 1);
+    slot = __shfl_sync(0xffffffffu, slot, 0);
+    if (slot >= F4_BM) {                           // cannot happen while T <= 128; recorded, the row is dropped
+      if (lane == 0) { report_error(err, ERR_BOUNDS, 1500); pair_ppos[pair] = -1; }
+      continue;
+    }
+    const int prow = e * F4_BM + slot;
+    uint8_t* dst = packed + static_cast<long long>(prow) * (h >> 1);
+    for (int c = lane * 16; c < (h >> 1); c += 512) *reinterpret_cast<uint4*>(dst + c) = *reinterpret_cast<const uint4*>(q + c);
+    for (int kb = lane; kb < (h >> 4); kb += 32) sf[sf_offset(prow, kb, ktiles)] = qs[kb];
+    if (lane == 0) {
+      row_scale[prow] = g;
+      pair_ppos[pair] = prow;
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------------------------------------------------
+// The GEMM
 __global__ void __launch_bounds__(320, 1)
 fp4_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, Fp4Params p) {
   extern __shared__ uint8_t smem_raw[];
@@ -210,10 +286,36 @@ fp4_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, Fp4Params p) {
   const int tiles_n = p.N / F4_BN;
   const int num_ks = p.K / 256;                 // stages per tile
   const int ktiles = p.K >> 6;                  // 64-element scale chunks along K
-  for (int i = threadIdx.x; i <= p.groups; i += blockDim.x) {
-    s.gt[i] = p.group_tiles[i];
-    s.gr[i] = p.group_rows[i];
+  if (p.group_tiles != nullptr) {
+    for (int i = threadIdx.x; i <= p.groups; i += blockDim.x) {
+      s.gt[i] = p.group_tiles[i];
+      s.gr[i] = p.group_rows[i];
+    }
+  } else {
+    // fixed-slot layout (decode-sized batches): expert e owns the padded rows [128 e, 128 e + 128) and `group_rows` holds the
+    // experts' row COUNTS.  The tile table counts the experts that have rows, so an expert without rows costs no tile.
+    if (warp == 0) {
+      int carry_t = 0, carry_r = 0;
+      if (lane == 0) s.gt[0] = s.gr[0] = 0;
+      for (int base = 0; base < p.groups; base += 32) {
+        const int i = base + lane;
+        const int c = i < p.groups ? min(max(p.group_rows[i], 0), F4_BM) : 0;
+        int t = c > 0 ? 1 : 0, r = c;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+          const int tt = __shfl_up_sync(0xffffffffu, t, d), rr = __shfl_up_sync(0xffffffffu, r, d);
+          if (lane >= d) { t += tt; r += rr; }
+        }
+        if (i < p.groups) {
+          s.gt[i + 1] = carry_t + t;
+          s.gr[i + 1] = carry_r + r;
+        }
+        carry_t += __shfl_sync(0xffffffffu, t, 31);
+        carry_r += __shfl_sync(0xffffffffu, r, 31);
+      }
+    }
   }
+  const bool fixed_slots = p.group_tiles == nullptr;
   __syncthreads();
   const long long tiles = static_cast<long long>(s.gt[p.groups]) * tiles_n;
   // The number of tiles is only known on the device.  All CTAs take the same number of rounds; the stride is the smallest
@@ -245,7 +347,8 @@ fp4_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, Fp4Params p) {
   const uint32_t tmem_base = s.tmem_base;
   constexpr uint32_t kStageBytes = F4_BM * F4_BKB + F4_BN * F4_BKB + 2 * F4_SF_STAGE;
 
-  auto decode = [&](long long tile, int& e, int& mt, int& nt) {
+  // -> expert e, padded row tile mt, column tile nt, lt = index of the row tile inside the expert
+  auto decode = [&](long long tile, int& e, int& mt, int& nt, int& lt) {
     mt = static_cast<int>(tile / tiles_n);       // n fastest: the CTAs in flight share a row tile of activations
     nt = static_cast<int>(tile % tiles_n);
     int lo = 0, hi = p.groups;                   // group_tiles[lo] <= mt < group_tiles[hi]
@@ -254,6 +357,8 @@ fp4_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, Fp4Params p) {
       if (s.gt[mid] <= mt) lo = mid; else hi = mid;
     }
     e = lo;
+    lt = mt - s.gt[e];
+    if (fixed_slots) mt = e;
   };
 
   if (warp == 0) {
@@ -263,8 +368,8 @@ fp4_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, Fp4Params p) {
       uint32_t it = 0;
       bool ok = true;
       for (long long tile = tile0; tile < tiles && ok; tile += stride) {
-        int e, mt, nt;
-        decode(tile, e, mt, nt);
+        int e, mt, nt, lt;
+        decode(tile, e, mt, nt, lt);
         const uint8_t* sfa = p.sfa + static_cast<long long>(mt) * ktiles * 512;
         const uint8_t* sfb = p.sfb + (static_cast<long long>(e) * tiles_n + nt) * ktiles * 512;
         // the weight tile of a stage is one contiguous 16 KB image (rows already swizzled): a plain bulk copy, and DRAM sees
@@ -323,13 +428,13 @@ fp4_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, Fp4Params p) {
     uint32_t seg = 0;
     bool ok = true;
     for (long long tile = tile0; tile < tiles && ok; tile += stride, ++seg) {
-      int e, mt, nt;
-      decode(tile, e, mt, nt);
+      int e, mt, nt, lt;
+      decode(tile, e, mt, nt, lt);
       const uint32_t buf = seg & 1;
       if (!mbar_wait(&s.acc_full[buf], (seg >> 1) & 1, p.err, 1400 + buf)) { ok = false; break; }
       tc_fence_after();
       const int prow = mt * F4_BM + quarter * 32 + lane;                       // padded row
-      const int local = (mt - s.gt[e]) * F4_BM + quarter * 32 + lane; // row inside the expert
+      const int local = lt * F4_BM + quarter * 32 + lane;                      // row inside the expert
       const bool row_ok = local < s.gr[e + 1] - s.gr[e];
       const uint32_t t_row = tmem_base + buf * F4_BN + (static_cast<uint32_t>(quarter * 32) << 16);
       const float sa = p.a_row_scale ? p.a_row_scale[prow] : 1.f;
@@ -460,6 +565,22 @@ TYR_EXPORT int tyr_fp4_gather_quantize(const void* x, const int* pair_order, con
   return static_cast<int>(cudaGetLastError());
 }
 
+// Quantise + scatter into the fixed-slot layout (T <= 128 tokens; see fp4_scatter_quantize_fixed_kernel).  `cursors` [E]
+// int32 zero on entry; packed [128 E, h / 2]; sf 128 E / 128 * (h / 64) * 512 bytes; row_scale [128 E]; pair_ppos [T k].
+TYR_EXPORT int tyr_fp4_scatter_quantize_fixed(const void* x, const int* ids, int* cursors, void* packed, void* sf, float* row_scale,
+                                              int* pair_ppos, int T, int k, int h, int E, int* err, void* stream) {
+  if (T <= 0 || T > F4_BM || h <= 0 || (h & 255) || k <= 0 || E <= 0) return -1;
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(packed)) & 15) return -2;
+  const size_t per_warp = (static_cast<size_t>(h >> 1) + (h >> 4) + 15) & ~static_cast<size_t>(15);
+  const size_t smem = per_warp * F4_SCATTER_WARPS;
+  if (smem > 48 * 1024) return -3;
+  fp4_scatter_quantize_fixed_kernel<<<(T + F4_SCATTER_WARPS - 1) / F4_SCATTER_WARPS, F4_SCATTER_WARPS * 32, smem,
+                                      reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(x), ids, cursors, reinterpret_cast<uint8_t*>(packed), reinterpret_cast<uint8_t*>(sf),
+      row_scale, pair_ppos, T, k, h, E, err);
+  return static_cast<int>(cudaGetLastError());
+}
+
 struct TyrFp4GemmArgs {
   const void* a_packed;      // [padded_rows, K / 2]
   const void* a_sf;
@@ -468,8 +589,8 @@ struct TyrFp4GemmArgs {
   const void* w_sf;
   const float* w_global;     // [groups]
   const float* w_global2;    // mode 1
-  const int* group_tiles;    // [groups + 1]
-  const int* group_rows;     // [groups + 1]
+  const int* group_tiles;    // [groups + 1]; nullptr: fixed-slot layout (expert e = row tile e)
+  const int* group_rows;     // [groups + 1] prefix of true rows; fixed-slot layout: [groups] row counts
   void* out;
   void* out_sf;
   int padded_rows, N, K, groups, mode;
@@ -484,6 +605,7 @@ TYR_EXPORT int tyr_fp4_grouped_gemm(const TyrFp4GemmArgs* a) {
       a->groups > F4_MAX_GROUPS)
     return -1;
   if (a->mode != 0 && a->mode != 1) return -2;
+  if (a->group_rows == nullptr || (a->group_tiles == nullptr && a->padded_rows < a->groups * 128)) return -5;
   if (a->mode == 1 && (a->out_sf == nullptr || a->w_global2 == nullptr || ((a->N >> 1) & 63))) return -3;
   if ((reinterpret_cast<uintptr_t>(a->a_packed) | reinterpret_cast<uintptr_t>(a->w_packed) | reinterpret_cast<uintptr_t>(a->a_sf) |
        reinterpret_cast<uintptr_t>(a->w_sf) | reinterpret_cast<uintptr_t>(a->out)) & 15)

@@ -353,8 +353,9 @@ moe_combine_kernel(const __nv_bfloat16* y, const int* pair_pos, const float* wei
     for (int s = 0; s < k; ++s) {
       const int pair = tok * k + s;
       const float w = weights[pair];
-      if (!TYR_INDEX_OK(pair_pos[pair], static_cast<long long>(T) * k, 13)) continue;
-      uint4 u = reinterpret_cast<const uint4*>(y + static_cast<long long>(pair_pos[pair]) * h)[c];
+      const int pp = pair_pos[pair];
+      if (pp < 0) continue;                        // a pair that was not routed to an expert of this bank
+      uint4 u = reinterpret_cast<const uint4*>(y + static_cast<long long>(pp) * h)[c];
       float2 a0 = unpack_bf16x2(u.x), a1 = unpack_bf16x2(u.y), a2 = unpack_bf16x2(u.z), a3 = unpack_bf16x2(u.w);
       acc[0] += w * a0.x; acc[1] += w * a0.y; acc[2] += w * a1.x; acc[3] += w * a1.y;
       acc[4] += w * a2.x; acc[5] += w * a2.y; acc[6] += w * a3.x; acc[7] += w * a3.y;

@@ -132,7 +132,8 @@ def test_gpu_route_and_layout(softmax):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("T,path", [(1, "gemv"), (5, "gemv"), (40, "gemv"), (40, "gemm"), (300, "gemm")])
+@pytest.mark.parametrize("T,path", [(1, "gemv"), (5, "gemv"), (40, "gemv"), (40, "gemm"), (40, "gemm_sorted"), (128, "gemm"),
+                                    (3, "gemm"), (300, "gemm")])
 def test_gpu_moe_forward_vs_eager(T, path):
     torch.manual_seed(2)
     E, mi, h, k = 16, 256, 512, 4
@@ -153,6 +154,34 @@ def test_gpu_moe_forward_vs_eager(T, path):
         assert ((y.float() - same).norm() / same.norm()).item() < 3e-2
         nrmse = ((y.float() - ref).pow(2).mean().sqrt() / ref.pow(2).mean().sqrt()).item()
         assert nrmse <= 0.35, nrmse          # the reference's W4A4 against W4A16 bar (Tests/RunLagunaFused.lean:307-341)
+
+
+@pytest.mark.gpu
+def test_gpu_moe_fixed_slots_equal_sorted_layout():
+    """At most 128 tokens: the fixed-slot path (no sorted layout) against the sorted path; the two run the same quantiser and
+    the same tensor-core kernel on the same rows, so the outputs agree bit for bit.  One pair carries an id outside the bank
+    (what a rank sees for a pair that belongs elsewhere) and must contribute nothing."""
+    from tyr_b200.ops import fp4
+    torch.manual_seed(5)
+    E, mi, h, k = 16, 256, 512, 4
+    ex = _banks(E, mi, h, device="cuda")
+    for T in (1, 17, 128):
+        x = torch.randn(T, h, device="cuda").bfloat16()
+        ids, w, _ = moe.route(torch.randn(T, E, device="cuda"), k)
+        add = torch.randn(T, h, device="cuda").bfloat16()
+        assert fp4.fixed_slots_supported(T, h)
+        y_fixed = moe.moe_fp4_forward(x, ids, w, ex, add=add, force_path="gemm")
+        y_sorted = moe.moe_fp4_forward(x, ids, w, ex, add=add, force_path="gemm_sorted")
+        assert torch.equal(y_fixed, y_sorted), (y_fixed.float() - y_sorted.float()).abs().max().item()
+    ids2 = ids.clone()
+    ids2[0, 0] = E + 3
+    w2 = w.clone()
+    y = fp4.moe_fp4_tc_forward_fixed(x, ids2, w2, ex, add=add)
+    w2[0, 0] = 0.0
+    ids2[0, 0] = ids[0, 0]
+    y_ref = fp4.moe_fp4_tc_forward_fixed(x, ids2, w2, ex, add=add)
+    assert torch.isfinite(y.float()).all()
+    assert torch.equal(y, y_ref)
 
 
 @pytest.mark.gpu

@@ -13,6 +13,7 @@ What the reference does on the hardware it supports: cc/src/tyr_laguna_moe.cu:61
 from __future__ import annotations
 
 import ctypes
+import os
 from dataclasses import dataclass
 from typing import Optional, Tuple
 
@@ -43,6 +44,10 @@ def _sigs(lib_):
     fn = getattr(lib_, "tyr_fp4_grouped_gemm", None)
     if fn is not None:
         fn.argtypes = [ctypes.POINTER(_GemmArgs)]
+        fn.restype = I
+    fn = getattr(lib_, "tyr_fp4_scatter_quantize_fixed", None)
+    if fn is not None:
+        fn.argtypes = [P, P, P, P, P, P, P, I, I, I, I, P, P]
         fn.restype = I
 
 
@@ -199,7 +204,7 @@ def grouped_gemm_fp4(a_packed, a_sf, a_row_scale, w_packed, w_sf, w_global, tile
     [padded_rows, N/4] u8, scales flat u8) of silu(gate) * up."""
     padded = a_packed.shape[0]
     dev = a_packed.device
-    groups = tiles.numel() - 1
+    groups = tiles.numel() - 1 if tiles is not None else rows.numel()     # no tile table: ``rows`` are per-expert counts
     if mode == 0:
         out = torch.empty((padded, N), dtype=torch.bfloat16, device=dev)
         out_sf = None
@@ -210,7 +215,7 @@ def grouped_gemm_fp4(a_packed, a_sf, a_row_scale, w_packed, w_sf, w_global, tile
     a.a_packed, a.a_sf, a.a_row_scale = a_packed.data_ptr(), a_sf.data_ptr(), (a_row_scale.data_ptr() if a_row_scale is not None else None)
     a.w_packed, a.w_sf, a.w_global = w_packed.data_ptr(), w_sf.data_ptr(), w_global.data_ptr()
     a.w_global2 = w_global2.data_ptr() if w_global2 is not None else None
-    a.group_tiles, a.group_rows = tiles.data_ptr(), rows.data_ptr()
+    a.group_tiles, a.group_rows = (tiles.data_ptr() if tiles is not None else None), rows.data_ptr()
     a.out, a.out_sf = out.data_ptr(), (out_sf.data_ptr() if out_sf is not None else None)
     a.padded_rows, a.N, a.K, a.groups, a.mode, a.sm_count = padded, N, K, groups, mode, sm_count
     a.err = err_word(dev).data_ptr()
@@ -236,6 +241,48 @@ def moe_fp4_tc_forward(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor
     hq, hsf = grouped_gemm_fp4(xq, xsf, xrs, w4.gu_packed, w4.gu_sf, w4.gate_global, tiles, offsets,
                                2 * mi, h, mode=1, w_global2=w4.up_global)
     y = grouped_gemm_fp4(hq, hsf, None, w4.dn_packed, w4.dn_sf, w4.dn_global, tiles, offsets, h, mi, mode=0)
+    out = torch.empty_like(x)
+    check(lib().tyr_moe_combine(ptr(y), ptr(ppos), ptr(weights.float().contiguous()), ptr(add.contiguous() if add is not None else None),
+                                ptr(out), T, k, h, st), "moe_combine")
+    return out
+
+
+FIXED_SLOT_MAX_TOKENS = 128
+
+
+_FIXED_SLOTS = os.environ.get("TYR_MOE_FIXED_SLOTS", "1") != "0"     # 0: always build the sorted layout (for comparisons)
+
+
+def fixed_slots_supported(T: int, h: int) -> bool:
+    return (_FIXED_SLOTS and T <= FIXED_SLOT_MAX_TOKENS and h % 256 == 0
+            and hasattr(lib(), "tyr_fp4_scatter_quantize_fixed"))
+
+
+def moe_fp4_tc_forward_fixed(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, ex,
+                             add: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The same product for at most 128 tokens without a sorted layout: an expert can receive a token once, so every expert
+    owns 128 fixed rows of the padded activation matrix, a row takes its slot with one atomic, and the grouped GEMM reads the
+    slot cursors as its row counts.  Four launches (scatter + quantise, gate / up, down, combine) and one memset instead of the
+    count / offsets / scatter / tile table / quantise launches of the sorted layout.  Slots are handed out in arrival order,
+    which changes nothing: a row's result does not depend on where it sits."""
+    T, h = x.shape
+    k = ids.shape[1]
+    w4 = prepared(ex)
+    E, mi = ex.num_experts, w4.moe_int
+    dev = x.device
+    st = cur_stream(dev)
+    ids32 = ids.to(torch.int32).contiguous()
+    padded = E * 128
+    cursors = torch.zeros(E, dtype=torch.int32, device=dev)
+    xq = torch.empty((padded, h // 2), dtype=torch.uint8, device=dev)
+    xsf = torch.empty(padded * (h // 16), dtype=torch.uint8, device=dev)
+    xrs = torch.empty(padded, dtype=torch.float32, device=dev)
+    ppos = torch.empty(T * k, dtype=torch.int32, device=dev)
+    check(lib().tyr_fp4_scatter_quantize_fixed(ptr(x.contiguous()), ptr(ids32), ptr(cursors), ptr(xq), ptr(xsf), ptr(xrs), ptr(ppos),
+                                               T, k, h, E, ptr(err_word(dev)), st), "fp4_scatter_quantize_fixed")
+    hq, hsf = grouped_gemm_fp4(xq, xsf, xrs, w4.gu_packed, w4.gu_sf, w4.gate_global, None, cursors,
+                               2 * mi, h, mode=1, w_global2=w4.up_global)
+    y = grouped_gemm_fp4(hq, hsf, None, w4.dn_packed, w4.dn_sf, w4.dn_global, None, cursors, h, mi, mode=0)
     out = torch.empty_like(x)
     check(lib().tyr_moe_combine(ptr(y), ptr(ppos), ptr(weights.float().contiguous()), ptr(add.contiguous() if add is not None else None),
                                 ptr(out), T, k, h, st), "moe_combine")

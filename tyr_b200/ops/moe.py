@@ -317,9 +317,6 @@ def moe_fp4_forward(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, e
         g, u, d = ex.dense()
         y = moe_eager(x, ids, weights, g, u, d)
         return y + add if add is not None else y
-    if counts is None:
-        counts = count_experts(ids, E)
-    offsets, order, pos, tiles, active = layout(ids.to(torch.int32), counts, want_active=True)
     wf = weights.float().contiguous()
     from . import fp4
     tc_ok = fp4.available() and fp4.Fp4Experts.supported(h, mi) and x.dtype == torch.bfloat16
@@ -328,10 +325,16 @@ def moe_fp4_forward(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, e
     # expert sees more than about two rows (64 tokens: 0.27 ms against 0.39 ms)
     gemv_limit = (2 if tc_ok else GEMV_MAX_PAIRS_PER_EXPERT) * E
     path = force_path or ("gemv" if (T * k <= gemv_limit and gemv_ok) else "gemm")
-    if path == "gemm" and not tc_ok:
+    if path in ("gemm", "gemm_sorted") and not tc_ok:
         path = "gemv" if gemv_ok else "eager"
     if path == "gemv" and not gemv_ok:
         path = "gemm" if tc_ok else "eager"
+    if path == "gemm" and fp4.fixed_slots_supported(T, h):
+        # decode-sized batch: fixed 128-row slots per expert, no sorted layout ("gemm_sorted" forces the layout below)
+        return fp4.moe_fp4_tc_forward_fixed(x, ids, wf, ex, add=add)
+    if counts is None:
+        counts = count_experts(ids, E)
+    offsets, order, pos, tiles, active = layout(ids.to(torch.int32), counts, want_active=True)
     st = cur_stream(x.device)
     if path == "eager":      # shapes neither kernel tiles (tiny test models): per-expert loop on banks decoded on the fly
         g, u, d = ex.dense()
