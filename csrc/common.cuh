@@ -12,6 +12,7 @@
 #include <cuda_fp16.h>
 #include <cuda.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #define TYR_EXPORT __attribute__((visibility("default")))
 
@@ -64,6 +65,45 @@ __device__ __forceinline__ bool index_ok(long long i, long long n, int tag) {
 #define TYR_INDEX_OK(i, n, tag) true
 #define TYR_DEFINE_BOUNDS_STATUS(unit)
 #endif
+
+// ---- programmatic dependent launch ---------------------------------------------------------------------------------
+// A kernel launched through `launch_dependent` may become resident while the kernel before it in the stream still
+// runs: its CTAs take the slots that the earlier kernel's CTAs leave, so launch latency and the kernel's own set-up
+// (barrier init, TMEM allocation, descriptor prefetch) overlap the earlier kernel's tail.  Contract for such a kernel:
+// `pdl_trigger()` first (lets ITS successor do the same), then set-up that touches no global memory another kernel
+// writes, then `pdl_wait()` before the first access to such memory; `pdl_wait` returns when every earlier kernel of the
+// stream has completed and its writes are visible.  Both instructions do nothing in a kernel launched the plain way.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_entry() {
+  pdl_trigger();
+  pdl_wait();
+}
+
+// TYR_PDL=0 turns the launch attribute off (every kernel then starts after its predecessor has finished).
+inline bool pdl_enabled() {
+  static const bool on = [] {
+    const char* v = getenv("TYR_PDL");
+    return v == nullptr || v[0] != '0';
+  }();
+  return on;
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));

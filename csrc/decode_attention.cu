@@ -89,6 +89,7 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
 //   (undone when they are written out): accumulator (c, e, u) of lane (g, t) is channel 64c + 16t + 8u + e of head g.
 template <int D, bool WIDE>
 __global__ void __launch_bounds__(kDecWarps * 32) decode_attention_kernel(DecodeAttnArgs a) {
+  pdl_entry();
   constexpr int NJ = D / 32;                     // 16-byte chunks per lane of a K (or Q) row
   constexpr int NC = D / 64;                     // 64-channel blocks of a V row
   constexpr int R = WIDE ? 2 : 1;                // query heads per lane: g, and g + 8 when more than 8 heads share a K/V head
@@ -356,10 +357,10 @@ extern "C" TYR_EXPORT int tyr_decode_attention_gated(const void* q, const void* 
   a.gate = (const __nv_bfloat16*)gate; a.gate_bs = gate_bs; a.gate_hs = gate_hs; a.gate_mode = gate == nullptr ? 0 : gate_mode;
   const dim3 grid(splits, Hkv, B);
   const cudaStream_t st = (cudaStream_t)stream;
-  if (D == 64 && !wide) decode_attention_kernel<64, false><<<grid, kDecWarps * 32, 0, st>>>(a);
-  else if (D == 64) decode_attention_kernel<64, true><<<grid, kDecWarps * 32, 0, st>>>(a);
-  else if (D == 128 && !wide) decode_attention_kernel<128, false><<<grid, kDecWarps * 32, 0, st>>>(a);
-  else if (D == 128) decode_attention_kernel<128, true><<<grid, kDecWarps * 32, 0, st>>>(a);
-  else decode_attention_kernel<256, false><<<grid, kDecWarps * 32, 0, st>>>(a);
-  return (int)cudaGetLastError();
+  const dim3 block(kDecWarps * 32);
+  if (D == 64 && !wide) return (int)launch_dependent(decode_attention_kernel<64, false>, grid, block, 0, st, a);
+  if (D == 64) return (int)launch_dependent(decode_attention_kernel<64, true>, grid, block, 0, st, a);
+  if (D == 128 && !wide) return (int)launch_dependent(decode_attention_kernel<128, false>, grid, block, 0, st, a);
+  if (D == 128) return (int)launch_dependent(decode_attention_kernel<128, true>, grid, block, 0, st, a);
+  return (int)launch_dependent(decode_attention_kernel<256, false>, grid, block, 0, st, a);
 }

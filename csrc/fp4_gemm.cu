@@ -217,6 +217,7 @@ fp4_scatter_quantize_fixed_kernel(const __nv_bfloat16* __restrict__ x, const int
   uint8_t* qs = q + (h >> 1);
   const int ktiles = h >> 6;
   const int tok = blockIdx.x * F4_SCATTER_WARPS + warp;
+  pdl_entry();
   if (tok >= T) return;
   const __nv_bfloat16* src = x + static_cast<long long>(tok) * h;
   float amax = 0.f;
@@ -286,6 +287,25 @@ fp4_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, Fp4Params p) {
   const int tiles_n = p.N / F4_BN;
   const int num_ks = p.K / 256;                 // stages per tile
   const int ktiles = p.K >> 6;                  // 64-element scale chunks along K
+  // set-up that reads nothing another kernel wrote: it may run while the kernel before this one drains
+  pdl_trigger();
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < F4_STAGES; ++i) {
+      mbar_init(&s.full[i], 1);
+      mbar_init(&s.empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s.acc_full[i], 1);
+      mbar_init(&s.acc_empty[i], 8);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&s.tmem_base, 512);
+    tmem_relinquish();
+  }
+  if (warp == 0 && lane == 0) tma_prefetch_desc(&tmA);
+  pdl_wait();
   if (p.group_tiles != nullptr) {
     for (int i = threadIdx.x; i <= p.groups; i += blockDim.x) {
       s.gt[i] = p.group_tiles[i];
@@ -316,7 +336,9 @@ fp4_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, Fp4Params p) {
     }
   }
   const bool fixed_slots = p.group_tiles == nullptr;
+  tc_fence_before();
   __syncthreads();
+  tc_fence_after();
   const long long tiles = static_cast<long long>(s.gt[p.groups]) * tiles_n;
   // The number of tiles is only known on the device.  All CTAs take the same number of rounds; the stride is the smallest
   // number of CTAs that finishes in that many rounds, so no round runs on a fraction of the SMs while the rest idle
@@ -326,24 +348,6 @@ fp4_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, Fp4Params p) {
   const long long stride = rounds > 0 ? (tiles + rounds - 1) / rounds : 1;
   const long long tile0 = blockIdx.x < stride ? blockIdx.x : tiles;
 
-  if (threadIdx.x == 0) {
-    for (int i = 0; i < F4_STAGES; ++i) {
-      mbar_init(&s.full[i], 1);
-      mbar_init(&s.empty[i], 1);
-    }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&s.acc_full[i], 1);
-      mbar_init(&s.acc_empty[i], 8);
-    }
-    mbar_fence_init();
-  }
-  if (warp == 1) {
-    tmem_alloc(&s.tmem_base, 512);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
   const uint32_t tmem_base = s.tmem_base;
   constexpr uint32_t kStageBytes = F4_BM * F4_BKB + F4_BN * F4_BKB + 2 * F4_SF_STAGE;
 
@@ -364,7 +368,6 @@ fp4_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, Fp4Params p) {
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
     if (elect_one()) {
-      tma_prefetch_desc(&tmA);
       uint32_t it = 0;
       bool ok = true;
       for (long long tile = tile0; tile < tiles && ok; tile += stride) {
@@ -574,11 +577,10 @@ TYR_EXPORT int tyr_fp4_scatter_quantize_fixed(const void* x, const int* ids, int
   const size_t per_warp = (static_cast<size_t>(h >> 1) + (h >> 4) + 15) & ~static_cast<size_t>(15);
   const size_t smem = per_warp * F4_SCATTER_WARPS;
   if (smem > 48 * 1024) return -3;
-  fp4_scatter_quantize_fixed_kernel<<<(T + F4_SCATTER_WARPS - 1) / F4_SCATTER_WARPS, F4_SCATTER_WARPS * 32, smem,
-                                      reinterpret_cast<cudaStream_t>(stream)>>>(
-      reinterpret_cast<const __nv_bfloat16*>(x), ids, cursors, reinterpret_cast<uint8_t*>(packed), reinterpret_cast<uint8_t*>(sf),
-      row_scale, pair_ppos, T, k, h, E, err);
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(launch_dependent(
+      fp4_scatter_quantize_fixed_kernel, dim3((T + F4_SCATTER_WARPS - 1) / F4_SCATTER_WARPS), dim3(F4_SCATTER_WARPS * 32), smem,
+      reinterpret_cast<cudaStream_t>(stream), reinterpret_cast<const __nv_bfloat16*>(x), ids, cursors,
+      reinterpret_cast<uint8_t*>(packed), reinterpret_cast<uint8_t*>(sf), row_scale, pair_ppos, T, k, h, E, err));
 }
 
 struct TyrFp4GemmArgs {
@@ -635,8 +637,7 @@ TYR_EXPORT int tyr_fp4_grouped_gemm(const TyrFp4GemmArgs* a) {
   const long long max_tiles = static_cast<long long>(a->padded_rows / 128) * (a->N / 128);
   if (max_tiles < grid) grid = static_cast<int>(max_tiles);
   if (grid < 1) grid = 1;
-  fp4_grouped_gemm_kernel<<<grid, 320, smem, reinterpret_cast<cudaStream_t>(a->stream)>>>(tmA, p);
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e = launch_dependent(fp4_grouped_gemm_kernel, dim3(grid), dim3(320), smem, reinterpret_cast<cudaStream_t>(a->stream), tmA, p);
   return e == cudaSuccess ? 0 : 2000 + static_cast<int>(e);
 }
 

@@ -219,6 +219,7 @@ __global__ void __launch_bounds__(256) moe_route_fused_kernel(RouteArgs a, const
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tok0 = blockIdx.x * kRouteTok;
   const int nt = min(kRouteTok, a.T - tok0);
+  pdl_entry();
 #pragma unroll 4
   for (int i = threadIdx.x * 8; i < nt * h; i += blockDim.x * 8)
     *reinterpret_cast<uint4*>(xs + i) = *reinterpret_cast<const uint4*>(x + static_cast<long long>(tok0) * h + i);
@@ -345,6 +346,7 @@ moe_gather_rows_kernel(const __nv_bfloat16* src, const int* pair_order, __nv_bfl
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const __nv_bfloat16* y, const int* pair_pos, const float* weights, const __nv_bfloat16* add,
                    __nv_bfloat16* out, int T, int k, int h) {
+  pdl_entry();
   const int vec = h >> 3;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
        i < static_cast<long long>(T) * vec; i += static_cast<long long>(gridDim.x) * blockDim.x) {
@@ -659,9 +661,8 @@ extern "C" TYR_EXPORT int tyr_moe_route_fused(const void* x, const float* router
   }
   RouteArgs a{nullptr, bias, ids, weights, counts, T, E, k, softmax, renorm, softcap, scale};
   dim3 grid((T + kRouteTok - 1) / kRouteTok, (E + kRouteExp - 1) / kRouteExp);
-  moe_route_fused_kernel<<<grid, 256, smem, (cudaStream_t)stream>>>(a, (const __nv_bfloat16*)x, router_w, logits,
-                                                                    tickets, h);
-  return (int)cudaGetLastError();
+  return (int)launch_dependent(moe_route_fused_kernel, grid, dim3(256), smem, (cudaStream_t)stream, a, (const __nv_bfloat16*)x,
+                               router_w, logits, tickets, h);
 }
 
 extern "C" TYR_EXPORT int tyr_moe_layout(const int* ids, const int* counts, int* offsets, int* cursors,
@@ -693,9 +694,8 @@ extern "C" TYR_EXPORT int tyr_moe_gather_rows(const void* src, const int* pair_o
 extern "C" TYR_EXPORT int tyr_moe_combine(const void* y, const int* pair_pos, const float* weights, const void* add,
                                           void* out, int T, int k, int h, void* stream) {
   if (T <= 0 || (h & 7)) return -1;
-  moe_combine_kernel<<<blocks_for(1LL * T * (h / 8)), 256, 0, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)y, pair_pos, weights, (const __nv_bfloat16*)add, (__nv_bfloat16*)out, T, k, h);
-  return (int)cudaGetLastError();
+  return (int)launch_dependent(moe_combine_kernel, dim3(blocks_for(1LL * T * (h / 8))), dim3(256), 0, (cudaStream_t)stream,
+                               (const __nv_bfloat16*)y, pair_pos, weights, (const __nv_bfloat16*)add, (__nv_bfloat16*)out, T, k, h);
 }
 
 static int pick_split(int ctas, int steps, int sm_count) {

@@ -200,6 +200,7 @@ struct RmsWArgs {
 };
 
 __global__ void __launch_bounds__(256) rmsnorm_weighted_kernel(RmsWArgs a) {
+  pdl_entry();
   const int warps = blockDim.x >> 5;
   const int lane = threadIdx.x & 31;
   const int nvec = a.D >> 3;
@@ -269,6 +270,7 @@ __global__ void __launch_bounds__(256) rmsnorm_weighted_kernel(RmsWArgs a) {
 constexpr int kRowVecs = 4;     // 16-byte vectors per thread: D <= 256 * 4 * 8
 
 __global__ void __launch_bounds__(256) rmsnorm_weighted_row_kernel(RmsWArgs a) {
+  pdl_entry();
   __shared__ float red[8];
   const int tid = threadIdx.x;
   const int nvec = a.D >> 3;
@@ -400,8 +402,6 @@ extern "C" TYR_EXPORT int tyr_rmsnorm_weighted(const void* x, const void* w, con
   a.resid_out = (__nv_bfloat16*)resid_out; a.y = (__nv_bfloat16*)y;
   a.rows = rows; a.D = D; a.eps = eps; a.one_plus_w = one_plus_w;
   if (rows <= 2048 && D >= 1024 && D <= 256 * kRowVecs * 8)
-    rmsnorm_weighted_row_kernel<<<rows, 256, 0, (cudaStream_t)stream>>>(a);
-  else
-    rmsnorm_weighted_kernel<<<grid_for_rows(rows, 8), 256, 0, (cudaStream_t)stream>>>(a);
-  return (int)cudaGetLastError();
+    return (int)launch_dependent(rmsnorm_weighted_row_kernel, dim3(rows), dim3(256), 0, (cudaStream_t)stream, a);
+  return (int)launch_dependent(rmsnorm_weighted_kernel, dim3(grid_for_rows(rows, 8)), dim3(256), 0, (cudaStream_t)stream, a);
 }

@@ -398,6 +398,7 @@ struct RopeNormArgs {
 };
 
 __global__ void __launch_bounds__(256) rope_norm_kernel(RopeNormArgs a) {
+  pdl_entry();
   const int lane = threadIdx.x & 31;
   const long long unit0 = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const long long units = static_cast<long long>(a.rows) * a.H;
@@ -493,8 +494,7 @@ extern "C" TYR_EXPORT int tyr_rope_norm(const void* x, void* y, const void* w, c
   if (rot > D || (rot & 1)) return -1;
   RopeNormArgs a{(const __nv_bfloat16*)x, (__nv_bfloat16*)y, (const __nv_bfloat16*)w, cosT, sinT,
                  pos, row_stride, y_row_stride, rows, T, H, D, rot, eps, one_plus_w};
-  rope_norm_kernel<<<grid_for_units(1LL * rows * H, 8), 256, 0, (cudaStream_t)stream>>>(a);
-  return (int)cudaGetLastError();
+  return (int)launch_dependent(rope_norm_kernel, dim3(grid_for_units(1LL * rows * H, 8)), dim3(256), 0, (cudaStream_t)stream, a);
 }
 
 TYR_DEFINE_BOUNDS_STATUS(rope)
