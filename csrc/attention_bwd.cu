@@ -106,6 +106,7 @@ __global__ void __launch_bounds__(640, 1)
 flash_bwd_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                       const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                       BwdParams p) {
+  pdl_trigger();
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   BwdSmem& s = *reinterpret_cast<BwdSmem*>(smem_raw);
   if ((smem_u32(smem_raw) & 1023u) != 0) {       // the swizzled tiles need a 1024-byte aligned base
@@ -150,6 +151,7 @@ flash_bwd_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = s.tmem_base;
+  pdl_wait();                                   // everything above touched no global memory
   constexpr uint32_t COL_S = 0, COL_DV = 128, COL_DP = 256, COL_DK = 384;
 
   if (warp >= 16) {
@@ -418,6 +420,7 @@ flash_bwd_prepare_kernel(const __nv_bfloat16* __restrict__ dO, const __nv_bfloat
                          const float* __restrict__ lse, float* __restrict__ lse2, float* __restrict__ delta, int B, int H,
                          int Tq, int Tpad, long long do_sb, long long do_st, long long do_sh, long long o_sb, long long o_st,
                          long long o_sh) {
+  pdl_entry();
   const int total = B * H * Tpad;
   const int sub = threadIdx.x & 15;
   for (int w = blockIdx.x * 16 + (threadIdx.x >> 4); w < total; w += gridDim.x * 16) {
@@ -480,6 +483,7 @@ __device__ __forceinline__ void k_range(const BwdParams& p, int r0, int& lo, int
 __global__ void __launch_bounds__(576, 1)
 flash_bwd_dq_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                          const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO, BwdParams p) {
+  pdl_trigger();
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   DqSmem& s = *reinterpret_cast<DqSmem*>(smem_raw);
   if ((smem_u32(smem_raw) & 1023u) != 0) {
@@ -523,6 +527,7 @@ flash_bwd_dq_d128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_c
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = s.tmem_base;
+  pdl_wait();                                   // everything above touched no global memory
   // S is double buffered (columns 0..127 and 384..511): S_{j+1} is computed while the score warps still work on block j,
   // so they go from dS_j straight to the exponentials of block j+1.
   constexpr uint32_t COL_S0 = 0, COL_DP = 128, COL_DQ = 256, COL_S1 = 384;
@@ -828,7 +833,7 @@ extern "C" TYR_EXPORT int tyr_flash_bwd(const void* dout, const void* q, const v
   {
     long long blocks = (rows + 15) / 16;
     if (blocks > 148LL * 64) blocks = 148LL * 64;
-    flash_bwd_prepare_kernel<<<(unsigned)blocks, 256, 0, cs>>>(
+    launch_dependent(flash_bwd_prepare_kernel, dim3((unsigned)blocks), dim3(256), 0, cs,
         (const __nv_bfloat16*)dout, (const __nv_bfloat16*)o, lse, lse2, delta, B, Hq, Tq, tpad, sdo[0], sdo[1],
         sdo[2], so[0], so[1], so[2]);
   }
@@ -844,8 +849,8 @@ extern "C" TYR_EXPORT int tyr_flash_bwd(const void* dout, const void* q, const v
   p.dq_sb = sdq[0]; p.dq_st = sdq[1]; p.dq_sh = sdq[2];
   p.err = err;
   dim3 grid((Tk + BW_T - 1) / BW_T, Hkv, B);
-  flash_bwd_d128_kernel<<<grid, 640, smem, cs>>>(tq, tk, tv, tdo, p);
-  flash_bwd_dq_d128_kernel<<<dim3((Tq + BW_T - 1) / BW_T, Hq, B), 576, smem_dq, cs>>>(tq, tk, tv, tdo, p);
+  launch_dependent(flash_bwd_d128_kernel, dim3(grid), dim3(640), smem, cs, tq, tk, tv, tdo, p);
+  launch_dependent(flash_bwd_dq_d128_kernel, dim3((Tq + BW_T - 1) / BW_T, Hq, B), dim3(576), smem_dq, cs, tq, tk, tv, tdo, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 2000 + (int)e;
 }

@@ -138,6 +138,7 @@ __global__ void __launch_bounds__(640, 1)
 flash_fwd_d128_kernel(const __grid_constant__ CUtensorMap tmQ,
                       const __grid_constant__ CUtensorMap tmK,
                       const __grid_constant__ CUtensorMap tmV, AttnParams p) {
+  pdl_trigger();
   extern __shared__ uint8_t smem_raw[];
   AttnSmem& s = *reinterpret_cast<AttnSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -184,6 +185,7 @@ flash_fwd_d128_kernel(const __grid_constant__ CUtensorMap tmQ,
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = s.tmem_base;
+  pdl_wait();                                   // everything above touched no global memory
   constexpr uint32_t kChunk = ATT_BM * 64 * 2;   // one [128 x 64] bf16 swizzled chunk = 16 KB
 
   // Register re-allocation between warpgroups: the four softmax warpgroups keep 64 scores per thread in registers, the
@@ -529,7 +531,7 @@ extern "C" TYR_EXPORT int tyr_flash_fwd(const void* q, const void* k, const void
   p.O = (__nv_bfloat16*)o; p.o_row_stride = o_st; p.o_batch_stride = o_sb; p.o_head_stride = o_sh;
   p.lse = lse; p.err = err;
   dim3 grid((Tq + 2 * ATT_BM - 1) / (2 * ATT_BM), Hq, B);
-  flash_fwd_d128_kernel<<<grid, 640, smem, (cudaStream_t)stream>>>(tq, tk, tv, p);
+  launch_dependent(flash_fwd_d128_kernel, dim3(grid), dim3(640), smem, (cudaStream_t)stream, tq, tk, tv, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 2000 + (int)e;
 }

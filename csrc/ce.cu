@@ -32,6 +32,7 @@ __device__ __forceinline__ float softcap(float l, float cap, float inv_cap) {
 }
 
 __global__ void __launch_bounds__(512) softcap_ce_kernel(CeArgs a) {
+  pdl_entry();
   __shared__ float red_m[16], red_s[16];
   __shared__ float sh_m, sh_lse;
   const int tid = threadIdx.x;
@@ -144,6 +145,6 @@ extern "C" TYR_EXPORT int tyr_softcap_ce(void* logits, const long long* targets,
   CeArgs a{(__nv_bfloat16*)logits, targets, loss_rows, bad_count, rows, V, ld, cap, gscale,
            gscale_dev, ignore_index, write_grad};
   const int grid = rows < 148 * 8 ? rows : 148 * 8;
-  softcap_ce_kernel<<<grid, 512, 0, (cudaStream_t)stream>>>(a);
+  launch_dependent(softcap_ce_kernel, dim3(grid), dim3(512), 0, (cudaStream_t)stream, a);
   return (int)cudaGetLastError();
 }

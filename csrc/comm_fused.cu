@@ -545,6 +545,7 @@ namespace tyr {
 __global__ void __launch_bounds__(256)
 slot_sum_bf16_kernel(const __nv_bfloat16* __restrict__ slots, int world, long long n, const __nv_bfloat16* __restrict__ add,
                      __nv_bfloat16* __restrict__ out) {
+  pdl_entry();
   const long long nvec = n >> 3;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
@@ -572,7 +573,7 @@ extern "C" TYR_EXPORT int tyr_slot_sum_bf16(const void* slots, int world, long l
   if (world < 1 || world > tyr::kMaxRanks || n <= 0 || (n & 7)) return -1;
   long long blocks = (n / 8 + 255) / 256;
   if (blocks > 148 * 8) blocks = 148 * 8;
-  tyr::slot_sum_bf16_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)slots, world, n,
+  tyr::launch_dependent(tyr::slot_sum_bf16_kernel, dim3((int)blocks), dim3(256), 0, (cudaStream_t)stream, (const __nv_bfloat16*)slots, world, n,
                                                                           (const __nv_bfloat16*)add, (__nv_bfloat16*)out);
   return (int)cudaGetLastError();
 }
@@ -585,6 +586,7 @@ extern "C" TYR_EXPORT int tyr_slot_sum_bf16(const void* slots, int world, long l
 namespace tyr {
 __global__ void __launch_bounds__(256)
 peer_sum_bf16_kernel(PeerPtrs src, int world, long long n, const __nv_bfloat16* __restrict__ add, __nv_bfloat16* __restrict__ out) {
+  pdl_entry();
   const long long nvec = n >> 3;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
@@ -640,6 +642,7 @@ struct TpArNormArgs {
 constexpr int kArVecs = 4;      // 16-byte vectors per thread: N <= 256 * 4 * 8 = 8192
 
 __global__ void __launch_bounds__(256) tp_allreduce_norm_kernel(TpArNormArgs a) {
+  pdl_entry();
   __shared__ float red[8];
   const int tid = threadIdx.x;
   const unsigned long long value = *a.seq + 1;
@@ -760,7 +763,7 @@ extern "C" TYR_EXPORT int tyr_tp_allreduce_norm(void* const* part_ptrs, void* co
   a.resid = (const __nv_bfloat16*)resid; a.norm_w = (const __nv_bfloat16*)norm_w;
   a.out_resid = (__nv_bfloat16*)out_resid; a.out_norm = (__nv_bfloat16*)out_norm;
   a.world = world; a.my_rank = my_rank; a.slot_base = slot_base; a.M = M; a.N = N; a.one_plus_w = one_plus_w; a.eps = eps; a.err = err;
-  tp_allreduce_norm_kernel<<<M, 256, 0, (cudaStream_t)stream>>>(a);
+  launch_dependent(tp_allreduce_norm_kernel, dim3(M), dim3(256), 0, (cudaStream_t)stream, a);
   return (int)cudaGetLastError();
 }
 
@@ -770,6 +773,7 @@ extern "C" TYR_EXPORT int tyr_tp_allreduce_norm(void* const* part_ptrs, void* co
 namespace tyr {
 __global__ void __launch_bounds__(256)
 peer_gather_cols_bf16_kernel(PeerPtrs src, int world, int M, int Nl, __nv_bfloat16* __restrict__ out) {
+  pdl_entry();
   const int vpr = Nl >> 3;                                    // vectors per source row
   const long long total = static_cast<long long>(world) * M * vpr;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
@@ -808,7 +812,7 @@ extern "C" TYR_EXPORT int tyr_peer_gather_cols_bf16(void* const* src_ptrs, int w
   long long blocks = (static_cast<long long>(world) * M * (Nl >> 3) + 1023) / 1024;
   if (blocks > 148 * 4) blocks = 148 * 4;
   if (blocks < 1) blocks = 1;
-  tyr::peer_gather_cols_bf16_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>(make_peers(src_ptrs, world), world, M, Nl,
+  tyr::launch_dependent(tyr::peer_gather_cols_bf16_kernel, dim3((int)blocks), dim3(256), 0, (cudaStream_t)stream, make_peers(src_ptrs, world), world, M, Nl,
                                                                                    (__nv_bfloat16*)out);
   return (int)cudaGetLastError();
 }
@@ -818,7 +822,7 @@ extern "C" TYR_EXPORT int tyr_peer_sum_bf16(void* const* src_ptrs, int world, lo
   if (world < 1 || world > tyr::kMaxRanks || n <= 0 || (n & 7)) return -1;
   long long blocks = (n / 8 + 255) / 256;
   if (blocks > 148 * 4) blocks = 148 * 4;
-  tyr::peer_sum_bf16_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>(make_peers(src_ptrs, world), world, n,
+  tyr::launch_dependent(tyr::peer_sum_bf16_kernel, dim3((int)blocks), dim3(256), 0, (cudaStream_t)stream, make_peers(src_ptrs, world), world, n,
                                                                           (const __nv_bfloat16*)add, (__nv_bfloat16*)out);
   return (int)cudaGetLastError();
 }

@@ -230,6 +230,11 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
 // ----------------------------------------------------------------------------------------
 // TMA (bulk tensor copies on this GPU's own memory; no load is ever multicast to several CTAs)
 // ----------------------------------------------------------------------------------------
+// Asks the L2 for `bytes` (a multiple of 16) from a 16-byte aligned global address; nothing waits for it.
+__device__ __forceinline__ void bulk_prefetch_l2(const void* gptr, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(gptr), "r"(bytes) : "memory");
+}
+
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }

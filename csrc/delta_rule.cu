@@ -21,6 +21,7 @@ gdr_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __re
                   int Hk, int Hv, int dv, long long q_bstride, long long v_bstride,
                   const __nv_bfloat16* __restrict__ z, long long z_bstride, const __nv_bfloat16* __restrict__ norm_w,
                   float norm_eps) {
+  pdl_entry();
   // z != nullptr (dv == 128, one column pass): the layer's gated RMSNorm runs in the epilogue,
   //   out = rmsnorm_over_dv(o) * norm_w * silu(z),
   // with o rounded to bf16 first, as the separate kernels see it.
@@ -115,6 +116,7 @@ gdn_conv_gates_kernel(const __nv_bfloat16* __restrict__ mixed, const __nv_bfloat
                       const __nv_bfloat16* __restrict__ conv_w, const __nv_bfloat16* __restrict__ conv_b,
                       const float* __restrict__ dt_bias, const float* __restrict__ a_log, __nv_bfloat16* __restrict__ conv_out,
                       float* __restrict__ g, float* __restrict__ beta, int B, int cd, int K, int Hv) {
+  pdl_entry();
   const long long idx = blockIdx.x * 256LL + threadIdx.x;
   const long long n_conv = static_cast<long long>(B) * cd;
   if (idx < n_conv) {
@@ -738,7 +740,7 @@ extern "C" TYR_EXPORT int tyr_gdn_conv_gates(const void* mixed, const void* b_in
   using namespace tyr;
   if (B <= 0 || cd <= 0 || K < 1 || K > 8 || Hv <= 0) return -1;
   const long long n = static_cast<long long>(B) * cd + static_cast<long long>(B) * Hv;
-  gdn_conv_gates_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  launch_dependent(gdn_conv_gates_kernel, dim3(static_cast<unsigned>((n + 255) / 256)), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
       (const __nv_bfloat16*)mixed, (const __nv_bfloat16*)b_in, (const __nv_bfloat16*)a_in, ld_m, ld_b, ld_a, (__nv_bfloat16*)conv_state,
       (const __nv_bfloat16*)conv_w, (const __nv_bfloat16*)conv_b, dt_bias, a_log, (__nv_bfloat16*)conv_out, g, beta, B, cd, K, Hv);
   return static_cast<int>(cudaGetLastError());
@@ -771,10 +773,10 @@ extern "C" TYR_EXPORT int tyr_gdr_decode_norm(const void* q, const void* k, cons
   auto* vv = reinterpret_cast<const __nv_bfloat16*>(v);
   auto* oo = reinterpret_cast<__nv_bfloat16*>(out);
   if (dk == 128)
-    gdr_decode_kernel<128><<<grid, 512, 0, st>>>(qq, kk, vv, g, beta, state, oo, Hk, Hv, dv, q_bstride, v_bstride, zz, z_bstride,
+    launch_dependent(gdr_decode_kernel<128>, dim3(grid), dim3(512), 0, st, qq, kk, vv, g, beta, state, oo, Hk, Hv, dv, q_bstride, v_bstride, zz, z_bstride,
                                                  nw, norm_eps);
   else if (dk == 64)
-    gdr_decode_kernel<64><<<grid, 512, 0, st>>>(qq, kk, vv, g, beta, state, oo, Hk, Hv, dv, q_bstride, v_bstride, zz, z_bstride,
+    launch_dependent(gdr_decode_kernel<64>, dim3(grid), dim3(512), 0, st, qq, kk, vv, g, beta, state, oo, Hk, Hv, dv, q_bstride, v_bstride, zz, z_bstride,
                                                 nw, norm_eps);
   else
     return -2;

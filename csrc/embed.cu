@@ -20,6 +20,7 @@ __global__ void __launch_bounds__(256)
 embed_grad_sorted_kernel(const __nv_bfloat16* __restrict__ dy, const long long* __restrict__ order,
                          const long long* __restrict__ sorted_ids, float* __restrict__ grad, int N, int d, long long ld,
                          int V) {
+  pdl_entry();
   __shared__ long long s_row[kEmbedRun];
   __shared__ long long s_id[kEmbedRun];
   const int p0 = blockIdx.x * kEmbedRun;
@@ -76,7 +77,7 @@ extern "C" TYR_EXPORT int tyr_embed_grad_sorted(const void* dy, const long long*
   if ((reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(grad)) & 15) return -1;
   const int blocks = (N + tyr::kEmbedRun - 1) / tyr::kEmbedRun;
   const int threads = d / 8 >= 256 ? 256 : ((d / 8 + 31) / 32) * 32;
-  tyr::embed_grad_sorted_kernel<<<blocks, threads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  tyr::launch_dependent(tyr::embed_grad_sorted_kernel, dim3(blocks), dim3(threads), 0, reinterpret_cast<cudaStream_t>(stream),
       reinterpret_cast<const __nv_bfloat16*>(dy), order, sorted_ids, grad, N, d, ld, V);
   return static_cast<int>(cudaGetLastError());
 }

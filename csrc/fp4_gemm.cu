@@ -147,6 +147,7 @@ fp4_gather_quantize_kernel(const __nv_bfloat16* __restrict__ x, const int* __res
                            const int* __restrict__ ids, const int* __restrict__ offsets,
                            const int* __restrict__ group_tiles, uint8_t* __restrict__ packed, uint8_t* __restrict__ sf,
                            float* __restrict__ row_scale, int* __restrict__ pair_ppos, int pairs, int k, int h, int E) {
+  pdl_entry();
   const int lane = threadIdx.x & 31;
   const int ktiles = h >> 6;
   for (int pos = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); pos < pairs; pos += gridDim.x * (blockDim.x >> 5)) {
@@ -562,7 +563,7 @@ TYR_EXPORT int tyr_fp4_gather_quantize(const void* x, const int* pair_order, con
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(packed)) & 15) return -2;
   long long blocks = (pairs + 7) / 8;
   if (blocks > 148 * 16) blocks = 148 * 16;
-  fp4_gather_quantize_kernel<<<static_cast<unsigned>(blocks), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  launch_dependent(fp4_gather_quantize_kernel, dim3(static_cast<unsigned>(blocks)), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
       reinterpret_cast<const __nv_bfloat16*>(x), pair_order, ids, offsets, group_tiles, reinterpret_cast<uint8_t*>(packed),
       reinterpret_cast<uint8_t*>(sf), row_scale, pair_ppos, pairs, k, h, E);
   return static_cast<int>(cudaGetLastError());

@@ -167,22 +167,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
   const int tiles_m = (p.M + TILE_M - 1) / TILE_M;
   const int tiles_n = (p.N + BN - 1) / BN;
   const int num_kb = (p.K + BK - 1) / BK;
-  const bool grouped = p.group_offsets != nullptr;
-  const long long tiles = grouped ? static_cast<long long>(p.group_tiles[p.batch]) * tiles_n
-                                  : static_cast<long long>(tiles_m) * tiles_n * p.batch;
-
-  // Work range for this CTA, in (tile, k-block) units.
-  long long unit_begin, unit_end;
-  if (p.out_mode == 2) {
-    const long long units = tiles * num_kb;
-    unit_begin = units * worker / n_workers;
-    unit_end = units * (worker + 1) / n_workers;
-  } else {
-    // tile-granular, strided assignment expressed in the same unit space
-    unit_begin = 0;
-    unit_end = 0;
-  }
-
+  // set-up that reads nothing another kernel wrote: it may overlap the tail of the kernel before this one
+  pdl_trigger();
   if (threadIdx.x == 0) {
     for (int i = 0; i < STAGES; ++i) {
       mbar_init(&s.full[i], 1);
@@ -212,6 +198,23 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
   }
   tc_fence_after();
   const uint32_t tmem_base = s.tmem_base;
+  pdl_wait();
+
+  const bool grouped = p.group_offsets != nullptr;
+  const long long tiles = grouped ? static_cast<long long>(p.group_tiles[p.batch]) * tiles_n
+                                  : static_cast<long long>(tiles_m) * tiles_n * p.batch;
+
+  // Work range for this CTA, in (tile, k-block) units.
+  long long unit_begin, unit_end;
+  if (p.out_mode == 2) {
+    const long long units = tiles * num_kb;
+    unit_begin = units * worker / n_workers;
+    unit_end = units * (worker + 1) / n_workers;
+  } else {
+    // tile-granular, strided assignment expressed in the same unit space
+    unit_begin = 0;
+    unit_end = 0;
+  }
 
   constexpr uint32_t kStageBytes = BM * BK * 2 + BNL * BK * 2;
 
@@ -900,14 +903,16 @@ static int launch_gemm(const TyrGemmArgs& a, const CUtensorMap& tmA, const CUten
     cfg.blockDim = dim3(kThreads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = reinterpret_cast<cudaStream_t>(a.stream);
-    cudaLaunchAttribute at[1];
+    cudaLaunchAttribute at[2];
     at[0].id = cudaLaunchAttributeClusterDimension;
     at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
-    cfg.attrs = at; cfg.numAttrs = 1;
+    at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[1].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+    cfg.attrs = at; cfg.numAttrs = 2;
     cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmC, tmP, p);
     return e == cudaSuccess ? 0 : 2000 + static_cast<int>(e);
   }
-  kern<<<grid, 256, smem, reinterpret_cast<cudaStream_t>(a.stream)>>>(tmA, tmB, tmC, tmP, p);
+  launch_dependent(kern, dim3(grid), dim3(256), smem, reinterpret_cast<cudaStream_t>(a.stream), tmA, tmB, tmC, tmP, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 2000 + static_cast<int>(e);
 }

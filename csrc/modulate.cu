@@ -29,6 +29,7 @@ __global__ void __launch_bounds__(256)
 layernorm_modulate_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ scale,
                           const __nv_bfloat16* __restrict__ shift, __nv_bfloat16* __restrict__ y,
                           long long rows, int seq, int D, long long mod_bstride, float eps) {
+  pdl_entry();
   const int warps = blockDim.x >> 5, lane = threadIdx.x & 31;
   const int nvec = D >> 3;
   for (long long row = blockIdx.x * static_cast<long long>(warps) + (threadIdx.x >> 5); row < rows;
@@ -68,6 +69,7 @@ __global__ void __launch_bounds__(256)
 gate_residual_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ yv,
                      const __nv_bfloat16* __restrict__ gate, __nv_bfloat16* __restrict__ out,
                      long long rows, int seq, int D, long long mod_bstride) {
+  pdl_entry();
   const int nvec = D >> 3;
   const long long total = rows * nvec;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
@@ -101,6 +103,7 @@ struct FluxQkPostArgs {
 // One warp per (batch, row, head): lane l owns elements 4l .. 4l+3 of the 128-wide head, i.e. the rotation pairs 2l and 2l+1.
 // fp32 throughout; one rounding to bf16 at the end (the unfused sequence rounds after the norm as well).
 __global__ void __launch_bounds__(256) flux_qk_post_kernel(FluxQkPostArgs a) {
+  pdl_entry();
   const int lane = threadIdx.x & 31;
   const long long total = static_cast<long long>(a.B) * a.S * a.H;
   const float2 wq0 = unpack_bf16x2(reinterpret_cast<const uint32_t*>(a.wq)[2 * lane]);
@@ -162,7 +165,7 @@ extern "C" TYR_EXPORT int tyr_flux_qk_post(const void* src, long long src_sb, lo
   a.B = B; a.S = S; a.H = H; a.dst_row0 = dst_row0; a.copy_v = copy_v; a.eps = eps;
   long long blocks = (static_cast<long long>(B) * S * H + 7) / 8;
   if (blocks > 148LL * 32) blocks = 148LL * 32;
-  flux_qk_post_kernel<<<static_cast<int>(blocks), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(a);
+  launch_dependent(flux_qk_post_kernel, dim3(static_cast<int>(blocks)), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream), a);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -173,7 +176,7 @@ extern "C" TYR_EXPORT int tyr_layernorm_modulate(const void* x, const void* scal
   if (rows <= 0 || seq <= 0 || (D & 7) || (mod_bstride & 7)) return -1;
   long long blocks = (rows + 7) / 8;
   if (blocks > 148 * 16) blocks = 148 * 16;
-  layernorm_modulate_kernel<<<static_cast<int>(blocks), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  launch_dependent(layernorm_modulate_kernel, dim3(static_cast<int>(blocks)), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
       (const __nv_bfloat16*)x, (const __nv_bfloat16*)scale, (const __nv_bfloat16*)shift, (__nv_bfloat16*)y, rows, seq, D,
       mod_bstride, eps);
   return static_cast<int>(cudaGetLastError());
@@ -185,7 +188,7 @@ extern "C" TYR_EXPORT int tyr_gate_residual(const void* x, const void* y, const 
   if (rows <= 0 || seq <= 0 || (D & 7) || (mod_bstride & 7)) return -1;
   long long blocks = (rows * (D >> 3) + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
-  gate_residual_kernel<<<static_cast<int>(blocks), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  launch_dependent(gate_residual_kernel, dim3(static_cast<int>(blocks)), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
       (const __nv_bfloat16*)x, (const __nv_bfloat16*)y, (const __nv_bfloat16*)gate, (__nv_bfloat16*)out, rows, seq, D,
       mod_bstride);
   return static_cast<int>(cudaGetLastError());

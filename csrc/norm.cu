@@ -39,6 +39,7 @@ template <int NIN>
 __global__ void __launch_bounds__(256)
 lincomb_rmsnorm_fwd_kernel(LincombArgs a, __nv_bfloat16* __restrict__ out,
                            __nv_bfloat16* __restrict__ normed) {
+  pdl_entry();
   const int warps = blockDim.x >> 5;
   const int lane = threadIdx.x & 31;
   float s[NIN];
@@ -110,6 +111,7 @@ struct LincombBwdArgs {
 template <int NIN>
 __global__ void __launch_bounds__(256)
 lincomb_rmsnorm_bwd_kernel(LincombBwdArgs a) {
+  pdl_entry();
   const int warps = blockDim.x >> 5;
   const int lane = threadIdx.x & 31;
   const int wid = threadIdx.x >> 5;
@@ -356,10 +358,10 @@ extern "C" TYR_EXPORT int tyr_lincomb_rmsnorm_fwd(const void* t0, const void* t1
   auto o = (__nv_bfloat16*)out;
   auto n = (__nv_bfloat16*)normed;
   switch (n_in) {
-    case 1: lincomb_rmsnorm_fwd_kernel<1><<<grid, 256, 0, st>>>(a, o, n); break;
-    case 2: lincomb_rmsnorm_fwd_kernel<2><<<grid, 256, 0, st>>>(a, o, n); break;
-    case 3: lincomb_rmsnorm_fwd_kernel<3><<<grid, 256, 0, st>>>(a, o, n); break;
-    default: lincomb_rmsnorm_fwd_kernel<4><<<grid, 256, 0, st>>>(a, o, n); break;
+    case 1: launch_dependent(lincomb_rmsnorm_fwd_kernel<1>, dim3(grid), dim3(256), 0, st, a, o, n); break;
+    case 2: launch_dependent(lincomb_rmsnorm_fwd_kernel<2>, dim3(grid), dim3(256), 0, st, a, o, n); break;
+    case 3: launch_dependent(lincomb_rmsnorm_fwd_kernel<3>, dim3(grid), dim3(256), 0, st, a, o, n); break;
+    default: launch_dependent(lincomb_rmsnorm_fwd_kernel<4>, dim3(grid), dim3(256), 0, st, a, o, n); break;
   }
   return (int)cudaGetLastError();
 }
@@ -383,10 +385,10 @@ extern "C" TYR_EXPORT int tyr_lincomb_rmsnorm_bwd(const void* const* t, void* co
   const int grid = grid_for_rows(rows, 8);
   cudaStream_t st = (cudaStream_t)stream;
   switch (n_in) {
-    case 1: lincomb_rmsnorm_bwd_kernel<1><<<grid, 256, 0, st>>>(a); break;
-    case 2: lincomb_rmsnorm_bwd_kernel<2><<<grid, 256, 0, st>>>(a); break;
-    case 3: lincomb_rmsnorm_bwd_kernel<3><<<grid, 256, 0, st>>>(a); break;
-    default: lincomb_rmsnorm_bwd_kernel<4><<<grid, 256, 0, st>>>(a); break;
+    case 1: launch_dependent(lincomb_rmsnorm_bwd_kernel<1>, dim3(grid), dim3(256), 0, st, a); break;
+    case 2: launch_dependent(lincomb_rmsnorm_bwd_kernel<2>, dim3(grid), dim3(256), 0, st, a); break;
+    case 3: launch_dependent(lincomb_rmsnorm_bwd_kernel<3>, dim3(grid), dim3(256), 0, st, a); break;
+    default: launch_dependent(lincomb_rmsnorm_bwd_kernel<4>, dim3(grid), dim3(256), 0, st, a); break;
   }
   return (int)cudaGetLastError();
 }

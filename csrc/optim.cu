@@ -43,6 +43,7 @@ __device__ __forceinline__ void adam_elem(float& p, float g, float& m, float& v,
 }
 
 __global__ void __launch_bounds__(256) adamw_kernel(AdamArgs a) {
+  pdl_entry();
   const long long n4 = a.n >> 2;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n4;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
@@ -89,6 +90,7 @@ struct MuonMomArgs {
 };
 
 __global__ void __launch_bounds__(256) muon_momentum_kernel(MuonMomArgs a) {
+  pdl_entry();
   // grid.y = matrix index, grid.x = chunk of the matrix
   const int b = blockIdx.y;
   const long long base = static_cast<long long>(b) * a.per;
@@ -126,6 +128,7 @@ __global__ void __launch_bounds__(256) muon_momentum_kernel(MuonMomArgs a) {
 
 __global__ void __launch_bounds__(256)
 scale_by_inv_norm_kernel(__nv_bfloat16* x, const float* sumsq, long long per, float eps) {
+  pdl_entry();
   const int b = blockIdx.y;
   const float inv = 1.f / (sqrtf(sumsq[b]) + eps);
   const long long base = static_cast<long long>(b) * per;
@@ -145,6 +148,7 @@ scale_by_inv_norm_kernel(__nv_bfloat16* x, const float* sumsq, long long per, fl
 __global__ void __launch_bounds__(256)
 muon_apply_kernel(float* p, __nv_bfloat16* p_bf16, const __nv_bfloat16* o, long long n, float lr,
                   float wd) {
+  pdl_entry();
   const long long n4 = n >> 2;
   const float decay = 1.f - lr * wd;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n4;
@@ -185,7 +189,7 @@ extern "C" TYR_EXPORT int tyr_adamw_step(float* p, void* p_bf16, const void* g, 
   if (n <= 0) return -1;
   AdamArgs a{p, (__nv_bfloat16*)p_bf16, g, m, v, n, lr, beta1, beta2, eps, wd, bc1, bc2, grad_scale,
              g_is_bf16};
-  adamw_kernel<<<grid_1d(n / 4 + 1), 256, 0, (cudaStream_t)stream>>>(a);
+  launch_dependent(adamw_kernel, dim3(grid_1d(n / 4 + 1)), dim3(256), 0, (cudaStream_t)stream, a);
   return (int)cudaGetLastError();
 }
 
@@ -198,7 +202,7 @@ extern "C" TYR_EXPORT int tyr_muon_momentum(const void* g, float* mom, void* u, 
   int cap = (148 * 8 + B - 1) / B;
   if (cap < 1) cap = 1;
   if (gx > cap) gx = cap;
-  muon_momentum_kernel<<<dim3(gx, B), 256, 0, (cudaStream_t)stream>>>(a);
+  launch_dependent(muon_momentum_kernel, dim3(gx, B), dim3(256), 0, (cudaStream_t)stream, a);
   return (int)cudaGetLastError();
 }
 
@@ -209,7 +213,7 @@ extern "C" TYR_EXPORT int tyr_scale_by_inv_norm(void* x, const float* sumsq, lon
   int cap = (148 * 8 + B - 1) / B;
   if (cap < 1) cap = 1;
   if (gx > cap) gx = cap;
-  scale_by_inv_norm_kernel<<<dim3(gx, B), 256, 0, (cudaStream_t)stream>>>((__nv_bfloat16*)x, sumsq,
+  launch_dependent(scale_by_inv_norm_kernel, dim3(gx, B), dim3(256), 0, (cudaStream_t)stream, (__nv_bfloat16*)x, sumsq,
                                                                          per, eps);
   return (int)cudaGetLastError();
 }
@@ -217,7 +221,7 @@ extern "C" TYR_EXPORT int tyr_scale_by_inv_norm(void* x, const float* sumsq, lon
 extern "C" TYR_EXPORT int tyr_muon_apply(float* p, void* p_bf16, const void* o, long long n,
                                          float lr, float wd, void* stream) {
   if (n <= 0 || (n & 3)) return -1;
-  muon_apply_kernel<<<grid_1d(n / 4), 256, 0, (cudaStream_t)stream>>>(
+  launch_dependent(muon_apply_kernel, dim3(grid_1d(n / 4)), dim3(256), 0, (cudaStream_t)stream,
       p, (__nv_bfloat16*)p_bf16, (const __nv_bfloat16*)o, n, lr, wd);
   return (int)cudaGetLastError();
 }

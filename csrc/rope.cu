@@ -25,6 +25,7 @@ struct QkvPostArgs {
 
 // D == 128 fast path: lane l owns x1[2l..2l+1] and x2[2l..2l+1].
 __global__ void __launch_bounds__(256) qkv_post_fwd_kernel(QkvPostArgs a) {
+  pdl_entry();
   const int lane = threadIdx.x & 31;
   const long long unit0 = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const long long units = static_cast<long long>(a.rows) * 3 * a.H;
@@ -100,6 +101,7 @@ struct QkvPostBwdArgs {
 };
 
 __global__ void __launch_bounds__(256) qkv_post_bwd_kernel(QkvPostBwdArgs a) {
+  pdl_entry();
   const int lane = threadIdx.x & 31;
   const int wid = threadIdx.x >> 5;
   const long long unit0 = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + wid;
@@ -220,6 +222,7 @@ __device__ __forceinline__ float group8_sum(float v) {
 }
 
 __global__ void __launch_bounds__(256) qkv_post_fwd_d128_kernel(QkvPostArgs a) {
+  pdl_entry();
   const int lane = threadIdx.x & 31;
   const int sub = lane >> 3;          // head within the group of 4
   const int ch = (lane & 7) * 8;      // channel offset inside a 64-wide half
@@ -288,6 +291,7 @@ __global__ void __launch_bounds__(256) qkv_post_fwd_d128_kernel(QkvPostArgs a) {
 }
 
 __global__ void __launch_bounds__(256) qkv_post_bwd_d128_kernel(QkvPostBwdArgs a) {
+  pdl_entry();
   const int lane = threadIdx.x & 31;
   const int wid = threadIdx.x >> 5;
   const int sub = lane >> 3;
@@ -462,10 +466,10 @@ extern "C" TYR_EXPORT int tyr_qkv_post_fwd(const void* qkv, const void* ve, cons
                 (__nv_bfloat16*)out, rows, T, H, D, eps};
   if (D == 128) {
     const long long units = static_cast<long long>(rows) * ((3 * H + 3) / 4);
-    qkv_post_fwd_d128_kernel<<<grid_for_units(units, 8), 256, 0, (cudaStream_t)stream>>>(a);
+    launch_dependent(qkv_post_fwd_d128_kernel, dim3(grid_for_units(units, 8)), dim3(256), 0, (cudaStream_t)stream, a);
     return (int)cudaGetLastError();
   }
-  qkv_post_fwd_kernel<<<grid_for_units(3LL * rows * H, 8), 256, 0, (cudaStream_t)stream>>>(a);
+  launch_dependent(qkv_post_fwd_kernel, dim3(grid_for_units(3LL * rows * H, 8)), dim3(256), 0, (cudaStream_t)stream, a);
   return (int)cudaGetLastError();
 }
 
@@ -480,10 +484,10 @@ extern "C" TYR_EXPORT int tyr_qkv_post_bwd(const void* qkv, const void* ve, cons
                    rows, T, H, D, eps};
   if (D == 128) {
     const long long units = static_cast<long long>(rows) * ((3 * H + 3) / 4);
-    qkv_post_bwd_d128_kernel<<<grid_for_units(units, 8), 256, 0, (cudaStream_t)stream>>>(a);
+    launch_dependent(qkv_post_bwd_d128_kernel, dim3(grid_for_units(units, 8)), dim3(256), 0, (cudaStream_t)stream, a);
     return (int)cudaGetLastError();
   }
-  qkv_post_bwd_kernel<<<grid_for_units(3LL * rows * H, 8), 256, 0, (cudaStream_t)stream>>>(a);
+  launch_dependent(qkv_post_bwd_kernel, dim3(grid_for_units(3LL * rows * H, 8)), dim3(256), 0, (cudaStream_t)stream, a);
   return (int)cudaGetLastError();
 }
 

@@ -32,12 +32,29 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+constexpr long long kSkPrefetchBytes = 32LL << 20;   // L2 prefetch issued by one launch before its input is ready
+
 template <int TILES, bool GATED>                   // token tiles of 8: M <= 8 * TILES; GATED: two matrices, SwiGLU epilogue
 __global__ void __launch_bounds__(kSkWarps * 32) skinny_gemm_kernel(SkinnyArgs a) {
   __shared__ float part[GATED ? 2 : 1][kSkWarps][TILES][16][8];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
   const int row0 = blockIdx.x * 16;
+  // The weights are constants: while the kernel that produces `x` still runs (this one may already be resident, see
+  // launch_dependent), pull the head of every weight row of this CTA into the L2.  The whole grid asks for at most
+  // kSkPrefetchBytes, so what it brings in is still there when the loop below reads it.
+  pdl_trigger();
+  if (tid < (GATED ? 32 : 16) && (a.ldw & 7) == 0) {
+    const int r = row0 + (tid & 15);
+    const int chunks = a.K >> 5;
+    const int c0 = static_cast<int>(static_cast<long long>(chunks) * blockIdx.y / gridDim.y);
+    const int c1 = static_cast<int>(static_cast<long long>(chunks) * (blockIdx.y + 1) / gridDim.y);
+    long long per_row = kSkPrefetchBytes / (static_cast<long long>(gridDim.x) * gridDim.y * (GATED ? 32 : 16));
+    per_row = min(per_row & ~127LL, static_cast<long long>(c1 - c0) * 64);
+    if (r < a.N && per_row >= 128)
+      bulk_prefetch_l2((tid < 16 ? a.w : a.w2) + static_cast<long long>(r) * a.ldw + 32LL * c0, static_cast<uint32_t>(per_row));
+  }
+  pdl_wait();
   int r_lo = row0 + g, r_hi = row0 + g + 8;
   r_lo = r_lo < a.N ? r_lo : a.N - 1;            // clamped rows are not written
   r_hi = r_hi < a.N ? r_hi : a.N - 1;
@@ -121,6 +138,7 @@ __global__ void __launch_bounds__(kSkWarps * 32) skinny_gemm_kernel(SkinnyArgs a
 
 // Second pass of a split reduction: round the fp32 sums (+ bias) and leave the workspace zeroed for the next call.
 __global__ void __launch_bounds__(256) skinny_finish_kernel(SkinnyArgs a) {
+  pdl_entry();
   const long long n = static_cast<long long>(a.M) * a.N;
   for (long long i = blockIdx.x * 256LL + threadIdx.x; i < n; i += static_cast<long long>(gridDim.x) * 256) {
     const int tok = static_cast<int>(i / a.N), row = static_cast<int>(i - static_cast<long long>(tok) * a.N);
@@ -153,13 +171,13 @@ extern "C" TYR_EXPORT int tyr_skinny_gemm_bf16(const void* x, const void* w, con
   SkinnyArgs a{(const __nv_bfloat16*)x, (const __nv_bfloat16*)w, nullptr, (const __nv_bfloat16*)bias, (__nv_bfloat16*)y, (float*)ws, ldx, ldw, ldy, M, N, K};
   const int splits = ws != nullptr ? tyr_skinny_gemm_splits(N, K) : 1;
   const dim3 grid((N + 15) / 16, splits);
-  if (M <= 8) skinny_gemm_kernel<1, false><<<grid, kSkWarps * 32, 0, (cudaStream_t)stream>>>(a);
-  else if (M <= 16) skinny_gemm_kernel<2, false><<<grid, kSkWarps * 32, 0, (cudaStream_t)stream>>>(a);
-  else skinny_gemm_kernel<4, false><<<grid, kSkWarps * 32, 0, (cudaStream_t)stream>>>(a);
+  if (M <= 8) launch_dependent(skinny_gemm_kernel<1, false>, dim3(grid), dim3(kSkWarps * 32), 0, (cudaStream_t)stream, a);
+  else if (M <= 16) launch_dependent(skinny_gemm_kernel<2, false>, dim3(grid), dim3(kSkWarps * 32), 0, (cudaStream_t)stream, a);
+  else launch_dependent(skinny_gemm_kernel<4, false>, dim3(grid), dim3(kSkWarps * 32), 0, (cudaStream_t)stream, a);
   if (splits > 1) {
     long long blocks = (static_cast<long long>(M) * N + 255) / 256;
     if (blocks > 592) blocks = 592;
-    skinny_finish_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>(a);
+    launch_dependent(skinny_finish_kernel, dim3((int)blocks), dim3(256), 0, (cudaStream_t)stream, a);
   }
   return (int)cudaGetLastError();
 }
@@ -174,8 +192,8 @@ extern "C" TYR_EXPORT int tyr_skinny_swiglu_bf16(const void* x, const void* wg, 
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(wg) | reinterpret_cast<uintptr_t>(wu)) & 15) return -3;
   SkinnyArgs a{(const __nv_bfloat16*)x, (const __nv_bfloat16*)wg, (const __nv_bfloat16*)wu, nullptr, (__nv_bfloat16*)y, nullptr, ldx, ldw, ldy, M, N, K};
   const dim3 grid((N + 15) / 16, 1);
-  if (M <= 8) skinny_gemm_kernel<1, true><<<grid, kSkWarps * 32, 0, (cudaStream_t)stream>>>(a);
-  else if (M <= 16) skinny_gemm_kernel<2, true><<<grid, kSkWarps * 32, 0, (cudaStream_t)stream>>>(a);
-  else skinny_gemm_kernel<4, true><<<grid, kSkWarps * 32, 0, (cudaStream_t)stream>>>(a);
+  if (M <= 8) launch_dependent(skinny_gemm_kernel<1, true>, dim3(grid), dim3(kSkWarps * 32), 0, (cudaStream_t)stream, a);
+  else if (M <= 16) launch_dependent(skinny_gemm_kernel<2, true>, dim3(grid), dim3(kSkWarps * 32), 0, (cudaStream_t)stream, a);
+  else launch_dependent(skinny_gemm_kernel<4, true>, dim3(grid), dim3(kSkWarps * 32), 0, (cudaStream_t)stream, a);
   return (int)cudaGetLastError();
 }
