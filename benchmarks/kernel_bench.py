@@ -171,6 +171,24 @@ def bench_gdr(results, small=False):
         print(f"gated delta rule prefill B{B} S{S} 16/48 heads x 128: ours {ours:7.3f} ms" + (f" | library ops {row['library_ms']:7.3f} ms" if "library_ms" in row else ""), flush=True)
 
 
+def bench_gdr_decode(results, small=False):
+    """Gated delta rule, one token per row (decode): bound by one read and one write of the fp32 state
+    [B, value heads, 128, 128]; reports the fraction of the measured copy bandwidth."""
+    from tyr_b200.ops import delta_rule as DR
+    dev = torch.device("cuda")
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    peak = 6538.0                      # measured copy bandwidth of this pool, GB/s
+    for B, Hk, Hv in (((32, 8, 24),) if small else ((32, 8, 24), (32, 16, 48), (8, 16, 48), (64, 16, 48))):
+        q, k, v, gl, beta = _gdr_inputs(B, 1, Hk, Hv, 128, dev)
+        state = torch.randn(B, Hv, 128, 128, device=dev) * 0.1
+        gl, beta = gl.float().contiguous(), beta.float().contiguous()
+        fn = lambda: DR.gdr_decode_step(q, k, v, gl, beta, state)
+        ms = _time(fn, iters=3 if small else 20, warmup=2 if small else 5, flush=flush)
+        gbs = 2.0 * state.numel() * 4 / ms / 1e6
+        results.append({"kernel": "gdr_decode", "B": B, "Hv": Hv, "ms": ms, "gbs": gbs, "of_measured_copy": gbs / peak})
+        print(f"gated delta rule decode B{B} {Hk}/{Hv} heads x 128: {ms * 1e3:7.1f} us  {gbs:7.0f} GB/s  ({gbs / peak:.2f} of measured copy)", flush=True)
+
+
 def bench_moe(results, cases=None):
     """Fused NVFP4 MoE op at Laguna-S-2.1 shapes (hidden 3072, 256 experts, top-10, FFN 1024): effective
     FP4 weight-read bandwidth for decode-sized batches (the reference's bar is >= 150 GB/s at one token,
@@ -403,6 +421,10 @@ def main(argv):
         bench_attention_bwd(results)
     if what in ("gdr", "all"):
         bench_gdr(results)
+    if what in ("gdr-decode", "all"):
+        bench_gdr_decode(results)
+    if what == "gdr-decode-small":
+        bench_gdr_decode(results, small=True)
     if what == "gdr-small":
         bench_gdr(results, small=True)
     if what == "attention-fwd-small":

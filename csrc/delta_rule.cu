@@ -14,28 +14,33 @@
 namespace tyr {
 
 template <int DK>
-__global__ void __launch_bounds__(512)
+__global__ void __launch_bounds__(512, 2)      // 64 registers: two CTAs per SM (at 128 registers one CTA kept a quarter of the warps busy)
 gdr_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
                   const __nv_bfloat16* __restrict__ v, const float* __restrict__ g,
                   const float* __restrict__ beta, float* __restrict__ state, __nv_bfloat16* __restrict__ out,
                   int Hk, int Hv, int dv, long long q_bstride, long long v_bstride,
                   const __nv_bfloat16* __restrict__ z, long long z_bstride, const __nv_bfloat16* __restrict__ norm_w,
                   float norm_eps) {
-  pdl_entry();
   // z != nullptr (dv == 128, one column pass): the layer's gated RMSNorm runs in the epilogue,
   //   out = rmsnorm_over_dv(o) * norm_w * silu(z),
   // with o rounded to bf16 first, as the separate kernels see it.
-  // 128 state columns x 4 row groups per CTA: a thread keeps DK / 4 values of one column in registers; the two column
-  // reductions (S^T k and S^T q) are finished across the row groups through shared memory.
-  constexpr int RPT = DK / 4;
+  // 128 state columns per pass.  A warp is one group of DK / 16 state rows; a lane owns four adjacent columns, so a warp's
+  // access to a state row is one contiguous 512-byte line of 16-byte vectors.  The two column reductions (S^T k and S^T q) are
+  // finished across the sixteen row groups through shared memory.
+  constexpr int RPT = DK / 16;
   __shared__ float sq[DK], sk[DK];
   __shared__ float red[2][16];
-  __shared__ float part[4][128];
+  __shared__ __align__(16) float part[16][128];
   const int bh = blockIdx.x;
   const int b = bh / Hv, hv = bh % Hv;
   const int hk = hv / (Hv / Hk);
   const int tid = threadIdx.x;
-  const int cl = tid & 127, rg = tid >> 7;
+  const int quad = tid & 31, rg = tid >> 5;
+  float* S = state + static_cast<long long>(bh) * DK * dv;
+  // The state was last written one decode step ago: ask the L2 for it while the kernel in front of this one still runs.
+  pdl_trigger();
+  if (dv == 128 && tid < 16) bulk_prefetch_l2(S + tid * (DK * 8), DK * 8 * 4);
+  pdl_wait();
   const __nv_bfloat16* qp = q + b * q_bstride + static_cast<long long>(hk) * DK;
   const __nv_bfloat16* kp = k + b * q_bstride + static_cast<long long>(hk) * DK;
   float qs = 0.f, ks = 0.f;
@@ -54,50 +59,95 @@ gdr_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __re
   const float kn = rsqrtf(ks + 1e-6f);
   const float decay = __expf(g[bh]);
   const float bt = beta[bh];
-  float* S = state + static_cast<long long>(bh) * DK * dv;
   const int r0 = rg * RPT;
+  const bool vec_ok = (dv & 3) == 0;               // 16-byte state accesses need dv to be a multiple of 4
   for (int col0 = blockIdx.y * 128; col0 < dv; col0 += gridDim.y * 128) {
-    const int col = col0 + cl;
-    const bool live = col < dv;
-    float s[RPT];
-    float kv = 0.f;
+    const int col = col0 + 4 * quad;
+    float s[RPT][4];
+    float kv[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int r = 0; r < RPT; ++r) {
-      s[r] = live ? S[static_cast<long long>(r0 + r) * dv + col] * decay : 0.f;
-      kv += s[r] * sk[r0 + r];
+      float* row = S + static_cast<long long>(r0 + r) * dv + col;
+      if (vec_ok && col + 3 < dv) {
+        const float4 t = *reinterpret_cast<const float4*>(row);
+        s[r][0] = t.x; s[r][1] = t.y; s[r][2] = t.z; s[r][3] = t.w;
+      } else {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) s[r][c] = col + c < dv ? row[c] : 0.f;
+      }
+      const float kk = sk[r0 + r];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        s[r][c] *= decay;
+        kv[c] += s[r][c] * kk;
+      }
     }
-    part[rg][cl] = kv;
+    *reinterpret_cast<float4*>(&part[rg][4 * quad]) = make_float4(kv[0], kv[1], kv[2], kv[3]);
     __syncthreads();
-    kv = (part[0][cl] + part[1][cl] + part[2][cl] + part[3][cl]) * kn;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) kv[c] = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const float4 t = *reinterpret_cast<const float4*>(&part[i][4 * quad]);
+      kv[0] += t.x; kv[1] += t.y; kv[2] += t.z; kv[3] += t.w;
+    }
     __syncthreads();
-    const float vt = live ? __bfloat162float(v[b * v_bstride + static_cast<long long>(hv) * dv + col]) : 0.f;
-    const float delta = (vt - kv) * bt * kn;       // k enters normalised: k_hat = kn * k
-    float o = 0.f;
+    float delta[4], o[4] = {0.f, 0.f, 0.f, 0.f};
+    const __nv_bfloat16* vp = v + b * v_bstride + static_cast<long long>(hv) * dv;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const float vt = col + c < dv ? __bfloat162float(vp[col + c]) : 0.f;
+      delta[c] = (vt - kv[c] * kn) * bt * kn;       // k enters normalised: k_hat = kn * k
+    }
 #pragma unroll
     for (int r = 0; r < RPT; ++r) {
-      s[r] += sk[r0 + r] * delta;
-      o += s[r] * sq[r0 + r];
-      if (live) S[static_cast<long long>(r0 + r) * dv + col] = s[r];
-    }
-    part[rg][cl] = o;
-    __syncthreads();
-    if (z == nullptr) {
-      if (rg == 0 && live)
-        out[(static_cast<long long>(bh)) * dv + col] = __float2bfloat16((part[0][cl] + part[1][cl] + part[2][cl] + part[3][cl]) * qn);
-    } else {
-      float ov = 0.f;
-      if (rg == 0 && live) ov = __bfloat162float(__float2bfloat16((part[0][cl] + part[1][cl] + part[2][cl] + part[3][cl]) * qn));
-      float sq2 = warp_sum(ov * ov);                      // row groups 1..3 contribute zeros
-      if ((tid & 31) == 0) red[0][tid >> 5] = sq2;
-      __syncthreads();
-      if (rg == 0 && live) {
-        float tot = 0.f;
+      const float kk = sk[r0 + r], qq = sq[r0 + r];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) tot += red[0][i];
-        const float rstd = rsqrtf(tot / static_cast<float>(dv) + norm_eps);
-        const float zz = __bfloat162float(z[b * z_bstride + static_cast<long long>(hv) * dv + col]);
-        const float y = ov * rstd * __bfloat162float(norm_w[col]);
-        out[(static_cast<long long>(bh)) * dv + col] = __float2bfloat16(y * (zz / (1.f + __expf(-zz))));
+      for (int c = 0; c < 4; ++c) {
+        s[r][c] += kk * delta[c];
+        o[c] += s[r][c] * qq;
+      }
+      float* row = S + static_cast<long long>(r0 + r) * dv + col;
+      if (vec_ok && col + 3 < dv) {
+        *reinterpret_cast<float4*>(row) = make_float4(s[r][0], s[r][1], s[r][2], s[r][3]);
+      } else {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+          if (col + c < dv) row[c] = s[r][c];
+      }
+    }
+    *reinterpret_cast<float4*>(&part[rg][4 * quad]) = make_float4(o[0], o[1], o[2], o[3]);
+    __syncthreads();
+    if (rg == 0) {                                   // one warp finishes the 128 outputs of this pass, four per lane
+#pragma unroll
+      for (int c = 0; c < 4; ++c) o[c] = 0.f;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const float4 t = *reinterpret_cast<const float4*>(&part[i][4 * quad]);
+        o[0] += t.x; o[1] += t.y; o[2] += t.z; o[3] += t.w;
+      }
+      __nv_bfloat16* op = out + static_cast<long long>(bh) * dv;
+      if (z == nullptr) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+          if (col + c < dv) op[col + c] = __float2bfloat16(o[c] * qn);
+      } else {
+        float ssq = 0.f;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          o[c] = col + c < dv ? __bfloat162float(__float2bfloat16(o[c] * qn)) : 0.f;
+          ssq += o[c] * o[c];
+        }
+        ssq = warp_sum(ssq);
+        const float rstd = rsqrtf(ssq / static_cast<float>(dv) + norm_eps);
+        const __nv_bfloat16* zp = z + b * z_bstride + static_cast<long long>(hv) * dv;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          if (col + c >= dv) continue;
+          const float zz = __bfloat162float(zp[col + c]);
+          const float y = o[c] * rstd * __bfloat162float(norm_w[col + c]);
+          op[col + c] = __float2bfloat16(y * (zz / (1.f + __expf(-zz))));
+        }
       }
     }
     __syncthreads();

@@ -57,6 +57,7 @@ struct Fp4Params {
   const float* w_global;       // [groups]: result is divided by it
   const float* w_global2;      // mode 1: the global of the `up` bank (w_global is the gate bank's)
   int mode;
+  int all_active;              // fixed-slot layout: the caller expects every expert to have rows (enables the weight prefetch)
   void* out;                   // mode 0: bf16 [padded rows, N]; mode 1: packed e2m1 [padded rows, N / 4] bytes
   uint8_t* out_sf;             // mode 1: scales of `out` in tensor-core order for a reduction length of N / 2
   int* err;
@@ -305,7 +306,25 @@ fp4_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, Fp4Params p) {
     tmem_alloc(&s.tmem_base, 512);
     tmem_relinquish();
   }
-  if (warp == 0 && lane == 0) tma_prefetch_desc(&tmA);
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmA);
+    if (p.all_active && p.group_tiles == nullptr) {
+      // Which tiles this CTA gets depends on the row counts, which the kernel in front of this one is still writing.  When
+      // (nearly) every expert has rows, tile t belongs to expert t / tiles_n: ask the L2 for the weights of the first tiles
+      // under that assumption.  A wrong guess costs bandwidth, never correctness.
+      const long long tiles_g = static_cast<long long>(p.groups) * tiles_n;
+      const long long rounds_g = (tiles_g + gridDim.x - 1) / gridDim.x;
+      const long long stride_g = (tiles_g + rounds_g - 1) / rounds_g;
+      const int n_pref = num_ks >= 8 ? 1 : 8 / num_ks;
+      if (blockIdx.x < stride_g)
+        for (int i = 0; i < n_pref; ++i) {
+          const long long t = blockIdx.x + i * stride_g;
+          if (t >= tiles_g) break;
+          bulk_prefetch_l2(p.w_tiled + t * num_ks * (F4_BN * F4_BKB), static_cast<uint32_t>(num_ks) * (F4_BN * F4_BKB));
+          bulk_prefetch_l2(p.sfb + t * ktiles * 512, static_cast<uint32_t>(ktiles) * 512);
+        }
+    }
+  }
   pdl_wait();
   if (p.group_tiles != nullptr) {
     for (int i = threadIdx.x; i <= p.groups; i += blockDim.x) {
@@ -598,6 +617,7 @@ struct TyrFp4GemmArgs {
   void* out_sf;
   int padded_rows, N, K, groups, mode;
   int sm_count;
+  int all_active;            // fixed-slot layout only: 1 = the caller expects every group to have rows (weight prefetch hint)
   int* err;
   void* stream;
 };
@@ -633,7 +653,7 @@ TYR_EXPORT int tyr_fp4_grouped_gemm(const TyrFp4GemmArgs* a) {
   p.sfa = reinterpret_cast<const uint8_t*>(a->a_sf); p.sfb = reinterpret_cast<const uint8_t*>(a->w_sf);
   p.w_tiled = reinterpret_cast<const uint8_t*>(a->w_packed);
   p.a_row_scale = a->a_row_scale; p.w_global = a->w_global; p.w_global2 = a->w_global2;
-  p.mode = a->mode; p.out = a->out; p.out_sf = reinterpret_cast<uint8_t*>(a->out_sf); p.err = a->err;
+  p.mode = a->mode; p.all_active = a->all_active; p.out = a->out; p.out_sf = reinterpret_cast<uint8_t*>(a->out_sf); p.err = a->err;
   int grid = a->sm_count > 0 ? a->sm_count : sms[dev];
   const long long max_tiles = static_cast<long long>(a->padded_rows / 128) * (a->N / 128);
   if (max_tiles < grid) grid = static_cast<int>(max_tiles);

@@ -31,7 +31,8 @@ class _GemmArgs(ctypes.Structure):
                 ("w_global2", ctypes.c_void_p), ("group_tiles", ctypes.c_void_p), ("group_rows", ctypes.c_void_p),
                 ("out", ctypes.c_void_p), ("out_sf", ctypes.c_void_p),
                 ("padded_rows", ctypes.c_int), ("N", ctypes.c_int), ("K", ctypes.c_int), ("groups", ctypes.c_int),
-                ("mode", ctypes.c_int), ("sm_count", ctypes.c_int), ("err", ctypes.c_void_p), ("stream", ctypes.c_void_p)]
+                ("mode", ctypes.c_int), ("sm_count", ctypes.c_int), ("all_active", ctypes.c_int),
+                ("err", ctypes.c_void_p), ("stream", ctypes.c_void_p)]
 
 
 @register_signatures
@@ -199,7 +200,7 @@ def gather_quantize(x: torch.Tensor, order: Optional[torch.Tensor], ids: Optiona
 
 
 def grouped_gemm_fp4(a_packed, a_sf, a_row_scale, w_packed, w_sf, w_global, tiles, rows, N: int, K: int, *, mode: int = 0,
-                     w_global2=None, sm_count: int = 0):
+                     w_global2=None, sm_count: int = 0, all_active: bool = False):
     """``w_packed``: the weights as ``tile_weights`` images.  mode 0 -> bf16 [padded_rows, N]; mode 1 -> (packed
     [padded_rows, N/4] u8, scales flat u8) of silu(gate) * up."""
     padded = a_packed.shape[0]
@@ -218,6 +219,7 @@ def grouped_gemm_fp4(a_packed, a_sf, a_row_scale, w_packed, w_sf, w_global, tile
     a.group_tiles, a.group_rows = (tiles.data_ptr() if tiles is not None else None), rows.data_ptr()
     a.out, a.out_sf = out.data_ptr(), (out_sf.data_ptr() if out_sf is not None else None)
     a.padded_rows, a.N, a.K, a.groups, a.mode, a.sm_count = padded, N, K, groups, mode, sm_count
+    a.all_active = 1 if (all_active and tiles is None) else 0
     a.err = err_word(dev).data_ptr()
     a.stream = cur_stream(dev)
     check(lib().tyr_fp4_grouped_gemm(ctypes.byref(a)), "fp4_grouped_gemm")
@@ -280,9 +282,12 @@ def moe_fp4_tc_forward_fixed(x: torch.Tensor, ids: torch.Tensor, weights: torch.
     ppos = torch.empty(T * k, dtype=torch.int32, device=dev)
     check(lib().tyr_fp4_scatter_quantize_fixed(ptr(x.contiguous()), ptr(ids32), ptr(cursors), ptr(xq), ptr(xsf), ptr(xrs), ptr(ppos),
                                                T, k, h, E, ptr(err_word(dev)), st), "fp4_scatter_quantize_fixed")
+    # with six or more pairs per expert on average an expert without rows is rare (e^-6 under uniform routing): the GEMMs
+    # may then fetch the weights of their first tiles before the row counts exist
+    dense = T * k >= 6 * E
     hq, hsf = grouped_gemm_fp4(xq, xsf, xrs, w4.gu_packed, w4.gu_sf, w4.gate_global, None, cursors,
-                               2 * mi, h, mode=1, w_global2=w4.up_global)
-    y = grouped_gemm_fp4(hq, hsf, None, w4.dn_packed, w4.dn_sf, w4.dn_global, None, cursors, h, mi, mode=0)
+                               2 * mi, h, mode=1, w_global2=w4.up_global, all_active=dense)
+    y = grouped_gemm_fp4(hq, hsf, None, w4.dn_packed, w4.dn_sf, w4.dn_global, None, cursors, h, mi, mode=0, all_active=dense)
     out = torch.empty_like(x)
     check(lib().tyr_moe_combine(ptr(y), ptr(ppos), ptr(weights.float().contiguous()), ptr(add.contiguous() if add is not None else None),
                                 ptr(out), T, k, h, st), "moe_combine")
