@@ -154,6 +154,158 @@ gdr_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __re
   }
 }
 
+// The same step for dv == 128 with the state tile staged in shared memory.  The [DK, 128] fp32 state of one (batch, value
+// head) is one contiguous block: a bulk copy brings it into shared memory while the threads normalise q and k, the two
+// passes (S^T k, then update + S^T q) run on shared memory, and one bulk copy writes the tile back.  No thread keeps state
+// in registers, so three CTAs (192 KB of tiles) fit an SM and their load / compute / store phases overlap.
+__device__ __forceinline__ void gdr_bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)),
+               "l"(src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void gdr_bulk_store(void* dst, const void* src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(smem_u32(src)), "r"(bytes)
+               : "memory");
+}
+
+template <int DK>
+__global__ void __launch_bounds__(256)
+gdr_decode_tile_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
+                       const __nv_bfloat16* __restrict__ v, const float* __restrict__ g,
+                       const float* __restrict__ beta, float* __restrict__ state, __nv_bfloat16* __restrict__ out,
+                       int Hk, int Hv, long long q_bstride, long long v_bstride,
+                       const __nv_bfloat16* __restrict__ z, long long z_bstride, const __nv_bfloat16* __restrict__ norm_w,
+                       float norm_eps, int* err) {
+  constexpr int DV = 128, RG = 8, RPT = DK / RG;
+  constexpr uint32_t kBytes = DK * DV * 4, kPiece = kBytes / 4;
+  extern __shared__ __align__(128) uint8_t gdr_smem[];
+  float* tile = reinterpret_cast<float*>(gdr_smem);                      // [DK][128]
+  __shared__ float sq[DK], sk[DK];
+  __shared__ float red[2][RG];
+  __shared__ __align__(16) float part[RG][DV];
+  __shared__ __align__(8) uint64_t bar;
+  const int bh = blockIdx.x;
+  const int b = bh / Hv, hv = bh % Hv;
+  const int hk = hv / (Hv / Hk);
+  const int tid = threadIdx.x;
+  const int quad = tid & 31, rg = tid >> 5;
+  uint8_t* S = reinterpret_cast<uint8_t*>(state + static_cast<long long>(bh) * DK * DV);
+  pdl_trigger();
+  if (tid == 0) {
+    mbar_init(&bar, 1);
+    mbar_fence_init();
+  }
+  if (tid < 4) bulk_prefetch_l2(S + tid * kPiece, kPiece);   // the state was last written a whole decode step ago
+  pdl_wait();
+  if (tid == 0) {
+    mbar_expect_tx(&bar, kBytes);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) gdr_bulk_load(gdr_smem + i * kPiece, S + i * kPiece, kPiece, &bar);
+  }
+  const __nv_bfloat16* qp = q + b * q_bstride + static_cast<long long>(hk) * DK;
+  const __nv_bfloat16* kp = k + b * q_bstride + static_cast<long long>(hk) * DK;
+  float qs = 0.f, ks = 0.f;
+  if (tid < DK) {
+    const float a = __bfloat162float(qp[tid]), c = __bfloat162float(kp[tid]);
+    sq[tid] = a; sk[tid] = c;
+    qs = a * a; ks = c * c;
+  }
+  qs = warp_sum(qs); ks = warp_sum(ks);
+  if (quad == 0) { red[0][rg] = qs; red[1][rg] = ks; }
+  __syncthreads();                                   // also orders the barrier's init before every thread's wait
+  qs = 0.f; ks = 0.f;
+#pragma unroll
+  for (int i = 0; i < RG; ++i) { qs += red[0][i]; ks += red[1][i]; }
+  const float qn = rsqrtf(qs + 1e-6f) * rsqrtf(static_cast<float>(DK));
+  const float kn = rsqrtf(ks + 1e-6f);
+  const float decay = __expf(g[bh]);
+  const float bt = beta[bh];
+  const int col = 4 * quad;
+  const __nv_bfloat16* vp = v + b * v_bstride + static_cast<long long>(hv) * DV;
+  float vt[4];
+  {
+    const uint2 u = *reinterpret_cast<const uint2*>(vp + col);
+    const float2 a = unpack_bf16x2(u.x), c = unpack_bf16x2(u.y);
+    vt[0] = a.x; vt[1] = a.y; vt[2] = c.x; vt[3] = c.y;
+  }
+  if (!mbar_wait(&bar, 0, err, 1600)) {
+    mbar_wait(&bar, 0, nullptr, 0);                  // the copy still targets this CTA's shared memory: do not leave before it lands
+    return;
+  }
+  float4* trow = reinterpret_cast<float4*>(tile) + static_cast<long long>(rg * RPT) * (DV / 4) + quad;
+  float kv[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int r = 0; r < RPT; ++r) {
+    const float4 t = trow[r * (DV / 4)];
+    const float kk = sk[rg * RPT + r];
+    kv[0] += t.x * kk; kv[1] += t.y * kk; kv[2] += t.z * kk; kv[3] += t.w * kk;
+  }
+  *reinterpret_cast<float4*>(&part[rg][col]) = make_float4(kv[0], kv[1], kv[2], kv[3]);
+  __syncthreads();
+#pragma unroll
+  for (int c = 0; c < 4; ++c) kv[c] = 0.f;
+#pragma unroll
+  for (int i = 0; i < RG; ++i) {
+    const float4 t = *reinterpret_cast<const float4*>(&part[i][col]);
+    kv[0] += t.x; kv[1] += t.y; kv[2] += t.z; kv[3] += t.w;
+  }
+  __syncthreads();
+  float delta[4], o[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int c = 0; c < 4; ++c) delta[c] = (vt[c] - kv[c] * decay * kn) * bt * kn;     // k enters normalised: k_hat = kn * k
+#pragma unroll
+  for (int r = 0; r < RPT; ++r) {
+    float4 t = trow[r * (DV / 4)];
+    const float kk = sk[rg * RPT + r], qq = sq[rg * RPT + r];
+    t.x = t.x * decay + kk * delta[0]; t.y = t.y * decay + kk * delta[1];
+    t.z = t.z * decay + kk * delta[2]; t.w = t.w * decay + kk * delta[3];
+    o[0] += t.x * qq; o[1] += t.y * qq; o[2] += t.z * qq; o[3] += t.w * qq;
+    trow[r * (DV / 4)] = t;
+  }
+  *reinterpret_cast<float4*>(&part[rg][col]) = make_float4(o[0], o[1], o[2], o[3]);
+  fence_proxy_async();                               // the tile's new values must be visible to the bulk copy engine
+  __syncthreads();
+  if (tid == 0) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) gdr_bulk_store(S + i * kPiece, gdr_smem + i * kPiece, kPiece);
+    tma_store_commit();
+  }
+  if (rg == 0) {                                     // one warp finishes the 128 outputs, four per lane
+#pragma unroll
+    for (int c = 0; c < 4; ++c) o[c] = 0.f;
+#pragma unroll
+    for (int i = 0; i < RG; ++i) {
+      const float4 t = *reinterpret_cast<const float4*>(&part[i][col]);
+      o[0] += t.x; o[1] += t.y; o[2] += t.z; o[3] += t.w;
+    }
+    __nv_bfloat16* op = out + static_cast<long long>(bh) * DV + col;
+    if (z != nullptr) {
+      float ssq = 0.f;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        o[c] = __bfloat162float(__float2bfloat16(o[c] * qn));
+        ssq += o[c] * o[c];
+      }
+      ssq = warp_sum(ssq);
+      const float rstd = rsqrtf(ssq / static_cast<float>(DV) + norm_eps);
+      const __nv_bfloat16* zp = z + b * z_bstride + static_cast<long long>(hv) * DV + col;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const float zz = __bfloat162float(zp[c]);
+        o[c] = o[c] * rstd * __bfloat162float(norm_w[col + c]) * (zz / (1.f + __expf(-zz)));
+      }
+    } else {
+#pragma unroll
+      for (int c = 0; c < 4; ++c) o[c] *= qn;
+    }
+    uint2 u;
+    u.x = pack_bf16x2(o[0], o[1]);
+    u.y = pack_bf16x2(o[2], o[3]);
+    *reinterpret_cast<uint2*>(op) = u;
+  }
+  if (tid == 0) tma_store_wait_read<0>();            // shared memory must outlive the copy engine's reads
+}
+
 // Everything in front of the recurrent step for one new token per row: the causal depthwise conv (window of K taps kept as
 // the layer's conv state, shifted in place: a channel belongs to exactly one thread) with bias and SiLU, and the per-head
 // gates beta = sigmoid(b), g = -softplus(a + dt_bias) * exp(a_log).  `mixed` / `b_in` / `a_in` are rows of projection outputs
@@ -803,6 +955,46 @@ extern "C" TYR_EXPORT int tyr_gdr_decode(const void* q, const void* k, const voi
                                          long long q_bstride, long long v_bstride, void* stream) {
   return tyr_gdr_decode_norm(q, k, v, g, beta, state, out, B, Hk, Hv, dk, dv, q_bstride, v_bstride, nullptr, 0, nullptr, 0.f,
                              stream);
+}
+
+// dv == 128, dk 64 or 128, v / z rows 8-byte aligned (strides multiples of 4 elements): the shared-memory tile form of the
+// step (gdr_decode_tile_kernel); `z` / `norm_w` may be null (no gated RMSNorm).  `err`: the device error record.
+extern "C" TYR_EXPORT int tyr_gdr_decode_tile(const void* q, const void* k, const void* v, const float* g, const float* beta,
+                                              float* state, void* out, int B, int Hk, int Hv, int dk,
+                                              long long q_bstride, long long v_bstride, const void* z, long long z_bstride,
+                                              const void* norm_w, float norm_eps, int* err, void* stream) {
+  using namespace tyr;
+  if (B <= 0 || Hk <= 0 || Hv <= 0 || Hv % Hk != 0 || (dk != 64 && dk != 128)) return -1;
+  if (z != nullptr && norm_w == nullptr) return -3;
+  if ((v_bstride & 3) || (z != nullptr && (z_bstride & 3))) return -4;
+  if ((reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(z) | reinterpret_cast<uintptr_t>(out)) & 7) return -4;
+  if (reinterpret_cast<uintptr_t>(state) & 15) return -4;
+  const size_t smem = static_cast<size_t>(dk) * 128 * 4;
+  static bool configured[64][2] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+  const int which = dk == 128 ? 1 : 0;
+  if (!configured[dev][which]) {
+    cudaError_t e = dk == 128 ? cudaFuncSetAttribute(gdr_decode_tile_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+                              : cudaFuncSetAttribute(gdr_decode_tile_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return 1000 + static_cast<int>(e);
+    configured[dev][which] = true;
+  }
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  auto* qq = reinterpret_cast<const __nv_bfloat16*>(q);
+  auto* kk = reinterpret_cast<const __nv_bfloat16*>(k);
+  auto* vv = reinterpret_cast<const __nv_bfloat16*>(v);
+  auto* zz = reinterpret_cast<const __nv_bfloat16*>(z);
+  auto* nw = reinterpret_cast<const __nv_bfloat16*>(norm_w);
+  auto* oo = reinterpret_cast<__nv_bfloat16*>(out);
+  cudaError_t e;
+  if (dk == 128)
+    e = launch_dependent(gdr_decode_tile_kernel<128>, dim3(B * Hv), dim3(256), smem, st, qq, kk, vv, g, beta, state, oo, Hk, Hv,
+                         q_bstride, v_bstride, zz, z_bstride, nw, norm_eps, err);
+  else
+    e = launch_dependent(gdr_decode_tile_kernel<64>, dim3(B * Hv), dim3(256), smem, st, qq, kk, vv, g, beta, state, oo, Hk, Hv,
+                         q_bstride, v_bstride, zz, z_bstride, nw, norm_eps, err);
+  return static_cast<int>(e);
 }
 
 // The same step with the layer's gated RMSNorm in the epilogue when `z` (bf16 [B, Hv, dv], batch stride z_bstride) and

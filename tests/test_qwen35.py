@@ -89,11 +89,14 @@ def test_loader_roundtrip(tmp_path):
 
 
 @pytest.mark.gpu
-def test_gpu_gdr_decode_kernel_matches_recurrence():
-    q, k, v, g, beta = _gdr_inputs(B=3, S=6, H=8, dk=128, dv=128, device="cuda", dtype=torch.bfloat16)
+@pytest.mark.parametrize("tile,dk", [(True, 128), (False, 128), (True, 64), (False, 64)])
+def test_gpu_gdr_decode_kernel_matches_recurrence(tile, dk, monkeypatch):
+    """Both forms of the decode step (state tile staged in shared memory by bulk copies; state columns held in registers)."""
+    monkeypatch.setattr(D, "_GDR_TILE", tile)
+    q, k, v, g, beta = _gdr_inputs(B=3, S=6, H=8, dk=dk, dv=128, device="cuda", dtype=torch.bfloat16)
     qk, kk = q[:, :, :4].contiguous(), k[:, :, :4].contiguous()
     ref, sref = D.recurrent_gated_delta_rule(qk.float().repeat_interleave(2, 2), kk.float().repeat_interleave(2, 2), v.float(), g, beta)
-    state = torch.zeros(3, 8, 128, 128, device="cuda")
+    state = torch.zeros(3, 8, dk, 128, device="cuda")
     outs = []
     for i in range(6):
         outs.append(D.gdr_decode_step(qk[:, i:i + 1].contiguous(), kk[:, i:i + 1].contiguous(), v[:, i:i + 1].contiguous(),
@@ -104,12 +107,14 @@ def test_gpu_gdr_decode_kernel_matches_recurrence():
 
 
 @pytest.mark.gpu
-def test_gpu_gdn_decode_fused_matches_library_op_sequence():
+@pytest.mark.parametrize("tile", [True, False])
+def test_gpu_gdn_decode_fused_matches_library_op_sequence(tile, monkeypatch):
     """Conv + gates kernel and the recurrent kernel with the gated-norm epilogue against the op-by-op decode branch, on column
     windows of one projection output, over several tokens (conv window and recurrent state carried in place)."""
     cfg = tiny(0, hidden_size=256, intermediate_size=512, head_dim=128, half_rotary_dim=32, linear_key_head_dim=128, linear_value_head_dim=128,
                num_attention_heads=4, num_key_value_heads=1)
     m = Q.init(cfg, device="cuda", dtype=torch.bfloat16)
+    monkeypatch.setattr(D, "_GDR_TILE", tile)
     layer = next(l for i, l in enumerate(m.layers) if not cfg.is_full(i))
     mix = layer.mixer
     mix.conv1d_bias = (torch.randn(cfg.linear_conv_dim, device="cuda") * 0.1).bfloat16()
@@ -122,7 +127,8 @@ def test_gpu_gdn_decode_fused_matches_library_op_sequence():
                              torch.randn(B, Hv, cfg.linear_key_head_dim, cfg.linear_value_head_dim, device="cuda", generator=gs) * 0.1)
     s_ref, s_fused = fresh(), fresh()
     for t in range(4):
-        proj = torch.randn(B, 1, cd + vd + 2 * Hv + 6, device="cuda", generator=g).bfloat16()
+        proj = torch.randn(B, 1, cd + vd + 2 * Hv + 8, device="cuda", generator=g).bfloat16()
+        assert D._tile_ok(128, proj[..., cd:cd + vd], proj[..., cd:cd + vd]) == tile      # the z window is 8-byte aligned
         views = (proj[..., :cd], proj[..., cd:cd + vd], proj[..., cd + vd:cd + vd + Hv], proj[..., cd + vd + Hv:cd + vd + 2 * Hv])
         D._GDN_FUSED = False
         try:

@@ -11,7 +11,7 @@ from typing import Optional, Tuple
 import torch
 
 from .._native import register_signatures
-from ._common import check, cur_stream, lib, ptr
+from ._common import check, cur_stream, err_word, lib, ptr
 
 
 @register_signatures
@@ -25,6 +25,10 @@ def _sigs(lib_):
     fn = getattr(lib_, "tyr_gdr_decode_norm", None)
     if fn is not None:
         fn.argtypes = [P, P, P, P, P, P, P, I, I, I, I, I, L, L, P, L, P, ctypes.c_float, P]
+        fn.restype = ctypes.c_int
+    fn = getattr(lib_, "tyr_gdr_decode_tile", None)
+    if fn is not None:
+        fn.argtypes = [P, P, P, P, P, P, P, I, I, I, I, L, L, P, L, P, ctypes.c_float, P, P]
         fn.restype = ctypes.c_int
     fn = getattr(lib_, "tyr_gdn_conv_gates", None)
     if fn is not None:
@@ -168,6 +172,11 @@ def gdr_decode_step(q, k, v, g, beta, state: torch.Tensor) -> torch.Tensor:
             and q.stride(2) == dk and k.stride(2) == dk and v.stride(2) == dv and q.stride(0) == k.stride(0)):
         out = torch.empty((B, 1, Hv, dv), dtype=q.dtype, device=q.device)
         gc, bc = g.float().contiguous(), beta.float().contiguous()
+        if _tile_ok(dv, v, None):
+            check(lib().tyr_gdr_decode_tile(ptr(q), ptr(k), ptr(v), ptr(gc), ptr(bc), ptr(state), ptr(out), B, Hk, Hv, dk,
+                                            q.stride(0), v.stride(0), None, 0, None, 0.0, ptr(err_word(q.device)),
+                                            cur_stream(q.device)), "gdr_decode_tile")
+            return out
         check(lib().tyr_gdr_decode(ptr(q), ptr(k), ptr(v), ptr(gc), ptr(bc), ptr(state), ptr(out), B, Hk, Hv, dk, dv,
                                    q.stride(0), v.stride(0), cur_stream(q.device)), "gdr_decode")
         return out
@@ -179,6 +188,17 @@ def gdr_decode_step(q, k, v, g, beta, state: torch.Tensor) -> torch.Tensor:
 
 
 _GDN_FUSED = os.environ.get("TYR_GDN_DECODE_FUSED", "1") != "0"
+_GDR_TILE = os.environ.get("TYR_GDR_DECODE_TILE", "1") != "0"      # 0: the register-resident form of the decode step
+
+
+def _tile_ok(dv: int, v: torch.Tensor, z: Optional[torch.Tensor]) -> bool:
+    """The shared-memory tile form of the decode step: dv == 128 and 8-byte aligned v / z rows."""
+    if not (_GDR_TILE and dv == 128 and hasattr(lib(), "tyr_gdr_decode_tile")):
+        return False
+    for t in (v, z):
+        if t is not None and (t.data_ptr() % 8 or t.stride(0) % 4):
+            return False
+    return True
 
 
 def gdn_decode_fused_supported(mixed, conv_state, rec_state, dk: int, dv: int) -> bool:
@@ -215,6 +235,10 @@ def gdn_decode_fused(mixed, z, b, a, conv_state, conv_w, conv_b, dt_bias, a_log,
     q, k, v = conv_out[:, :kd], conv_out[:, kd:2 * kd], conv_out[:, 2 * kd:]
     out = torch.empty((B, 1, Hv * dv), dtype=torch.bfloat16, device=dev)
     nw = norm_w if (norm_w.dtype == torch.bfloat16 and norm_w.is_contiguous()) else norm_w.to(torch.bfloat16).contiguous()
+    if _tile_ok(dv, v, z):
+        check(lib().tyr_gdr_decode_tile(ptr(q), ptr(k), ptr(v), ptr(g), ptr(beta), ptr(rec_state), ptr(out), B, Hk, Hv, dk, cd, cd,
+                                        ptr(z), z.stride(0), ptr(nw), eps, ptr(err_word(dev)), cur_stream(dev)), "gdr_decode_tile")
+        return out
     check(lib().tyr_gdr_decode_norm(ptr(q), ptr(k), ptr(v), ptr(g), ptr(beta), ptr(rec_state), ptr(out), B, Hk, Hv, dk, dv, cd, cd,
                                     ptr(z), z.stride(0), ptr(nw), eps, cur_stream(dev)), "gdr_decode_norm")
     return out
