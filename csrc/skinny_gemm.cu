@@ -151,6 +151,37 @@ __global__ void __launch_bounds__(256) skinny_finish_kernel(SkinnyArgs a) {
 
 }  // namespace tyr
 
+// The kernels above read the activations through the L1: the eight CTAs of an SM walk the same rows of x.  A kernel with a
+// large shared-memory footprint earlier in the stream leaves the SMs split in favour of shared memory, and a kernel that
+// states no preference inherits that split.  Ask for just the shared memory that the resident CTAs need (registers and
+// threads bound their number); the rest is L1.
+template <int TILES, bool GATED>
+static void skinny_set_carveout() {
+  const int per_cta = (GATED ? 2 : 1) * tyr::kSkWarps * TILES * 16 * 8 * 4 + 1024;
+  int ctas = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctas, tyr::skinny_gemm_kernel<TILES, GATED>, tyr::kSkWarps * 32, 0) != cudaSuccess ||
+      ctas < 1)
+    return;
+  int pct = (ctas * per_cta * 100 + 227 * 1024 - 1) / (227 * 1024);
+  if (pct > 100) pct = 100;
+  cudaFuncSetAttribute(tyr::skinny_gemm_kernel<TILES, GATED>, cudaFuncAttributePreferredSharedMemoryCarveout, pct);
+}
+static void skinny_prefer_l1() {
+  static bool done[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+  if (done[dev]) return;
+  done[dev] = true;
+  const char* v = getenv("TYR_SKINNY_CARVEOUT");
+  if (v != nullptr && v[0] == '0') return;
+  skinny_set_carveout<1, false>();
+  skinny_set_carveout<2, false>();
+  skinny_set_carveout<4, false>();
+  skinny_set_carveout<1, true>();
+  skinny_set_carveout<2, true>();
+  skinny_set_carveout<4, true>();
+}
+
 // Number of CTAs the reduction should be split over for this shape (1 = no workspace needed): enough CTAs to cover the
 // SMs about three times, at least 1024 channels per split.
 extern "C" TYR_EXPORT int tyr_skinny_gemm_splits(int N, int K) {
@@ -171,6 +202,7 @@ extern "C" TYR_EXPORT int tyr_skinny_gemm_bf16(const void* x, const void* w, con
   SkinnyArgs a{(const __nv_bfloat16*)x, (const __nv_bfloat16*)w, nullptr, (const __nv_bfloat16*)bias, (__nv_bfloat16*)y, (float*)ws, ldx, ldw, ldy, M, N, K};
   const int splits = ws != nullptr ? tyr_skinny_gemm_splits(N, K) : 1;
   const dim3 grid((N + 15) / 16, splits);
+  skinny_prefer_l1();
   if (M <= 8) launch_dependent(skinny_gemm_kernel<1, false>, dim3(grid), dim3(kSkWarps * 32), 0, (cudaStream_t)stream, a);
   else if (M <= 16) launch_dependent(skinny_gemm_kernel<2, false>, dim3(grid), dim3(kSkWarps * 32), 0, (cudaStream_t)stream, a);
   else launch_dependent(skinny_gemm_kernel<4, false>, dim3(grid), dim3(kSkWarps * 32), 0, (cudaStream_t)stream, a);
@@ -192,6 +224,7 @@ extern "C" TYR_EXPORT int tyr_skinny_swiglu_bf16(const void* x, const void* wg, 
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(wg) | reinterpret_cast<uintptr_t>(wu)) & 15) return -3;
   SkinnyArgs a{(const __nv_bfloat16*)x, (const __nv_bfloat16*)wg, (const __nv_bfloat16*)wu, nullptr, (__nv_bfloat16*)y, nullptr, ldx, ldw, ldy, M, N, K};
   const dim3 grid((N + 15) / 16, 1);
+  skinny_prefer_l1();
   if (M <= 8) launch_dependent(skinny_gemm_kernel<1, true>, dim3(grid), dim3(kSkWarps * 32), 0, (cudaStream_t)stream, a);
   else if (M <= 16) launch_dependent(skinny_gemm_kernel<2, true>, dim3(grid), dim3(kSkWarps * 32), 0, (cudaStream_t)stream, a);
   else launch_dependent(skinny_gemm_kernel<4, true>, dim3(grid), dim3(kSkWarps * 32), 0, (cudaStream_t)stream, a);

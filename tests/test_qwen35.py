@@ -93,6 +93,7 @@ def test_loader_roundtrip(tmp_path):
 def test_gpu_gdr_decode_kernel_matches_recurrence(tile, dk, monkeypatch):
     """Both forms of the decode step (state tile staged in shared memory by bulk copies; state columns held in registers)."""
     monkeypatch.setattr(D, "_GDR_TILE", tile)
+    monkeypatch.setattr(D, "_GDR_TILE_MIN_TILES", 0)
     q, k, v, g, beta = _gdr_inputs(B=3, S=6, H=8, dk=dk, dv=128, device="cuda", dtype=torch.bfloat16)
     qk, kk = q[:, :, :4].contiguous(), k[:, :, :4].contiguous()
     ref, sref = D.recurrent_gated_delta_rule(qk.float().repeat_interleave(2, 2), kk.float().repeat_interleave(2, 2), v.float(), g, beta)
@@ -115,6 +116,7 @@ def test_gpu_gdn_decode_fused_matches_library_op_sequence(tile, monkeypatch):
                num_attention_heads=4, num_key_value_heads=1)
     m = Q.init(cfg, device="cuda", dtype=torch.bfloat16)
     monkeypatch.setattr(D, "_GDR_TILE", tile)
+    monkeypatch.setattr(D, "_GDR_TILE_MIN_TILES", 0)
     layer = next(l for i, l in enumerate(m.layers) if not cfg.is_full(i))
     mix = layer.mixer
     mix.conv1d_bias = (torch.randn(cfg.linear_conv_dim, device="cuda") * 0.1).bfloat16()
@@ -128,7 +130,7 @@ def test_gpu_gdn_decode_fused_matches_library_op_sequence(tile, monkeypatch):
     s_ref, s_fused = fresh(), fresh()
     for t in range(4):
         proj = torch.randn(B, 1, cd + vd + 2 * Hv + 8, device="cuda", generator=g).bfloat16()
-        assert D._tile_ok(128, proj[..., cd:cd + vd], proj[..., cd:cd + vd]) == tile      # the z window is 8-byte aligned
+        assert D._tile_ok(128, proj[..., cd:cd + vd], proj[..., cd:cd + vd], B * Hv) == tile      # the z window is 8-byte aligned
         views = (proj[..., :cd], proj[..., cd:cd + vd], proj[..., cd + vd:cd + vd + Hv], proj[..., cd + vd + Hv:cd + vd + 2 * Hv])
         D._GDN_FUSED = False
         try:

@@ -172,7 +172,7 @@ def gdr_decode_step(q, k, v, g, beta, state: torch.Tensor) -> torch.Tensor:
             and q.stride(2) == dk and k.stride(2) == dk and v.stride(2) == dv and q.stride(0) == k.stride(0)):
         out = torch.empty((B, 1, Hv, dv), dtype=q.dtype, device=q.device)
         gc, bc = g.float().contiguous(), beta.float().contiguous()
-        if _tile_ok(dv, v, None):
+        if _tile_ok(dv, v, None, B * Hv):
             check(lib().tyr_gdr_decode_tile(ptr(q), ptr(k), ptr(v), ptr(gc), ptr(bc), ptr(state), ptr(out), B, Hk, Hv, dk,
                                             q.stride(0), v.stride(0), None, 0, None, 0.0, ptr(err_word(q.device)),
                                             cur_stream(q.device)), "gdr_decode_tile")
@@ -189,11 +189,15 @@ def gdr_decode_step(q, k, v, g, beta, state: torch.Tensor) -> torch.Tensor:
 
 _GDN_FUSED = os.environ.get("TYR_GDN_DECODE_FUSED", "1") != "0"
 _GDR_TILE = os.environ.get("TYR_GDR_DECODE_TILE", "1") != "0"      # 0: the register-resident form of the decode step
+# Fewer (batch, head) tiles than this: the register-resident form.  The tile form was faster at every size measured (8 to 64
+# rows x 48 heads) once the weight-streaming GEMMs state their own shared-memory / L1 split (csrc/skinny_gemm.cu): its
+# 64 KB tiles leave the SMs configured for shared memory.
+_GDR_TILE_MIN_TILES = int(os.environ.get("TYR_GDR_TILE_MIN_TILES", "0"))
 
 
-def _tile_ok(dv: int, v: torch.Tensor, z: Optional[torch.Tensor]) -> bool:
-    """The shared-memory tile form of the decode step: dv == 128 and 8-byte aligned v / z rows."""
-    if not (_GDR_TILE and dv == 128 and hasattr(lib(), "tyr_gdr_decode_tile")):
+def _tile_ok(dv: int, v: torch.Tensor, z: Optional[torch.Tensor], tiles: int) -> bool:
+    """The shared-memory tile form of the decode step: dv == 128, 8-byte aligned v / z rows, enough tiles."""
+    if not (_GDR_TILE and dv == 128 and tiles >= _GDR_TILE_MIN_TILES and hasattr(lib(), "tyr_gdr_decode_tile")):
         return False
     for t in (v, z):
         if t is not None and (t.data_ptr() % 8 or t.stride(0) % 4):
@@ -235,7 +239,7 @@ def gdn_decode_fused(mixed, z, b, a, conv_state, conv_w, conv_b, dt_bias, a_log,
     q, k, v = conv_out[:, :kd], conv_out[:, kd:2 * kd], conv_out[:, 2 * kd:]
     out = torch.empty((B, 1, Hv * dv), dtype=torch.bfloat16, device=dev)
     nw = norm_w if (norm_w.dtype == torch.bfloat16 and norm_w.is_contiguous()) else norm_w.to(torch.bfloat16).contiguous()
-    if _tile_ok(dv, v, z):
+    if _tile_ok(dv, v, z, B * Hv):
         check(lib().tyr_gdr_decode_tile(ptr(q), ptr(k), ptr(v), ptr(g), ptr(beta), ptr(rec_state), ptr(out), B, Hk, Hv, dk, cd, cd,
                                         ptr(z), z.stride(0), ptr(nw), eps, ptr(err_word(dev)), cur_stream(dev)), "gdr_decode_tile")
         return out
