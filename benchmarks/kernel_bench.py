@@ -272,6 +272,38 @@ def bench_skinny(results):
         print(f"skinny M={M:2d} N={N:6d} K={K:5d}: ours {ours * 1e3:7.1f} us {gb / ours * 1e3:6.0f} GB/s | library {libms * 1e3:7.1f} us {gb / libms * 1e3:6.0f} GB/s", flush=True)
 
 
+def bench_decode_gemm(results, small=False):
+    """Tensor-core weight-streaming linear for 17 .. 64 rows (csrc/decode_gemm.cu) against the library GEMM and, for the
+    gated form at up to 32 rows, against the mma.sync weight-streaming kernel; Qwen3.5-27B MLP shapes, whole and halved
+    (tensor parallel over two GPUs).  Bandwidth counts the weight bytes; fraction of the measured copy bandwidth."""
+    import torch.nn.functional as F
+    from tyr_b200.ops import decode_gemm as DG
+    from tyr_b200.ops import skinny
+    dev = torch.device("cuda")
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    cases = ((32, 17408, 5120, True),) if small else ((32, 17408, 5120, True), (64, 17408, 5120, True), (32, 8704, 5120, True),
+                                                      (32, 17408, 5120, False), (32, 5120, 17408, False), (64, 5120, 17408, False),
+                                                      (32, 12288, 5120, False))
+    for M, N, K, gated in cases:
+        w = (torch.randn(N, K, device=dev) * K ** -0.5).bfloat16()
+        w2 = (torch.randn(N, K, device=dev) * K ** -0.5).bfloat16() if gated else None
+        x = torch.randn(M, K, device=dev).bfloat16()
+        it, wu = (3, 2) if small else (20, 5)
+        if gated:
+            ours = _time(lambda: DG.decode_swiglu(x, w, w2), iters=it, warmup=wu, flush=flush)
+            libms = _time(lambda: F.silu(F.linear(x, w)) * F.linear(x, w2), iters=it, warmup=wu, flush=flush)
+            old = _time(lambda: skinny.skinny_swiglu(x, w, w2), iters=it, warmup=wu, flush=flush) if M <= 32 else float("nan")
+        else:
+            ours = _time(lambda: DG.decode_linear(x, w), iters=it, warmup=wu, flush=flush)
+            libms = _time(lambda: F.linear(x, w), iters=it, warmup=wu, flush=flush)
+            old = float("nan")
+        gb = (2 if gated else 1) * N * K * 2 / 1e9
+        results.append({"kernel": "decode_gemm_" + ("swiglu" if gated else "plain"), "M": M, "N": N, "K": K, "ms": ours, "gbs": gb / ours * 1e3,
+                        "of_measured_copy": gb / ours * 1e3 / 6538.0, "lib_ms": libms, "mma_sync_ms": old})
+        print(f"decode gemm {'swiglu' if gated else 'plain '} M={M:2d} N={N:6d} K={K:5d}: ours {ours * 1e3:7.1f} us {gb / ours * 1e3:6.0f} GB/s "
+              f"({gb / ours * 1e3 / 6538.0:.2f} of measured copy) | library {libms * 1e3:7.1f} us | mma.sync kernel {old * 1e3:7.1f} us", flush=True)
+
+
 def bench_gemm_fwd_small(results):
     """The forward qkv projection of NanoChat d20 alone, few launches: the case to put under a profiler."""
     from tyr_b200.ops.gemm import gemm
@@ -421,6 +453,10 @@ def main(argv):
         bench_attention_bwd(results)
     if what in ("gdr", "all"):
         bench_gdr(results)
+    if what in ("decode-gemm", "all"):
+        bench_decode_gemm(results)
+    if what == "decode-gemm-small":
+        bench_decode_gemm(results, small=True)
     if what in ("gdr-decode", "all"):
         bench_gdr_decode(results)
     if what == "gdr-decode-small":

@@ -490,6 +490,29 @@ def test_decode_attention_matches_reference(B, Hq, Hkv, D, cap, pos, ring, windo
         assert (got.float() - want).abs().max().item() < 2e-2 * max(1.0, want.abs().max().item()), list(kw)
 
 
+@pytest.mark.parametrize("M,N,K", [(17, 512, 1024), (32, 2176, 5120), (33, 300, 192), (64, 1152, 4096), (48, 128, 64)])
+def test_decode_gemm_tensor_core_matches_reference(M, N, K):
+    """Weights on the 128-row side of tcgen05.mma, 17 .. 64 tokens on the narrow side: plain and gated, ragged row counts
+    (the last CTA's weight tile runs past N), strided output and strided weight rows."""
+    from tyr_b200.ops import decode_gemm as DG
+    g = torch.Generator().manual_seed(M * 7 + N)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
+    wcat = (torch.randn(2 * N, K + 8, generator=g) * K ** -0.5).to(torch.bfloat16).cuda()
+    wg, wu = wcat[:N, :K], wcat[N:, :K]                                # row stride K + 8: a window of a wider matrix
+    assert DG.supported(x, wg, wu, min_tiles=1) and DG.supported(x, wg, min_tiles=1)
+    ref_g, ref_u = x.float() @ wg.float().T, x.float() @ wu.float().T
+    buf = torch.zeros(M, N + 16, dtype=torch.bfloat16, device="cuda")
+    DG.decode_linear(x, wg, out=buf[:, 8:8 + N])
+    assert (buf[:, 8:8 + N].float() - ref_g).abs().max().item() < 2e-2 * max(1.0, ref_g.abs().max().item())
+    assert torch.equal(buf[:, :8], torch.zeros_like(buf[:, :8])) and torch.equal(buf[:, 8 + N:], torch.zeros_like(buf[:, 8 + N:]))
+    ref = torch.nn.functional.silu(ref_g) * ref_u
+    got = DG.decode_swiglu(x, wg, wu)
+    assert (got.float() - ref).abs().max().item() < 2e-2 * max(1.0, ref.abs().max().item())
+    from tyr_b200.ops._common import raise_on_device_error
+    torch.cuda.synchronize()
+    raise_on_device_error(x.device)
+
+
 @pytest.mark.parametrize("M,N,K", [(17, 512, 1024), (32, 2176, 5120), (25, 100, 96)])
 def test_skinny_swiglu_up_to_32_rows_and_strided_out(M, N, K):
     from tyr_b200.ops import skinny

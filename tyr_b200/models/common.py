@@ -16,6 +16,7 @@ import torch
 import torch.nn.functional as F
 
 from ..ops.gemm import gemm as _gemm
+from ..ops import decode_gemm as _decode_gemm
 from ..ops import skinny as _skinny
 from ..ops.attention import attention
 from ..ops.norm import rms_norm_weighted
@@ -50,6 +51,11 @@ def lin(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor] = None, act:
 
 def swiglu_mlp(x, gate_w, up_w, down_w):
     rows = x.numel() // x.shape[-1]
+    if rows <= _decode_gemm.MAX_ROWS and x.is_cuda and not torch.is_grad_enabled():
+        x2 = x.reshape(rows, -1)
+        if _decode_gemm.supported(x2, gate_w, up_w, min_tiles=_decode_gemm.GATED_MIN_ROW_TILES):
+            # 17 .. 64 rows and a wide MLP: weights on the 128-row side of the tensor core, SwiGLU in the epilogue
+            return lin(_decode_gemm.decode_swiglu(x2, gate_w, up_w).reshape(*x.shape[:-1], gate_w.shape[0]), down_w)
     if rows <= _skinny.MAX_ROWS and x.is_cuda and not torch.is_grad_enabled():
         x2 = x.reshape(rows, -1)
         if _skinny.swiglu_supported(x2, gate_w, up_w):          # decode: gate and up in one pass, SwiGLU in the epilogue

@@ -187,8 +187,10 @@ class TPCache:
     @staticmethod
     def _mlp_hidden(h, gate_up):
         """silu(h gate^T) * (h up^T) for the local column slice; decode-sized rows take the one-pass weight-streaming kernel."""
-        from ..ops import skinny
+        from ..ops import decode_gemm, skinny
         I = gate_up.shape[0] // 2
+        if h.is_cuda and decode_gemm.supported(h, gate_up[:I], gate_up[I:], min_tiles=decode_gemm.GATED_MIN_ROW_TILES):
+            return decode_gemm.decode_swiglu(h, gate_up[:I], gate_up[I:])
         if h.shape[0] <= skinny.MAX_ROWS and h.is_cuda and skinny.swiglu_supported(h, gate_up[:I], gate_up[I:]):
             return skinny.skinny_swiglu(h, gate_up[:I], gate_up[I:])
         return TPCache._swiglu(lin(h, gate_up))
