@@ -210,6 +210,11 @@ __device__ __forceinline__ uint32_t cluster_ctarank() {
   asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
   return r;
 }
+__device__ __forceinline__ uint32_t cluster_nctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+  return r;
+}
 // Address of the same shared-memory location in CTA `rank` of this cluster (shared::cluster window).
 __device__ __forceinline__ uint32_t mapa_shared(uint32_t cta_addr, uint32_t rank) {
   uint32_t r;

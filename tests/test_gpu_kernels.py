@@ -508,6 +508,14 @@ def test_decode_gemm_tensor_core_matches_reference(M, N, K):
     ref = torch.nn.functional.silu(ref_g) * ref_u
     got = DG.decode_swiglu(x, wg, wu)
     assert (got.float() - ref).abs().max().item() < 2e-2 * max(1.0, ref.abs().max().item())
+    # contraction split over the CTAs of a cluster, partial sums through distributed shared memory
+    for split in (1, 2, 3, 4):
+        if K // 64 < split or (split == 4 and M > 32):
+            continue
+        got = DG.decode_swiglu(x, wg, wu, split=split)
+        assert (got.float() - ref).abs().max().item() < 2e-2 * max(1.0, ref.abs().max().item()), split
+        got = DG.decode_linear(x, wg, split=split)
+        assert (got.float() - ref_g).abs().max().item() < 2e-2 * max(1.0, ref_g.abs().max().item()), split
     from tyr_b200.ops._common import raise_on_device_error
     torch.cuda.synchronize()
     raise_on_device_error(x.device)

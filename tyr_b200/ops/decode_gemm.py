@@ -29,7 +29,7 @@ def _sigs(lib_):
     P, I, L = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
     fn = getattr(lib_, "tyr_decode_gemm_bf16", None)
     if fn is not None:
-        fn.argtypes = [P, P, P, P, L, L, L, I, I, I, P, P]
+        fn.argtypes = [P, P, P, P, L, L, L, I, I, I, I, P, P]
         fn.restype = I
 
 
@@ -51,28 +51,29 @@ def supported(x2: torch.Tensor, w: torch.Tensor, w2: Optional[torch.Tensor] = No
     return _operand_ok(x2) and _operand_ok(w) and w.shape[1] == K
 
 
-def _run(x2, w, w2, out):
+def _run(x2, w, w2, out, split: int = 0):
     M, K = x2.shape
     N = w.shape[0]
     y = torch.empty((M, N), dtype=torch.bfloat16, device=x2.device) if out is None else out
     assert y.shape == (M, N) and y.dtype == torch.bfloat16 and y.stride(1) == 1
-    check(lib().tyr_decode_gemm_bf16(ptr(x2), ptr(w), ptr(w2), ptr(y), x2.stride(0), w.stride(0), y.stride(0), M, N, K,
+    check(lib().tyr_decode_gemm_bf16(ptr(x2), ptr(w), ptr(w2), ptr(y), x2.stride(0), w.stride(0), y.stride(0), M, N, K, split,
                                      ptr(err_word(x2.device)), cur_stream(x2.device)), "decode_gemm_bf16")
     return y
 
 
-def decode_linear(x2: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """x2 [17..64, K] bf16, w [N, K] bf16 (rows may be strided) -> [M, N] bf16, fp32 accumulation."""
+def decode_linear(x2: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, split: int = 0) -> torch.Tensor:
+    """x2 [17..64, K] bf16, w [N, K] bf16 (rows may be strided) -> [M, N] bf16, fp32 accumulation.  ``split``: CTAs of a
+    thread-block cluster that share one 128-row tile's contraction (0: chosen from the shape so that one wave fills the SMs)."""
     if not x2.is_cuda:
         y = (x2.float() @ w.float().T).to(x2.dtype)
         if out is not None:
             out.copy_(y)
             return out
         return y
-    return _run(x2, w, None, out)
+    return _run(x2, w, None, out, split)
 
 
-def decode_swiglu(x2: torch.Tensor, gate_w: torch.Tensor, up_w: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+def decode_swiglu(x2: torch.Tensor, gate_w: torch.Tensor, up_w: torch.Tensor, out: Optional[torch.Tensor] = None, split: int = 0) -> torch.Tensor:
     """silu(x2 gate_w^T) * (x2 up_w^T) as [M, N] bf16."""
     if not x2.is_cuda:
         y = (torch.nn.functional.silu(x2.float() @ gate_w.float().T) * (x2.float() @ up_w.float().T)).to(x2.dtype)
@@ -80,4 +81,4 @@ def decode_swiglu(x2: torch.Tensor, gate_w: torch.Tensor, up_w: torch.Tensor, ou
             out.copy_(y)
             return out
         return y
-    return _run(x2, gate_w, up_w, out)
+    return _run(x2, gate_w, up_w, out, split)
