@@ -27,6 +27,14 @@ from .._native import host, register_host_signatures
 from .sampler import DistributedSampler, DistributedSamplerConfig  # noqa: F401
 
 
+# Transport callbacks handed to the native lifecycle (csrc/host/pg_registry.cpp): it decides the order of operations,
+# these only talk to c10d.  Each returns 0, or records its error natively and returns 1; the Python exception object is
+# kept aside so that the caller can chain it.
+_RENDEZVOUS_FN = ctypes.CFUNCTYPE(ctypes.c_int, ctypes.c_void_p)
+_WAIT_FN = ctypes.CFUNCTYPE(ctypes.c_int, ctypes.c_void_p, ctypes.c_uint64)
+_SHUTDOWN_FN = ctypes.CFUNCTYPE(ctypes.c_int, ctypes.c_void_p)
+
+
 @register_host_signatures
 def _sigs(lib):
     L, U = ctypes.c_longlong, ctypes.c_uint64
@@ -47,12 +55,6 @@ def _sigs(lib):
     lib.tyr_pg_destroy.argtypes = [_WAIT_FN, _SHUTDOWN_FN, ctypes.c_void_p]
 
 
-# Transport callbacks handed to the native lifecycle (csrc/host/pg_registry.cpp): it decides the order of operations,
-# these only talk to c10d.  Each returns 0, or records its error natively and returns 1; the Python exception object is
-# kept aside so that the caller can chain it.
-_RENDEZVOUS_FN = ctypes.CFUNCTYPE(ctypes.c_int, ctypes.c_void_p)
-_WAIT_FN = ctypes.CFUNCTYPE(ctypes.c_int, ctypes.c_void_p, ctypes.c_uint64)
-_SHUTDOWN_FN = ctypes.CFUNCTYPE(ctypes.c_int, ctypes.c_void_p)
 _last_exc: List[Optional[BaseException]] = [None]
 
 

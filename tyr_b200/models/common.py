@@ -41,6 +41,10 @@ def lin(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor] = None, act:
         if _skinny.supported(x2, w):
             y = _skinny.skinny_linear(x2, w, b).reshape(*x.shape[:-1], w.shape[0])
             return F.relu(y) if act == "relu" else (F.relu(y).square() if act == "relu2" else y)
+    if rows <= _decode_gemm.MAX_ROWS and x.is_cuda and b is None and act is None and not torch.is_grad_enabled():
+        x2 = x.reshape(rows, -1)
+        if _decode_gemm.supported(x2, w):                # 17 .. 64 rows, matrices with enough 128-row tiles (ops/decode_gemm.py)
+            return _decode_gemm.decode_linear(x2, w).reshape(*x.shape[:-1], w.shape[0])
     y = F.linear(x, w.to(x.dtype), None if b is None else b.to(x.dtype))
     if act == "relu":
         y = F.relu(y)

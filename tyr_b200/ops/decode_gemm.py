@@ -17,9 +17,15 @@ from .._native import register_signatures
 from ._common import check, cur_stream, err_word, lib, ptr
 
 MIN_ROWS, MAX_ROWS = 17, 64
-# CTAs (of 128 weight rows) below which a product stays where it was.  Plain products tie with the library GEMM at 136 tiles
-# and lose below; the gated form replaces three launches and was ahead of both alternatives from 68 tiles on.
-MIN_ROW_TILES = int(os.environ.get("TYR_DECODE_GEMM_MIN_TILES", "144"))
+# CTAs (of 128 weight rows) below which a product stays where it was.  Alone, a plain product ties with the library GEMM
+# (within 3 % either way from 40 tiles on); inside a decode step it is ahead, because its weight loads start while the kernel
+# in front of it still runs: Qwen3.5-27B widths, 8 layers, batch 32: 2.19 ms per step with the library for plain products,
+# 2.10 ms from 40 tiles on, 2.11 ms from 16.  The gated form replaces three launches and is ahead of both alternatives from
+# 64 tiles on.
+MIN_ROW_TILES = int(os.environ.get("TYR_DECODE_GEMM_MIN_TILES", "40"))
+# ... and above which a plain product goes back to the library: one CTA per tile means several waves for a vocabulary-sized
+# matrix (784 tiles: the Laguna decode step was 0.4 % slower with this kernel for the lm_head than with the library).
+MAX_ROW_TILES = int(os.environ.get("TYR_DECODE_GEMM_MAX_TILES", "296"))
 GATED_MIN_ROW_TILES = int(os.environ.get("TYR_DECODE_GEMM_GATED_MIN_TILES", "64"))
 _ENABLED = os.environ.get("TYR_DECODE_GEMM", "1") != "0"
 
@@ -45,6 +51,8 @@ def supported(x2: torch.Tensor, w: torch.Tensor, w2: Optional[torch.Tensor] = No
     N = w.shape[0]
     tiles = (N + 127) // 128
     if not (MIN_ROWS <= M <= MAX_ROWS and K % 64 == 0 and K >= 64 and tiles >= (MIN_ROW_TILES if min_tiles is None else min_tiles)):
+        return False
+    if min_tiles is None and w2 is None and tiles > MAX_ROW_TILES:
         return False
     if w2 is not None and not (_operand_ok(w2) and w2.shape == w.shape and w2.stride(0) == w.stride(0)):
         return False

@@ -166,7 +166,7 @@ class TensorParallel:
         ``norm_w`` is ``None``).  On the fused path the partial product comes from the weight-streaming kernel straight into
         this rank's symmetric buffer and ONE kernel does the flag barrier, the sum over the peers' partials, the residual add
         and the norm (``tyr_tp_allreduce_norm``); otherwise it falls back to ``linear_all_reduce`` and the norm op."""
-        from ..ops import skinny
+        from ..ops import decode_gemm, skinny
         from ..ops.norm import rms_norm_weighted
         M, N = x.shape[0], w.shape[0]
         fused = (self.fused and x.dtype == torch.bfloat16 and N % 8 == 0 and N <= 8192 and M * N <= self._slots[0].numel()
@@ -179,6 +179,8 @@ class TensorParallel:
         pv = part[:M * N].view(M, N)
         if skinny.supported(x, w):
             skinny.skinny_linear(x, w, out=pv)
+        elif decode_gemm.supported(x, w):
+            decode_gemm.decode_linear(x, w, out=pv)
         else:
             torch.matmul(x, w.T, out=pv)
         bar = self.barrier
