@@ -120,11 +120,12 @@ def stage_inventory():
     for p in (ROOT / "tests").glob("test_*.py"):
         text = p.read_text()
         module_mark = re.search(r"^pytestmark\s*=.*gpu", text, re.MULTILINE) is not None
-        for m in re.finditer(r"^((?:@[^\n]+\n)*)def (test_\w+)\(", text, re.MULTILINE):
+        # decorators may continue on indented lines (a long parametrize list)
+        for m in re.finditer(r"^((?:@[^\n]+\n(?:[ \t]+[^\n]*\n)*)*)def (test_\w+)\(", text, re.MULTILINE):
             start = m.end()
             nxt = re.search(r"^(?:@|def |class )", text[start:], re.MULTILINE)
             body = text[start:start + (nxt.start() if nxt else len(text))]
-            if re.search(r"""['"]cuda|\.cuda\(\)|_dev\(\)|Device\.cuda""", body) and not module_mark and "mark.gpu" not in m.group(1) \
+            if re.search(r"""['"]cuda(?::\d+)?['"]|\.cuda\(\)|_dev\(\)|Device\.cuda""", body) and not module_mark and "mark.gpu" not in m.group(1) \
                     and "skipif" not in m.group(1) and "is_available" not in body:
                 problems.append(f"{p.relative_to(ROOT).as_posix()}::{m.group(2)} uses CUDA without the gpu marker")
     tail = "\n".join(problems) or f"{len(files)} test files, {sum(collected.values())} tests, all reachable"
