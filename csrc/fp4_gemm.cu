@@ -18,6 +18,9 @@
 //   * rows: every expert's rows start at a multiple of 128 (`128 * group_tiles[e]`, the exclusive prefix sum of
 //     ceil(rows_e / 128) the routing kernels already produce), so a row tile never straddles two experts and the scale
 //     chunks line up with the tiles.  Padding rows are computed and ignored.
+//   * fixed-slot form (at most 128 tokens): expert e owns the padded rows [128 e, 128 e + 128), a row takes its slot with
+//     one atomic on the expert's cursor (fp4_scatter_quantize_fixed_kernel) and the GEMM reads the cursors as row counts
+//     (`group_tiles == nullptr`): its tile table counts only the experts that have rows.
 //
 // Kernel: persistent, 320 threads: warp 0 TMA producer (5 stages of 36 KB), warp 1 MMA issuer (scale copies + four
 // K = 64 MMAs per stage, double-buffered 128-column accumulator), warps 2-9 epilogue.  Epilogues:
@@ -25,7 +28,9 @@
 //   mode 1  SwiGLU over the tile's column halves (64 gate | 64 up rows interleaved at load time), then re-quantisation
 //           of the 64 results to NVFP4 (values + scale bytes in the layout above): the down projection consumes them
 //           without another pass.
-// Every wait is bounded; a timeout records an error and unwinds through the normal teardown.
+// Every wait is bounded; a timeout records an error and unwinds through the normal teardown.  The kernel is launched as a
+// programmatic dependent: barrier init, TMEM allocation and (when every expert is expected to have rows) an L2 prefetch of
+// the first tiles' weights run before it waits for the kernel that produces its activations and row counts.
 //
 // The reference reaches a block-scaled tensor-core product only through cuBLASLt and only on compute capability 12
 // (cc/src/tyr_laguna_moe.cu:839-982, gate at :1317-1319; scale order :612-627; activation quantisation :678-728;
