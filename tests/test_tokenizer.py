@@ -62,3 +62,44 @@ def test_chat_templates():
     assert tk.chatml_prompt(msgs, system="be brief").startswith("<|im_start|>system\nbe brief<|im_end|>\n")
     assert tk.chatml_prompt(msgs, enable_thinking=False).endswith("<think>\n\n</think>\n\n")
     assert tk.gemma_prompt(msgs) == "<bos><start_of_turn>user\nhi<end_of_turn>\n<start_of_turn>model\n"
+
+
+def test_native_bpe_loops_equal_the_python_loops(monkeypatch):
+    """Merge training and chunk encoding in csrc/host/bpe.cpp against the Python loops: same merges (ties included), same ids,
+    on random corpora with multi-byte characters, runs of one character (overlapping pairs) and special tokens."""
+    import random
+    from tyr_b200.tokenizer import bpe
+    if bpe._host() is None:
+        pytest.skip("host library not built")
+    rng = random.Random(3)
+    alpha = "abcdeé中 \n0123,.!'xyzAB"
+    def corpus(n, L):
+        return ["".join(rng.choice(alpha) * rng.choice([1, 1, 1, 2, 3]) for _ in range(rng.randint(1, L))) for _ in range(n)]
+    for trial in range(8):
+        docs = corpus(rng.randint(1, 30), rng.randint(1, 50))
+        vocab = 256 + 1 + rng.randint(0, 100)
+        monkeypatch.setattr(bpe, "_NATIVE", True)
+        a = bpe.train_bpe(docs, vocab, ["<|bos|>"])
+        monkeypatch.setattr(bpe, "_NATIVE", False)
+        b = bpe.train_bpe(docs, vocab, ["<|bos|>"])
+        assert [(m.left, m.right, m.result) for m in a.merges] == [(m.left, m.right, m.result) for m in b.merges], trial
+        assert a.id_to_bytes == b.id_to_bytes and a.special_tokens == b.special_tokens
+        texts = corpus(12, 60) + ["", "<|bos|>x<|bos|>", "éé中中", "aaaaaaa"]
+        monkeypatch.setattr(bpe, "_NATIVE", True)
+        ids_native = [a.encode(t) for t in texts]
+        assert a._handle is not None or not a.merges                     # the native table was really used
+        monkeypatch.setattr(bpe, "_NATIVE", False)
+        ids_python = [b.encode(t) for t in texts]
+        assert ids_native == ids_python, trial
+        assert all(a.decode(e) == t for e, t in zip(ids_native, texts))
+
+
+def test_native_bpe_reports_a_byte_without_a_token(monkeypatch):
+    from tyr_b200.tokenizer import bpe
+    if bpe._host() is None:
+        pytest.skip("host library not built")
+    monkeypatch.setattr(bpe, "_NATIVE", True)
+    tok = bpe.BPETokenizer([bytes([i]) if i != ord("q") else b"" for i in range(256)] + [b"ab"], [bpe.MergeRule(ord("a"), ord("b"), 256)])
+    assert tok.encode("abab") == [256, 256]
+    with pytest.raises(KeyError):
+        tok.encode("aqb")

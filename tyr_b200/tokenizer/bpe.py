@@ -4,9 +4,15 @@ special tokens, the GPT-4 split pattern (IO.lean:23), the `TYR_BPE1` binary form
 magic, u32 version / vocab / merges / specials, u16-length-prefixed token bytes, u32 merge triples,
 specials as u16 length + utf-8 + u32 id) and the bytes-per-token table used for bits-per-byte
 evaluation (TokenBytes.lean:25-135).
+
+The two hot loops - encoding pre-tokenised chunks against the merge table and the merge training itself - run in native code
+(csrc/host/bpe.cpp) with exactly the semantics of the Python loops below, which remain as the fallback and the oracle of the
+tests (``TYR_BPE_NATIVE=0`` selects them).
 """
 from __future__ import annotations
 
+import ctypes
+import os
 import struct
 from collections import Counter
 from dataclasses import dataclass, field
@@ -24,6 +30,39 @@ GPT4_SPLIT_PATTERN = (r"'(?i:[sdmt]|ll|ve|re)|[^\r\n\p{L}\p{N}]?+\p{L}+|\p{N}{1,
                       r"\s*[\r\n]|\s+(?!\S)|\s+")
 DEFAULT_SPECIAL_TOKENS = ["<|bos|>", "<|user_start|>", "<|user_end|>", "<|assistant_start|>", "<|assistant_end|>",
                           "<|python_start|>", "<|python_end|>", "<|output_start|>", "<|output_end|>"]
+
+
+_NATIVE = os.environ.get("TYR_BPE_NATIVE", "1") != "0"
+_native_lib = None
+
+
+def _host():
+    """libtyr_host.so with the BPE entry points declared, or None when it cannot be loaded or predates them."""
+    global _native_lib
+    if _native_lib is None:
+        try:
+            from .._native import host
+            lib = host()
+            P, L, I = ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int
+            lib.tyr_bpe_new.argtypes, lib.tyr_bpe_new.restype = [P, P, P, L, P], P
+            lib.tyr_bpe_free.argtypes, lib.tyr_bpe_free.restype = [P], None
+            lib.tyr_bpe_encode_chunks.argtypes, lib.tyr_bpe_encode_chunks.restype = [P, P, P, L, P, P, I], L
+            lib.tyr_bpe_train.argtypes, lib.tyr_bpe_train.restype = [P, P, P, L, L, ctypes.c_int32, P, P], L
+            _native_lib = lib
+        except Exception:
+            _native_lib = False
+    return _native_lib or None
+
+
+def _pack_chunks(chunks: Sequence[bytes]):
+    """Concatenated bytes and the int64 offsets array (n + 1 entries) of a list of byte strings."""
+    offsets = (ctypes.c_longlong * (len(chunks) + 1))()
+    total = 0
+    for i, c in enumerate(chunks):
+        offsets[i] = total
+        total += len(c)
+    offsets[len(chunks)] = total
+    return b"".join(chunks), offsets, total
 
 
 def pretokenize(text: str, pattern: str = GPT4_SPLIT_PATTERN) -> List[str]:
@@ -49,6 +88,41 @@ class BPETokenizer:
         self.merge_lookup = {(m.left, m.right): m.result for m in self.merges}
         self.merge_priority = {(m.left, m.right): i for i, m in enumerate(self.merges)}
         self._cache: Dict[str, List[int]] = {}
+        self._handle = None                 # native merge table, built on first use
+
+    def __del__(self):
+        h, lib = getattr(self, "_handle", None), _native_lib
+        if h and lib:
+            lib.tyr_bpe_free(h)
+            self._handle = None
+
+    def _native_handle(self):
+        if self._handle is None and _NATIVE:
+            lib = _host()
+            if lib is None:
+                return None
+            n = len(self.merges)
+            arr = lambda vals: (ctypes.c_int32 * max(1, n))(*vals)
+            b2i = (ctypes.c_int32 * 256)(*[self.bytes_to_id.get(bytes([b]), -1) for b in range(256)])
+            self._handle = lib.tyr_bpe_new(arr(m.left for m in self.merges), arr(m.right for m in self.merges),
+                                           arr(m.result for m in self.merges), n, b2i) or None
+        return self._handle
+
+    def _encode_chunks_native(self, chunks: List[str]) -> Optional[List[List[int]]]:
+        """Ids of every chunk through the native loop, or None when the library is not available."""
+        h = self._native_handle()
+        if h is None:
+            return None
+        raw = [c.encode("utf-8") for c in chunks]
+        data, offsets, total = _pack_chunks(raw)
+        out = (ctypes.c_int32 * max(1, total))()
+        counts = (ctypes.c_longlong * max(1, len(raw)))()
+        rc = _native_lib.tyr_bpe_encode_chunks(h, data, offsets, len(raw), out, counts, min(8, os.cpu_count() or 1))
+        if rc != 0:
+            if rc > 0:
+                raise KeyError(f"chunk {chunks[rc - 1]!r} holds a byte without a token")
+            return None
+        return [out[offsets[i]:offsets[i] + counts[i]] for i in range(len(raw))]
 
     @property
     def vocab_size(self) -> int:
@@ -87,8 +161,23 @@ class BPETokenizer:
         return ids
 
     def encode_ordinary(self, text: str) -> List[int]:
-        out: List[int] = []
-        for chunk in pretokenize(text, self.pattern):
+        chunks = pretokenize(text, self.pattern)
+        if _NATIVE and self.merges:
+            # the chunks this tokenizer has not seen go to the native loop in one call
+            new = [c for c in dict.fromkeys(chunks) if c not in self._cache]
+            if new:
+                ids = self._encode_chunks_native(new)
+                if ids is not None:
+                    room = 200000 - len(self._cache)
+                    fresh = dict(zip(new, ids))
+                    for c in new[:max(0, room)]:
+                        self._cache[c] = fresh[c]
+                    out: List[int] = []
+                    for c in chunks:
+                        out.extend(self._cache[c] if c in self._cache else fresh[c])
+                    return out
+        out = []
+        for chunk in chunks:
             out.extend(self._encode_chunk(chunk))
         return out
 
@@ -232,6 +321,21 @@ def train_bpe(texts: Iterable[str], vocab_size: int, special_tokens: Optional[Se
             t = t[:max_chars - seen]
         seen += len(t)
         words.update(pretokenize(t, pattern))
+    lib = _host() if _NATIVE else None
+    if lib is not None and n_merges > 0 and words:
+        raw = [w.encode("utf-8") for w in words]
+        data, offsets, _ = _pack_chunks(raw)
+        fr = (ctypes.c_longlong * len(raw))(*[words[w] for w in words])
+        left, right = (ctypes.c_int32 * n_merges)(), (ctypes.c_int32 * n_merges)()
+        made = lib.tyr_bpe_train(data, offsets, fr, len(raw), n_merges, 256, left, right)
+        if made >= 0:
+            id_to_bytes = [bytes([i]) for i in range(256)]
+            merges = []
+            for j in range(made):
+                id_to_bytes.append(id_to_bytes[left[j]] + id_to_bytes[right[j]])
+                merges.append(MergeRule(left[j], right[j], 256 + j))
+            special_map = {s: len(id_to_bytes) + i for i, s in enumerate(specials)}
+            return BPETokenizer(id_to_bytes, merges, special_map, pattern)
     seqs = [list(w.encode("utf-8")) for w in words]
     freqs = [words[w] for w in words]
     pair_counts: Counter = Counter()
