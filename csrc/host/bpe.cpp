@@ -123,6 +123,24 @@ TYR_HOST_EXPORT long long tyr_bpe_encode_chunks(const TyrBpe* t, const uint8_t* 
   return first < 0 ? 0 : 1 + first;
 }
 
+// The same encoding with the ids of all chunks written back to back at the start of `out` (room for offsets[n_chunks] ids);
+// returns their number, -1 on a null argument, or -(2 + i) when chunk i holds a byte without a token.
+TYR_HOST_EXPORT long long tyr_bpe_encode_concat(const TyrBpe* t, const uint8_t* bytes, const long long* offsets, long long n_chunks,
+                                                int32_t* out, int threads) {
+  if (t == nullptr || offsets == nullptr || n_chunks < 0 || (n_chunks > 0 && (bytes == nullptr || out == nullptr))) return -1;
+  std::vector<long long> counts(static_cast<size_t>(n_chunks > 0 ? n_chunks : 1));
+  const long long rc = tyr_bpe_encode_chunks(t, bytes, offsets, n_chunks, out, counts.data(), threads);
+  if (rc < 0) return -1;
+  if (rc > 0) return -(1 + rc);
+  long long w = 0;
+  for (long long i = 0; i < n_chunks; ++i) {
+    const long long c = counts[static_cast<size_t>(i)];
+    if (w != offsets[i]) std::copy(out + offsets[i], out + offsets[i] + c, out + w);     // moves left: ranges never clobber
+    w += c;
+  }
+  return w;
+}
+
 // Word i is the byte string bytes[offsets[i], offsets[i + 1]) seen freqs[i] times.  New token ids start at `first_id`
 // (256 for a byte-level vocabulary whose byte b has id b).  Writes up to max_merges rules to out_left / out_right (rule j
 // creates id first_id + j) and returns how many were made, or -1 on a bad argument.

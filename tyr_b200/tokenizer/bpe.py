@@ -47,6 +47,7 @@ def _host():
             lib.tyr_bpe_new.argtypes, lib.tyr_bpe_new.restype = [P, P, P, L, P], P
             lib.tyr_bpe_free.argtypes, lib.tyr_bpe_free.restype = [P], None
             lib.tyr_bpe_encode_chunks.argtypes, lib.tyr_bpe_encode_chunks.restype = [P, P, P, L, P, P, I], L
+            lib.tyr_bpe_encode_concat.argtypes, lib.tyr_bpe_encode_concat.restype = [P, P, P, L, P, I], L
             lib.tyr_bpe_train.argtypes, lib.tyr_bpe_train.restype = [P, P, P, L, L, ctypes.c_int32, P, P], L
             _native_lib = lib
         except Exception:
@@ -108,22 +109,6 @@ class BPETokenizer:
                                            arr(m.result for m in self.merges), n, b2i) or None
         return self._handle
 
-    def _encode_chunks_native(self, chunks: List[str]) -> Optional[List[List[int]]]:
-        """Ids of every chunk through the native loop, or None when the library is not available."""
-        h = self._native_handle()
-        if h is None:
-            return None
-        raw = [c.encode("utf-8") for c in chunks]
-        data, offsets, total = _pack_chunks(raw)
-        out = (ctypes.c_int32 * max(1, total))()
-        counts = (ctypes.c_longlong * max(1, len(raw)))()
-        rc = _native_lib.tyr_bpe_encode_chunks(h, data, offsets, len(raw), out, counts, min(8, os.cpu_count() or 1))
-        if rc != 0:
-            if rc > 0:
-                raise KeyError(f"chunk {chunks[rc - 1]!r} holds a byte without a token")
-            return None
-        return [out[offsets[i]:offsets[i] + counts[i]] for i in range(len(raw))]
-
     @property
     def vocab_size(self) -> int:
         return max(len(self.id_to_bytes), max(self.special_tokens.values(), default=-1) + 1)
@@ -162,20 +147,17 @@ class BPETokenizer:
 
     def encode_ordinary(self, text: str) -> List[int]:
         chunks = pretokenize(text, self.pattern)
-        if _NATIVE and self.merges:
-            # the chunks this tokenizer has not seen go to the native loop in one call
-            new = [c for c in dict.fromkeys(chunks) if c not in self._cache]
-            if new:
-                ids = self._encode_chunks_native(new)
-                if ids is not None:
-                    room = 200000 - len(self._cache)
-                    fresh = dict(zip(new, ids))
-                    for c in new[:max(0, room)]:
-                        self._cache[c] = fresh[c]
-                    out: List[int] = []
-                    for c in chunks:
-                        out.extend(self._cache[c] if c in self._cache else fresh[c])
-                    return out
+        if _NATIVE and self.merges and chunks:
+            h = self._native_handle()
+            if h is not None:            # every chunk through the native loop, ids back to back: no per-chunk Python work
+                raw = [c.encode("utf-8") for c in chunks]
+                data, offsets, total = _pack_chunks(raw)
+                buf = (ctypes.c_int32 * max(1, total))()
+                n = _native_lib.tyr_bpe_encode_concat(h, data, offsets, len(raw), buf, min(8, os.cpu_count() or 1))
+                if n <= -2:
+                    raise KeyError(f"chunk {chunks[-n - 2]!r} holds a byte without a token")
+                if n >= 0:
+                    return buf[:n]
         out = []
         for chunk in chunks:
             out.extend(self._encode_chunk(chunk))
